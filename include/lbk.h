@@ -1,0 +1,164 @@
+/*
+ * lbk — B200 (sm_100a) kernels for lemonade-burn's packed 2-bit ternary x int8 matmul path.
+ *
+ * Plain C ABI: pointers and sizes only. Every entry point returns an lbk_status; nothing
+ * throws or aborts across the boundary. `lbk_last_error()` gives the message of the last
+ * failure on the calling thread. The reference (Rust) panics via assert! on shape/dtype
+ * mismatch (crates/lb-ternary/src/pack.rs:40, gemm.rs:129-134,197-200;
+ * crates/lb-model/src/ops.rs:232,303-308): a binding turns a non-zero status into the same
+ * panic / Err.
+ *
+ * Layout contract (crates/lb-ternary/src/pack.rs:1-24): a weight matrix W[rows, cols] is
+ * row-major packed, cols padded to a multiple of 128; each 128-weight block is 32 bytes;
+ * byte j of a block holds in bits 2k..2k+1 the code (w + 1) of column block*128 + k*32 + j.
+ * One f32 scale per matrix = 1 / mean|W|. Activations are f32 [m, cols] row-major.
+ * Outputs are [m, rows] row-major (x @ W^T), as in gemm.rs:117.
+ *
+ * Threading: one caller thread at a time per context (the reference drives its kernels from
+ * one model thread, crates/lb-server/src/main.rs:385-387). Device-pointer entry points are
+ * asynchronous on the given stream; host-pointer entry points synchronise before returning.
+ */
+#ifndef LBK_H
+#define LBK_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum lbk_status {
+    LBK_OK = 0,
+    LBK_ERR_INVALID = 1,     /* null pointer, bad handle, bad count */
+    LBK_ERR_SHAPE = 2,       /* a shape/length the reference would assert on */
+    LBK_ERR_CUDA = 3,        /* a CUDA runtime/driver call failed */
+    LBK_ERR_UNSUPPORTED = 4, /* valid request outside what the kernels cover (size limits) */
+    LBK_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up; results are invalid */
+    LBK_ERR_NOMEM = 6
+} lbk_status;
+
+typedef struct lbk_ctx lbk_ctx;       /* one per device; owns scratch and the error word   */
+typedef struct lbk_weight lbk_weight; /* a packed ternary matrix resident in device memory */
+typedef struct lbk_plan lbk_plan;     /* a recorded sequence of fused ternary-linear groups */
+
+#define LBK_MAX_GROUP 4   /* matrices sharing one input in a fused call (q/k/v, gate/up)  */
+#define LBK_GEMV_MAX_M 16 /* token rows served by the bandwidth-bound GEMV kernel         */
+
+/* Message of the last failure on this thread ("" if none). Never NULL. */
+const char *lbk_last_error(void);
+/* ABI version, bumped on any signature change. */
+int lbk_abi_version(void);
+
+/* ---- context --------------------------------------------------------------------------- */
+
+/* Creates a context on CUDA device `device`. Fails with LBK_ERR_UNSUPPORTED unless the
+ * device is compute capability 10.x. No counterpart in the reference (CPU only). */
+int lbk_init(int device, lbk_ctx **out);
+int lbk_destroy(lbk_ctx *ctx);
+/* Reads and clears the device-side error word (set when a bounded wait inside a kernel gave
+ * up). Synchronises the device. Returns LBK_OK or LBK_ERR_TIMEOUT. */
+int lbk_check_device_error(lbk_ctx *ctx);
+/* Number of kernel launches this context has issued since creation (benchmark bookkeeping). */
+uint64_t lbk_launch_count(const lbk_ctx *ctx);
+
+/* ---- layout helpers: crates/lb-ternary/src/pack.rs:22-24,83-85 -------------------------- */
+
+size_t lbk_padded_cols(size_t cols);
+size_t lbk_row_bytes(size_t cols);
+
+/* ---- weights: TernaryView::new / PackedTernary (pack.rs:28-81) -------------------------- */
+
+/* Copies `packed` (rows * lbk_row_bytes(cols) bytes, host) to the device. packed_len must
+ * equal that product (pack.rs:40 asserts the same) else LBK_ERR_SHAPE. */
+int lbk_weight_upload(lbk_ctx *ctx, size_t rows, size_t cols, const uint8_t *packed,
+                      size_t packed_len, float scale, lbk_weight **out);
+/* Borrows device memory that already holds the packed rows (pitch = lbk_row_bytes(cols),
+ * 16-byte aligned base), e.g. a slice of a safetensors buffer copied to the GPU, or a
+ * contiguous row range of another matrix (how the reference splits rows across memory
+ * domains, crates/lb-model/src/ops.rs:255-297). The caller keeps ownership. */
+int lbk_weight_wrap(lbk_ctx *ctx, size_t rows, size_t cols, const void *packed_dev, float scale,
+                    lbk_weight **out);
+int lbk_weight_free(lbk_weight *w);
+size_t lbk_weight_rows(const lbk_weight *w);
+size_t lbk_weight_cols(const lbk_weight *w);
+float lbk_weight_scale(const lbk_weight *w);
+const void *lbk_weight_data(const lbk_weight *w); /* device pointer */
+
+/* ---- host-pointer entry points: one per public function of lb-ternary -------------------
+ * All buffers are HOST memory; the call copies in, runs the CUDA kernels, copies out and
+ * synchronises. These are what a drop-in binding of the Rust functions calls. */
+
+/* quantize_acts (crates/lb-ternary/src/quant.rs:37-75). x: f32 [m, k]. q: int8
+ * [m, lbk_padded_cols(k)] zero padded; scale[m] = 127/max|x|; sum[m] = sum of q. */
+int lbk_quantize_acts(lbk_ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
+                      int32_t *sum);
+
+/* ternary_gemm_i32 (crates/lb-ternary/src/gemm.rs:95-114). q: int8 [m, padded_cols],
+ * sum: i32 [m]. out: i32 [m, rows], exact. */
+int lbk_ternary_gemm_i32(lbk_ctx *ctx, const lbk_weight *w, const int8_t *q, const int32_t *sum,
+                         size_t m, int32_t *out);
+
+/* ternary_gemm_multi (gemm.rs:128-195; ternary_gemm :117 is n == 1). n <= LBK_MAX_GROUP
+ * matrices of equal cols share q. outs[i]: f32 [m, rows_i] =
+ * (float)dot * (1.0f / (scale[t] * wscale_i)), bit-identical to separate calls. */
+int lbk_ternary_gemm_multi(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, const int8_t *q,
+                           const float *scale, const int32_t *sum, size_t m, float *const *outs);
+
+/* The fused op of crates/lb-model/src/ops.rs:301-329 (ternary_linear / ternary_linear2 /
+ * ternary_linear3 for n = 1, 2, 3) on HOST buffers: x f32 [m, cols]; outs[i] f32
+ * [m, rows_i]; iouts (may be NULL, entries may be NULL) receives the exact int32 dots. */
+int lbk_ternary_linear_host(lbk_ctx *ctx, const float *x, size_t m, const lbk_weight *const *ws,
+                            size_t n, float *const *outs, int32_t *const *iouts);
+
+/* bf16_gemv (crates/lb-ternary/src/bf16.rs:14-27) on HOST buffers. w: bf16 bits
+ * [rows, cols]; x f32 [cols]; out f32 [rows]. Float: summation order differs from the
+ * reference's 8-lane order, agreement is to rounding (bf16.rs:113-136 allows 1e-4 abs). */
+int lbk_bf16_gemv_host(lbk_ctx *ctx, const uint16_t *w, size_t rows, size_t cols, const float *x,
+                       float *out);
+
+/* ---- device-pointer entry points (the fast path; asynchronous on `stream`) --------------
+ * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream). */
+
+/* ops.rs:301-329 with everything resident: per-token absmax int8 quantisation, the packed
+ * ternary x int8 dot in int32, and the 1/(s_a*s_w) epilogue. m <= LBK_GEMV_MAX_M runs one
+ * fused bandwidth-bound kernel; larger m runs quantise + the tcgen05 int8 GEMM.
+ * x_dev: f32 [m, cols] (16-byte aligned); outs_dev[i]: f32 [m, rows_i]; iouts_dev may be NULL. */
+int lbk_ternary_linear_n(lbk_ctx *ctx, const float *x_dev, size_t m, const lbk_weight *const *ws,
+                         size_t n, float *const *outs_dev, int32_t *const *iouts_dev,
+                         void *stream);
+
+/* quantize_acts (quant.rs:37-75) device to device. q_dev: int8 [m, padded_cols(k)]. */
+int lbk_quantize_acts_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_t k, int8_t *q_dev,
+                          float *scale_dev, int32_t *sum_dev, void *stream);
+
+/* ternary_gemm_multi (gemm.rs:128-195) on already quantised device inputs. */
+int lbk_ternary_gemm_dev(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, const int8_t *q_dev,
+                         const float *scale_dev, const int32_t *sum_dev, size_t m,
+                         float *const *outs_dev, int32_t *const *iouts_dev, void *stream);
+
+/* bf16_linear (crates/lb-model/src/ops.rs:199-218): x f32 [m, cols] @ W^T, W bf16
+ * [rows, cols] -> out f32 [m, rows], all device memory. */
+int lbk_bf16_linear(lbk_ctx *ctx, const float *x_dev, size_t m, const uint16_t *w_dev, size_t rows,
+                    size_t cols, float *out_dev, void *stream);
+
+/* ---- plans: a whole decode-like sequence in one launch -----------------------------------
+ * The reference runs 4 fused ternary ops per layer x 30 layers = 120 parallel regions per
+ * token (crates/lb-ternary/benches/kbench.rs:148-194, crates/lb-model/src/model.rs:331-366).
+ * A plan records such a sequence once and replays it with a single persistent-kernel
+ * launch. Groups in a plan must not read each other's outputs unless `barrier` is set on
+ * the reading group. */
+int lbk_plan_create(lbk_ctx *ctx, lbk_plan **out);
+/* Appends one fused group (same meaning as lbk_ternary_linear_n with m == 1). */
+int lbk_plan_add(lbk_plan *plan, const float *x_dev, const lbk_weight *const *ws, size_t n,
+                 float *const *outs_dev, int32_t *const *iouts_dev);
+int lbk_plan_finalize(lbk_plan *plan);
+int lbk_plan_run(lbk_plan *plan, void *stream);
+/* Packed weight bytes one run streams (the figure kbench reports bandwidth on, kbench.rs:61). */
+size_t lbk_plan_weight_bytes(const lbk_plan *plan);
+int lbk_plan_destroy(lbk_plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LBK_H */

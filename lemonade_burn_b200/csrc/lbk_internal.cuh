@@ -1,0 +1,94 @@
+// Internal declarations shared by the lbk translation units (not part of the C ABI).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#include "lbk.h"
+
+namespace lbk {
+
+constexpr int kBlock = 128;      // weights per packed block (pack.rs:18)
+constexpr int kBlockBytes = 32;  // bytes per packed block   (pack.rs:19)
+
+// ---- error plumbing ------------------------------------------------------------------
+void set_error(const char *fmt, ...);
+int fail(int status, const char *fmt, ...);
+
+#define LBK_CUDA(expr)                                                                       \
+    do {                                                                                     \
+        cudaError_t e__ = (expr);                                                            \
+        if (e__ != cudaSuccess)                                                              \
+            return ::lbk::fail(LBK_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,                 \
+                               cudaGetErrorString(e__), __FILE__, __LINE__);                 \
+    } while (0)
+
+#define LBK_TRY(expr)                \
+    do {                             \
+        int s__ = (expr);            \
+        if (s__ != LBK_OK) return s__; \
+    } while (0)
+
+// ---- handles -------------------------------------------------------------------------
+struct Ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    int *err_word = nullptr;     // device: non-zero once a bounded wait gave up
+    uint64_t launches = 0;
+    // grow-only device scratch for the host-pointer entry points and the GEMM pre-pass
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    cudaStream_t own_stream = nullptr;  // used by the host-pointer entry points
+};
+
+struct Weight {
+    Ctx *ctx = nullptr;
+    size_t rows = 0, cols = 0, kp = 0, rb = 0;
+    const uint8_t *data = nullptr;  // device
+    bool owned = false;
+    float scale = 1.0f;
+    alignas(64) CUtensorMap tmap_gemv;  // box [16 rows][128 B], SWIZZLE_128B
+    alignas(64) CUtensorMap tmap_gemm;  // box [128 rows][32 B], no swizzle (GEMM expander)
+};
+
+int ctx_scratch(Ctx *ctx, size_t bytes, void **out);
+// One-time per-context kernel attribute set-up (opt-in shared memory sizes).
+int kernels_init(Ctx *ctx);
+int gemv_init(Ctx *ctx);
+int gemm_init(Ctx *ctx);
+int encode_weight_maps(Weight *w);
+
+// ---- launchers -----------------------------------------------------------------------
+struct GroupArgs {
+    const Weight *w[LBK_MAX_GROUP];
+    float *out[LBK_MAX_GROUP];
+    int32_t *iout[LBK_MAX_GROUP];
+    int n = 0;
+    size_t m = 0;
+    // exactly one of x (f32, quantised inside the kernel) or q/scale/sum is set
+    const float *x = nullptr;
+    const int8_t *q = nullptr;
+    const float *qscale = nullptr;
+    const int32_t *qsum = nullptr;
+};
+
+// Fused GEMV kernel (m <= LBK_GEMV_MAX_M). Returns LBK_ERR_UNSUPPORTED when the quantised
+// activations do not fit in shared memory next to the weight ring.
+int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
+bool gemv_fits(const Ctx *ctx, size_t kp, size_t m);
+
+int launch_quantize(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
+                    int32_t *sum, cudaStream_t stream);
+
+// tcgen05 int8 GEMM on quantised inputs (any m).
+int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
+
+int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows,
+                       size_t cols, float *out, cudaStream_t stream);
+
+}  // namespace lbk

@@ -1,0 +1,119 @@
+// Plans: a recorded decode-like sequence of fused ternary-linear groups replayed as one
+// unit. Stands in for the reference's per-token loop of 120 parallel regions
+// (crates/lb-ternary/benches/kbench.rs:148-194, crates/lb-model/src/model.rs:331-366).
+#include <new>
+#include <vector>
+
+#include "lbk_internal.cuh"
+
+namespace lbk {
+
+struct Plan {
+    Ctx *ctx = nullptr;
+    std::vector<GroupArgs> groups;
+    size_t weight_bytes = 0;
+    bool finalized = false;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+};
+
+int kernels_init(Ctx *ctx) {
+    LBK_TRY(gemv_init(ctx));
+    LBK_TRY(gemm_init(ctx));
+    return LBK_OK;
+}
+
+}  // namespace lbk
+
+using namespace lbk;
+
+extern "C" {
+
+int lbk_plan_create(lbk_ctx *c, lbk_plan **out) {
+    if (!c || !out) return fail(LBK_ERR_INVALID, "lbk_plan_create: null argument");
+    Plan *p = new (std::nothrow) Plan();
+    if (!p) return fail(LBK_ERR_NOMEM, "out of host memory");
+    p->ctx = reinterpret_cast<Ctx *>(c);
+    *out = reinterpret_cast<lbk_plan *>(p);
+    return LBK_OK;
+}
+
+int lbk_plan_add(lbk_plan *pl, const float *x_dev, const lbk_weight *const *ws, size_t n, float *const *outs_dev,
+                 int32_t *const *iouts_dev) {
+    if (!pl) return fail(LBK_ERR_INVALID, "plan is null");
+    Plan *p = reinterpret_cast<Plan *>(pl);
+    if (p->finalized) return fail(LBK_ERR_INVALID, "plan is already finalized");
+    if (!ws || n < 1 || n > LBK_MAX_GROUP) return fail(LBK_ERR_INVALID, "group of %zu matrices (1..%d allowed)", n, LBK_MAX_GROUP);
+    if (!x_dev || !outs_dev) return fail(LBK_ERR_INVALID, "lbk_plan_add: null buffer");
+    GroupArgs g;
+    g.n = static_cast<int>(n);
+    g.m = 1;
+    g.x = x_dev;
+    for (size_t i = 0; i < n; ++i) {
+        const Weight *w = reinterpret_cast<const Weight *>(ws[i]);
+        if (!w || w->ctx != p->ctx) return fail(LBK_ERR_INVALID, "matrix %zu is null or belongs to another context", i);
+        if (w->cols != reinterpret_cast<const Weight *>(ws[0])->cols) return fail(LBK_ERR_SHAPE, "inner dimension mismatch in group");
+        if (!outs_dev[i]) return fail(LBK_ERR_INVALID, "output %zu is null", i);
+        g.w[i] = w;
+        g.out[i] = outs_dev[i];
+        g.iout[i] = iouts_dev ? iouts_dev[i] : nullptr;
+        p->weight_bytes += w->rows * w->rb;
+    }
+    if (!gemv_fits(p->ctx, g.w[0]->kp, 1)) return fail(LBK_ERR_UNSUPPORTED, "%zu columns do not fit the decode kernel", g.w[0]->cols);
+    p->groups.push_back(g);
+    return LBK_OK;
+}
+
+int lbk_plan_finalize(lbk_plan *pl) {
+    if (!pl) return fail(LBK_ERR_INVALID, "plan is null");
+    Plan *p = reinterpret_cast<Plan *>(pl);
+    if (p->finalized) return LBK_OK;
+    Ctx *ctx = p->ctx;
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    if (!p->groups.empty()) {
+        cudaStream_t st = ctx->own_stream;
+        LBK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        int status = LBK_OK;
+        const uint64_t before = ctx->launches;
+        for (const GroupArgs &g : p->groups) {
+            status = launch_gemv(ctx, g, st);
+            if (status != LBK_OK) break;
+        }
+        ctx->launches = before;  // recording is not launching
+        cudaGraph_t graph = nullptr;
+        cudaError_t e = cudaStreamEndCapture(st, &graph);
+        if (status != LBK_OK) {
+            if (graph) cudaGraphDestroy(graph);
+            return status;
+        }
+        if (e != cudaSuccess) return fail(LBK_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(e));
+        p->graph = graph;
+        LBK_CUDA(cudaGraphInstantiate(&p->exec, graph, 0));
+    }
+    p->finalized = true;
+    return LBK_OK;
+}
+
+int lbk_plan_run(lbk_plan *pl, void *stream) {
+    if (!pl) return fail(LBK_ERR_INVALID, "plan is null");
+    Plan *p = reinterpret_cast<Plan *>(pl);
+    if (!p->finalized) return fail(LBK_ERR_INVALID, "plan is not finalized");
+    if (!p->exec) return LBK_OK;
+    LBK_CUDA(cudaSetDevice(p->ctx->device));
+    LBK_CUDA(cudaGraphLaunch(p->exec, static_cast<cudaStream_t>(stream)));
+    p->ctx->launches += p->groups.size();
+    return LBK_OK;
+}
+
+size_t lbk_plan_weight_bytes(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->weight_bytes : 0; }
+
+int lbk_plan_destroy(lbk_plan *pl) {
+    if (!pl) return LBK_OK;
+    Plan *p = reinterpret_cast<Plan *>(pl);
+    if (p->exec) cudaGraphExecDestroy(p->exec);
+    if (p->graph) cudaGraphDestroy(p->graph);
+    delete p;
+    return LBK_OK;
+}
+
+}  // extern "C"

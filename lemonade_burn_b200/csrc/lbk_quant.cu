@@ -1,0 +1,94 @@
+// Per-token absmax int8 activation quantiser, standalone form.
+//
+// Replaces quantize_acts / quantize_acts_into / quantize_row_scalar / quantize_row_avx2
+// (crates/lb-ternary/src/quant.rs:37-193): one CTA per token row computes
+// scale = 127/max(amax,1e-5), q = clamp(round_half_even(x*scale)), sum(q), and writes q
+// zero padded to padded_cols(k). The decode GEMV has its own fused copy of this; this
+// kernel feeds the prefill GEMM and the quantize_acts entry point.
+#include "lbk_internal.cuh"
+
+namespace lbk {
+
+namespace {
+
+constexpr int kQThreads = 256;
+
+__device__ __forceinline__ int quant_one(float v, float scale) {
+    int r = __float2int_rn(__fmul_rn(v, scale));  // NaN -> 0 like `NaN as i8` (quant.rs:115-118)
+    return max(-128, min(127, r));
+}
+
+__global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__restrict__ x, int k,
+                                                            int kp, int8_t *__restrict__ q,
+                                                            float *__restrict__ scale,
+                                                            int32_t *__restrict__ sum) {
+    __shared__ float s_f[kQThreads / 32];
+    __shared__ int s_i[kQThreads / 32];
+    __shared__ float s_scale;
+    const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float *xr = x + static_cast<size_t>(row) * k;
+    int8_t *qr = q + static_cast<size_t>(row) * kp;
+    const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+
+    float am = 0.0f;  // fmaxf drops a NaN operand, as f32::max does (quant.rs:101-104)
+    if (vec) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+        for (int i = tid; i < (k >> 2); i += kQThreads) {
+            float4 v = __ldg(x4 + i);
+            am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        }
+    } else {
+        for (int i = tid; i < k; i += kQThreads) am = fmaxf(am, fabsf(__ldg(xr + i)));
+    }
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    if (lane == 0) s_f[warp] = am;
+    __syncthreads();
+    if (tid == 0) {
+        float a = 0.0f;
+        for (int w = 0; w < kQThreads / 32; ++w) a = fmaxf(a, s_f[w]);
+        s_scale = __fdiv_rn(127.0f, fmaxf(a, 1e-5f));
+    }
+    __syncthreads();
+    const float sc = s_scale;
+    int acc = 0;
+    for (int i = tid * 4; i < kp; i += kQThreads * 4) {
+        int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
+        if (vec && i + 3 < k) {
+            float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
+            q0 = quant_one(v.x, sc); q1 = quant_one(v.y, sc);
+            q2 = quant_one(v.z, sc); q3 = quant_one(v.w, sc);
+        } else {
+            if (i < k) q0 = quant_one(__ldg(xr + i), sc);
+            if (i + 1 < k) q1 = quant_one(__ldg(xr + i + 1), sc);
+            if (i + 2 < k) q2 = quant_one(__ldg(xr + i + 2), sc);
+            if (i + 3 < k) q3 = quant_one(__ldg(xr + i + 3), sc);
+        }
+        acc += q0 + q1 + q2 + q3;
+        *reinterpret_cast<uint32_t *>(qr + i) = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) |
+                                                (static_cast<uint32_t>(q3 & 255) << 24);
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_i[warp] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        int s = 0;
+        for (int w = 0; w < kQThreads / 32; ++w) s += s_i[w];
+        scale[row] = sc;
+        sum[row] = s;
+    }
+}
+
+}  // namespace
+
+int launch_quantize(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
+                    int32_t *sum, cudaStream_t stream) {
+    if (m == 0) return LBK_OK;
+    const size_t kp = lbk_padded_cols(k);
+    quantize_kernel<<<static_cast<unsigned>(m), kQThreads, 0, stream>>>(
+        x, static_cast<int>(k), static_cast<int>(kp), q, scale, sum);
+    LBK_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return LBK_OK;
+}
+
+}  // namespace lbk

@@ -1,0 +1,152 @@
+"""Device-resident ops on torch CUDA tensors: the B200 side of lb-model's op boundary.
+
+Mirrors `ternary_linear`, `ternary_linear2`, `ternary_linear3`, `bf16_linear`
+(crates/lb-model/src/ops.rs:332-397) and `TernaryLinear` (crates/lb-model/src/model.rs:38-83).
+torch is used for device memory and streams only; all arithmetic is in liblbk.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import torch
+
+from . import _lib
+from .pack import row_bytes
+from .ternary import Context, DeviceWeight, default_context
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class TernaryLinear:
+    """A packed ternary projection resident on the GPU (model.rs:38-63).
+
+    `packed` is a uint8 CUDA tensor [rows, row_bytes(cols)] in the lb-ternary layout (what
+    `<linear>.qweight` holds in model.lbt.safetensors); `scale` is `<linear>.wscale`."""
+
+    def __init__(self, packed: torch.Tensor, scale: float, cols: int, ctx: Optional[Context] = None):
+        if packed.dtype != torch.uint8:  # ops.rs:228
+            raise TypeError("ternary_linear expects u8 packed weights")
+        if packed.dim() != 2:
+            raise ValueError("expected a rank-2 tensor")
+        if not packed.is_cuda:
+            raise ValueError("packed weights must live on the GPU")
+        self.ctx = ctx or default_context()
+        self.packed = packed.contiguous()
+        self.rows = int(packed.shape[0])
+        self.cols = int(cols)
+        self.scale = float(scale)
+        if packed.shape[1] != row_bytes(cols):  # pack.rs:40
+            raise ValueError("packed data length mismatch")
+        self.weight = DeviceWeight.wrap(self.ctx, self.rows, self.cols, self.packed.data_ptr(), self.scale)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ternary_linear_multi(x, [self])[0]
+
+    __call__ = forward
+
+
+def ternary_linear_multi(x: torch.Tensor, linears: Sequence[TernaryLinear], want_i32: bool = False):
+    """flex_ternary_multi (ops.rs:301-329): quantise `x` once, one fused launch over all
+    matrices. x: f32 CUDA [m, cols]. Returns a list of f32 [m, rows_i] (and the exact int32
+    dots when want_i32)."""
+    if x.dtype != torch.float32:  # ops.rs:306
+        raise TypeError("ternary_linear expects f32 activations")
+    if x.dim() != 2:
+        raise ValueError("expected a rank-2 tensor")
+    ctx = linears[0].ctx
+    x = x.contiguous()
+    m, k = x.shape
+    for l in linears:
+        if l.cols != k:  # ops.rs:308
+            raise ValueError("inner dimension mismatch")
+    outs = [torch.empty((m, l.rows), dtype=torch.float32, device=x.device) for l in linears]
+    iouts = [torch.empty((m, l.rows), dtype=torch.int32, device=x.device) for l in linears] if want_i32 else None
+    wp, _k1 = _lib.ptr_array([l.weight.handle.value for l in linears])
+    op, _k2 = _lib.ptr_array([o.data_ptr() for o in outs])
+    ip, _k3 = _lib.ptr_array([o.data_ptr() for o in iouts]) if iouts else (None, None)
+    _lib.check(ctx._lib.lbk_ternary_linear_n(ctx.handle, C.c_void_p(x.data_ptr()), m, wp, len(linears), op, ip,
+                                             C.c_void_p(_stream_ptr())))
+    return (outs, iouts) if want_i32 else outs
+
+
+def ternary_linear(x: torch.Tensor, lin: TernaryLinear) -> torch.Tensor:
+    """ops.rs:332-339"""
+    return ternary_linear_multi(x, [lin])[0]
+
+
+def ternary_linear2(x: torch.Tensor, p: Sequence[TernaryLinear]) -> List[torch.Tensor]:
+    """ops.rs:342-345 (gate/up)"""
+    if len(p) != 2:
+        raise ValueError("ternary_linear2 takes two matrices")
+    return ternary_linear_multi(x, p)
+
+
+def ternary_linear3(x: torch.Tensor, p: Sequence[TernaryLinear]) -> List[torch.Tensor]:
+    """ops.rs:348-358 (q/k/v)"""
+    if len(p) != 3:
+        raise ValueError("ternary_linear3 takes three matrices")
+    return ternary_linear_multi(x, p)
+
+
+def bf16_linear(x: torch.Tensor, w: torch.Tensor, ctx: Optional[Context] = None) -> torch.Tensor:
+    """ops.rs:391-397 / 199-218: x f32 [m, k] @ w^T with w bf16 [n, k] -> f32 [m, n]."""
+    ctx = ctx or default_context()
+    if x.dtype != torch.float32:
+        raise TypeError("bf16_linear expects f32 activations")
+    if w.dtype != torch.bfloat16:  # ops.rs:204
+        raise TypeError("bf16_linear expects bf16 weights")
+    if x.dim() != 2 or w.dim() != 2:
+        raise ValueError("expected rank-2 tensors")
+    if x.shape[1] != w.shape[1]:  # ops.rs:207
+        raise ValueError("inner dimension mismatch")
+    x, w = x.contiguous(), w.contiguous()
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+    _lib.check(ctx._lib.lbk_bf16_linear(ctx.handle, C.c_void_p(x.data_ptr()), m, C.c_void_p(w.data_ptr()), n, k,
+                                        C.c_void_p(out.data_ptr()), C.c_void_p(_stream_ptr())))
+    return out
+
+
+class Plan:
+    """A recorded sequence of fused decode groups replayed with one call (lbk_plan_*)."""
+
+    def __init__(self, ctx: Optional[Context] = None):
+        self.ctx = ctx or default_context()
+        h = C.c_void_p()
+        _lib.check(self.ctx._lib.lbk_plan_create(self.ctx.handle, C.byref(h)))
+        self.handle = h
+        self._keep = []
+
+    def add(self, x: torch.Tensor, linears: Sequence[TernaryLinear], outs: Sequence[torch.Tensor],
+            iouts: Optional[Sequence[torch.Tensor]] = None):
+        if x.dtype != torch.float32 or x.numel() != linears[0].cols:
+            raise ValueError("plan groups take one f32 token row of `cols` elements")
+        wp, k1 = _lib.ptr_array([l.weight.handle.value for l in linears])
+        op, k2 = _lib.ptr_array([o.data_ptr() for o in outs])
+        ip, k3 = _lib.ptr_array([o.data_ptr() for o in iouts]) if iouts else (None, None)
+        _lib.check(self.ctx._lib.lbk_plan_add(self.handle, C.c_void_p(x.data_ptr()), wp, len(linears), op, ip))
+        self._keep.append((x, list(linears), list(outs), list(iouts) if iouts else None))
+
+    def finalize(self):
+        _lib.check(self.ctx._lib.lbk_plan_finalize(self.handle))
+
+    def run(self):
+        _lib.check(self.ctx._lib.lbk_plan_run(self.handle, C.c_void_p(_stream_ptr())))
+
+    def weight_bytes(self) -> int:
+        return int(self.ctx._lib.lbk_plan_weight_bytes(self.handle))
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx._lib.lbk_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
