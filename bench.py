@@ -1,0 +1,354 @@
+#!/usr/bin/env python
+"""Benchmark of the packed-ternary x int8 decode path: one JSON line per run.
+
+Workload at N=1 ("bitnet2b_decode_sweep"): the BitNet-b1.58-2B4T-shaped decode weight
+stream at batch 1 -- 30 layers x (QKV 2560->3840, O 2560->2560, gate/up 2560->2x6912,
+down 6912->2560), every group with its own fused per-token int8 activation quantisation,
+distinct seeded weights per layer (521 011 200 packed bytes, larger than L2, so every step
+streams them from HBM). One step = one whole-model sweep = one token-equivalent, which is how
+the reference's own microbenchmark times it (crates/lb-ternary/benches/kbench.rs:148-194).
+Weights are i.i.d. ternary with P(-1)=P(+1)=0.3, P(0)=0.4; activations N(0,1); synthetic.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+`value`   tok/s with inputs resident in HBM (CUDA events around exactly K steps)
+`e2e`     tok/s through the host-buffer C-ABI call (H2D inputs, sweep, D2H outputs per step)
+`roofline` algorithmic bytes per sweep / measured time, against the measured HBM copy peak
+`cpu_baseline` the C port of the reference's SIMD kernels on this box's host cores
+`--impl reference` times only that CPU port (the reference itself is Rust and cannot be
+built where there is no Rust toolchain) and prints the same line with "impl": "reference".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+HIDDEN, INTER, LAYERS = 2560, 6912, 30
+GROUPS = [  # (cols, [rows...]) per layer, in the model's order (model.rs:333,359,362,365)
+    (HIDDEN, [2560, 640, 640]),
+    (HIDDEN, [2560]),
+    (HIDDEN, [INTER, INTER]),
+    (INTER, [2560]),
+]
+WSCALE = float(np.float32(1.0) / np.float32(0.02 * np.sqrt(2.0 / np.pi)))  # 1/mean|N(0,0.02)|
+METRIC = "decode tok/s (BitNet-2B shape)"
+WORKLOAD = "bitnet2b_decode_sweep"
+
+
+def weight_bytes_per_sweep() -> int:
+    return LAYERS * sum(sum(rows) * cols // 4 for cols, rows in GROUPS)
+
+
+def algorithmic_bytes_per_sweep() -> int:
+    """Packed weights once + f32 input row per group + f32 outputs."""
+    io = LAYERS * sum(cols * 4 + sum(rows) * 4 for cols, rows in GROUPS)
+    return weight_bytes_per_sweep() + io
+
+
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+# ---------------------------------------------------------------------------------------
+# clocks sampling (nvidia-smi in the background during the timed regions)
+# ---------------------------------------------------------------------------------------
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,utilization.gpu,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.idx = gpu_index
+        self.proc = None
+        self.path = None
+
+    def start(self):
+        try:
+            f = tempfile.NamedTemporaryFile(prefix="lbk_clocks_", suffix=".csv", delete=False)
+            self.path = f.name
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.idx)], stdout=f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if not self.proc:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        try:
+            for line in Path(self.path).read_text().splitlines():
+                parts = [p.strip() for p in line.split(",")]
+                if len(parts) >= 10:
+                    rows.append(parts)
+            os.unlink(self.path)
+        except Exception:
+            pass
+        if not rows:
+            return out
+        def num(v):
+            try:
+                return float(v)
+            except Exception:
+                return None
+        busy = [r for r in rows if (num(r[4]) or 0) > 0] or rows
+        sm = sorted(v for v in (num(r[1]) for r in busy) if v is not None)
+        mx = [v for v in (num(r[2]) for r in rows) if v is not None]
+        reasons = set()
+        for r in busy:
+            for name, col in (("hw_slowdown", 6), ("hw_thermal_slowdown", 7), ("sw_thermal_slowdown", 8), ("sw_power_cap", 9)):
+                if r[col].lower().startswith("active"):
+                    reasons.add(name)
+        out.update(sm_mhz=sm[len(sm) // 2] if sm else None, sm_max_mhz=max(mx) if mx else None,
+                   reasons=sorted(reasons), samples=len(busy))
+        return out
+
+
+# ---------------------------------------------------------------------------------------
+# CPU baseline: the C port of the reference's SIMD kernels (oracle/lbt_simd.c)
+# ---------------------------------------------------------------------------------------
+def cpu_sweep_baseline(packed_layers, xs, budget_s: float = 12.0, max_layers: int = 30):
+    """Times whole-layer passes of the SIMD port on the host cores over a bounded sample of
+    the sweep's layers. Returns (tok_per_s, cores, kernel, sample description)."""
+    from oracle import oracle as o
+    o.build()
+    kern = o.simd_best_kernel()
+    threads = o.simd_max_threads()
+    n_layers = min(len(packed_layers), max_layers)
+
+    def one_pass():
+        for li in range(n_layers):
+            for gi, (cols, rows) in enumerate(GROUPS):
+                x = xs[li * len(GROUPS) + gi]
+                q, s, ssum = o.simd_quantize_acts(x.reshape(1, cols))
+                o.simd_gemm_multi(packed_layers[li][gi], [WSCALE] * len(rows), q, s, ssum, kernel=kern)
+
+    one_pass()  # warm (page in)
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        one_pass()
+        reps += 1
+        dt = time.perf_counter() - t0
+        if dt > budget_s or reps >= 20:
+            break
+    per_sweep = dt / reps * (LAYERS / n_layers)
+    sample = (f"{reps} passes over {n_layers} of {LAYERS} layers "
+              f"({n_layers * weight_bytes_per_sweep() // LAYERS} packed bytes per pass), "
+              f"{o.simd_kernel_name(kern)} kernel, scaled to a full sweep")
+    return 1.0 / per_sweep, threads, o.simd_kernel_name(kern), sample
+
+
+def host_weights(seed: int, n_layers: int):
+    """Seeded packed weights and inputs on the host (for --impl reference, no GPU needed).
+    Packed bytes are drawn so that every 2-bit code is i.i.d. with P = (0.3, 0.4, 0.3)."""
+    rng = np.random.default_rng(seed)
+    layers, xs = [], []
+    for li in range(n_layers):
+        groups = []
+        for cols, rows in GROUPS:
+            mats = []
+            for r in rows:
+                u = rng.random((4, r, cols // 4), dtype=np.float32)
+                codes = (u > 0.3).astype(np.uint8) + (u > 0.7).astype(np.uint8)
+                mats.append(np.ascontiguousarray(codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)))
+            groups.append(mats)
+            xs.append(rng.standard_normal(cols).astype(np.float32))
+        layers.append(groups)
+    return layers, xs
+
+
+def run_reference(args):
+    """The reference arm: the CPU implementation of the path on this box's host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    n_layers = 6  # bounded sample: 104 MB of packed weights per pass, well beyond host caches
+    layers, xs = host_weights(1234, n_layers)
+    budget = min(60.0, max(2.0, 0.05 * args.steps))
+    toks, cores, kern, sample = cpu_sweep_baseline(layers, xs, budget_s=budget, max_layers=n_layers)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / toks, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": LAYERS, "hidden": HIDDEN, "intermediate": INTER, "batch": 1},
+        "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "C port of lb-ternary's SIMD kernels (the Rust reference cannot be built: no rustc/cargo here)",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------
+# ours
+# ---------------------------------------------------------------------------------------
+def build_sweep(torch, ops, ctx, device, seed: int):
+    """Seeded packed weights on the device + a plan of 120 fused groups using plan arenas."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    plan = ops.Plan(ctx)
+    linears = []
+    for li in range(LAYERS):
+        for cols, rows in GROUPS:
+            lins = []
+            for r in rows:
+                u = torch.rand((4, r, cols // 4), generator=g, device=device)
+                codes = (u > 0.3).to(torch.uint8) + (u > 0.7).to(torch.uint8)
+                packed = codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)
+                lins.append(ops.TernaryLinear(packed.contiguous(), WSCALE, cols, ctx))
+                del u, codes
+            plan.add_arena(lins)
+            linears.append(lins)
+    plan.finalize()
+    return plan, linears
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    from lemonade_burn_b200 import ops, ternary
+    ctx = ternary.Context(local)
+    plan, linears = build_sweep(torch, ops, ctx, device, 1234 + rank)
+    nx, ny = plan.input_elems(), plan.output_elems()
+    x_host = torch.randn(nx, generator=torch.Generator().manual_seed(99 + rank)).pin_memory()
+    y_host = torch.empty(ny, dtype=torch.float32).pin_memory()
+    torch.cuda.synchronize()
+    plan.run_host(x_host, y_host)  # also fills the arena; warms everything once
+    ctx.check_device_error()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+
+    # ---- device-timed: inputs resident, exactly K steps ---------------------------------
+    for _ in range(args.warmup):
+        plan.run()
+    barrier()
+    launches0 = ctx.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        plan.run()
+    e1.record()
+    barrier()
+    launches = ctx.launch_count() - launches0
+    dev_ms = e0.elapsed_time(e1)
+    ctx.check_device_error()
+
+    # ---- end to end: host buffers through the C ABI, copies inside the timed region --------
+    for _ in range(min(args.warmup, 10)):
+        plan.run_host(x_host, y_host)
+    barrier()
+    e2e_steps = args.steps
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        plan.run_host(x_host, y_host)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+
+    clocks = sampler.stop() if rank == 0 else {}
+
+    times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_ms = float(times[0]), float(times[1])
+
+    if rank == 0:
+        tok_s = world * args.steps / (dev_ms * 1e-3)
+        e2e_tok_s = world * e2e_steps / (e2e_ms * 1e-3)
+        peak, peak_kind = measured_peaks()
+        sweep_s = dev_ms * 1e-3 / args.steps
+        achieved = algorithmic_bytes_per_sweep() / sweep_s / 1e9
+        # CPU baseline on this box's host cores: same weights, a bounded sample of layers
+        n_cpu_layers = 6
+        packed_layers = []
+        xs = []
+        xh = x_host.numpy()
+        off = 0
+        for li in range(n_cpu_layers):
+            groups = []
+            for gi, (cols, rows) in enumerate(GROUPS):
+                groups.append([l.packed.cpu().numpy() for l in linears[li * len(GROUPS) + gi]])
+            packed_layers.append(groups)
+        for li in range(LAYERS):
+            for cols, rows in GROUPS:
+                xs.append(xh[off:off + cols].copy())
+                off += cols
+        cpu_toks, cores, kern, sample = cpu_sweep_baseline(packed_layers, xs, budget_s=10.0, max_layers=n_cpu_layers)
+        line = {
+            "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "layers": LAYERS, "hidden": HIDDEN, "intermediate": INTER, "batch": 1,
+                       "groups_per_step": LAYERS * len(GROUPS), "packed_weight_bytes": weight_bytes_per_sweep(),
+                       "l2": "inputs larger than L2 (521 MB of distinct weights per step)",
+                       "parallelism": "replicas" if world > 1 else "single"},
+            "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": nx * 4, "d2h_bytes_per_step": ny * 4},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": None, "peak_kind": peak_kind, "kernel": "gemv_kernel<1>",
+                         "algorithmic_bytes_per_step": algorithmic_bytes_per_sweep(),
+                         "frac_of_nominal_8TBs": achieved / 8000.0},
+            "cpu_baseline": {"value": cpu_toks, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=50)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_ours(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

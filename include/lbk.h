@@ -149,11 +149,24 @@ int lbk_bf16_linear(lbk_ctx *ctx, const float *x_dev, size_t m, const uint16_t *
  * launch. Groups in a plan must not read each other's outputs unless `barrier` is set on
  * the reading group. */
 int lbk_plan_create(lbk_ctx *ctx, lbk_plan **out);
-/* Appends one fused group (same meaning as lbk_ternary_linear_n with m == 1). */
+/* Appends one fused group (same meaning as lbk_ternary_linear_n with m == 1). With x_dev
+ * and outs_dev both NULL the group reads its input from, and writes its f32 outputs to, the
+ * plan's own device arenas (allocated by lbk_plan_finalize; slots in order of addition:
+ * inputs are `cols` floats each, outputs rows_0 + rows_1 + ... floats each). */
 int lbk_plan_add(lbk_plan *plan, const float *x_dev, const lbk_weight *const *ws, size_t n,
                  float *const *outs_dev, int32_t *const *iouts_dev);
 int lbk_plan_finalize(lbk_plan *plan);
 int lbk_plan_run(lbk_plan *plan, void *stream);
+/* One decode-like step on HOST buffers, for plans whose groups all use the arenas: copies
+ * x_host (every group's input row, concatenated) to the device, runs the plan, copies every
+ * group's outputs back to y_host and synchronises `stream`. This is the host-buffer form of
+ * the reference's per-token loop (crates/lb-ternary/benches/kbench.rs:173-190). */
+int lbk_plan_run_host(lbk_plan *plan, const float *x_host, size_t x_len, float *y_host,
+                      size_t y_len, void *stream);
+size_t lbk_plan_input_elems(const lbk_plan *plan);
+size_t lbk_plan_output_elems(const lbk_plan *plan);
+const float *lbk_plan_input_arena(const lbk_plan *plan);  /* device pointers, after finalize */
+const float *lbk_plan_output_arena(const lbk_plan *plan);
 /* Packed weight bytes one run streams (the figure kbench reports bandwidth on, kbench.rs:61). */
 size_t lbk_plan_weight_bytes(const lbk_plan *plan);
 int lbk_plan_destroy(lbk_plan *plan);

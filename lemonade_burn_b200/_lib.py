@@ -47,6 +47,11 @@ SYMBOLS = [
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),
     ("lbk_plan_finalize", _i, [_vp]),
     ("lbk_plan_run", _i, [_vp, _vp]),
+    ("lbk_plan_run_host", _i, [_vp, _vp, _sz, _vp, _sz, _vp]),
+    ("lbk_plan_input_elems", _sz, [_vp]),
+    ("lbk_plan_output_elems", _sz, [_vp]),
+    ("lbk_plan_input_arena", _vp, [_vp]),
+    ("lbk_plan_output_arena", _vp, [_vp]),
     ("lbk_plan_weight_bytes", _sz, [_vp]),
     ("lbk_plan_destroy", _i, [_vp]),
 ]

@@ -11,6 +11,10 @@ namespace lbk {
 struct Plan {
     Ctx *ctx = nullptr;
     std::vector<GroupArgs> groups;
+    // groups added without buffers get slots in plan-owned arenas (x then y, in add order)
+    std::vector<int> arena_group;  // indices of such groups
+    float *x_arena = nullptr, *y_arena = nullptr;
+    size_t x_elems = 0, y_elems = 0;
     size_t weight_bytes = 0;
     bool finalized = false;
     cudaGraph_t graph = nullptr;
@@ -44,7 +48,8 @@ int lbk_plan_add(lbk_plan *pl, const float *x_dev, const lbk_weight *const *ws, 
     Plan *p = reinterpret_cast<Plan *>(pl);
     if (p->finalized) return fail(LBK_ERR_INVALID, "plan is already finalized");
     if (!ws || n < 1 || n > LBK_MAX_GROUP) return fail(LBK_ERR_INVALID, "group of %zu matrices (1..%d allowed)", n, LBK_MAX_GROUP);
-    if (!x_dev || !outs_dev) return fail(LBK_ERR_INVALID, "lbk_plan_add: null buffer");
+    const bool arena = !x_dev && !outs_dev;
+    if (!arena && (!x_dev || !outs_dev)) return fail(LBK_ERR_INVALID, "lbk_plan_add: give both x_dev and outs_dev, or neither");
     GroupArgs g;
     g.n = static_cast<int>(n);
     g.m = 1;
@@ -53,13 +58,18 @@ int lbk_plan_add(lbk_plan *pl, const float *x_dev, const lbk_weight *const *ws, 
         const Weight *w = reinterpret_cast<const Weight *>(ws[i]);
         if (!w || w->ctx != p->ctx) return fail(LBK_ERR_INVALID, "matrix %zu is null or belongs to another context", i);
         if (w->cols != reinterpret_cast<const Weight *>(ws[0])->cols) return fail(LBK_ERR_SHAPE, "inner dimension mismatch in group");
-        if (!outs_dev[i]) return fail(LBK_ERR_INVALID, "output %zu is null", i);
+        if (!arena && !outs_dev[i]) return fail(LBK_ERR_INVALID, "output %zu is null", i);
         g.w[i] = w;
-        g.out[i] = outs_dev[i];
+        g.out[i] = arena ? nullptr : outs_dev[i];
         g.iout[i] = iouts_dev ? iouts_dev[i] : nullptr;
         p->weight_bytes += w->rows * w->rb;
     }
     if (!gemv_fits(p->ctx, g.w[0]->kp, 1)) return fail(LBK_ERR_UNSUPPORTED, "%zu columns do not fit the decode kernel", g.w[0]->cols);
+    if (arena) {
+        p->arena_group.push_back(static_cast<int>(p->groups.size()));
+        p->x_elems += g.w[0]->cols;
+        for (int i = 0; i < g.n; ++i) p->y_elems += g.w[i]->rows;
+    }
     p->groups.push_back(g);
     return LBK_OK;
 }
@@ -70,6 +80,21 @@ int lbk_plan_finalize(lbk_plan *pl) {
     if (p->finalized) return LBK_OK;
     Ctx *ctx = p->ctx;
     LBK_CUDA(cudaSetDevice(ctx->device));
+    if (!p->arena_group.empty()) {
+        cudaError_t e = cudaMalloc(&p->x_arena, (p->x_elems + 4) * sizeof(float));
+        if (e == cudaSuccess) e = cudaMalloc(&p->y_arena, (p->y_elems + 4) * sizeof(float));
+        if (e != cudaSuccess) return fail(LBK_ERR_NOMEM, "plan arenas: %s", cudaGetErrorString(e));
+        size_t xo = 0, yo = 0;
+        for (int gi : p->arena_group) {
+            GroupArgs &g = p->groups[gi];
+            g.x = p->x_arena + xo;  // cols are multiples of 4 for every 16-byte aligned slot
+            xo += g.w[0]->cols;
+            for (int i = 0; i < g.n; ++i) {
+                g.out[i] = p->y_arena + yo;
+                yo += g.w[i]->rows;
+            }
+        }
+    }
     if (!p->groups.empty()) {
         cudaStream_t st = ctx->own_stream;
         LBK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
@@ -105,6 +130,29 @@ int lbk_plan_run(lbk_plan *pl, void *stream) {
     return LBK_OK;
 }
 
+int lbk_plan_run_host(lbk_plan *pl, const float *x_host, size_t x_len, float *y_host, size_t y_len, void *stream) {
+    if (!pl) return fail(LBK_ERR_INVALID, "plan is null");
+    Plan *p = reinterpret_cast<Plan *>(pl);
+    if (!p->finalized) return fail(LBK_ERR_INVALID, "plan is not finalized");
+    if (p->arena_group.size() != p->groups.size())
+        return fail(LBK_ERR_INVALID, "lbk_plan_run_host needs every group added without device buffers");
+    if (x_len != p->x_elems || y_len != p->y_elems)
+        return fail(LBK_ERR_SHAPE, "host arenas: got %zu inputs / %zu outputs, plan has %zu / %zu", x_len, y_len, p->x_elems, p->y_elems);
+    if ((x_len && !x_host) || (y_len && !y_host)) return fail(LBK_ERR_INVALID, "host buffer is null");
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LBK_CUDA(cudaSetDevice(p->ctx->device));
+    if (x_len) LBK_CUDA(cudaMemcpyAsync(p->x_arena, x_host, x_len * sizeof(float), cudaMemcpyHostToDevice, st));
+    LBK_TRY(lbk_plan_run(pl, stream));
+    if (y_len) LBK_CUDA(cudaMemcpyAsync(y_host, p->y_arena, y_len * sizeof(float), cudaMemcpyDeviceToHost, st));
+    LBK_CUDA(cudaStreamSynchronize(st));
+    return LBK_OK;
+}
+
+size_t lbk_plan_input_elems(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->x_elems : 0; }
+size_t lbk_plan_output_elems(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->y_elems : 0; }
+const float *lbk_plan_input_arena(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->x_arena : nullptr; }
+const float *lbk_plan_output_arena(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->y_arena : nullptr; }
+
 size_t lbk_plan_weight_bytes(const lbk_plan *pl) { return pl ? reinterpret_cast<const Plan *>(pl)->weight_bytes : 0; }
 
 int lbk_plan_destroy(lbk_plan *pl) {
@@ -112,6 +160,8 @@ int lbk_plan_destroy(lbk_plan *pl) {
     Plan *p = reinterpret_cast<Plan *>(pl);
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
+    if (p->x_arena) cudaFree(p->x_arena);
+    if (p->y_arena) cudaFree(p->y_arena);
     delete p;
     return LBK_OK;
 }

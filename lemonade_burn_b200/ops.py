@@ -131,6 +131,30 @@ class Plan:
         _lib.check(self.ctx._lib.lbk_plan_add(self.handle, C.c_void_p(x.data_ptr()), wp, len(linears), op, ip))
         self._keep.append((x, list(linears), list(outs), list(iouts) if iouts else None))
 
+    def add_arena(self, linears: Sequence[TernaryLinear]):
+        """Append a group whose input row and outputs live in the plan's own arenas."""
+        wp, k1 = _lib.ptr_array([l.weight.handle.value for l in linears])
+        _lib.check(self.ctx._lib.lbk_plan_add(self.handle, None, wp, len(linears), None, None))
+        self._keep.append((None, list(linears), None, None))
+
+    def run_host(self, x_host: torch.Tensor, y_host: torch.Tensor):
+        """One step on host buffers (pinned for speed): H2D inputs, run, D2H outputs, sync."""
+        _lib.check(self.ctx._lib.lbk_plan_run_host(self.handle, C.c_void_p(x_host.data_ptr()), x_host.numel(),
+                                                   C.c_void_p(y_host.data_ptr()), y_host.numel(),
+                                                   C.c_void_p(_stream_ptr())))
+
+    def input_elems(self) -> int:
+        return int(self.ctx._lib.lbk_plan_input_elems(self.handle))
+
+    def output_elems(self) -> int:
+        return int(self.ctx._lib.lbk_plan_output_elems(self.handle))
+
+    def input_arena_ptr(self) -> int:
+        return int(self.ctx._lib.lbk_plan_input_arena(self.handle) or 0)
+
+    def output_arena_ptr(self) -> int:
+        return int(self.ctx._lib.lbk_plan_output_arena(self.handle) or 0)
+
     def finalize(self):
         _lib.check(self.ctx._lib.lbk_plan_finalize(self.handle))
 

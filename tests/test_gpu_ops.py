@@ -1,0 +1,123 @@
+"""Device-resident ops (torch CUDA tensors in, CUDA tensors out) against the oracle:
+ternary_linear / ternary_linear2 / ternary_linear3 / bf16_linear (crates/lb-model/src/ops.rs)
+and a recorded plan of decode groups (the reference's per-token loop of fused ops)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def make_linear(o, rows, cols, seed, ctx, scale=None):
+    import torch
+    from lemonade_burn_b200 import ops
+    rng = np.random.default_rng(seed)
+    t = rng.choice(np.array([-1, 0, 1], dtype=np.int8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+    p = o.pack_matrix(t)
+    ws = np.float32(scale if scale is not None else 1.0 / (0.02 * 0.8))
+    lin = ops.TernaryLinear(torch.from_numpy(p).cuda(), float(ws), cols, ctx)
+    return lin, p, ws
+
+
+@pytest.mark.parametrize("m", [1, 2, 8, 9, 16])
+def test_ternary_linear3_qkv(oracle, ctx, m):
+    import torch
+    from lemonade_burn_b200 import ops
+    cols = 2560
+    lins = [make_linear(oracle, r, cols, 10 + i, ctx, sc) for i, (r, sc) in enumerate([(2560, 41.0), (640, 57.5), (640, 63.25)])]
+    x = np.random.default_rng(m).standard_normal((m, cols)).astype(np.float32)
+    outs, iouts = ops.ternary_linear_multi(torch.from_numpy(x).cuda(), [l for l, _, _ in lins], want_i32=True)
+    torch.cuda.synchronize()
+    q, s, ssum = oracle.quantize_acts(x)
+    wf, wi = oracle.simd_gemm_multi([p for _, p, _ in lins], [w for _, _, w in lins], q, s, ssum, want_i32=True)
+    for o_, i_, ef, ei in zip(outs, iouts, wf, wi):
+        assert np.array_equal(i_.cpu().numpy(), ei)
+        assert np.array_equal(o_.cpu().numpy().view(np.uint32), ef.view(np.uint32))
+    three = ops.ternary_linear3(torch.from_numpy(x).cuda(), [l for l, _, _ in lins])
+    single = ops.ternary_linear(torch.from_numpy(x).cuda(), lins[1][0])
+    assert torch.equal(three[1], single)  # fused == separate, bit for bit (ops.rs:27-29)
+    ctx.check_device_error()
+
+
+def test_ternary_linear2_gate_up_and_down(oracle, ctx):
+    import torch
+    from lemonade_burn_b200 import ops
+    g, pg, wg = make_linear(oracle, 6912, 2560, 21, ctx, 50.0)
+    u, pu, wu = make_linear(oracle, 6912, 2560, 22, ctx, 52.0)
+    d, pd, wd = make_linear(oracle, 2560, 6912, 23, ctx, 49.0)
+    x = np.random.default_rng(7).standard_normal((1, 2560)).astype(np.float32)
+    a, b = ops.ternary_linear2(torch.from_numpy(x).cuda(), [g, u])
+    q, s, ssum = oracle.quantize_acts(x)
+    wf, _ = oracle.simd_gemm_multi([pg, pu], [wg, wu], q, s, ssum)
+    assert np.array_equal(a.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
+    assert np.array_equal(b.cpu().numpy().view(np.uint32), wf[1].view(np.uint32))
+    x2 = np.random.default_rng(8).standard_normal((3, 6912)).astype(np.float32)
+    y = ops.ternary_linear(torch.from_numpy(x2).cuda(), d)
+    q, s, ssum = oracle.quantize_acts(x2)
+    wf, _ = oracle.simd_gemm_multi([pd], [wd], q, s, ssum)
+    assert np.array_equal(y.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
+
+
+def test_dtype_and_shape_errors(oracle, ctx):
+    import torch
+    from lemonade_burn_b200 import ops
+    lin, _, _ = make_linear(oracle, 16, 256, 1, ctx)
+    with pytest.raises(TypeError, match="f32 activations"):       # ops.rs:306
+        ops.ternary_linear(torch.zeros(1, 256, dtype=torch.float16, device="cuda"), lin)
+    with pytest.raises(ValueError, match="inner dimension mismatch"):  # ops.rs:308
+        ops.ternary_linear(torch.zeros(1, 128, device="cuda"), lin)
+    with pytest.raises(TypeError, match="u8 packed weights"):     # ops.rs:228
+        ops.TernaryLinear(torch.zeros(4, 64, dtype=torch.int8, device="cuda"), 1.0, 256, ctx)
+    with pytest.raises(TypeError, match="bf16 weights"):          # ops.rs:204
+        ops.bf16_linear(torch.zeros(1, 8, device="cuda"), torch.zeros(4, 8, device="cuda"))
+
+
+@pytest.mark.parametrize("m", [1, 3, 4, 7])
+def test_bf16_linear(oracle, ctx, m):
+    import torch
+    from lemonade_burn_b200 import ops
+    rows, cols = 1000, 2560
+    g = torch.Generator().manual_seed(m)
+    w = (torch.randn(rows, cols, generator=g) * 0.02).to(torch.bfloat16)
+    x = torch.randn(m, cols, generator=g)
+    out = ops.bf16_linear(x.cuda(), w.cuda()).cpu().numpy()
+    bits = w.view(torch.int16).numpy().view(np.uint16)
+    for t in range(m):
+        ref = oracle.bf16_gemv(bits, x[t].numpy())
+        assert np.abs(out[t] - ref).max() < 1e-4  # bf16.rs:113-136 bound
+        assert np.allclose(out[t], ref, rtol=1e-3, atol=1e-5)
+
+
+def test_plan_replays_groups(oracle, ctx):
+    """Two layers' worth of decode groups (q/k/v, o, gate/up, down), recorded once and run as
+    one unit, equal to the oracle group by group."""
+    import torch
+    from lemonade_burn_b200 import ops
+    shapes = [[(256, 512), (64, 512), (64, 512)], [(512, 512)], [(640, 512), (640, 512)], [(512, 640)]]
+    plan = ops.Plan(ctx)
+    recs = []
+    seed = 100
+    for layer in range(2):
+        for grp in shapes:
+            cols = grp[0][1]
+            lins = []
+            for rows, _ in grp:
+                seed += 1
+                lins.append(make_linear(oracle, rows, cols, seed, ctx, 40.0 + seed % 7))
+            x = np.random.default_rng(seed).standard_normal((1, cols)).astype(np.float32)
+            xd = torch.from_numpy(x).cuda()
+            outs = [torch.zeros(1, l.rows, device="cuda") for l, _, _ in lins]
+            iouts = [torch.zeros(1, l.rows, dtype=torch.int32, device="cuda") for l, _, _ in lins]
+            plan.add(xd, [l for l, _, _ in lins], outs, iouts)
+            recs.append((x, lins, outs, iouts))
+    plan.finalize()
+    assert plan.weight_bytes() == sum(p.size for _, lins, _, _ in recs for _, p, _ in lins)
+    for _ in range(2):
+        plan.run()
+    torch.cuda.synchronize()
+    ctx.check_device_error()
+    for x, lins, outs, iouts in recs:
+        q, s, ssum = oracle.quantize_acts(x)
+        wf, wi = oracle.simd_gemm_multi([p for _, p, _ in lins], [w for _, _, w in lins], q, s, ssum, want_i32=True)
+        for o_, i_, ef, ei in zip(outs, iouts, wf, wi):
+            assert np.array_equal(i_.cpu().numpy(), ei)
+            assert np.array_equal(o_.cpu().numpy().view(np.uint32), ef.view(np.uint32))
