@@ -19,22 +19,13 @@
 //
 // Algorithmic bytes per call: the packed weights once, plus m*k*4 activation bytes and
 // m*rows*4 output bytes.
-#include "lbk_internal.cuh"
-#include "lbk_ptx.cuh"
+#include "lbk_gemv_core.cuh"
 
 namespace lbk {
 
-namespace {
+using namespace gemv;
 
-constexpr int kWarps = 8;
-constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 6;                             // TMA ring depth per warp
-constexpr int kTileRows = 16;                          // weight rows per MMA tile
-constexpr int kChunkBytes = 128;                       // packed bytes per row per stage
-constexpr int kChunkCols = kChunkBytes * 4;            // 512 columns
-constexpr int kStageBytes = kTileRows * kChunkBytes;   // 2048
-constexpr uint32_t kWaitLimit = 1u << 22;              // polls before a wait gives up
-constexpr int kMaxM = LBK_GEMV_MAX_M;
+namespace {
 
 struct GemvParams {
     CUtensorMap tmap[LBK_MAX_GROUP];
@@ -54,13 +45,17 @@ struct GemvParams {
     const float *qscale;   // f32 [m]
     const int32_t *qsum;   // i32 [m]
     int *err_word;
+#ifdef LBK_TIMELINE
+    long long *timeline;   // [warps_total][8] clock samples, debugging only
+#endif
 };
 
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
 struct SmemLayout {
     uint32_t stages;   // kWarps * kStages * kStageBytes
-    uint32_t bars;     // kWarps * kStages * 8
-    uint32_t part;     // f32/i32 [kMaxM][kWarps] reduction scratch
+    uint32_t full;     // kWarps * kStages mbarriers: stage filled (TMA complete_tx)
+    uint32_t part;     // f32 [kMaxM][kWarps] partial maxima
+    uint32_t parti;    // i32 [kMaxM][kWarps] partial sums
     uint32_t scale;    // f32 [kMaxM]
     uint32_t sum;      // i32 [kMaxM]
     uint32_t inv;      // f32 [LBK_MAX_GROUP][kMaxM]
@@ -72,8 +67,9 @@ __host__ __device__ inline SmemLayout smem_layout(int m, int xq_stride) {
     SmemLayout L;
     uint32_t o = 0;
     L.stages = o; o += kWarps * kStages * kStageBytes;
-    L.bars = o;   o += kWarps * kStages * 8;
+    L.full = o;   o += kWarps * kStages * 8;
     L.part = o;   o += kMaxM * kWarps * 4;
+    L.parti = o;  o += kMaxM * kWarps * 4;
     L.scale = o;  o += kMaxM * 4;
     L.sum = o;    o += kMaxM * 4;
     L.inv = o;    o += LBK_MAX_GROUP * kMaxM * 4;
@@ -83,32 +79,8 @@ __host__ __device__ inline SmemLayout smem_layout(int m, int xq_stride) {
     return L;
 }
 
-// Position of natural column n inside a token row of the shared activation buffer. The
-// order puts, for every MMA, the eight bytes a lane needs next to those of its three
-// neighbours: [chunk][k-group][c][t][8] with n = (chunk*4 + t)*128 + kgroup*32 + c*8 + e.
-__device__ __forceinline__ uint32_t xq_pos(uint32_t n) {
-    uint32_t chunk = n >> 9, t = (n >> 7) & 3, kk = (n >> 5) & 3, c = (n >> 3) & 3, e = n & 7;
-    return ((((chunk * 4 + kk) * 4 + c) * 4 + t) << 3) + e;
-}
-
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-    return v;
-}
-
-__device__ __forceinline__ int warp_sum(int v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-    return v;
-}
-
-// quant.rs:115-118: (v*scale).round_ties_even().clamp(-128,127) as i8, NaN -> 0.
-__device__ __forceinline__ int quant_one(float v, float scale) {
-    int r = __float2int_rn(__fmul_rn(v, scale));  // NaN -> 0, saturates
-    return max(-128, min(127, r));
-}
-
+// Every warp owns a contiguous run of 16-row tiles and a ring of kStages TMA stages that its
+// lane 0 keeps full; the main loop never synchronises across warps.
 template <int MT>
 __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant__ GemvParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -119,104 +91,128 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
+    const int chunks = p.chunks;
+#ifdef LBK_TIMELINE
+    long long tl_start = clock64(), tl_prologue = 0, tl_first = 0, tl_polls = 0;
+    long long tl_a = 0, tl_b = 0, tl_c = 0, tl_d = 0;
+    unsigned long long tl_gstart;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_gstart));
+#endif
 
     // ---- this warp's run of tiles --------------------------------------------------------
     const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
     const long long nw = static_cast<long long>(gridDim.x) * kWarps;
     const int tile_begin = static_cast<int>(gw * p.total_tiles / nw);
     const int tile_end = static_cast<int>((gw + 1) * p.total_tiles / nw);
-    const int chunks = p.chunks;
     const int n_items = (tile_end - tile_begin) * chunks;
-
     const uint32_t stage0 = base + L.stages + warp * (kStages * kStageBytes);
-    const uint32_t bar0 = base + L.bars + warp * (kStages * 8);
+    const uint32_t full0 = base + L.full + warp * (kStages * 8);
 
-    // producer state (lane 0 only): next item to issue
+    // issue cursor (lane 0 only): next item to fetch
     int issue_tile = tile_begin, issue_chunk = 0, issue_mat = 0;
     auto issue = [&](int s) {  // s: the ring stage the next item goes into
         while (issue_mat < p.n_mat - 1 && issue_tile >= p.tile_end[issue_mat]) ++issue_mat;
         const int tile_in_mat = issue_tile - (issue_mat ? p.tile_end[issue_mat - 1] : 0);
-        ptx::mbar_arrive_expect_tx(bar0 + s * 8, kStageBytes);
-        ptx::tma_load_2d(stage0 + s * kStageBytes, &p.tmap[issue_mat], bar0 + s * 8,
+        ptx::mbar_arrive_expect_tx(full0 + s * 8, kStageBytes);
+        ptx::tma_load_2d(stage0 + s * kStageBytes, &p.tmap[issue_mat], full0 + s * 8,
                          issue_chunk * kChunkBytes, tile_in_mat * kTileRows);
         if (++issue_chunk == chunks) {
             issue_chunk = 0;
             ++issue_tile;
         }
     };
-
     if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) ptx::mbar_init(bar0 + s * 8, 1);
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
         const int first = n_items < kStages ? n_items : kStages;
         for (int i = 0; i < first; ++i) issue(i);
     }
 
-    // ---- prologue: quantised activations into shared memory ------------------------------
+#ifdef LBK_TIMELINE
+    tl_a = clock64();  // after barrier init + first TMA issues
+#endif
+    // ---- prologue: quantised activations into shared memory (overlaps the first loads) -----
     float *s_part = reinterpret_cast<float *>(sm + L.part);
+    int *s_parti = reinterpret_cast<int *>(sm + L.parti);
     float *s_scale = reinterpret_cast<float *>(sm + L.scale);
     int *s_sum = reinterpret_cast<int *>(sm + L.sum);
     float *s_inv = reinterpret_cast<float *>(sm + L.inv);
     uint8_t *s_xq = sm + L.xq;
     const int m = p.m, k = p.k;
     const int kfill = chunks * kChunkCols;  // columns held per token row (zero padded)
+    int P = 1;
 
     if (p.x != nullptr) {
+        // P warps share a token row; kWarps/P rows are in flight at once.
+        P = m > 8 ? 1 : (m > 4 ? 2 : (m > 2 ? 4 : (m > 1 ? 8 : 16)));
+        const int rows_at_once = kWarps / P;
+        const int sub = warp % P, slot = warp / P;
+        const int idx = sub * 32 + lane, nthr = P * 32;
         const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
-        // pass 1: per-token absmax (quant.rs:101-104)
-        for (int tk = 0; tk < m; ++tk) {
-            const float *xr = p.x + static_cast<size_t>(tk) * k;
-            float am = 0.0f;
-            if (vec) {
-                const float4 *x4 = reinterpret_cast<const float4 *>(xr);
-                for (int i = tid; i < (k >> 2); i += kThreads) {
-                    float4 v = __ldg(x4 + i);
-                    am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-                }
-            } else {
-                for (int i = tid; i < k; i += kThreads) am = fmaxf(am, fabsf(__ldg(xr + i)));
+        const bool cached = vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV && m <= rows_at_once;
+        if (cached) {
+            // one row per warp group, read once and kept in registers across the reduction
+            RowCache rc;
+            const bool have = slot < m;
+            if (have) {
+                const float am = warp_max(absmax_cached(p.x + static_cast<size_t>(slot) * k, k, idx, nthr, rc));
+                if (lane == 0) s_part[slot * kWarps + sub] = am;
             }
-            am = warp_max(am);
-            if (lane == 0) s_part[tk * kWarps + warp] = am;
-        }
-        __syncthreads();
-        if (tid < m) {
-            float am = 0.0f;
-            for (int w = 0; w < kWarps; ++w) am = fmaxf(am, s_part[tid * kWarps + w]);
-            s_scale[tid] = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));  // quant.rs:105
-        }
-        __syncthreads();
-        // pass 2: quantise four columns per thread step, accumulate sum(q)
-        int *s_parti = reinterpret_cast<int *>(s_part);
-        for (int tk = 0; tk < m; ++tk) {
-            const float *xr = p.x + static_cast<size_t>(tk) * k;
-            const float sc = s_scale[tk];
-            uint8_t *dst = s_xq + static_cast<size_t>(tk) * p.xq_stride;
-            int acc = 0;
-            for (int i = tid * 4; i < kfill; i += kThreads * 4) {
-                int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
-                if (vec && i + 3 < k) {
-                    float4 v = __ldg(reinterpret_cast<const float4 *>(xr + i));
-                    q0 = quant_one(v.x, sc); q1 = quant_one(v.y, sc);
-                    q2 = quant_one(v.z, sc); q3 = quant_one(v.w, sc);
-                } else {
-                    if (i < k) q0 = quant_one(__ldg(xr + i), sc);
-                    if (i + 1 < k) q1 = quant_one(__ldg(xr + i + 1), sc);
-                    if (i + 2 < k) q2 = quant_one(__ldg(xr + i + 2), sc);
-                    if (i + 3 < k) q3 = quant_one(__ldg(xr + i + 3), sc);
+#ifdef LBK_TIMELINE
+            tl_b = clock64();  // row loaded, warp max done
+#endif
+            __syncthreads();
+#ifdef LBK_TIMELINE
+            tl_c = clock64();  // after the first CTA barrier
+#endif
+            if (have) {
+                float am = 0.0f;
+                for (int w = 0; w < P; ++w) am = fmaxf(am, s_part[slot * kWarps + w]);
+                const float sc = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));  // quant.rs:105
+                uint8_t *dst = s_xq + static_cast<size_t>(slot) * p.xq_stride;
+                int acc = quantize_cached(rc, kfill, sc, dst, idx, nthr);
+                zero_tail(dst, nthr * kCacheV * 4, kfill, idx, nthr);
+                acc = warp_sum(acc);
+                if (lane == 0) {
+                    s_parti[slot * kWarps + sub] = acc;
+                    if (sub == 0) s_scale[slot] = sc;
                 }
-                acc += q0 + q1 + q2 + q3;
-                uint32_t word = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) |
-                                (static_cast<uint32_t>(q3 & 255) << 24);
-                *reinterpret_cast<uint32_t *>(dst + xq_pos(i)) = word;
             }
-            acc = warp_sum(acc);
-            if (lane == 0) s_parti[tk * kWarps + warp] = acc;
+        } else {
+            // a warp serves at most two rows: tk = slot and slot + rows_at_once
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {  // quant.rs:101-104
+                const int tk = slot + r * rows_at_once;
+                if (tk < m) {
+                    float am = warp_max(absmax_span(p.x + static_cast<size_t>(tk) * k, k, vec, idx, nthr));
+                    if (lane == 0) s_part[tk * kWarps + sub] = am;
+                }
+            }
+            __syncthreads();
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                const int tk = slot + r * rows_at_once;
+                if (tk < m) {
+                    float am = 0.0f;
+                    for (int w = 0; w < P; ++w) am = fmaxf(am, s_part[tk * kWarps + w]);
+                    const float sc = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));  // quant.rs:105
+                    int acc = quantize_span(p.x + static_cast<size_t>(tk) * k, k, kfill, vec, sc,
+                                            s_xq + static_cast<size_t>(tk) * p.xq_stride, idx, nthr);
+                    acc = warp_sum(acc);
+                    if (lane == 0) {
+                        s_parti[tk * kWarps + sub] = acc;
+                        if (sub == 0) s_scale[tk] = sc;
+                    }
+                }
+            }
         }
+#ifdef LBK_TIMELINE
+        tl_d = clock64();  // quantised and stored
+#endif
         __syncthreads();
         if (tid < m) {
             int s = 0;
-            for (int w = 0; w < kWarps; ++w) s += s_parti[tid * kWarps + w];
+            for (int w = 0; w < P; ++w) s += s_parti[tid * kWarps + w];
             s_sum[tid] = s;
         }
     } else {
@@ -242,13 +238,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     __syncthreads();
 
     if (n_items == 0) return;
+#ifdef LBK_TIMELINE
+    tl_prologue = clock64();
+#endif
 
     // ---- main loop -----------------------------------------------------------------------
-    // Lane (g, t) reads 16-byte units 2t and 2t+1 of rows g and g+8 of the stage: block t of
-    // the chunk's four blocks, bytes 0..15 and 16..31. The 128B swizzle (unit ^= row & 7)
-    // spreads the eight lanes of a quarter warp over all banks.
-    const uint32_t offA = g * 128 + (((2 * t) ^ g) << 4);
-    const uint32_t offB = g * 128 + (((2 * t + 1) ^ g) << 4);
+    const LaneOffsets off = lane_offsets(lane);
     const uint8_t *xrow[MT];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -258,47 +253,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     }
     const uint8_t *stage_ptr = sm + L.stages + warp * (kStages * kStageBytes);
 
-    int acc[MT][4][4];
+    int acc[MT][2][4][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) acc[mt][kk][j] = 0;
+            for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[mt][h][kk][j] = 0;
 
     int tile = tile_begin, chunk = 0, mat = 0;
     int s = 0;
     uint32_t phase = 0;
     bool ok = true;
     for (int item = 0; item < n_items; ++item) {
-        if (!ptx::mbar_wait(bar0 + s * 8, phase, kWaitLimit)) {
+#ifdef LBK_TIMELINE
+        const long long tl_w0 = clock64();
+#endif
+        if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
             ok = false;
             break;
         }
-        const uint8_t *st = stage_ptr + s * kStageBytes;
-        const uint4 W0 = *reinterpret_cast<const uint4 *>(st + offA);
-        const uint4 W1 = *reinterpret_cast<const uint4 *>(st + offB);
-        const uint4 V0 = *reinterpret_cast<const uint4 *>(st + 1024 + offA);
-        const uint4 V1 = *reinterpret_cast<const uint4 *>(st + 1024 + offB);
-        const uint32_t wlo[4] = {W0.x, W0.z, W1.x, W1.z};  // row g,   first word of pair c
-        const uint32_t whi[4] = {W0.y, W0.w, W1.y, W1.w};  // row g,   second word
-        const uint32_t vlo[4] = {V0.x, V0.z, V1.x, V1.z};  // row g+8
-        const uint32_t vhi[4] = {V0.y, V0.w, V1.y, V1.w};
-        const uint32_t xoff = static_cast<uint32_t>(chunk) * kChunkCols;
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {
-            const uint32_t mask = 0x03030303u << (2 * kk);
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const uint32_t a0 = wlo[c] & mask, a1 = vlo[c] & mask;
-                const uint32_t a2 = whi[c] & mask, a3 = vhi[c] & mask;
-#pragma unroll
-                for (int mt = 0; mt < MT; ++mt) {
-                    const uint2 b = *reinterpret_cast<const uint2 *>(xrow[mt] + xoff + ((kk * 4 + c) << 5));
-                    ptx::mma_u8s8(acc[mt][kk], a0, a1, a2, a3, b.x, b.y);
-                }
-            }
-        }
+#ifdef LBK_TIMELINE
+        if (item == 0) tl_first = clock64();
+        else tl_polls += clock64() - tl_w0;  // cycles spent waiting for data after the first item
+#endif
+        consume_stage<MT>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
         __syncwarp();  // every lane has read the stage before it is refilled
         if (lane == 0 && item + kStages < n_items) issue(s);
         if (++s == kStages) {
@@ -317,8 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    const int v = acc[mt][0][j] + (acc[mt][1][j] >> 2) + (acc[mt][2][j] >> 4) +
-                                  (acc[mt][3][j] >> 6);
+                    const int v = take_acc<MT>(acc, mt, j);
                     const int row = row0 + g + ((j & 2) ? 8 : 0);
                     const int tok = mt * 8 + 2 * t + (j & 1);
                     if (row < rows && tok < m) {
@@ -327,26 +307,39 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                         if (iout) iout[o] = d;
                         if (out) out[o] = __fmul_rn(__int2float_rn(d), s_inv[mat * kMaxM + tok]);
                     }
-#pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) acc[mt][kk][j] = 0;
                 }
             chunk = 0;
             ++tile;
         }
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 1);
+#ifdef LBK_TIMELINE
+    if (lane == 0 && p.timeline) {
+        unsigned long long gend;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gend));
+        long long *d = p.timeline + gw * 16;
+        d[0] = tl_prologue - tl_start; d[1] = tl_first - tl_prologue; d[2] = clock64() - tl_first;
+        d[3] = n_items; d[4] = static_cast<long long>(tl_gstart); d[5] = static_cast<long long>(gend); d[6] = tl_polls; d[7] = blockIdx.x;
+        d[8] = tl_a - tl_start; d[9] = tl_b - tl_a; d[10] = tl_c - tl_b; d[11] = tl_d - tl_c; d[12] = tl_prologue - tl_d;
+    }
+#endif
 }
 
 }  // namespace
 
-static int xq_stride_for(size_t kp) {
+#ifdef LBK_TIMELINE
+static long long *g_timeline = nullptr;
+extern "C" void lbk_debug_set_timeline(long long *buf) { g_timeline = buf; }
+#endif
+
+int gemv_xq_stride(size_t kp) {
     const size_t chunks = (kp / 4 + kChunkBytes - 1) / kChunkBytes;
     return static_cast<int>(chunks * kChunkCols + 32);  // +32: token rows land on distinct banks
 }
 
 bool gemv_fits(const Ctx *ctx, size_t kp, size_t m) {
     if (m == 0 || m > kMaxM) return false;
-    const SmemLayout L = smem_layout(static_cast<int>(m), xq_stride_for(kp));
+    const SmemLayout L = smem_layout(static_cast<int>(m), gemv_xq_stride(kp));
     return static_cast<size_t>(L.total) + 1024 <= ctx->smem_optin;
 }
 
@@ -378,13 +371,16 @@ int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.m = static_cast<int>(g.m);
     p.k = static_cast<int>(cols);
     p.chunks = static_cast<int>((kp / 4 + kChunkBytes - 1) / kChunkBytes);
-    p.xq_stride = xq_stride_for(kp);
+    p.xq_stride = gemv_xq_stride(kp);
     p.total_tiles = tiles;
     p.x = g.x;
     p.q = g.q;
     p.qscale = g.qscale;
     p.qsum = g.qsum;
     p.err_word = ctx->err_word;
+#ifdef LBK_TIMELINE
+    p.timeline = g_timeline;
+#endif
     if (tiles == 0) return LBK_OK;
 
     const SmemLayout L = smem_layout(p.m, p.xq_stride);

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <vector>
 
 #include "lbk.h"
 
@@ -61,6 +62,7 @@ int ctx_scratch(Ctx *ctx, size_t bytes, void **out);
 int kernels_init(Ctx *ctx);
 int gemv_init(Ctx *ctx);
 int gemm_init(Ctx *ctx);
+int sweep_init(Ctx *ctx);
 int encode_weight_maps(Weight *w);
 
 // ---- launchers -----------------------------------------------------------------------
@@ -81,6 +83,14 @@ struct GroupArgs {
 // activations do not fit in shared memory next to the weight ring.
 int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
 bool gemv_fits(const Ctx *ctx, size_t kp, size_t m);
+
+int gemv_xq_stride(size_t kp);
+
+// Persistent sweep over recorded groups (lbk_sweep.cu).
+struct SweepTables;
+int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **out);
+int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream);
+void sweep_free(SweepTables *tb);
 
 int launch_quantize(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
                     int32_t *sum, cudaStream_t stream);

@@ -17,6 +17,9 @@ struct Plan {
     size_t x_elems = 0, y_elems = 0;
     size_t weight_bytes = 0;
     bool finalized = false;
+    // one persistent launch when every activation row fits a warp's slice of shared memory,
+    // else a CUDA graph of one fused launch per group
+    SweepTables *sweep = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
 };
@@ -24,6 +27,7 @@ struct Plan {
 int kernels_init(Ctx *ctx) {
     LBK_TRY(gemv_init(ctx));
     LBK_TRY(gemm_init(ctx));
+    LBK_TRY(sweep_init(ctx));
     return LBK_OK;
 }
 
@@ -58,6 +62,7 @@ int lbk_plan_add(lbk_plan *pl, const float *x_dev, const lbk_weight *const *ws, 
         const Weight *w = reinterpret_cast<const Weight *>(ws[i]);
         if (!w || w->ctx != p->ctx) return fail(LBK_ERR_INVALID, "matrix %zu is null or belongs to another context", i);
         if (w->cols != reinterpret_cast<const Weight *>(ws[0])->cols) return fail(LBK_ERR_SHAPE, "inner dimension mismatch in group");
+        if (w->cols == 0 || w->rows == 0) return fail(LBK_ERR_UNSUPPORTED, "plans take non-empty matrices");
         if (!arena && !outs_dev[i]) return fail(LBK_ERR_INVALID, "output %zu is null", i);
         g.w[i] = w;
         g.out[i] = arena ? nullptr : outs_dev[i];
@@ -96,6 +101,10 @@ int lbk_plan_finalize(lbk_plan *pl) {
         }
     }
     if (!p->groups.empty()) {
+        int st_sweep = sweep_build(ctx, p->groups, &p->sweep);
+        if (st_sweep != LBK_OK && st_sweep != LBK_ERR_UNSUPPORTED) return st_sweep;
+    }
+    if (!p->groups.empty() && !p->sweep) {
         cudaStream_t st = ctx->own_stream;
         LBK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
         int status = LBK_OK;
@@ -123,8 +132,9 @@ int lbk_plan_run(lbk_plan *pl, void *stream) {
     if (!pl) return fail(LBK_ERR_INVALID, "plan is null");
     Plan *p = reinterpret_cast<Plan *>(pl);
     if (!p->finalized) return fail(LBK_ERR_INVALID, "plan is not finalized");
-    if (!p->exec) return LBK_OK;
     LBK_CUDA(cudaSetDevice(p->ctx->device));
+    if (p->sweep) return sweep_launch(p->ctx, p->sweep, static_cast<cudaStream_t>(stream));
+    if (!p->exec) return LBK_OK;
     LBK_CUDA(cudaGraphLaunch(p->exec, static_cast<cudaStream_t>(stream)));
     p->ctx->launches += p->groups.size();
     return LBK_OK;
@@ -158,6 +168,7 @@ size_t lbk_plan_weight_bytes(const lbk_plan *pl) { return pl ? reinterpret_cast<
 int lbk_plan_destroy(lbk_plan *pl) {
     if (!pl) return LBK_OK;
     Plan *p = reinterpret_cast<Plan *>(pl);
+    if (p->sweep) sweep_free(p->sweep);
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
     if (p->x_arena) cudaFree(p->x_arena);

@@ -1,0 +1,417 @@
+// Persistent decode sweep: a whole recorded sequence of fused ternary-linear groups (one token
+// row each) in ONE launch.
+//
+// Stands in for the reference's per-token loop of 120 parallel regions
+// (crates/lb-ternary/benches/kbench.rs:148-194; crates/lb-model/src/model.rs:331-366 issues the
+// same four fused ops per layer). The concatenated weight stream of all groups is cut into
+// equal-byte runs of 16-row tiles, one run per warp (148 CTAs x 8 warps). A warp walks its run
+// with its own TMA ring; when the run crosses into another group the warp quantises that
+// group's activation row itself (absmax, scale, round-half-even, sum) into its private slice of
+// shared memory. No warp ever waits for another one, so groups must not depend on each other's
+// outputs. Arithmetic per output element is exactly that of the single-group kernel.
+#include <vector>
+
+#include "lbk_gemv_core.cuh"
+
+namespace lbk {
+
+using namespace gemv;
+
+constexpr int kMaxSlots = 4;  // groups one CTA's warps may touch (activation slots in shared memory)
+
+struct alignas(64) SweepMat {
+    CUtensorMap tmap;
+    float *out;
+    int32_t *iout;
+    float wscale;
+    int rows;
+    int pad_[10];
+};
+
+struct SweepGroup {
+    const float *x;
+    int k;
+    int chunks;
+    int n_mat;
+    int mat0;                      // index of the group's first SweepMat
+    int tile0;                     // global index of the group's first tile
+    int tiles;
+    int tile_end[LBK_MAX_GROUP];   // running count of 16-row tiles up to and including matrix i
+};
+
+struct SweepParams {
+    const SweepMat *mats;
+    const SweepGroup *groups;
+    const int4 *warp_run;    // [n_warps] {first tile, end tile, group of the first tile, unused}
+    const int2 *cta_groups;  // [grid] {first group, number of groups} touched by the CTA's warps
+    int xq_bytes;            // bytes per activation slot
+    int *err_word;
+#ifdef LBK_TIMELINE
+    long long *timeline;     // [warps][16] clock samples, debugging only
+#endif
+};
+
+namespace {
+
+// tile_end[i] without dynamic indexing (keeps the group record in registers)
+__device__ __forceinline__ int tile_end_of(const SweepGroup &g, int i) {
+    return i == 0 ? g.tile_end[0] : (i == 1 ? g.tile_end[1] : (i == 2 ? g.tile_end[2] : g.tile_end[3]));
+}
+
+// Every warp walks its own run of tiles; its lane 0 keeps the warp's TMA ring full. The
+// activation rows of the (at most kMaxSlots) groups the CTA touches are quantised once, by the
+// whole CTA, while the first loads are in flight.
+__global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int gw = blockIdx.x * kWarps + warp;
+#ifdef LBK_TIMELINE
+    long long tl_start = clock64(), tl_setup = 0, tl_quant = 0, tl_wait = 0, tl_items = 0, tl_nq = 0;
+    unsigned long long tl_g0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_g0));
+#endif
+    const int4 run = __ldg(p.warp_run + gw);
+    const int t_begin = run.x, t_end = run.y;
+    const int2 cg2 = __ldg(p.cta_groups + blockIdx.x);
+    const int slot_g0 = cg2.x, n_slots = cg2.y;
+
+    constexpr uint32_t kRing = kStages * kStageBytes;
+    const uint32_t stage0 = base + warp * kRing;
+    const uint8_t *stage_ptr = sm + warp * kRing;
+    const uint32_t full0 = base + kWarps * kRing + warp * (kStages * 8);
+    uint8_t *s_misc = sm + kWarps * kRing + kWarps * kStages * 8;       // reductions, scales, sums
+    float *s_part = reinterpret_cast<float *>(s_misc);                  // [kMaxSlots][4]
+    int *s_parti = reinterpret_cast<int *>(s_misc + 64);                // [kMaxSlots][4]
+    float *s_scale = reinterpret_cast<float *>(s_misc + 128);           // [kMaxSlots]
+    int *s_sum = reinterpret_cast<int *>(s_misc + 144);                 // [kMaxSlots]
+    uint8_t *s_xq = s_misc + 256;                                       // [kMaxSlots][xq_bytes]
+
+    // ---- issue cursor (meaningful on lane 0 only) -----------------------------------------
+    int ig = run.z;
+    SweepGroup igrp = p.groups[t_begin < t_end ? ig : 0];
+    int itile = t_begin, ichunk = 0, imat = 0;
+    auto issue = [&](int s) {
+        while (itile >= igrp.tile0 + igrp.tiles) {
+            igrp = p.groups[++ig];
+            imat = 0;
+        }
+        const int local = itile - igrp.tile0;
+        while (imat < igrp.n_mat - 1 && local >= tile_end_of(igrp, imat)) ++imat;
+        const int tile_in_mat = local - (imat ? tile_end_of(igrp, imat - 1) : 0);
+        ptx::mbar_arrive_expect_tx(full0 + s * 8, kStageBytes);
+        ptx::tma_load_2d(stage0 + s * kStageBytes, &p.mats[igrp.mat0 + imat].tmap, full0 + s * 8,
+                         ichunk * kChunkBytes, tile_in_mat * kTileRows);
+        if (++ichunk == igrp.chunks) {
+            ichunk = 0;
+            ++itile;
+        }
+    };
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
+        ptx::fence_barrier_init();
+        for (int s = 0; s < kStages && itile < t_end; ++s) issue(s);
+    }
+#ifdef LBK_TIMELINE
+    tl_setup = clock64() - tl_start;
+#endif
+
+    // ---- CTA prologue: quantise the activation row of every group this CTA touches ----------
+    // (quant.rs:100-118). Four warps per slot; rows of up to 4096 columns are read once.
+    {
+        const int slot = warp >> 2, sub = warp & 3;
+        const int idx = sub * 32 + lane, nthr = 128;
+        const bool have = slot < n_slots;
+        const float *x = nullptr;
+        int k = 0, kfill = 0;
+        bool vec = false, cached = false;
+        RowCache rc;
+        if (have) {
+            const SweepGroup *gp = p.groups + slot_g0 + slot;
+            x = gp->x;
+            k = __ldg(&gp->k);
+            kfill = __ldg(&gp->chunks) * kChunkCols;
+            vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+            cached = vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV;
+            const float am = warp_max(cached ? absmax_cached(x, k, idx, nthr, rc) : absmax_span(x, k, vec, idx, nthr));
+            if (lane == 0) s_part[slot * 4 + sub] = am;
+        }
+        __syncthreads();
+        if (have) {
+            const float am = fmaxf(fmaxf(s_part[slot * 4], s_part[slot * 4 + 1]), fmaxf(s_part[slot * 4 + 2], s_part[slot * 4 + 3]));
+            const float sc = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));
+            uint8_t *dst = s_xq + static_cast<size_t>(slot) * p.xq_bytes;
+            int acc;
+            if (cached) {
+                acc = quantize_cached(rc, kfill, sc, dst, idx, nthr);
+                zero_tail(dst, nthr * kCacheV * 4, kfill, idx, nthr);
+            } else {
+                acc = quantize_span(x, k, kfill, vec, sc, dst, idx, nthr);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) {
+                s_parti[slot * 4 + sub] = acc;
+                if (sub == 0) s_scale[slot] = sc;
+            }
+        }
+        __syncthreads();
+        if (tid < n_slots) s_sum[tid] = s_parti[tid * 4] + s_parti[tid * 4 + 1] + s_parti[tid * 4 + 2] + s_parti[tid * 4 + 3];
+        __syncthreads();
+    }
+#ifdef LBK_TIMELINE
+    tl_quant = clock64() - tl_start - tl_setup;
+#endif
+    if (t_begin >= t_end) return;
+
+    // ---- consume cursor ----------------------------------------------------------------
+    const LaneOffsets off = lane_offsets(lane);
+    const uint8_t *xrow[1] = {s_xq + t * 8};
+    int acc[1][2][4][4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[0][h][kk][j] = 0;
+
+    int cg = run.z - 1;  // forces the first group set-up
+    SweepGroup cgrp{};
+    int cmat = -1, mat_tile_base = 0, mat_tile_end = 0, rows = 0;
+    float *out = nullptr;
+    int32_t *iout = nullptr;
+    float a_scale = 0.0f, inv = 0.0f;
+    int a_sum = 0;
+    int chunk = 0, s = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+
+    for (int tile = t_begin; tile < t_end;) {
+        if (tile >= cgrp.tile0 + cgrp.tiles) {
+            // ---- the run enters another group: switch to its activation slot
+            do {
+                cgrp = p.groups[++cg];
+            } while (tile >= cgrp.tile0 + cgrp.tiles);
+            const int slot = cg - slot_g0;
+            xrow[0] = s_xq + static_cast<size_t>(slot) * p.xq_bytes + t * 8;
+            a_scale = s_scale[slot];
+            a_sum = s_sum[slot];
+            cmat = -1;
+        }
+#ifdef LBK_TIMELINE
+        const long long tw0 = clock64();
+#endif
+        if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
+            ok = false;
+            break;
+        }
+#ifdef LBK_TIMELINE
+        tl_wait += clock64() - tw0;
+        ++tl_items;
+#endif
+        consume_stage<1>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
+        __syncwarp();  // every lane has read the stage before it is refilled
+        if (lane == 0 && itile < t_end) issue(s);
+        if (++s == kStages) {
+            s = 0;
+            phase ^= 1;
+        }
+        if (++chunk == cgrp.chunks) {
+            // ---- tile epilogue: dot = acc - sum(q), y = (float)dot * (1/(s_a*s_w)) -------------
+            const int local = tile - cgrp.tile0;
+            if (cmat < 0 || local >= mat_tile_end) {
+                if (cmat < 0) cmat = 0;
+                while (cmat < cgrp.n_mat - 1 && local >= tile_end_of(cgrp, cmat)) ++cmat;
+                mat_tile_end = tile_end_of(cgrp, cmat);
+                mat_tile_base = cmat ? tile_end_of(cgrp, cmat - 1) : 0;
+                const SweepMat *mt = p.mats + cgrp.mat0 + cmat;
+                rows = __ldg(&mt->rows);
+                out = mt->out;
+                iout = mt->iout;
+                inv = __fdiv_rn(1.0f, __fmul_rn(a_scale, __ldg(&mt->wscale)));  // gemm.rs:141
+            }
+            const int row0 = (local - mat_tile_base) * kTileRows;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int v = take_acc<1>(acc, 0, j);
+                const int row = row0 + g + ((j & 2) ? 8 : 0);
+                if (t == 0 && (j & 1) == 0 && row < rows) {  // token 0 lives in column 0 of the tile
+                    const int d = v - a_sum;
+                    if (iout) iout[row] = d;
+                    if (out) out[row] = __fmul_rn(__int2float_rn(d), inv);
+                }
+            }
+            chunk = 0;
+            ++tile;
+        }
+    }
+    if (!ok && lane == 0) atomicExch(p.err_word, 2);
+#ifdef LBK_TIMELINE
+    if (lane == 0 && p.timeline) {
+        unsigned long long g1;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g1));
+        long long *d = p.timeline + static_cast<long long>(gw) * 16;
+        d[0] = tl_setup; d[1] = tl_quant; d[2] = tl_wait; d[3] = tl_items; d[4] = static_cast<long long>(tl_g0);
+        d[5] = static_cast<long long>(g1); d[6] = clock64() - tl_start; d[7] = tl_nq;
+    }
+#endif
+}
+
+}  // namespace
+
+// ---- host side: tables and launch ---------------------------------------------------------
+
+struct SweepTables {
+    SweepMat *mats = nullptr;
+    SweepGroup *groups = nullptr;
+    int4 *warp_run = nullptr;
+    int2 *cta_groups = nullptr;
+    int xq_bytes = 0;
+    int grid = 0;
+    size_t smem = 0;
+};
+
+void sweep_free(SweepTables *t) {
+    if (!t) return;
+    cudaFree(t->mats);
+    cudaFree(t->groups);
+    cudaFree(t->warp_run);
+    cudaFree(t->cta_groups);
+    delete t;
+}
+
+int sweep_init(Ctx *ctx) {
+    LBK_CUDA(cudaFuncSetAttribute(sweep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  static_cast<int>(ctx->smem_optin)));
+    return LBK_OK;
+}
+
+// Builds the device tables for `groups` (each with m == 1 and f32 input). Returns
+// LBK_ERR_UNSUPPORTED when a group's activation row does not fit the per-warp slice.
+int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **out) {
+    *out = nullptr;
+    std::vector<SweepMat> mats;
+    std::vector<SweepGroup> grps;
+    std::vector<int> tile_chunks;  // per global tile: stages it costs
+    int max_chunks = 0, tiles_total = 0;
+    for (const GroupArgs &g : groups) {
+        SweepGroup sg{};
+        sg.x = g.x;
+        sg.k = static_cast<int>(g.w[0]->cols);
+        sg.chunks = static_cast<int>((g.w[0]->rb + kChunkBytes - 1) / kChunkBytes);
+        sg.n_mat = g.n;
+        sg.mat0 = static_cast<int>(mats.size());
+        sg.tile0 = tiles_total;
+        int t = 0;
+        for (int i = 0; i < g.n; ++i) {
+            SweepMat sm{};
+            sm.tmap = g.w[i]->tmap_gemv;
+            sm.out = g.out[i];
+            sm.iout = g.iout[i];
+            sm.wscale = g.w[i]->scale;
+            sm.rows = static_cast<int>(g.w[i]->rows);
+            t += static_cast<int>((g.w[i]->rows + kTileRows - 1) / kTileRows);
+            sg.tile_end[i] = t;
+            mats.push_back(sm);
+        }
+        sg.tiles = t;
+        tiles_total += t;
+        for (int i = 0; i < t; ++i) tile_chunks.push_back(sg.chunks);
+        if (sg.chunks > max_chunks) max_chunks = sg.chunks;
+        if (t > 0 && sg.chunks > 0) grps.push_back(sg);
+        else mats.resize(sg.mat0);
+    }
+    SweepTables *tb = new SweepTables();
+    tb->xq_bytes = max_chunks * kChunkCols;
+    tb->smem = static_cast<size_t>(kWarps) * (kStages * kStageBytes + kStages * 8) + 256 +
+               static_cast<size_t>(kMaxSlots) * tb->xq_bytes + 1024;
+    if (tb->smem > ctx->smem_optin) {
+        delete tb;
+        return fail(LBK_ERR_UNSUPPORTED, "sweep: %d columns per activation row need %zu B of shared memory (limit %zu)",
+                    max_chunks * kChunkCols, tb->smem, ctx->smem_optin);
+    }
+    if (grps.empty()) {
+        *out = tb;
+        return LBK_OK;
+    }
+    // equal-cost runs: warp w starts at the first tile whose cumulative cost reaches w/nw of the total
+    const int grid = ctx->sm_count;
+    const int nw = grid * kWarps;
+    long long total = 0;
+    for (int c : tile_chunks) total += c;
+    std::vector<int> wt(nw + 1), wg(nw);
+    {
+        long long cum = 0;
+        int tile = 0;
+        for (int w = 0; w < nw; ++w) {
+            const long long target = total * w / nw;
+            while (tile < tiles_total && cum < target) cum += tile_chunks[tile++];
+            wt[w] = tile;
+        }
+        wt[nw] = tiles_total;
+        size_t gi = 0;
+        for (int w = 0; w < nw; ++w) {
+            while (gi + 1 < grps.size() && wt[w] >= grps[gi].tile0 + grps[gi].tiles) ++gi;
+            wg[w] = static_cast<int>(gi);
+        }
+    }
+    std::vector<int4> runs(nw);
+    std::vector<int2> ctas(grid);
+    for (int w = 0; w < nw; ++w) runs[w] = make_int4(wt[w], wt[w + 1], wg[w], 0);
+    for (int c = 0; c < grid; ++c) {
+        // groups between the CTA's first tile and its last one
+        const int first_tile = wt[c * kWarps], end_tile = wt[(c + 1) * kWarps];
+        int g0 = wg[c * kWarps], g1 = g0;
+        if (end_tile > first_tile)
+            while (g1 + 1 < static_cast<int>(grps.size()) && end_tile - 1 >= grps[g1].tile0 + grps[g1].tiles) ++g1;
+        const int n = end_tile > first_tile ? g1 - g0 + 1 : 0;
+        if (n > kMaxSlots) {
+            delete tb;
+            return fail(LBK_ERR_UNSUPPORTED, "sweep: a CTA's run spans %d groups (limit %d); groups are too small", n, kMaxSlots);
+        }
+        ctas[c] = make_int2(g0, n);
+    }
+    tb->grid = grid;
+    cudaError_t e = cudaMalloc(&tb->mats, mats.size() * sizeof(SweepMat));
+    if (e == cudaSuccess) e = cudaMalloc(&tb->groups, grps.size() * sizeof(SweepGroup));
+    if (e == cudaSuccess) e = cudaMalloc(&tb->warp_run, runs.size() * sizeof(int4));
+    if (e == cudaSuccess) e = cudaMalloc(&tb->cta_groups, ctas.size() * sizeof(int2));
+    if (e == cudaSuccess) e = cudaMemcpy(tb->mats, mats.data(), mats.size() * sizeof(SweepMat), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(tb->groups, grps.data(), grps.size() * sizeof(SweepGroup), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(tb->warp_run, runs.data(), runs.size() * sizeof(int4), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(tb->cta_groups, ctas.data(), ctas.size() * sizeof(int2), cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        sweep_free(tb);
+        return fail(LBK_ERR_CUDA, "sweep tables: %s", cudaGetErrorString(e));
+    }
+    *out = tb;
+    return LBK_OK;
+}
+
+#ifdef LBK_TIMELINE
+static long long *g_sweep_timeline = nullptr;
+extern "C" void lbk_debug_set_sweep_timeline(long long *buf) { g_sweep_timeline = buf; }
+#endif
+
+int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream) {
+    if (!tb || tb->grid == 0) return LBK_OK;
+    SweepParams p{};
+    p.mats = tb->mats;
+    p.groups = tb->groups;
+    p.warp_run = tb->warp_run;
+    p.cta_groups = tb->cta_groups;
+    p.xq_bytes = tb->xq_bytes;
+    p.err_word = ctx->err_word;
+#ifdef LBK_TIMELINE
+    p.timeline = g_sweep_timeline;
+#endif
+    sweep_kernel<<<tb->grid, kThreads, tb->smem, stream>>>(p);
+    LBK_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return LBK_OK;
+}
+
+}  // namespace lbk
