@@ -121,6 +121,19 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             ++issue_tile;
         }
     };
+    // The activation row loads are issued before lane 0 sets up the ring, so that both latency
+    // chains (row from L2, first TMA issues) run side by side. P warps share a token row;
+    // kWarps/P rows are in flight at once.
+    const int m = p.m, k = p.k;
+    const int P = m > 8 ? 1 : (m > 4 ? 2 : (m > 2 ? 4 : (m > 1 ? 8 : 16)));
+    const int rows_at_once = kWarps / P;
+    const int sub = warp % P, slot = warp / P;
+    const int idx = sub * 32 + lane, nthr = P * 32;
+    const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+    const bool cached = p.x != nullptr && vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV && m <= rows_at_once;
+    RowCache rc;
+    if (cached && slot < m) load_cached(p.x + static_cast<size_t>(slot) * k, k, idx, nthr, rc);
+
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
@@ -138,24 +151,14 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     int *s_sum = reinterpret_cast<int *>(sm + L.sum);
     float *s_inv = reinterpret_cast<float *>(sm + L.inv);
     uint8_t *s_xq = sm + L.xq;
-    const int m = p.m, k = p.k;
     const int kfill = chunks * kChunkCols;  // columns held per token row (zero padded)
-    int P = 1;
 
     if (p.x != nullptr) {
-        // P warps share a token row; kWarps/P rows are in flight at once.
-        P = m > 8 ? 1 : (m > 4 ? 2 : (m > 2 ? 4 : (m > 1 ? 8 : 16)));
-        const int rows_at_once = kWarps / P;
-        const int sub = warp % P, slot = warp / P;
-        const int idx = sub * 32 + lane, nthr = P * 32;
-        const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
-        const bool cached = vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV && m <= rows_at_once;
         if (cached) {
             // one row per warp group, read once and kept in registers across the reduction
-            RowCache rc;
             const bool have = slot < m;
             if (have) {
-                const float am = warp_max(absmax_cached(p.x + static_cast<size_t>(slot) * k, k, idx, nthr, rc));
+                const float am = warp_max(max_cached(rc));
                 if (lane == 0) s_part[slot * kWarps + sub] = am;
             }
 #ifdef LBK_TIMELINE

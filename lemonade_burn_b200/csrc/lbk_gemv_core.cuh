@@ -108,15 +108,25 @@ constexpr int kCacheV = 8;
 struct RowCache {
     float4 v[kCacheV];
 };
-__device__ __forceinline__ float absmax_cached(const float *xr, int k, int idx, int nthr, RowCache &rc) {
+__device__ __forceinline__ void load_cached(const float *xr, int k, int idx, int nthr, RowCache &rc) {
     const float4 *x4 = reinterpret_cast<const float4 *>(xr);
     const int n4 = k >> 2;
-    float am = 0.0f;
 #pragma unroll
     for (int j = 0; j < kCacheV; ++j) {
         const int i = idx + j * nthr;
         rc.v[j] = i < n4 ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
+}
+__device__ __forceinline__ float max_cached(const RowCache &rc) {
+    float am = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kCacheV; ++j)
+        am = fmaxf(am, fmaxf(fmaxf(fabsf(rc.v[j].x), fabsf(rc.v[j].y)), fmaxf(fabsf(rc.v[j].z), fabsf(rc.v[j].w))));
+    return am;
+}
+__device__ __forceinline__ float absmax_cached(const float *xr, int k, int idx, int nthr, RowCache &rc) {
+    load_cached(xr, k, idx, nthr, rc);
+    float am = 0.0f;
 #pragma unroll
     for (int j = 0; j < kCacheV; ++j)
         am = fmaxf(am, fmaxf(fmaxf(fabsf(rc.v[j].x), fabsf(rc.v[j].y)), fmaxf(fabsf(rc.v[j].z), fabsf(rc.v[j].w))));

@@ -39,11 +39,25 @@ struct SweepGroup {
     int tile_end[LBK_MAX_GROUP];   // running count of 16-row tiles up to and including matrix i
 };
 
+// What a CTA needs to quantise one activation row, in one 16-byte load.
+struct alignas(16) SlotRec {
+    const float *x;
+    int k;
+    int chunks;
+};
+
+struct alignas(16) CtaRec {
+    int group0;   // first group the CTA's warps touch
+    int n_slots;  // how many groups they touch (<= kMaxSlots)
+    int pad_[2];
+    SlotRec slot[kMaxSlots];
+};
+
 struct SweepParams {
     const SweepMat *mats;
     const SweepGroup *groups;
     const int4 *warp_run;    // [n_warps] {first tile, end tile, group of the first tile, unused}
-    const int2 *cta_groups;  // [grid] {first group, number of groups} touched by the CTA's warps
+    const CtaRec *cta;       // [grid]
     int xq_bytes;            // bytes per activation slot
     int *err_word;
 #ifdef LBK_TIMELINE
@@ -77,8 +91,30 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
 #endif
     const int4 run = __ldg(p.warp_run + gw);
     const int t_begin = run.x, t_end = run.y;
-    const int2 cg2 = __ldg(p.cta_groups + blockIdx.x);
-    const int slot_g0 = cg2.x, n_slots = cg2.y;
+    const int4 chead = __ldg(reinterpret_cast<const int4 *>(p.cta + blockIdx.x));
+    const int slot_g0 = chead.x, n_slots = chead.y;
+
+    // Two chains of dependent loads start here and are interleaved on purpose: (a) this warp
+    // group's activation row (slot record -> row), (b) lane 0's first TMA loads (group record ->
+    // tensor map). The row loads are issued first and consumed after the TMA issue.
+    const int q_slot = warp >> 2, q_sub = warp & 3;
+    const int q_idx = q_sub * 32 + lane;
+    constexpr int q_nthr = 128;
+    const bool q_have = q_slot < n_slots;
+    const float *q_x = nullptr;
+    int q_k = 0, q_kfill = 0;
+    bool q_vec = false, q_cached = false;
+    RowCache rc;
+    if (q_have) {
+        const int4 rec = __ldg(reinterpret_cast<const int4 *>(&p.cta[blockIdx.x].slot[q_slot]));
+        q_x = reinterpret_cast<const float *>((static_cast<unsigned long long>(static_cast<unsigned>(rec.y)) << 32) |
+                                              static_cast<unsigned>(rec.x));
+        q_k = rec.z;
+        q_kfill = rec.w * kChunkCols;
+        q_vec = (q_k & 3) == 0 && (reinterpret_cast<uintptr_t>(q_x) & 15) == 0;
+        q_cached = q_vec && ((q_k >> 2) + q_nthr - 1) / q_nthr <= kCacheV;
+        if (q_cached) load_cached(q_x, q_k, q_idx, q_nthr, rc);
+    }
 
     constexpr uint32_t kRing = kStages * kStageBytes;
     const uint32_t stage0 = base + warp * kRing;
@@ -123,39 +159,27 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     // ---- CTA prologue: quantise the activation row of every group this CTA touches ----------
     // (quant.rs:100-118). Four warps per slot; rows of up to 4096 columns are read once.
     {
-        const int slot = warp >> 2, sub = warp & 3;
-        const int idx = sub * 32 + lane, nthr = 128;
-        const bool have = slot < n_slots;
-        const float *x = nullptr;
-        int k = 0, kfill = 0;
-        bool vec = false, cached = false;
-        RowCache rc;
-        if (have) {
-            const SweepGroup *gp = p.groups + slot_g0 + slot;
-            x = gp->x;
-            k = __ldg(&gp->k);
-            kfill = __ldg(&gp->chunks) * kChunkCols;
-            vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
-            cached = vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV;
-            const float am = warp_max(cached ? absmax_cached(x, k, idx, nthr, rc) : absmax_span(x, k, vec, idx, nthr));
-            if (lane == 0) s_part[slot * 4 + sub] = am;
+        if (q_have) {
+            const float am = warp_max(q_cached ? max_cached(rc) : absmax_span(q_x, q_k, q_vec, q_idx, q_nthr));
+            if (lane == 0) s_part[q_slot * 4 + q_sub] = am;
         }
         __syncthreads();
-        if (have) {
-            const float am = fmaxf(fmaxf(s_part[slot * 4], s_part[slot * 4 + 1]), fmaxf(s_part[slot * 4 + 2], s_part[slot * 4 + 3]));
+        if (q_have) {
+            const float am = fmaxf(fmaxf(s_part[q_slot * 4], s_part[q_slot * 4 + 1]),
+                                   fmaxf(s_part[q_slot * 4 + 2], s_part[q_slot * 4 + 3]));
             const float sc = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));
-            uint8_t *dst = s_xq + static_cast<size_t>(slot) * p.xq_bytes;
+            uint8_t *dst = s_xq + static_cast<size_t>(q_slot) * p.xq_bytes;
             int acc;
-            if (cached) {
-                acc = quantize_cached(rc, kfill, sc, dst, idx, nthr);
-                zero_tail(dst, nthr * kCacheV * 4, kfill, idx, nthr);
+            if (q_cached) {
+                acc = quantize_cached(rc, q_kfill, sc, dst, q_idx, q_nthr);
+                zero_tail(dst, q_nthr * kCacheV * 4, q_kfill, q_idx, q_nthr);
             } else {
-                acc = quantize_span(x, k, kfill, vec, sc, dst, idx, nthr);
+                acc = quantize_span(q_x, q_k, q_kfill, q_vec, sc, dst, q_idx, q_nthr);
             }
             acc = warp_sum(acc);
             if (lane == 0) {
-                s_parti[slot * 4 + sub] = acc;
-                if (sub == 0) s_scale[slot] = sc;
+                s_parti[q_slot * 4 + q_sub] = acc;
+                if (q_sub == 0) s_scale[q_slot] = sc;
             }
         }
         __syncthreads();
@@ -268,7 +292,7 @@ struct SweepTables {
     SweepMat *mats = nullptr;
     SweepGroup *groups = nullptr;
     int4 *warp_run = nullptr;
-    int2 *cta_groups = nullptr;
+    CtaRec *cta = nullptr;
     int xq_bytes = 0;
     int grid = 0;
     size_t smem = 0;
@@ -279,7 +303,7 @@ void sweep_free(SweepTables *t) {
     cudaFree(t->mats);
     cudaFree(t->groups);
     cudaFree(t->warp_run);
-    cudaFree(t->cta_groups);
+    cudaFree(t->cta);
     delete t;
 }
 
@@ -359,7 +383,7 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
         }
     }
     std::vector<int4> runs(nw);
-    std::vector<int2> ctas(grid);
+    std::vector<CtaRec> ctas(grid);
     for (int w = 0; w < nw; ++w) runs[w] = make_int4(wt[w], wt[w + 1], wg[w], 0);
     for (int c = 0; c < grid; ++c) {
         // groups between the CTA's first tile and its last one
@@ -372,17 +396,25 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
             delete tb;
             return fail(LBK_ERR_UNSUPPORTED, "sweep: a CTA's run spans %d groups (limit %d); groups are too small", n, kMaxSlots);
         }
-        ctas[c] = make_int2(g0, n);
+        CtaRec rec{};
+        rec.group0 = g0;
+        rec.n_slots = n;
+        for (int i = 0; i < n; ++i) {
+            rec.slot[i].x = grps[g0 + i].x;
+            rec.slot[i].k = grps[g0 + i].k;
+            rec.slot[i].chunks = grps[g0 + i].chunks;
+        }
+        ctas[c] = rec;
     }
     tb->grid = grid;
     cudaError_t e = cudaMalloc(&tb->mats, mats.size() * sizeof(SweepMat));
     if (e == cudaSuccess) e = cudaMalloc(&tb->groups, grps.size() * sizeof(SweepGroup));
     if (e == cudaSuccess) e = cudaMalloc(&tb->warp_run, runs.size() * sizeof(int4));
-    if (e == cudaSuccess) e = cudaMalloc(&tb->cta_groups, ctas.size() * sizeof(int2));
+    if (e == cudaSuccess) e = cudaMalloc(&tb->cta, ctas.size() * sizeof(CtaRec));
     if (e == cudaSuccess) e = cudaMemcpy(tb->mats, mats.data(), mats.size() * sizeof(SweepMat), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(tb->groups, grps.data(), grps.size() * sizeof(SweepGroup), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(tb->warp_run, runs.data(), runs.size() * sizeof(int4), cudaMemcpyHostToDevice);
-    if (e == cudaSuccess) e = cudaMemcpy(tb->cta_groups, ctas.data(), ctas.size() * sizeof(int2), cudaMemcpyHostToDevice);
+    if (e == cudaSuccess) e = cudaMemcpy(tb->cta, ctas.data(), ctas.size() * sizeof(CtaRec), cudaMemcpyHostToDevice);
     if (e != cudaSuccess) {
         sweep_free(tb);
         return fail(LBK_ERR_CUDA, "sweep tables: %s", cudaGetErrorString(e));
@@ -402,7 +434,7 @@ int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream) {
     p.mats = tb->mats;
     p.groups = tb->groups;
     p.warp_run = tb->warp_run;
-    p.cta_groups = tb->cta_groups;
+    p.cta = tb->cta;
     p.xq_bytes = tb->xq_bytes;
     p.err_word = ctx->err_word;
 #ifdef LBK_TIMELINE
