@@ -1,0 +1,102 @@
+"""Prefill path (more than 16 token rows -> tcgen05 int8 GEMM) against the oracle, through the
+C ABI. Integers bit-exact, f32 bit-exact (same epilogue order as gemm.rs:158,178), 1e-3 relative
+as the documented bound. Shapes follow BASELINE config 2 (K=2560->N=6912, K=6912->N=2560) plus
+the reference's padded / token-tile / extreme cases (crates/lb-ternary/tests/golden.rs)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 1e-3
+
+
+def T():
+    from lemonade_burn_b200 import ternary
+    return ternary
+
+
+def run_case(o, ctx, t, ws, p, x):
+    rows, cols = t.shape
+    m = x.shape[0]
+    dw = T().DeviceWeight(T().TernaryView(rows, cols, p.reshape(-1), float(ws)), ctx)
+    outs, iouts = T().ternary_linear_host(x, [dw], want_i32=True, ctx=ctx)
+    q, s, ssum = o.quantize_acts(x)
+    wf, wi = o.simd_gemm_multi([p], [ws], q, s, ssum, want_i32=True)
+    assert np.array_equal(iouts[0], wi[0])
+    assert np.array_equal(outs[0].view(np.uint32), wf[0].view(np.uint32))
+    assert np.allclose(outs[0], wf[0], rtol=REL_TOL, atol=0)
+    ctx.check_device_error()
+
+
+@pytest.mark.parametrize("rows,cols,m,seed", [(23, 384, 17, 1), (37, 2560, 40, 78), (300, 640, 64, 3), (257, 128, 129, 4),
+                                               (5, 300, 33, 5), (5, 1, 20, 6), (130, 300, 130, 2)])
+def test_small_and_padded(oracle, ctx, rows, cols, m, seed):
+    run_case(oracle, ctx, *oracle.golden_case(rows, cols, m, seed))
+
+
+def random_case(rows, cols, m, seed, oracle):
+    rng = np.random.default_rng(seed)
+    t = rng.choice(np.array([-1, 0, 1], dtype=np.int8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+    x = rng.standard_normal((m, cols)).astype(np.float32)
+    return t, np.float32(62.66), oracle.pack_matrix(t), x
+
+
+@pytest.mark.parametrize("rows,cols,m", [(6912, 2560, 64), (2560, 6912, 64), (6912, 2560, 256)])
+def test_config2_shapes(oracle, ctx, rows, cols, m):
+    run_case(oracle, ctx, *random_case(rows, cols, m, rows + m, oracle))
+
+
+def test_extreme_long_rows(oracle, ctx):
+    # golden.rs:181-194 at a prefill token count: all +1 weights, +-1 activations, K = 13824
+    rows, cols, m = 3, 6912 * 2, 40
+    p = oracle.pack_matrix(np.ones((rows, cols), dtype=np.int8))
+    dw = T().DeviceWeight(T().TernaryView(rows, cols, p.reshape(-1), 1.0), ctx)
+    for sign in (1.0, -1.0):
+        outs, iouts = T().ternary_linear_host(np.full((m, cols), sign, dtype=np.float32), [dw], want_i32=True, ctx=ctx)
+        assert (iouts[0] == int(sign) * 127 * cols).all()
+        assert (outs[0] == np.float32(sign * cols)).all()
+
+
+def test_code3_and_multi(oracle, ctx):
+    """Random packed bytes (code 3 decodes to +2, pack.rs:7-8) in a fused q/k/v-like group."""
+    rng = np.random.default_rng(11)
+    cols, m = 640, 70
+    mats = []
+    for rows, sc in [(96, 0.7), (24, 1.3), (300, 2.1)]:
+        p = rng.integers(0, 256, size=(rows, cols // 4), dtype=np.uint8)
+        mats.append((p, np.float32(sc), T().DeviceWeight(T().TernaryView(rows, cols, p.reshape(-1), sc), ctx)))
+    x = rng.standard_normal((m, cols)).astype(np.float32)
+    outs, iouts = T().ternary_linear_host(x, [d for _, _, d in mats], want_i32=True, ctx=ctx)
+    q, s, ssum = oracle.quantize_acts(x)
+    for (p, sc, _), of, oi in zip(mats, outs, iouts):
+        assert np.array_equal(oi, oracle.ternary_gemm_i32(p, cols, q, ssum))
+        assert np.array_equal(of.view(np.uint32), oracle.ternary_gemm(p, cols, sc, q, s, ssum).view(np.uint32))
+
+
+@pytest.mark.parametrize("m", [1024, 2048])
+def test_full_size_properties(oracle, ctx, m):
+    """BASELINE config 2 at full token counts, checked through properties the oracle can afford:
+    (a) first and last 64 weight rows against the oracle for every token, (b) sixteen sampled
+    token rows, all weight rows, against the decode kernel (which is checked against the oracle
+    elsewhere), (c) permuting token rows permutes the output rows."""
+    import torch
+    from lemonade_burn_b200 import ops
+    rows, cols = 6912, 2560
+    t, ws, p, x = random_case(rows, cols, m, 4242 + m, oracle)
+    lin = ops.TernaryLinear(torch.from_numpy(p).cuda(), float(ws), cols, ctx)
+    xd = torch.from_numpy(x).cuda()
+    outs, iouts = ops.ternary_linear_multi(xd, [lin], want_i32=True)
+    got_i = iouts[0].cpu().numpy()
+    got_f = outs[0].cpu().numpy()
+    q, s, ssum = oracle.quantize_acts(x)
+    for sl in (slice(0, 64), slice(rows - 64, rows)):
+        wf, wi = oracle.simd_gemm_multi([p[sl]], [ws], q, s, ssum, want_i32=True)
+        assert np.array_equal(got_i[:, sl], wi[0])
+        assert np.array_equal(got_f[:, sl].view(np.uint32), wf[0].view(np.uint32))
+    pick = np.linspace(0, m - 1, 16).astype(np.int64)
+    o2, i2 = ops.ternary_linear_multi(xd[torch.from_numpy(pick).cuda()].contiguous(), [lin], want_i32=True)
+    assert np.array_equal(i2[0].cpu().numpy(), got_i[pick])
+    assert np.array_equal(o2[0].cpu().numpy().view(np.uint32), got_f[pick].view(np.uint32))
+    perm = torch.randperm(m, generator=torch.Generator().manual_seed(1)).cuda()
+    o3 = ops.ternary_linear_multi(xd[perm].contiguous(), [lin])[0]
+    assert torch.equal(o3, outs[0][perm])
+    ctx.check_device_error()
