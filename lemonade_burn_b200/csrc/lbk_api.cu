@@ -65,15 +65,15 @@ int encode_weight_maps(Weight *w) {
     // GEMV: [16 rows][128 bytes] boxes with the 128-byte swizzle; rows/bytes past the matrix
     // edge are filled with zero bytes (code 0), which the kernels pair with zero activations.
     LBK_TRY(encode_2d_u8(&w->tmap_gemv, w->data, w->rb, w->rows, w->rb, 128, 16, CU_TENSOR_MAP_SWIZZLE_128B));
-    // GEMM: [256 rows][32 bytes] boxes (one packed block per row), plain layout.
-    LBK_TRY(encode_2d_u8(&w->tmap_gemm, w->data, w->rb, w->rows, w->rb, 32, 256, CU_TENSOR_MAP_SWIZZLE_NONE));
+    // GEMM: [128 rows][128 bytes] boxes (four packed blocks per row) with the 128-byte swizzle.
+    LBK_TRY(encode_2d_u8(&w->tmap_gemm, w->data, w->rb, w->rows, w->rb, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B));
     return LBK_OK;
 }
 
-// Quantised activations int8 [m][kp] as [128 rows][128 bytes] boxes with the 128-byte swizzle
+// Quantised activations int8 [m][kp] as [box_rows][128 bytes] boxes with the 128-byte swizzle
 // (the K-major operand layout of the tensor core); rows past m read as zeros.
-int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp) {
-    return encode_2d_u8(map, q, kp, m, kp, 128, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int box_rows) {
+    return encode_2d_u8(map, q, kp, m, kp, 128, static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 int ctx_scratch(Ctx *ctx, size_t bytes, void **out) {

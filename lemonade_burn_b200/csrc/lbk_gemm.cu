@@ -1,22 +1,28 @@
 // Prefill GEMM (more than 16 token rows): int8 activations x packed ternary weights on the
-// 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in TMEM).
+// 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators AND the weight operand in TMEM).
 //
 // Replaces ternary_gemm_multi's prefill branch and the AVX-512 register tile under it
-// (crates/lb-ternary/src/gemm.rs:155-194, 245-268, 483-550). Per output tile of 128 token rows x
-// 256 weight rows, per 128-column block of K (one packed 32-byte block per weight row):
+// (crates/lb-ternary/src/gemm.rs:155-194, 245-268, 483-550).
 //
-//   TMA warp       int8 activations [128 tok][128 B] (SWIZZLE_128B) and packed weights
-//                  [256 rows][32 B] into a 3-stage ring
-//   4 expander     2 bits -> u8 codes, written as the K-major SWIZZLE_128B tile the MMA wants:
-//   warps          (word >> 2k) & 0x03030303 is four consecutive columns k*32 + j..j+3, so every
-//                  16 packed bytes become four 16-byte stores, no shuffles (pack.rs:10-13)
-//   MMA thread     4 x tcgen05.mma (M=128 tokens, N=256 rows, K=32), s8 x u8 -> s32 in TMEM;
-//                  tcgen05.commit frees the stage / publishes the accumulator
+// Orientation: the 128 weight rows of a tile are the MMA's M side, NT token rows its N side
+// (D[row][token] in TMEM). Per 128-column block of K (one packed 32-byte block per weight row):
+//
+//   TMA warp       int8 activations [NT tok][128 B] (SWIZZLE_128B, the K-major B operand) and
+//                  packed weights [128 rows][32 B] into a deep shared-memory ring
+//   4 expander     thread r owns weight row r = TMEM lane r: 32 packed bytes -> 32 words of u8
+//   warps          codes, word c = columns 4c..4c+3 = (packed word >> 2k) & 0x03030303
+//                  (pack.rs:10-13: no shuffles), written straight to TMEM with tcgen05.st.
+//                  The expanded tile never touches shared memory: expanding into shared memory
+//                  cost 112 KB of shared-memory traffic per 512 cycles of MMA and starved the
+//                  tensor pipe (measured 27 % of peak).
+//   MMA thread     4 x tcgen05.mma (A from TMEM, u8; B from shared memory, s8; K = 32 each);
+//                  tcgen05.commit frees the rings / publishes the accumulator
 //   4 epilogue     tcgen05.ld, dot = acc - sum(q) (codes are w+1: gemm.rs:6-9,306-308),
-//   warps          y = (float)dot * (1/(s_a*s_w)) (gemm.rs:158,178), stores [token][row]
+//   warps          y = (float)dot * (1/(s_a*s_w)) (gemm.rs:158,178); a warp's 32 lanes are 32
+//                  consecutive weight rows, so every store instruction writes 128 contiguous bytes
 //
-// Two 256-column accumulators in TMEM let the epilogue of one tile overlap the MMAs of the next.
-// Bound: int8 tensor pipe. Work per call: 2*m*rows*cols integer operations.
+// TMEM columns: two accumulators of NT columns (the epilogue of one tile overlaps the MMAs of the
+// next) + a 4-deep ring of 32-column weight tiles. Bound: int8 tensor pipe; 2*m*rows*cols ops.
 #include "lbk_internal.cuh"
 #include "lbk_ptx.cuh"
 
@@ -24,26 +30,48 @@ namespace lbk {
 
 namespace {
 
-constexpr int kBM = 128;           // token rows per tile (MMA M)
-constexpr int kBN = 256;           // weight rows per tile (MMA N)
+constexpr int kBMW = 128;          // weight rows per tile (MMA M, TMEM lanes)
 constexpr int kBK = 128;           // columns per stage = one packed block
-constexpr int kStages = 3;
-constexpr int kActBytes = kBM * kBK;          // 16 KB int8, swizzled
-constexpr int kExpBytes = kBN * kBK;          // 32 KB u8 codes, swizzled
-constexpr int kPackBytes = kBN * kBlockBytes; //  8 KB packed
-constexpr int kStageBytes = kActBytes + kExpBytes + kPackBytes;
+constexpr int kPackBlocks = 4;      // K-blocks per packed-weight stage: [128 rows][128 B] boxes
+constexpr int kPackBytes = kBMW * kBlockBytes * kPackBlocks;  // 16 KB, SWIZZLE_128B
+constexpr int kAStages = 4;        // expanded weight tiles in TMEM (32 columns each)
 constexpr int kEpiWarps = 4, kExpWarps = 4;
-constexpr int kTmaWarp = 4, kMmaWarp = 5, kExpWarp0 = 6;
-constexpr int kThreads = (kEpiWarps + 2 + kExpWarps) * 32;  // 320
-constexpr uint32_t kTmemCols = 512;
+constexpr int kExpWarp0 = 4, kTmaWarp = 8, kMmaWarp = 9;   // warps 0-3 epilogue, 4-7 expanders
+constexpr int kThreads = 10 * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
+constexpr uint32_t kTmemCols = 512;
 
-// instruction descriptor: D s32, A s8 (activations), B u8 (codes), both K-major, N=256, M=128
-constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (0u << 10) | ((kBN >> 3) << 17) | ((kBM >> 4) << 24);
+template <int NT>  // token rows per tile (MMA N): 192 or 64
+struct Cfg {
+    static constexpr int kActBytes = NT * kBK;                  // multiple of 1024 for NT = 192, 64
+    static constexpr int kLoadStages = NT == 192 ? 6 : 12;      // activation ring
+    static constexpr int kPackStages = 3;                       // packed-weight ring
+    static constexpr uint32_t kPack0 = kLoadStages * kActBytes;
+    static constexpr uint32_t kAcc0 = 0, kAcc1 = NT, kA0 = 2 * NT;  // TMEM column map
+    static_assert(2 * NT + kAStages * 32 <= 512, "TMEM budget");
+    // instruction descriptor: D s32, A u8 (codes, TMEM), B s8 (activations), K-major, M=128, N=NT
+    static constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((NT >> 3) << 17) | ((kBMW >> 4) << 24);
+    static constexpr uint32_t kBars = kPack0 + kPackStages * kPackBytes;
+    static constexpr uint32_t kMisc = kBars + 48 * 8;
+    static constexpr uint32_t kTok = kMisc + 64;              // per-token sum(q) and 1/(s_a*s_w): 2 x [2][NT]
+    static constexpr uint32_t kTotal = kTok + 2 * 2 * NT * 4;
+    // One "full" barrier per K-block slot collects both operands: the activation bytes (TMA
+    // transaction count) and the four expander warps' arrivals for the TMEM weight tile, so the
+    // MMA thread waits once per block. One "consumed" barrier per slot (a single tcgen05.commit
+    // per block) releases both the activation stage and, AS blocks later, the TMEM weight slot.
+    static constexpr int kBarFull = 0;                        // [LS]
+    static constexpr int kBarConsumed = kLoadStages;          // [LS]
+    static constexpr int kBarFullPack = 2 * kLoadStages;      // [PS] packed weights landed
+    static constexpr int kBarEmptyPack = kBarFullPack + kPackStages;  // [PS] expanders are done with them
+    static constexpr int kBarAccFull = kBarEmptyPack + kPackStages;   // [2]
+    static constexpr int kBarAccEmpty = kBarAccFull + 2;      // [2]
+    static_assert(kBarAccEmpty + 2 <= 48, "barrier area too small");
+    static_assert(kAStages < kLoadStages, "a consumed-barrier phase must still be observable AS blocks later");
+};
 
 struct GemmParams {
-    CUtensorMap act;                    // int8 [m][kp], box [128][128], SWIZZLE_128B
-    CUtensorMap wpk[LBK_MAX_GROUP];     // u8 [rows][rb], box [256][32]
+    CUtensorMap act;                    // int8 [m][kp], box [NT][128], SWIZZLE_128B
+    CUtensorMap wpk[LBK_MAX_GROUP];     // u8 [rows][rb], box [128][128], SWIZZLE_128B
     float *out[LBK_MAX_GROUP];
     int32_t *iout[LBK_MAX_GROUP];
     float wscale[LBK_MAX_GROUP];
@@ -53,7 +81,16 @@ struct GemmParams {
     const float *qscale;
     const int32_t *qsum;
     int *err_word;
+#ifdef LBK_TIMELINE
+    long long *timeline;  // [grid][16]: cycles each role spent waiting, debugging only
+#endif
 };
+
+#ifdef LBK_TIMELINE
+#define TL_WAIT(slot, expr) ([&]() { const long long t0__ = clock64(); const bool r__ = (expr); tl[slot] += clock64() - t0__; return r__; }())
+#else
+#define TL_WAIT(slot, expr) (expr)
+#endif
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -64,15 +101,6 @@ __device__ __forceinline__ void tmem_relinquish() {
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
 }
 // mbarrier arrive once every MMA issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -92,6 +120,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// A operand from TMEM, B from shared memory
+__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // K-major SWIZZLE_128B shared-memory matrix descriptor: rows of 128 bytes, 8-row groups 1024 B
 // apart (SBO), version 1, layout type 2; `addr` may be advanced by 32 B per K=32 step.
@@ -115,61 +165,38 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
     return false;
 }
 
-struct Smem {
-    uint32_t stage[kStages];      // byte offsets from the aligned base
-    uint32_t bars;                // mbarriers
-    uint32_t misc;                // tmem base, abort flag
-    uint32_t total;
-};
-__host__ __device__ inline Smem smem_map() {
-    Smem s;
-    uint32_t o = 0;
-    for (int i = 0; i < kStages; ++i) {
-        s.stage[i] = o;
-        o += kStageBytes;
-    }
-    s.bars = o;
-    o += 32 * 8;
-    s.misc = o;
-    o += 64;
-    s.total = o;
-    return s;
-}
-// barrier indices
-constexpr int kBarFullAct = 0;               // [kStages] TMA activations landed
-constexpr int kBarFullPack = kStages;        // [kStages] TMA packed weights landed
-constexpr int kBarFullExp = 2 * kStages;     // [kStages] expanders finished the u8 tile
-constexpr int kBarEmpty = 3 * kStages;       // [kStages] MMAs that read the stage completed
-constexpr int kBarAccFull = 4 * kStages;     // [2] accumulator complete
-constexpr int kBarAccEmpty = 4 * kStages + 2;// [2] accumulator drained by the epilogue
-
+template <int NT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
+    using C = Cfg<NT>;
+    constexpr int LS = C::kLoadStages, AS = kAStages, PS = C::kPackStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - raw);
-    const Smem S = smem_map();
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t bar0 = base + S.bars;
-    volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(sm + S.misc);
-    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + S.misc + 4);
+    const uint32_t bar0 = base + C::kBars;
+    volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(sm + C::kMisc);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + C::kMisc + 4);
+    auto bar = [&](int idx) { return bar0 + idx * 8; };
 
     if (tid == 0) {
-        for (int i = 0; i < kStages; ++i) {
-            ptx::mbar_init(bar0 + (kBarFullAct + i) * 8, 1);
-            ptx::mbar_init(bar0 + (kBarFullPack + i) * 8, 1);
-            ptx::mbar_init(bar0 + (kBarFullExp + i) * 8, kExpWarps);
-            ptx::mbar_init(bar0 + (kBarEmpty + i) * 8, 1);
+        for (int i = 0; i < LS; ++i) {
+            ptx::mbar_init(bar(C::kBarFull + i), 1 + kExpWarps);
+            ptx::mbar_init(bar(C::kBarConsumed + i), 1);
+        }
+        for (int i = 0; i < PS; ++i) {
+            ptx::mbar_init(bar(C::kBarFullPack + i), 1);
+            ptx::mbar_init(bar(C::kBarEmptyPack + i), kExpWarps);
         }
         for (int a = 0; a < 2; ++a) {
-            ptx::mbar_init(bar0 + (kBarAccFull + a) * 8, 1);
-            ptx::mbar_init(bar0 + (kBarAccEmpty + a) * 8, kEpiWarps);
+            ptx::mbar_init(bar(C::kBarAccFull + a), 1);
+            ptx::mbar_init(bar(C::kBarAccEmpty + a), kEpiWarps);
         }
         *s_abort = 0;
         ptx::fence_barrier_init();
     }
     if (warp == kMmaWarp) {
-        tmem_alloc(base + S.misc, kTmemCols);
+        tmem_alloc(base + C::kMisc, kTmemCols);
         tmem_relinquish();
     }
     tc_fence_before();
@@ -179,66 +206,90 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
     const int k_blocks = p.k_blocks;
     bool ok = true;
+#ifdef LBK_TIMELINE
+    long long tl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    const long long tl_begin = clock64();
+#endif
+    // tile -> (matrix, weight-row tile, token tile); token tiles vary fastest so that CTAs
+    // running side by side share the same packed weights in L2
+    auto decode_tile = [&](int tile, int &mat, int &m_tile, int &n_tile) {
+        mat = 0;
+        while (mat < p.n_mat - 1 && tile >= p.tile_end[mat]) ++mat;
+        const int local = tile - (mat ? p.tile_end[mat - 1] : 0);
+        m_tile = local % p.m_tiles;
+        n_tile = local / p.m_tiles;
+    };
 
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            int it = 0;
+            int it = 0, pit = 0;  // activation items, packed-weight items
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                int mat = 0;
-                while (mat < p.n_mat - 1 && tile >= p.tile_end[mat]) ++mat;
-                const int local = tile - (mat ? p.tile_end[mat - 1] : 0);
-                const int m_tile = local % p.m_tiles, n_tile = local / p.m_tiles;
+                int mat, m_tile, n_tile;
+                decode_tile(tile, mat, m_tile, n_tile);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages, round = it / kStages;
-                    if (round > 0 && !wait_bar(bar0 + (kBarEmpty + s) * 8, (round - 1) & 1, s_abort)) {
+                    if ((kb % kPackBlocks) == 0) {
+                        const int ps = pit % PS, pround = pit / PS;
+                        if (pround > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort))) {
+                            ok = false;
+                            break;
+                        }
+                        ptx::mbar_arrive_expect_tx(bar(C::kBarFullPack + ps), kPackBytes);
+                        ptx::tma_load_2d(base + C::kPack0 + ps * kPackBytes, &p.wpk[mat], bar(C::kBarFullPack + ps),
+                                         kb * kBlockBytes, n_tile * kBMW);
+                        ++pit;
+                    }
+                    const int s = it % LS, round = it / LS;
+                    if (round > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort))) {
                         ok = false;
                         break;
                     }
-                    const uint32_t st = base + S.stage[s];
-                    ptx::mbar_arrive_expect_tx(bar0 + (kBarFullAct + s) * 8, kActBytes);
-                    ptx::tma_load_2d(st, &p.act, bar0 + (kBarFullAct + s) * 8, kb * kBK, m_tile * kBM);
-                    ptx::mbar_arrive_expect_tx(bar0 + (kBarFullPack + s) * 8, kPackBytes);
-                    ptx::tma_load_2d(st + kActBytes + kExpBytes, &p.wpk[mat], bar0 + (kBarFullPack + s) * 8,
-                                     kb * kBlockBytes, n_tile * kBN);
+                    ptx::mbar_arrive_expect_tx(bar(C::kBarFull + s), C::kActBytes);
+                    ptx::tma_load_2d(base + s * C::kActBytes, &p.act, bar(C::kBarFull + s), kb * kBK, m_tile * NT);
                 }
             }
         }
-    } else if (warp >= kExpWarp0) {
-        // ================= expanders: packed 2-bit -> swizzled K-major u8 =================
-        const int et = tid - kExpWarp0 * 32;  // 0..127; rows et and et + 128 of the tile
-        int it = 0;
+    } else if (warp >= kExpWarp0 && warp < kExpWarp0 + kExpWarps) {
+        // ================= expanders: packed 2-bit -> u8 codes in TMEM =================
+        const int r = (warp - kExpWarp0) * 32 + lane;  // weight row of the tile = TMEM lane
+        const uint32_t lane_field = static_cast<uint32_t>((warp - kExpWarp0) * 32) << 16;
+        int it = 0, pit = -1;
         for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                const int s = it % kStages, round = it / kStages;
-                if (!wait_bar(bar0 + (kBarFullPack + s) * 8, round & 1, s_abort)) {
+                const int as = it % AS, sub = kb % kPackBlocks;
+                if (sub == 0) {
+                    ++pit;
+                    if (!TL_WAIT(1, wait_bar(bar(C::kBarFullPack + pit % PS), (pit / PS) & 1, s_abort))) {
+                        ok = false;
+                        break;
+                    }
+                }
+                // TMEM slot `as` was last read by block it - AS
+                if (it >= AS && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + (it - AS) % LS), ((it - AS) / LS) & 1, s_abort))) {
                     ok = false;
                     break;
                 }
-                const uint8_t *pk = sm + S.stage[s] + kActBytes + kExpBytes;
-                uint8_t *ex = sm + S.stage[s] + kActBytes;
+                tc_fence_after();
+                // row r of the [128][128 B] swizzled stage; this block's 32 bytes are units 2*sub, 2*sub+1
+                const uint8_t *pk = sm + C::kPack0 + (pit % PS) * kPackBytes + r * 128;
+                const int x = r & 7;
+                const uint4 w0 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub) ^ x) << 4));      // packed bytes j = 0..15
+                const uint4 w1 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub + 1) ^ x) << 4));  // packed bytes j = 16..31
+                const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                uint32_t v[32];  // word 8k + i = columns k*32 + 4i .. 4i+3
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    const int r = et + h * 128;
-                    const uint4 w0 = *reinterpret_cast<const uint4 *>(pk + r * kBlockBytes);       // bytes j = 0..15
-                    const uint4 w1 = *reinterpret_cast<const uint4 *>(pk + r * kBlockBytes + 16);  // bytes j = 16..31
-                    uint8_t *row = ex + r * 128;
-                    const int x = r & 7;
+                for (int k = 0; k < 4; ++k)
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint4 c0, c1;
-                        c0.x = (w0.x >> (2 * k)) & 0x03030303u; c0.y = (w0.y >> (2 * k)) & 0x03030303u;
-                        c0.z = (w0.z >> (2 * k)) & 0x03030303u; c0.w = (w0.w >> (2 * k)) & 0x03030303u;
-                        c1.x = (w1.x >> (2 * k)) & 0x03030303u; c1.y = (w1.y >> (2 * k)) & 0x03030303u;
-                        c1.z = (w1.z >> (2 * k)) & 0x03030303u; c1.w = (w1.w >> (2 * k)) & 0x03030303u;
-                        // columns k*32 + 0..15 are 16-byte unit 2k, columns k*32 + 16..31 unit 2k+1
-                        *reinterpret_cast<uint4 *>(row + (((2 * k) ^ x) << 4)) = c0;
-                        *reinterpret_cast<uint4 *>(row + (((2 * k + 1) ^ x) << 4)) = c1;
-                    }
+                    for (int i = 0; i < 8; ++i) v[8 * k + i] = (w[i] >> (2 * k)) & 0x03030303u;
+                tmem_st32(tmem_base + lane_field + C::kA0 + as * 32, v);
+                if (sub == kPackBlocks - 1 || kb == k_blocks - 1) {  // last read of this packed stage
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive(bar(C::kBarEmptyPack + pit % PS));
                 }
-                ptx::fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's reads
+                tmem_st_wait();
+                tc_fence_before();
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar0 + (kBarFullExp + s) * 8);
+                if (lane == 0) ptx::mbar_arrive(bar(C::kBarFull + it % LS));
             }
         }
     } else if (warp == kMmaWarp) {
@@ -247,91 +298,124 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             int it = 0, tcount = 0;
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
                 const int a = tcount & 1, around = tcount >> 1;
-                if (around > 0 && !wait_bar(bar0 + (kBarAccEmpty + a) * 8, (around - 1) & 1, s_abort)) {
+                if (around > 0 && !TL_WAIT(3, wait_bar(bar(C::kBarAccEmpty + a), (around - 1) & 1, s_abort))) {
                     ok = false;
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + a * kBN;
+                const uint32_t d_tmem = tmem_base + (a ? C::kAcc1 : C::kAcc0);
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % kStages, round = it / kStages;
-                    if (!wait_bar(bar0 + (kBarFullAct + s) * 8, round & 1, s_abort) ||
-                        !wait_bar(bar0 + (kBarFullExp + s) * 8, round & 1, s_abort)) {
+                    const int ls = it % LS, as = it % AS;
+                    if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + ls), (it / LS) & 1, s_abort))) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_addr = base + S.stage[s], b_addr = a_addr + kActBytes;
+                    const uint32_t b_addr = base + ls * C::kActBytes;
+                    const uint32_t a_tmem = tmem_base + C::kA0 + as * 32;
 #pragma unroll
-                    for (int ks = 0; ks < kBK / 32; ++ks)
-                        umma_i8(d_tmem, smem_desc_sw128(a_addr + ks * 32), smem_desc_sw128(b_addr + ks * 32), kIdesc,
-                                (kb | ks) ? 1u : 0u);
-                    umma_commit(bar0 + (kBarEmpty + s) * 8);  // stage reusable once these MMAs retire
+                    for (int ks = 0; ks < kBK / 32; ++ks)  // K = 32 int8 = 8 TMEM columns of A, 32 bytes of B
+                        umma_i8_ts(d_tmem, a_tmem + ks * 8, smem_desc_sw128(b_addr + ks * 32), C::kIdesc, (kb | ks) ? 1u : 0u);
+                    umma_commit(bar(C::kBarConsumed + ls));  // both operands' slots are reusable once these MMAs retire
                 }
                 if (!ok) break;
-                umma_commit(bar0 + (kBarAccFull + a) * 8);    // accumulator complete
+                umma_commit(bar(C::kBarAccFull + a));  // accumulator complete
             }
         }
-    } else {
+    } else if (warp < kEpiWarps) {
         // ================= epilogue (warps 0..3 = TMEM lane quadrants 0..3) =================
+        int *s_qs = reinterpret_cast<int *>(sm + C::kTok);
+        float *s_inv = reinterpret_cast<float *>(sm + C::kTok + 2 * NT * 4);
         int tcount = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
             const int a = tcount & 1, around = tcount >> 1;
-            int mat = 0;
-            while (mat < p.n_mat - 1 && tile >= p.tile_end[mat]) ++mat;
-            const int local = tile - (mat ? p.tile_end[mat - 1] : 0);
-            const int m_tile = local % p.m_tiles, n_tile = local / p.m_tiles;
-            const int token = m_tile * kBM + warp * 32 + lane;
+            int mat, m_tile, n_tile;
+            decode_tile(tile, mat, m_tile, n_tile);
             const int rows = p.rows[mat];
+            const int row = n_tile * kBMW + warp * 32 + lane;
+            const int tok0 = m_tile * NT;
             float *out = p.out[mat];
             int32_t *iout = p.iout[mat];
-            int qs = 0;
-            float inv = 0.0f;
-            if (token < p.m) {
-                qs = p.qsum[token];
-                if (out) inv = __fdiv_rn(1.0f, __fmul_rn(p.qscale[token], p.wscale[mat]));  // gemm.rs:158
+            // per-token terms of this tile (each warp fills its own copy: no cross-warp barrier)
+            int *qs = s_qs + a * NT;  // reuse by accumulator parity is safe: see acc_empty below
+            float *inv = s_inv + a * NT;
+            if (warp == 0) {
+                for (int i = lane; i < NT; i += 32) {
+                    const int tk = tok0 + i;
+                    qs[i] = tk < p.m ? p.qsum[tk] : 0;
+                    inv[i] = (tk < p.m && p.qscale) ? __fdiv_rn(1.0f, __fmul_rn(p.qscale[tk], p.wscale[mat])) : 0.0f;  // gemm.rs:158
+                }
             }
-            if (!wait_bar(bar0 + (kBarAccFull + a) * 8, around & 1, s_abort)) {
+            asm volatile("bar.sync 2, 128;" ::: "memory");  // the four epilogue warps
+#ifdef LBK_TIMELINE
+            const long long tl_e0 = clock64();
+#endif
+            if (!TL_WAIT(6, wait_bar(bar(C::kBarAccFull + a), around & 1, s_abort))) {
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const bool vec = (rows & 3) == 0;
+            const int ntok = p.m - tok0 < NT ? p.m - tok0 : NT;
 #pragma unroll 1
-            for (int c = 0; c < kBN / 32; ++c) {
+            for (int c = 0; c < NT / 32; ++c) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + a * kBN + c * 32, v);
-                tmem_ld_wait();
-                const int row0 = n_tile * kBN + c * 32;
-                if (token < p.m && row0 < rows) {
-                    const size_t o = static_cast<size_t>(token) * rows + row0;
-                    if (vec && row0 + 32 <= rows) {
+                tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + (a ? C::kAcc1 : C::kAcc0) + c * 32, v);
+                // per-token terms into registers first: the stores below may alias the shared
+                // arrays as far as the compiler knows, which would serialise load -> store pairs
+                int q[32];
+                float sc[32];
 #pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const int d0 = static_cast<int>(v[i]) - qs, d1 = static_cast<int>(v[i + 1]) - qs;
-                            const int d2 = static_cast<int>(v[i + 2]) - qs, d3 = static_cast<int>(v[i + 3]) - qs;
-                            if (iout) *reinterpret_cast<int4 *>(iout + o + i) = make_int4(d0, d1, d2, d3);
-                            if (out)
-                                *reinterpret_cast<float4 *>(out + o + i) =
-                                    make_float4(__fmul_rn(__int2float_rn(d0), inv), __fmul_rn(__int2float_rn(d1), inv),
-                                                __fmul_rn(__int2float_rn(d2), inv), __fmul_rn(__int2float_rn(d3), inv));
+                for (int i = 0; i < 32; i += 4) {
+                    const int4 q4 = *reinterpret_cast<const int4 *>(qs + c * 32 + i);
+                    const float4 s4 = *reinterpret_cast<const float4 *>(inv + c * 32 + i);
+                    q[i] = q4.x; q[i + 1] = q4.y; q[i + 2] = q4.z; q[i + 3] = q4.w;
+                    sc[i] = s4.x; sc[i + 1] = s4.y; sc[i + 2] = s4.z; sc[i + 3] = s4.w;
+                }
+                tmem_ld_wait();
+                if (row < rows) {
+                    const size_t o0 = static_cast<size_t>(tok0 + c * 32) * rows + row;
+                    if (c * 32 + 32 <= ntok) {
+                        if (out) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i)
+                                out[o0 + static_cast<size_t>(i) * rows] = __fmul_rn(__int2float_rn(static_cast<int>(v[i]) - q[i]), sc[i]);
+                        }
+                        if (iout) {
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) iout[o0 + static_cast<size_t>(i) * rows] = static_cast<int>(v[i]) - q[i];
                         }
                     } else {
-                        for (int i = 0; i < 32 && row0 + i < rows; ++i) {
-                            const int d = static_cast<int>(v[i]) - qs;
-                            if (iout) iout[o + i] = d;
-                            if (out) out[o + i] = __fmul_rn(__int2float_rn(d), inv);
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (c * 32 + i < ntok) {
+                                const int d = static_cast<int>(v[i]) - q[i];
+                                if (iout) iout[o0 + static_cast<size_t>(i) * rows] = d;
+                                if (out) out[o0 + static_cast<size_t>(i) * rows] = __fmul_rn(__int2float_rn(d), sc[i]);
+                            }
                         }
                     }
                 }
             }
             tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar0 + (kBarAccEmpty + a) * 8);
+#ifdef LBK_TIMELINE
+            tl[7] += clock64() - tl_e0;  // wait + drain of this tile
+            tl[5] += 1;
+#endif
+            asm volatile("bar.sync 2, 128;" ::: "memory");  // all four warps are done with qs/inv of this parity
+            if (lane == 0) ptx::mbar_arrive(bar(C::kBarAccEmpty + a));
         }
     }
 
     if (!ok && lane == 0) atomicExch(p.err_word, 5);
+#ifdef LBK_TIMELINE
+    if (p.timeline && lane == 0) {
+        long long *d = p.timeline + static_cast<long long>(blockIdx.x) * 16;
+        if (warp == kTmaWarp) d[0] = tl[0];
+        if (warp == kExpWarp0) { d[1] = tl[1]; d[2] = tl[2]; }
+        if (warp == kMmaWarp) { d[3] = tl[3]; d[4] = tl[4]; d[5] = tl[5]; d[8] = clock64() - tl_begin; }
+        if (warp == 0) { d[6] = tl[6]; d[7] = clock64() - tl_begin; d[9] = tl[7]; d[10] = tl[5]; }
+    }
+#endif
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -342,12 +426,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
 }  // namespace
 
-int gemm_init(Ctx *ctx) {
-    const Smem S = smem_map();
-    if (S.total + 1024 > ctx->smem_optin) return fail(LBK_ERR_UNSUPPORTED, "gemm kernel needs %u B of shared memory", S.total + 1024);
-    LBK_CUDA(cudaFuncSetAttribute(gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(S.total + 1024)));
+template <int NT>
+static int init_one(Ctx *ctx) {
+    const size_t smem = Cfg<NT>::kTotal + 1024;
+    if (smem > ctx->smem_optin) return fail(LBK_ERR_UNSUPPORTED, "gemm kernel needs %zu B of shared memory", smem);
+    LBK_CUDA(cudaFuncSetAttribute(gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     return LBK_OK;
 }
+
+int gemm_init(Ctx *ctx) {
+    LBK_TRY(init_one<192>(ctx));
+    LBK_TRY(init_one<64>(ctx));
+    return LBK_OK;
+}
+
+#ifdef LBK_TIMELINE
+static long long *g_gemm_timeline = nullptr;
+extern "C" void lbk_debug_set_gemm_timeline(long long *buf) { g_gemm_timeline = buf; }
+#endif
 
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     if (!g.q || !g.qsum) return fail(LBK_ERR_INVALID, "gemm: quantised activations are required");
@@ -355,9 +451,10 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     if (g.m == 0) return LBK_OK;
     GemmParams p{};
     const size_t kp = g.w[0]->kp;
-    LBK_TRY(encode_act_map(&p.act, g.q, g.m, kp));
+    const int nt = g.m <= 64 ? 64 : 192;
+    LBK_TRY(encode_act_map(&p.act, g.q, g.m, kp, nt));
     p.m = static_cast<int>(g.m);
-    p.m_tiles = static_cast<int>((g.m + kBM - 1) / kBM);
+    p.m_tiles = static_cast<int>((g.m + nt - 1) / nt);
     p.k_blocks = static_cast<int>(kp / kBK);
     int tiles = 0;
     for (int i = 0; i < g.n; ++i) {
@@ -369,7 +466,7 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
         p.iout[i] = g.iout[i];
         p.wscale[i] = w->scale;
         p.rows[i] = static_cast<int>(w->rows);
-        tiles += p.m_tiles * static_cast<int>((w->rows + kBN - 1) / kBN);
+        tiles += p.m_tiles * static_cast<int>((w->rows + kBMW - 1) / kBMW);
         p.tile_end[i] = tiles;
     }
     p.n_mat = g.n;
@@ -377,10 +474,15 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.qscale = g.qscale;
     p.qsum = g.qsum;
     p.err_word = ctx->err_word;
+#ifdef LBK_TIMELINE
+    p.timeline = g_gemm_timeline;
+#endif
     if (tiles == 0 || p.k_blocks == 0) return LBK_OK;
-    const Smem S = smem_map();
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    gemm_kernel<<<grid, kThreads, S.total + 1024, stream>>>(p);
+    if (nt == 192)
+        gemm_kernel<192><<<grid, kThreads, Cfg<192>::kTotal + 1024, stream>>>(p);
+    else
+        gemm_kernel<64><<<grid, kThreads, Cfg<64>::kTotal + 1024, stream>>>(p);
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
     return LBK_OK;

@@ -54,7 +54,7 @@ struct Weight {
     bool owned = false;
     float scale = 1.0f;
     alignas(64) CUtensorMap tmap_gemv;  // box [16 rows][128 B], SWIZZLE_128B
-    alignas(64) CUtensorMap tmap_gemm;  // box [256 rows][32 B], no swizzle (GEMM expander)
+    alignas(64) CUtensorMap tmap_gemm;  // box [128 rows][128 B], SWIZZLE_128B (prefill expander)
 };
 
 int ctx_scratch(Ctx *ctx, size_t bytes, void **out);
@@ -64,7 +64,7 @@ int gemv_init(Ctx *ctx);
 int gemm_init(Ctx *ctx);
 int sweep_init(Ctx *ctx);
 int encode_weight_maps(Weight *w);
-int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp);
+int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int box_rows);
 
 // ---- launchers -----------------------------------------------------------------------
 struct GroupArgs {
