@@ -128,6 +128,25 @@ int lbk_ternary_linear_n(lbk_ctx *ctx, const float *x_dev, size_t m, const lbk_w
                          size_t n, float *const *outs_dev, int32_t *const *iouts_dev,
                          void *stream);
 
+/* No counterpart in the reference (its CPU path owns its own Vec buffers). Same operation and
+ * results as lbk_ternary_linear_n on the prefill path (quantise, then the tensor-core GEMM), for
+ * callers that may not allocate device memory: a serving loop that bans allocator calls after
+ * start-up, a process whose memory budget belongs to another component, a plug-in inside a host
+ * application that owns the CUDA heap. The quantised activations live in a fixed array inside the
+ * library image (LBK_STATIC_SCRATCH_BYTES on every GPU that loads the library, until exit), so the
+ * call makes no cudaMalloc/cudaFree and uses no allocating library routine.
+ *   Limits: m <= 4096 token rows and m * lbk_padded_cols(cols) <= 8 MiB; beyond that the call
+ *   returns LBK_ERR_UNSUPPORTED and says so in lbk_last_error().
+ *   The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+ *   that first call before any stream capture.
+ *   All calls share the one array, and it keeps the previous call's contents (nothing in it needs
+ *   clearing: each call overwrites all it reads). Two calls that overlap on the GPU -- different
+ *   streams, or different contexts on the same device -- race on it; serialise them. */
+#define LBK_STATIC_SCRATCH_BYTES ((8u << 20) + 2u * 4096u * 4u)
+int lbk_ternary_linear_prefill_static(lbk_ctx *ctx, const float *x_dev, size_t m,
+                                      const lbk_weight *const *ws, size_t n, float *const *outs_dev,
+                                      int32_t *const *iouts_dev, void *stream);
+
 /* quantize_acts (quant.rs:37-75) device to device. q_dev: int8 [m, padded_cols(k)]. */
 int lbk_quantize_acts_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_t k, int8_t *q_dev,
                           float *scale_dev, int32_t *sum_dev, void *stream);

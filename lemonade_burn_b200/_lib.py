@@ -40,6 +40,7 @@ SYMBOLS = [
     ("lbk_ternary_linear_host", _i, [_vp, _vp, _sz, _pp, _sz, _pp, _pp]),
     ("lbk_bf16_gemv_host", _i, [_vp, _vp, _sz, _sz, _vp, _vp]),
     ("lbk_ternary_linear_n", _i, [_vp, _vp, _sz, _pp, _sz, _pp, _pp, _vp]),
+    ("lbk_ternary_linear_prefill_static", _i, [_vp, _vp, _sz, _pp, _sz, _pp, _pp, _vp]),
     ("lbk_quantize_acts_dev", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     ("lbk_ternary_gemm_dev", _i, [_vp, _pp, _sz, _vp, _vp, _vp, _sz, _pp, _pp, _vp]),
     ("lbk_bf16_linear", _i, [_vp, _vp, _sz, _vp, _sz, _sz, _vp, _vp]),
