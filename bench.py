@@ -97,6 +97,150 @@ def config0_gemv(torch, ops, ctx, device, copies: int = 64, reps: int = 20):
             "us_per_call": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes_per_call": nbytes}
 
 
+# int8 tensor-core peak measured on this pool's B200 with a no-load tcgen05.mma kind::i8 loop
+# (M=128, N=256 and N=128, K=32; 4568-4588 TOPS; nominal dense figure 4500)
+INT8_PEAK_TOPS_MEASURED = 4568.0
+
+
+def config2_prefill(torch, ops, ctx, device, ms=(64, 256, 1024, 2048), reps=5, per_graph=10):
+    """Config 2: prefill ternary GEMM at the BitNet-2B projections, per token count. One call =
+    per-token int8 quantisation kernel + tcgen05 GEMM kernel; timed as CUDA-graph replays."""
+    import ctypes as C
+    from lemonade_burn_b200 import _lib
+    g = torch.Generator(device=device).manual_seed(2222)
+    out = []
+    for rows, cols in ((INTER, HIDDEN), (HIDDEN, INTER)):
+        u = torch.rand((4, rows, cols // 4), generator=g, device=device)
+        codes = (u > 0.3).to(torch.uint8) + (u > 0.7).to(torch.uint8)
+        lin = ops.TernaryLinear((codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)).contiguous(), WSCALE, cols, ctx)
+        del u, codes
+        for m in ms:
+            x = torch.randn(m, cols, generator=g, device=device)
+            y = torch.empty(m, rows, device=device)
+            wp, _k1 = _lib.ptr_array([lin.weight.handle.value])
+            op, _k2 = _lib.ptr_array([y.data_ptr()])
+
+            def call(stream):
+                _lib.check(ctx._lib.lbk_ternary_linear_n(ctx.handle, C.c_void_p(x.data_ptr()), m, wp, 1, op, None, C.c_void_p(stream)))
+
+            for _ in range(2):
+                call(torch.cuda.current_stream().cuda_stream)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    for _ in range(per_graph):
+                        call(side.cuda_stream)
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                graph.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
+            tops = 2.0 * m * rows * cols / us / 1e6
+            out.append({"k": cols, "n": rows, "m": m, "us": us, "int8_TOPS": tops,
+                        "frac_of_measured_int8_peak": tops / INT8_PEAK_TOPS_MEASURED, "frac_of_nominal_4500": tops / 4500.0})
+    return {"workload": "prefill ternary GEMM, quantise + tcgen05 kernel per call", "peak_TOPS_measured": INT8_PEAK_TOPS_MEASURED,
+            "cases": out}
+
+
+# ---------------------------------------------------------------------------------------
+# config 4: 70B-shaped ternary decoder, tensor parallel (column-parallel q/k/v/gate/up,
+# row-parallel o/down with an exact int32 all-reduce), batch-64 decode weight sweep
+# ---------------------------------------------------------------------------------------
+TP_HIDDEN, TP_INTER, TP_LAYERS, TP_KV = 8192, 28672, 80, 1024
+TP_BATCH = 64
+
+
+def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers=TP_LAYERS, batch=TP_BATCH):
+    """One step = every projection of every layer once at `batch` token rows (no attention / FFN
+    math between them, like the reference's KB_MODEL sweep). Returns a dict for the JSON line."""
+    from lemonade_burn_b200 import tp
+
+    def rand_packed(rows, rb, gen):
+        b = torch.randint(0, 256, (rows, rb), dtype=torch.uint8, device=device, generator=gen)
+        return b & ~((b >> 1) & b & 0x55)  # clear code 3 -> valid ternary (P(0)=0.5, P(+-1)=0.25)
+
+    gen = torch.Generator(device=device).manual_seed(777 + rank)
+    H, I = TP_HIDDEN, TP_INTER
+    lays = []
+    for _ in range(layers):
+        # shards are generated directly at their local size (no need to build the full matrices)
+        lays.append({
+            "qkv": [rand_packed(H // world, H // 4, gen), rand_packed(TP_KV // world, H // 4, gen), rand_packed(TP_KV // world, H // 4, gen)],
+            "o": rand_packed(H, H // world // 4, gen),
+            "gu": [rand_packed(I // world, H // 4, gen), rand_packed(I // world, H // 4, gen)],
+            "down": rand_packed(H, I // world // 4, gen),
+        })
+    mods = []
+    for L in lays:
+        mods.append((tp.ColumnParallelTernary(L["qkv"], [WSCALE] * 3, H, 1, 0, ctx),
+                     tp.RowParallelTernary(L["o"], WSCALE, H // world, 1, 0, ctx=ctx),
+                     tp.ColumnParallelTernary(L["gu"], [WSCALE] * 2, H, 1, 0, ctx),
+                     tp.RowParallelTernary(L["down"], WSCALE, I // world, 1, 0, ctx=ctx)))
+    for _, o_, _, d_ in mods:  # the layers were built from local shards; give them the real world size
+        o_.world = world
+        d_.world = world
+    del lays
+    g2 = torch.Generator(device=device).manual_seed(5)
+    x_h = torch.randn(batch, H, device=device, generator=g2)
+    x_o = torch.randn(batch, H // world, device=device, generator=g2)
+    x_d = torch.randn(batch, I // world, device=device, generator=g2)
+
+    def sweep():
+        for qkv, o_, gu, d_ in mods:
+            qkv.forward(x_h)
+            o_.forward(x_o)
+            gu.forward(x_h)
+            d_.forward(x_d)
+
+    for _ in range(warmup):
+        sweep()
+    torch.cuda.synchronize()
+    # one CUDA graph per sweep (kernels and NCCL all-reduces) strips ~1000 host-side launches
+    run, mode = sweep, "eager"
+    try:
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                sweep()
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        run, mode = graph.replay, "cuda graph"
+    except Exception as exc:  # capture is an optimisation only
+        mode = f"eager (graph capture failed: {type(exc).__name__})"
+        torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = float(ms[0]) / steps
+    packed_total = layers * ((H + 2 * TP_KV) * H // 4 + H * H // 4 + 2 * I * H // 4 + H * I // 4)
+    ops_total = 2.0 * batch * packed_total * 4
+    return {"workload": "ternary70b_tp_decode_sweep", "layers": layers, "hidden": H, "intermediate": I, "batch": batch,
+            "parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": ms_step,
+            "tok_per_s": batch / (ms_step * 1e-3), "int8_TOPS": ops_total / (ms_step * 1e-3) / 1e12,
+            "packed_weight_bytes_total": packed_total, "allreduce_int32_bytes_per_layer": 2 * batch * H * 4,
+            "launch": mode, "weights": "valid ternary codes, P(0)=0.5, drawn per rank at shard size"}
+
+
 def measured_peaks():
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
@@ -357,7 +501,16 @@ def run_ours(args):
                 xs.append(xh[off:off + cols].copy())
                 off += cols
         cpu_toks, cores, kern, sample = cpu_sweep_baseline(packed_layers, xs, budget_s=10.0, max_layers=n_cpu_layers)
-        extra = {"config0_gemv": config0_gemv(torch, ops, ctx, device)}
+        extra = {"config0_gemv": config0_gemv(torch, ops, ctx, device),
+                 "config2_prefill": config2_prefill(torch, ops, ctx, device)}
+    del plan, linears
+    torch.cuda.empty_cache()
+    tp_res = None
+    if args.tp70b or world > 1:
+        tp_res = tp70b_sweep(torch, dist, ctx, device, world, rank, layers=args.tp_layers)
+    if rank == 0:
+        if tp_res is not None:
+            extra["tp70b"] = tp_res
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
@@ -389,6 +542,8 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--tp70b", action="store_true", help="also time the 70B-shaped tensor-parallel sweep at N=1")
+    ap.add_argument("--tp-layers", type=int, default=TP_LAYERS)
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -151,6 +151,22 @@ int lbk_ternary_linear_prefill_static(lbk_ctx *ctx, const float *x_dev, size_t m
 int lbk_quantize_acts_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_t k, int8_t *q_dev,
                           float *scale_dev, int32_t *sum_dev, void *stream);
 
+/* Tensor-parallel pieces. The reference has no multi-device path; its nearest relative is the
+ * two-socket row split of crates/lb-model/src/ops.rs:255-297. When the columns (K) of a matrix are
+ * split across ranks, per-token quantisation still has to use the maximum over the whole row
+ * (quant.rs:101-105), and the int32 dots of the slices add up exactly:
+ *   lbk_absmax_dev              amax[t] = max|x[t, :]| of this rank's column slice
+ *   (all-reduce MAX over ranks, done by the caller)
+ *   lbk_quantize_acts_amax_dev  quantize_acts with scale = 127 / max(amax[t], 1e-5) given
+ *   lbk_ternary_gemm_dev        int32 dots of the slice (iouts only)
+ *   (all-reduce SUM of the int32 dots, done by the caller: exact, order independent)
+ *   lbk_scale_epilogue_dev      out[t, r] = (float)dot * (1 / (scale[t] * wscale))  (gemm.rs:141) */
+int lbk_absmax_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_t k, float *amax_dev, void *stream);
+int lbk_quantize_acts_amax_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_t k, const float *amax_dev,
+                               int8_t *q_dev, float *scale_dev, int32_t *sum_dev, void *stream);
+int lbk_scale_epilogue_dev(lbk_ctx *ctx, const int32_t *dots_dev, const float *scale_dev, float wscale,
+                           size_t m, size_t rows, float *out_dev, void *stream);
+
 /* ternary_gemm_multi (gemm.rs:128-195) on already quantised device inputs. */
 int lbk_ternary_gemm_dev(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, const int8_t *q_dev,
                          const float *scale_dev, const int32_t *sum_dev, size_t m,
@@ -160,6 +176,36 @@ int lbk_ternary_gemm_dev(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, co
  * [rows, cols] -> out f32 [m, rows], all device memory. */
 int lbk_bf16_linear(lbk_ctx *ctx, const float *x_dev, size_t m, const uint16_t *w_dev, size_t rows,
                     size_t cols, float *out_dev, void *stream);
+
+/* ---- decoder-step glue: the non-matmul parts of BitNet::forward (crates/lb-model/src/model.rs:305-374)
+ * All device pointers; `b` independent sequences; kernels that depend on the decode position read
+ * it from pos_dev (device int32), so a captured CUDA graph of one step can be replayed per token. */
+
+/* embed (model.rs:274-282): out[b, hidden] = f32(table[tokens[b], :]), table is bf16 bits. */
+int lbk_embed_bf16(lbk_ctx *ctx, const uint16_t *table_dev, const int32_t *tokens_dev, size_t b, size_t hidden,
+                   float *out_dev, void *stream);
+/* rms_norm (model.rs:267-272): out = x * (1/sqrt(mean(x^2) + eps)) * w over rows of n. */
+int lbk_rms_norm(lbk_ctx *ctx, const float *x_dev, const float *w_dev, size_t rows, size_t n, float eps,
+                 float *out_dev, void *stream);
+/* apply_rope on q (in place) and k, then k and v stored as bf16 at position *pos_dev of the caches
+ * [b][kv_heads][cap][head_dim] (model.rs:295-303,334-347; the reference keeps f32 caches). cos/sin:
+ * f32 [max_pos][head_dim], both halves duplicated (model.rs:213-230). */
+int lbk_rope_kv_append(lbk_ctx *ctx, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                       const float *sin_dev, const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads,
+                       size_t head_dim, size_t cap, uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream);
+/* Grouped-query attention of one new token per sequence over keys 0..*pos_dev (model.rs:350-357),
+ * head_dim 128, split over the sequence. scratch_dev: b*n_heads*splits*(head_dim+4) floats, 16-byte aligned. */
+int lbk_attn_decode(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev,
+                    const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                    size_t splits, float *scratch_dev, float *out_dev, void *stream);
+/* relu(g)^2 * u (model.rs:363). */
+int lbk_relu2_mul(lbk_ctx *ctx, const float *g_dev, const float *u_dev, size_t n, float *out_dev, void *stream);
+/* x += y (the residual adds of model.rs:359,365). */
+int lbk_add_inplace(lbk_ctx *ctx, float *x_dev, const float *y_dev, size_t n, void *stream);
+/* argmax (crates/lb-model/src/sample.rs:17-25): first index of the maximum of each row. */
+int lbk_argmax(lbk_ctx *ctx, const float *logits_dev, size_t rows, size_t n, int32_t *out_dev, void *stream);
+/* *pos_dev += 1 (cache.len = total, model.rs:367). */
+int lbk_advance_pos(lbk_ctx *ctx, int32_t *pos_dev, void *stream);
 
 /* ---- plans: a whole decode-like sequence in one launch -----------------------------------
  * The reference runs 4 fused ternary ops per layer x 30 layers = 120 parallel regions per

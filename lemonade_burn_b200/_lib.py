@@ -42,8 +42,19 @@ SYMBOLS = [
     ("lbk_ternary_linear_n", _i, [_vp, _vp, _sz, _pp, _sz, _pp, _pp, _vp]),
     ("lbk_ternary_linear_prefill_static", _i, [_vp, _vp, _sz, _pp, _sz, _pp, _pp, _vp]),
     ("lbk_quantize_acts_dev", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
+    ("lbk_absmax_dev", _i, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    ("lbk_quantize_acts_amax_dev", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp, _vp]),
+    ("lbk_scale_epilogue_dev", _i, [_vp, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
     ("lbk_ternary_gemm_dev", _i, [_vp, _pp, _sz, _vp, _vp, _vp, _sz, _pp, _pp, _vp]),
     ("lbk_bf16_linear", _i, [_vp, _vp, _sz, _vp, _sz, _sz, _vp, _vp]),
+    ("lbk_embed_bf16", _i, [_vp, _vp, _vp, _sz, _sz, _vp, _vp]),
+    ("lbk_rms_norm", _i, [_vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
+    ("lbk_rope_kv_append", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_attn_decode", _i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_relu2_mul", _i, [_vp, _vp, _vp, _sz, _vp, _vp]),
+    ("lbk_add_inplace", _i, [_vp, _vp, _vp, _sz, _vp]),
+    ("lbk_argmax", _i, [_vp, _vp, _sz, _sz, _vp, _vp]),
+    ("lbk_advance_pos", _i, [_vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),
     ("lbk_plan_finalize", _i, [_vp]),

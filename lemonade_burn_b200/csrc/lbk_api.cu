@@ -315,6 +315,29 @@ int lbk_quantize_acts_dev(lbk_ctx *c, const float *x_dev, size_t m, size_t k, in
     return launch_quantize(C_(c), x_dev, m, k, q_dev, scale_dev, sum_dev, static_cast<cudaStream_t>(stream));
 }
 
+int lbk_absmax_dev(lbk_ctx *c, const float *x_dev, size_t m, size_t k, float *amax_dev, void *stream) {
+    if (!c) return fail(LBK_ERR_INVALID, "context is null");
+    if (m && (!amax_dev || (k && !x_dev))) return fail(LBK_ERR_INVALID, "lbk_absmax_dev: null buffer");
+    LBK_CUDA(cudaSetDevice(C_(c)->device));
+    return launch_quantize_ex(C_(c), x_dev, m, k, nullptr, nullptr, nullptr, nullptr, amax_dev, static_cast<cudaStream_t>(stream));
+}
+
+int lbk_quantize_acts_amax_dev(lbk_ctx *c, const float *x_dev, size_t m, size_t k, const float *amax_dev, int8_t *q_dev,
+                               float *scale_dev, int32_t *sum_dev, void *stream) {
+    if (!c) return fail(LBK_ERR_INVALID, "context is null");
+    if (m && (!q_dev || !scale_dev || !sum_dev || !amax_dev || (k && !x_dev))) return fail(LBK_ERR_INVALID, "lbk_quantize_acts_amax_dev: null buffer");
+    LBK_CUDA(cudaSetDevice(C_(c)->device));
+    return launch_quantize_ex(C_(c), x_dev, m, k, q_dev, scale_dev, sum_dev, amax_dev, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int lbk_scale_epilogue_dev(lbk_ctx *c, const int32_t *dots_dev, const float *scale_dev, float wscale, size_t m, size_t rows,
+                           float *out_dev, void *stream) {
+    if (!c) return fail(LBK_ERR_INVALID, "context is null");
+    if (m * rows && (!dots_dev || !scale_dev || !out_dev)) return fail(LBK_ERR_INVALID, "lbk_scale_epilogue_dev: null buffer");
+    LBK_CUDA(cudaSetDevice(C_(c)->device));
+    return launch_scale_epilogue(C_(c), dots_dev, scale_dev, wscale, m, rows, out_dev, static_cast<cudaStream_t>(stream));
+}
+
 static int fill_group(GroupArgs &g, const lbk_weight *const *ws, size_t n, float *const *outs, int32_t *const *iouts, size_t m) {
     g.n = static_cast<int>(n);
     g.m = m;

@@ -96,6 +96,11 @@ void sweep_free(SweepTables *tb);
 int launch_quantize(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
                     int32_t *sum, cudaStream_t stream);
 
+int launch_quantize_ex(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale, int32_t *sum,
+                       const float *amax_in, float *amax_out, cudaStream_t stream);
+int launch_scale_epilogue(Ctx *ctx, const int32_t *dots, const float *ascale, float wscale, size_t m, size_t rows,
+                          float *out, cudaStream_t stream);
+
 // tcgen05 int8 GEMM on quantised inputs (any m).
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
 

@@ -18,10 +18,15 @@ __device__ __forceinline__ int quant_one(float v, float scale) {
     return max(-128, min(127, r));
 }
 
+// amax_in: per-row max|x| supplied by the caller (tensor-parallel: the maximum over all ranks'
+// column slices), or null to compute it here. amax_out: when non-null only the row maximum is
+// written and nothing is quantised.
 __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__restrict__ x, int k,
                                                             int kp, int8_t *__restrict__ q,
                                                             float *__restrict__ scale,
-                                                            int32_t *__restrict__ sum) {
+                                                            int32_t *__restrict__ sum,
+                                                            const float *__restrict__ amax_in,
+                                                            float *__restrict__ amax_out) {
     __shared__ float s_f[kQThreads / 32];
     __shared__ int s_i[kQThreads / 32];
     __shared__ float s_scale;
@@ -31,7 +36,9 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__rest
     const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
 
     float am = 0.0f;  // fmaxf drops a NaN operand, as f32::max does (quant.rs:101-104)
-    if (vec) {
+    if (amax_in != nullptr) {
+        am = amax_in[row];
+    } else if (vec) {
         const float4 *x4 = reinterpret_cast<const float4 *>(xr);
         for (int i = tid; i < (k >> 2); i += kQThreads) {
             float4 v = __ldg(x4 + i);
@@ -46,9 +53,11 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__rest
     if (tid == 0) {
         float a = 0.0f;
         for (int w = 0; w < kQThreads / 32; ++w) a = fmaxf(a, s_f[w]);
+        if (amax_out != nullptr) amax_out[row] = a;
         s_scale = __fdiv_rn(127.0f, fmaxf(a, 1e-5f));
     }
     __syncthreads();
+    if (amax_out != nullptr) return;
     const float sc = s_scale;
     int acc = 0;
     for (int i = tid * 4; i < kp; i += kQThreads * 4) {
@@ -78,14 +87,49 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__rest
     }
 }
 
+// y[t, r] = (float)dot[t, r] * (1 / (s_a[t] * s_w)): the epilogue of gemm.rs:141,158 as a kernel
+// of its own, for dots that were summed across ranks first.
+__global__ void __launch_bounds__(256) scale_epilogue_kernel(const int32_t *__restrict__ dots,
+                                                            const float *__restrict__ ascale, float wscale,
+                                                            int rows, size_t total, float *__restrict__ out) {
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float inv = __fdiv_rn(1.0f, __fmul_rn(ascale[i / rows], wscale));
+        out[i] = __fmul_rn(__int2float_rn(dots[i]), inv);
+    }
+}
+
 }  // namespace
+
+int launch_scale_epilogue(Ctx *ctx, const int32_t *dots, const float *ascale, float wscale, size_t m, size_t rows,
+                          float *out, cudaStream_t stream) {
+    const size_t total = m * rows;
+    if (total == 0) return LBK_OK;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > static_cast<size_t>(ctx->sm_count) * 8) blocks = static_cast<size_t>(ctx->sm_count) * 8;
+    scale_epilogue_kernel<<<static_cast<unsigned>(blocks), 256, 0, stream>>>(dots, ascale, wscale, static_cast<int>(rows), total, out);
+    LBK_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return LBK_OK;
+}
+
+int launch_quantize_ex(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale, int32_t *sum,
+                       const float *amax_in, float *amax_out, cudaStream_t stream) {
+    if (m == 0) return LBK_OK;
+    const size_t kp = lbk_padded_cols(k);
+    quantize_kernel<<<static_cast<unsigned>(m), kQThreads, 0, stream>>>(x, static_cast<int>(k), static_cast<int>(kp), q,
+                                                                        scale, sum, amax_in, amax_out);
+    LBK_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return LBK_OK;
+}
 
 int launch_quantize(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, float *scale,
                     int32_t *sum, cudaStream_t stream) {
     if (m == 0) return LBK_OK;
     const size_t kp = lbk_padded_cols(k);
     quantize_kernel<<<static_cast<unsigned>(m), kQThreads, 0, stream>>>(
-        x, static_cast<int>(k), static_cast<int>(kp), q, scale, sum);
+        x, static_cast<int>(k), static_cast<int>(kp), q, scale, sum, nullptr, nullptr);
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
     return LBK_OK;

@@ -1,0 +1,232 @@
+"""BitNet b1.58 decoder on the GPU: the device-side mirror of lb-model's `BitNet`
+(crates/lb-model/src/model.rs). Same names and meaning: `Config`, `BitNet.load`,
+`BitNet.new_cache`, `BitNet.forward`, checkpoint format "lemonade-burn-ternary" v1
+(crates/lb-convert/src/lib.rs:1-16). Differences, all stated: the KV cache is bf16 (the
+reference keeps f32, model.rs:245), `forward` takes one new token per sequence (decode; `b`
+independent sequences advance together), and every op runs in liblbk.so.
+
+Per layer (model.rs:331-366):
+    n1 = rms(x); q,k,v = ternary3(n1); rope(q), rope(k); cache k,v; a = gqa(q, K, V)
+    x += o(rms(a, attn_sub_norm)); n2 = rms(x)
+    g,u = ternary2(n2); x += down(rms(relu(g)^2 * u, ffn_sub_norm))
+then final norm, bf16 LM head (tied embedding), greedy argmax.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import json
+import math
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Dict, Optional
+
+import numpy as np
+import torch
+
+from . import _lib, ops
+from .pack import row_bytes
+from .ternary import Context, default_context
+
+FORMAT = "lemonade-burn-ternary"      # lb-convert/src/lib.rs:14
+FILE_NAME = "model.lbt.safetensors"   # lb-convert/src/lib.rs:16
+LINEARS = ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+           "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj"]  # lb-convert/src/lib.rs:18-26
+
+
+@dataclass
+class Config:
+    """model.rs:23-42"""
+    hidden_size: int
+    intermediate_size: int
+    num_attention_heads: int
+    num_key_value_heads: int
+    num_hidden_layers: int
+    vocab_size: int
+    rms_norm_eps: float
+    rope_theta: float
+    max_position_embeddings: int
+    hidden_act: str = "relu2"
+    tie_word_embeddings: bool = True
+    bos_token_id: int = 0
+
+    def head_dim(self) -> int:
+        return self.hidden_size // self.num_attention_heads
+
+    @staticmethod
+    def bitnet_2b4t(layers: int = 30, max_pos: int = 4352) -> "Config":
+        return Config(2560, 6912, 20, 5, layers, 128256, 1e-5, 500000.0, max_pos)
+
+
+def rope_tables(cfg: Config):
+    """model.rs:213-230: inv_freq in f32, freq = pos as f32 * inv (f32), sin/cos in f64, stored
+    f32, duplicated to both halves."""
+    hd = cfg.head_dim()
+    inv = np.array([1.0 / cfg.rope_theta ** ((2 * i) / hd) for i in range(hd // 2)], dtype=np.float64).astype(np.float32)
+    pos = np.arange(cfg.max_position_embeddings, dtype=np.float32)
+    f = (pos[:, None] * inv[None, :]).astype(np.float32).astype(np.float64)
+    cos = np.concatenate([np.cos(f), np.cos(f)], axis=1).astype(np.float32)
+    sin = np.concatenate([np.sin(f), np.sin(f)], axis=1).astype(np.float32)
+    return cos, sin
+
+
+class KvCache:
+    """model.rs:136-141, here fixed capacity, bf16, [layers][b][kv_heads][cap][head_dim]."""
+
+    def __init__(self, cfg: Config, b: int, cap: int, device):
+        shape = (cfg.num_hidden_layers, b, cfg.num_key_value_heads, cap, cfg.head_dim())
+        self.k = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros(shape, dtype=torch.bfloat16, device=device)
+        self.pos = torch.zeros(1, dtype=torch.int32, device=device)  # cache.len, on the device
+        self.b, self.cap = b, cap
+
+    @property
+    def len(self) -> int:
+        return int(self.pos.item())
+
+
+class BitNet:
+    def __init__(self, cfg: Config, tensors: Dict[str, torch.Tensor], ctx: Optional[Context] = None, device="cuda:0"):
+        if cfg.hidden_act != "relu2" or not cfg.tie_word_embeddings:  # model.rs:151-153
+            raise ValueError(f"unsupported config: act={cfg.hidden_act} tied={cfg.tie_word_embeddings}")
+        self.cfg, self.ctx, self.device = cfg, ctx or default_context(), torch.device(device)
+        dev = self.device
+        H, I = cfg.hidden_size, cfg.intermediate_size
+
+        def linear(name, cols):
+            qw = tensors[f"{name}.qweight"]
+            if qw.dtype != torch.uint8 or qw.shape[1] != row_bytes(cols):
+                raise ValueError(f"{name}: unexpected dtype/shape")
+            scale = float(tensors[f"{name}.wscale"].reshape(-1)[0])
+            return ops.TernaryLinear(qw.to(dev), scale, cols, self.ctx)
+
+        def vec(name):
+            t = tensors[name]
+            if t.dtype != torch.float32:
+                raise ValueError(f"{name}: expected F32")  # model.rs:165
+            return t.to(dev).contiguous()
+
+        self.layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}"
+            self.layers.append(dict(
+                input_norm=vec(f"{p}.input_layernorm.weight"), post_attn_norm=vec(f"{p}.post_attention_layernorm.weight"),
+                attn_sub_norm=vec(f"{p}.self_attn.attn_sub_norm.weight"), ffn_sub_norm=vec(f"{p}.mlp.ffn_sub_norm.weight"),
+                q=linear(f"{p}.self_attn.q_proj", H), k=linear(f"{p}.self_attn.k_proj", H), v=linear(f"{p}.self_attn.v_proj", H),
+                o=linear(f"{p}.self_attn.o_proj", H), gate=linear(f"{p}.mlp.gate_proj", H), up=linear(f"{p}.mlp.up_proj", H),
+                down=linear(f"{p}.mlp.down_proj", I)))
+        self.final_norm = vec("model.norm.weight")
+        emb = tensors["model.embed_tokens.weight"]
+        if emb.dtype != torch.bfloat16 or tuple(emb.shape) != (cfg.vocab_size, H):  # model.rs:204
+            raise ValueError("embed_tokens: unexpected dtype/shape")
+        self.lm_head = emb.to(dev).contiguous()
+        cos, sin = rope_tables(cfg)
+        self.cos, self.sin = torch.from_numpy(cos).to(dev), torch.from_numpy(sin).to(dev)
+        self._bufs = {}
+
+    # ---- checkpoint --------------------------------------------------------------------------
+    @classmethod
+    def load(cls, directory, ctx: Optional[Context] = None, device="cuda:0") -> "BitNet":
+        """model.rs:149-232: config.json + model.lbt.safetensors with metadata format check."""
+        from safetensors import safe_open
+        directory = Path(directory)
+        raw = json.loads((directory / "config.json").read_text())
+        cfg = Config(**{k: raw[k] for k in Config.__dataclass_fields__ if k in raw})
+        path = directory / FILE_NAME
+        tensors = {}
+        with safe_open(str(path), framework="pt", device="cpu") as f:
+            meta = f.metadata() or {}
+            if meta.get("format") != FORMAT:  # model.rs:158-161
+                raise ValueError(f"{path} is not a lemonade-burn ternary file (format={meta.get('format')!r})")
+            for k in f.keys():
+                tensors[k] = f.get_tensor(k)
+        return cls(cfg, tensors, ctx, device)
+
+    def new_cache(self, b: int = 1, cap: Optional[int] = None) -> KvCache:
+        """model.rs:234-236"""
+        return KvCache(self.cfg, b, cap or self.cfg.max_position_embeddings, self.device)
+
+    # ---- one decode step -------------------------------------------------------------------------
+    def _buf(self, name, shape, dtype=torch.float32):
+        key = (name, tuple(shape), dtype)
+        if key not in self._bufs:
+            self._bufs[key] = torch.empty(shape, dtype=dtype, device=self.device)
+        return self._bufs[key]
+
+    def forward(self, tokens: torch.Tensor, cache: KvCache, splits: int = 32) -> torch.Tensor:
+        """One new token per sequence at position cache.len (model.rs:305-374 with m = 1).
+        tokens: int32 CUDA [b]. Returns logits f32 [b, vocab] and advances the cache."""
+        cfg, lib, h = self.cfg, self.ctx._lib, self.ctx.handle
+        b = tokens.shape[0]
+        if b != cache.b:
+            raise ValueError("batch size differs from the cache's")
+        H, I, nh, kvh, hd = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim()
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        P = lambda t: C.c_void_p(t.data_ptr())
+        eps = C.c_float(cfg.rms_norm_eps)
+        x = self._buf("x", (b, H))
+        n = self._buf("n", (b, H))
+        attn = self._buf("attn", (b, nh * hd))
+        act = self._buf("act", (b, I))
+        scratch = self._buf("attn_part", (b * nh * splits * (hd + 4),))
+        chk = _lib.check
+        chk(lib.lbk_embed_bf16(h, P(self.lm_head), P(tokens), b, H, P(x), st))
+        for li, l in enumerate(self.layers):
+            chk(lib.lbk_rms_norm(h, P(x), P(l["input_norm"]), b, H, eps, P(n), st))
+            q, k, v = ops.ternary_linear3(n, [l["q"], l["k"], l["v"]])
+            chk(lib.lbk_rope_kv_append(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
+                                       P(cache.k[li]), P(cache.v[li]), st))
+            chk(lib.lbk_attn_decode(h, P(q), P(cache.k[li]), P(cache.v[li]), P(cache.pos), b, nh, kvh, hd, cache.cap, splits,
+                                    P(scratch), P(attn), st))
+            chk(lib.lbk_rms_norm(h, P(attn), P(l["attn_sub_norm"]), b, nh * hd, eps, P(attn), st))
+            o = ops.ternary_linear(attn, l["o"])
+            chk(lib.lbk_add_inplace(h, P(x), P(o), b * H, st))
+            chk(lib.lbk_rms_norm(h, P(x), P(l["post_attn_norm"]), b, H, eps, P(n), st))
+            g, u = ops.ternary_linear2(n, [l["gate"], l["up"]])
+            chk(lib.lbk_relu2_mul(h, P(g), P(u), b * I, P(act), st))
+            chk(lib.lbk_rms_norm(h, P(act), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+            d = ops.ternary_linear(act, l["down"])
+            chk(lib.lbk_add_inplace(h, P(x), P(d), b * H, st))
+        chk(lib.lbk_rms_norm(h, P(x), P(self.final_norm), b, H, eps, P(n), st))
+        logits = ops.bf16_linear(n, self.lm_head, self.ctx)
+        chk(lib.lbk_advance_pos(h, P(cache.pos), st))
+        return logits
+
+    def argmax(self, logits: torch.Tensor) -> torch.Tensor:
+        """sample.rs:17-25 on the device."""
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        _lib.check(self.ctx._lib.lbk_argmax(self.ctx.handle, C.c_void_p(logits.data_ptr()), logits.shape[0], logits.shape[1],
+                                            C.c_void_p(out.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return out
+
+
+def random_checkpoint(cfg: Config, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random-init weights in checkpoint naming (there is no real checkpoint where this is built):
+    valid ternary codes, scales near 1/mean|N(0,0.02)|, norm gains near 1, bf16 embedding N(0,0.02)."""
+    g = torch.Generator().manual_seed(seed)
+    H, I, hd = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim()
+    rows = {"self_attn.q_proj": (cfg.num_attention_heads * hd, H), "self_attn.k_proj": (cfg.num_key_value_heads * hd, H),
+            "self_attn.v_proj": (cfg.num_key_value_heads * hd, H), "self_attn.o_proj": (H, cfg.num_attention_heads * hd),
+            "mlp.gate_proj": (I, H), "mlp.up_proj": (I, H), "mlp.down_proj": (H, I)}
+    t: Dict[str, torch.Tensor] = {}
+    for i in range(cfg.num_hidden_layers):
+        p = f"model.layers.{i}"
+        for name, (r, c) in rows.items():
+            b = torch.randint(0, 256, (r, row_bytes(c)), dtype=torch.uint8, generator=g)
+            t[f"{p}.{name}.qweight"] = b & ~((b >> 1) & b & 0x55)   # code 3 -> 1: valid ternary
+            t[f"{p}.{name}.wscale"] = torch.tensor([60.0 + 5.0 * torch.rand(1, generator=g).item()], dtype=torch.float32)
+        for nm, sz in (("input_layernorm", H), ("post_attention_layernorm", H), ("self_attn.attn_sub_norm", H), ("mlp.ffn_sub_norm", I)):
+            t[f"{p}.{nm}.weight"] = (1.0 + 0.05 * torch.randn(sz, generator=g)).float()
+    t["model.norm.weight"] = (1.0 + 0.05 * torch.randn(H, generator=g)).float()
+    t["model.embed_tokens.weight"] = (0.02 * torch.randn(cfg.vocab_size, H, generator=g)).to(torch.bfloat16)
+    return t
+
+
+def save_checkpoint(directory, cfg: Config, tensors: Dict[str, torch.Tensor]) -> None:
+    """Writes config.json + model.lbt.safetensors with the metadata lb-convert writes
+    (crates/lb-convert/src/main.rs:111-115)."""
+    from safetensors.torch import save_file
+    directory = Path(directory)
+    directory.mkdir(parents=True, exist_ok=True)
+    (directory / "config.json").write_text(json.dumps(cfg.__dict__))
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(directory / FILE_NAME),
+              metadata={"format": FORMAT, "version": "1", "quant": "absmean-ternary", "layout": "lb-ternary-128x2bit"})

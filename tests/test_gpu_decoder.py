@@ -1,0 +1,105 @@
+"""One decode step of the BitNet decoder on the GPU against the CPU restatement of
+crates/lb-model/src/model.rs:305-374 (oracle/decoder_oracle.py). The projections are bit-exact by
+themselves (tested elsewhere); everything between them is float math whose summation order the
+reference does not pin, so the bar here is the reference's own end-to-end metrics
+(crates/lb-model/src/bin/lb-run.rs:223-259): greedy token equality where the margin is clear, and
+max |delta logit| small against the logit range. Tolerance: 2e-3 of max |logit|."""
+import json
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+TOL = 2e-3
+
+
+def _to_oracle_weights(cfg, tensors):
+    import torch
+    from oracle import decoder_oracle as D
+    w = {}
+    for k, v in tensors.items():
+        w[k] = v.view(torch.int16).numpy().view(np.uint16) if v.dtype == torch.bfloat16 else v.numpy()
+    w["_cos"], w["_sin"] = D.rope_tables(cfg.head_dim(), cfg.rope_theta, cfg.max_position_embeddings)
+    return w
+
+
+def _run(cfg, b, steps, ctx, seed=1):
+    import torch
+    from lemonade_burn_b200 import model
+    from oracle import decoder_oracle as D
+    tensors = model.random_checkpoint(cfg, seed)
+    net = model.BitNet(cfg, tensors, ctx)
+    cache = net.new_cache(b=b, cap=cfg.max_position_embeddings)
+    w = _to_oracle_weights(cfg, tensors)
+    c = cfg.__dict__
+    kvh, hd = cfg.num_key_value_heads, cfg.head_dim()
+    okc = [[np.zeros((kvh, cfg.max_position_embeddings, hd), np.float32) for _ in range(cfg.num_hidden_layers)] for _ in range(b)]
+    ovc = [[np.zeros((kvh, cfg.max_position_embeddings, hd), np.float32) for _ in range(cfg.num_hidden_layers)] for _ in range(b)]
+    rng = np.random.default_rng(seed)
+    toks = rng.integers(0, cfg.vocab_size, size=(steps, b)).astype(np.int32)
+    worst = 0.0
+    for s in range(steps):
+        logits = net.forward(torch.from_numpy(toks[s]).cuda(), cache)
+        greedy = net.argmax(logits).cpu().numpy()
+        got = logits.cpu().numpy()
+        for bi in range(b):
+            ref = D.decode_step(c, w, int(toks[s, bi]), okc[bi], ovc[bi], s)
+            scale = np.abs(ref).max()
+            err = np.abs(got[bi] - ref).max() / scale
+            worst = max(worst, err)
+            assert err < TOL, f"step {s} seq {bi}: max |delta logit| / max |logit| = {err}"
+            srt = np.sort(ref)
+            if srt[-1] - srt[-2] > 4 * TOL * scale:
+                assert greedy[bi] == int(np.argmax(ref))
+            assert greedy[bi] == int(np.argmax(got[bi]))  # device argmax == first max of its own logits
+    assert cache.len == steps
+    ctx.check_device_error()
+    return worst
+
+
+def test_small_decoder_batch2(ctx):
+    from lemonade_burn_b200 import model
+    cfg = model.Config(512, 768, 4, 2, 2, 1000, 1e-5, 500000.0, 16)
+    _run(cfg, b=2, steps=6, ctx=ctx)
+
+
+def test_bitnet_width_two_layers(ctx):
+    """Full BitNet-2B4T layer shapes (hidden 2560, 20/5 heads of 128, intermediate 6912), two layers,
+    reduced vocabulary, batch 1 and 3."""
+    from lemonade_burn_b200 import model
+    cfg = model.Config(2560, 6912, 20, 5, 2, 8000, 1e-5, 500000.0, 8)
+    _run(cfg, b=1, steps=3, ctx=ctx, seed=2)
+    _run(cfg, b=3, steps=2, ctx=ctx, seed=3)
+
+
+def test_checkpoint_roundtrip_and_format_check(ctx, tmp_path):
+    import torch
+    from safetensors.torch import save_file
+    from lemonade_burn_b200 import model
+    cfg = model.Config(512, 768, 4, 2, 1, 500, 1e-5, 500000.0, 8)
+    tensors = model.random_checkpoint(cfg, 5)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    a = model.BitNet(cfg, tensors, ctx)
+    b = model.BitNet.load(tmp_path, ctx)
+    tok = torch.tensor([7], dtype=torch.int32, device="cuda")
+    la = a.forward(tok, a.new_cache(1, 8))
+    lb = b.forward(tok, b.new_cache(1, 8))
+    assert torch.equal(la, lb)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / model.FILE_NAME), metadata={"format": "something-else"})
+    with pytest.raises(ValueError, match="not a lemonade-burn ternary file"):   # model.rs:158-161
+        model.BitNet.load(tmp_path, ctx)
+    bad = dict(cfg.__dict__, hidden_act="silu")
+    (tmp_path / "config.json").write_text(json.dumps(bad))
+    with pytest.raises(ValueError):
+        model.BitNet.load(tmp_path, ctx)
+
+
+def test_argmax_first_max(ctx):
+    import torch
+    from lemonade_burn_b200 import model
+    cfg = model.Config(512, 768, 4, 2, 1, 500, 1e-5, 500000.0, 8)
+    net = model.BitNet(cfg, model.random_checkpoint(cfg, 6), ctx)
+    x = torch.full((3, 128256), -1.0, device="cuda")
+    x[0, 777] = 5.0; x[0, 90000] = 5.0          # first of two equal maxima
+    x[2, 128255] = 0.5
+    assert net.argmax(x).cpu().tolist() == [777, 0, 128255]

@@ -1,0 +1,131 @@
+"""Tensor-parallel pieces on the GPU. With one GPU the ranks are emulated in one process (their
+slices run one after the other and the two all-reduces are done by hand on the device), which
+checks the kernels the multi-GPU path is made of; with two or more GPUs the same layer runs as
+NCCL ranks (child processes) and must reproduce the unsharded output bit for bit."""
+import ctypes as C
+import os
+import socket
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _case(oracle, rows=2560, cols=1024, m=40, seed=3):
+    rng = np.random.default_rng(seed)
+    t = rng.choice(np.array([-1, 0, 1], dtype=np.int8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+    x = rng.standard_normal((m, cols)).astype(np.float32)
+    x[m - 1, cols - 5] = 11.0  # the last token row has its maximum in the last rank's slice
+    return oracle.pack_matrix(t), np.float32(57.25), x
+
+
+@pytest.mark.parametrize("m", [1, 7, 40, 200])
+@pytest.mark.parametrize("world", [2, 4])
+def test_emulated_ranks_row_parallel(oracle, ctx, world, m):
+    import torch
+    from lemonade_burn_b200 import _lib, ops, tp
+    packed, ws, x = _case(oracle, m=m)
+    rows, cols = packed.shape[0], x.shape[1]
+    lib, h = ctx._lib, ctx.handle
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    lins, xs, amaxs = [], [], []
+    for r in range(world):
+        sl, lc = tp.shard_cols(packed, cols, world, r)
+        lins.append(ops.TernaryLinear(torch.from_numpy(np.ascontiguousarray(sl)).cuda(), float(ws), lc, ctx))
+        xs.append(torch.from_numpy(np.ascontiguousarray(x[:, r * lc:(r + 1) * lc])).cuda())
+        a = torch.empty(m, device="cuda")
+        _lib.check(lib.lbk_absmax_dev(h, C.c_void_p(xs[r].data_ptr()), m, lc, C.c_void_p(a.data_ptr()), st))
+        amaxs.append(a)
+    amax = torch.stack(amaxs).max(dim=0).values.contiguous()          # all-reduce MAX
+    total = torch.zeros((m, rows), dtype=torch.int32, device="cuda")
+    scale = None
+    for r in range(world):
+        lc = lins[r].cols
+        q = torch.empty((m, lc), dtype=torch.int8, device="cuda")
+        scale = torch.empty(m, device="cuda")
+        ssum = torch.empty(m, dtype=torch.int32, device="cuda")
+        _lib.check(lib.lbk_quantize_acts_amax_dev(h, C.c_void_p(xs[r].data_ptr()), m, lc, C.c_void_p(amax.data_ptr()),
+                                                  C.c_void_p(q.data_ptr()), C.c_void_p(scale.data_ptr()),
+                                                  C.c_void_p(ssum.data_ptr()), st))
+        dots = torch.empty((m, rows), dtype=torch.int32, device="cuda")
+        wp, _k1 = _lib.ptr_array([lins[r].weight.handle.value])
+        ip, _k2 = _lib.ptr_array([dots.data_ptr()])
+        _lib.check(lib.lbk_ternary_gemm_dev(h, wp, 1, C.c_void_p(q.data_ptr()), None, C.c_void_p(ssum.data_ptr()), m, None, ip, st))
+        total += dots                                                   # all-reduce SUM (exact)
+    out = torch.empty((m, rows), device="cuda")
+    _lib.check(lib.lbk_scale_epilogue_dev(h, C.c_void_p(total.data_ptr()), C.c_void_p(scale.data_ptr()), C.c_float(float(ws)),
+                                          m, rows, C.c_void_p(out.data_ptr()), st))
+    torch.cuda.synchronize()
+    q, s, ssum = oracle.quantize_acts(x)
+    wf, wi = oracle.simd_gemm_multi([packed], [ws], q, s, ssum, want_i32=True)
+    assert np.array_equal(scale.cpu().numpy().view(np.uint32), s.view(np.uint32))
+    assert np.array_equal(total.cpu().numpy(), wi[0])
+    assert np.array_equal(out.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
+    ctx.check_device_error()
+
+
+def test_world_one_layers(oracle, ctx):
+    import torch
+    from lemonade_burn_b200 import tp
+    packed, ws, x = _case(oracle, rows=640, m=3)
+    cols = x.shape[1]
+    row = tp.RowParallelTernary(packed, ws, cols, 1, 0, ctx=ctx)
+    col = tp.ColumnParallelTernary([packed], [ws], cols, 1, 0, ctx=ctx)
+    xd = torch.from_numpy(x).cuda()
+    out, dots = row.forward(xd)
+    ref = col.forward(xd)[0]
+    assert torch.equal(out, ref)
+    q, s, ssum = oracle.quantize_acts(x)
+    assert np.array_equal(dots.cpu().numpy(), oracle.ternary_gemm_i32(packed, cols, q, ssum))
+
+
+def _nccl_worker(rank, world, port, ok_q):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lemonade_burn_b200 import ternary, tp
+        from oracle import oracle as o
+        ctx = ternary.Context(rank)
+        packed, ws, x = _case(o, m=40)
+        cols = x.shape[1]
+        lc = cols // world
+        row = tp.RowParallelTernary(packed, ws, cols, world, rank, ctx=ctx)
+        out, dots = row.forward(torch.from_numpy(np.ascontiguousarray(x[:, rank * lc:(rank + 1) * lc])).cuda())
+        col = tp.ColumnParallelTernary([packed], [ws], cols, world, rank, ctx=ctx)
+        part = col.forward(torch.from_numpy(x).cuda())[0]
+        torch.cuda.synchronize()
+        q, s, ssum = o.quantize_acts(x)
+        wf, wi = o.simd_gemm_multi([packed], [ws], q, s, ssum, want_i32=True)
+        n = packed.shape[0] // world
+        ok = (np.array_equal(dots.cpu().numpy(), wi[0]) and np.array_equal(out.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
+              and np.array_equal(part.cpu().numpy().view(np.uint32), wf[0][:, rank * n:(rank + 1) * n].view(np.uint32)))
+        ok_q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_nccl_ranks_match_unsharded():
+    import torch
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    ok_q = mpc.Queue()
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    procs = [mpc.Process(target=_nccl_worker, args=(r, world, port, ok_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [ok_q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in res), res
