@@ -149,6 +149,60 @@ def config2_prefill(torch, ops, ctx, device, ms=(64, 256, 1024, 2048), reps=5, p
             "cases": out}
 
 
+def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
+    """Config 3: full decode step of a random-init BitNet-b1.58-2B4T-architecture decoder (30 layers,
+    20/5 heads of 128, tied 128256-token bf16 head) at position `context` of a seeded bf16 KV cache,
+    greedy next token on the device. One CUDA graph per step, replayed `steps` times."""
+    from lemonade_burn_b200 import model
+    cfg = model.Config.bitnet_2b4t(max_pos=context + 64)
+    net = model.BitNet(cfg, model.random_checkpoint(cfg, 11, device=device), ctx, device)
+    res = []
+    for b in batches:
+        cache = net.new_cache(b=b, cap=context + 64)
+        g = torch.Generator(device=device).manual_seed(100 + b)
+        for t in (cache.k, cache.v):  # seeded cache contents, in slabs to bound temporary memory
+            for li in range(cfg.num_hidden_layers):
+                t[li].copy_(torch.randn(t[li].shape, generator=g, device=device).to(torch.bfloat16))
+        tokens = torch.randint(0, cfg.vocab_size, (b,), dtype=torch.int32, device=device, generator=g)
+        nxt = torch.zeros(b, dtype=torch.int32, device=device)
+
+        def step():
+            logits = net.forward(tokens, cache)
+            nxt.copy_(net.argmax(logits))
+
+        cache.pos.fill_(context)
+        step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        cache.pos.fill_(context)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                step()
+        torch.cuda.synchronize()
+        cache.pos.fill_(context)
+        graph.replay()
+        torch.cuda.synchronize()
+        cache.pos.fill_(context)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        kv_bytes = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * (context + steps // 2) * cfg.head_dim() * 2 * b
+        head_bytes = cfg.vocab_size * cfg.hidden_size * 2 * ((b + 3) // 4)   # the head streams W once per 4 token rows
+        nbytes = weight_bytes_per_sweep() + head_bytes + kv_bytes
+        res.append({"batch": b, "ms_per_step": ms, "tok_per_s": b / (ms * 1e-3), "context": context,
+                    "algorithmic_bytes_per_step": nbytes, "GBps": nbytes / (ms * 1e-3) / 1e9,
+                    "next_tokens": nxt.cpu().tolist()[:4]})
+        del cache, graph
+        torch.cuda.empty_cache()
+    return {"workload": "BitNet-2B4T-architecture decode step, random init, bf16 KV cache, greedy", "cases": res}
+
+
 # ---------------------------------------------------------------------------------------
 # config 4: 70B-shaped ternary decoder, tensor parallel (column-parallel q/k/v/gate/up,
 # row-parallel o/down with an exact int32 all-reduce), batch-64 decode weight sweep
@@ -505,6 +559,9 @@ def run_ours(args):
                  "config2_prefill": config2_prefill(torch, ops, ctx, device)}
     del plan, linears
     torch.cuda.empty_cache()
+    if rank == 0 and world == 1:
+        extra["config3_decode"] = config3_decode(torch, ctx, device)
+        torch.cuda.empty_cache()
     tp_res = None
     if args.tp70b or world > 1:
         tp_res = tp70b_sweep(torch, dist, ctx, device, world, rank, layers=args.tp_layers)

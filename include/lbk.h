@@ -202,6 +202,13 @@ int lbk_attn_decode(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev
 int lbk_relu2_mul(lbk_ctx *ctx, const float *g_dev, const float *u_dev, size_t n, float *out_dev, void *stream);
 /* x += y (the residual adds of model.rs:359,365). */
 int lbk_add_inplace(lbk_ctx *ctx, float *x_dev, const float *y_dev, size_t n, void *stream);
+/* Fusions of the above for the decode step (rows of a multiple of 4, at most 8192, columns;
+ * 16-byte aligned): x += y then out = rms_norm(x) (model.rs:359-361, 365 + the next norm); and
+ * out = rms_norm(relu(g)^2 * u) (model.rs:363-364). */
+int lbk_add_rms_norm(lbk_ctx *ctx, float *x_dev, const float *y_dev, const float *w_dev, size_t rows, size_t n,
+                     float eps, float *out_dev, void *stream);
+int lbk_relu2_mul_rms_norm(lbk_ctx *ctx, const float *g_dev, const float *u_dev, const float *w_dev, size_t rows,
+                           size_t n, float eps, float *out_dev, void *stream);
 /* argmax (crates/lb-model/src/sample.rs:17-25): first index of the maximum of each row. */
 int lbk_argmax(lbk_ctx *ctx, const float *logits_dev, size_t rows, size_t n, int32_t *out_dev, void *stream);
 /* *pos_dev += 1 (cache.len = total, model.rs:367). */

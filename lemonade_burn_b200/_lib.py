@@ -53,6 +53,8 @@ SYMBOLS = [
     ("lbk_attn_decode", _i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
     ("lbk_relu2_mul", _i, [_vp, _vp, _vp, _sz, _vp, _vp]),
     ("lbk_add_inplace", _i, [_vp, _vp, _vp, _sz, _vp]),
+    ("lbk_add_rms_norm", _i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
+    ("lbk_relu2_mul_rms_norm", _i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
     ("lbk_argmax", _i, [_vp, _vp, _sz, _sz, _vp, _vp]),
     ("lbk_advance_pos", _i, [_vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),

@@ -181,7 +181,7 @@ int lbk_init(int device, lbk_ctx **out) {
     ctx->device = device;
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
-    if (cudaMalloc(&ctx->err_word, sizeof(int)) != cudaSuccess || cudaMemset(ctx->err_word, 0, sizeof(int)) != cudaSuccess ||
+    if (cudaMalloc(&ctx->small_scratch, kSmallScratchBytes) != cudaSuccess || cudaMalloc(&ctx->err_word, sizeof(int)) != cudaSuccess || cudaMemset(ctx->err_word, 0, sizeof(int)) != cudaSuccess ||
         cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess) {
         delete ctx;
         return fail(LBK_ERR_CUDA, "context setup failed: %s", cudaGetErrorString(cudaGetLastError()));
@@ -202,6 +202,7 @@ int lbk_destroy(lbk_ctx *c) {
     cudaDeviceSynchronize();
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->err_word) cudaFree(ctx->err_word);
+    if (ctx->small_scratch) cudaFree(ctx->small_scratch);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return LBK_OK;

@@ -52,11 +52,36 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x, const flo
                                                       float eps, float *out) {  // out may alias x
     __shared__ float s_red[8];
     const float *xr = x + static_cast<size_t>(blockIdx.x) * n;
+    float *orow = out + static_cast<size_t>(blockIdx.x) * n;
+    const bool vec = (n & 3) == 0 && n <= 8192 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(out) |
+                                                     reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+    if (vec) {
+        // the row is read once and stays in registers between the reduction and the scaling
+        const int n4 = n >> 2;
+        float4 v[8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = threadIdx.x + j * 256;
+            v[j] = i < n4 ? reinterpret_cast<const float4 *>(xr)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+        }
+        const float r = 1.0f / sqrtf(block_sum(ss, s_red) / static_cast<float>(n) + eps);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int i = threadIdx.x + j * 256;
+            if (i < n4) {
+                const float4 g = __ldg(reinterpret_cast<const float4 *>(w) + i);
+                reinterpret_cast<float4 *>(orow)[i] = make_float4(v[j].x * r * g.x, v[j].y * r * g.y, v[j].z * r * g.z, v[j].w * r * g.w);
+            }
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int i = threadIdx.x; i < n; i += 256) ss += xr[i] * xr[i];
     const float mean = block_sum(ss, s_red) / static_cast<float>(n);
     const float r = 1.0f / sqrtf(mean + eps);
-    for (int i = threadIdx.x; i < n; i += 256) out[static_cast<size_t>(blockIdx.x) * n + i] = xr[i] * r * w[i];
+    for (int i = threadIdx.x; i < n; i += 256) orow[i] = xr[i] * r * w[i];
 }
 
 // One block per (sequence, head). q heads first, then k heads (which are also written to the
@@ -112,20 +137,40 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
     const uint16_t *vb = vc + (static_cast<size_t>(b) * kvh + kh) * cap * kHd;
     float mx = -INFINITY, sum = 0.0f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int p = p0; p < p1; ++p) {
-        const uint2 kr = *reinterpret_cast<const uint2 *>(kb + static_cast<size_t>(p) * kHd + lane * 4);
-        float d = qv.x * bf16_to_f32(kr.x & 0xffff) + qv.y * bf16_to_f32(kr.x >> 16) + qv.z * bf16_to_f32(kr.y & 0xffff) +
-                  qv.w * bf16_to_f32(kr.y >> 16);
-        for (int o = 16; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-        const float sc = d * scaling;
-        const float nm = fmaxf(mx, sc);
-        const float corr = __expf(mx - nm), w = __expf(sc - nm);
-        const uint2 vr = *reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(p) * kHd + lane * 4);
-        acc.x = acc.x * corr + w * bf16_to_f32(vr.x & 0xffff);
-        acc.y = acc.y * corr + w * bf16_to_f32(vr.x >> 16);
-        acc.z = acc.z * corr + w * bf16_to_f32(vr.y & 0xffff);
-        acc.w = acc.w * corr + w * bf16_to_f32(vr.y >> 16);
-        sum = sum * corr + w;
+    constexpr int U = 8;  // positions in flight per iteration: their loads and shuffle trees overlap
+    for (int pc = p0; pc < p1; pc += U) {
+        float sc[U];
+        uint2 vr[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int p = pc + j < p1 ? pc + j : p1 - 1;
+            const uint2 kr = *reinterpret_cast<const uint2 *>(kb + static_cast<size_t>(p) * kHd + lane * 4);
+            vr[j] = *reinterpret_cast<const uint2 *>(vb + static_cast<size_t>(p) * kHd + lane * 4);
+            sc[j] = qv.x * bf16_to_f32(kr.x & 0xffff) + qv.y * bf16_to_f32(kr.x >> 16) + qv.z * bf16_to_f32(kr.y & 0xffff) +
+                    qv.w * bf16_to_f32(kr.y >> 16);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+            for (int j = 0; j < U; ++j) sc[j] += __shfl_xor_sync(0xffffffffu, sc[j], o);
+        float nm = mx;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            sc[j] = pc + j < p1 ? sc[j] * scaling : -INFINITY;
+            nm = fmaxf(nm, sc[j]);
+        }
+        const float corr = __expf(mx - nm);
+        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+        sum *= corr;
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const float w = __expf(sc[j] - nm);  // 0 for the padded tail
+            acc.x += w * bf16_to_f32(vr[j].x & 0xffff);
+            acc.y += w * bf16_to_f32(vr[j].x >> 16);
+            acc.z += w * bf16_to_f32(vr[j].y & 0xffff);
+            acc.w += w * bf16_to_f32(vr[j].y >> 16);
+            sum += w;
+        }
         mx = nm;
     }
     float *o = part + ((static_cast<size_t>(b) * nh + head) * splits + sp) * kPartStride;
@@ -138,19 +183,99 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
 
 __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
+    extern __shared__ float s_w[];  // [splits] weights exp(m_s - m), then their normaliser in s_w[splits]
+    __shared__ float s_red[4];
     const size_t bh = blockIdx.x;  // b * nh + head
     const float *p = part + bh * splits * kPartStride;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float mx = -INFINITY;
-    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, p[s * kPartStride + kHd]);
-    float sum = 0.0f, acc = 0.0f;
-    for (int s = 0; s < splits; ++s) {
+    for (int s = tid; s < splits; s += 128) mx = fmaxf(mx, p[s * kPartStride + kHd]);
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[warp] = mx;
+    __syncthreads();
+    mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    float sum = 0.0f;
+    for (int s = tid; s < splits; s += 128) {
         const float m = p[s * kPartStride + kHd];
-        if (m == -INFINITY) continue;  // empty slice
-        const float w = __expf(m - mx);
+        const float w = m == -INFINITY ? 0.0f : __expf(m - mx);  // empty slices weigh nothing
+        s_w[s] = w;
         sum += w * p[s * kPartStride + kHd + 1];
-        acc += w * p[s * kPartStride + threadIdx.x];
     }
-    out[bh * kHd + threadIdx.x] = acc / sum;
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    __syncthreads();
+    if (lane == 0) s_red[warp] = sum;
+    __syncthreads();
+    sum = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    float acc = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < splits; ++s) acc += s_w[s] * p[s * kPartStride + tid];
+    out[bh * kHd + tid] = acc / sum;
+}
+
+// x += y, then out = rms_norm(x): the residual add of model.rs:359,365 fused with the norm that
+// follows it (model.rs:361 and the next layer's :332 / the final :369).
+__global__ void __launch_bounds__(256) add_rms_norm_kernel(float *x, const float *__restrict__ y, const float *__restrict__ w, int n,
+                                                          float eps, float *__restrict__ out) {
+    __shared__ float s_red[8];
+    float *xr = x + static_cast<size_t>(blockIdx.x) * n;
+    const float *yr = y + static_cast<size_t>(blockIdx.x) * n;
+    float *orow = out + static_cast<size_t>(blockIdx.x) * n;
+    const int n4 = n >> 2;  // callers guarantee n % 4 == 0, n <= 8192, 16-byte aligned rows
+    float4 v[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 a = reinterpret_cast<const float4 *>(xr)[i], c = reinterpret_cast<const float4 *>(yr)[i];
+            v[j] = make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w);
+            reinterpret_cast<float4 *>(xr)[i] = v[j];
+        } else {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+    const float r = 1.0f / sqrtf(block_sum(ss, s_red) / static_cast<float>(n) + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 g = __ldg(reinterpret_cast<const float4 *>(w) + i);
+            reinterpret_cast<float4 *>(orow)[i] = make_float4(v[j].x * r * g.x, v[j].y * r * g.y, v[j].z * r * g.z, v[j].w * r * g.w);
+        }
+    }
+}
+
+// out = rms_norm(relu(g)^2 * u) (model.rs:363-364 in one pass).
+__global__ void __launch_bounds__(256) relu2_mul_rms_norm_kernel(const float *__restrict__ g, const float *__restrict__ u,
+                                                                const float *__restrict__ w, int n, float eps, float *__restrict__ out) {
+    __shared__ float s_red[8];
+    const float *gr = g + static_cast<size_t>(blockIdx.x) * n, *ur = u + static_cast<size_t>(blockIdx.x) * n;
+    float *orow = out + static_cast<size_t>(blockIdx.x) * n;
+    const int n4 = n >> 2;
+    float4 v[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 a = reinterpret_cast<const float4 *>(gr)[i], c = reinterpret_cast<const float4 *>(ur)[i];
+            const float r0 = fmaxf(a.x, 0.f), r1 = fmaxf(a.y, 0.f), r2 = fmaxf(a.z, 0.f), r3 = fmaxf(a.w, 0.f);
+            v[j] = make_float4(r0 * r0 * c.x, r1 * r1 * c.y, r2 * r2 * c.z, r3 * r3 * c.w);
+        } else {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+    const float r = 1.0f / sqrtf(block_sum(ss, s_red) / static_cast<float>(n) + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = threadIdx.x + j * 256;
+        if (i < n4) {
+            const float4 gw = __ldg(reinterpret_cast<const float4 *>(w) + i);
+            reinterpret_cast<float4 *>(orow)[i] = make_float4(v[j].x * r * gw.x, v[j].y * r * gw.y, v[j].z * r * gw.z, v[j].w * r * gw.w);
+        }
+    }
 }
 
 __global__ void relu2_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, size_t n, float *__restrict__ out) {
@@ -165,41 +290,59 @@ __global__ void add_inplace_kernel(float *__restrict__ x, const float *__restric
         x[i] += y[i];
 }
 
-// First index of the maximum (strict >, sample.rs:17-25): compare (value desc, index asc).
-__global__ void __launch_bounds__(1024) argmax_kernel(const float *__restrict__ logits, int n, int *__restrict__ out) {
-    __shared__ float s_v[32];
-    __shared__ int s_i[32];
-    const float *row = logits + static_cast<size_t>(blockIdx.x) * n;
+// First index of the maximum (strict >, sample.rs:17-25), two stages: kArgParts blocks per row
+// reduce their slice to (value, index), then one warp merges them. Order: value desc, index asc.
+constexpr int kArgParts = 32;
+constexpr size_t kSmallScratchRows = 256;
+static_assert(kSmallScratchRows * kArgParts * 8 <= kSmallScratchBytes, "context small scratch too small");
+__device__ __forceinline__ bool arg_better(float v, int i, float bv, int bi) { return v > bv || (v == bv && i < bi); }
+
+__global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restrict__ logits, int n, float *__restrict__ pv,
+                                                         int *__restrict__ pi) {
+    __shared__ float s_v[8];
+    __shared__ int s_i[8];
+    const float *row = logits + static_cast<size_t>(blockIdx.y) * n;
+    const int per = (n + kArgParts - 1) / kArgParts;
+    const int i0 = blockIdx.x * per, i1 = min(n, i0 + per);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {  // ascending i: strict > keeps the first maximum
+    for (int i = i0 + threadIdx.x; i < i1; i += 256) {  // ascending i: strict > keeps the first maximum
         const float v = row[i];
         if (v > bv) {
             bv = v;
             bi = i;
         }
     }
-    auto better = [](float v, int i, float bv2, int bi2) { return v > bv2 || (v == bv2 && i < bi2); };
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+        if (arg_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { s_v[warp] = bv; s_i[warp] = bi; }
     __syncthreads();
-    if (warp == 0) {
-        bv = lane < (blockDim.x >> 5) ? s_v[lane] : -INFINITY;
-        bi = lane < (blockDim.x >> 5) ? s_i[lane] : 0x7fffffff;
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
-        }
-        // the reference starts from index 0 and only moves on a strict >: a NaN in front, or a row
-        // with nothing above -inf, stays at 0
-        if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff || row[0] != row[0]) ? 0 : bi;
+    if (threadIdx.x == 0) {
+        for (int w2 = 1; w2 < 8; ++w2)
+            if (arg_better(s_v[w2], s_i[w2], bv, bi)) { bv = s_v[w2]; bi = s_i[w2]; }
+        pv[blockIdx.y * kArgParts + blockIdx.x] = bv;
+        pi[blockIdx.y * kArgParts + blockIdx.x] = bi;
     }
+}
+
+__global__ void __launch_bounds__(32) argmax_merge_kernel(const float *__restrict__ logits, int n, const float *__restrict__ pv,
+                                                         const int *__restrict__ pi, int *__restrict__ out) {
+    const int lane = threadIdx.x;
+    float bv = lane < kArgParts ? pv[blockIdx.x * kArgParts + lane] : -INFINITY;
+    int bi = lane < kArgParts ? pi[blockIdx.x * kArgParts + lane] : 0x7fffffff;
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (arg_better(ov, oi, bv, bi)) { bv = ov; bi = oi; }
+    }
+    // the reference starts from index 0 and only moves on a strict >: a NaN in front, or a row
+    // with nothing above -inf, stays at 0
+    const float first = logits[static_cast<size_t>(blockIdx.x) * n];
+    if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff || first != first) ? 0 : bi;
 }
 
 __global__ void advance_pos_kernel(int *pos) { *pos += 1; }
@@ -262,12 +405,13 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     if (head_dim != kHd) return fail(LBK_ERR_UNSUPPORTED, "attention kernel is built for head_dim 128, got %zu", head_dim);
     if (kv_heads == 0 || n_heads % kv_heads || n_heads / kv_heads > 8) return fail(LBK_ERR_UNSUPPORTED, "query group size must be 1..8");
     if (splits == 0) return fail(LBK_ERR_INVALID, "splits must be positive");
+    if (splits > 4096) return fail(LBK_ERR_UNSUPPORTED, "at most 4096 splits");
     dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
-    attn_partial_kernel<<<grid, 256, 0, st>>>(q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
+    attn_partial_kernel<<<grid, static_cast<unsigned>(32 * (n_heads / kv_heads)), 0, st>>>(q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
                                               scratch_dev);
     LBK_CUDA(cudaGetLastError());
-    attn_combine_kernel<<<static_cast<unsigned>(b * n_heads), kHd, 0, st>>>(scratch_dev, static_cast<int>(splits), out_dev);
+    attn_combine_kernel<<<static_cast<unsigned>(b * n_heads), kHd, (splits + 1) * sizeof(float), st>>>(scratch_dev, static_cast<int>(splits), out_dev);
     ctx->launches++;
     LBK_DEC_POST();
 }
@@ -288,12 +432,50 @@ int lbk_add_inplace(lbk_ctx *c, float *x_dev, const float *y_dev, size_t n, void
     LBK_DEC_POST();
 }
 
+static bool fused_norm_ok(const void *a, const void *b2, const void *w, const void *o, size_t n) {
+    return (n & 3) == 0 && n <= 8192 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b2) | reinterpret_cast<uintptr_t>(w) |
+                                           reinterpret_cast<uintptr_t>(o)) & 15) == 0;
+}
+
+int lbk_add_rms_norm(lbk_ctx *c, float *x_dev, const float *y_dev, const float *w_dev, size_t rows, size_t n, float eps, float *out_dev,
+                     void *stream) {
+    LBK_DEC_PRE("lbk_add_rms_norm");
+    if (rows == 0) return LBK_OK;
+    if (!x_dev || !y_dev || !w_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_add_rms_norm: null buffer or empty row");
+    if (!fused_norm_ok(x_dev, y_dev, w_dev, out_dev, n))
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_add_rms_norm needs 16-byte aligned rows of a multiple of 4, at most 8192, columns");
+    add_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(x_dev, y_dev, w_dev, static_cast<int>(n), eps, out_dev);
+    LBK_DEC_POST();
+}
+
+int lbk_relu2_mul_rms_norm(lbk_ctx *c, const float *g_dev, const float *u_dev, const float *w_dev, size_t rows, size_t n, float eps,
+                           float *out_dev, void *stream) {
+    LBK_DEC_PRE("lbk_relu2_mul_rms_norm");
+    if (rows == 0) return LBK_OK;
+    if (!g_dev || !u_dev || !w_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_relu2_mul_rms_norm: null buffer or empty row");
+    if (!fused_norm_ok(g_dev, u_dev, w_dev, out_dev, n))
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_relu2_mul_rms_norm needs 16-byte aligned rows of a multiple of 4, at most 8192, columns");
+    relu2_mul_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(g_dev, u_dev, w_dev, static_cast<int>(n), eps, out_dev);
+    LBK_DEC_POST();
+}
+
 int lbk_argmax(lbk_ctx *c, const float *logits_dev, size_t rows, size_t n, int32_t *out_dev, void *stream) {
     LBK_DEC_PRE("lbk_argmax");
     if (rows == 0) return LBK_OK;
     if (!logits_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_argmax: null buffer or empty row");
-    argmax_kernel<<<static_cast<unsigned>(rows), 1024, 0, st>>>(logits_dev, static_cast<int>(n), out_dev);
-    LBK_DEC_POST();
+    // per-row partial (value, index) pairs live in a small buffer the context owns from start-up
+    // (never reallocated, so captured graphs stay valid); larger batches go through in slices
+    float *pv = static_cast<float *>(ctx->small_scratch);
+    int *pi = reinterpret_cast<int *>(pv + kSmallScratchRows * kArgParts);
+    for (size_t r0 = 0; r0 < rows; r0 += kSmallScratchRows) {
+        const size_t nr = rows - r0 < kSmallScratchRows ? rows - r0 : kSmallScratchRows;
+        argmax_part_kernel<<<dim3(kArgParts, static_cast<unsigned>(nr)), 256, 0, st>>>(logits_dev + r0 * n, static_cast<int>(n), pv, pi);
+        LBK_CUDA(cudaGetLastError());
+        argmax_merge_kernel<<<static_cast<unsigned>(nr), 32, 0, st>>>(logits_dev + r0 * n, static_cast<int>(n), pv, pi, out_dev + r0);
+        LBK_CUDA(cudaGetLastError());
+        ctx->launches += 2;
+    }
+    return LBK_OK;
 }
 
 int lbk_advance_pos(lbk_ctx *c, int32_t *pos_dev, void *stream) {

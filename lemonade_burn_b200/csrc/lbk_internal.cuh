@@ -34,6 +34,8 @@ int fail(int status, const char *fmt, ...);
         if (s__ != LBK_OK) return s__; \
     } while (0)
 
+constexpr size_t kSmallScratchBytes = 64 * 1024;
+
 // ---- handles -------------------------------------------------------------------------
 struct Ctx {
     int device = 0;
@@ -45,6 +47,7 @@ struct Ctx {
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
     cudaStream_t own_stream = nullptr;  // used by the host-pointer entry points
+    void *small_scratch = nullptr;      // kSmallScratchBytes, allocated once at init (reductions)
 };
 
 struct Weight {

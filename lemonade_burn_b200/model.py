@@ -152,10 +152,12 @@ class BitNet:
             self._bufs[key] = torch.empty(shape, dtype=dtype, device=self.device)
         return self._bufs[key]
 
-    def forward(self, tokens: torch.Tensor, cache: KvCache, splits: int = 32) -> torch.Tensor:
+    def forward(self, tokens: torch.Tensor, cache: KvCache, splits: Optional[int] = None) -> torch.Tensor:
         """One new token per sequence at position cache.len (model.rs:305-374 with m = 1).
         tokens: int32 CUDA [b]. Returns logits f32 [b, vocab] and advances the cache."""
         cfg, lib, h = self.cfg, self.ctx._lib, self.ctx.handle
+        if splits is None:  # enough blocks in flight to cover HBM latency on long contexts
+            splits = max(1, min(128, cache.cap // 32))
         b = tokens.shape[0]
         if b != cache.b:
             raise ValueError("batch size differs from the cache's")
@@ -169,9 +171,11 @@ class BitNet:
         act = self._buf("act", (b, I))
         scratch = self._buf("attn_part", (b * nh * splits * (hd + 4),))
         chk = _lib.check
+        fused = H % 4 == 0 and H <= 8192 and I % 4 == 0 and I <= 8192
         chk(lib.lbk_embed_bf16(h, P(self.lm_head), P(tokens), b, H, P(x), st))
+        chk(lib.lbk_rms_norm(h, P(x), P(self.layers[0]["input_norm"]), b, H, eps, P(n), st))
         for li, l in enumerate(self.layers):
-            chk(lib.lbk_rms_norm(h, P(x), P(l["input_norm"]), b, H, eps, P(n), st))
+            # n holds rms_norm(x, input_norm) on entry
             q, k, v = ops.ternary_linear3(n, [l["q"], l["k"], l["v"]])
             chk(lib.lbk_rope_kv_append(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
                                        P(cache.k[li]), P(cache.v[li]), st))
@@ -179,14 +183,24 @@ class BitNet:
                                     P(scratch), P(attn), st))
             chk(lib.lbk_rms_norm(h, P(attn), P(l["attn_sub_norm"]), b, nh * hd, eps, P(attn), st))
             o = ops.ternary_linear(attn, l["o"])
-            chk(lib.lbk_add_inplace(h, P(x), P(o), b * H, st))
-            chk(lib.lbk_rms_norm(h, P(x), P(l["post_attn_norm"]), b, H, eps, P(n), st))
+            nxt = self.layers[li + 1]["input_norm"] if li + 1 < len(self.layers) else self.final_norm
+            if fused:
+                chk(lib.lbk_add_rms_norm(h, P(x), P(o), P(l["post_attn_norm"]), b, H, eps, P(n), st))
+            else:
+                chk(lib.lbk_add_inplace(h, P(x), P(o), b * H, st))
+                chk(lib.lbk_rms_norm(h, P(x), P(l["post_attn_norm"]), b, H, eps, P(n), st))
             g, u = ops.ternary_linear2(n, [l["gate"], l["up"]])
-            chk(lib.lbk_relu2_mul(h, P(g), P(u), b * I, P(act), st))
-            chk(lib.lbk_rms_norm(h, P(act), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+            if fused:
+                chk(lib.lbk_relu2_mul_rms_norm(h, P(g), P(u), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+            else:
+                chk(lib.lbk_relu2_mul(h, P(g), P(u), b * I, P(act), st))
+                chk(lib.lbk_rms_norm(h, P(act), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
             d = ops.ternary_linear(act, l["down"])
-            chk(lib.lbk_add_inplace(h, P(x), P(d), b * H, st))
-        chk(lib.lbk_rms_norm(h, P(x), P(self.final_norm), b, H, eps, P(n), st))
+            if fused:  # residual add + the next layer's input norm (or the final norm)
+                chk(lib.lbk_add_rms_norm(h, P(x), P(d), P(nxt), b, H, eps, P(n), st))
+            else:
+                chk(lib.lbk_add_inplace(h, P(x), P(d), b * H, st))
+                chk(lib.lbk_rms_norm(h, P(x), P(nxt), b, H, eps, P(n), st))
         logits = ops.bf16_linear(n, self.lm_head, self.ctx)
         chk(lib.lbk_advance_pos(h, P(cache.pos), st))
         return logits
@@ -199,10 +213,10 @@ class BitNet:
         return out
 
 
-def random_checkpoint(cfg: Config, seed: int = 0) -> Dict[str, torch.Tensor]:
+def random_checkpoint(cfg: Config, seed: int = 0, device="cpu") -> Dict[str, torch.Tensor]:
     """Random-init weights in checkpoint naming (there is no real checkpoint where this is built):
     valid ternary codes, scales near 1/mean|N(0,0.02)|, norm gains near 1, bf16 embedding N(0,0.02)."""
-    g = torch.Generator().manual_seed(seed)
+    g = torch.Generator(device=device).manual_seed(seed)
     H, I, hd = cfg.hidden_size, cfg.intermediate_size, cfg.head_dim()
     rows = {"self_attn.q_proj": (cfg.num_attention_heads * hd, H), "self_attn.k_proj": (cfg.num_key_value_heads * hd, H),
             "self_attn.v_proj": (cfg.num_key_value_heads * hd, H), "self_attn.o_proj": (H, cfg.num_attention_heads * hd),
@@ -211,13 +225,13 @@ def random_checkpoint(cfg: Config, seed: int = 0) -> Dict[str, torch.Tensor]:
     for i in range(cfg.num_hidden_layers):
         p = f"model.layers.{i}"
         for name, (r, c) in rows.items():
-            b = torch.randint(0, 256, (r, row_bytes(c)), dtype=torch.uint8, generator=g)
+            b = torch.randint(0, 256, (r, row_bytes(c)), dtype=torch.uint8, generator=g, device=device)
             t[f"{p}.{name}.qweight"] = b & ~((b >> 1) & b & 0x55)   # code 3 -> 1: valid ternary
-            t[f"{p}.{name}.wscale"] = torch.tensor([60.0 + 5.0 * torch.rand(1, generator=g).item()], dtype=torch.float32)
+            t[f"{p}.{name}.wscale"] = torch.tensor([60.0 + 5.0 * torch.rand(1, generator=g, device=device).item()], dtype=torch.float32)
         for nm, sz in (("input_layernorm", H), ("post_attention_layernorm", H), ("self_attn.attn_sub_norm", H), ("mlp.ffn_sub_norm", I)):
-            t[f"{p}.{nm}.weight"] = (1.0 + 0.05 * torch.randn(sz, generator=g)).float()
-    t["model.norm.weight"] = (1.0 + 0.05 * torch.randn(H, generator=g)).float()
-    t["model.embed_tokens.weight"] = (0.02 * torch.randn(cfg.vocab_size, H, generator=g)).to(torch.bfloat16)
+            t[f"{p}.{nm}.weight"] = (1.0 + 0.05 * torch.randn(sz, generator=g, device=device)).float()
+    t["model.norm.weight"] = (1.0 + 0.05 * torch.randn(H, generator=g, device=device)).float()
+    t["model.embed_tokens.weight"] = (0.02 * torch.randn(cfg.vocab_size, H, generator=g, device=device)).to(torch.bfloat16)
     return t
 
 

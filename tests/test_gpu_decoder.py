@@ -103,3 +103,60 @@ def test_argmax_first_max(ctx):
     x[0, 777] = 5.0; x[0, 90000] = 5.0          # first of two equal maxima
     x[2, 128255] = 0.5
     assert net.argmax(x).cpu().tolist() == [777, 0, 128255]
+
+
+@pytest.mark.parametrize("total,splits", [(1, 1), (37, 4), (1000, 128), (4097, 128), (300, 512)])
+def test_attention_long_context_against_numpy(ctx, total, splits):
+    """lbk_attn_decode at contexts the tiny decoders above never reach, slices shorter and longer
+    than one pass of the kernel's position loop and empty trailing slices, against softmax(qK/sqrt(d))V
+    in float64 (model.rs:343-353). Tolerance 1e-5 absolute on outputs of magnitude <= 1."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    b, nh, kvh, hd, cap = 2, 8, 2, 128, max(total, 8)
+    g = torch.Generator().manual_seed(total)
+    q = torch.randn(b, nh, hd, generator=g)
+    k = torch.randn(b, kvh, cap, hd, generator=g).bfloat16()
+    v = torch.rand(b, kvh, cap, hd, generator=g).bfloat16()
+    pos = torch.tensor([total - 1], dtype=torch.int32)
+    qd, kd, vd, pd = q.cuda(), k.cuda(), v.cuda(), pos.cuda()
+    scratch = torch.empty(b * nh * splits * (hd + 4), device="cuda")
+    out = torch.empty(b, nh * hd, device="cuda")
+    rc = lib.lbk_attn_decode(ctx.handle, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), pd.data_ptr(), b, nh, kvh, hd, cap, splits,
+                             scratch.data_ptr(), out.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    _lib.check(rc)
+    got = out.cpu().numpy().reshape(b, nh, hd)
+    kf, vf, qf = k.double().numpy()[:, :, :total], v.double().numpy()[:, :, :total], q.double().numpy()
+    for h in range(nh):
+        s = np.einsum("bd,bpd->bp", qf[:, h], kf[:, h // (nh // kvh)]) / np.sqrt(hd)
+        w = np.exp(s - s.max(axis=1, keepdims=True))
+        w /= w.sum(axis=1, keepdims=True)
+        ref = np.einsum("bp,bpd->bd", w, vf[:, h // (nh // kvh)])
+        assert np.abs(got[:, h] - ref).max() < 1e-5
+    ctx.check_device_error()
+
+
+def test_fused_norms_match_their_parts(ctx):
+    """lbk_add_rms_norm and lbk_relu2_mul_rms_norm give the bits of the unfused op pairs."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    for rows, n in [(1, 2560), (3, 6912), (2, 8192), (5, 512)]:
+        g = torch.Generator().manual_seed(n)
+        x = torch.randn(rows, n, generator=g).cuda(); y = torch.randn(rows, n, generator=g).cuda()
+        w = torch.rand(n, generator=g).cuda() + 0.5
+        x1, x2 = x.clone(), x.clone()
+        o1, o2 = torch.empty_like(x), torch.empty_like(x)
+        assert lib.lbk_add_inplace(ctx.handle, x1.data_ptr(), y.data_ptr(), rows * n, st) == 0
+        assert lib.lbk_rms_norm(ctx.handle, x1.data_ptr(), w.data_ptr(), rows, n, 1e-5, o1.data_ptr(), st) == 0
+        assert lib.lbk_add_rms_norm(ctx.handle, x2.data_ptr(), y.data_ptr(), w.data_ptr(), rows, n, 1e-5, o2.data_ptr(), st) == 0
+        assert torch.equal(x1, x2) and torch.equal(o1, o2)
+        a1, a2 = torch.empty_like(x), torch.empty_like(x)
+        assert lib.lbk_relu2_mul(ctx.handle, x.data_ptr(), y.data_ptr(), rows * n, a1.data_ptr(), st) == 0
+        assert lib.lbk_rms_norm(ctx.handle, a1.data_ptr(), w.data_ptr(), rows, n, 1e-5, a1.data_ptr(), st) == 0
+        assert lib.lbk_relu2_mul_rms_norm(ctx.handle, x.data_ptr(), y.data_ptr(), w.data_ptr(), rows, n, 1e-5, a2.data_ptr(), st) == 0
+        assert torch.equal(a1, a2)
+    bad = torch.empty(1, 8196, device="cuda")
+    assert lib.lbk_add_rms_norm(ctx.handle, bad.data_ptr(), bad.data_ptr(), bad.data_ptr(), 1, 8196, 1e-5, bad.data_ptr(), st) != 0
+    ctx.check_device_error()
