@@ -3,12 +3,15 @@
 //
 // Stands in for the reference's per-token loop of 120 parallel regions
 // (crates/lb-ternary/benches/kbench.rs:148-194; crates/lb-model/src/model.rs:331-366 issues the
-// same four fused ops per layer). The concatenated weight stream of all groups is cut into
-// equal-byte runs of 16-row tiles, one run per warp (148 CTAs x 8 warps). A warp walks its run
-// with its own TMA ring; when the run crosses into another group the warp quantises that
-// group's activation row itself (absmax, scale, round-half-even, sum) into its private slice of
-// shared memory. No warp ever waits for another one, so groups must not depend on each other's
-// outputs. Arithmetic per output element is exactly that of the single-group kernel.
+// same four fused ops per layer). The concatenated weight stream of all groups, counted in
+// 2 KB stages ([16 rows][128 B] boxes), is cut into runs of EQUAL stage count, one run per warp
+// (148 CTAs x 16 warps), each walked with the warp's own TMA ring. A cut may fall inside a
+// 16-row tile: the two warps that share such a tile each leave their int32 partial sums in a
+// small workspace and bump a counter; whichever arrives second adds the two and writes the
+// outputs. Nobody waits for anybody. The activation rows of the groups a CTA touches are
+// quantised once per CTA into shared memory. Groups must not depend on each other's outputs.
+// Arithmetic per output element is exactly that of the single-group kernel (integer partial
+// sums add exactly).
 #include <vector>
 
 #include "lbk_gemv_core.cuh"
@@ -17,6 +20,7 @@ namespace lbk {
 
 using namespace gemv;
 
+constexpr int kHandoffInts = 64;  // [0,16) first half's partials, [16,32) second half's, [32] arrivals
 constexpr int kMaxSlots = 4;  // groups one CTA's warps may touch (activation slots in shared memory)
 
 struct alignas(64) SweepMat {
@@ -56,7 +60,8 @@ struct alignas(16) CtaRec {
 struct SweepParams {
     const SweepMat *mats;
     const SweepGroup *groups;
-    const int4 *warp_run;    // [n_warps] {first tile, end tile, group of the first tile, unused}
+    const int4 *warp_run;    // [n_warps] {first tile, stages in the run, group of the first tile, first chunk}
+    int *handoff;            // [n_warps + 1][kHandoffInts]: partial sums of tiles shared by two warps
     const CtaRec *cta;       // [grid]
     int xq_bytes;            // bytes per activation slot
     int *err_word;
@@ -90,7 +95,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_g0));
 #endif
     const int4 run = __ldg(p.warp_run + gw);
-    const int t_begin = run.x, t_end = run.y;
+    const int t_begin = run.x, n_stages = run.y, c_begin = run.w;
     const int4 chead = __ldg(reinterpret_cast<const int4 *>(p.cta + blockIdx.x));
     const int slot_g0 = chead.x, n_slots = chead.y;
 
@@ -127,30 +132,44 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     int *s_sum = reinterpret_cast<int *>(s_misc + 144);                 // [kMaxSlots]
     uint8_t *s_xq = s_misc + 256;                                       // [kMaxSlots][xq_bytes]
 
-    // ---- issue cursor (meaningful on lane 0 only) -----------------------------------------
+    // ---- issue cursor (meaningful on lane 0 only): kept incremental so that the common case is
+    // the two PTX instructions plus a counter; matrices and groups change on a slow path.
     int ig = run.z;
-    SweepGroup igrp = p.groups[t_begin < t_end ? ig : 0];
-    int itile = t_begin, ichunk = 0, imat = 0;
-    auto issue = [&](int s) {
-        while (itile >= igrp.tile0 + igrp.tiles) {
-            igrp = p.groups[++ig];
-            imat = 0;
-        }
-        const int local = itile - igrp.tile0;
+    SweepGroup igrp = p.groups[n_stages > 0 ? ig : 0];
+    int ichunk = c_begin, ichunks = igrp.chunks, imat = 0, irow = 0, imat_left = 0, issued = 0;
+    const CUtensorMap *itmap = nullptr;
+    {
+        const int local = t_begin - igrp.tile0;
         while (imat < igrp.n_mat - 1 && local >= tile_end_of(igrp, imat)) ++imat;
-        const int tile_in_mat = local - (imat ? tile_end_of(igrp, imat - 1) : 0);
+        const int mat_base = imat ? tile_end_of(igrp, imat - 1) : 0;
+        irow = (local - mat_base) * kTileRows;
+        imat_left = tile_end_of(igrp, imat) - local;
+        itmap = &p.mats[igrp.mat0 + imat].tmap;
+    }
+    auto issue = [&](int s) {
+        while (imat_left == 0) {  // the previous tile was the last one of its matrix
+            if (++imat == igrp.n_mat) {
+                igrp = p.groups[++ig];
+                imat = 0;
+                ichunks = igrp.chunks;
+            }
+            imat_left = tile_end_of(igrp, imat) - (imat ? tile_end_of(igrp, imat - 1) : 0);
+            irow = 0;
+            itmap = &p.mats[igrp.mat0 + imat].tmap;
+        }
         ptx::mbar_arrive_expect_tx(full0 + s * 8, kStageBytes);
-        ptx::tma_load_2d(stage0 + s * kStageBytes, &p.mats[igrp.mat0 + imat].tmap, full0 + s * 8,
-                         ichunk * kChunkBytes, tile_in_mat * kTileRows);
-        if (++ichunk == igrp.chunks) {
+        ptx::tma_load_2d(stage0 + s * kStageBytes, itmap, full0 + s * 8, ichunk * kChunkBytes, irow);
+        ++issued;
+        if (++ichunk == ichunks) {
             ichunk = 0;
-            ++itile;
+            irow += kTileRows;
+            --imat_left;
         }
     };
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
-        for (int s = 0; s < kStages && itile < t_end; ++s) issue(s);
+        for (int s = 0; s < kStages && issued < n_stages; ++s) issue(s);
     }
 #ifdef LBK_TIMELINE
     tl_setup = clock64() - tl_start;
@@ -189,7 +208,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
 #ifdef LBK_TIMELINE
     tl_quant = clock64() - tl_start - tl_setup;
 #endif
-    if (t_begin >= t_end) return;
+    if (n_stages <= 0) return;
 
     // ---- consume cursor ----------------------------------------------------------------
     const LaneOffsets off = lane_offsets(lane);
@@ -209,11 +228,67 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     int32_t *iout = nullptr;
     float a_scale = 0.0f, inv = 0.0f;
     int a_sum = 0;
-    int chunk = 0, s = 0;
+    int chunk = c_begin, s = 0, tile = t_begin;
     uint32_t phase = 0;
     bool ok = true;
 
-    for (int tile = t_begin; tile < t_end;) {
+    // dot = acc - sum(q), y = (float)dot * (1/(s_a*s_w)) for the 16 rows of `tile`; v_lo / v_hi are
+    // the complete sums of rows g and g + 8 (meaningful on lanes with t == 0).
+    auto write_tile = [&](int v_lo, int v_hi) {
+        const int local = tile - cgrp.tile0;
+        if (cmat < 0 || local >= mat_tile_end) {
+            if (cmat < 0) cmat = 0;
+            while (cmat < cgrp.n_mat - 1 && local >= tile_end_of(cgrp, cmat)) ++cmat;
+            mat_tile_end = tile_end_of(cgrp, cmat);
+            mat_tile_base = cmat ? tile_end_of(cgrp, cmat - 1) : 0;
+            const SweepMat *mt = p.mats + cgrp.mat0 + cmat;
+            rows = __ldg(&mt->rows);
+            out = mt->out;
+            iout = mt->iout;
+            inv = __fdiv_rn(1.0f, __fmul_rn(a_scale, __ldg(&mt->wscale)));  // gemm.rs:141
+        }
+        const int row0 = (local - mat_tile_base) * kTileRows;
+        if (t == 0) {  // token 0 lives in column 0 of the tile
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int row = row0 + g + h * 8;
+                if (row < rows) {
+                    const int d = (h ? v_hi : v_lo) - a_sum;
+                    if (iout) iout[row] = d;
+                    if (out) out[row] = __fmul_rn(__int2float_rn(d), inv);
+                }
+            }
+        }
+    };
+    // This warp holds only part of the tile's columns: leave the partial sums for the warp that
+    // holds the rest, or, when that warp has been here already, add its sums and finish the tile.
+    // `second` tells which half of the record is ours. Both warps write before they count, so the
+    // later one always finds the other's numbers; the record is left zeroed for the next launch.
+    auto share_tile = [&](int boundary, bool second, int v_lo, int v_hi) {
+        int *rec = p.handoff + static_cast<size_t>(boundary) * kHandoffInts;
+        const int mine = second ? 16 : 0, theirs = second ? 0 : 16;
+        if (t == 0) {
+            __stcg(rec + mine + g, v_lo);
+            __stcg(rec + mine + 8 + g, v_hi);
+            __threadfence();
+        }
+        __syncwarp();
+        int arrived = 0;
+        if (lane == 0) arrived = atomicAdd(rec + 32, 1);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        if (arrived == 0) return;
+        __threadfence();
+        int o_lo = 0, o_hi = 0;
+        if (t == 0) {
+            o_lo = __ldcg(rec + theirs + g);
+            o_hi = __ldcg(rec + theirs + 8 + g);
+        }
+        __syncwarp();
+        if (lane == 0) __stcg(rec + 32, 0);
+        write_tile(v_lo + o_lo, v_hi + o_hi);
+    };
+
+    for (int n = 0; n < n_stages; ++n) {
         if (tile >= cgrp.tile0 + cgrp.tiles) {
             // ---- the run enters another group: switch to its activation slot
             do {
@@ -238,39 +313,24 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
 #endif
         consume_stage<1>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
         __syncwarp();  // every lane has read the stage before it is refilled
-        if (lane == 0 && itile < t_end) issue(s);
+        if (lane == 0 && issued < n_stages) issue(s);
         if (++s == kStages) {
             s = 0;
             phase ^= 1;
         }
         if (++chunk == cgrp.chunks) {
-            // ---- tile epilogue: dot = acc - sum(q), y = (float)dot * (1/(s_a*s_w)) -------------
-            const int local = tile - cgrp.tile0;
-            if (cmat < 0 || local >= mat_tile_end) {
-                if (cmat < 0) cmat = 0;
-                while (cmat < cgrp.n_mat - 1 && local >= tile_end_of(cgrp, cmat)) ++cmat;
-                mat_tile_end = tile_end_of(cgrp, cmat);
-                mat_tile_base = cmat ? tile_end_of(cgrp, cmat - 1) : 0;
-                const SweepMat *mt = p.mats + cgrp.mat0 + cmat;
-                rows = __ldg(&mt->rows);
-                out = mt->out;
-                iout = mt->iout;
-                inv = __fdiv_rn(1.0f, __fmul_rn(a_scale, __ldg(&mt->wscale)));  // gemm.rs:141
-            }
-            const int row0 = (local - mat_tile_base) * kTileRows;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int v = take_acc<1>(acc, 0, j);
-                const int row = row0 + g + ((j & 2) ? 8 : 0);
-                if (t == 0 && (j & 1) == 0 && row < rows) {  // token 0 lives in column 0 of the tile
-                    const int d = v - a_sum;
-                    if (iout) iout[row] = d;
-                    if (out) out[row] = __fmul_rn(__int2float_rn(d), inv);
-                }
-            }
+            const int v_lo = take_acc<1>(acc, 0, 0), v_hi = take_acc<1>(acc, 0, 2);
+            (void)take_acc<1>(acc, 0, 1);
+            (void)take_acc<1>(acc, 0, 3);
+            if (tile == t_begin && c_begin > 0) share_tile(gw, true, v_lo, v_hi);
+            else write_tile(v_lo, v_hi);
             chunk = 0;
             ++tile;
         }
+    }
+    if (ok && chunk != 0) {  // the run ends inside a tile: the next warp holds the remaining columns
+        const int v_lo = take_acc<1>(acc, 0, 0), v_hi = take_acc<1>(acc, 0, 2);
+        share_tile(gw + 1, false, v_lo, v_hi);
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 2);
 #ifdef LBK_TIMELINE
@@ -293,6 +353,7 @@ struct SweepTables {
     SweepGroup *groups = nullptr;
     int4 *warp_run = nullptr;
     CtaRec *cta = nullptr;
+    int *handoff = nullptr;
     int xq_bytes = 0;
     int grid = 0;
     size_t smem = 0;
@@ -304,6 +365,7 @@ void sweep_free(SweepTables *t) {
     cudaFree(t->groups);
     cudaFree(t->warp_run);
     cudaFree(t->cta);
+    cudaFree(t->handoff);
     delete t;
 }
 
@@ -361,37 +423,55 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
         *out = tb;
         return LBK_OK;
     }
-    // equal-cost runs: warp w starts at the first tile whose cumulative cost reaches w/nw of the total
+    // Runs of equal stage count: warp w owns stages [total*w/nw, total*(w+1)/nw) of the stream. When
+    // the share is short against a tile (tiny plans) cuts are moved to tile boundaries instead, so
+    // that no tile is ever shared by more than two warps.
     const int grid = ctx->sm_count;
     const int nw = grid * kWarps;
-    long long total = 0;
-    for (int c : tile_chunks) total += c;
-    std::vector<int> wt(nw + 1), wg(nw);
+    std::vector<long long> tile_start(tiles_total + 1);
+    tile_start[0] = 0;
+    for (int i = 0; i < tiles_total; ++i) tile_start[i + 1] = tile_start[i] + tile_chunks[i];
+    const long long total = tile_start[tiles_total];
+    const bool split = total / nw >= 2LL * max_chunks;
+    std::vector<long long> cut(nw + 1);
+    std::vector<int> cut_tile(nw + 1);
     {
-        long long cum = 0;
         int tile = 0;
-        for (int w = 0; w < nw; ++w) {
-            const long long target = total * w / nw;
-            while (tile < tiles_total && cum < target) cum += tile_chunks[tile++];
-            wt[w] = tile;
-        }
-        wt[nw] = tiles_total;
-        size_t gi = 0;
-        for (int w = 0; w < nw; ++w) {
-            while (gi + 1 < grps.size() && wt[w] >= grps[gi].tile0 + grps[gi].tiles) ++gi;
-            wg[w] = static_cast<int>(gi);
+        for (int w = 0; w <= nw; ++w) {
+            long long c = total * w / nw;
+            while (tile < tiles_total && tile_start[tile + 1] <= c) ++tile;
+            if (!split && tile < tiles_total && c > tile_start[tile]) c = tile_start[++tile];  // round up to a tile boundary
+            if (c < tile_start[tile]) c = tile_start[tile];  // an earlier cut was rounded past this one
+            cut[w] = c;
+            cut_tile[w] = tile;  // the tile that holds stage c (tiles_total at the very end)
         }
     }
+    auto group_of_tile = [&](int tile) {
+        size_t lo = 0, hi = grps.size() - 1;
+        while (lo < hi) {
+            const size_t mid = (lo + hi) / 2;
+            if (tile >= grps[mid].tile0 + grps[mid].tiles) lo = mid + 1;
+            else hi = mid;
+        }
+        return static_cast<int>(lo);
+    };
     std::vector<int4> runs(nw);
     std::vector<CtaRec> ctas(grid);
-    for (int w = 0; w < nw; ++w) runs[w] = make_int4(wt[w], wt[w + 1], wg[w], 0);
+    for (int w = 0; w < nw; ++w) {
+        const int n = static_cast<int>(cut[w + 1] - cut[w]);
+        const int t0 = cut_tile[w] < tiles_total ? cut_tile[w] : tiles_total - 1;
+        runs[w] = make_int4(t0, n, group_of_tile(t0), n > 0 ? static_cast<int>(cut[w] - tile_start[t0]) : 0);
+    }
     for (int c = 0; c < grid; ++c) {
-        // groups between the CTA's first tile and its last one
-        const int first_tile = wt[c * kWarps], end_tile = wt[(c + 1) * kWarps];
-        int g0 = wg[c * kWarps], g1 = g0;
-        if (end_tile > first_tile)
-            while (g1 + 1 < static_cast<int>(grps.size()) && end_tile - 1 >= grps[g1].tile0 + grps[g1].tiles) ++g1;
-        const int n = end_tile > first_tile ? g1 - g0 + 1 : 0;
+        // groups between the CTA's first stage and its last one
+        const long long s0 = cut[c * kWarps], s1 = cut[(c + 1) * kWarps];
+        int n = 0, g0 = 0;
+        if (s1 > s0) {
+            g0 = group_of_tile(cut_tile[c * kWarps]);
+            int last_tile = cut_tile[(c + 1) * kWarps];
+            if (last_tile >= tiles_total || tile_start[last_tile] == s1) --last_tile;  // s1 - 1 lies in the tile before
+            n = group_of_tile(last_tile) - g0 + 1;
+        }
         if (n > kMaxSlots) {
             delete tb;
             return fail(LBK_ERR_UNSUPPORTED, "sweep: a CTA's run spans %d groups (limit %d); groups are too small", n, kMaxSlots);
@@ -411,6 +491,9 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
     if (e == cudaSuccess) e = cudaMalloc(&tb->groups, grps.size() * sizeof(SweepGroup));
     if (e == cudaSuccess) e = cudaMalloc(&tb->warp_run, runs.size() * sizeof(int4));
     if (e == cudaSuccess) e = cudaMalloc(&tb->cta, ctas.size() * sizeof(CtaRec));
+    const size_t handoff_bytes = static_cast<size_t>(nw + 1) * kHandoffInts * sizeof(int);
+    if (e == cudaSuccess) e = cudaMalloc(&tb->handoff, handoff_bytes);
+    if (e == cudaSuccess) e = cudaMemset(tb->handoff, 0, handoff_bytes);
     if (e == cudaSuccess) e = cudaMemcpy(tb->mats, mats.data(), mats.size() * sizeof(SweepMat), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(tb->groups, grps.data(), grps.size() * sizeof(SweepGroup), cudaMemcpyHostToDevice);
     if (e == cudaSuccess) e = cudaMemcpy(tb->warp_run, runs.data(), runs.size() * sizeof(int4), cudaMemcpyHostToDevice);
@@ -435,6 +518,7 @@ int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream) {
     p.groups = tb->groups;
     p.warp_run = tb->warp_run;
     p.cta = tb->cta;
+    p.handoff = tb->handoff;
     p.xq_bytes = tb->xq_bytes;
     p.err_word = ctx->err_word;
 #ifdef LBK_TIMELINE
