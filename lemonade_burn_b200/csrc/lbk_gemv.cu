@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     for (int mt = 0; mt < MT; ++mt) {
         int tok = mt * 8 + g;
         tok = tok < m ? tok : m - 1;  // lanes beyond the last token re-read it; never stored
-        xrow[mt] = s_xq + static_cast<size_t>(tok) * p.xq_stride + t * 8;
+        xrow[mt] = s_xq + static_cast<size_t>(tok) * p.xq_stride + t * 16;
     }
     const uint8_t *stage_ptr = sm + L.stages + warp * (kStages * kStageBytes);
 
@@ -337,7 +337,7 @@ extern "C" void lbk_debug_set_timeline(long long *buf) { g_timeline = buf; }
 
 int gemv_xq_stride(size_t kp) {
     const size_t chunks = (kp / 4 + kChunkBytes - 1) / kChunkBytes;
-    return static_cast<int>(chunks * kChunkCols + 32);  // +32: token rows land on distinct banks
+    return static_cast<int>(chunks * kChunkCols + 64);  // +64: the 128-bit loads of two token rows land on distinct banks
 }
 
 bool gemv_fits(const Ctx *ctx, size_t kp, size_t m) {

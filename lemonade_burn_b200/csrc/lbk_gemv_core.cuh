@@ -33,11 +33,12 @@ constexpr uint32_t kWaitLimit = 1u << 22;             // polls before a wait giv
 constexpr int kMaxM = LBK_GEMV_MAX_M;
 
 // Position of natural column n inside a token row of the shared activation buffer:
-// [chunk][k-group][c][t][8] with n = (chunk*4 + t)*128 + kgroup*32 + c*8 + e. For every MMA
-// the eight bytes a lane needs sit next to those of its three neighbours.
+// [chunk][k-group][c/2][t][c%2][8] with n = (chunk*4 + t)*128 + kgroup*32 + c*8 + e. The sixteen
+// bytes a lane needs for two consecutive MMAs are one 128-bit load, next to those of its three
+// neighbours.
 __device__ __forceinline__ uint32_t xq_pos(uint32_t n) {
     uint32_t chunk = n >> 9, t = (n >> 7) & 3, kk = (n >> 5) & 3, c = (n >> 3) & 3, e = n & 7;
-    return ((((chunk * 4 + kk) * 4 + c) * 4 + t) << 3) + e;
+    return ((((chunk * 4 + kk) * 2 + (c >> 1)) * 4 + t) << 4) + ((c & 1) << 3) + e;
 }
 
 __device__ __forceinline__ float warp_max(float v) {
@@ -179,8 +180,9 @@ __device__ __forceinline__ LaneOffsets lane_offsets(int lane) {
 }
 
 // One stage: 16 rows x 512 columns against MT groups of 8 token rows. xrow[mt] points at
-// this lane's 8-byte slot (t*8) of the token row it feeds; xoff = chunk * 512.
-template <int MT>
+// this lane's 16-byte slot (t*16) of the token row it feeds; xoff = chunk * 512.
+// FIRST: the accumulators are overwritten by this stage (first stage of a tile) instead of added to.
+template <int MT, bool FIRST = false>
 __device__ __forceinline__ void consume_stage(const uint8_t *st, LaneOffsets off,
                                               const uint8_t *const (&xrow)[MT], uint32_t xoff,
                                               int (&acc)[MT][2][4][4]) {
@@ -193,16 +195,23 @@ __device__ __forceinline__ void consume_stage(const uint8_t *st, LaneOffsets off
     const uint32_t vlo[4] = {V0.x, V0.z, V1.x, V1.z};  // row g+8
     const uint32_t vhi[4] = {V0.y, V0.w, V1.y, V1.w};
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
+    for (int cp = 0; cp < 2; ++cp) {
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
             const uint32_t mask = 0x03030303u << (2 * kk);
-            const uint32_t a0 = wlo[c] & mask, a1 = vlo[c] & mask;
-            const uint32_t a2 = whi[c] & mask, a3 = vhi[c] & mask;
+            uint4 b[MT];
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt) {
-                const uint2 b = *reinterpret_cast<const uint2 *>(xrow[mt] + xoff + ((kk * 4 + c) << 5));
-                ptx::mma_u8s8(acc[mt][c & 1][kk], a0, a1, a2, a3, b.x, b.y);
+            for (int mt = 0; mt < MT; ++mt) b[mt] = *reinterpret_cast<const uint4 *>(xrow[mt] + xoff + ((kk * 2 + cp) << 6));
+#pragma unroll
+            for (int ci = 0; ci < 2; ++ci) {
+                const int c = cp * 2 + ci;
+                const uint32_t a0 = wlo[c] & mask, a1 = vlo[c] & mask;
+                const uint32_t a2 = whi[c] & mask, a3 = vhi[c] & mask;
+#pragma unroll
+                for (int mt = 0; mt < MT; ++mt) {
+                    if (FIRST && cp == 0) ptx::mma_u8s8_init(acc[mt][ci][kk], a0, a1, a2, a3, ci ? b[mt].z : b[mt].x, ci ? b[mt].w : b[mt].y);
+                    else ptx::mma_u8s8(acc[mt][ci][kk], a0, a1, a2, a3, ci ? b[mt].z : b[mt].x, ci ? b[mt].w : b[mt].y);
+                }
             }
         }
     }
@@ -219,6 +228,15 @@ __device__ __forceinline__ int take_acc(int (&acc)[MT][2][4][4], int mt, int j) 
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) acc[mt][h][kk][j] = 0;
     }
+    return v;
+}
+
+// take_acc without the zeroing, for accumulators that the next tile's first stage overwrites
+template <int MT>
+__device__ __forceinline__ int read_acc(const int (&acc)[MT][2][4][4], int mt, int j) {
+    int v = 0;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) v += acc[mt][h][0][j] + (acc[mt][h][1][j] >> 2) + (acc[mt][h][2][j] >> 4) + (acc[mt][h][3][j] >> 6);
     return v;
 }
 

@@ -1,6 +1,7 @@
 // Plans: a recorded decode-like sequence of fused ternary-linear groups replayed as one
 // unit. Stands in for the reference's per-token loop of 120 parallel regions
 // (crates/lb-ternary/benches/kbench.rs:148-194, crates/lb-model/src/model.rs:331-366).
+#include <cstdlib>
 #include <new>
 #include <vector>
 
@@ -89,6 +90,8 @@ int lbk_plan_finalize(lbk_plan *pl) {
         cudaError_t e = cudaMalloc(&p->x_arena, (p->x_elems + 4) * sizeof(float));
         if (e == cudaSuccess) e = cudaMalloc(&p->y_arena, (p->y_elems + 4) * sizeof(float));
         if (e != cudaSuccess) return fail(LBK_ERR_NOMEM, "plan arenas: %s", cudaGetErrorString(e));
+        LBK_CUDA(cudaMemset(p->x_arena, 0, (p->x_elems + 4) * sizeof(float)));
+        LBK_CUDA(cudaMemset(p->y_arena, 0, (p->y_elems + 4) * sizeof(float)));
         size_t xo = 0, yo = 0;
         for (int gi : p->arena_group) {
             GroupArgs &g = p->groups[gi];

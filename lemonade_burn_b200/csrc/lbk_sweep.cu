@@ -20,6 +20,10 @@ namespace lbk {
 
 using namespace gemv;
 
+#ifndef LBK_SWEEP_STAGES
+#define LBK_SWEEP_STAGES 3
+#endif
+constexpr int kSweepStages = LBK_SWEEP_STAGES;  // TMA ring depth per warp in this kernel
 constexpr int kHandoffInts = 64;  // [0,16) first half's partials, [16,32) second half's, [32] arrivals
 constexpr int kMaxSlots = 4;  // groups one CTA's warps may touch (activation slots in shared memory)
 
@@ -121,11 +125,11 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         if (q_cached) load_cached(q_x, q_k, q_idx, q_nthr, rc);
     }
 
-    constexpr uint32_t kRing = kStages * kStageBytes;
+    constexpr uint32_t kRing = kSweepStages * kStageBytes;
     const uint32_t stage0 = base + warp * kRing;
     const uint8_t *stage_ptr = sm + warp * kRing;
-    const uint32_t full0 = base + kWarps * kRing + warp * (kStages * 8);
-    uint8_t *s_misc = sm + kWarps * kRing + kWarps * kStages * 8;       // reductions, scales, sums
+    const uint32_t full0 = base + kWarps * kRing + warp * (kSweepStages * 8);
+    uint8_t *s_misc = sm + kWarps * kRing + kWarps * kSweepStages * 8;       // reductions, scales, sums
     float *s_part = reinterpret_cast<float *>(s_misc);                  // [kMaxSlots][4]
     int *s_parti = reinterpret_cast<int *>(s_misc + 64);                // [kMaxSlots][4]
     float *s_scale = reinterpret_cast<float *>(s_misc + 128);           // [kMaxSlots]
@@ -167,9 +171,9 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         }
     };
     if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
+        for (int s = 0; s < kSweepStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
-        for (int s = 0; s < kStages && issued < n_stages; ++s) issue(s);
+        for (int s = 0; s < kSweepStages && issued < n_stages; ++s) issue(s);
     }
 #ifdef LBK_TIMELINE
     tl_setup = clock64() - tl_start;
@@ -212,14 +216,8 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
 
     // ---- consume cursor ----------------------------------------------------------------
     const LaneOffsets off = lane_offsets(lane);
-    const uint8_t *xrow[1] = {s_xq + t * 8};
-    int acc[1][2][4][4];
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) acc[0][h][kk][j] = 0;
+    const uint8_t *xrow[1] = {s_xq + t * 16};
+    int acc[1][2][4][4];  // written by the first stage of every tile
 
     int cg = run.z - 1;  // forces the first group set-up
     SweepGroup cgrp{};
@@ -228,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     int32_t *iout = nullptr;
     float a_scale = 0.0f, inv = 0.0f;
     int a_sum = 0;
-    int chunk = c_begin, s = 0, tile = t_begin;
+    int s = 0, tile = t_begin;
     uint32_t phase = 0;
     bool ok = true;
 
@@ -288,49 +286,48 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         write_tile(v_lo + o_lo, v_hi + o_hi);
     };
 
-    for (int n = 0; n < n_stages; ++n) {
+    // One pass of the outer loop per tile (or per part of a tile at either end of the run).
+    for (int remaining = n_stages, c0 = c_begin; remaining > 0 && ok; c0 = 0, ++tile) {
         if (tile >= cgrp.tile0 + cgrp.tiles) {
             // ---- the run enters another group: switch to its activation slot
             do {
                 cgrp = p.groups[++cg];
             } while (tile >= cgrp.tile0 + cgrp.tiles);
             const int slot = cg - slot_g0;
-            xrow[0] = s_xq + static_cast<size_t>(slot) * p.xq_bytes + t * 8;
+            xrow[0] = s_xq + static_cast<size_t>(slot) * p.xq_bytes + t * 16;
             a_scale = s_scale[slot];
             a_sum = s_sum[slot];
             cmat = -1;
         }
+        const int c1 = min(cgrp.chunks, c0 + remaining);
+        remaining -= c1 - c0;
+        for (int chunk = c0; chunk < c1; ++chunk) {
 #ifdef LBK_TIMELINE
-        const long long tw0 = clock64();
+            const long long tw0 = clock64();
 #endif
-        if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
-            ok = false;
-            break;
-        }
+            if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
+                ok = false;
+                break;
+            }
 #ifdef LBK_TIMELINE
-        tl_wait += clock64() - tw0;
-        ++tl_items;
+            tl_wait += clock64() - tw0;
+            ++tl_items;
 #endif
-        consume_stage<1>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
-        __syncwarp();  // every lane has read the stage before it is refilled
-        if (lane == 0 && issued < n_stages) issue(s);
-        if (++s == kStages) {
-            s = 0;
-            phase ^= 1;
+            if (chunk == c0) consume_stage<1, true>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
+            else consume_stage<1, false>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
+            __syncwarp();  // every lane has read the stage before it is refilled
+            if (lane == 0 && issued < n_stages) issue(s);
+            if (++s == kSweepStages) {
+                s = 0;
+                phase ^= 1;
+            }
         }
-        if (++chunk == cgrp.chunks) {
-            const int v_lo = take_acc<1>(acc, 0, 0), v_hi = take_acc<1>(acc, 0, 2);
-            (void)take_acc<1>(acc, 0, 1);
-            (void)take_acc<1>(acc, 0, 3);
-            if (tile == t_begin && c_begin > 0) share_tile(gw, true, v_lo, v_hi);
-            else write_tile(v_lo, v_hi);
-            chunk = 0;
-            ++tile;
-        }
-    }
-    if (ok && chunk != 0) {  // the run ends inside a tile: the next warp holds the remaining columns
-        const int v_lo = take_acc<1>(acc, 0, 0), v_hi = take_acc<1>(acc, 0, 2);
-        share_tile(gw + 1, false, v_lo, v_hi);
+        if (!ok) break;
+        // columns 1..7 of the MMA tile repeat token 0 and are never read
+        const int v_lo = read_acc<1>(acc, 0, 0), v_hi = read_acc<1>(acc, 0, 2);
+        if (c0 > 0) share_tile(gw, true, v_lo, v_hi);             // the previous warp holds the first columns
+        else if (c1 < cgrp.chunks) share_tile(gw + 1, false, v_lo, v_hi);  // the next warp holds the rest
+        else write_tile(v_lo, v_hi);
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 2);
 #ifdef LBK_TIMELINE
@@ -412,7 +409,7 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
     }
     SweepTables *tb = new SweepTables();
     tb->xq_bytes = max_chunks * kChunkCols;
-    tb->smem = static_cast<size_t>(kWarps) * (kStages * kStageBytes + kStages * 8) + 256 +
+    tb->smem = static_cast<size_t>(kWarps) * (kSweepStages * kStageBytes + kSweepStages * 8) + 256 +
                static_cast<size_t>(kMaxSlots) * tb->xq_bytes + 1024;
     if (tb->smem > ctx->smem_optin) {
         delete tb;
