@@ -110,12 +110,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 
     // issue cursor (lane 0 only): next item to fetch
     int issue_tile = tile_begin, issue_chunk = 0, issue_mat = 0;
+    const uint64_t stream_once = ptx::policy_evict_first();  // weights are read once per launch
     auto issue = [&](int s) {  // s: the ring stage the next item goes into
         while (issue_mat < p.n_mat - 1 && issue_tile >= p.tile_end[issue_mat]) ++issue_mat;
         const int tile_in_mat = issue_tile - (issue_mat ? p.tile_end[issue_mat - 1] : 0);
         ptx::mbar_arrive_expect_tx(full0 + s * 8, kStageBytes);
-        ptx::tma_load_2d(stage0 + s * kStageBytes, &p.tmap[issue_mat], full0 + s * 8,
-                         issue_chunk * kChunkBytes, tile_in_mat * kTileRows);
+        ptx::tma_load_2d_hint(stage0 + s * kStageBytes, &p.tmap[issue_mat], full0 + s * 8,
+                         issue_chunk * kChunkBytes, tile_in_mat * kTileRows, stream_once);
         if (++issue_chunk == chunks) {
             issue_chunk = 0;
             ++issue_tile;

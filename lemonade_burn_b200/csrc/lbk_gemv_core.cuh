@@ -118,6 +118,21 @@ __device__ __forceinline__ void load_cached(const float *xr, int k, int idx, int
         rc.v[j] = i < n4 ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
     }
 }
+// load_cached with an L2 policy: rows that are read again by every launch ask to stay resident
+__device__ __forceinline__ void load_cached_hint(const float *xr, int k, int idx, int nthr, RowCache &rc, uint64_t policy) {
+    const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+    const int n4 = k >> 2;
+#pragma unroll
+    for (int j = 0; j < kCacheV; ++j) {
+        const int i = idx + j * nthr;
+        if (i < n4) {
+            const uint4 u = ptx::ldg_hint(x4 + i, policy);
+            rc.v[j] = make_float4(__uint_as_float(u.x), __uint_as_float(u.y), __uint_as_float(u.z), __uint_as_float(u.w));
+        } else {
+            rc.v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+}
 __device__ __forceinline__ float max_cached(const RowCache &rc) {
     float am = 0.0f;
 #pragma unroll

@@ -12,6 +12,8 @@
 // quantised once per CTA into shared memory. Groups must not depend on each other's outputs.
 // Arithmetic per output element is exactly that of the single-group kernel (integer partial
 // sums add exactly).
+#include <cstdio>
+#include <cstdlib>
 #include <vector>
 
 #include "lbk_gemv_core.cuh"
@@ -36,7 +38,7 @@ struct alignas(64) SweepMat {
     int pad_[10];
 };
 
-struct SweepGroup {
+struct alignas(16) SweepGroup {
     const float *x;
     int k;
     int chunks;
@@ -81,6 +83,17 @@ __device__ __forceinline__ int tile_end_of(const SweepGroup &g, int i) {
     return i == 0 ? g.tile_end[0] : (i == 1 ? g.tile_end[1] : (i == 2 ? g.tile_end[2] : g.tile_end[3]));
 }
 
+static_assert(sizeof(SweepGroup) == 48, "SweepGroup is read as three 16-byte words");
+__device__ __forceinline__ SweepGroup load_group(const SweepGroup *g, uint64_t policy) {
+    union {
+        SweepGroup grp;
+        uint4 w[3];
+    } u;
+#pragma unroll
+    for (int i = 0; i < 3; ++i) u.w[i] = ptx::ldg_hint(reinterpret_cast<const uint4 *>(g) + i, policy);
+    return u.grp;
+}
+
 // Every warp walks its own run of tiles; its lane 0 keeps the warp's TMA ring full. The
 // activation rows of the (at most kMaxSlots) groups the CTA touches are quantised once, by the
 // whole CTA, while the first loads are in flight.
@@ -98,9 +111,14 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     unsigned long long tl_g0;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_g0));
 #endif
-    const int4 run = __ldg(p.warp_run + gw);
+    // The tables and activation rows are read again by the next launch while half a gigabyte of
+    // weights streams through L2 in between: ask L2 to keep the former and drop the latter first.
+    const uint64_t keep = ptx::policy_evict_last(), stream_once = ptx::policy_evict_first();
+    const uint4 run_u = ptx::ldg_hint(p.warp_run + gw, keep);
+    const int4 run = make_int4(run_u.x, run_u.y, run_u.z, run_u.w);
     const int t_begin = run.x, n_stages = run.y, c_begin = run.w;
-    const int4 chead = __ldg(reinterpret_cast<const int4 *>(p.cta + blockIdx.x));
+    const uint4 chead_u = ptx::ldg_hint(p.cta + blockIdx.x, keep);
+    const int4 chead = make_int4(chead_u.x, chead_u.y, chead_u.z, chead_u.w);
     const int slot_g0 = chead.x, n_slots = chead.y;
 
     // Two chains of dependent loads start here and are interleaved on purpose: (a) this warp
@@ -115,14 +133,15 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     bool q_vec = false, q_cached = false;
     RowCache rc;
     if (q_have) {
-        const int4 rec = __ldg(reinterpret_cast<const int4 *>(&p.cta[blockIdx.x].slot[q_slot]));
+        const uint4 rec_u = ptx::ldg_hint(&p.cta[blockIdx.x].slot[q_slot], keep);
+        const int4 rec = make_int4(rec_u.x, rec_u.y, rec_u.z, rec_u.w);
         q_x = reinterpret_cast<const float *>((static_cast<unsigned long long>(static_cast<unsigned>(rec.y)) << 32) |
                                               static_cast<unsigned>(rec.x));
         q_k = rec.z;
         q_kfill = rec.w * kChunkCols;
         q_vec = (q_k & 3) == 0 && (reinterpret_cast<uintptr_t>(q_x) & 15) == 0;
         q_cached = q_vec && ((q_k >> 2) + q_nthr - 1) / q_nthr <= kCacheV;
-        if (q_cached) load_cached(q_x, q_k, q_idx, q_nthr, rc);
+        if (q_cached) load_cached_hint(q_x, q_k, q_idx, q_nthr, rc, keep);
     }
 
     constexpr uint32_t kRing = kSweepStages * kStageBytes;
@@ -139,7 +158,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     // ---- issue cursor (meaningful on lane 0 only): kept incremental so that the common case is
     // the two PTX instructions plus a counter; matrices and groups change on a slow path.
     int ig = run.z;
-    SweepGroup igrp = p.groups[n_stages > 0 ? ig : 0];
+    SweepGroup igrp = load_group(p.groups + (n_stages > 0 ? ig : 0), keep);
     int ichunk = c_begin, ichunks = igrp.chunks, imat = 0, irow = 0, imat_left = 0, issued = 0;
     const CUtensorMap *itmap = nullptr;
     {
@@ -153,7 +172,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     auto issue = [&](int s) {
         while (imat_left == 0) {  // the previous tile was the last one of its matrix
             if (++imat == igrp.n_mat) {
-                igrp = p.groups[++ig];
+                igrp = load_group(p.groups + ++ig, keep);
                 imat = 0;
                 ichunks = igrp.chunks;
             }
@@ -162,7 +181,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
             itmap = &p.mats[igrp.mat0 + imat].tmap;
         }
         ptx::mbar_arrive_expect_tx(full0 + s * 8, kStageBytes);
-        ptx::tma_load_2d(stage0 + s * kStageBytes, itmap, full0 + s * 8, ichunk * kChunkBytes, irow);
+        ptx::tma_load_2d_hint(stage0 + s * kStageBytes, itmap, full0 + s * 8, ichunk * kChunkBytes, irow, stream_once);
         ++issued;
         if (++ichunk == ichunks) {
             ichunk = 0;
@@ -291,7 +310,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         if (tile >= cgrp.tile0 + cgrp.tiles) {
             // ---- the run enters another group: switch to its activation slot
             do {
-                cgrp = p.groups[++cg];
+                cgrp = load_group(p.groups + ++cg, keep);
             } while (tile >= cgrp.tile0 + cgrp.tiles);
             const int slot = cg - slot_g0;
             xrow[0] = s_xq + static_cast<size_t>(slot) * p.xq_bytes + t * 16;
@@ -337,6 +356,9 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         long long *d = p.timeline + static_cast<long long>(gw) * 16;
         d[0] = tl_setup; d[1] = tl_quant; d[2] = tl_wait; d[3] = tl_items; d[4] = static_cast<long long>(tl_g0);
         d[5] = static_cast<long long>(g1); d[6] = clock64() - tl_start; d[7] = tl_nq;
+        unsigned smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        d[8] = smid;
     }
 #endif
 }
@@ -434,8 +456,30 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
     std::vector<int> cut_tile(nw + 1);
     {
         int tile = 0;
+#ifdef LBK_TIMELINE
+        std::vector<double> prefix(grid + 1, 0.0);  // experiment: per-CTA shares from a file of doubles
+        {
+            std::vector<double> wts(grid, 1.0);
+            if (const char *path = getenv("LBK_SWEEP_WEIGHTS")) {
+                if (FILE *f = fopen(path, "rb")) {
+                    if (fread(wts.data(), sizeof(double), grid, f) != static_cast<size_t>(grid)) wts.assign(grid, 1.0);
+                    fclose(f);
+                }
+            }
+            for (int c = 0; c < grid; ++c) prefix[c + 1] = prefix[c] + (split ? wts[c] : 1.0);
+        }
+#endif
         for (int w = 0; w <= nw; ++w) {
+#ifdef LBK_TIMELINE
+            long long c = total;
+            if (w < nw) {
+                const int cta = w / kWarps, sub = w % kWarps;
+                c = static_cast<long long>(static_cast<double>(total) * (prefix[cta] + (prefix[cta + 1] - prefix[cta]) * sub / kWarps) / prefix[grid]);
+                if (w > 0 && c < cut[w - 1]) c = cut[w - 1];
+            }
+#else
             long long c = total * w / nw;
+#endif
             while (tile < tiles_total && tile_start[tile + 1] <= c) ++tile;
             if (!split && tile < tiles_total && c > tile_start[tile]) c = tile_start[++tile];  // round up to a tile boundary
             if (c < tile_start[tile]) c = tile_start[tile];  // an earlier cut was rounded past this one
