@@ -9,8 +9,9 @@
 //
 //   TMA warp       int8 activations [NT tok][128 B] (SWIZZLE_128B, the K-major B operand) and
 //                  packed weights [128 rows][32 B] into a deep shared-memory ring
-//   4 expander     thread r owns weight row r = TMEM lane r: 32 packed bytes -> 32 words of u8
-//   warps          codes, word c = columns 4c..4c+3 = (packed word >> 2k) & 0x03030303
+//   2 x 4 expander thread r owns weight row r = TMEM lane r: 32 packed bytes -> 32 words of u8
+//   warps          codes, word c = columns 4c..4c+3 = (packed word >> 2k) & 0x03030303; the two
+//                  sets of four warps take alternate K blocks (one set alone was the bottleneck)
 //                  (pack.rs:10-13: no shuffles), written straight to TMEM with tcgen05.st.
 //                  The expanded tile never touches shared memory: expanding into shared memory
 //                  cost 112 KB of shared-memory traffic per 512 cycles of MMA and starved the
@@ -35,38 +36,44 @@ constexpr int kBK = 128;           // columns per stage = one packed block
 constexpr int kPackBlocks = 4;      // K-blocks per packed-weight stage: [128 rows][128 B] boxes
 constexpr int kPackBytes = kBMW * kBlockBytes * kPackBlocks;  // 16 KB, SWIZZLE_128B
 constexpr int kAStages = 4;        // expanded weight tiles in TMEM (32 columns each)
-constexpr int kEpiWarps = 4, kExpWarps = 4;
-constexpr int kExpWarp0 = 4, kTmaWarp = 8, kMmaWarp = 9;   // warps 0-3 epilogue, 4-7 expanders
-constexpr int kThreads = 10 * 32;
+constexpr int kEpiWarps = 4, kExpWarps = 4, kExpSets = 2;
+// warps 0-3 epilogue, 4-7 and 8-11 expanders (warp % 4 = the TMEM lane quadrant a warp may touch)
+constexpr int kExpWarp0 = 4, kTmaWarp = 12, kMmaWarp = 13;
+constexpr int kThreads = 14 * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr uint32_t kTmemCols = 512;
 
-template <int NT>  // token rows per tile (MMA N): 192 or 64
+template <int NT>  // capacity in token rows per tile (MMA N): 192 or 64; a launch uses nt <= NT
 struct Cfg {
     static constexpr int kActBytes = NT * kBK;                  // multiple of 1024 for NT = 192, 64
-    static constexpr int kLoadStages = NT == 192 ? 6 : 12;      // activation ring
+    static constexpr int kLoadStages = NT == 192 ? 6 : 12;      // activation ring, in K blocks
+    static constexpr int kPairStages = kLoadStages / 2;         // ... in pairs of K blocks (the unit of hand-off)
     static constexpr int kPackStages = 3;                       // packed-weight ring
     static constexpr uint32_t kPack0 = kLoadStages * kActBytes;
     static constexpr uint32_t kAcc0 = 0, kAcc1 = NT, kA0 = 2 * NT;  // TMEM column map
     static_assert(2 * NT + kAStages * 32 <= 512, "TMEM budget");
-    // instruction descriptor: D s32, A u8 (codes, TMEM), B s8 (activations), K-major, M=128, N=NT
-    static constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((NT >> 3) << 17) | ((kBMW >> 4) << 24);
+    // instruction descriptor without N: D s32, A u8 (codes, TMEM), B s8 (activations), K-major, M=128
+    static constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((kBMW >> 4) << 24);
     static constexpr uint32_t kBars = kPack0 + kPackStages * kPackBytes;
     static constexpr uint32_t kMisc = kBars + 48 * 8;
     static constexpr uint32_t kTok = kMisc + 64;              // per-token sum(q) and 1/(s_a*s_w): 2 x [2][NT]
     static constexpr uint32_t kTotal = kTok + 2 * 2 * NT * 4;
-    // One "full" barrier per K-block slot collects both operands: the activation bytes (TMA
-    // transaction count) and the four expander warps' arrivals for the TMEM weight tile, so the
-    // MMA thread waits once per block. One "consumed" barrier per slot (a single tcgen05.commit
-    // per block) releases both the activation stage and, AS blocks later, the TMEM weight slot.
-    static constexpr int kBarFull = 0;                        // [LS]
-    static constexpr int kBarConsumed = kLoadStages;          // [LS]
+    // Hand-off is by PAIRS of K blocks. Every barrier wait in the MMA thread drains the tensor
+    // pipe for a few hundred cycles whatever the MMA shape (measured: 4 MMAs + one wait per loop
+    // turn run at 590 cycles a turn, 8 MMAs + one wait at 900), so a wait has to buy as many MMAs
+    // as shared memory allows. One "full" barrier per pair collects both operands: the
+    // activation bytes of one or two blocks (TMA transaction count) and the arrivals of all eight
+    // expander warps (set 0 expands the pair's first block, set 1 its second; a warp with no
+    // block at the odd end of K arrives all the same). One "consumed" barrier per pair (a single
+    // tcgen05.commit) releases the activation stages and, two pairs later, the TMEM weight slots.
+    static constexpr int kBarFull = 0;                        // [pair stages]
+    static constexpr int kBarConsumed = kLoadStages;          // [pair stages]
     static constexpr int kBarFullPack = 2 * kLoadStages;      // [PS] packed weights landed
     static constexpr int kBarEmptyPack = kBarFullPack + kPackStages;  // [PS] expanders are done with them
     static constexpr int kBarAccFull = kBarEmptyPack + kPackStages;   // [2]
     static constexpr int kBarAccEmpty = kBarAccFull + 2;      // [2]
     static_assert(kBarAccEmpty + 2 <= 48, "barrier area too small");
-    static_assert(kAStages < kLoadStages, "a consumed-barrier phase must still be observable AS blocks later");
+    static_assert(kAStages / 2 < kPairStages, "a consumed-barrier phase must still be observable two pairs later");
 };
 
 struct GemmParams {
@@ -78,11 +85,13 @@ struct GemmParams {
     int rows[LBK_MAX_GROUP];
     int tile_end[LBK_MAX_GROUP];        // running tile count up to and including matrix i
     int n_mat, m, m_tiles, k_blocks, total_tiles;
+    int nt;                             // token rows per tile in this launch (multiple of 16, <= capacity)
     const float *qscale;
     const int32_t *qsum;
     int *err_word;
 #ifdef LBK_TIMELINE
     long long *timeline;  // [grid][16]: cycles each role spent waiting, debugging only
+    long long *trace;     // CTA 0: [8][512] clock per K block and event, debugging only
 #endif
 };
 
@@ -90,6 +99,11 @@ struct GemmParams {
 #define TL_WAIT(slot, expr) ([&]() { const long long t0__ = clock64(); const bool r__ = (expr); tl[slot] += clock64() - t0__; return r__; }())
 #else
 #define TL_WAIT(slot, expr) (expr)
+#endif
+#ifdef LBK_TIMELINE
+#define TRACE(ev, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 512) p.trace[(ev) * 512 + (idx)] = clock64(); } while (0)
+#else
+#define TRACE(ev, idx) do { } while (0)
 #endif
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------
@@ -121,14 +135,28 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// A operand from TMEM, B from shared memory
-__device__ __forceinline__ void umma_i8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+// A operand from TMEM (u8 codes), B from shared memory (s8 activations).
+// The four K = 32 steps of one 128-column block in one go: A advances 8 TMEM columns and B 32
+// bytes (2 descriptor units) per step; only the first step may start a fresh accumulator.
+__device__ __forceinline__ void umma_i8_ts_block(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
     asm volatile(
         "{\n"
-        ".reg .pred p;\n"
+        ".reg .pred p, q;\n"
+        ".reg .b64 b1, b2, b3;\n"
+        ".reg .b32 a1, a2, a3;\n"
         "setp.ne.b32 p, %4, 0;\n"
+        "setp.eq.b32 q, 0, 0;\n"
+        "add.u64 b1, %2, 2;\n"
+        "add.u64 b2, %2, 4;\n"
+        "add.u64 b3, %2, 6;\n"
+        "add.u32 a1, %1, 8;\n"
+        "add.u32 a2, %1, 16;\n"
+        "add.u32 a3, %1, 24;\n"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [a1], b1, %3, q;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [a2], b2, %3, q;\n"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], [a3], b3, %3, q;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -168,7 +196,8 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
     using C = Cfg<NT>;
-    constexpr int LS = C::kLoadStages, AS = kAStages, PS = C::kPackStages;
+    constexpr int PG = C::kPairStages, PS = C::kPackStages;
+    static_assert(kAStages == 4 && kExpSets == 2 && kPackBlocks == 4, "the pair hand-off assumes these");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -180,13 +209,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     auto bar = [&](int idx) { return bar0 + idx * 8; };
 
     if (tid == 0) {
-        for (int i = 0; i < LS; ++i) {
-            ptx::mbar_init(bar(C::kBarFull + i), 1 + kExpWarps);
+        for (int i = 0; i < PG; ++i) {
+            ptx::mbar_init(bar(C::kBarFull + i), 1 + kExpWarps * kExpSets);
             ptx::mbar_init(bar(C::kBarConsumed + i), 1);
         }
         for (int i = 0; i < PS; ++i) {
             ptx::mbar_init(bar(C::kBarFullPack + i), 1);
-            ptx::mbar_init(bar(C::kBarEmptyPack + i), kExpWarps);
+            ptx::mbar_init(bar(C::kBarEmptyPack + i), kExpWarps * kExpSets);
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(bar(C::kBarAccFull + a), 1);
@@ -223,11 +252,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            int it = 0, pit = 0;  // activation items, packed-weight items
+            int pr = 0, pit = 0;  // pairs of activation blocks, packed-weight stages
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
                 int mat, m_tile, n_tile;
                 decode_tile(tile, mat, m_tile, n_tile);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                for (int kb = 0; kb < k_blocks; kb += 2, ++pr) {
                     if ((kb % kPackBlocks) == 0) {
                         const int ps = pit % PS, pround = pit / PS;
                         if (pround > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort))) {
@@ -239,63 +268,86 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                                          kb * kBlockBytes, n_tile * kBMW);
                         ++pit;
                     }
-                    const int s = it % LS, round = it / LS;
+                    const int s = pr % PG, round = pr / PG;
                     if (round > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort))) {
                         ok = false;
                         break;
                     }
-                    ptx::mbar_arrive_expect_tx(bar(C::kBarFull + s), C::kActBytes);
-                    ptx::tma_load_2d(base + s * C::kActBytes, &p.act, bar(C::kBarFull + s), kb * kBK, m_tile * NT);
+                    const int nblk = k_blocks - kb < 2 ? 1 : 2;
+                    ptx::mbar_arrive_expect_tx(bar(C::kBarFull + s), static_cast<uint32_t>(nblk * p.nt) * kBK);
+                    for (int b = 0; b < nblk; ++b)
+                        ptx::tma_load_2d(base + (s * 2 + b) * C::kActBytes, &p.act, bar(C::kBarFull + s), (kb + b) * kBK, m_tile * p.nt);
                 }
             }
         }
-    } else if (warp >= kExpWarp0 && warp < kExpWarp0 + kExpWarps) {
+    } else if (warp >= kExpWarp0 && warp < kExpWarp0 + kExpWarps * kExpSets) {
         // ================= expanders: packed 2-bit -> u8 codes in TMEM =================
-        const int r = (warp - kExpWarp0) * 32 + lane;  // weight row of the tile = TMEM lane
-        const uint32_t lane_field = static_cast<uint32_t>((warp - kExpWarp0) * 32) << 16;
-        int it = 0, pit = -1;
+        const int quad = (warp - kExpWarp0) % kExpWarps, set = (warp - kExpWarp0) / kExpWarps;
+        const int r = quad * 32 + lane;  // weight row of the tile = TMEM lane
+        const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
+        // Ring positions are counters (no divisions in the loop): pair `pr` uses barrier slot `sp`
+        // and the TMEM slots of parity pr & 1; (lg, lg_phase) follow pair pr - 2, whose MMAs were the
+        // last readers of those TMEM slots; (ps, pphase) follow the packed-weight stage.
+        int pr = 0, sp = 0, lg = PG - 2, ps = -1;
+        uint32_t lg_phase = 1, pphase = 1;
         for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                const int as = it % AS, sub = kb % kPackBlocks;
-                if (sub == 0) {
-                    ++pit;
-                    if (!TL_WAIT(1, wait_bar(bar(C::kBarFullPack + pit % PS), (pit / PS) & 1, s_abort))) {
+            for (int kb = 0; kb < k_blocks; kb += 2, ++pr) {
+                const int sub = (kb & 2) + set;  // this warp's block inside the packed stage
+                if ((kb & 2) == 0) {
+                    if (++ps == PS) ps = 0;
+                    if (ps == 0) pphase ^= 1u;
+                    if (!TL_WAIT(1, wait_bar(bar(C::kBarFullPack + ps), pphase, s_abort))) {
                         ok = false;
                         break;
                     }
                 }
-                // TMEM slot `as` was last read by block it - AS
-                if (it >= AS && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + (it - AS) % LS), ((it - AS) / LS) & 1, s_abort))) {
-                    ok = false;
-                    break;
+                const bool have = kb + set < k_blocks;
+                const bool last_of_stage = (kb & 2) != 0 || kb + 2 >= k_blocks;
+                if (have) {
+                    // the TMEM slots of this parity were last read by pair pr - 2
+                    if (pr >= 2 && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort))) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    // row r of the [128][128 B] swizzled stage; this block's 32 bytes are units 2*sub, 2*sub+1
+                    const uint8_t *pk = sm + C::kPack0 + ps * kPackBytes + r * 128;
+                    const int x = r & 7;
+                    const uint4 w0 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub) ^ x) << 4));      // packed bytes j = 0..15
+                    const uint4 w1 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub + 1) ^ x) << 4));  // packed bytes j = 16..31
+                    const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    uint32_t v[32];  // word 8k + i = columns k*32 + 4i .. 4i+3
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[8 * k + i] = (w[i] >> (2 * k)) & 0x03030303u;
+                    tmem_st32(tmem_base + lane_field + C::kA0 + ((pr & 1) * 2 + set) * 32, v);
                 }
-                tc_fence_after();
-                // row r of the [128][128 B] swizzled stage; this block's 32 bytes are units 2*sub, 2*sub+1
-                const uint8_t *pk = sm + C::kPack0 + (pit % PS) * kPackBytes + r * 128;
-                const int x = r & 7;
-                const uint4 w0 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub) ^ x) << 4));      // packed bytes j = 0..15
-                const uint4 w1 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub + 1) ^ x) << 4));  // packed bytes j = 16..31
-                const uint32_t w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                uint32_t v[32];  // word 8k + i = columns k*32 + 4i .. 4i+3
-#pragma unroll
-                for (int k = 0; k < 4; ++k)
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[8 * k + i] = (w[i] >> (2 * k)) & 0x03030303u;
-                tmem_st32(tmem_base + lane_field + C::kA0 + as * 32, v);
-                if (sub == kPackBlocks - 1 || kb == k_blocks - 1) {  // last read of this packed stage
+                if (last_of_stage) {  // this warp's last read of the packed stage is behind it
                     __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive(bar(C::kBarEmptyPack + pit % PS));
+                    if (lane == 0) ptx::mbar_arrive(bar(C::kBarEmptyPack + ps));
                 }
-                tmem_st_wait();
-                tc_fence_before();
+                if (have) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                }
                 __syncwarp();
-                if (lane == 0) ptx::mbar_arrive(bar(C::kBarFull + it % LS));
+                if (lane == 0) ptx::mbar_arrive(bar(C::kBarFull + sp));
+                if (++sp == PG) sp = 0;
+                if (++lg == PG) {
+                    lg = 0;
+                    lg_phase ^= 1u;
+                }
             }
         }
     } else if (warp == kMmaWarp) {
         // ================= MMA issuer (one thread) =================
         if (lane == 0) {
-            int it = 0, tcount = 0;
+            // Ring positions are kept as counters: this thread's instruction stream is the critical
+            // path of the whole CTA (one thread issues every MMA), so no divisions by the ring size here.
+            int tcount = 0, sp = 0;
+            uint32_t full_phase = 0, pa = 0;
+            const uint64_t bdesc0 = smem_desc_sw128(base);  // activation block stage 0; stage s adds s * kActBytes / 16
             for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
                 const int a = tcount & 1, around = tcount >> 1;
                 if (around > 0 && !TL_WAIT(3, wait_bar(bar(C::kBarAccEmpty + a), (around - 1) & 1, s_abort))) {
@@ -304,19 +356,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (a ? C::kAcc1 : C::kAcc0);
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int ls = it % LS, as = it % AS;
-                    if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + ls), (it / LS) & 1, s_abort))) {
+                // N of this tile: the launch's token tile, less for the last tile of a ragged batch
+                int mat, m_tile, n_tile;
+                decode_tile(tile, mat, m_tile, n_tile);
+                const int left = p.m - m_tile * p.nt;
+                const int n_mma = left < p.nt ? (left + 15) & ~15 : p.nt;
+                const uint32_t idesc = C::kIdesc | (static_cast<uint32_t>(n_mma >> 3) << 17);
+                for (int kb = 0; kb < k_blocks; kb += 2) {
+                    if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + sp), full_phase, s_abort))) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t b_addr = base + ls * C::kActBytes;
-                    const uint32_t a_tmem = tmem_base + C::kA0 + as * 32;
-#pragma unroll
-                    for (int ks = 0; ks < kBK / 32; ++ks)  // K = 32 int8 = 8 TMEM columns of A, 32 bytes of B
-                        umma_i8_ts(d_tmem, a_tmem + ks * 8, smem_desc_sw128(b_addr + ks * 32), C::kIdesc, (kb | ks) ? 1u : 0u);
-                    umma_commit(bar(C::kBarConsumed + ls));  // both operands' slots are reusable once these MMAs retire
+                    const uint32_t a_tmem = tmem_base + C::kA0 + pa * 64;
+                    const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(sp * 2 * (C::kActBytes >> 4));
+                    umma_i8_ts_block(d_tmem, a_tmem, bdesc, idesc, kb ? 1u : 0u);
+                    if (kb + 1 < k_blocks) umma_i8_ts_block(d_tmem, a_tmem + 32, bdesc + (C::kActBytes >> 4), idesc, 1u);
+                    umma_commit(bar(C::kBarConsumed + sp));  // both operands' slots are reusable once these MMAs retire
+                    if (++sp == PG) {
+                        sp = 0;
+                        full_phase ^= 1u;
+                    }
+                    pa ^= 1u;
                 }
                 if (!ok) break;
                 umma_commit(bar(C::kBarAccFull + a));  // accumulator complete
@@ -333,14 +394,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             decode_tile(tile, mat, m_tile, n_tile);
             const int rows = p.rows[mat];
             const int row = n_tile * kBMW + warp * 32 + lane;
-            const int tok0 = m_tile * NT;
+            const int nt = p.nt;
+            const int tok0 = m_tile * nt;
             float *out = p.out[mat];
             int32_t *iout = p.iout[mat];
             // per-token terms of this tile (each warp fills its own copy: no cross-warp barrier)
             int *qs = s_qs + a * NT;  // reuse by accumulator parity is safe: see acc_empty below
             float *inv = s_inv + a * NT;
             if (warp == 0) {
-                for (int i = lane; i < NT; i += 32) {
+                for (int i = lane; i < ((nt + 31) & ~31); i += 32) {
                     const int tk = tok0 + i;
                     qs[i] = tk < p.m ? p.qsum[tk] : 0;
                     inv[i] = (tk < p.m && p.qscale) ? __fdiv_rn(1.0f, __fmul_rn(p.qscale[tk], p.wscale[mat])) : 0.0f;  // gemm.rs:158
@@ -355,9 +417,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 break;
             }
             tc_fence_after();
-            const int ntok = p.m - tok0 < NT ? p.m - tok0 : NT;
+            const int ntok = p.m - tok0 < nt ? p.m - tok0 : nt;
 #pragma unroll 1
-            for (int c = 0; c < NT / 32; ++c) {
+            for (int c = 0; c * 32 < ntok; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + (a ? C::kAcc1 : C::kAcc0) + c * 32, v);
                 // per-token terms into registers first: the stores below may alias the shared
@@ -441,9 +503,34 @@ int gemm_init(Ctx *ctx) {
 }
 
 #ifdef LBK_TIMELINE
-static long long *g_gemm_timeline = nullptr;
+static long long *g_gemm_timeline = nullptr, *g_gemm_trace = nullptr;
 extern "C" void lbk_debug_set_gemm_timeline(long long *buf) { g_gemm_timeline = buf; }
+extern "C" void lbk_debug_set_gemm_trace(long long *buf) { g_gemm_trace = buf; }
+
 #endif
+
+// Token rows per tile for a launch: the multiple of 16 (at most 192) whose tile count fills whole
+// rounds of the grid best. Per K block a tile costs the larger of the tensor-pipe time
+// (proportional to nt, about 400 cycles at nt = 192) and the issue thread's turn-around (about
+// 470 cycles whatever nt is: measured), plus the epilogue's share that the next tile cannot hide.
+static int choose_nt(size_t m, int row_tiles, int k_blocks, int sms) {
+    if (m <= 64) return static_cast<int>((m + 15) & ~static_cast<size_t>(15));
+    int best_nt = 192;
+    double best = 1e30;
+    for (int tiles_m = static_cast<int>((m + 191) / 192); tiles_m <= static_cast<int>((m + 63) / 64); ++tiles_m) {
+        const int nt = static_cast<int>(((m + tiles_m - 1) / tiles_m + 15) & ~static_cast<size_t>(15));
+        if (nt > 192 || nt < 64) continue;
+        const long long tiles = static_cast<long long>(row_tiles) * ((m + nt - 1) / nt);
+        const long long rounds = (tiles + sms - 1) / sms;
+        const double block = nt * (400.0 / 192.0) > 470.0 ? nt * (400.0 / 192.0) : 470.0;
+        const double cost = static_cast<double>(rounds) * (k_blocks * block + 12.0 * nt);
+        if (cost < best) {
+            best = cost;
+            best_nt = nt;
+        }
+    }
+    return best_nt;
+}
 
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     if (!g.q || !g.qsum) return fail(LBK_ERR_INVALID, "gemm: quantised activations are required");
@@ -451,8 +538,11 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     if (g.m == 0) return LBK_OK;
     GemmParams p{};
     const size_t kp = g.w[0]->kp;
-    const int nt = g.m <= 64 ? 64 : 192;
+    int row_tiles = 0;
+    for (int i = 0; i < g.n; ++i) row_tiles += static_cast<int>((g.w[i]->rows + kBMW - 1) / kBMW);
+    const int nt = choose_nt(g.m, row_tiles, static_cast<int>(kp / kBK), ctx->sm_count);
     LBK_TRY(encode_act_map(&p.act, g.q, g.m, kp, nt));
+    p.nt = nt;
     p.m = static_cast<int>(g.m);
     p.m_tiles = static_cast<int>((g.m + nt - 1) / nt);
     p.k_blocks = static_cast<int>(kp / kBK);
@@ -476,10 +566,11 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.err_word = ctx->err_word;
 #ifdef LBK_TIMELINE
     p.timeline = g_gemm_timeline;
+    p.trace = g_gemm_trace;
 #endif
     if (tiles == 0 || p.k_blocks == 0) return LBK_OK;
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    if (nt == 192)
+    if (nt > 64)
         gemm_kernel<192><<<grid, kThreads, Cfg<192>::kTotal + 1024, stream>>>(p);
     else
         gemm_kernel<64><<<grid, kThreads, Cfg<64>::kTotal + 1024, stream>>>(p);
