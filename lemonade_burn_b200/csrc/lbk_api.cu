@@ -203,6 +203,7 @@ int lbk_destroy(lbk_ctx *c) {
     if (ctx->scratch) cudaFree(ctx->scratch);
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->small_scratch) cudaFree(ctx->small_scratch);
+    if (ctx->gemm_acc) cudaFree(ctx->gemm_acc);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return LBK_OK;

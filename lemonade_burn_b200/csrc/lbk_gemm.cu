@@ -86,6 +86,8 @@ struct GemmParams {
     int tile_end[LBK_MAX_GROUP];        // running tile count up to and including matrix i
     int n_mat, m, m_tiles, k_blocks, total_tiles;
     int nt;                             // token rows per tile in this launch (multiple of 16, <= capacity)
+    int ksplit, kb_part;                // every tile's K blocks are cut into ksplit parts of kb_part blocks (a multiple of 4)
+    int32_t *acc[LBK_MAX_GROUP];        // ksplit > 1: zeroed int32 [m][rows] that the parts add their sums into
     const float *qscale;
     const int32_t *qsum;
     int *err_word;
@@ -249,14 +251,25 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         n_tile = local / p.m_tiles;
     };
 
+    // A work item is one tile, or one of the ksplit equal parts of a tile's K blocks. All roles walk
+    // items blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int total_items = p.total_tiles * p.ksplit;
+    auto item_range = [&](int item, int &tile, int &kb0, int &kb1) {
+        tile = item / p.ksplit;
+        const int part = item - tile * p.ksplit;
+        kb0 = part * p.kb_part;
+        kb1 = kb0 + p.kb_part < k_blocks ? kb0 + p.kb_part : k_blocks;
+    };
+
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
             int pr = 0, pit = 0;  // pairs of activation blocks, packed-weight stages
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-                int mat, m_tile, n_tile;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                int tile, kb0, kb1, mat, m_tile, n_tile;
+                item_range(item, tile, kb0, kb1);
                 decode_tile(tile, mat, m_tile, n_tile);
-                for (int kb = 0; kb < k_blocks; kb += 2, ++pr) {
+                for (int kb = kb0; kb < kb1; kb += 2, ++pr) {
                     if ((kb % kPackBlocks) == 0) {
                         const int ps = pit % PS, pround = pit / PS;
                         if (pround > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort))) {
@@ -273,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                         ok = false;
                         break;
                     }
-                    const int nblk = k_blocks - kb < 2 ? 1 : 2;
+                    const int nblk = kb1 - kb < 2 ? 1 : 2;
                     ptx::mbar_arrive_expect_tx(bar(C::kBarFull + s), static_cast<uint32_t>(nblk * p.nt) * kBK);
                     for (int b = 0; b < nblk; ++b)
                         ptx::tma_load_2d(base + (s * 2 + b) * C::kActBytes, &p.act, bar(C::kBarFull + s), (kb + b) * kBK, m_tile * p.nt);
@@ -290,8 +303,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         // last readers of those TMEM slots; (ps, pphase) follow the packed-weight stage.
         int pr = 0, sp = 0, lg = PG - 2, ps = -1;
         uint32_t lg_phase = 1, pphase = 1;
-        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x) {
-            for (int kb = 0; kb < k_blocks; kb += 2, ++pr) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+            int tile, kb0, kb1;
+            item_range(item, tile, kb0, kb1);
+            for (int kb = kb0; kb < kb1; kb += 2, ++pr) {
                 const int sub = (kb & 2) + set;  // this warp's block inside the packed stage
                 if ((kb & 2) == 0) {
                     if (++ps == PS) ps = 0;
@@ -301,8 +316,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                         break;
                     }
                 }
-                const bool have = kb + set < k_blocks;
-                const bool last_of_stage = (kb & 2) != 0 || kb + 2 >= k_blocks;
+                const bool have = kb + set < kb1;
+                const bool last_of_stage = (kb & 2) != 0 || kb + 2 >= kb1;
                 if (have) {
                     // the TMEM slots of this parity were last read by pair pr - 2
                     if (pr >= 2 && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort))) {
@@ -348,7 +363,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             int tcount = 0, sp = 0;
             uint32_t full_phase = 0, pa = 0;
             const uint64_t bdesc0 = smem_desc_sw128(base);  // activation block stage 0; stage s adds s * kActBytes / 16
-            for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tcount) {
                 const int a = tcount & 1, around = tcount >> 1;
                 if (around > 0 && !TL_WAIT(3, wait_bar(bar(C::kBarAccEmpty + a), (around - 1) & 1, s_abort))) {
                     ok = false;
@@ -357,12 +372,13 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (a ? C::kAcc1 : C::kAcc0);
                 // N of this tile: the launch's token tile, less for the last tile of a ragged batch
-                int mat, m_tile, n_tile;
+                int tile, kb0, kb1, mat, m_tile, n_tile;
+                item_range(item, tile, kb0, kb1);
                 decode_tile(tile, mat, m_tile, n_tile);
                 const int left = p.m - m_tile * p.nt;
                 const int n_mma = left < p.nt ? (left + 15) & ~15 : p.nt;
                 const uint32_t idesc = C::kIdesc | (static_cast<uint32_t>(n_mma >> 3) << 17);
-                for (int kb = 0; kb < k_blocks; kb += 2) {
+                for (int kb = kb0; kb < kb1; kb += 2) {
                     if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + sp), full_phase, s_abort))) {
                         ok = false;
                         break;
@@ -370,8 +386,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     tc_fence_after();
                     const uint32_t a_tmem = tmem_base + C::kA0 + pa * 64;
                     const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(sp * 2 * (C::kActBytes >> 4));
-                    umma_i8_ts_block(d_tmem, a_tmem, bdesc, idesc, kb ? 1u : 0u);
-                    if (kb + 1 < k_blocks) umma_i8_ts_block(d_tmem, a_tmem + 32, bdesc + (C::kActBytes >> 4), idesc, 1u);
+                    umma_i8_ts_block(d_tmem, a_tmem, bdesc, idesc, kb != kb0 ? 1u : 0u);
+                    if (kb + 1 < kb1) umma_i8_ts_block(d_tmem, a_tmem + 32, bdesc + (C::kActBytes >> 4), idesc, 1u);
                     umma_commit(bar(C::kBarConsumed + sp));  // both operands' slots are reusable once these MMAs retire
                     if (++sp == PG) {
                         sp = 0;
@@ -388,9 +404,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         int *s_qs = reinterpret_cast<int *>(sm + C::kTok);
         float *s_inv = reinterpret_cast<float *>(sm + C::kTok + 2 * NT * 4);
         int tcount = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles && ok; tile += gridDim.x, ++tcount) {
+        for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tcount) {
             const int a = tcount & 1, around = tcount >> 1;
-            int mat, m_tile, n_tile;
+            int tile, kb0, kb1, mat, m_tile, n_tile;
+            item_range(item, tile, kb0, kb1);
             decode_tile(tile, mat, m_tile, n_tile);
             const int rows = p.rows[mat];
             const int row = n_tile * kBMW + warp * 32 + lane;
@@ -434,6 +451,17 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     sc[i] = s4.x; sc[i + 1] = s4.y; sc[i + 2] = s4.z; sc[i + 3] = s4.w;
                 }
                 tmem_ld_wait();
+                if (p.ksplit > 1) {
+                    // one of several parts of this tile: add the sums into the zeroed int32 buffer
+                    // (the part that starts at block 0 also takes off sum(q)); a small kernel scales later
+                    if (row < rows) {
+                        int32_t *dst = p.acc[mat] + static_cast<size_t>(tok0 + c * 32) * rows + row;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i < ntok) atomicAdd(dst + static_cast<size_t>(i) * rows, static_cast<int>(v[i]) - (kb0 == 0 ? q[i] : 0));
+                    }
+                    continue;
+                }
                 if (row < rows) {
                     const size_t o0 = static_cast<size_t>(tok0 + c * 32) * rows + row;
                     if (c * 32 + 32 <= ntok) {
@@ -499,7 +527,31 @@ static int init_one(Ctx *ctx) {
 int gemm_init(Ctx *ctx) {
     LBK_TRY(init_one<192>(ctx));
     LBK_TRY(init_one<64>(ctx));
+    LBK_CUDA(cudaMalloc(&ctx->gemm_acc, kGemmAccBytes));
     return LBK_OK;
+}
+
+// Parts to cut every tile's K blocks into. A launch with few tiles against the SM count (small
+// token batches, tensor-parallel shards) or with a ragged last round leaves SMs idle; parts add
+// their int32 sums into a zeroed buffer and a small kernel scales them afterwards. Cost model in
+// K-block times of one CTA (about 500 cycles); the zeroing and the scaling kernel are charged as 30.
+static int choose_ksplit(int tiles, int k_blocks, int sms, int *kb_part) {
+    int best = 1;
+    long long best_cost = static_cast<long long>((tiles + sms - 1) / sms) * k_blocks;
+    *kb_part = k_blocks;
+    for (int s = 2; s <= 8; ++s) {
+        const int per = ((k_blocks + s - 1) / s + kPackBlocks - 1) / kPackBlocks * kPackBlocks;
+        if (per < 2 * kPackBlocks) break;
+        const int parts = (k_blocks + per - 1) / per;
+        if (parts != s) continue;  // rounding made fewer parts: that count is or was tried as itself
+        const long long cost = static_cast<long long>((static_cast<long long>(tiles) * s + sms - 1) / sms) * per + 30;
+        if (cost * 100 < best_cost * 85) {
+            best_cost = cost;
+            best = s;
+            *kb_part = per;
+        }
+    }
+    return best;
 }
 
 #ifdef LBK_TIMELINE
@@ -569,13 +621,41 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.trace = g_gemm_trace;
 #endif
     if (tiles == 0 || p.k_blocks == 0) return LBK_OK;
-    const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    p.ksplit = choose_ksplit(tiles, p.k_blocks, ctx->sm_count, &p.kb_part);
+    if (p.ksplit > 1) {
+        // int32 targets: the caller's integer outputs where given, else slices of the context's buffer
+        size_t need = 0;
+        for (int i = 0; i < g.n; ++i)
+            if (!g.iout[i]) need += (g.m * g.w[i]->rows * sizeof(int32_t) + 255) / 256 * 256;
+        if (need > kGemmAccBytes) {
+            p.ksplit = 1;
+            p.kb_part = p.k_blocks;
+        } else {
+            size_t off = 0;
+            for (int i = 0; i < g.n; ++i) {
+                const size_t bytes = g.m * g.w[i]->rows * sizeof(int32_t);
+                if (g.iout[i]) {
+                    p.acc[i] = g.iout[i];
+                } else {
+                    p.acc[i] = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(ctx->gemm_acc) + off);
+                    off += (bytes + 255) / 256 * 256;
+                }
+                LBK_CUDA(cudaMemsetAsync(p.acc[i], 0, bytes, stream));
+            }
+        }
+    }
+    const int items = tiles * p.ksplit;
+    const int grid = items < ctx->sm_count ? items : ctx->sm_count;
     if (nt > 64)
         gemm_kernel<192><<<grid, kThreads, Cfg<192>::kTotal + 1024, stream>>>(p);
     else
         gemm_kernel<64><<<grid, kThreads, Cfg<64>::kTotal + 1024, stream>>>(p);
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
+    if (p.ksplit > 1) {
+        for (int i = 0; i < g.n; ++i)
+            if (g.out[i]) LBK_TRY(launch_scale_epilogue(ctx, p.acc[i], g.qscale, g.w[i]->scale, g.m, g.w[i]->rows, g.out[i], stream));
+    }
     return LBK_OK;
 }
 

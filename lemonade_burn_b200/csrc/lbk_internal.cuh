@@ -35,6 +35,7 @@ int fail(int status, const char *fmt, ...);
     } while (0)
 
 constexpr size_t kSmallScratchBytes = 64 * 1024;
+constexpr size_t kGemmAccBytes = 32u << 20;
 
 // ---- handles -------------------------------------------------------------------------
 struct Ctx {
@@ -48,6 +49,7 @@ struct Ctx {
     size_t scratch_bytes = 0;
     cudaStream_t own_stream = nullptr;  // used by the host-pointer entry points
     void *small_scratch = nullptr;      // kSmallScratchBytes, allocated once at init (reductions)
+    int32_t *gemm_acc = nullptr;        // kGemmAccBytes, allocated once at init: int32 sums of a prefill GEMM split along K
 };
 
 struct Weight {
