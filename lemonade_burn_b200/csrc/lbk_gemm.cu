@@ -35,7 +35,6 @@ constexpr int kBMW = 128;          // weight rows per tile (MMA M, TMEM lanes)
 constexpr int kBK = 128;           // columns per stage = one packed block
 constexpr int kPackBlocks = 4;      // K-blocks per packed-weight stage: [128 rows][128 B] boxes
 constexpr int kPackBytes = kBMW * kBlockBytes * kPackBlocks;  // 16 KB, SWIZZLE_128B
-constexpr int kAStages = 4;        // expanded weight tiles in TMEM (32 columns each)
 constexpr int kEpiWarps = 4, kExpWarps = 4, kExpSets = 2;
 // warps 0-3 epilogue, 4-7 and 8-11 expanders (warp % 4 = the TMEM lane quadrant a warp may touch)
 constexpr int kExpWarp0 = 4, kTmaWarp = 12, kMmaWarp = 13;
@@ -47,33 +46,37 @@ template <int NT>  // capacity in token rows per tile (MMA N): 192 or 64; a laun
 struct Cfg {
     static constexpr int kActBytes = NT * kBK;                  // multiple of 1024 for NT = 192, 64
     static constexpr int kLoadStages = NT == 192 ? 6 : 12;      // activation ring, in K blocks
-    static constexpr int kPairStages = kLoadStages / 2;         // ... in pairs of K blocks (the unit of hand-off)
+    static constexpr int kGroup = NT == 192 ? 2 : 4;            // K blocks per hand-off (see kBarFull below)
+    static constexpr int kGroupStages = kLoadStages / kGroup;   // activation ring in hand-off units
+    static constexpr int kAStages = 2 * kGroup;                 // expanded weight tiles in TMEM (32 columns each): two groups
     static constexpr int kPackStages = 3;                       // packed-weight ring
     static constexpr uint32_t kPack0 = kLoadStages * kActBytes;
-    static constexpr uint32_t kAcc0 = 0, kAcc1 = NT, kA0 = 2 * NT;  // TMEM column map
+    static constexpr uint32_t kAcc0 = 0, kAcc1 = NT, kA0 = 2 * NT;  // TMEM column map: two accumulators, then the weight tiles
     static_assert(2 * NT + kAStages * 32 <= 512, "TMEM budget");
+    static_assert(kGroup == 2 || kGroup == kPackBlocks, "a group is half a packed-weight stage or a whole one");
     // instruction descriptor without N: D s32, A u8 (codes, TMEM), B s8 (activations), K-major, M=128
     static constexpr uint32_t kIdesc = (2u << 4) | (0u << 7) | (1u << 10) | ((kBMW >> 4) << 24);
     static constexpr uint32_t kBars = kPack0 + kPackStages * kPackBytes;
     static constexpr uint32_t kMisc = kBars + 48 * 8;
     static constexpr uint32_t kTok = kMisc + 64;              // per-token sum(q) and 1/(s_a*s_w): 2 x [2][NT]
     static constexpr uint32_t kTotal = kTok + 2 * 2 * NT * 4;
-    // Hand-off is by PAIRS of K blocks. Every barrier wait in the MMA thread drains the tensor
-    // pipe for a few hundred cycles whatever the MMA shape (measured: 4 MMAs + one wait per loop
-    // turn run at 590 cycles a turn, 8 MMAs + one wait at 900), so a wait has to buy as many MMAs
-    // as shared memory allows. One "full" barrier per pair collects both operands: the
-    // activation bytes of one or two blocks (TMA transaction count) and the arrivals of all eight
-    // expander warps (set 0 expands the pair's first block, set 1 its second; a warp with no
-    // block at the odd end of K arrives all the same). One "consumed" barrier per pair (a single
-    // tcgen05.commit) releases the activation stages and, two pairs later, the TMEM weight slots.
-    static constexpr int kBarFull = 0;                        // [pair stages]
-    static constexpr int kBarConsumed = kLoadStages;          // [pair stages]
+    // Hand-off is by GROUPS of kGroup K blocks. Every barrier wait in the MMA thread drains the
+    // tensor pipe for a few hundred cycles whatever the MMA shape (measured: 4 MMAs + one wait per
+    // loop turn run at 590 cycles a turn, 8 MMAs + one wait at 900), so a wait has to buy as many
+    // MMAs as shared memory and TMEM allow: 2 blocks of 192 token rows, 4 blocks of 64. One "full"
+    // barrier per group collects both operands: the activation bytes of its blocks (TMA
+    // transaction count) and one arrival from each of the eight expander warps (set 0 expands the
+    // group's even blocks, set 1 its odd ones; a warp with no block at the ragged end of K arrives
+    // all the same). One "consumed" barrier per group (a single tcgen05.commit) releases the
+    // activation stages and, two groups later, the TMEM weight slots.
+    static constexpr int kBarFull = 0;                        // [group stages]
+    static constexpr int kBarConsumed = kLoadStages;          // [group stages]
     static constexpr int kBarFullPack = 2 * kLoadStages;      // [PS] packed weights landed
     static constexpr int kBarEmptyPack = kBarFullPack + kPackStages;  // [PS] expanders are done with them
     static constexpr int kBarAccFull = kBarEmptyPack + kPackStages;   // [2]
     static constexpr int kBarAccEmpty = kBarAccFull + 2;      // [2]
     static_assert(kBarAccEmpty + 2 <= 48, "barrier area too small");
-    static_assert(kAStages / 2 < kPairStages, "a consumed-barrier phase must still be observable two pairs later");
+    static_assert(2 < kGroupStages, "a consumed-barrier phase must still be observable two groups later");
 };
 
 struct GemmParams {
@@ -198,8 +201,8 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
     using C = Cfg<NT>;
-    constexpr int PG = C::kPairStages, PS = C::kPackStages;
-    static_assert(kAStages == 4 && kExpSets == 2 && kPackBlocks == 4, "the pair hand-off assumes these");
+    constexpr int G = C::kGroup, PG = C::kGroupStages, PS = C::kPackStages;
+    static_assert(kExpSets == 2 && kPackBlocks == 4, "the group hand-off assumes these");
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
@@ -264,12 +267,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            int pr = 0, pit = 0;  // pairs of activation blocks, packed-weight stages
+            int gr = 0, pit = 0;  // groups of activation blocks, packed-weight stages
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int tile, kb0, kb1, mat, m_tile, n_tile;
                 item_range(item, tile, kb0, kb1);
                 decode_tile(tile, mat, m_tile, n_tile);
-                for (int kb = kb0; kb < kb1; kb += 2, ++pr) {
+                for (int kb = kb0; kb < kb1; kb += G, ++gr) {
                     if ((kb % kPackBlocks) == 0) {
                         const int ps = pit % PS, pround = pit / PS;
                         if (pround > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort))) {
@@ -281,15 +284,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                                          kb * kBlockBytes, n_tile * kBMW);
                         ++pit;
                     }
-                    const int s = pr % PG, round = pr / PG;
+                    const int s = gr % PG, round = gr / PG;
                     if (round > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort))) {
                         ok = false;
                         break;
                     }
-                    const int nblk = kb1 - kb < 2 ? 1 : 2;
+                    const int nblk = kb1 - kb < G ? kb1 - kb : G;
                     ptx::mbar_arrive_expect_tx(bar(C::kBarFull + s), static_cast<uint32_t>(nblk * p.nt) * kBK);
                     for (int b = 0; b < nblk; ++b)
-                        ptx::tma_load_2d(base + (s * 2 + b) * C::kActBytes, &p.act, bar(C::kBarFull + s), (kb + b) * kBK, m_tile * p.nt);
+                        ptx::tma_load_2d(base + (s * G + b) * C::kActBytes, &p.act, bar(C::kBarFull + s), (kb + b) * kBK, m_tile * p.nt);
                 }
             }
         }
@@ -298,17 +301,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         const int quad = (warp - kExpWarp0) % kExpWarps, set = (warp - kExpWarp0) / kExpWarps;
         const int r = quad * 32 + lane;  // weight row of the tile = TMEM lane
         const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
-        // Ring positions are counters (no divisions in the loop): pair `pr` uses barrier slot `sp`
-        // and the TMEM slots of parity pr & 1; (lg, lg_phase) follow pair pr - 2, whose MMAs were the
-        // last readers of those TMEM slots; (ps, pphase) follow the packed-weight stage.
-        int pr = 0, sp = 0, lg = PG - 2, ps = -1;
+        // Ring positions are counters (no divisions in the loop): group `gr` uses barrier slot `sp`
+        // and the TMEM slots of parity gr & 1; (lg, lg_phase) follow group gr - 2, whose MMAs were
+        // the last readers of those TMEM slots; (ps, pphase) follow the packed-weight stage.
+        int gr = 0, sp = 0, lg = PG - 2, ps = -1;
         uint32_t lg_phase = 1, pphase = 1;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
             int tile, kb0, kb1;
             item_range(item, tile, kb0, kb1);
-            for (int kb = kb0; kb < kb1; kb += 2, ++pr) {
-                const int sub = (kb & 2) + set;  // this warp's block inside the packed stage
-                if ((kb & 2) == 0) {
+            for (int kb = kb0; kb < kb1; kb += G, ++gr) {
+                if ((kb % kPackBlocks) == 0) {
                     if (++ps == PS) ps = 0;
                     if (ps == 0) pphase ^= 1u;
                     if (!TL_WAIT(1, wait_bar(bar(C::kBarFullPack + ps), pphase, s_abort))) {
@@ -316,16 +318,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                         break;
                     }
                 }
-                const bool have = kb + set < kb1;
-                const bool last_of_stage = (kb & 2) != 0 || kb + 2 >= kb1;
-                if (have) {
-                    // the TMEM slots of this parity were last read by pair pr - 2
-                    if (pr >= 2 && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort))) {
-                        ok = false;
-                        break;
+                bool wrote = false;
+#pragma unroll
+                for (int b = set; b < G; b += kExpSets) {  // this warp's blocks of the group
+                    if (kb + b >= kb1) break;
+                    if (!wrote) {
+                        // the TMEM slots of this parity were last read by group gr - 2
+                        if (gr >= 2 && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort))) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        wrote = true;
                     }
-                    tc_fence_after();
                     // row r of the [128][128 B] swizzled stage; this block's 32 bytes are units 2*sub, 2*sub+1
+                    const int sub = ((kb + b) % kPackBlocks);
                     const uint8_t *pk = sm + C::kPack0 + ps * kPackBytes + r * 128;
                     const int x = r & 7;
                     const uint4 w0 = *reinterpret_cast<const uint4 *>(pk + (((2 * sub) ^ x) << 4));      // packed bytes j = 0..15
@@ -336,13 +343,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     for (int k = 0; k < 4; ++k)
 #pragma unroll
                         for (int i = 0; i < 8; ++i) v[8 * k + i] = (w[i] >> (2 * k)) & 0x03030303u;
-                    tmem_st32(tmem_base + lane_field + C::kA0 + ((pr & 1) * 2 + set) * 32, v);
+                    tmem_st32(tmem_base + lane_field + C::kA0 + ((gr & 1) * G + b) * 32, v);
                 }
-                if (last_of_stage) {  // this warp's last read of the packed stage is behind it
+                if (!ok) break;
+                // this warp's last read of the packed stage is behind it when the stage's last block is
+                if (((kb + G) % kPackBlocks) == 0 || kb + G >= kb1) {
                     __syncwarp();
                     if (lane == 0) ptx::mbar_arrive(bar(C::kBarEmptyPack + ps));
                 }
-                if (have) {
+                if (wrote) {
                     tmem_st_wait();
                     tc_fence_before();
                 }
@@ -378,16 +387,18 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const int left = p.m - m_tile * p.nt;
                 const int n_mma = left < p.nt ? (left + 15) & ~15 : p.nt;
                 const uint32_t idesc = C::kIdesc | (static_cast<uint32_t>(n_mma >> 3) << 17);
-                for (int kb = kb0; kb < kb1; kb += 2) {
+                for (int kb = kb0; kb < kb1; kb += G) {
                     if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + sp), full_phase, s_abort))) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    const uint32_t a_tmem = tmem_base + C::kA0 + pa * 64;
-                    const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(sp * 2 * (C::kActBytes >> 4));
+                    const uint32_t a_tmem = tmem_base + C::kA0 + pa * (G * 32);
+                    const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(sp * G * (C::kActBytes >> 4));
                     umma_i8_ts_block(d_tmem, a_tmem, bdesc, idesc, kb != kb0 ? 1u : 0u);
-                    if (kb + 1 < kb1) umma_i8_ts_block(d_tmem, a_tmem + 32, bdesc + (C::kActBytes >> 4), idesc, 1u);
+#pragma unroll
+                    for (int b = 1; b < G; ++b)
+                        if (kb + b < kb1) umma_i8_ts_block(d_tmem, a_tmem + b * 32, bdesc + static_cast<uint64_t>(b * (C::kActBytes >> 4)), idesc, 1u);
                     umma_commit(bar(C::kBarConsumed + sp));  // both operands' slots are reusable once these MMAs retire
                     if (++sp == PG) {
                         sp = 0;
