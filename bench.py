@@ -211,9 +211,13 @@ TP_HIDDEN, TP_INTER, TP_LAYERS, TP_KV = 8192, 28672, 80, 1024
 TP_BATCH = 64
 
 
-def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers=TP_LAYERS, batch=TP_BATCH):
+def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers=TP_LAYERS, batch=TP_BATCH,
+                prefill_tokens=2048, prefill_layers=8):
     """One step = every projection of every layer once at `batch` token rows (no attention / FFN
-    math between them, like the reference's KB_MODEL sweep). Returns a dict for the JSON line."""
+    math between them, like the reference's KB_MODEL sweep). Row-parallel layers run through the
+    two fused peer-memory kernels and, for comparison, through NCCL all-reduces; a 2048-token
+    prefill of `prefill_layers` layers (NCCL: the partial dots are too large for the one-shot
+    exchange) is timed as well. Returns a dict for the JSON line."""
     from lemonade_burn_b200 import tp
 
     def rand_packed(rows, rb, gen):
@@ -231,6 +235,7 @@ def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers
             "gu": [rand_packed(I // world, H // 4, gen), rand_packed(I // world, H // 4, gen)],
             "down": rand_packed(H, I // world // 4, gen),
         })
+    comm = tp.TpComm(ctx, world, rank) if world > 1 else None
     mods = []
     for L in lays:
         mods.append((tp.ColumnParallelTernary(L["qkv"], [WSCALE] * 3, H, 1, 0, ctx),
@@ -242,57 +247,80 @@ def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers
         d_.world = world
     del lays
     g2 = torch.Generator(device=device).manual_seed(5)
-    x_h = torch.randn(batch, H, device=device, generator=g2)
-    x_o = torch.randn(batch, H // world, device=device, generator=g2)
-    x_d = torch.randn(batch, I // world, device=device, generator=g2)
 
-    def sweep():
-        for qkv, o_, gu, d_ in mods:
-            qkv.forward(x_h)
-            o_.forward(x_o)
-            gu.forward(x_h)
-            d_.forward(x_d)
+    def timed(tokens, n_layers, use_comm, n_steps):
+        x_h = torch.randn(tokens, H, device=device, generator=g2)
+        x_o = torch.randn(tokens, H // world, device=device, generator=g2)
+        x_d = torch.randn(tokens, I // world, device=device, generator=g2)
+        for _, o_, _, d_ in mods:
+            o_.comm = comm if use_comm else None
+            d_.comm = comm if use_comm else None
 
-    for _ in range(warmup):
-        sweep()
-    torch.cuda.synchronize()
-    # one CUDA graph per sweep (kernels and NCCL all-reduces) strips ~1000 host-side launches
-    run, mode = sweep, "eager"
-    try:
-        graph = torch.cuda.CUDAGraph()
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            with torch.cuda.graph(graph, stream=side):
-                sweep()
-        torch.cuda.current_stream().wait_stream(side)
+        def sweep():
+            for qkv, o_, gu, d_ in mods[:n_layers]:
+                qkv.forward(x_h)
+                o_.forward(x_o)
+                gu.forward(x_h)
+                d_.forward(x_d)
+
+        for _ in range(warmup):
+            sweep()
         torch.cuda.synchronize()
-        graph.replay()
+        # one CUDA graph per sweep (kernels and collectives) strips ~1000 host-side launches
+        run, mode = sweep, "eager"
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(graph, stream=side):
+                    sweep()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph.replay()
+            torch.cuda.synchronize()
+            run, mode = graph.replay, "cuda graph"
+        except Exception as exc:  # capture is an optimisation only
+            mode = f"eager (graph capture failed: {type(exc).__name__})"
+            torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         torch.cuda.synchronize()
-        run, mode = graph.replay, "cuda graph"
-    except Exception as exc:  # capture is an optimisation only
-        mode = f"eager (graph capture failed: {type(exc).__name__})"
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n_steps):
+            run()
+        e1.record()
         torch.cuda.synchronize()
+        ctx.check_device_error()
+        ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms[0]) / n_steps, mode
+
+    per_layer = (H + 2 * TP_KV) * H // 4 + H * H // 4 + 2 * I * H // 4 + H * I // 4
+    packed_total = layers * per_layer
+    ms_step, mode = timed(batch, layers, True, steps)
+    res = {"workload": "ternary70b_tp_decode_sweep", "layers": layers, "hidden": H, "intermediate": I, "batch": batch,
+           "parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": ms_step,
+           "tok_per_s": batch / (ms_step * 1e-3), "int8_TOPS": 2.0 * batch * packed_total * 4 / (ms_step * 1e-3) / 1e12,
+           "packed_weight_bytes_total": packed_total, "allreduce_int32_bytes_per_layer": 2 * batch * H * 4,
+           "collectives": "two fused peer-memory kernels per row-parallel layer (NVLink loads/stores)" if world > 1 else "none (one rank)",
+           "launch": mode, "weights": "valid ternary codes, P(0)=0.5, drawn per rank at shard size"}
     if world > 1:
+        ms_nccl, _ = timed(batch, layers, False, steps)
+        res["ms_per_step_nccl_allreduce"] = ms_nccl
+    pl = min(prefill_layers, layers)
+    ms_pf, mode_pf = timed(prefill_tokens, pl, False, 3)
+    res["prefill"] = {"tokens": prefill_tokens, "layers_timed": pl, "ms_per_layer": ms_pf / pl,
+                      "ms_per_80_layers": ms_pf / pl * TP_LAYERS,
+                      "int8_TOPS_per_gpu": 2.0 * prefill_tokens * per_layer * 4 * pl / world / (ms_pf * 1e-3) / 1e12,
+                      "collectives": "NCCL all-reduce (MAX of 2048 floats, SUM of int32 [2048, 8192])" if world > 1 else "none (one rank)",
+                      "launch": mode_pf}
+    if comm is not None:
         dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
-        run()
-    e1.record()
-    torch.cuda.synchronize()
-    ms = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_step = float(ms[0]) / steps
-    packed_total = layers * ((H + 2 * TP_KV) * H // 4 + H * H // 4 + 2 * I * H // 4 + H * I // 4)
-    ops_total = 2.0 * batch * packed_total * 4
-    return {"workload": "ternary70b_tp_decode_sweep", "layers": layers, "hidden": H, "intermediate": I, "batch": batch,
-            "parallelism": f"tp{world}", "scaling": "strong", "ms_per_step": ms_step,
-            "tok_per_s": batch / (ms_step * 1e-3), "int8_TOPS": ops_total / (ms_step * 1e-3) / 1e12,
-            "packed_weight_bytes_total": packed_total, "allreduce_int32_bytes_per_layer": 2 * batch * H * 4,
-            "launch": mode, "weights": "valid ternary codes, P(0)=0.5, drawn per rank at shard size"}
+        comm.close()
+    return res
 
 
 def measured_peaks():

@@ -167,6 +167,35 @@ int lbk_quantize_acts_amax_dev(lbk_ctx *ctx, const float *x_dev, size_t m, size_
 int lbk_scale_epilogue_dev(lbk_ctx *ctx, const int32_t *dots_dev, const float *scale_dev, float wscale,
                            size_t m, size_t rows, float *out_dev, void *stream);
 
+/* The row-parallel layer fused with its two exchanges, over NVLink peer memory (plain loads and
+ * stores; no reference counterpart). Every rank allocates one region, passes its 64-byte CUDA IPC
+ * handle to the other ranks (the caller's transport: torch.distributed, MPI, a file), opens theirs
+ * and builds a communicator from the `world` region pointers (its own at index `rank`).
+ *   lbk_tp_quantize       = lbk_absmax_dev + all-reduce MAX + lbk_quantize_acts_amax_dev, one kernel;
+ *                           at most lbk_tp_max_tokens() token rows
+ *   lbk_tp_partial_buffer   where lbk_ternary_gemm_dev must write this rank's int32 dots
+ *   lbk_tp_reduce_scale   = all-reduce SUM of the int32 dots + lbk_scale_epilogue_dev, one kernel;
+ *                           m * rows * 4 <= lbk_tp_partial_bytes(), rows % 4 == 0; dots_out_dev
+ *                           (optional) receives the summed int32 dots
+ * All ranks must make the same calls in the same order, alternating quantize / reduce_scale.
+ * Waits on a peer are bounded: a rank that never arrives yields LBK_ERR_TIMEOUT from
+ * lbk_check_device_error, not a hang. Results are bit-identical to the unsharded operator. */
+typedef struct lbk_tp_comm lbk_tp_comm;
+size_t lbk_tp_region_bytes(void);
+size_t lbk_tp_max_tokens(void);
+size_t lbk_tp_partial_bytes(void);
+int lbk_tp_region_alloc(lbk_ctx *ctx, void **region_out, unsigned char handle_out[64]);
+int lbk_tp_region_open(lbk_ctx *ctx, const unsigned char handle[64], void **region_out);
+int lbk_tp_region_close(lbk_ctx *ctx, void *region);
+int lbk_tp_region_free(lbk_ctx *ctx, void *region);
+int lbk_tp_comm_create(lbk_ctx *ctx, int world, int rank, void *const *regions, lbk_tp_comm **out);
+int lbk_tp_comm_destroy(lbk_tp_comm *comm);
+void *lbk_tp_partial_buffer(lbk_tp_comm *comm);
+int lbk_tp_quantize(lbk_tp_comm *comm, const float *x_dev, size_t m, size_t k, int8_t *q_dev, float *scale_dev,
+                    int32_t *sum_dev, void *stream);
+int lbk_tp_reduce_scale(lbk_tp_comm *comm, const float *scale_dev, float wscale, size_t m, size_t rows,
+                        float *out_dev, int32_t *dots_out_dev, void *stream);
+
 /* ternary_gemm_multi (gemm.rs:128-195) on already quantised device inputs. */
 int lbk_ternary_gemm_dev(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, const int8_t *q_dev,
                          const float *scale_dev, const int32_t *sum_dev, size_t m,

@@ -57,6 +57,18 @@ SYMBOLS = [
     ("lbk_relu2_mul_rms_norm", _i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
     ("lbk_argmax", _i, [_vp, _vp, _sz, _sz, _vp, _vp]),
     ("lbk_advance_pos", _i, [_vp, _vp, _vp]),
+    ("lbk_tp_region_bytes", _sz, []),
+    ("lbk_tp_max_tokens", _sz, []),
+    ("lbk_tp_partial_bytes", _sz, []),
+    ("lbk_tp_region_alloc", _i, [_vp, _pp, _vp]),
+    ("lbk_tp_region_open", _i, [_vp, _vp, _pp]),
+    ("lbk_tp_region_close", _i, [_vp, _vp]),
+    ("lbk_tp_region_free", _i, [_vp, _vp]),
+    ("lbk_tp_comm_create", _i, [_vp, _i, _i, _pp, _pp]),
+    ("lbk_tp_comm_destroy", _i, [_vp]),
+    ("lbk_tp_partial_buffer", _vp, [_vp]),
+    ("lbk_tp_quantize", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
+    ("lbk_tp_reduce_scale", _i, [_vp, _vp, _f, _sz, _sz, _vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),
     ("lbk_plan_finalize", _i, [_vp]),

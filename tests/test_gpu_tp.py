@@ -107,6 +107,29 @@ def _nccl_worker(rank, world, port, ok_q):
         n = packed.shape[0] // world
         ok = (np.array_equal(dots.cpu().numpy(), wi[0]) and np.array_equal(out.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
               and np.array_equal(part.cpu().numpy().view(np.uint32), wf[0][:, rank * n:(rank + 1) * n].view(np.uint32)))
+        # the same layer through the two fused peer-memory kernels: three calls in a row (the
+        # exchange slots alternate and the sequence numbers advance), then a second layer that
+        # shares the communicator, all against the same oracle numbers
+        comm = tp.TpComm(ctx, world, rank)
+        fused = tp.RowParallelTernary(packed, ws, cols, world, rank, ctx=ctx, comm=comm)
+        xl = torch.from_numpy(np.ascontiguousarray(x[:, rank * lc:(rank + 1) * lc])).cuda()
+        for _ in range(3):
+            fo, fd = fused.forward(xl)
+            torch.cuda.synchronize()
+            ok = ok and np.array_equal(fd.cpu().numpy(), wi[0]) and np.array_equal(fo.cpu().numpy().view(np.uint32), wf[0].view(np.uint32))
+        packed2, ws2, x2 = _case(o, rows=512, cols=2048, m=7, seed=9)
+        lc2 = 2048 // world
+        fused2 = tp.RowParallelTernary(packed2, ws2, 2048, world, rank, ctx=ctx, comm=comm)
+        fo2, fd2 = fused2.forward(torch.from_numpy(np.ascontiguousarray(x2[:, rank * lc2:(rank + 1) * lc2])).cuda())
+        fo, fd = fused.forward(xl)
+        torch.cuda.synchronize()
+        q2, s2, ssum2 = o.quantize_acts(x2)
+        wf2, wi2 = o.simd_gemm_multi([packed2], [ws2], q2, s2, ssum2, want_i32=True)
+        ok = (ok and np.array_equal(fd2.cpu().numpy(), wi2[0]) and np.array_equal(fo2.cpu().numpy().view(np.uint32), wf2[0].view(np.uint32))
+              and np.array_equal(fd.cpu().numpy(), wi[0]))
+        ctx.check_device_error()
+        dist.barrier()
+        comm.close()
         ok_q.put((rank, bool(ok)))
     finally:
         dist.destroy_process_group()
