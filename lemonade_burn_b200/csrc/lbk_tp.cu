@@ -171,14 +171,21 @@ __global__ void __launch_bounds__(256) tp_reduce_scale_kernel(const TpPtrs peers
     }
     __syncthreads();
     for (int i = blockIdx.x * 256 + tid; i < total4; i += gridDim.x * 256) {
+        // One 16-byte volatile load per rank, all in flight before the first add. Volatile: the same
+        // addresses hold new numbers every call, and a peer's memory must not be served from a stale line.
+        int4 v[kTpMaxWorld];
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r) {
+            v[r] = make_int4(0, 0, 0, 0);
+            if (r < world) {
+                const int4 *src = reinterpret_cast<const int4 *>(peers.r[r]->partial) + i;
+                asm volatile("ld.volatile.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v[r].x), "=r"(v[r].y), "=r"(v[r].z), "=r"(v[r].w) : "l"(src));
+            }
+        }
         int4 acc = make_int4(0, 0, 0, 0);
-        for (int r = 0; r < world; ++r) {
-            // volatile: the same addresses hold new numbers every call, and peers' memory must not
-            // be served from a stale line
-            const volatile int4 *src = reinterpret_cast<const volatile int4 *>(peers.r[r]->partial) + i;
-            int4 v;
-            v.x = src->x; v.y = src->y; v.z = src->z; v.w = src->w;
-            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+        for (int r = 0; r < kTpMaxWorld; ++r) {
+            acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
         }
         const int e = i * 4;
         const float inv = __fdiv_rn(1.0f, __fmul_rn(ascale[e / rows], wscale));
