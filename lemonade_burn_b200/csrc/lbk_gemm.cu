@@ -237,6 +237,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    // Everything above overlapped the tail of the kernel before this one when the launch was
+    // programmatic (the quantiser that produces this kernel's activations); from here on its
+    // results are read. Without such a launch this returns at once.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     const int k_blocks = p.k_blocks;
     bool ok = true;
@@ -657,10 +661,24 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     }
     const int items = tiles * p.ksplit;
     const int grid = items < ctx->sm_count ? items : ctx->sm_count;
-    if (nt > 64)
-        gemm_kernel<192><<<grid, kThreads, Cfg<192>::kTotal + 1024, stream>>>(p);
-    else
-        gemm_kernel<64><<<grid, kThreads, Cfg<64>::kTotal + 1024, stream>>>(p);
+    // programmatic stream serialisation: this grid may start while the previous kernel of the
+    // stream is still draining (see griddepcontrol.wait in the kernel)
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(static_cast<unsigned>(grid));
+    cfg.blockDim = dim3(kThreads);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    if (nt > 64) {
+        cfg.dynamicSmemBytes = Cfg<192>::kTotal + 1024;
+        LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<192>, p));
+    } else {
+        cfg.dynamicSmemBytes = Cfg<64>::kTotal + 1024;
+        LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<64>, p));
+    }
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
     if (p.ksplit > 1) {

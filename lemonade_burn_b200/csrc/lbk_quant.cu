@@ -30,14 +30,38 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__rest
     __shared__ float s_f[kQThreads / 32];
     __shared__ int s_i[kQThreads / 32];
     __shared__ float s_scale;
+    // A kernel launched behind this one with programmatic stream serialisation (the prefill GEMM)
+    // may start its prologue now; it waits for this grid's results with griddepcontrol.wait.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float *xr = x + static_cast<size_t>(row) * k;
     int8_t *qr = q + static_cast<size_t>(row) * kp;
     const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
 
+    // Rows of up to kRowCache float4 per thread are read once and kept in registers between the
+    // maximum and the rounding (prefill feeds this kernel 2048 rows of 2560..6912 floats).
+    constexpr int kRowCache = 8;
+    float4 cache[kRowCache];
+    const int n4 = k >> 2;
+    const bool cached = vec && n4 <= kRowCache * kQThreads;
     float am = 0.0f;  // fmaxf drops a NaN operand, as f32::max does (quant.rs:101-104)
+    if (cached) {
+        const float4 *x4 = reinterpret_cast<const float4 *>(xr);
+#pragma unroll
+        for (int j = 0; j < kRowCache; ++j) {
+            const int i = tid + j * kQThreads;
+            cache[j] = i < n4 ? __ldg(x4 + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        if (amax_in == nullptr) {
+#pragma unroll
+            for (int j = 0; j < kRowCache; ++j)
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(cache[j].x), fabsf(cache[j].y)), fmaxf(fabsf(cache[j].z), fabsf(cache[j].w))));
+        }
+    }
     if (amax_in != nullptr) {
         am = amax_in[row];
+    } else if (cached) {
+        // done above
     } else if (vec) {
         const float4 *x4 = reinterpret_cast<const float4 *>(xr);
         for (int i = tid; i < (k >> 2); i += kQThreads) {
@@ -60,6 +84,20 @@ __global__ void __launch_bounds__(kQThreads) quantize_kernel(const float *__rest
     if (amax_out != nullptr) return;
     const float sc = s_scale;
     int acc = 0;
+    if (cached) {
+#pragma unroll
+        for (int j = 0; j < kRowCache; ++j) {
+            const int i = (tid + j * kQThreads) * 4;
+            if (i < kp) {  // columns past k hold zeros, which quantise to zero
+                const int q0 = quant_one(cache[j].x, sc), q1 = quant_one(cache[j].y, sc);
+                const int q2 = quant_one(cache[j].z, sc), q3 = quant_one(cache[j].w, sc);
+                acc += q0 + q1 + q2 + q3;
+                *reinterpret_cast<uint32_t *>(qr + i) = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) |
+                                                        (static_cast<uint32_t>(q3 & 255) << 24);
+            }
+        }
+        for (int i = (tid + kRowCache * kQThreads) * 4; i < kp; i += kQThreads * 4) *reinterpret_cast<uint32_t *>(qr + i) = 0u;
+    } else
     for (int i = tid * 4; i < kp; i += kQThreads * 4) {
         int q0 = 0, q1 = 0, q2 = 0, q3 = 0;
         if (vec && i + 3 < k) {
