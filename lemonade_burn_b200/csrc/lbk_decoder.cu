@@ -181,21 +181,24 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
     }
 }
 
-__global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restrict__ part, int splits,
+__global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
-    extern __shared__ float s_w[];  // [splits] weights exp(m_s - m), then their normaliser in s_w[splits]
-    __shared__ float s_red[4];
+    extern __shared__ float s_w[];  // [splits] weights exp(m_s - m)
+    __shared__ float s_red[8];
+    __shared__ float s_half[kHd];
     const size_t bh = blockIdx.x;  // b * nh + head
     const float *p = part + bh * splits * kPartStride;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     float mx = -INFINITY;
-    for (int s = tid; s < splits; s += 128) mx = fmaxf(mx, p[s * kPartStride + kHd]);
+    for (int s = tid; s < splits; s += 256) mx = fmaxf(mx, p[s * kPartStride + kHd]);
     for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
     if (lane == 0) s_red[warp] = mx;
     __syncthreads();
-    mx = fmaxf(fmaxf(s_red[0], s_red[1]), fmaxf(s_red[2], s_red[3]));
+    mx = s_red[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) mx = fmaxf(mx, s_red[w]);
     float sum = 0.0f;
-    for (int s = tid; s < splits; s += 128) {
+    for (int s = tid; s < splits; s += 256) {
         const float m = p[s * kPartStride + kHd];
         const float w = m == -INFINITY ? 0.0f : __expf(m - mx);  // empty slices weigh nothing
         s_w[s] = w;
@@ -205,11 +208,18 @@ __global__ void __launch_bounds__(128) attn_combine_kernel(const float *__restri
     __syncthreads();
     if (lane == 0) s_red[warp] = sum;
     __syncthreads();
-    sum = s_red[0] + s_red[1] + s_red[2] + s_red[3];
+    sum = 0.0f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) sum += s_red[w];
+    // two halves of the slices side by side, 128 dimensions each, many loads in flight
+    const int d = tid & (kHd - 1), half = tid >> 7;
+    const int s0 = half ? (splits + 1) / 2 : 0, s1 = half ? splits : (splits + 1) / 2;
     float acc = 0.0f;
-#pragma unroll 8
-    for (int s = 0; s < splits; ++s) acc += s_w[s] * p[s * kPartStride + tid];
-    out[bh * kHd + tid] = acc / sum;
+#pragma unroll 16
+    for (int s = s0; s < s1; ++s) acc += s_w[s] * p[s * kPartStride + d];
+    if (half) s_half[d] = acc;
+    __syncthreads();
+    if (!half) out[bh * kHd + d] = (acc + s_half[d]) / sum;
 }
 
 // x += y, then out = rms_norm(x): the residual add of model.rs:359,365 fused with the norm that
@@ -411,7 +421,7 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
                                               scratch_dev);
     LBK_CUDA(cudaGetLastError());
-    attn_combine_kernel<<<static_cast<unsigned>(b * n_heads), kHd, (splits + 1) * sizeof(float), st>>>(scratch_dev, static_cast<int>(splits), out_dev);
+    attn_combine_kernel<<<static_cast<unsigned>(b * n_heads), 256, (splits + 1) * sizeof(float), st>>>(scratch_dev, static_cast<int>(splits), out_dev);
     ctx->launches++;
     LBK_DEC_POST();
 }

@@ -156,8 +156,8 @@ class BitNet:
         """One new token per sequence at position cache.len (model.rs:305-374 with m = 1).
         tokens: int32 CUDA [b]. Returns logits f32 [b, vocab] and advances the cache."""
         cfg, lib, h = self.cfg, self.ctx._lib, self.ctx.handle
-        if splits is None:  # enough blocks in flight to cover HBM latency on long contexts
-            splits = max(1, min(128, cache.cap // 32))
+        if splits is None:  # 32 positions (four passes of the kernel's loop) per slice: enough blocks in flight on long contexts
+            splits = max(1, min(256, (cache.cap + 31) // 32))
         b = tokens.shape[0]
         if b != cache.b:
             raise ValueError("batch size differs from the cache's")
