@@ -72,6 +72,14 @@ int encode_weight_maps(Weight *w) {
 
 // Quantised activations int8 [m][kp] as [box_rows][128 bytes] boxes with the 128-byte swizzle
 // (the K-major operand layout of the tensor core); rows past m read as zeros.
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char *e = getenv("LBK_NO_PDL");
+        return !(e && e[0] == '1');
+    }();
+    return on;
+}
+
 int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int box_rows) {
     return encode_2d_u8(map, q, kp, m, kp, 128, static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }

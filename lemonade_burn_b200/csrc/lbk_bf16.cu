@@ -7,6 +7,7 @@
 // Summation order differs from the reference's 8-lane order, so results agree to rounding,
 // not bit for bit (the reference allows 1e-4 absolute, bf16.rs:113-136).
 #include "lbk_internal.cuh"
+#include "lbk_ptx.cuh"
 
 namespace lbk {
 
@@ -24,6 +25,9 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_kernel(const float *__re
                                                               const uint16_t *__restrict__ w,
                                                               int rows, int cols, int m_total,
                                                               int t0, float *__restrict__ out) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+
     extern __shared__ float s_x[];  // [T][cols]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     for (int i = tid; i < T * cols; i += kThreads) {
@@ -85,19 +89,19 @@ int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, si
         if (left >= kTok) {
             const size_t smem = smem1 * kTok;
             LBK_CUDA(cudaFuncSetAttribute(bf16_linear_kernel<kTok>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            bf16_linear_kernel<kTok><<<grid, kThreads, smem, stream>>>(x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out);
+            LBK_CUDA(launch_chained(bf16_linear_kernel<kTok>, dim3(grid), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out));
         } else if (left >= 2) {
             const size_t smem = smem1 * 2;
             LBK_CUDA(cudaFuncSetAttribute(bf16_linear_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-            bf16_linear_kernel<2><<<grid, kThreads, smem, stream>>>(x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out);
+            LBK_CUDA(launch_chained(bf16_linear_kernel<2>, dim3(grid), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out));
             if (left == 3) {  // the odd last row
                 LBK_CUDA(cudaFuncSetAttribute(bf16_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem1)));
-                bf16_linear_kernel<1><<<grid, kThreads, smem1, stream>>>(x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0 + 2), out);
+                LBK_CUDA(launch_chained(bf16_linear_kernel<1>, dim3(grid), dim3(kThreads), smem1, stream, x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0 + 2), out));
                 ctx->launches++;
             }
         } else {
             LBK_CUDA(cudaFuncSetAttribute(bf16_linear_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem1)));
-            bf16_linear_kernel<1><<<grid, kThreads, smem1, stream>>>(x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out);
+            LBK_CUDA(launch_chained(bf16_linear_kernel<1>, dim3(grid), dim3(kThreads), smem1, stream, x, w, static_cast<int>(rows), static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), out));
         }
         LBK_CUDA(cudaGetLastError());
         ctx->launches++;

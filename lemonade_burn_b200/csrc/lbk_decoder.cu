@@ -16,6 +16,7 @@
 // float results agree with the reference to rounding (its tensor library's summation order is
 // not visible), not bit for bit.
 #include "lbk_internal.cuh"
+#include "lbk_ptx.cuh"
 
 namespace lbk {
 
@@ -43,13 +44,19 @@ __device__ __forceinline__ float block_sum(float v, float *s_red) {
 
 __global__ void embed_kernel(const uint16_t *__restrict__ table, const int *__restrict__ tokens, int hidden,
                              float *__restrict__ out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     const int b = blockIdx.x;
     const uint16_t *row = table + static_cast<size_t>(tokens[b]) * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[static_cast<size_t>(b) * hidden + i] = bf16_to_f32(row[i]);
 }
 
 __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x, const float *__restrict__ w, int n,
-                                                      float eps, float *out) {  // out may alias x
+                                                      float eps, float *out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on (out may alias x)
+
     __shared__ float s_red[8];
     const float *xr = x + static_cast<size_t>(blockIdx.x) * n;
     float *orow = out + static_cast<size_t>(blockIdx.x) * n;
@@ -90,6 +97,9 @@ __global__ void rope_append_kernel(float *__restrict__ q, const float *__restric
                                    const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                    const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap,
                                    uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     const int b = blockIdx.y, h = blockIdx.x, pos = *pos_dev;
     const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
     const int half = hd >> 1;
@@ -125,6 +135,9 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
                                                           const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
                                                           int nh, int kvh, int cap, float scaling, int splits,
                                                           float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp >= group) return;
@@ -183,6 +196,9 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
 
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     extern __shared__ float s_w[];  // [splits] weights exp(m_s - m)
     __shared__ float s_red[8];
     __shared__ float s_half[kHd];
@@ -226,6 +242,9 @@ __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restri
 // follows it (model.rs:361 and the next layer's :332 / the final :369).
 __global__ void __launch_bounds__(256) add_rms_norm_kernel(float *x, const float *__restrict__ y, const float *__restrict__ w, int n,
                                                           float eps, float *__restrict__ out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     __shared__ float s_red[8];
     float *xr = x + static_cast<size_t>(blockIdx.x) * n;
     const float *yr = y + static_cast<size_t>(blockIdx.x) * n;
@@ -259,6 +278,9 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(float *x, const float
 // out = rms_norm(relu(g)^2 * u) (model.rs:363-364 in one pass).
 __global__ void __launch_bounds__(256) relu2_mul_rms_norm_kernel(const float *__restrict__ g, const float *__restrict__ u,
                                                                 const float *__restrict__ w, int n, float eps, float *__restrict__ out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     __shared__ float s_red[8];
     const float *gr = g + static_cast<size_t>(blockIdx.x) * n, *ur = u + static_cast<size_t>(blockIdx.x) * n;
     float *orow = out + static_cast<size_t>(blockIdx.x) * n;
@@ -289,6 +311,9 @@ __global__ void __launch_bounds__(256) relu2_mul_rms_norm_kernel(const float *__
 }
 
 __global__ void relu2_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, size_t n, float *__restrict__ out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const float r = fmaxf(g[i], 0.0f);
         out[i] = r * r * u[i];
@@ -296,6 +321,9 @@ __global__ void relu2_mul_kernel(const float *__restrict__ g, const float *__res
 }
 
 __global__ void add_inplace_kernel(float *__restrict__ x, const float *__restrict__ y, size_t n) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += static_cast<size_t>(gridDim.x) * blockDim.x)
         x[i] += y[i];
 }
@@ -309,6 +337,9 @@ __device__ __forceinline__ bool arg_better(float v, int i, float bv, int bi) { r
 
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restrict__ logits, int n, float *__restrict__ pv,
                                                          int *__restrict__ pi) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     __shared__ float s_v[8];
     __shared__ int s_i[8];
     const float *row = logits + static_cast<size_t>(blockIdx.y) * n;
@@ -341,6 +372,9 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restric
 
 __global__ void __launch_bounds__(32) argmax_merge_kernel(const float *__restrict__ logits, int n, const float *__restrict__ pv,
                                                          const int *__restrict__ pi, int *__restrict__ out) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+
     const int lane = threadIdx.x;
     float bv = lane < kArgParts ? pv[blockIdx.x * kArgParts + lane] : -INFINITY;
     int bi = lane < kArgParts ? pi[blockIdx.x * kArgParts + lane] : 0x7fffffff;
@@ -355,7 +389,10 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const float *__restric
     if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff || first != first) ? 0 : bi;
 }
 
-__global__ void advance_pos_kernel(int *pos) { *pos += 1; }
+__global__ void advance_pos_kernel(int *pos) {
+    ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
+    ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
+ *pos += 1; }
 
 }  // namespace
 }  // namespace lbk
@@ -379,7 +416,7 @@ int lbk_embed_bf16(lbk_ctx *c, const uint16_t *table_dev, const int32_t *tokens_
     LBK_DEC_PRE("lbk_embed_bf16");
     if (b == 0) return LBK_OK;
     if (!table_dev || !tokens_dev || !out_dev) return fail(LBK_ERR_INVALID, "lbk_embed_bf16: null buffer");
-    embed_kernel<<<static_cast<unsigned>(b), 256, 0, st>>>(table_dev, tokens_dev, static_cast<int>(hidden), out_dev);
+    LBK_CUDA(launch_chained(embed_kernel, dim3(static_cast<unsigned>(b)), dim3(256), 0, st, table_dev, tokens_dev, static_cast<int>(hidden), out_dev));
     LBK_DEC_POST();
 }
 
@@ -387,7 +424,7 @@ int lbk_rms_norm(lbk_ctx *c, const float *x_dev, const float *w_dev, size_t rows
     LBK_DEC_PRE("lbk_rms_norm");
     if (rows == 0) return LBK_OK;
     if (!x_dev || !w_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_rms_norm: null buffer or empty row");
-    rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(x_dev, w_dev, static_cast<int>(n), eps, out_dev);
+    LBK_CUDA(launch_chained(rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, x_dev, w_dev, static_cast<int>(n), eps, out_dev));
     LBK_DEC_POST();
 }
 
@@ -400,9 +437,9 @@ int lbk_rope_kv_append(lbk_ctx *c, float *q_dev, const float *k_dev, const float
         return fail(LBK_ERR_INVALID, "lbk_rope_kv_append: null buffer");
     if (head_dim & 1) return fail(LBK_ERR_SHAPE, "head_dim must be even");
     dim3 grid(static_cast<unsigned>(n_heads + kv_heads), static_cast<unsigned>(b));
-    rope_append_kernel<<<grid, 64, 0, st>>>(q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
+    LBK_CUDA(launch_chained(rope_append_kernel, dim3(grid), dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
                                             static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap),
-                                            kcache_dev, vcache_dev);
+                                            kcache_dev, vcache_dev));
     LBK_DEC_POST();
 }
 
@@ -417,11 +454,11 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     if (splits == 0) return fail(LBK_ERR_INVALID, "splits must be positive");
     if (splits > 4096) return fail(LBK_ERR_UNSUPPORTED, "at most 4096 splits");
     dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
-    attn_partial_kernel<<<grid, static_cast<unsigned>(32 * (n_heads / kv_heads)), 0, st>>>(q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
+    LBK_CUDA(launch_chained(attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
-                                              scratch_dev);
+                                              scratch_dev));
     LBK_CUDA(cudaGetLastError());
-    attn_combine_kernel<<<static_cast<unsigned>(b * n_heads), 256, (splits + 1) * sizeof(float), st>>>(scratch_dev, static_cast<int>(splits), out_dev);
+    LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st, scratch_dev, static_cast<int>(splits), out_dev));
     ctx->launches++;
     LBK_DEC_POST();
 }
@@ -430,7 +467,7 @@ int lbk_relu2_mul(lbk_ctx *c, const float *g_dev, const float *u_dev, size_t n, 
     LBK_DEC_PRE("lbk_relu2_mul");
     if (n == 0) return LBK_OK;
     if (!g_dev || !u_dev || !out_dev) return fail(LBK_ERR_INVALID, "lbk_relu2_mul: null buffer");
-    relu2_mul_kernel<<<static_cast<unsigned>((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184), 256, 0, st>>>(g_dev, u_dev, n, out_dev);
+    LBK_CUDA(launch_chained(relu2_mul_kernel, dim3(static_cast<unsigned>((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184)), dim3(256), 0, st, g_dev, u_dev, n, out_dev));
     LBK_DEC_POST();
 }
 
@@ -438,7 +475,7 @@ int lbk_add_inplace(lbk_ctx *c, float *x_dev, const float *y_dev, size_t n, void
     LBK_DEC_PRE("lbk_add_inplace");
     if (n == 0) return LBK_OK;
     if (!x_dev || !y_dev) return fail(LBK_ERR_INVALID, "lbk_add_inplace: null buffer");
-    add_inplace_kernel<<<static_cast<unsigned>((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184), 256, 0, st>>>(x_dev, y_dev, n);
+    LBK_CUDA(launch_chained(add_inplace_kernel, dim3(static_cast<unsigned>((n + 255) / 256 < 1184 ? (n + 255) / 256 : 1184)), dim3(256), 0, st, x_dev, y_dev, n));
     LBK_DEC_POST();
 }
 
@@ -454,7 +491,7 @@ int lbk_add_rms_norm(lbk_ctx *c, float *x_dev, const float *y_dev, const float *
     if (!x_dev || !y_dev || !w_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_add_rms_norm: null buffer or empty row");
     if (!fused_norm_ok(x_dev, y_dev, w_dev, out_dev, n))
         return fail(LBK_ERR_UNSUPPORTED, "lbk_add_rms_norm needs 16-byte aligned rows of a multiple of 4, at most 8192, columns");
-    add_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(x_dev, y_dev, w_dev, static_cast<int>(n), eps, out_dev);
+    LBK_CUDA(launch_chained(add_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, x_dev, y_dev, w_dev, static_cast<int>(n), eps, out_dev));
     LBK_DEC_POST();
 }
 
@@ -465,7 +502,7 @@ int lbk_relu2_mul_rms_norm(lbk_ctx *c, const float *g_dev, const float *u_dev, c
     if (!g_dev || !u_dev || !w_dev || !out_dev || n == 0) return fail(LBK_ERR_INVALID, "lbk_relu2_mul_rms_norm: null buffer or empty row");
     if (!fused_norm_ok(g_dev, u_dev, w_dev, out_dev, n))
         return fail(LBK_ERR_UNSUPPORTED, "lbk_relu2_mul_rms_norm needs 16-byte aligned rows of a multiple of 4, at most 8192, columns");
-    relu2_mul_rms_norm_kernel<<<static_cast<unsigned>(rows), 256, 0, st>>>(g_dev, u_dev, w_dev, static_cast<int>(n), eps, out_dev);
+    LBK_CUDA(launch_chained(relu2_mul_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, g_dev, u_dev, w_dev, static_cast<int>(n), eps, out_dev));
     LBK_DEC_POST();
 }
 
@@ -479,9 +516,9 @@ int lbk_argmax(lbk_ctx *c, const float *logits_dev, size_t rows, size_t n, int32
     int *pi = reinterpret_cast<int *>(pv + kSmallScratchRows * kArgParts);
     for (size_t r0 = 0; r0 < rows; r0 += kSmallScratchRows) {
         const size_t nr = rows - r0 < kSmallScratchRows ? rows - r0 : kSmallScratchRows;
-        argmax_part_kernel<<<dim3(kArgParts, static_cast<unsigned>(nr)), 256, 0, st>>>(logits_dev + r0 * n, static_cast<int>(n), pv, pi);
+        LBK_CUDA(launch_chained(argmax_part_kernel, dim3(dim3(kArgParts, static_cast<unsigned>(nr))), dim3(256), 0, st, logits_dev + r0 * n, static_cast<int>(n), pv, pi));
         LBK_CUDA(cudaGetLastError());
-        argmax_merge_kernel<<<static_cast<unsigned>(nr), 32, 0, st>>>(logits_dev + r0 * n, static_cast<int>(n), pv, pi, out_dev + r0);
+        LBK_CUDA(launch_chained(argmax_merge_kernel, dim3(static_cast<unsigned>(nr)), dim3(32), 0, st, logits_dev + r0 * n, static_cast<int>(n), pv, pi, out_dev + r0));
         LBK_CUDA(cudaGetLastError());
         ctx->launches += 2;
     }
@@ -491,7 +528,7 @@ int lbk_argmax(lbk_ctx *c, const float *logits_dev, size_t rows, size_t n, int32
 int lbk_advance_pos(lbk_ctx *c, int32_t *pos_dev, void *stream) {
     LBK_DEC_PRE("lbk_advance_pos");
     if (!pos_dev) return fail(LBK_ERR_INVALID, "lbk_advance_pos: null buffer");
-    advance_pos_kernel<<<1, 1, 0, st>>>(pos_dev);
+    LBK_CUDA(launch_chained(advance_pos_kernel, dim3(1), dim3(1), 0, st, pos_dev));
     LBK_DEC_POST();
 }
 

@@ -97,6 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int chunks = p.chunks;
+    ptx::pdl_trigger();  // the kernel after this one may be scheduled; it orders itself with pdl_wait
 #ifdef LBK_TIMELINE
     long long tl_start = clock64(), tl_prologue = 0, tl_first = 0, tl_polls = 0;
     long long tl_a = 0, tl_b = 0, tl_c = 0, tl_d = 0;
@@ -137,6 +138,16 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const int idx = sub * 32 + lane, nthr = P * 32;
     const bool vec = (k & 3) == 0 && (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
     const bool cached = p.x != nullptr && vec && ((k >> 2) + nthr - 1) / nthr <= kCacheV && m <= rows_at_once;
+    // Weights do not depend on the kernel before this one, activations do: set up the ring and
+    // start the first weight loads, THEN wait for the predecessor (a chained launch overlaps all of
+    // this with its tail), then read the activation rows.
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
+        ptx::fence_barrier_init();
+        const int first = n_items < kStages ? n_items : kStages;
+        for (int i = 0; i < first; ++i) issue(i);
+    }
+    ptx::pdl_wait();
     RowCache rc;
     if (cached && slot < m) load_cached(p.x + static_cast<size_t>(slot) * k, k, idx, nthr, rc);
     // input transform (decoder step): second operand and norm weights, loaded alongside the row
@@ -144,13 +155,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     if (p.pre != 0 && cached && slot < m) {
         load_cached(p.pre_w, k, idx, nthr, rc_w);
         if (p.pre != LBK_PRE_RMS) load_cached(p.pre_y + static_cast<size_t>(slot) * k, k, idx, nthr, rc_y);
-    }
-
-    if (lane == 0) {
-        for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
-        ptx::fence_barrier_init();
-        const int first = n_items < kStages ? n_items : kStages;
-        for (int i = 0; i < first; ++i) issue(i);
     }
 
 #ifdef LBK_TIMELINE
@@ -459,9 +463,9 @@ int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
                     g.m, cols, smem, ctx->smem_optin);
     const int grid = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     if (p.m <= 8)
-        gemv_kernel<1><<<grid, kThreads, smem, stream>>>(p);
+        LBK_CUDA(launch_chained(gemv_kernel<1>, dim3(grid), dim3(kThreads), smem, stream, p));
     else
-        gemv_kernel<2><<<grid, kThreads, smem, stream>>>(p);
+        LBK_CUDA(launch_chained(gemv_kernel<2>, dim3(grid), dim3(kThreads), smem, stream, p));
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
     return LBK_OK;

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
+#include <utility>
 #include <vector>
 
 #include "lbk.h"
@@ -94,6 +95,25 @@ struct GroupArgs {
     float pre_eps = 0.0f;
 };
 bool gemv_pre_supported(size_t m, size_t cols);
+
+// Launch with programmatic stream serialisation: the grid may be scheduled while the previous
+// kernel of the stream drains; the kernel orders itself with ptx::pdl_wait(). The environment
+// variable LBK_NO_PDL=1 turns every such launch into an ordinary one (for A/B timing).
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr{};
+    attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr.val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
 
 // Fused GEMV kernel (m <= LBK_GEMV_MAX_M). Returns LBK_ERR_UNSUPPORTED when the quantised
 // activations do not fit in shared memory next to the weight ring.

@@ -117,6 +117,14 @@ __device__ __forceinline__ uint4 ldg_hint(const void *ptr, uint64_t policy) {
     return v;
 }
 
+// Programmatic dependent launch. A kernel launched with launch_chained() may start while the
+// kernel before it in the stream is still running; pdl_wait() returns once that kernel has
+// completed and its writes are visible (at once when the launch was an ordinary one), so it goes
+// before the first access to anything a predecessor produces or still reads. pdl_trigger() lets
+// the NEXT kernel of the stream start early in the same way.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap *map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
