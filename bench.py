@@ -543,7 +543,7 @@ def run_ours(args):
         sampler.start()
 
     # ---- device-timed: inputs resident, exactly K steps ---------------------------------
-    torch.cuda.profiler.start()  # lets `ncu --profile-from-start off` see only the measured part
+    torch.cuda.profiler.start()  # `ncu --profile-from-start off` skips the set-up; use --extras none to list the sweep alone
     for _ in range(args.warmup):
         plan.run()
     barrier()
@@ -569,7 +569,6 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     barrier()
-    torch.cuda.profiler.stop()
 
     continued = False
     if rank == 0:
@@ -610,12 +609,15 @@ def run_ours(args):
                 xs.append(xh[off:off + cols].copy())
                 off += cols
         cpu_toks, cores, kern, sample = cpu_sweep_baseline(packed_layers, xs, budget_s=10.0, max_layers=n_cpu_layers)
-        extra = {"config0_gemv": config0_gemv(torch, ops, ctx, device),
-                 "config2_prefill": config2_prefill(torch, ops, ctx, device)}
+        extra = {}
+        if "config0" in args.extras:
+            extra["config0_gemv"] = config0_gemv(torch, ops, ctx, device)
+        if "config2" in args.extras:
+            extra["config2_prefill"] = config2_prefill(torch, ops, ctx, device)
     del plan, linears
     torch.cuda.empty_cache()
-    if rank == 0 and world == 1:
-        extra["config3_decode"] = config3_decode(torch, ctx, device)
+    if rank == 0 and world == 1 and "config3" in args.extras:
+        extra["config3_decode"] = config3_decode(torch, ctx, device, batches=tuple(args.decode_batches))
         torch.cuda.empty_cache()
     tp_res = None
     if args.tp70b or world > 1:
@@ -656,8 +658,12 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tp70b", action="store_true", help="also time the 70B-shaped tensor-parallel sweep at N=1")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS)
+    ap.add_argument("--extras", default="config0,config2,config3",
+                    help="side measurements to add under `extra` (comma list of config0, config2, config3; 'none' for a profiler run)")
+    ap.add_argument("--decode-batches", type=int, nargs="+", default=[1, 16], help="batch sizes of the config-3 decode step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    args.extras = set(args.extras.split(","))
     if args.impl == "reference":
         return run_reference(args)
     return run_ours(args)
