@@ -12,8 +12,6 @@
 // quantised once per CTA into shared memory. Groups must not depend on each other's outputs.
 // Arithmetic per output element is exactly that of the single-group kernel (integer partial
 // sums add exactly).
-#include <cstdio>
-#include <cstdlib>
 #include <vector>
 
 #include "lbk_gemv_core.cuh"
@@ -356,9 +354,7 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         long long *d = p.timeline + static_cast<long long>(gw) * 16;
         d[0] = tl_setup; d[1] = tl_quant; d[2] = tl_wait; d[3] = tl_items; d[4] = static_cast<long long>(tl_g0);
         d[5] = static_cast<long long>(g1); d[6] = clock64() - tl_start; d[7] = tl_nq;
-        unsigned smid;
-        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
-        d[8] = smid;
+
     }
 #endif
 }
@@ -456,30 +452,8 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
     std::vector<int> cut_tile(nw + 1);
     {
         int tile = 0;
-#ifdef LBK_TIMELINE
-        std::vector<double> prefix(grid + 1, 0.0);  // experiment: per-CTA shares from a file of doubles
-        {
-            std::vector<double> wts(grid, 1.0);
-            if (const char *path = getenv("LBK_SWEEP_WEIGHTS")) {
-                if (FILE *f = fopen(path, "rb")) {
-                    if (fread(wts.data(), sizeof(double), grid, f) != static_cast<size_t>(grid)) wts.assign(grid, 1.0);
-                    fclose(f);
-                }
-            }
-            for (int c = 0; c < grid; ++c) prefix[c + 1] = prefix[c] + (split ? wts[c] : 1.0);
-        }
-#endif
         for (int w = 0; w <= nw; ++w) {
-#ifdef LBK_TIMELINE
-            long long c = total;
-            if (w < nw) {
-                const int cta = w / kWarps, sub = w % kWarps;
-                c = static_cast<long long>(static_cast<double>(total) * (prefix[cta] + (prefix[cta + 1] - prefix[cta]) * sub / kWarps) / prefix[grid]);
-                if (w > 0 && c < cut[w - 1]) c = cut[w - 1];
-            }
-#else
             long long c = total * w / nw;
-#endif
             while (tile < tiles_total && tile_start[tile + 1] <= c) ++tile;
             if (!split && tile < tiles_total && c > tile_start[tile]) c = tile_start[++tile];  // round up to a tile boundary
             if (c < tile_start[tile]) c = tile_start[tile];  // an earlier cut was rounded past this one
