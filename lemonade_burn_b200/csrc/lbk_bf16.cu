@@ -75,6 +75,92 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_kernel(const float *__re
     }
 }
 
+// Two to sixteen token rows per pass over W on the tensor cores (mma.sync m16n8k16, bf16 x bf16 ->
+// f32). The f32 activations are split into two bf16 terms, x = hi + lo with lo = bf16(x - hi), so
+// that the products are those of the reference's f32 math to within 2^-17 relative; W's bf16 values
+// are exact. Token rows are the MMA's M side, 16 weight rows per warp step its N side.
+//
+// K is consumed 32 columns at a time and the MMA's k slots are permuted so that every lane's
+// operands are contiguous: lane (g, t) loads the 16 bytes W[row g][32c + 8t .. 8t+7] (eight rows x
+// 64 contiguous bytes per load instruction, whole sectors) and one 16-byte word of x per token row
+// at the same columns; slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take columns 8t+0..3,
+// those of the second 8t+4..7. The permutation is the same for both operands, so the sum is the
+// plain dot product.
+constexpr int kMmaTok = 16;
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t f32_to_bf16_rn(float v) {  // round to nearest even; NaN kept a NaN
+    const uint32_t u = __float_as_uint(v);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x40u;
+    return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
+}
+
+__global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w, int rows,
+                                                                  int cols, int m_total, int t0, int xs_stride /* bytes */,
+                                                                  float *__restrict__ out) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    extern __shared__ __align__(16) uint8_t s_raw[];
+    uint8_t *s_hi = s_raw, *s_lo = s_raw + kMmaTok * xs_stride;  // [16 tokens][xs_stride] bf16
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    for (int i = tid; i < kMmaTok * (cols >> 1); i += kThreads) {  // two columns per step
+        const int tk = i / (cols >> 1), c = (i - tk * (cols >> 1)) * 2;
+        float2 v = make_float2(0.f, 0.f);
+        if (t0 + tk < m_total) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(t0 + tk) * cols + c);
+        const uint32_t h0 = f32_to_bf16_rn(v.x), h1 = f32_to_bf16_rn(v.y);
+        const uint32_t l0 = f32_to_bf16_rn(v.x - __uint_as_float(h0 << 16)), l1 = f32_to_bf16_rn(v.y - __uint_as_float(h1 << 16));
+        *reinterpret_cast<uint32_t *>(s_hi + tk * xs_stride + c * 2) = h0 | (h1 << 16);
+        *reinterpret_cast<uint32_t *>(s_lo + tk * xs_stride + c * 2) = l0 | (l1 << 16);
+    }
+    __syncthreads();
+    const int slices = cols >> 5;
+    const int groups = (rows + 15) >> 4;  // 16 weight rows per warp step
+    const int warps_total = gridDim.x * (kThreads / 32);
+    const uint8_t *xa = s_hi + g * xs_stride + t * 16, *xb = s_hi + (g + 8) * xs_stride + t * 16;
+    const size_t lo_off = static_cast<size_t>(kMmaTok) * xs_stride;
+    for (int grp = blockIdx.x * (kThreads / 32) + warp; grp < groups; grp += warps_total) {
+        const int r0 = grp * 16;
+        const int ra = min(r0 + g, rows - 1), rb = min(r0 + 8 + g, rows - 1);  // clamped rows are computed and dropped
+        const uint4 *wa = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(ra) * cols) + t;
+        const uint4 *wb = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(rb) * cols) + t;
+        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+        for (int c = 0; c < slices; ++c) {
+            const uint4 va = __ldcs(wa + c * 4), vb = __ldcs(wb + c * 4);  // streamed once
+            const uint4 h0 = *reinterpret_cast<const uint4 *>(xa + c * 64), h1 = *reinterpret_cast<const uint4 *>(xb + c * 64);
+            const uint4 l0 = *reinterpret_cast<const uint4 *>(xa + lo_off + c * 64), l1 = *reinterpret_cast<const uint4 *>(xb + lo_off + c * 64);
+            mma_bf16(d0, h0.x, h1.x, h0.y, h1.y, va.x, va.y);
+            mma_bf16(d0, h0.z, h1.z, h0.w, h1.w, va.z, va.w);
+            mma_bf16(d0, l0.x, l1.x, l0.y, l1.y, va.x, va.y);
+            mma_bf16(d0, l0.z, l1.z, l0.w, l1.w, va.z, va.w);
+            mma_bf16(d1, h0.x, h1.x, h0.y, h1.y, vb.x, vb.y);
+            mma_bf16(d1, h0.z, h1.z, h0.w, h1.w, vb.z, vb.w);
+            mma_bf16(d1, l0.x, l1.x, l0.y, l1.y, vb.x, vb.y);
+            mma_bf16(d1, l0.z, l1.z, l0.w, l1.w, vb.z, vb.w);
+        }
+        // D[token][row]: lane (g, t) holds tokens g, g+8 and rows 2t, 2t+1 of each 8-row half
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const float *d = half ? d1 : d0;
+            const int row = r0 + half * 8 + 2 * t;
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                const int tk = t0 + g + hh * 8;
+                if (tk < m_total) {
+                    if (row < rows) out[static_cast<size_t>(tk) * rows + row] = d[hh * 2];
+                    if (row + 1 < rows) out[static_cast<size_t>(tk) * rows + row + 1] = d[hh * 2 + 1];
+                }
+            }
+        }
+    }
+}
+
 }  // namespace
 
 int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows,
@@ -84,6 +170,20 @@ int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, si
     if (smem1 * kTok > ctx->smem_optin)
         return fail(LBK_ERR_UNSUPPORTED, "bf16_linear: %zu columns do not fit in shared memory", cols);
     const int grid = ctx->sm_count * 4;
+    // two or more token rows: tensor cores, sixteen rows per pass over W (needs whole 32-column slices
+    // and 16-byte aligned rows; anything else takes the FMA kernel below)
+    const int xs_stride = static_cast<int>(cols * 2 + 64);  // +64: the 16-byte loads of two token rows land on distinct banks
+    if (m >= 2 && (cols & 31) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
+        static_cast<size_t>(2 * kMmaTok) * xs_stride <= ctx->smem_optin) {
+        const size_t smem = static_cast<size_t>(2 * kMmaTok) * xs_stride;
+        LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        for (size_t t0 = 0; t0 < m; t0 += kMmaTok) {
+            LBK_CUDA(launch_chained(bf16_linear_mma_kernel, dim3(ctx->sm_count), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows),
+                                    static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, out));
+            ctx->launches++;
+        }
+        return LBK_OK;
+    }
     for (size_t t0 = 0; t0 < m; t0 += kTok) {
         const size_t left = m - t0;
         if (left >= kTok) {

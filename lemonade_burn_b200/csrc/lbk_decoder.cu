@@ -194,6 +194,111 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
     }
 }
 
+// The same slice-of-positions kernel for grouped-query attention with the K/V rows staged in
+// shared memory: the warps of a block are the query heads of ONE KV head, so the rows are fetched
+// from HBM once per block (128-bit loads, all in flight at once: one DRAM round trip per 32
+// positions) instead of once per warp, and the per-position warp reductions of the kernel above
+// disappear: for q.K lane p owns position p and walks its row (K rows are padded to 272 bytes, which
+// makes the 16-byte reads of 8 neighbouring lanes hit distinct banks; q is read as a broadcast);
+// for P.V lane l owns dims 4l..4l+3 and the weights travel by shuffle.
+constexpr int kAttnChunk = 32;           // positions staged at a time (one per lane)
+constexpr int kKRow = kHd * 2 + 16;      // bytes per staged K row
+constexpr int kVRow = kHd * 2;           // bytes per staged V row
+__global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
+                                                                 const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
+                                                                 int nh, int kvh, int cap, float scaling, int splits,
+                                                                 float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];
+    __shared__ __align__(16) uint8_t s_v[kAttnChunk * kVRow];
+    __shared__ __align__(16) float s_q[8 * kHd];
+    const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
+    const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
+    const int total = *pos_dev + 1;  // keys 0..pos
+    const int per = (total + splits - 1) / splits;
+    const int p0 = sp * per, p1 = min(total, p0 + per);
+    const int head = kh * group + warp;
+    for (int i = tid; i < group * kHd; i += nthr) s_q[i] = q[(static_cast<size_t>(b) * nh + kh * group) * kHd + i] * scaling;
+    const uint16_t *kb = kc + (static_cast<size_t>(b) * kvh + kh) * cap * kHd;
+    const uint16_t *vb = vc + (static_cast<size_t>(b) * kvh + kh) * cap * kHd;
+    float mx = -INFINITY, sum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int pc = p0; pc < p1; pc += kAttnChunk) {
+        const int n = min(kAttnChunk, p1 - pc);
+        __syncthreads();  // the previous chunk has been consumed (and s_q is written, first time round)
+        // stage n rows of K and of V, 16 segments of 16 bytes per row: every load is issued before
+        // the first store, so the chunk costs one trip to HBM
+        constexpr int kSegIters = kAttnChunk * 16 / 128;  // blocks of 128 threads and more (4 query heads per KV head)
+        uint4 kreg[kSegIters], vreg[kSegIters];
+#pragma unroll
+        for (int j = 0; j < kSegIters; ++j) {
+            const int i = tid + j * nthr;
+            if (i < n * 16) {
+                const int r = i >> 4, seg = i & 15;
+                kreg[j] = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+                vreg[j] = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kSegIters; ++j) {
+            const int i = tid + j * nthr;
+            if (i < n * 16) {
+                const int r = i >> 4, seg = i & 15;
+                *reinterpret_cast<uint4 *>(s_k + r * kKRow + seg * 16) = kreg[j];
+                *reinterpret_cast<uint4 *>(s_v + r * kVRow + seg * 16) = vreg[j];
+            }
+        }
+        __syncthreads();
+        // q.K: lane p walks row p
+        float sc = -INFINITY;
+        if (lane < n) {
+            const uint8_t *kr = s_k + lane * kKRow;
+            const float *qh = s_q + warp * kHd;
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int it = 0; it < kHd / 8; ++it) {
+                const uint4 kk = *reinterpret_cast<const uint4 *>(kr + it * 16);
+                const float4 qa = *reinterpret_cast<const float4 *>(qh + it * 8), qb = *reinterpret_cast<const float4 *>(qh + it * 8 + 4);
+                d0 += qa.x * bf16_to_f32(kk.x & 0xffff) + qa.y * bf16_to_f32(kk.x >> 16) + qa.z * bf16_to_f32(kk.y & 0xffff) +
+                      qa.w * bf16_to_f32(kk.y >> 16);
+                d1 += qb.x * bf16_to_f32(kk.z & 0xffff) + qb.y * bf16_to_f32(kk.z >> 16) + qb.z * bf16_to_f32(kk.w & 0xffff) +
+                      qb.w * bf16_to_f32(kk.w >> 16);
+            }
+            sc = d0 + d1;
+        }
+        float nm = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(0xffffffffu, nm, o));
+        nm = fmaxf(nm, mx);
+        const float corr = __expf(mx - nm);
+        const float w = lane < n ? __expf(sc - nm) : 0.0f;
+        float ws = w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        sum = sum * corr + ws;
+        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+        // P.V: lane l owns dims 4l..4l+3
+        const uint8_t *vr = s_v + lane * 8;
+#pragma unroll 8
+        for (int p = 0; p < n; ++p) {
+            const float wp = __shfl_sync(0xffffffffu, w, p);
+            const uint2 vv = *reinterpret_cast<const uint2 *>(vr + p * kVRow);
+            acc.x += wp * bf16_to_f32(vv.x & 0xffff);
+            acc.y += wp * bf16_to_f32(vv.x >> 16);
+            acc.z += wp * bf16_to_f32(vv.y & 0xffff);
+            acc.w += wp * bf16_to_f32(vv.y >> 16);
+        }
+        mx = nm;
+    }
+    float *o = part + ((static_cast<size_t>(b) * nh + head) * splits + sp) * kPartStride;
+    *reinterpret_cast<float4 *>(o + lane * 4) = acc;
+    if (lane == 0) {
+        o[kHd] = mx;
+        o[kHd + 1] = sum;
+    }
+}
+
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
@@ -454,7 +559,8 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     if (splits == 0) return fail(LBK_ERR_INVALID, "splits must be positive");
     if (splits > 4096) return fail(LBK_ERR_UNSUPPORTED, "at most 4096 splits");
     dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
-    LBK_CUDA(launch_chained(attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
+    const bool staged = n_heads / kv_heads >= 4;  // several query heads share the rows: fetch them once per block
+    LBK_CUDA(launch_chained(staged ? attn_partial_staged_kernel : attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
                                               scratch_dev));
     LBK_CUDA(cudaGetLastError());

@@ -71,11 +71,14 @@ def test_dtype_and_shape_errors(oracle, ctx):
         ops.bf16_linear(torch.zeros(1, 8, device="cuda"), torch.zeros(4, 8, device="cuda"))
 
 
-@pytest.mark.parametrize("m", [1, 3, 4, 7])
-def test_bf16_linear(oracle, ctx, m):
+@pytest.mark.parametrize("m,rows,cols", [(1, 1000, 2560), (3, 1000, 2560), (4, 1000, 2560), (7, 1000, 2560), (16, 1003, 2560),
+                                         (19, 37, 512), (2, 1000, 2568), (5, 64, 40)])
+def test_bf16_linear(oracle, ctx, m, rows, cols):
+    """One token row takes the FMA kernel, two or more the tensor-core kernel (activations split into
+    two bf16 terms), ragged row counts and more than sixteen token rows included; column counts that
+    are not whole 32-column slices fall back to the FMA kernel."""
     import torch
     from lemonade_burn_b200 import ops
-    rows, cols = 1000, 2560
     g = torch.Generator().manual_seed(m)
     w = (torch.randn(rows, cols, generator=g) * 0.02).to(torch.bfloat16)
     x = torch.randn(m, cols, generator=g)
