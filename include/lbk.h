@@ -231,6 +231,16 @@ int lbk_attn_decode(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev
 int lbk_relu2_mul(lbk_ctx *ctx, const float *g_dev, const float *u_dev, size_t n, float *out_dev, void *stream);
 /* x += y (the residual adds of model.rs:359,365). */
 int lbk_add_inplace(lbk_ctx *ctx, float *x_dev, const float *y_dev, size_t n, void *stream);
+/* lbk_rope_kv_append + lbk_attn_decode in one launch, for 4..8 query heads per KV head, head_dim
+ * 128 and at most 256 splits (lbk_attn_decode_fused_supported): q_dev, k_dev, v_dev are the raw
+ * projections ([b][n_heads*128], [b][kv_heads*128] x 2); the new position's K/V row is appended to
+ * the caches by the kernel. scratch as for lbk_attn_decode; counters_dev: b * kv_heads ints, zero
+ * before the first call (the kernel leaves them zero). */
+int lbk_attn_decode_fused_supported(size_t n_heads, size_t kv_heads, size_t head_dim, size_t splits);
+int lbk_attn_decode_fused(lbk_ctx *ctx, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                          const float *sin_dev, const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads,
+                          size_t head_dim, size_t cap, size_t splits, uint16_t *kcache_dev, uint16_t *vcache_dev,
+                          float *scratch_dev, int32_t *counters_dev, float *out_dev, void *stream);
 /* Fusions of the above for the decode step (rows of a multiple of 4, at most 8192, columns;
  * 16-byte aligned): x += y then out = rms_norm(x) (model.rs:359-361, 365 + the next norm); and
  * out = rms_norm(relu(g)^2 * u) (model.rs:363-364). */

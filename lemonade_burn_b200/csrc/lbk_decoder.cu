@@ -299,6 +299,164 @@ __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *_
     }
 }
 
+// The whole attention of a decode step in one launch, for grouped queries (4..8 query heads per KV
+// head, head dim 128): RoPE on q and on the new k (model.rs:298-302), the new position's K/V row
+// appended to the bf16 cache, the staged slice kernel above, and the merge of the slices done by
+// whichever block of a KV head finishes last (each block counts itself after publishing its
+// partial results; the counter resets itself). Grid (splits, kvh, b), block 32 * group threads.
+// `counters`: b * kvh ints, zero before the first launch.
+template <bool MERGE>
+__global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restrict__ q_raw, const float *__restrict__ k_new,
+                                                        const float *__restrict__ v_new, const float *__restrict__ cos_t,
+                                                        const float *__restrict__ sin_t, const int *__restrict__ pos_dev, int nh, int kvh,
+                                                        int cap, float scaling, int splits, uint16_t *__restrict__ kc,
+                                                        uint16_t *__restrict__ vc, float *__restrict__ part, int *__restrict__ counters,
+                                                        float *__restrict__ out /* [b][nh*hd] */) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];  // later: the merge's weights, [group][splits]
+    __shared__ __align__(16) uint8_t s_v[kAttnChunk * kVRow];
+    __shared__ __align__(16) float s_q[8 * kHd];
+    __shared__ int s_last;
+    const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
+    const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
+    const int pos = *pos_dev, total = pos + 1;  // keys 0..pos
+    const int per = (total + splits - 1) / splits;
+    const int p0 = sp * per, p1 = min(total, p0 + per);
+    const int head = kh * group + warp;
+    const float *cs = cos_t + static_cast<size_t>(pos) * kHd, *sn = sin_t + static_cast<size_t>(pos) * kHd;
+    // x * cos + rotate_half(x) * sin, rotate_half = cat(-x2, x1), then the 1/sqrt(d) of the scores
+    for (int i = tid; i < group * kHd; i += nthr) {
+        const int d = i & (kHd - 1);
+        const float *qh = q_raw + (static_cast<size_t>(b) * nh + kh * group) * kHd + (i - d);
+        const float v = d < kHd / 2 ? qh[d] * cs[d] + (-qh[d + kHd / 2]) * sn[d] : qh[d] * cs[d] + qh[d - kHd / 2] * sn[d];
+        s_q[i] = v * scaling;
+    }
+    uint16_t *kb = kc + (static_cast<size_t>(b) * kvh + kh) * cap * kHd;
+    uint16_t *vb = vc + (static_cast<size_t>(b) * kvh + kh) * cap * kHd;
+    float mx = -INFINITY, sum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int pc = p0; pc < p1; pc += kAttnChunk) {
+        const int n = min(kAttnChunk, p1 - pc);
+        __syncthreads();  // the previous chunk has been consumed (and s_q is written, first time round)
+        constexpr int kSegIters = kAttnChunk * 16 / 128;
+        uint4 kreg[kSegIters], vreg[kSegIters];
+#pragma unroll
+        for (int j = 0; j < kSegIters; ++j) {
+            const int i = tid + j * nthr;
+            if (i < n * 16 && pc + (i >> 4) != pos) {  // the row of the new position is not in the cache yet
+                const int r = i >> 4, seg = i & 15;
+                kreg[j] = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+                vreg[j] = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < kSegIters; ++j) {
+            const int i = tid + j * nthr;
+            if (i < n * 16 && pc + (i >> 4) != pos) {
+                const int r = i >> 4, seg = i & 15;
+                *reinterpret_cast<uint4 *>(s_k + r * kKRow + seg * 16) = kreg[j];
+                *reinterpret_cast<uint4 *>(s_v + r * kVRow + seg * 16) = vreg[j];
+            }
+        }
+        if (pos >= pc && pos < pc + n && tid < kHd) {
+            // the new position: RoPE on k, both rows rounded to bf16 as the cache holds them, stored
+            // in the cache by this block (the only one whose slice contains the position)
+            const float *kn = k_new + (static_cast<size_t>(b) * kvh + kh) * kHd, *vn = v_new + (static_cast<size_t>(b) * kvh + kh) * kHd;
+            const int d = tid;
+            const float kr = d < kHd / 2 ? kn[d] * cs[d] + (-kn[d + kHd / 2]) * sn[d] : kn[d] * cs[d] + kn[d - kHd / 2] * sn[d];
+            const uint16_t kbits = f32_to_bf16(kr), vbits = f32_to_bf16(vn[d]);
+            reinterpret_cast<uint16_t *>(s_k + (pos - pc) * kKRow)[d] = kbits;
+            reinterpret_cast<uint16_t *>(s_v + (pos - pc) * kVRow)[d] = vbits;
+            kb[static_cast<size_t>(pos) * kHd + d] = kbits;
+            vb[static_cast<size_t>(pos) * kHd + d] = vbits;
+        }
+        __syncthreads();
+        float sc = -INFINITY;
+        if (lane < n) {
+            const uint8_t *kr = s_k + lane * kKRow;
+            const float *qh = s_q + warp * kHd;
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int it = 0; it < kHd / 8; ++it) {
+                const uint4 kk = *reinterpret_cast<const uint4 *>(kr + it * 16);
+                const float4 qa = *reinterpret_cast<const float4 *>(qh + it * 8), qb = *reinterpret_cast<const float4 *>(qh + it * 8 + 4);
+                d0 += qa.x * bf16_to_f32(kk.x & 0xffff) + qa.y * bf16_to_f32(kk.x >> 16) + qa.z * bf16_to_f32(kk.y & 0xffff) +
+                      qa.w * bf16_to_f32(kk.y >> 16);
+                d1 += qb.x * bf16_to_f32(kk.z & 0xffff) + qb.y * bf16_to_f32(kk.z >> 16) + qb.z * bf16_to_f32(kk.w & 0xffff) +
+                      qb.w * bf16_to_f32(kk.w >> 16);
+            }
+            sc = d0 + d1;
+        }
+        float nm = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(0xffffffffu, nm, o));
+        nm = fmaxf(nm, mx);
+        const float corr = __expf(mx - nm);
+        const float w = lane < n ? __expf(sc - nm) : 0.0f;
+        float ws = w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        sum = sum * corr + ws;
+        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+        const uint8_t *vr = s_v + lane * 8;
+#pragma unroll 8
+        for (int p = 0; p < n; ++p) {
+            const float wp = __shfl_sync(0xffffffffu, w, p);
+            const uint2 vv = *reinterpret_cast<const uint2 *>(vr + p * kVRow);
+            acc.x += wp * bf16_to_f32(vv.x & 0xffff);
+            acc.y += wp * bf16_to_f32(vv.x >> 16);
+            acc.z += wp * bf16_to_f32(vv.y & 0xffff);
+            acc.w += wp * bf16_to_f32(vv.y >> 16);
+        }
+        mx = nm;
+    }
+    float *prt = part + (static_cast<size_t>(b) * nh + head) * splits * kPartStride;
+    float *o = prt + static_cast<size_t>(sp) * kPartStride;
+    *reinterpret_cast<float4 *>(o + lane * 4) = acc;
+    if (lane == 0) {
+        o[kHd] = mx;
+        o[kHd + 1] = sum;
+    }
+    if (!MERGE) return;  // the caller merges the slices with attn_combine_kernel
+    // ---- merge by the last block of this KV head --------------------------------------------
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int *cnt = counters + b * kvh + kh;
+        const int old = atomicAdd(cnt, 1);
+        s_last = old == splits - 1;
+        if (s_last) *cnt = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float *s_w = reinterpret_cast<float *>(s_k) + warp * splits;  // this head's weights exp(m_s - m); splits <= 256
+    float gm = -INFINITY;
+    for (int s2 = lane; s2 < splits; s2 += 32) gm = fmaxf(gm, __ldcg(prt + s2 * kPartStride + kHd));
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o2));
+    float gs = 0.0f;
+    for (int s2 = lane; s2 < splits; s2 += 32) {
+        const float m = __ldcg(prt + s2 * kPartStride + kHd);
+        const float w = m == -INFINITY ? 0.0f : __expf(m - gm);  // empty slices weigh nothing
+        s_w[s2] = w;
+        gs += w * __ldcg(prt + s2 * kPartStride + kHd + 1);
+    }
+#pragma unroll
+    for (int o2 = 16; o2 > 0; o2 >>= 1) gs += __shfl_xor_sync(0xffffffffu, gs, o2);
+    __syncwarp();
+    float4 tot = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 8
+    for (int s2 = 0; s2 < splits; ++s2) {
+        const float w = s_w[s2];
+        const float4 a = __ldcg(reinterpret_cast<const float4 *>(prt + s2 * kPartStride) + lane);
+        tot.x += w * a.x; tot.y += w * a.y; tot.z += w * a.z; tot.w += w * a.w;
+    }
+    const float inv = 1.0f / gs;
+    *reinterpret_cast<float4 *>(out + (static_cast<size_t>(b) * nh + head) * kHd + lane * 4) = make_float4(tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
+}
+
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
@@ -566,6 +724,43 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     LBK_CUDA(cudaGetLastError());
     LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st, scratch_dev, static_cast<int>(splits), out_dev));
     ctx->launches++;
+    LBK_DEC_POST();
+}
+
+int lbk_attn_decode_fused_supported(size_t n_heads, size_t kv_heads, size_t head_dim, size_t splits) {
+    return head_dim == kHd && kv_heads != 0 && n_heads % kv_heads == 0 && n_heads / kv_heads >= 4 && n_heads / kv_heads <= 8 && splits >= 1 &&
+                   splits <= 256
+               ? 1
+               : 0;
+}
+
+int lbk_attn_decode_fused(lbk_ctx *c, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                          const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits,
+                          uint16_t *kcache_dev, uint16_t *vcache_dev, float *scratch_dev, int32_t *counters_dev, float *out_dev, void *stream) {
+    LBK_DEC_PRE("lbk_attn_decode_fused");
+    if (b == 0) return LBK_OK;
+    if (!q_dev || !k_dev || !v_dev || !cos_dev || !sin_dev || !pos_dev || !kcache_dev || !vcache_dev || !scratch_dev || !counters_dev || !out_dev)
+        return fail(LBK_ERR_INVALID, "lbk_attn_decode_fused: null buffer");
+    if (!lbk_attn_decode_fused_supported(n_heads, kv_heads, head_dim, splits))
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_attn_decode_fused: head_dim 128, 4..8 query heads per KV head and at most 256 splits");
+    dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
+    // Merging inside the kernel (by the last block of a KV head) saves a launch but serialises the
+    // merge of a whole KV head in one block; measured slower than the separate combine kernel
+    // (1.60 ms against 1.49 ms per batch-1 step), so it is used only when there is a single slice.
+    if (splits == 1) {
+        LBK_CUDA(launch_chained(attn_fused_kernel<true>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
+                                cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
+                                1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
+                                counters_dev, out_dev));
+    } else {
+        LBK_CUDA(launch_chained(attn_fused_kernel<false>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
+                                cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
+                                1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
+                                counters_dev, out_dev));
+        LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st,
+                                scratch_dev, static_cast<int>(splits), out_dev));
+        ctx->launches++;
+    }
     LBK_DEC_POST();
 }
 

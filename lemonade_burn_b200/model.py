@@ -177,6 +177,11 @@ class BitNet:
         # Where the decode kernel can hold the input row in registers (small batches), the norms, the
         # residual adds and the gate run inside the projection kernels: 7 launches a layer, not 13.
         pre_h, pre_a, pre_i = ops.pre_supported(b, H), ops.pre_supported(b, nh * hd), ops.pre_supported(b, I)
+        attn_fused = bool(lib.lbk_attn_decode_fused_supported(nh, kvh, hd, splits))
+        key = ("attn_counters", (b * kvh,), torch.int32)
+        if key not in self._bufs:
+            self._bufs[key] = torch.zeros(b * kvh, dtype=torch.int32, device=self.device)  # zero once; the kernel keeps them zero
+        counters = self._bufs[key]
 
         def add_norm(xin, y, w, xout):  # xout = xin + y; n = rms_norm(xout) * w
             if fused and xin is xout:
@@ -203,10 +208,14 @@ class BitNet:
                 x, x2 = x2, x
             else:
                 q, k, v = ops.ternary_linear3(add_norm(x, d, l["input_norm"], x), qkv_l)
-            chk(lib.lbk_rope_kv_append(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
-                                       P(cache.k[li]), P(cache.v[li]), st))
-            chk(lib.lbk_attn_decode(h, P(q), P(cache.k[li]), P(cache.v[li]), P(cache.pos), b, nh, kvh, hd, cache.cap, splits,
-                                    P(scratch), P(attn), st))
+            if attn_fused:  # RoPE, KV append, attention slices and their merge in one launch
+                chk(lib.lbk_attn_decode_fused(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
+                                              splits, P(cache.k[li]), P(cache.v[li]), P(scratch), P(counters), P(attn), st))
+            else:
+                chk(lib.lbk_rope_kv_append(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache.pos), b, nh, kvh, hd, cache.cap,
+                                           P(cache.k[li]), P(cache.v[li]), st))
+                chk(lib.lbk_attn_decode(h, P(q), P(cache.k[li]), P(cache.v[li]), P(cache.pos), b, nh, kvh, hd, cache.cap, splits,
+                                        P(scratch), P(attn), st))
             if pre_a:
                 o = ops.ternary_linear_pre(ops.PRE_RMS, attn, None, l["attn_sub_norm"], e, [l["o"]])[0]
             else:

@@ -204,3 +204,56 @@ def test_projection_with_input_transform(oracle, ctx, m, cols):
     with pytest.raises(_lib.LbkError):
         ops.ternary_linear_pre(ops.PRE_RMS, torch.randn(16, cols).cuda(), None, w, eps, [lin]) if not ops.pre_supported(16, cols) else (_ for _ in ()).throw(_lib.LbkError(7, "n/a"))
     ctx.check_device_error()
+
+
+@pytest.mark.parametrize("total,splits,nh,kvh", [(1, 1, 8, 2), (37, 4, 8, 2), (1000, 32, 8, 2), (4097, 130, 20, 5), (300, 256, 16, 2)])
+def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh):
+    """lbk_attn_decode_fused (RoPE on q and the new k, append of the new K/V row, slices, merge by the
+    last block) against RoPE + softmax(qK/sqrt(d))V in float64, two calls in a row on the same
+    buffers (the merge counters must come back to zero). The appended rows must be the bf16 of the
+    rotated k and of v. Tolerance 1e-5 absolute on outputs of magnitude <= 1."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    assert lib.lbk_attn_decode_fused_supported(nh, kvh, 128, splits)
+    b, hd, cap = 2, 128, max(total, 8)
+    g = torch.Generator().manual_seed(total + nh)
+    q = torch.randn(b, nh, hd, generator=g)
+    kn = torch.randn(b, kvh, hd, generator=g)
+    vn = torch.rand(b, kvh, hd, generator=g)
+    k = torch.randn(b, kvh, cap, hd, generator=g).bfloat16()
+    v = torch.rand(b, kvh, cap, hd, generator=g).bfloat16()
+    ang = torch.rand(cap, hd // 2, generator=g) * 6.0
+    cos = torch.cat([torch.cos(ang), torch.cos(ang)], dim=1).contiguous()
+    sin = torch.cat([torch.sin(ang), torch.sin(ang)], dim=1).contiguous()
+    pos = total - 1
+
+    def rope(x):  # model.rs:298-302
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        return x * cos[pos] + torch.cat([-x2, x1], dim=-1) * sin[pos]
+
+    qd, knd, vnd, kd, vd = q.cuda(), kn.cuda(), vn.cuda(), k.cuda(), v.cuda()
+    cd, sd, pd = cos.cuda(), sin.cuda(), torch.tensor([pos], dtype=torch.int32).cuda()
+    scratch = torch.empty(b * nh * splits * (hd + 4), device="cuda")
+    counters = torch.zeros(b * kvh, dtype=torch.int32, device="cuda")
+    out = torch.empty(b, nh * hd, device="cuda")
+    kref = k.clone(); vref = v.clone()
+    kref[:, :, pos] = rope(kn).bfloat16(); vref[:, :, pos] = vn.bfloat16()
+    kf, vf = kref.double().numpy()[:, :, :total], vref.double().numpy()[:, :, :total]
+    qf = rope(q).double().numpy()
+    for _ in range(2):
+        out.zero_()
+        _lib.check(lib.lbk_attn_decode_fused(ctx.handle, qd.data_ptr(), knd.data_ptr(), vnd.data_ptr(), cd.data_ptr(), sd.data_ptr(),
+                                             pd.data_ptr(), b, nh, kvh, hd, cap, splits, kd.data_ptr(), vd.data_ptr(),
+                                             scratch.data_ptr(), counters.data_ptr(), out.data_ptr(),
+                                             torch.cuda.current_stream().cuda_stream))
+        got = out.cpu().numpy().reshape(b, nh, hd)
+        assert int(counters.abs().sum()) == 0
+        assert torch.equal(kd.cpu()[:, :, pos], kref[:, :, pos]) and torch.equal(vd.cpu()[:, :, pos], vref[:, :, pos])
+        for h in range(nh):
+            s = np.einsum("bd,bpd->bp", qf[:, h], kf[:, h // (nh // kvh)]) / np.sqrt(hd)
+            w = np.exp(s - s.max(axis=1, keepdims=True))
+            w /= w.sum(axis=1, keepdims=True)
+            ref = np.einsum("bp,bpd->bd", w, vf[:, h // (nh // kvh)])
+            assert np.abs(got[:, h] - ref).max() < 1e-5
+    ctx.check_device_error()
