@@ -23,7 +23,73 @@ struct Plan {
     SweepTables *sweep = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
+    // lbk_plan_run_host pipelines the sweep against its own copies: the groups are cut into a few
+    // segments of about equal weight bytes, each with its own sweep tables; segment s computes while
+    // segment s+1's inputs come in and segment s-1's outputs go out (copy engines of both
+    // directions and the SMs all busy). Streams and events are created once, here.
+    struct Segment {
+        SweepTables *sweep = nullptr;
+        size_t x_off = 0, x_len = 0, y_off = 0, y_len = 0;  // in floats, inside the arenas
+        cudaEvent_t in_done = nullptr, compute_done = nullptr;
+    };
+    std::vector<Segment> segments;
+    cudaStream_t in_stream = nullptr, out_stream = nullptr;
+    cudaEvent_t start = nullptr, out_done = nullptr;
 };
+
+static void plan_free_segments(Plan *p) {
+    for (Plan::Segment &sg : p->segments) {
+        if (sg.sweep) sweep_free(sg.sweep);
+        if (sg.in_done) cudaEventDestroy(sg.in_done);
+        if (sg.compute_done) cudaEventDestroy(sg.compute_done);
+    }
+    p->segments.clear();
+    if (p->in_stream) cudaStreamDestroy(p->in_stream);
+    if (p->out_stream) cudaStreamDestroy(p->out_stream);
+    if (p->start) cudaEventDestroy(p->start);
+    if (p->out_done) cudaEventDestroy(p->out_done);
+    p->in_stream = p->out_stream = nullptr;
+    p->start = p->out_done = nullptr;
+}
+
+// Cuts an all-arena plan into segments for the pipelined host path. Failure of any step just
+// leaves the plan without segments (run_host then copies, runs and copies in sequence).
+static void plan_build_segments(Plan *p) {
+    const char *env = getenv("LBK_HOST_SEGMENTS");
+    int want = env ? atoi(env) : 3;
+    if (want < 2 || !p->sweep || p->arena_group.size() != p->groups.size() || p->groups.size() < static_cast<size_t>(2 * want)) return;
+    size_t total = 0;
+    for (const GroupArgs &g : p->groups)
+        for (int i = 0; i < g.n; ++i) total += g.w[i]->rows * g.w[i]->rb;
+    bool ok = cudaStreamCreateWithFlags(&p->in_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaStreamCreateWithFlags(&p->out_stream, cudaStreamNonBlocking) == cudaSuccess &&
+              cudaEventCreateWithFlags(&p->start, cudaEventDisableTiming) == cudaSuccess &&
+              cudaEventCreateWithFlags(&p->out_done, cudaEventDisableTiming) == cudaSuccess;
+    size_t gi = 0, x_off = 0, y_off = 0, bytes_done = 0;
+    for (int sidx = 0; sidx < want && ok; ++sidx) {
+        Plan::Segment sg;
+        sg.x_off = x_off;
+        sg.y_off = y_off;
+        std::vector<GroupArgs> sub;
+        const size_t target = total * (sidx + 1) / want;
+        while (gi < p->groups.size() && (bytes_done < target || sidx == want - 1)) {
+            const GroupArgs &g = p->groups[gi++];
+            sub.push_back(g);
+            sg.x_len += g.w[0]->cols;
+            for (int i = 0; i < g.n; ++i) {
+                sg.y_len += g.w[i]->rows;
+                bytes_done += g.w[i]->rows * g.w[i]->rb;
+            }
+        }
+        x_off += sg.x_len;
+        y_off += sg.y_len;
+        ok = !sub.empty() && sweep_build(p->ctx, sub, &sg.sweep) == LBK_OK && sg.sweep != nullptr &&
+             cudaEventCreateWithFlags(&sg.in_done, cudaEventDisableTiming) == cudaSuccess &&
+             cudaEventCreateWithFlags(&sg.compute_done, cudaEventDisableTiming) == cudaSuccess;
+        p->segments.push_back(sg);
+    }
+    if (!ok || gi != p->groups.size()) plan_free_segments(p);
+}
 
 int kernels_init(Ctx *ctx) {
     LBK_TRY(gemv_init(ctx));
@@ -127,6 +193,7 @@ int lbk_plan_finalize(lbk_plan *pl) {
         p->graph = graph;
         LBK_CUDA(cudaGraphInstantiate(&p->exec, graph, 0));
     }
+    plan_build_segments(p);
     p->finalized = true;
     return LBK_OK;
 }
@@ -154,6 +221,28 @@ int lbk_plan_run_host(lbk_plan *pl, const float *x_host, size_t x_len, float *y_
     if ((x_len && !x_host) || (y_len && !y_host)) return fail(LBK_ERR_INVALID, "host buffer is null");
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     LBK_CUDA(cudaSetDevice(p->ctx->device));
+    if (!p->segments.empty()) {
+        // inputs of every segment queue up on the inbound stream; a segment's sweep waits for its own
+        // inputs only, and its outputs leave on the outbound stream while the next segment computes
+        LBK_CUDA(cudaEventRecord(p->start, st));
+        LBK_CUDA(cudaStreamWaitEvent(p->in_stream, p->start, 0));
+        LBK_CUDA(cudaStreamWaitEvent(p->out_stream, p->start, 0));
+        for (Plan::Segment &sg : p->segments) {
+            LBK_CUDA(cudaMemcpyAsync(p->x_arena + sg.x_off, x_host + sg.x_off, sg.x_len * sizeof(float), cudaMemcpyHostToDevice, p->in_stream));
+            LBK_CUDA(cudaEventRecord(sg.in_done, p->in_stream));
+        }
+        for (Plan::Segment &sg : p->segments) {
+            LBK_CUDA(cudaStreamWaitEvent(st, sg.in_done, 0));
+            LBK_TRY(sweep_launch(p->ctx, sg.sweep, st));
+            LBK_CUDA(cudaEventRecord(sg.compute_done, st));
+            LBK_CUDA(cudaStreamWaitEvent(p->out_stream, sg.compute_done, 0));
+            LBK_CUDA(cudaMemcpyAsync(y_host + sg.y_off, p->y_arena + sg.y_off, sg.y_len * sizeof(float), cudaMemcpyDeviceToHost, p->out_stream));
+        }
+        LBK_CUDA(cudaEventRecord(p->out_done, p->out_stream));
+        LBK_CUDA(cudaStreamWaitEvent(st, p->out_done, 0));
+        LBK_CUDA(cudaStreamSynchronize(st));
+        return LBK_OK;
+    }
     if (x_len) LBK_CUDA(cudaMemcpyAsync(p->x_arena, x_host, x_len * sizeof(float), cudaMemcpyHostToDevice, st));
     LBK_TRY(lbk_plan_run(pl, stream));
     if (y_len) LBK_CUDA(cudaMemcpyAsync(y_host, p->y_arena, y_len * sizeof(float), cudaMemcpyDeviceToHost, st));
@@ -172,6 +261,7 @@ int lbk_plan_destroy(lbk_plan *pl) {
     if (!pl) return LBK_OK;
     Plan *p = reinterpret_cast<Plan *>(pl);
     if (p->sweep) sweep_free(p->sweep);
+    plan_free_segments(p);
     if (p->exec) cudaGraphExecDestroy(p->exec);
     if (p->graph) cudaGraphDestroy(p->graph);
     if (p->x_arena) cudaFree(p->x_arena);

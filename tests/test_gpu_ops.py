@@ -124,3 +124,37 @@ def test_plan_replays_groups(oracle, ctx):
         for o_, i_, ef, ei in zip(outs, iouts, wf, wi):
             assert np.array_equal(i_.cpu().numpy(), ei)
             assert np.array_equal(o_.cpu().numpy().view(np.uint32), ef.view(np.uint32))
+
+
+@pytest.mark.parametrize("n_groups", [2, 9])
+def test_plan_host_arenas(oracle, ctx, n_groups):
+    """lbk_plan_run_host: groups added without buffers live in the plan's arenas; one call copies the
+    inputs in, runs the plan and copies the outputs out. With nine groups the call is pipelined in
+    segments (inputs of one segment arrive while another computes); with two it is sequential. Both
+    against the oracle, twice with different inputs."""
+    import torch
+    from lemonade_burn_b200 import ops
+    plan = ops.Plan(ctx)
+    lins_all = []
+    for gi in range(n_groups):
+        cols = 512 if gi % 3 else 640
+        lins = [make_linear(oracle, rows, cols, 300 + gi * 5 + j, ctx, 30.0 + gi) for j, rows in enumerate([96, 40][: 1 + gi % 2])]
+        plan.add_arena([l for l, _, _ in lins])
+        lins_all.append((cols, lins))
+    plan.finalize()
+    nx, ny = plan.input_elems(), plan.output_elems()
+    assert nx == sum(c for c, _ in lins_all) and ny == sum(l.rows for _, lins in lins_all for l, _, _ in lins)
+    for rep in range(2):
+        x_host = torch.from_numpy(np.random.default_rng(rep).standard_normal(nx).astype(np.float32)).pin_memory()
+        y_host = torch.zeros(ny).pin_memory()
+        plan.run_host(x_host, y_host)
+        xo = yo = 0
+        for cols, lins in lins_all:
+            x = x_host.numpy()[xo:xo + cols][None, :]
+            xo += cols
+            q, s, ssum = oracle.quantize_acts(x)
+            wf = oracle.simd_gemm_multi([p for _, p, _ in lins], [w for _, _, w in lins], q, s, ssum)[0]
+            for (l, _, _), ef in zip(lins, wf):
+                assert np.array_equal(y_host.numpy()[yo:yo + l.rows].view(np.uint32), np.ascontiguousarray(ef).reshape(-1).view(np.uint32))
+                yo += l.rows
+    ctx.check_device_error()
