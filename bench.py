@@ -56,8 +56,8 @@ def algorithmic_bytes_per_sweep() -> int:
     return weight_bytes_per_sweep() + io
 
 
-# DRAM bytes one sweep moves, from the ncu capture summarised in
-# profiles/sweep_kernel_bitnet2b_decode_sweep.md (dram__bytes_read.sum + dram__bytes_write.sum).
+# DRAM bytes one sweep moves, from an ncu capture of this same workload (dram__bytes_read.sum +
+# dram__bytes_write.sum of one sweep_kernel launch; the summary is kept with the other profile notes).
 NCU_TRAFFIC_BYTES_PER_SWEEP = 532_251_904 + 5_107_712
 
 

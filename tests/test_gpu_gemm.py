@@ -1,6 +1,6 @@
 """Prefill path (more than 16 token rows -> tcgen05 int8 GEMM) against the oracle, through the
 C ABI. Integers bit-exact, f32 bit-exact (same epilogue order as gemm.rs:158,178), 1e-3 relative
-as the documented bound. Shapes follow BASELINE config 2 (K=2560->N=6912, K=6912->N=2560) plus
+as the documented bound. Shapes are the BitNet-2B projections (K=2560->N=6912, K=6912->N=2560) plus
 the reference's padded / token-tile / extreme cases (crates/lb-ternary/tests/golden.rs)."""
 import numpy as np
 import pytest
@@ -74,7 +74,7 @@ def test_code3_and_multi(oracle, ctx):
 
 @pytest.mark.parametrize("m", [1024, 2048])
 def test_full_size_properties(oracle, ctx, m):
-    """BASELINE config 2 at full token counts, checked through properties the oracle can afford:
+    """The BitNet-2B gate projection at full prefill token counts, checked through properties the oracle can afford:
     (a) first and last 64 weight rows against the oracle for every token, (b) sixteen sampled
     token rows, all weight rows, against the decode kernel (which is checked against the oracle
     elsewhere), (c) permuting token rows permutes the output rows."""
