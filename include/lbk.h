@@ -267,6 +267,40 @@ int lbk_argmax(lbk_ctx *ctx, const float *logits_dev, size_t rows, size_t n, int
 /* *pos_dev += 1 (cache.len = total, model.rs:367). */
 int lbk_advance_pos(lbk_ctx *ctx, int32_t *pos_dev, void *stream);
 
+/* ---- the decoder as a native runtime (crates/lb-model/src/model.rs) ----------------------------
+ * lbk_model_load      BitNet::load (model.rs:149-232): `dir/config.json` + `dir/model.lbt.safetensors`
+ *                     as lb-convert writes them; the format check and the supported family
+ *                     (relu2, tied embeddings) are the reference's; head_dim must be 128.
+ * lbk_model_new_cache BitNet::new_cache (model.rs:234-236): here bf16, of fixed capacity
+ *                     (0 = max_position_embeddings), for `batch` (1..16) independent sequences.
+ * lbk_model_forward   BitNet::forward (model.rs:305-374) for one sequence (cache of batch 1):
+ *                     appends `n` tokens at cache.len and writes the logits of every token
+ *                     ([n][vocab], all_logits != 0) or of the last one ([vocab]) to host memory.
+ *                     Several tokens are run through the decode step one after the other.
+ * lbk_model_decode    one new token for each of the cache's sequences: tokens_dev int32 [batch];
+ *                     logits_dev f32 [batch][vocab] and/or next_dev int32 [batch] (greedy argmax,
+ *                     sample.rs:17-25) may be null. Asynchronous on `stream`.
+ * A step is recorded into a CUDA graph at a cache's first use and replayed afterwards. */
+typedef struct lbk_model lbk_model;
+typedef struct lbk_kv_cache lbk_kv_cache;
+typedef struct lbk_model_config {
+    size_t hidden_size, intermediate_size, num_attention_heads, num_key_value_heads, num_hidden_layers, vocab_size,
+        max_position_embeddings;
+    float rms_norm_eps, rope_theta;
+    int bos_token_id;
+} lbk_model_config;
+int lbk_model_load(lbk_ctx *ctx, const char *directory, lbk_model **out);
+int lbk_model_get_config(const lbk_model *model, lbk_model_config *out);
+int lbk_model_free(lbk_model *model);
+int lbk_model_new_cache(lbk_model *model, size_t batch, size_t capacity, lbk_kv_cache **out);
+size_t lbk_kv_cache_len(const lbk_kv_cache *cache);
+int lbk_kv_cache_reset(lbk_kv_cache *cache);
+int lbk_kv_cache_free(lbk_kv_cache *cache);
+int lbk_model_forward(lbk_model *model, lbk_kv_cache *cache, const uint32_t *tokens, size_t n, int all_logits,
+                      float *logits_out);
+int lbk_model_decode(lbk_model *model, lbk_kv_cache *cache, const int32_t *tokens_dev, float *logits_dev,
+                     int32_t *next_dev, void *stream);
+
 /* ---- plans: a whole decode-like sequence in one launch -----------------------------------
  * The reference runs 4 fused ternary ops per layer x 30 layers = 120 parallel regions per
  * token (crates/lb-ternary/benches/kbench.rs:148-194, crates/lb-model/src/model.rs:331-366).

@@ -73,6 +73,15 @@ SYMBOLS = [
     ("lbk_tp_partial_buffer", _vp, [_vp]),
     ("lbk_tp_quantize", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     ("lbk_tp_reduce_scale", _i, [_vp, _vp, _f, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_model_load", _i, [_vp, C.c_char_p, _pp]),
+    ("lbk_model_get_config", _i, [_vp, _vp]),
+    ("lbk_model_free", _i, [_vp]),
+    ("lbk_model_new_cache", _i, [_vp, _sz, _sz, _pp]),
+    ("lbk_kv_cache_len", _sz, [_vp]),
+    ("lbk_kv_cache_reset", _i, [_vp]),
+    ("lbk_kv_cache_free", _i, [_vp]),
+    ("lbk_model_forward", _i, [_vp, _vp, _vp, _sz, _i, _vp]),
+    ("lbk_model_decode", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),
     ("lbk_plan_finalize", _i, [_vp]),

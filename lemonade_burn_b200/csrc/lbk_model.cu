@@ -1,0 +1,643 @@
+// The BitNet b1.58 decoder as a native runtime behind the C ABI: checkpoint loader, KV cache and the
+// decode step, for hosts that want lb-model's `BitNet::{load, new_cache, forward}`
+// (crates/lb-model/src/model.rs:149-232, 234-236, 305-374) without a tensor framework in between.
+//
+// Checkpoint: `config.json` + `model.lbt.safetensors` exactly as lb-convert writes them
+// (crates/lb-convert/src/lib.rs:14-26: metadata format "lemonade-burn-ternary"; per linear
+// `<name>.qweight` U8 [rows, padded(cols)/4] and `<name>.wscale` F32 [1]; norm gains F32; the tied
+// embedding / LM head BF16). The packed weights go to the GPU as they are.
+//
+// Differences from the reference, all deliberate: the KV cache is bf16 with a fixed capacity
+// (the reference grows an f32 cache, model.rs:245); a call with several tokens of one sequence
+// (prompt ingestion) runs them through the decode step one after the other, which is the same
+// causal computation as the reference's batched prefill; several independent sequences can
+// advance together (lbk_model_decode), which the reference cannot do. One step is recorded into a
+// CUDA graph the first time a cache is used and replayed afterwards (the position lives in
+// device memory).
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "lbk_internal.cuh"
+
+namespace lbk {
+
+namespace {
+
+// ---- a small JSON reader (objects, arrays, strings, numbers, true/false/null) -----------------
+struct Json {
+    enum Kind { Null, Bool, Num, Str, Arr, Obj } kind = Null;
+    bool b = false;
+    double num = 0.0;
+    std::string str;
+    std::vector<Json> arr;
+    std::vector<std::pair<std::string, Json>> obj;
+    const Json *get(const char *key) const {
+        for (const auto &kv : obj)
+            if (kv.first == key) return &kv.second;
+        return nullptr;
+    }
+};
+
+struct JsonParser {
+    const char *p, *end;
+    bool ok = true;
+    void ws() {
+        while (p < end && (*p == ' ' || *p == '\n' || *p == '\t' || *p == '\r')) ++p;
+    }
+    bool lit(const char *s) {
+        const size_t n = strlen(s);
+        if (static_cast<size_t>(end - p) >= n && memcmp(p, s, n) == 0) {
+            p += n;
+            return true;
+        }
+        return false;
+    }
+    std::string string() {
+        std::string out;
+        if (p >= end || *p != '"') {
+            ok = false;
+            return out;
+        }
+        ++p;
+        while (p < end && *p != '"') {
+            if (*p == '\\' && p + 1 < end) {
+                ++p;
+                switch (*p) {
+                    case 'n': out += '\n'; break;
+                    case 't': out += '\t'; break;
+                    case 'r': out += '\r'; break;
+                    case 'b': out += '\b'; break;
+                    case 'f': out += '\f'; break;
+                    case 'u':  // keep the escape as text: tensor names and the fields read here are ASCII
+                        out += "\\u";
+                        break;
+                    default: out += *p;
+                }
+                ++p;
+            } else {
+                out += *p++;
+            }
+        }
+        if (p >= end) ok = false;
+        else ++p;
+        return out;
+    }
+    Json value(int depth = 0) {
+        Json j;
+        ws();
+        if (p >= end || depth > 64) {
+            ok = false;
+            return j;
+        }
+        if (*p == '{') {
+            j.kind = Json::Obj;
+            ++p;
+            ws();
+            if (p < end && *p == '}') {
+                ++p;
+                return j;
+            }
+            while (ok) {
+                ws();
+                std::string key = string();
+                ws();
+                if (!ok || p >= end || *p != ':') {
+                    ok = false;
+                    break;
+                }
+                ++p;
+                j.obj.emplace_back(std::move(key), value(depth + 1));
+                ws();
+                if (p < end && *p == ',') {
+                    ++p;
+                    continue;
+                }
+                if (p < end && *p == '}') {
+                    ++p;
+                    break;
+                }
+                ok = false;
+            }
+        } else if (*p == '[') {
+            j.kind = Json::Arr;
+            ++p;
+            ws();
+            if (p < end && *p == ']') {
+                ++p;
+                return j;
+            }
+            while (ok) {
+                j.arr.push_back(value(depth + 1));
+                ws();
+                if (p < end && *p == ',') {
+                    ++p;
+                    continue;
+                }
+                if (p < end && *p == ']') {
+                    ++p;
+                    break;
+                }
+                ok = false;
+            }
+        } else if (*p == '"') {
+            j.kind = Json::Str;
+            j.str = string();
+        } else if (lit("true")) {
+            j.kind = Json::Bool;
+            j.b = true;
+        } else if (lit("false")) {
+            j.kind = Json::Bool;
+        } else if (lit("null")) {
+            j.kind = Json::Null;
+        } else {
+            char *e = nullptr;
+            j.kind = Json::Num;
+            j.num = strtod(p, &e);
+            if (e == p || e > end) ok = false;
+            else p = e;
+        }
+        return j;
+    }
+};
+
+bool parse_json(const std::string &text, Json &out) {
+    JsonParser ps{text.data(), text.data() + text.size()};
+    out = ps.value();
+    ps.ws();
+    return ps.ok && ps.p == ps.end;
+}
+
+bool read_file(const std::string &path, std::string &out) {
+    FILE *f = fopen(path.c_str(), "rb");
+    if (!f) return false;
+    std::string data;
+    char buf[1 << 16];
+    size_t n;
+    while ((n = fread(buf, 1, sizeof(buf), f)) > 0) data.append(buf, n);
+    fclose(f);
+    out.swap(data);
+    return true;
+}
+
+struct TensorEntry {
+    std::string dtype;
+    std::vector<size_t> shape;
+    size_t begin = 0, end = 0;  // byte range inside the data section
+};
+
+}  // namespace
+
+struct Model {
+    Ctx *ctx = nullptr;
+    lbk_model_config cfg{};
+    size_t head_dim = 0;
+    struct Layer {
+        lbk_weight *q = nullptr, *k = nullptr, *v = nullptr, *o = nullptr, *gate = nullptr, *up = nullptr, *down = nullptr;
+        float *input_norm = nullptr, *post_attn_norm = nullptr, *attn_sub_norm = nullptr, *ffn_sub_norm = nullptr;
+    };
+    std::vector<Layer> layers;
+    float *final_norm = nullptr;
+    uint16_t *embed = nullptr;  // bf16 [vocab][hidden], also the LM head (tied)
+    float *cos = nullptr, *sin = nullptr;
+    std::vector<void *> device_allocs;
+    std::vector<lbk_weight *> weights;
+};
+
+struct Cache {
+    Model *model = nullptr;
+    size_t b = 0, cap = 0, splits = 1;
+    uint16_t *k = nullptr, *v = nullptr;  // [layers][b][kv_heads][cap][head_dim]
+    int32_t *pos = nullptr;               // cache length, on the device
+    size_t len = 0;                       // the same, on the host
+    // work buffers of one step
+    int32_t *tokens = nullptr, *next = nullptr, *counters = nullptr;
+    float *x = nullptr, *x2 = nullptr, *n = nullptr, *q = nullptr, *kk = nullptr, *vv = nullptr, *attn = nullptr, *o = nullptr, *g = nullptr,
+          *u = nullptr, *d = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr;
+    cudaGraphExec_t step = nullptr;
+    std::vector<void *> device_allocs;
+};
+
+namespace {
+
+int dev_alloc(std::vector<void *> &owner, size_t bytes, void **out) {
+    void *p = nullptr;
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 16);
+    if (e != cudaSuccess) return fail(LBK_ERR_NOMEM, "cudaMalloc(%zu) failed: %s", bytes, cudaGetErrorString(e));
+    owner.push_back(p);
+    *out = p;
+    return LBK_OK;
+}
+
+// model.rs:213-230: inv_freq in f32, angle = pos as f32 * inv_freq (f32), sin/cos evaluated in f64,
+// stored as f32, the 64 values repeated for both halves of the head.
+void rope_tables(const lbk_model_config &c, size_t hd, std::vector<float> &cs, std::vector<float> &sn) {
+    const size_t half = hd / 2, np = c.max_position_embeddings;
+    cs.resize(np * hd);
+    sn.resize(np * hd);
+    std::vector<float> inv(half);
+    for (size_t i = 0; i < half; ++i) inv[i] = static_cast<float>(1.0 / std::pow(static_cast<double>(c.rope_theta), (2.0 * i) / hd));
+    for (size_t p = 0; p < np; ++p)
+        for (size_t i = 0; i < half; ++i) {
+            const float ang = static_cast<float>(p) * inv[i];
+            const float cv = static_cast<float>(std::cos(static_cast<double>(ang))), sv = static_cast<float>(std::sin(static_cast<double>(ang)));
+            cs[p * hd + i] = cs[p * hd + half + i] = cv;
+            sn[p * hd + i] = sn[p * hd + half + i] = sv;
+        }
+}
+
+size_t json_size(const Json *j, bool &ok) {
+    if (!j || j->kind != Json::Num || j->num < 0) {
+        ok = false;
+        return 0;
+    }
+    return static_cast<size_t>(j->num);
+}
+
+// One decode step for cache->b sequences: the C++ twin of the Python mirror's BitNet.forward.
+int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
+    lbk_ctx *h = reinterpret_cast<lbk_ctx *>(m->ctx);
+    const lbk_model_config &cfg = m->cfg;
+    const size_t b = c->b, H = cfg.hidden_size, I = cfg.intermediate_size, nh = cfg.num_attention_heads, kvh = cfg.num_key_value_heads,
+                 hd = m->head_dim, L = cfg.num_hidden_layers;
+    const float eps = cfg.rms_norm_eps;
+    const bool pre_h = lbk_ternary_linear_pre_supported(b, H), pre_a = lbk_ternary_linear_pre_supported(b, nh * hd),
+               pre_i = lbk_ternary_linear_pre_supported(b, I);
+    const bool fused_norms = H % 4 == 0 && H <= 8192 && I % 4 == 0 && I <= 8192;
+    const bool attn_fused = lbk_attn_decode_fused_supported(nh, kvh, hd, c->splits) != 0;
+    const size_t layer_kv = b * kvh * c->cap * hd;
+    float *x = c->x, *x2 = c->x2;
+    auto add_norm = [&](float *xin, const float *y, const float *w) -> int {  // xin += y; n = rms_norm(xin) * w
+        if (fused_norms) return lbk_add_rms_norm(h, xin, y, w, b, H, eps, c->n, st);
+        LBK_TRY(lbk_add_inplace(h, xin, y, b * H, st));
+        return lbk_rms_norm(h, xin, w, b, H, eps, c->n, st);
+    };
+    LBK_TRY(lbk_embed_bf16(h, m->embed, c->tokens, b, H, x, st));
+    bool have_d = false;  // c->d holds the previous layer's down projection, not yet added to x
+    for (size_t li = 0; li < L; ++li) {
+        const Model::Layer &l = m->layers[li];
+        const lbk_weight *qkv[3] = {l.q, l.k, l.v};
+        float *qkv_out[3] = {c->q, c->kk, c->vv};
+        if (!have_d) {
+            if (pre_h) {
+                LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_RMS, x, nullptr, l.input_norm, eps, nullptr, b, qkv, 3, qkv_out, nullptr, st));
+            } else {
+                LBK_TRY(lbk_rms_norm(h, x, l.input_norm, b, H, eps, c->n, st));
+                LBK_TRY(lbk_ternary_linear_n(h, c->n, b, qkv, 3, qkv_out, nullptr, st));
+            }
+        } else if (pre_h) {
+            LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_ADD_RMS, x, c->d, l.input_norm, eps, x2, b, qkv, 3, qkv_out, nullptr, st));
+            std::swap(x, x2);
+        } else {
+            LBK_TRY(add_norm(x, c->d, l.input_norm));
+            LBK_TRY(lbk_ternary_linear_n(h, c->n, b, qkv, 3, qkv_out, nullptr, st));
+        }
+        uint16_t *kc = c->k + li * layer_kv, *vc = c->v + li * layer_kv;
+        if (attn_fused) {
+            LBK_TRY(lbk_attn_decode_fused(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, c->splits, kc, vc, c->scratch,
+                                          c->counters, c->attn, st));
+        } else {
+            LBK_TRY(lbk_rope_kv_append(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, kc, vc, st));
+            LBK_TRY(lbk_attn_decode(h, c->q, kc, vc, c->pos, b, nh, kvh, hd, c->cap, c->splits, c->scratch, c->attn, st));
+        }
+        const lbk_weight *ow[1] = {l.o};
+        float *oo[1] = {c->o};
+        if (pre_a) {
+            LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_RMS, c->attn, nullptr, l.attn_sub_norm, eps, nullptr, b, ow, 1, oo, nullptr, st));
+        } else {
+            LBK_TRY(lbk_rms_norm(h, c->attn, l.attn_sub_norm, b, nh * hd, eps, c->attn, st));
+            LBK_TRY(lbk_ternary_linear_n(h, c->attn, b, ow, 1, oo, nullptr, st));
+        }
+        const lbk_weight *gu[2] = {l.gate, l.up};
+        float *guo[2] = {c->g, c->u};
+        if (pre_h) {
+            LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_ADD_RMS, x, c->o, l.post_attn_norm, eps, x2, b, gu, 2, guo, nullptr, st));
+            std::swap(x, x2);
+        } else {
+            LBK_TRY(add_norm(x, c->o, l.post_attn_norm));
+            LBK_TRY(lbk_ternary_linear_n(h, c->n, b, gu, 2, guo, nullptr, st));
+        }
+        const lbk_weight *dw[1] = {l.down};
+        float *dout[1] = {c->d};
+        if (pre_i) {
+            LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_RELU2_MUL_RMS, c->g, c->u, l.ffn_sub_norm, eps, nullptr, b, dw, 1, dout, nullptr, st));
+        } else {
+            if (fused_norms) {
+                LBK_TRY(lbk_relu2_mul_rms_norm(h, c->g, c->u, l.ffn_sub_norm, b, I, eps, c->act, st));
+            } else {
+                LBK_TRY(lbk_relu2_mul(h, c->g, c->u, b * I, c->act, st));
+                LBK_TRY(lbk_rms_norm(h, c->act, l.ffn_sub_norm, b, I, eps, c->act, st));
+            }
+            LBK_TRY(lbk_ternary_linear_n(h, c->act, b, dw, 1, dout, nullptr, st));
+        }
+        have_d = true;
+    }
+    if (have_d) LBK_TRY(add_norm(x, c->d, m->final_norm));
+    else LBK_TRY(lbk_rms_norm(h, x, m->final_norm, b, H, eps, c->n, st));
+    LBK_TRY(lbk_bf16_linear(h, c->n, b, m->embed, cfg.vocab_size, H, c->logits, st));
+    LBK_TRY(lbk_argmax(h, c->logits, b, cfg.vocab_size, c->next, st));  // sample.rs:17-25
+    LBK_TRY(lbk_advance_pos(h, c->pos, st));
+    return LBK_OK;
+}
+
+// Records the step into a graph on the context's own stream (a few eager steps first: the library's
+// scratch buffers must exist before anything is captured; those steps run on a scratch position).
+int ensure_graph(Model *m, Cache *c) {
+    if (c->step) return LBK_OK;
+    Ctx *ctx = m->ctx;
+    cudaStream_t st = ctx->own_stream;
+    int32_t saved = 0;
+    LBK_CUDA(cudaMemcpy(&saved, c->pos, sizeof(saved), cudaMemcpyDeviceToHost));
+    LBK_TRY(enqueue_step(m, c, st));  // eager warm-up: writes the K/V row of position `saved`, which the real step rewrites
+    LBK_CUDA(cudaStreamSynchronize(st));
+    LBK_CUDA(cudaMemcpy(c->pos, &saved, sizeof(saved), cudaMemcpyHostToDevice));
+    const uint64_t before = ctx->launches;
+    LBK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    const int status = enqueue_step(m, c, st);
+    cudaGraph_t graph = nullptr;
+    const cudaError_t e = cudaStreamEndCapture(st, &graph);
+    ctx->launches = before;  // recording is not launching
+    if (status != LBK_OK) {
+        if (graph) cudaGraphDestroy(graph);
+        return status;
+    }
+    if (e != cudaSuccess) return fail(LBK_ERR_CUDA, "capture of the decode step failed: %s", cudaGetErrorString(e));
+    const cudaError_t ei = cudaGraphInstantiate(&c->step, graph, 0);
+    cudaGraphDestroy(graph);
+    if (ei != cudaSuccess) return fail(LBK_ERR_CUDA, "cudaGraphInstantiate: %s", cudaGetErrorString(ei));
+    return LBK_OK;
+}
+
+}  // namespace
+
+}  // namespace lbk
+
+using namespace lbk;
+
+extern "C" {
+
+int lbk_model_free(lbk_model *mp) {
+    if (!mp) return LBK_OK;
+    Model *m = reinterpret_cast<Model *>(mp);
+    cudaSetDevice(m->ctx->device);
+    cudaDeviceSynchronize();
+    for (lbk_weight *w : m->weights) lbk_weight_free(w);
+    for (void *p : m->device_allocs) cudaFree(p);
+    delete m;
+    return LBK_OK;
+}
+
+int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
+    if (!c || !directory || !out) return fail(LBK_ERR_INVALID, "lbk_model_load: null argument");
+    *out = nullptr;
+    Ctx *ctx = reinterpret_cast<Ctx *>(c);
+    LBK_CUDA(cudaSetDevice(ctx->device));
+    const std::string dir(directory);
+    std::string text;
+    if (!read_file(dir + "/config.json", text)) return fail(LBK_ERR_INVALID, "cannot read %s/config.json", directory);
+    Json cj;
+    if (!parse_json(text, cj) || cj.kind != Json::Obj) return fail(LBK_ERR_INVALID, "%s/config.json is not a JSON object", directory);
+    std::unique_ptr<Model, int (*)(Model *)> model(new Model(), [](Model *m) { return lbk_model_free(reinterpret_cast<lbk_model *>(m)); });
+    Model *m = model.get();
+    m->ctx = ctx;
+    bool ok = true;
+    lbk_model_config &cfg = m->cfg;
+    cfg.hidden_size = json_size(cj.get("hidden_size"), ok);
+    cfg.intermediate_size = json_size(cj.get("intermediate_size"), ok);
+    cfg.num_attention_heads = json_size(cj.get("num_attention_heads"), ok);
+    cfg.num_key_value_heads = json_size(cj.get("num_key_value_heads"), ok);
+    cfg.num_hidden_layers = json_size(cj.get("num_hidden_layers"), ok);
+    cfg.vocab_size = json_size(cj.get("vocab_size"), ok);
+    cfg.max_position_embeddings = json_size(cj.get("max_position_embeddings"), ok);
+    const Json *je = cj.get("rms_norm_eps"), *jt = cj.get("rope_theta");
+    if (!je || je->kind != Json::Num || !jt || jt->kind != Json::Num) ok = false;
+    if (!ok) return fail(LBK_ERR_INVALID, "%s/config.json: a required field is missing or not a number", directory);
+    cfg.rms_norm_eps = static_cast<float>(je->num);
+    cfg.rope_theta = static_cast<float>(jt->num);
+    const Json *jb = cj.get("bos_token_id");
+    cfg.bos_token_id = jb && jb->kind == Json::Num ? static_cast<int>(jb->num) : 0;
+    // model.rs:151-153: only the relu2, tied-embedding family
+    const Json *ja = cj.get("hidden_act"), *jtie = cj.get("tie_word_embeddings");
+    if (ja && !(ja->kind == Json::Str && ja->str == "relu2")) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: hidden_act must be relu2");
+    if (jtie && !(jtie->kind == Json::Bool && jtie->b)) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: tie_word_embeddings must be true");
+    if (!cfg.num_attention_heads || !cfg.num_key_value_heads || cfg.hidden_size % cfg.num_attention_heads ||
+        cfg.num_attention_heads % cfg.num_key_value_heads || !cfg.num_hidden_layers || !cfg.max_position_embeddings)
+        return fail(LBK_ERR_INVALID, "config.json: inconsistent head counts or sizes");
+    m->head_dim = cfg.hidden_size / cfg.num_attention_heads;
+    if (m->head_dim != 128) return fail(LBK_ERR_UNSUPPORTED, "the attention kernels are built for head_dim 128, this model has %zu", m->head_dim);
+
+    // ---- model.lbt.safetensors: u64 header length, JSON header, data -------------------------
+    const std::string path = dir + "/model.lbt.safetensors";
+    FILE *f = fopen(path.c_str(), "rb");
+    if (!f) return fail(LBK_ERR_INVALID, "cannot open %s", path.c_str());
+    std::unique_ptr<FILE, int (*)(FILE *)> closer(f, fclose);
+    unsigned char lenb[8];
+    if (fread(lenb, 1, 8, f) != 8) return fail(LBK_ERR_INVALID, "%s: truncated", path.c_str());
+    uint64_t hlen = 0;
+    for (int i = 7; i >= 0; --i) hlen = (hlen << 8) | lenb[i];
+    if (hlen == 0 || hlen > (100u << 20)) return fail(LBK_ERR_INVALID, "%s: implausible header length %llu", path.c_str(), static_cast<unsigned long long>(hlen));
+    std::string header(hlen, '\0');
+    if (fread(&header[0], 1, hlen, f) != hlen) return fail(LBK_ERR_INVALID, "%s: truncated header", path.c_str());
+    Json hj;
+    if (!parse_json(header, hj) || hj.kind != Json::Obj) return fail(LBK_ERR_INVALID, "%s: header is not a JSON object", path.c_str());
+    const Json *meta = hj.get("__metadata__");
+    const Json *fmt = meta ? meta->get("format") : nullptr;
+    if (!fmt || fmt->kind != Json::Str || fmt->str != "lemonade-burn-ternary")  // model.rs:158-161
+        return fail(LBK_ERR_INVALID, "%s is not a lemonade-burn ternary file (format=%s)", path.c_str(), fmt && fmt->kind == Json::Str ? fmt->str.c_str() : "none");
+    std::map<std::string, TensorEntry> entries;
+    for (const auto &kv : hj.obj) {
+        if (kv.first == "__metadata__") continue;
+        const Json &t = kv.second;
+        const Json *dt = t.get("dtype"), *sh = t.get("shape"), *off = t.get("data_offsets");
+        if (!dt || dt->kind != Json::Str || !sh || sh->kind != Json::Arr || !off || off->kind != Json::Arr || off->arr.size() != 2)
+            return fail(LBK_ERR_INVALID, "%s: malformed entry %s", path.c_str(), kv.first.c_str());
+        TensorEntry e;
+        e.dtype = dt->str;
+        for (const Json &d : sh->arr) e.shape.push_back(static_cast<size_t>(d.num));
+        e.begin = static_cast<size_t>(off->arr[0].num);
+        e.end = static_cast<size_t>(off->arr[1].num);
+        if (e.end < e.begin) return fail(LBK_ERR_INVALID, "%s: malformed offsets of %s", path.c_str(), kv.first.c_str());
+        entries[kv.first] = e;
+    }
+    const long data0 = static_cast<long>(8 + hlen);
+    std::vector<unsigned char> staging;
+    auto read_tensor = [&](const std::string &name, const char *dtype, size_t elems, size_t elem_bytes) -> int {
+        auto it = entries.find(name);
+        if (it == entries.end()) return fail(LBK_ERR_INVALID, "%s: tensor %s is missing", path.c_str(), name.c_str());
+        const TensorEntry &e = it->second;
+        size_t n = 1;
+        for (size_t d : e.shape) n *= d;
+        if (e.dtype != dtype || n != elems || e.end - e.begin != elems * elem_bytes)
+            return fail(LBK_ERR_SHAPE, "%s: %s has dtype %s and %zu elements, expected %s and %zu", path.c_str(), name.c_str(), e.dtype.c_str(), n, dtype, elems);
+        staging.resize(elems * elem_bytes);
+        if (fseek(f, data0 + static_cast<long>(e.begin), SEEK_SET) != 0 || fread(staging.data(), 1, staging.size(), f) != staging.size())
+            return fail(LBK_ERR_INVALID, "%s: cannot read %s", path.c_str(), name.c_str());
+        return LBK_OK;
+    };
+    auto load_vec = [&](const std::string &name, size_t elems, float **dst) -> int {  // model.rs:165: norm gains are F32
+        LBK_TRY(read_tensor(name, "F32", elems, 4));
+        LBK_TRY(dev_alloc(m->device_allocs, elems * 4, reinterpret_cast<void **>(dst)));
+        LBK_CUDA(cudaMemcpy(*dst, staging.data(), elems * 4, cudaMemcpyHostToDevice));
+        return LBK_OK;
+    };
+    auto load_linear = [&](const std::string &name, size_t rows, size_t cols, lbk_weight **dst) -> int {
+        LBK_TRY(read_tensor(name + ".wscale", "F32", 1, 4));
+        float scale;
+        memcpy(&scale, staging.data(), 4);
+        LBK_TRY(read_tensor(name + ".qweight", "U8", rows * lbk_row_bytes(cols), 1));
+        LBK_TRY(lbk_weight_upload(c, rows, cols, staging.data(), staging.size(), scale, dst));
+        m->weights.push_back(*dst);
+        return LBK_OK;
+    };
+    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, hd = m->head_dim;
+    m->layers.resize(cfg.num_hidden_layers);
+    for (size_t i = 0; i < cfg.num_hidden_layers; ++i) {
+        const std::string p = "model.layers." + std::to_string(i);
+        Model::Layer &l = m->layers[i];
+        LBK_TRY(load_vec(p + ".input_layernorm.weight", H, &l.input_norm));
+        LBK_TRY(load_vec(p + ".post_attention_layernorm.weight", H, &l.post_attn_norm));
+        LBK_TRY(load_vec(p + ".self_attn.attn_sub_norm.weight", H, &l.attn_sub_norm));
+        LBK_TRY(load_vec(p + ".mlp.ffn_sub_norm.weight", I, &l.ffn_sub_norm));
+        LBK_TRY(load_linear(p + ".self_attn.q_proj", cfg.num_attention_heads * hd, H, &l.q));
+        LBK_TRY(load_linear(p + ".self_attn.k_proj", cfg.num_key_value_heads * hd, H, &l.k));
+        LBK_TRY(load_linear(p + ".self_attn.v_proj", cfg.num_key_value_heads * hd, H, &l.v));
+        LBK_TRY(load_linear(p + ".self_attn.o_proj", H, cfg.num_attention_heads * hd, &l.o));
+        LBK_TRY(load_linear(p + ".mlp.gate_proj", I, H, &l.gate));
+        LBK_TRY(load_linear(p + ".mlp.up_proj", I, H, &l.up));
+        LBK_TRY(load_linear(p + ".mlp.down_proj", H, I, &l.down));
+    }
+    LBK_TRY(load_vec("model.norm.weight", H, &m->final_norm));
+    LBK_TRY(read_tensor("model.embed_tokens.weight", "BF16", cfg.vocab_size * H, 2));  // model.rs:204
+    LBK_TRY(dev_alloc(m->device_allocs, staging.size(), reinterpret_cast<void **>(&m->embed)));
+    LBK_CUDA(cudaMemcpy(m->embed, staging.data(), staging.size(), cudaMemcpyHostToDevice));
+    std::vector<float> cs, sn;
+    rope_tables(cfg, hd, cs, sn);
+    LBK_TRY(dev_alloc(m->device_allocs, cs.size() * 4, reinterpret_cast<void **>(&m->cos)));
+    LBK_TRY(dev_alloc(m->device_allocs, sn.size() * 4, reinterpret_cast<void **>(&m->sin)));
+    LBK_CUDA(cudaMemcpy(m->cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpy(m->sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    *out = reinterpret_cast<lbk_model *>(model.release());
+    return LBK_OK;
+}
+
+int lbk_model_get_config(const lbk_model *mp, lbk_model_config *out) {
+    if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_model_get_config: null argument");
+    *out = reinterpret_cast<const Model *>(mp)->cfg;
+    return LBK_OK;
+}
+
+int lbk_kv_cache_free(lbk_kv_cache *cp) {
+    if (!cp) return LBK_OK;
+    Cache *c = reinterpret_cast<Cache *>(cp);
+    cudaSetDevice(c->model->ctx->device);
+    cudaDeviceSynchronize();
+    if (c->step) cudaGraphExecDestroy(c->step);
+    for (void *p : c->device_allocs) cudaFree(p);
+    delete c;
+    return LBK_OK;
+}
+
+int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cache **out) {
+    if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_model_new_cache: null argument");
+    *out = nullptr;
+    Model *m = reinterpret_cast<Model *>(mp);
+    if (batch == 0 || batch > LBK_GEMV_MAX_M) return fail(LBK_ERR_UNSUPPORTED, "a cache serves 1..%d sequences (got %zu)", LBK_GEMV_MAX_M, batch);
+    if (capacity == 0) capacity = m->cfg.max_position_embeddings;
+    if (capacity > m->cfg.max_position_embeddings) return fail(LBK_ERR_INVALID, "capacity %zu exceeds max_position_embeddings %zu", capacity, m->cfg.max_position_embeddings);
+    LBK_CUDA(cudaSetDevice(m->ctx->device));
+    std::unique_ptr<Cache, int (*)(Cache *)> cache(new Cache(), [](Cache *c) { return lbk_kv_cache_free(reinterpret_cast<lbk_kv_cache *>(c)); });
+    Cache *c = cache.get();
+    c->model = m;
+    c->b = batch;
+    c->cap = capacity;
+    const lbk_model_config &cfg = m->cfg;
+    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, nh = cfg.num_attention_heads, kvh = cfg.num_key_value_heads, hd = m->head_dim;
+    c->splits = (capacity + 31) / 32;  // 32 positions per attention slice
+    if (c->splits > 256) c->splits = 256;
+    const size_t kv_elems = cfg.num_hidden_layers * batch * kvh * capacity * hd;
+    LBK_TRY(dev_alloc(c->device_allocs, kv_elems * 2, reinterpret_cast<void **>(&c->k)));
+    LBK_TRY(dev_alloc(c->device_allocs, kv_elems * 2, reinterpret_cast<void **>(&c->v)));
+    LBK_CUDA(cudaMemset(c->k, 0, kv_elems * 2));
+    LBK_CUDA(cudaMemset(c->v, 0, kv_elems * 2));
+    struct { void **p; size_t bytes; } bufs[] = {
+        {reinterpret_cast<void **>(&c->pos), 4}, {reinterpret_cast<void **>(&c->tokens), batch * 4}, {reinterpret_cast<void **>(&c->next), batch * 4},
+        {reinterpret_cast<void **>(&c->counters), batch * kvh * 4}, {reinterpret_cast<void **>(&c->x), batch * H * 4},
+        {reinterpret_cast<void **>(&c->x2), batch * H * 4}, {reinterpret_cast<void **>(&c->n), batch * H * 4},
+        {reinterpret_cast<void **>(&c->q), batch * nh * hd * 4}, {reinterpret_cast<void **>(&c->kk), batch * kvh * hd * 4},
+        {reinterpret_cast<void **>(&c->vv), batch * kvh * hd * 4}, {reinterpret_cast<void **>(&c->attn), batch * nh * hd * 4},
+        {reinterpret_cast<void **>(&c->o), batch * H * 4}, {reinterpret_cast<void **>(&c->g), batch * I * 4}, {reinterpret_cast<void **>(&c->u), batch * I * 4},
+        {reinterpret_cast<void **>(&c->d), batch * H * 4}, {reinterpret_cast<void **>(&c->act), batch * I * 4},
+        {reinterpret_cast<void **>(&c->logits), batch * cfg.vocab_size * 4}, {reinterpret_cast<void **>(&c->scratch), batch * nh * c->splits * (hd + 4) * 4}};
+    for (auto &bf : bufs) {
+        LBK_TRY(dev_alloc(c->device_allocs, bf.bytes, bf.p));
+        LBK_CUDA(cudaMemset(*bf.p, 0, bf.bytes));
+    }
+    *out = reinterpret_cast<lbk_kv_cache *>(cache.release());
+    return LBK_OK;
+}
+
+size_t lbk_kv_cache_len(const lbk_kv_cache *cp) { return cp ? reinterpret_cast<const Cache *>(cp)->len : 0; }
+
+int lbk_kv_cache_reset(lbk_kv_cache *cp) {
+    if (!cp) return fail(LBK_ERR_INVALID, "cache is null");
+    Cache *c = reinterpret_cast<Cache *>(cp);
+    LBK_CUDA(cudaSetDevice(c->model->ctx->device));
+    LBK_CUDA(cudaDeviceSynchronize());
+    LBK_CUDA(cudaMemset(c->pos, 0, 4));
+    c->len = 0;
+    return LBK_OK;
+}
+
+int lbk_model_decode(lbk_model *mp, lbk_kv_cache *cp, const int32_t *tokens_dev, float *logits_dev, int32_t *next_dev, void *stream) {
+    if (!mp || !cp || !tokens_dev) return fail(LBK_ERR_INVALID, "lbk_model_decode: null argument");
+    Model *m = reinterpret_cast<Model *>(mp);
+    Cache *c = reinterpret_cast<Cache *>(cp);
+    if (c->model != m) return fail(LBK_ERR_INVALID, "the cache belongs to another model");
+    if (c->len >= c->cap) return fail(LBK_ERR_INVALID, "the cache is full (%zu positions)", c->cap);
+    LBK_CUDA(cudaSetDevice(m->ctx->device));
+    LBK_TRY(ensure_graph(m, c));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    LBK_CUDA(cudaMemcpyAsync(c->tokens, tokens_dev, c->b * 4, cudaMemcpyDeviceToDevice, st));
+    LBK_CUDA(cudaGraphLaunch(c->step, st));
+    m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
+    if (logits_dev) LBK_CUDA(cudaMemcpyAsync(logits_dev, c->logits, c->b * m->cfg.vocab_size * 4, cudaMemcpyDeviceToDevice, st));
+    if (next_dev) LBK_CUDA(cudaMemcpyAsync(next_dev, c->next, c->b * 4, cudaMemcpyDeviceToDevice, st));
+    c->len += 1;
+    return LBK_OK;
+}
+
+int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, size_t n, int all_logits, float *logits_out) {
+    if (!mp || !cp || (n && !tokens)) return fail(LBK_ERR_INVALID, "lbk_model_forward: null argument");
+    Model *m = reinterpret_cast<Model *>(mp);
+    Cache *c = reinterpret_cast<Cache *>(cp);
+    if (c->model != m) return fail(LBK_ERR_INVALID, "the cache belongs to another model");
+    if (c->b != 1) return fail(LBK_ERR_INVALID, "lbk_model_forward drives one sequence; this cache was made for %zu", c->b);
+    if (n == 0) return LBK_OK;
+    if (c->len + n > c->cap) return fail(LBK_ERR_INVALID, "%zu tokens do not fit: %zu of %zu positions are used", n, c->len, c->cap);
+    LBK_CUDA(cudaSetDevice(m->ctx->device));
+    LBK_TRY(ensure_graph(m, c));
+    cudaStream_t st = m->ctx->own_stream;
+    const size_t V = m->cfg.vocab_size;
+    for (size_t i = 0; i < n; ++i) {
+        if (tokens[i] >= V) return fail(LBK_ERR_INVALID, "token %u is outside the vocabulary of %zu", tokens[i], V);
+        const int32_t tk = static_cast<int32_t>(tokens[i]);
+        LBK_CUDA(cudaMemcpyAsync(c->tokens, &tk, 4, cudaMemcpyHostToDevice, st));
+        LBK_CUDA(cudaStreamSynchronize(st));  // `tk` is a stack variable
+        LBK_CUDA(cudaGraphLaunch(c->step, st));
+        m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
+        c->len += 1;
+        if (logits_out && (all_logits || i + 1 == n)) {
+            float *dst = logits_out + (all_logits ? i * V : 0);
+            LBK_CUDA(cudaMemcpyAsync(dst, c->logits, V * 4, cudaMemcpyDeviceToHost, st));
+        }
+    }
+    LBK_CUDA(cudaStreamSynchronize(st));
+    return LBK_OK;
+}
+
+}  // extern "C"

@@ -282,3 +282,68 @@ def save_checkpoint(directory, cfg: Config, tensors: Dict[str, torch.Tensor]) ->
     (directory / "config.json").write_text(json.dumps(cfg.__dict__))
     save_file({k: v.contiguous() for k, v in tensors.items()}, str(directory / FILE_NAME),
               metadata={"format": FORMAT, "version": "1", "quant": "absmean-ternary", "layout": "lb-ternary-128x2bit"})
+
+
+class _ModelConfig(C.Structure):
+    _fields_ = [(n, C.c_size_t) for n in ("hidden_size", "intermediate_size", "num_attention_heads", "num_key_value_heads",
+                                          "num_hidden_layers", "vocab_size", "max_position_embeddings")] + \
+               [("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("bos_token_id", C.c_int)]
+
+
+class NativeBitNet:
+    """The same decoder driven entirely by liblbk.so (lbk_model_load / new_cache / forward / decode):
+    what a host without a tensor framework binds. Same checkpoint, same kernels, same results as
+    `BitNet`; this class only marshals pointers."""
+
+    def __init__(self, directory, ctx: Optional[Context] = None):
+        self.ctx = ctx or default_context()
+        self._lib = self.ctx._lib
+        h = C.c_void_p()
+        _lib.check(self._lib.lbk_model_load(self.ctx.handle, str(directory).encode(), C.byref(h)))
+        self.handle = h
+        raw = _ModelConfig()
+        _lib.check(self._lib.lbk_model_get_config(h, C.byref(raw)))
+        self.cfg = Config(raw.hidden_size, raw.intermediate_size, raw.num_attention_heads, raw.num_key_value_heads,
+                          raw.num_hidden_layers, raw.vocab_size, raw.rms_norm_eps, raw.rope_theta, raw.max_position_embeddings,
+                          bos_token_id=raw.bos_token_id)
+        self._caches = []
+
+    def new_cache(self, b: int = 1, cap: int = 0):
+        c = C.c_void_p()
+        _lib.check(self._lib.lbk_model_new_cache(self.handle, b, cap, C.byref(c)))
+        self._caches.append(c)
+        return c
+
+    def cache_len(self, cache) -> int:
+        return int(self._lib.lbk_kv_cache_len(cache))
+
+    def forward(self, tokens, cache, all_logits: bool = False) -> np.ndarray:
+        """model.rs:305: logits [n, vocab] (all_logits) or [vocab] of the last token, on the host."""
+        toks = np.ascontiguousarray(tokens, dtype=np.uint32)
+        out = np.empty((len(toks) if all_logits else 1, self.cfg.vocab_size), dtype=np.float32)
+        _lib.check(self._lib.lbk_model_forward(self.handle, cache, toks.ctypes.data_as(C.c_void_p), len(toks), int(all_logits),
+                                               out.ctypes.data_as(C.c_void_p)))
+        return out if all_logits else out[0]
+
+    def decode(self, tokens_dev: torch.Tensor, cache):
+        """One token per sequence; returns (logits [b, vocab], greedy next tokens [b]) on the device."""
+        b = tokens_dev.shape[0]
+        logits = torch.empty((b, self.cfg.vocab_size), dtype=torch.float32, device=tokens_dev.device)
+        nxt = torch.empty(b, dtype=torch.int32, device=tokens_dev.device)
+        _lib.check(self._lib.lbk_model_decode(self.handle, cache, C.c_void_p(tokens_dev.data_ptr()), C.c_void_p(logits.data_ptr()),
+                                              C.c_void_p(nxt.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        return logits, nxt
+
+    def close(self):
+        if getattr(self, "handle", None):
+            for c in self._caches:
+                self._lib.lbk_kv_cache_free(c)
+            self._caches = []
+            self._lib.lbk_model_free(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

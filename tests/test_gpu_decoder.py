@@ -257,3 +257,62 @@ def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh):
             ref = np.einsum("bp,bpd->bd", w, vf[:, h // (nh // kvh)])
             assert np.abs(got[:, h] - ref).max() < 1e-5
     ctx.check_device_error()
+
+
+def test_native_runtime_matches_python_mirror(ctx, tmp_path):
+    """lbk_model_load / new_cache / forward / decode (the decoder as a C-ABI runtime) on a checkpoint
+    written in lb-convert's format: logits bit-identical to the Python mirror's (same kernels, same
+    order), prompt ingestion + generation, a batch of three sequences, and the reference's loader
+    checks (model.rs:151-161)."""
+    import torch
+    from safetensors.torch import save_file
+    from lemonade_burn_b200 import _lib, model
+    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 64)   # 4 query heads per KV head: the fused attention
+    tensors = model.random_checkpoint(cfg, 21)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    py = model.BitNet.load(tmp_path, ctx)
+    nat = model.NativeBitNet(tmp_path, ctx)
+    assert nat.cfg.hidden_size == 512 and nat.cfg.num_key_value_heads == 1 and abs(nat.cfg.rope_theta - 500000.0) < 1e-3
+    prompt = [5, 77, 901, 3, 42]
+    # single sequence: all logits of the prompt, then three greedy steps
+    pc = py.new_cache(1, 64)
+    ref = []
+    for tk in prompt:
+        ref.append(py.forward(torch.tensor([tk], dtype=torch.int32, device="cuda"), pc).cpu().numpy()[0])
+    nc = nat.new_cache(1, 64)
+    got = nat.forward(prompt, nc, all_logits=True)
+    assert got.shape == (len(prompt), cfg.vocab_size)
+    for i in range(len(prompt)):
+        assert np.array_equal(got[i].view(np.uint32), ref[i].view(np.uint32))
+    assert nat.cache_len(nc) == len(prompt)
+    tk = int(np.argmax(got[-1]))
+    for _ in range(3):
+        lp = py.forward(torch.tensor([tk], dtype=torch.int32, device="cuda"), pc).cpu().numpy()[0]
+        ln = nat.forward([tk], nc)
+        assert np.array_equal(ln.view(np.uint32), lp.view(np.uint32))
+        tk = int(np.argmax(ln))
+    # three sequences advancing together
+    pc3, nc3 = py.new_cache(3, 16), nat.new_cache(3, 16)
+    toks = torch.tensor([9, 500, 31], dtype=torch.int32, device="cuda")
+    for _ in range(4):
+        lp = py.forward(toks, pc3)
+        ln, nxt = nat.decode(toks, nc3)
+        torch.cuda.synchronize()
+        assert torch.equal(ln, lp)
+        assert torch.equal(nxt, py.argmax(lp))
+        toks = nxt
+    ctx.check_device_error()
+    nat.close()
+    # loader checks
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / model.FILE_NAME), metadata={"format": "something-else"})
+    with pytest.raises(_lib.LbkError, match="not a lemonade-burn ternary file"):
+        model.NativeBitNet(tmp_path, ctx)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    (tmp_path / "config.json").write_text(json.dumps(dict(cfg.__dict__, hidden_act="silu")))
+    with pytest.raises(_lib.LbkError, match="relu2"):
+        model.NativeBitNet(tmp_path, ctx)
+    (tmp_path / "config.json").write_text(json.dumps(cfg.__dict__))
+    del tensors["model.norm.weight"]
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    with pytest.raises(_lib.LbkError, match="missing"):
+        model.NativeBitNet(tmp_path, ctx)
