@@ -40,6 +40,8 @@ struct GemvParams {
     int chunks;    // ceil(row_bytes / 128)
     int xq_stride; // bytes between token rows of the quantised activations in shared memory
     int total_tiles;
+    int split;             // 1: a CTA's warps share its tiles chunk by chunk and add up in shared memory
+    int acc_tiles;         // tiles per CTA at most (size of that shared-memory area)
     const float *x;        // f32 [m, k], or null when q is given
     const int8_t *q;       // int8 [m, kp]
     const float *qscale;   // f32 [m]
@@ -65,10 +67,11 @@ struct SmemLayout {
     uint32_t sum;      // i32 [kMaxM]
     uint32_t inv;      // f32 [LBK_MAX_GROUP][kMaxM]
     uint32_t xq;       // m * xq_stride
+    uint32_t acc;      // i32 [acc_tiles][MT][128]: sums of tiles whose chunks are spread over several warps
     uint32_t total;
 };
 
-__host__ __device__ inline SmemLayout smem_layout(int m, int xq_stride) {
+__host__ __device__ inline SmemLayout smem_layout(int m, int xq_stride, int acc_tiles = 0) {
     SmemLayout L;
     uint32_t o = 0;
     L.stages = o; o += kWarps * kStages * kStageBytes;
@@ -80,6 +83,8 @@ __host__ __device__ inline SmemLayout smem_layout(int m, int xq_stride) {
     L.inv = o;    o += LBK_MAX_GROUP * kMaxM * 4;
     o = (o + 127u) & ~127u;
     L.xq = o;     o += static_cast<uint32_t>(m) * static_cast<uint32_t>(xq_stride);
+    o = (o + 15u) & ~15u;
+    L.acc = o;    o += static_cast<uint32_t>(acc_tiles) * (m > 8 ? 2u : 1u) * 128u * 4u;
     L.total = o;
     return L;
 }
@@ -92,7 +97,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const uint32_t raw = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *sm = smem_raw + (base - raw);
-    const SmemLayout L = smem_layout(p.m, p.xq_stride);
+    const SmemLayout L = smem_layout(p.m, p.xq_stride, p.split ? p.acc_tiles : 0);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -105,17 +110,33 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_gstart));
 #endif
 
-    // ---- this warp's run of tiles --------------------------------------------------------
+    // ---- this warp's run --------------------------------------------------------------------
+    // Whole tiles per warp when every warp has several; otherwise (the decode shapes: 160..864
+    // tiles for 2368 warps) a CTA takes a contiguous range of tiles and its 16 warps share the
+    // range's stages (tile x chunk) equally, so that a tile of 14 chunks is streamed by up to 14
+    // warps at once instead of by one warp in 14 turns. Partial sums meet in shared memory.
     const long long gw = static_cast<long long>(blockIdx.x) * kWarps + warp;
     const long long nw = static_cast<long long>(gridDim.x) * kWarps;
-    const int tile_begin = static_cast<int>(gw * p.total_tiles / nw);
-    const int tile_end = static_cast<int>((gw + 1) * p.total_tiles / nw);
-    const int n_items = (tile_end - tile_begin) * chunks;
+    int tile_begin, chunk_begin, n_items, cta_tile0 = 0, cta_stages = 0;
+    if (p.split) {
+        cta_tile0 = static_cast<int>(static_cast<long long>(blockIdx.x) * p.total_tiles / gridDim.x);
+        const int cta_tile1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.total_tiles / gridDim.x);
+        cta_stages = (cta_tile1 - cta_tile0) * chunks;
+        const int s0 = cta_stages * warp / kWarps, s1 = cta_stages * (warp + 1) / kWarps;
+        tile_begin = cta_tile0 + s0 / chunks;
+        chunk_begin = s0 % chunks;
+        n_items = s1 - s0;
+    } else {
+        tile_begin = static_cast<int>(gw * p.total_tiles / nw);
+        const int tile_end = static_cast<int>((gw + 1) * p.total_tiles / nw);
+        chunk_begin = 0;
+        n_items = (tile_end - tile_begin) * chunks;
+    }
     const uint32_t stage0 = base + L.stages + warp * (kStages * kStageBytes);
     const uint32_t full0 = base + L.full + warp * (kStages * 8);
 
     // issue cursor (lane 0 only): next item to fetch
-    int issue_tile = tile_begin, issue_chunk = 0, issue_mat = 0;
+    int issue_tile = tile_begin, issue_chunk = chunk_begin, issue_mat = 0;
     const uint64_t stream_once = ptx::policy_evict_first();  // weights are read once per launch
     auto issue = [&](int s) {  // s: the ring stage the next item goes into
         while (issue_mat < p.n_mat - 1 && issue_tile >= p.tile_end[issue_mat]) ++issue_mat;
@@ -168,6 +189,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     float *s_inv = reinterpret_cast<float *>(sm + L.inv);
     uint8_t *s_xq = sm + L.xq;
     const int kfill = chunks * kChunkCols;  // columns held per token row (zero padded)
+    int *s_acc = reinterpret_cast<int *>(sm + L.acc);
+    if (p.split)
+        for (int i = tid; i < p.acc_tiles * MT * 128; i += kThreads) s_acc[i] = 0;  // published by the barriers below
 
     if (p.x != nullptr) {
         if (cached) {
@@ -294,7 +318,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     }
     __syncthreads();
 
-    if (n_items == 0) return;
+    if (n_items == 0 && !p.split) return;
 #ifdef LBK_TIMELINE
     tl_prologue = clock64();
 #endif
@@ -320,10 +344,34 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
 #pragma unroll
                 for (int j = 0; j < 4; ++j) acc[mt][h][kk][j] = 0;
 
-    int tile = tile_begin, chunk = 0, mat = 0;
+    int tile = tile_begin, chunk = chunk_begin, mat = 0;
     int s = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // dot = acc - sum(q) (gemm.rs:306-308), y = (float)dot * inv (gemm.rs:141) for one 16-row tile;
+    // v(mt, j) gives the complete sum of element j of token group mt
+    auto write_tile = [&](int tile_id, auto &&v) {
+        while (mat < p.n_mat - 1 && tile_id >= p.tile_end[mat]) ++mat;
+        const int row0 = (tile_id - (mat ? p.tile_end[mat - 1] : 0)) * kTileRows;
+        const int rows = p.rows[mat];
+        float *out = p.out[mat];
+        int32_t *iout = p.iout[mat];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int val = v(mt, j);
+                const int row = row0 + g + ((j & 2) ? 8 : 0);
+                const int tok = mt * 8 + 2 * t + (j & 1);
+                if (row < rows && tok < m) {
+                    const int d = val - s_sum[tok];
+                    const size_t o = static_cast<size_t>(tok) * rows + row;
+                    if (iout) iout[o] = d;
+                    if (out) out[o] = __fmul_rn(__int2float_rn(d), s_inv[mat * kMaxM + tok]);
+                }
+            }
+    };
+    int first_chunk = chunk_begin;  // chunk at which this warp entered the current tile
     for (int item = 0; item < n_items; ++item) {
 #ifdef LBK_TIMELINE
         const long long tl_w0 = clock64();
@@ -343,30 +391,43 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             s = 0;
             phase ^= 1;
         }
-
-        if (++chunk == chunks) {
-            // ---- tile epilogue -----------------------------------------------------------
-            while (mat < p.n_mat - 1 && tile >= p.tile_end[mat]) ++mat;
-            const int row0 = (tile - (mat ? p.tile_end[mat - 1] : 0)) * kTileRows;
-            const int rows = p.rows[mat];
-            float *out = p.out[mat];
-            int32_t *iout = p.iout[mat];
+        const bool tile_done = ++chunk == chunks;
+        if (tile_done || item + 1 == n_items) {
+            if (tile_done && first_chunk == 0) {
+                // this warp streamed the whole tile: write it out directly
+                write_tile(tile, [&](int mt, int j) { return take_acc<MT>(acc, mt, j); });
+            } else {
+                // part of a tile: add this warp's sums to the tile's record in shared memory
+                int *rec = s_acc + (static_cast<size_t>(tile - cta_tile0) * MT) * 128 + lane * 4;
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const int v = take_acc<MT>(acc, mt, j);
-                    const int row = row0 + g + ((j & 2) ? 8 : 0);
-                    const int tok = mt * 8 + 2 * t + (j & 1);
-                    if (row < rows && tok < m) {
-                        const int d = v - s_sum[tok];  // gemm.rs:306-308
-                        const size_t o = static_cast<size_t>(tok) * rows + row;
-                        if (iout) iout[o] = d;
-                        if (out) out[o] = __fmul_rn(__int2float_rn(d), s_inv[mat * kMaxM + tok]);
-                    }
-                }
-            chunk = 0;
-            ++tile;
+                    for (int j = 0; j < 4; ++j) atomicAdd(rec + mt * 128 + j, take_acc<MT>(acc, mt, j));
+            }
+            if (tile_done) {
+                chunk = 0;
+                first_chunk = 0;
+                ++tile;
+            }
+        }
+    }
+    if (p.split) {
+        __syncthreads();  // every warp's partial sums are in shared memory
+        if (ok && cta_stages > 0) {
+            // tiles that no single warp streamed alone: warp w finishes local tiles w, w + 16, ...
+            const int n_local = cta_stages / chunks;
+            auto owner = [&](int stage) {  // the warp whose run [S*w/16, S*(w+1)/16) holds `stage`
+                int w = static_cast<int>(static_cast<long long>(stage) * kWarps / cta_stages);
+                while (w + 1 < kWarps && cta_stages * (w + 1) / kWarps <= stage) ++w;
+                while (w > 0 && cta_stages * w / kWarps > stage) --w;
+                return w;
+            };
+            mat = 0;
+            for (int tl = warp; tl < n_local; tl += kWarps) {
+                if (owner(tl * chunks) == owner(tl * chunks + chunks - 1)) continue;  // written directly above
+                const int *rec = s_acc + (static_cast<size_t>(tl) * MT) * 128 + lane * 4;
+                write_tile(cta_tile0 + tl, [&](int mt, int j) { return rec[mt * 128 + j]; });
+            }
         }
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 1);
@@ -456,7 +517,17 @@ int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
 #endif
     if (tiles == 0) return LBK_OK;
 
-    const SmemLayout L = smem_layout(p.m, p.xq_stride);
+    // few tiles per warp: let the 16 warps of a CTA share its tiles chunk by chunk
+    const int grid_for = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    const int tiles_per_cta = (tiles + grid_for - 1) / grid_for;
+    p.split = tiles_per_cta <= 32 && tiles < 4 * ctx->sm_count * kWarps ? 1 : 0;
+    p.acc_tiles = p.split ? tiles_per_cta : 0;
+    SmemLayout L = smem_layout(p.m, p.xq_stride, p.acc_tiles);
+    if (p.split && static_cast<size_t>(L.total) + 1024 > ctx->smem_optin) {
+        p.split = 0;
+        p.acc_tiles = 0;
+        L = smem_layout(p.m, p.xq_stride, 0);
+    }
     const size_t smem = static_cast<size_t>(L.total) + 1024;
     if (smem > ctx->smem_optin)
         return fail(LBK_ERR_UNSUPPORTED, "gemv: %zu token rows of %zu columns need %zu B of shared memory (limit %zu)",
