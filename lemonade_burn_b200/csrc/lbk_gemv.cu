@@ -27,13 +27,11 @@ using namespace gemv;
 
 namespace {
 
+// Field order matters: kernel parameters sit in constant memory and every 64-byte line of them is a
+// cold miss at kernel start (about 300 ns each, serialised where one value decides the next load).
+// Everything the set-up needs comes first, in two lines; the tensor maps, which only the TMA unit
+// reads, come last.
 struct GemvParams {
-    CUtensorMap tmap[LBK_MAX_GROUP];
-    float *out[LBK_MAX_GROUP];
-    int32_t *iout[LBK_MAX_GROUP];
-    float wscale[LBK_MAX_GROUP];
-    int rows[LBK_MAX_GROUP];
-    int tile_end[LBK_MAX_GROUP];  // running count of 16-row tiles up to and including matrix i
     int n_mat;
     int m;
     int k;         // logical columns
@@ -47,14 +45,20 @@ struct GemvParams {
     const float *qscale;   // f32 [m]
     const int32_t *qsum;   // i32 [m]
     int pre;               // LBK_PRE_*: transform of x before the quantiser (register-cached rows only)
+    float pre_eps;
     const float *pre_y;
     const float *pre_w;
     float *pre_xout;
-    float pre_eps;
     int *err_word;
+    int tile_end[LBK_MAX_GROUP];  // running count of 16-row tiles up to and including matrix i
+    int rows[LBK_MAX_GROUP];
+    float wscale[LBK_MAX_GROUP];
+    float *out[LBK_MAX_GROUP];
+    int32_t *iout[LBK_MAX_GROUP];
 #ifdef LBK_TIMELINE
     long long *timeline;   // [warps_total][8] clock samples, debugging only
 #endif
+    alignas(64) CUtensorMap tmap[LBK_MAX_GROUP];
 };
 
 // Shared-memory carve-up (offsets from a 1024-byte aligned base).
@@ -162,11 +166,21 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     // Weights do not depend on the kernel before this one, activations do: set up the ring and
     // start the first weight loads, THEN wait for the predecessor (a chained launch overlaps all of
     // this with its tail), then read the activation rows.
+#ifdef LBK_TIMELINE
+    long long tl_e = 0, tl_f = 0;
+    const long long tl_s0 = clock64();
+#endif
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
+#ifdef LBK_TIMELINE
+        tl_e = clock64();
+#endif
         const int first = n_items < kStages ? n_items : kStages;
         for (int i = 0; i < first; ++i) issue(i);
+#ifdef LBK_TIMELINE
+        tl_f = clock64();
+#endif
     }
     ptx::pdl_wait();
     RowCache rc;
@@ -291,10 +305,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         tl_d = clock64();  // quantised and stored
 #endif
         __syncthreads();
-        if (tid < m) {
+        if (tid >= 32 && tid < 32 + m) {  // a different warp from the one that writes s_inv below: both run at once
+            const int tk = tid - 32;
             int s = 0;
-            for (int w = 0; w < P; ++w) s += s_parti[tid * kWarps + w];
-            s_sum[tid] = s;
+            for (int w = 0; w < P; ++w) s += s_parti[tk * kWarps + w];
+            s_sum[tk] = s;
         }
     } else {
         // already quantised (ternary_gemm_i32 / ternary_gemm_multi entry points): re-order
@@ -309,8 +324,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
             s_scale[tid] = p.qscale ? p.qscale[tid] : 1.0f;
             s_sum[tid] = p.qsum[tid];
         }
+        __syncthreads();  // s_scale of this branch is written right above
     }
-    __syncthreads();
     if (tid < m * p.n_mat) {
         const int mi = tid / m, tk = tid % m;
         // gemm.rs:141: inv = 1.0 / (x.scale * w.scale)
@@ -438,6 +453,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         long long *d = p.timeline + gw * 16;
         d[0] = tl_prologue - tl_start; d[1] = tl_first - tl_prologue; d[2] = clock64() - tl_first;
         d[3] = n_items; d[4] = static_cast<long long>(tl_gstart); d[5] = static_cast<long long>(gend); d[6] = tl_polls; d[7] = blockIdx.x;
+        d[13] = tl_s0 - tl_start; d[14] = tl_e - tl_s0; d[15] = tl_f - tl_e;
         d[8] = tl_a - tl_start; d[9] = tl_b - tl_a; d[10] = tl_c - tl_b; d[11] = tl_d - tl_c; d[12] = tl_prologue - tl_d;
     }
 #endif
