@@ -418,7 +418,11 @@ def cpu_sweep_baseline(packed_layers, xs, budget_s: float = 12.0, max_layers: in
     from oracle import oracle as o
     o.build()
     kern = o.simd_best_kernel()
-    threads = o.simd_max_threads()
+    # every core this process may run on, whatever OMP_NUM_THREADS says (torchrun sets it to 1)
+    try:
+        threads = len(os.sched_getaffinity(0))
+    except AttributeError:
+        threads = os.cpu_count() or 1
     n_layers = min(len(packed_layers), max_layers)
 
     def one_pass():
@@ -426,7 +430,7 @@ def cpu_sweep_baseline(packed_layers, xs, budget_s: float = 12.0, max_layers: in
             for gi, (cols, rows) in enumerate(GROUPS):
                 x = xs[li * len(GROUPS) + gi]
                 q, s, ssum = o.simd_quantize_acts(x.reshape(1, cols))
-                o.simd_gemm_multi(packed_layers[li][gi], [WSCALE] * len(rows), q, s, ssum, kernel=kern)
+                o.simd_gemm_multi(packed_layers[li][gi], [WSCALE] * len(rows), q, s, ssum, kernel=kern, threads=threads)
 
     one_pass()  # warm (page in)
     t0 = time.perf_counter()
