@@ -231,6 +231,18 @@ int lbk_attn_decode(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev
 int lbk_relu2_mul(lbk_ctx *ctx, const float *g_dev, const float *u_dev, size_t n, float *out_dev, void *stream);
 /* x += y (the residual adds of model.rs:359,365). */
 int lbk_add_inplace(lbk_ctx *ctx, float *x_dev, const float *y_dev, size_t n, void *stream);
+/* Prompt ingestion: n consecutive positions of ONE sequence (`seq` of the cache's batch) at once.
+ * lbk_rope_kv_append_rows: RoPE on q_dev [n][n_heads*hd] in place and on k_dev [n][kv_heads*hd];
+ * k and v_dev are appended at positions *pos_dev .. *pos_dev + n - 1.
+ * lbk_attn_prefill: causal attention of those n rows (row i sees keys 0 .. *pos_dev + i), head_dim
+ * 128, out_dev [n][n_heads*hd]. Neither advances *pos_dev. */
+int lbk_rope_kv_append_rows(lbk_ctx *ctx, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                            const float *sin_dev, const int32_t *pos_dev, size_t n, size_t n_heads, size_t kv_heads,
+                            size_t head_dim, size_t cap, size_t seq, uint16_t *kcache_dev, uint16_t *vcache_dev,
+                            void *stream);
+int lbk_attn_prefill(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev,
+                     const int32_t *pos_dev, size_t n, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                     size_t seq, float *out_dev, void *stream);
 /* lbk_rope_kv_append + lbk_attn_decode in one launch, for 4..8 query heads per KV head, head_dim
  * 128 and at most 256 splits (lbk_attn_decode_fused_supported): q_dev, k_dev, v_dev are the raw
  * projections ([b][n_heads*128], [b][kv_heads*128] x 2); the new position's K/V row is appended to
@@ -276,7 +288,7 @@ int lbk_advance_pos(lbk_ctx *ctx, int32_t *pos_dev, void *stream);
  * lbk_model_forward   BitNet::forward (model.rs:305-374) for one sequence (cache of batch 1):
  *                     appends `n` tokens at cache.len and writes the logits of every token
  *                     ([n][vocab], all_logits != 0) or of the last one ([vocab]) to host memory.
- *                     Several tokens are run through the decode step one after the other.
+ *                     Several tokens go through the projections together, up to 1024 rows a pass.
  * lbk_model_decode    one new token for each of the cache's sequences: tokens_dev int32 [batch];
  *                     logits_dev f32 [batch][vocab] and/or next_dev int32 [batch] (greedy argmax,
  *                     sample.rs:17-25) may be null. Asynchronous on `stream`.

@@ -55,6 +55,8 @@ SYMBOLS = [
     ("lbk_add_inplace", _i, [_vp, _vp, _vp, _sz, _vp]),
     ("lbk_add_rms_norm", _i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
     ("lbk_relu2_mul_rms_norm", _i, [_vp, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp]),
+    ("lbk_rope_kv_append_rows", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_attn_prefill", _i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp]),
     ("lbk_attn_decode_fused_supported", _i, [_sz, _sz, _sz, _sz]),
     ("lbk_attn_decode_fused", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
     ("lbk_ternary_linear_pre_supported", _i, [_sz, _sz]),

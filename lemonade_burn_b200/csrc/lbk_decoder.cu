@@ -457,6 +457,113 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
     *reinterpret_cast<float4 *>(out + (static_cast<size_t>(b) * nh + head) * kHd + lane * 4) = make_float4(tot.x * inv, tot.y * inv, tot.z * inv, tot.w * inv);
 }
 
+// ---- prompt ingestion: n consecutive positions of ONE sequence at once -----------------------------
+// RoPE on the n query rows (in place) and the n new key rows, which are appended with the value
+// rows at positions pos0 .. pos0 + n - 1 of sequence `seq` (model.rs:298-302, 339-341).
+__global__ void rope_append_rows_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                        const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                        const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap, int seq,
+                                        uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    const int row = blockIdx.y, h = blockIdx.x, pos = *pos_dev + row;
+    const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
+    const int half = hd >> 1;
+    if (h < nh) {
+        float *qh = q + (static_cast<size_t>(row) * nh + h) * hd;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float x1 = qh[i], x2 = qh[i + half];
+            qh[i] = x1 * c[i] + (-x2) * s[i];
+            qh[i + half] = x2 * c[i + half] + x1 * s[i + half];
+        }
+    } else {
+        const int kh = h - nh;
+        const float *kk = k + (static_cast<size_t>(row) * kvh + kh) * hd;
+        const float *vv = v + (static_cast<size_t>(row) * kvh + kh) * hd;
+        const size_t slot = ((static_cast<size_t>(seq) * kvh + kh) * cap + pos) * hd;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const float x1 = kk[i], x2 = kk[i + half];
+            kcache[slot + i] = f32_to_bf16(x1 * c[i] + (-x2) * s[i]);
+            kcache[slot + i + half] = f32_to_bf16(x2 * c[i + half] + x1 * s[i + half]);
+            vcache[slot + i] = f32_to_bf16(vv[i]);
+            vcache[slot + i + half] = f32_to_bf16(vv[i + half]);
+        }
+    }
+}
+
+// Causal attention of n query rows of one sequence over its cache: block (kv head, row) walks the
+// keys 0 .. pos0 + row in chunks of 32 positions staged in shared memory (the layout and the two
+// inner products are those of attn_partial_staged_kernel) and writes the normalised result itself:
+// no slices, no merge. The keys of a layer fit the L2, so the rows re-read them from there.
+__global__ void __launch_bounds__(256) attn_rows_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
+                                                       const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev, int nh, int kvh,
+                                                       int cap, int seq, float scaling, float *__restrict__ out /* [n][nh*hd] */) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];
+    __shared__ __align__(16) uint8_t s_v[kAttnChunk * kVRow];
+    __shared__ __align__(16) float s_q[8 * kHd];
+    const int kh = blockIdx.x, row = blockIdx.y;
+    const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
+    const int total = *pos_dev + row + 1;  // keys 0 .. this row's own position
+    const int head = kh * group + warp;
+    for (int i = tid; i < group * kHd; i += nthr) s_q[i] = q[(static_cast<size_t>(row) * nh + kh * group) * kHd + i] * scaling;
+    const uint16_t *kb = kc + (static_cast<size_t>(seq) * kvh + kh) * cap * kHd;
+    const uint16_t *vb = vc + (static_cast<size_t>(seq) * kvh + kh) * cap * kHd;
+    float mx = -INFINITY, sum = 0.0f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int pc = 0; pc < total; pc += kAttnChunk) {
+        const int n = min(kAttnChunk, total - pc);
+        __syncthreads();
+        for (int i = tid; i < n * 16; i += nthr) {
+            const int r = i >> 4, seg = i & 15;
+            *reinterpret_cast<uint4 *>(s_k + r * kKRow + seg * 16) = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+            *reinterpret_cast<uint4 *>(s_v + r * kVRow + seg * 16) = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + seg * 8);
+        }
+        __syncthreads();
+        float sc = -INFINITY;
+        if (lane < n) {
+            const uint8_t *kr = s_k + lane * kKRow;
+            const float *qh = s_q + warp * kHd;
+            float d0 = 0.f, d1 = 0.f;
+#pragma unroll
+            for (int it = 0; it < kHd / 8; ++it) {
+                const uint4 kk = *reinterpret_cast<const uint4 *>(kr + it * 16);
+                const float4 qa = *reinterpret_cast<const float4 *>(qh + it * 8), qb = *reinterpret_cast<const float4 *>(qh + it * 8 + 4);
+                d0 += qa.x * bf16_to_f32(kk.x & 0xffff) + qa.y * bf16_to_f32(kk.x >> 16) + qa.z * bf16_to_f32(kk.y & 0xffff) +
+                      qa.w * bf16_to_f32(kk.y >> 16);
+                d1 += qb.x * bf16_to_f32(kk.z & 0xffff) + qb.y * bf16_to_f32(kk.z >> 16) + qb.z * bf16_to_f32(kk.w & 0xffff) +
+                      qb.w * bf16_to_f32(kk.w >> 16);
+            }
+            sc = d0 + d1;
+        }
+        float nm = sc;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(0xffffffffu, nm, o));
+        nm = fmaxf(nm, mx);
+        const float corr = __expf(mx - nm);
+        const float w = lane < n ? __expf(sc - nm) : 0.0f;
+        float ws = w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
+        sum = sum * corr + ws;
+        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+        const uint8_t *vr = s_v + lane * 8;
+#pragma unroll 8
+        for (int p = 0; p < n; ++p) {
+            const float wp = __shfl_sync(0xffffffffu, w, p);
+            const uint2 vv = *reinterpret_cast<const uint2 *>(vr + p * kVRow);
+            acc.x += wp * bf16_to_f32(vv.x & 0xffff);
+            acc.y += wp * bf16_to_f32(vv.x >> 16);
+            acc.z += wp * bf16_to_f32(vv.y & 0xffff);
+            acc.w += wp * bf16_to_f32(vv.y >> 16);
+        }
+        mx = nm;
+    }
+    const float inv = 1.0f / sum;
+    *reinterpret_cast<float4 *>(out + (static_cast<size_t>(row) * nh + head) * kHd + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+}
+
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
                                                           float *__restrict__ out /* [b][nh*hd] */) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
@@ -724,6 +831,37 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     LBK_CUDA(cudaGetLastError());
     LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st, scratch_dev, static_cast<int>(splits), out_dev));
     ctx->launches++;
+    LBK_DEC_POST();
+}
+
+int lbk_rope_kv_append_rows(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                            const int32_t *pos_dev, size_t n, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t seq,
+                            uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream) {
+    LBK_DEC_PRE("lbk_rope_kv_append_rows");
+    if (n == 0) return LBK_OK;
+    if (!q_dev || !k_dev || !v_dev || !cos_dev || !sin_dev || !pos_dev || !kcache_dev || !vcache_dev)
+        return fail(LBK_ERR_INVALID, "lbk_rope_kv_append_rows: null buffer");
+    if (head_dim == 0 || (head_dim & 1)) return fail(LBK_ERR_INVALID, "head_dim must be even");
+    if (n > 65535) return fail(LBK_ERR_UNSUPPORTED, "at most 65535 rows per call");
+    dim3 grid(static_cast<unsigned>(n_heads + kv_heads), static_cast<unsigned>(n));
+    LBK_CUDA(launch_chained(rope_append_rows_kernel, grid, dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
+                            static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap), static_cast<int>(seq), kcache_dev,
+                            vcache_dev));
+    LBK_DEC_POST();
+}
+
+int lbk_attn_prefill(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev, const int32_t *pos_dev, size_t n,
+                     size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t seq, float *out_dev, void *stream) {
+    LBK_DEC_PRE("lbk_attn_prefill");
+    if (n == 0) return LBK_OK;
+    if (!q_dev || !kcache_dev || !vcache_dev || !pos_dev || !out_dev) return fail(LBK_ERR_INVALID, "lbk_attn_prefill: null buffer");
+    if (head_dim != kHd) return fail(LBK_ERR_UNSUPPORTED, "attention kernel is built for head_dim 128, got %zu", head_dim);
+    if (kv_heads == 0 || n_heads % kv_heads || n_heads / kv_heads > 8) return fail(LBK_ERR_UNSUPPORTED, "query group size must be 1..8");
+    if (n > 65535) return fail(LBK_ERR_UNSUPPORTED, "at most 65535 rows per call");
+    dim3 grid(static_cast<unsigned>(kv_heads), static_cast<unsigned>(n));
+    LBK_CUDA(launch_chained(attn_rows_kernel, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev,
+                            pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap), static_cast<int>(seq),
+                            1.0f / sqrtf(static_cast<float>(head_dim)), out_dev));
     LBK_DEC_POST();
 }
 

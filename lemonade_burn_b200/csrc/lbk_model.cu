@@ -8,12 +8,12 @@
 // embedding / LM head BF16). The packed weights go to the GPU as they are.
 //
 // Differences from the reference, all deliberate: the KV cache is bf16 with a fixed capacity
-// (the reference grows an f32 cache, model.rs:245); a call with several tokens of one sequence
-// (prompt ingestion) runs them through the decode step one after the other, which is the same
-// causal computation as the reference's batched prefill; several independent sequences can
-// advance together (lbk_model_decode), which the reference cannot do. One step is recorded into a
-// CUDA graph the first time a cache is used and replayed afterwards (the position lives in
-// device memory).
+// (the reference grows an f32 cache, model.rs:245); several independent sequences can advance
+// together (lbk_model_decode), which the reference cannot do. A call with several tokens of one
+// sequence (a prompt) sends up to 1024 rows at a time through the projections (the tcgen05 GEMM
+// above 16 rows) with causal attention over the cache, as the reference's forward does with
+// m > 1. One decode step is recorded into a CUDA graph the first time a cache is used and
+// replayed afterwards (the position lives in device memory).
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -221,6 +221,12 @@ struct Cache {
           *u = nullptr, *d = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr;
     cudaGraphExec_t step = nullptr;
     std::vector<void *> device_allocs;
+    // work buffers of the prompt path (lbk_model_forward with several tokens), sized for pf_rows rows
+    size_t pf_rows = 0;
+    std::vector<void *> pf_allocs;
+    int32_t *pf_tokens = nullptr;
+    float *pf_x = nullptr, *pf_n = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_o = nullptr, *pf_g = nullptr,
+          *pf_u = nullptr, *pf_act = nullptr, *pf_d = nullptr, *pf_logits = nullptr;
 };
 
 namespace {
@@ -342,6 +348,104 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
     LBK_TRY(lbk_bf16_linear(h, c->n, b, m->embed, cfg.vocab_size, H, c->logits, st));
     LBK_TRY(lbk_argmax(h, c->logits, b, cfg.vocab_size, c->next, st));  // sample.rs:17-25
     LBK_TRY(lbk_advance_pos(h, c->pos, st));
+    return LBK_OK;
+}
+
+constexpr size_t kPrefillChunk = 1024;  // prompt rows per pass (bounds the work buffers: 85 MB for the gate at 6912 columns)
+constexpr size_t kLogitRows = 128;      // rows of logits staged on the device at a time when every token's are wanted
+
+int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {
+    if (rows <= c->pf_rows) return LBK_OK;
+    LBK_CUDA(cudaDeviceSynchronize());
+    for (void *p : c->pf_allocs) cudaFree(p);
+    c->pf_allocs.clear();
+    c->pf_rows = 0;
+    const lbk_model_config &cfg = m->cfg;
+    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, nh = cfg.num_attention_heads, kvh = cfg.num_key_value_heads, hd = m->head_dim;
+    struct { void **p; size_t bytes; } bufs[] = {
+        {reinterpret_cast<void **>(&c->pf_tokens), rows * 4}, {reinterpret_cast<void **>(&c->pf_x), rows * H * 4},
+        {reinterpret_cast<void **>(&c->pf_n), rows * H * 4}, {reinterpret_cast<void **>(&c->pf_q), rows * nh * hd * 4},
+        {reinterpret_cast<void **>(&c->pf_k), rows * kvh * hd * 4}, {reinterpret_cast<void **>(&c->pf_v), rows * kvh * hd * 4},
+        {reinterpret_cast<void **>(&c->pf_attn), rows * nh * hd * 4}, {reinterpret_cast<void **>(&c->pf_o), rows * H * 4},
+        {reinterpret_cast<void **>(&c->pf_g), rows * I * 4}, {reinterpret_cast<void **>(&c->pf_u), rows * I * 4},
+        {reinterpret_cast<void **>(&c->pf_act), rows * I * 4}, {reinterpret_cast<void **>(&c->pf_d), rows * H * 4},
+        {reinterpret_cast<void **>(&c->pf_logits), kLogitRows * cfg.vocab_size * 4}};
+    for (auto &bf : bufs) LBK_TRY(dev_alloc(c->pf_allocs, bf.bytes, bf.p));
+    c->pf_rows = rows;
+    return LBK_OK;
+}
+
+// `n` (2..kPrefillChunk) consecutive tokens of the cache's single sequence in one pass: the
+// projections see n token rows (the tcgen05 GEMM above 16 rows), attention is causal over the cache
+// (model.rs:305-374 with m = n). Logits of every row (`all_logits`) or of the last one go to host
+// memory. Synchronous.
+int prefill_chunk(Model *m, Cache *c, const uint32_t *tokens, size_t n, int all_logits, float *logits_out) {
+    Ctx *ctx = m->ctx;
+    lbk_ctx *h = reinterpret_cast<lbk_ctx *>(ctx);
+    cudaStream_t st = ctx->own_stream;
+    const lbk_model_config &cfg = m->cfg;
+    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, nh = cfg.num_attention_heads, kvh = cfg.num_key_value_heads, hd = m->head_dim,
+                 L = cfg.num_hidden_layers, V = cfg.vocab_size;
+    const float eps = cfg.rms_norm_eps;
+    LBK_TRY(ensure_prefill_buffers(m, c, n));
+    std::vector<int32_t> toks(n);
+    for (size_t i = 0; i < n; ++i) toks[i] = static_cast<int32_t>(tokens[i]);
+    LBK_CUDA(cudaMemcpyAsync(c->pf_tokens, toks.data(), n * 4, cudaMemcpyHostToDevice, st));
+    LBK_CUDA(cudaStreamSynchronize(st));  // `toks` is pageable host memory that goes away
+    const bool fused_h = H % 4 == 0 && H <= 8192, fused_i = I % 4 == 0 && I <= 8192;
+    auto add_norm = [&](float *x, const float *y, const float *w) -> int {  // x += y; pf_n = rms_norm(x) * w
+        if (fused_h) return lbk_add_rms_norm(h, x, y, w, n, H, eps, c->pf_n, st);
+        LBK_TRY(lbk_add_inplace(h, x, y, n * H, st));
+        return lbk_rms_norm(h, x, w, n, H, eps, c->pf_n, st);
+    };
+    const size_t layer_kv = c->b * kvh * c->cap * hd;
+    LBK_TRY(lbk_embed_bf16(h, m->embed, c->pf_tokens, n, H, c->pf_x, st));
+    LBK_TRY(lbk_rms_norm(h, c->pf_x, m->layers[0].input_norm, n, H, eps, c->pf_n, st));
+    for (size_t li = 0; li < L; ++li) {
+        const Model::Layer &l = m->layers[li];
+        const lbk_weight *qkv[3] = {l.q, l.k, l.v};
+        float *qkv_out[3] = {c->pf_q, c->pf_k, c->pf_v};
+        LBK_TRY(lbk_ternary_linear_n(h, c->pf_n, n, qkv, 3, qkv_out, nullptr, st));
+        uint16_t *kc = c->k + li * layer_kv, *vc = c->v + li * layer_kv;
+        LBK_TRY(lbk_rope_kv_append_rows(h, c->pf_q, c->pf_k, c->pf_v, m->cos, m->sin, c->pos, n, nh, kvh, hd, c->cap, 0, kc, vc, st));
+        LBK_TRY(lbk_attn_prefill(h, c->pf_q, kc, vc, c->pos, n, nh, kvh, hd, c->cap, 0, c->pf_attn, st));
+        LBK_TRY(lbk_rms_norm(h, c->pf_attn, l.attn_sub_norm, n, nh * hd, eps, c->pf_attn, st));
+        const lbk_weight *ow[1] = {l.o};
+        float *oo[1] = {c->pf_o};
+        LBK_TRY(lbk_ternary_linear_n(h, c->pf_attn, n, ow, 1, oo, nullptr, st));
+        LBK_TRY(add_norm(c->pf_x, c->pf_o, l.post_attn_norm));
+        const lbk_weight *gu[2] = {l.gate, l.up};
+        float *guo[2] = {c->pf_g, c->pf_u};
+        LBK_TRY(lbk_ternary_linear_n(h, c->pf_n, n, gu, 2, guo, nullptr, st));
+        if (fused_i) {
+            LBK_TRY(lbk_relu2_mul_rms_norm(h, c->pf_g, c->pf_u, l.ffn_sub_norm, n, I, eps, c->pf_act, st));
+        } else {
+            LBK_TRY(lbk_relu2_mul(h, c->pf_g, c->pf_u, n * I, c->pf_act, st));
+            LBK_TRY(lbk_rms_norm(h, c->pf_act, l.ffn_sub_norm, n, I, eps, c->pf_act, st));
+        }
+        const lbk_weight *dw[1] = {l.down};
+        float *dout[1] = {c->pf_d};
+        LBK_TRY(lbk_ternary_linear_n(h, c->pf_act, n, dw, 1, dout, nullptr, st));
+        LBK_TRY(add_norm(c->pf_x, c->pf_d, li + 1 < L ? m->layers[li + 1].input_norm : m->final_norm));
+    }
+    // pf_n holds the final norm of every row
+    if (logits_out) {
+        if (all_logits) {
+            for (size_t r0 = 0; r0 < n; r0 += kLogitRows) {
+                const size_t rows = n - r0 < kLogitRows ? n - r0 : kLogitRows;
+                LBK_TRY(lbk_bf16_linear(h, c->pf_n + r0 * H, rows, m->embed, V, H, c->pf_logits, st));
+                LBK_CUDA(cudaMemcpyAsync(logits_out + r0 * V, c->pf_logits, rows * V * 4, cudaMemcpyDeviceToHost, st));
+                LBK_CUDA(cudaStreamSynchronize(st));  // the staging rows are reused by the next pass
+            }
+        } else {
+            LBK_TRY(lbk_bf16_linear(h, c->pf_n + (n - 1) * H, 1, m->embed, V, H, c->pf_logits, st));
+            LBK_CUDA(cudaMemcpyAsync(logits_out, c->pf_logits, V * 4, cudaMemcpyDeviceToHost, st));
+        }
+    }
+    const int32_t new_len = static_cast<int32_t>(c->len + n);
+    LBK_CUDA(cudaStreamSynchronize(st));
+    LBK_CUDA(cudaMemcpy(c->pos, &new_len, 4, cudaMemcpyHostToDevice));
+    c->len += n;
     return LBK_OK;
 }
 
@@ -538,6 +642,7 @@ int lbk_kv_cache_free(lbk_kv_cache *cp) {
     cudaDeviceSynchronize();
     if (c->step) cudaGraphExecDestroy(c->step);
     for (void *p : c->device_allocs) cudaFree(p);
+    for (void *p : c->pf_allocs) cudaFree(p);
     delete c;
     return LBK_OK;
 }
@@ -620,21 +725,32 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
     if (n == 0) return LBK_OK;
     if (c->len + n > c->cap) return fail(LBK_ERR_INVALID, "%zu tokens do not fit: %zu of %zu positions are used", n, c->len, c->cap);
     LBK_CUDA(cudaSetDevice(m->ctx->device));
-    LBK_TRY(ensure_graph(m, c));
     cudaStream_t st = m->ctx->own_stream;
     const size_t V = m->cfg.vocab_size;
-    for (size_t i = 0; i < n; ++i) {
+    for (size_t i = 0; i < n; ++i)
         if (tokens[i] >= V) return fail(LBK_ERR_INVALID, "token %u is outside the vocabulary of %zu", tokens[i], V);
-        const int32_t tk = static_cast<int32_t>(tokens[i]);
+    if (n >= 2) {  // a prompt: whole chunks of rows through the projections at once
+        for (size_t i0 = 0; i0 < n; i0 += kPrefillChunk) {
+            const size_t rows = n - i0 < kPrefillChunk ? n - i0 : kPrefillChunk;
+            const bool last = i0 + rows == n;
+            float *dst = logits_out ? (all_logits ? logits_out + i0 * V : (last ? logits_out : nullptr)) : nullptr;
+            if (rows == 1) {  // a single left-over token takes the decode step
+                LBK_TRY(lbk_model_forward(mp, cp, tokens + i0, 1, all_logits, dst));
+            } else {
+                LBK_TRY(prefill_chunk(m, c, tokens + i0, rows, all_logits, dst));
+            }
+        }
+        return LBK_OK;
+    }
+    LBK_TRY(ensure_graph(m, c));
+    {
+        const int32_t tk = static_cast<int32_t>(tokens[0]);
         LBK_CUDA(cudaMemcpyAsync(c->tokens, &tk, 4, cudaMemcpyHostToDevice, st));
         LBK_CUDA(cudaStreamSynchronize(st));  // `tk` is a stack variable
         LBK_CUDA(cudaGraphLaunch(c->step, st));
         m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
         c->len += 1;
-        if (logits_out && (all_logits || i + 1 == n)) {
-            float *dst = logits_out + (all_logits ? i * V : 0);
-            LBK_CUDA(cudaMemcpyAsync(dst, c->logits, V * 4, cudaMemcpyDeviceToHost, st));
-        }
+        if (logits_out) LBK_CUDA(cudaMemcpyAsync(logits_out, c->logits, V * 4, cudaMemcpyDeviceToHost, st));
     }
     LBK_CUDA(cudaStreamSynchronize(st));
     return LBK_OK;

@@ -262,8 +262,8 @@ def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh):
 def test_native_runtime_matches_python_mirror(ctx, tmp_path):
     """lbk_model_load / new_cache / forward / decode (the decoder as a C-ABI runtime) on a checkpoint
     written in lb-convert's format: logits bit-identical to the Python mirror's (same kernels, same
-    order), prompt ingestion + generation, a batch of three sequences, and the reference's loader
-    checks (model.rs:151-161)."""
+    order) for a prompt fed token by token + generation, a batch of three sequences, and the
+    reference's loader checks (model.rs:151-161)."""
     import torch
     from safetensors.torch import save_file
     from lemonade_burn_b200 import _lib, model
@@ -280,8 +280,7 @@ def test_native_runtime_matches_python_mirror(ctx, tmp_path):
     for tk in prompt:
         ref.append(py.forward(torch.tensor([tk], dtype=torch.int32, device="cuda"), pc).cpu().numpy()[0])
     nc = nat.new_cache(1, 64)
-    got = nat.forward(prompt, nc, all_logits=True)
-    assert got.shape == (len(prompt), cfg.vocab_size)
+    got = np.stack([nat.forward([tk], nc) for tk in prompt])   # one token per call: the decode step
     for i in range(len(prompt)):
         assert np.array_equal(got[i].view(np.uint32), ref[i].view(np.uint32))
     assert nat.cache_len(nc) == len(prompt)
@@ -316,3 +315,109 @@ def test_native_runtime_matches_python_mirror(ctx, tmp_path):
     model.save_checkpoint(tmp_path, cfg, tensors)
     with pytest.raises(_lib.LbkError, match="missing"):
         model.NativeBitNet(tmp_path, ctx)
+
+
+@pytest.mark.parametrize("pos0,n,nh,kvh", [(0, 1, 8, 2), (0, 37, 8, 2), (5, 64, 20, 5), (100, 33, 4, 4), (0, 130, 16, 2)])
+def test_prefill_rows_against_numpy(ctx, pos0, n, nh, kvh):
+    """lbk_rope_kv_append_rows + lbk_attn_prefill (n prompt rows of one sequence at once) against
+    RoPE + causal softmax(qK/sqrt(d))V in float64 over a cache that already holds pos0 positions:
+    the appended rows must be the bf16 of the rotated k and of v, everything else in the cache
+    untouched, and row i sees keys 0..pos0+i. Tolerance 1e-5 absolute on outputs of magnitude <= 1."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    b, seq, hd, cap = 2, 1, 128, pos0 + n + 3
+    g = torch.Generator().manual_seed(pos0 * 1000 + n)
+    q = torch.randn(n, nh, hd, generator=g)
+    kn = torch.randn(n, kvh, hd, generator=g)
+    vn = torch.rand(n, kvh, hd, generator=g)
+    k = torch.randn(b, kvh, cap, hd, generator=g).bfloat16()
+    v = torch.rand(b, kvh, cap, hd, generator=g).bfloat16()
+    ang = torch.rand(cap, hd // 2, generator=g) * 6.0
+    cos = torch.cat([torch.cos(ang), torch.cos(ang)], dim=1).contiguous()
+    sin = torch.cat([torch.sin(ang), torch.sin(ang)], dim=1).contiguous()
+
+    def rope(x):  # [n][heads][hd], row i at position pos0 + i (model.rs:298-302)
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        c, s_ = cos[pos0:pos0 + n, None, :], sin[pos0:pos0 + n, None, :]
+        return x * c + torch.cat([-x2, x1], dim=-1) * s_
+
+    qd, knd, vnd, kd, vd = q.cuda(), kn.cuda(), vn.cuda(), k.cuda(), v.cuda()
+    cd, sd, pd = cos.cuda(), sin.cuda(), torch.tensor([pos0], dtype=torch.int32).cuda()
+    out = torch.zeros(n, nh * hd, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    _lib.check(lib.lbk_rope_kv_append_rows(ctx.handle, qd.data_ptr(), knd.data_ptr(), vnd.data_ptr(), cd.data_ptr(), sd.data_ptr(),
+                                           pd.data_ptr(), n, nh, kvh, hd, cap, seq, kd.data_ptr(), vd.data_ptr(), st))
+    _lib.check(lib.lbk_attn_prefill(ctx.handle, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), pd.data_ptr(), n, nh, kvh, hd, cap, seq,
+                                    out.data_ptr(), st))
+    torch.cuda.synchronize()
+    kref, vref = k.clone(), v.clone()
+    kref[seq, :, pos0:pos0 + n] = rope(kn).bfloat16().transpose(0, 1)
+    vref[seq, :, pos0:pos0 + n] = vn.bfloat16().transpose(0, 1)
+    # v is a plain conversion; the rotated k is two products and a sum whose fusing into an fma the
+    # reference does not pin: equal up to one bf16 step, and nearly everywhere exactly
+    kgot = kd.cpu()
+    assert torch.equal(vd.cpu(), vref)
+    assert torch.equal(kgot[1 - seq], k[1 - seq]) and torch.equal(kgot[seq, :, :pos0], k[seq, :, :pos0])
+    dk = (kgot.float() - kref.float()).abs()
+    assert bool((dk <= kref.float().abs() * 2.0 ** -7 + 1e-30).all()) and float((dk != 0).float().mean()) < 1e-3
+    assert int(pd.cpu()[0]) == pos0
+    assert (qd.cpu() - rope(q)).abs().max() < 1e-5
+    qf = rope(q).double().numpy()
+    kf, vf = kgot[seq].double().numpy(), vref[seq].double().numpy()
+    got = out.cpu().numpy().reshape(n, nh, hd)
+    for h in range(nh):
+        kv = h // (nh // kvh)
+        sc = qf[:, h] @ kf[kv].T / np.sqrt(hd)                       # [n][cap]
+        mask = np.arange(cap)[None, :] <= (pos0 + np.arange(n))[:, None]
+        sc = np.where(mask, sc, -np.inf)
+        w = np.exp(sc - sc.max(axis=1, keepdims=True))
+        w /= w.sum(axis=1, keepdims=True)
+        assert np.abs(got[:, h] - w @ vf[kv]).max() < 1e-5
+    ctx.check_device_error()
+
+
+@pytest.mark.parametrize("n", [2, 7, 40, 300])
+def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n):
+    """lbk_model_forward with several tokens (one pass of n rows: GEMV batch up to 16 rows, the
+    tcgen05 GEMM above; causal attention over the cache) against the same tokens fed one call at a
+    time through the decode step, and against the CPU restatement for the first rows. The integer
+    projections are the same for both routes; the float summation orders of attention and of the
+    LM head differ, so the bar is the decoder's own: max |delta logit| <= 2e-3 of max |logit|, the
+    greedy token equal where the margin is clear. A second prompt pass then continues the same
+    cache (positions n..n+4), followed by a decode step."""
+    from lemonade_burn_b200 import model
+    from oracle import decoder_oracle as D
+    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 512)
+    tensors = model.random_checkpoint(cfg, 33)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    nat = model.NativeBitNet(tmp_path, ctx)
+    rng = np.random.default_rng(n)
+    toks = rng.integers(0, cfg.vocab_size, size=n + 6).astype(np.uint32)
+    c_seq, c_pf = nat.new_cache(1, 512), nat.new_cache(1, 512)
+    ref = np.stack([nat.forward([int(t)], c_seq) for t in toks])
+
+    def close(a, r):
+        scale = np.abs(r).max()
+        assert np.abs(a - r).max() <= TOL * scale
+        srt = np.sort(r)
+        if srt[-1] - srt[-2] > 4 * TOL * scale:
+            assert int(np.argmax(a)) == int(np.argmax(r))
+
+    got = nat.forward(toks[:n], c_pf, all_logits=True)
+    assert got.shape == (n, cfg.vocab_size) and nat.cache_len(c_pf) == n
+    for i in range(n):
+        close(got[i], ref[i])
+    last = nat.forward(toks[n:n + 5], c_pf)              # continues the cache; last row's logits only
+    assert nat.cache_len(c_pf) == n + 5
+    close(last, ref[n + 4])
+    close(nat.forward([int(toks[n + 5])], c_pf), ref[n + 5])   # and a decode step on top
+    # the CPU restatement, first rows
+    w = _to_oracle_weights(cfg, tensors)
+    kvh, hd = cfg.num_key_value_heads, cfg.head_dim()
+    okc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+    ovc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+    for i in range(min(n, 4)):
+        close(got[i], D.decode_step(cfg.__dict__, w, int(toks[i]), okc, ovc, i))
+    ctx.check_device_error()
+    nat.close()
