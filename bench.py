@@ -203,6 +203,34 @@ def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
     return {"workload": "BitNet-2B4T-architecture decode step, random init, bf16 KV cache, greedy", "cases": res}
 
 
+def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
+    """Config 3's other half: a prompt of n tokens through the native runtime (lbk_model_forward:
+    checkpoint on disk in the converter's format, up to 1024 rows per pass through the tcgen05 GEMM,
+    tensor-core causal attention, last row's logits back on the host). Wall clock around the
+    synchronous call, best of `reps`, fresh cache each time."""
+    from lemonade_burn_b200 import model
+    cfg = model.Config.bitnet_2b4t(max_pos=max(lengths) + 64)
+    res = []
+    with tempfile.TemporaryDirectory() as d:
+        model.save_checkpoint(d, cfg, model.random_checkpoint(cfg, 11))
+        nat = model.NativeBitNet(d, ctx)
+        rng = np.random.default_rng(5)
+        cache = nat.new_cache(1, max(lengths) + 64)
+        for n in lengths:
+            toks = rng.integers(0, cfg.vocab_size, size=n).astype(np.uint32)
+            times = []
+            for _ in range(reps + 1):   # the first pass allocates the work buffers and is not counted
+                nat.reset_cache(cache)
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                logits = nat.forward(toks, cache)
+                times.append(time.perf_counter() - t0)
+            best = min(times[1:])
+            res.append({"prompt_tokens": n, "ms": best * 1e3, "tok_per_s": n / best, "next_token": int(np.argmax(logits))})
+        nat.close()
+    return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res}
+
+
 # ---------------------------------------------------------------------------------------
 # config 4: 70B-shaped ternary decoder, tensor parallel (column-parallel q/k/v/gate/up,
 # row-parallel o/down with an exact int32 all-reduce), batch-64 decode weight sweep
@@ -622,6 +650,8 @@ def run_ours(args):
     torch.cuda.empty_cache()
     if rank == 0 and world == 1 and "config3" in args.extras:
         extra["config3_decode"] = config3_decode(torch, ctx, device, batches=tuple(args.decode_batches))
+        torch.cuda.empty_cache()
+        extra["config3_prompt"] = config3_prompt(torch, ctx)
         torch.cuda.empty_cache()
     tp_res = None
     if args.tp70b or world > 1:

@@ -460,28 +460,26 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
 // ---- prompt ingestion: n consecutive positions of ONE sequence at once -----------------------------
 // RoPE on the n query rows (in place) and the n new key rows, which are appended with the value
 // rows at positions pos0 .. pos0 + n - 1 of sequence `seq` (model.rs:298-302, 339-341).
-__global__ void rope_append_rows_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
-                                        const float *__restrict__ cos_t, const float *__restrict__ sin_t,
-                                        const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap, int seq,
-                                        uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
+__global__ void __launch_bounds__(256) rope_append_rows_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
+                                                              const float *__restrict__ cos_t, const float *__restrict__ sin_t,
+                                                              const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap, int seq,
+                                                              uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
-    const int row = blockIdx.y, h = blockIdx.x, pos = *pos_dev + row;
+    const int row = blockIdx.x, pos = *pos_dev + row, half = hd >> 1;  // one block per prompt row, all its heads
     const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
-    const int half = hd >> 1;
-    if (h < nh) {
-        float *qh = q + (static_cast<size_t>(row) * nh + h) * hd;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    for (int it = threadIdx.x; it < (nh + kvh) * half; it += blockDim.x) {
+        const int h = it / half, i = it - h * half;
+        if (h < nh) {
+            float *qh = q + (static_cast<size_t>(row) * nh + h) * hd;
             const float x1 = qh[i], x2 = qh[i + half];
             qh[i] = x1 * c[i] + (-x2) * s[i];
             qh[i + half] = x2 * c[i + half] + x1 * s[i + half];
-        }
-    } else {
-        const int kh = h - nh;
-        const float *kk = k + (static_cast<size_t>(row) * kvh + kh) * hd;
-        const float *vv = v + (static_cast<size_t>(row) * kvh + kh) * hd;
-        const size_t slot = ((static_cast<size_t>(seq) * kvh + kh) * cap + pos) * hd;
-        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        } else {
+            const int kh = h - nh;
+            const float *kk = k + (static_cast<size_t>(row) * kvh + kh) * hd;
+            const float *vv = v + (static_cast<size_t>(row) * kvh + kh) * hd;
+            const size_t slot = ((static_cast<size_t>(seq) * kvh + kh) * cap + pos) * hd;
             const float x1 = kk[i], x2 = kk[i + half];
             kcache[slot + i] = f32_to_bf16(x1 * c[i] + (-x2) * s[i]);
             kcache[slot + i + half] = f32_to_bf16(x2 * c[i + half] + x1 * s[i + half]);
@@ -491,77 +489,167 @@ __global__ void rope_append_rows_kernel(float *__restrict__ q, const float *__re
     }
 }
 
-// Causal attention of n query rows of one sequence over its cache: block (kv head, row) walks the
-// keys 0 .. pos0 + row in chunks of 32 positions staged in shared memory (the layout and the two
-// inner products are those of attn_partial_staged_kernel) and writes the normalised result itself:
-// no slices, no merge. The keys of a layer fit the L2, so the rows re-read them from there.
-__global__ void __launch_bounds__(256) attn_rows_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
-                                                       const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev, int nh, int kvh,
-                                                       int cap, int seq, float scaling, float *__restrict__ out /* [n][nh*hd] */) {
+// Causal attention of n query rows of one sequence over its cache, on the tensor cores: a block
+// takes one KV head and 16-row tiles of the query heads that share it (one warp per (head, tile): 16 query rows x 128 dimensions),
+// walks the keys in chunks of 64 staged in shared memory as bf16 and keeps the running softmax in
+// the accumulator layout of mma.sync m16n8k16 (scores S = Q K^T: 8 tiles of 16x8; output O += P V:
+// 16 tiles of 16x8). The f32 queries and the probabilities are each split into two bf16 terms
+// (x = hi + lo, |error| <= 2^-17 |x|), so that the only rounding beyond f32 summation is the bf16
+// of the cache itself, as in the decode kernels. Row i of the prompt sees keys 0 .. pos0 + i.
+constexpr int kPfKeys = 64;          // keys per staged chunk
+constexpr int kPfRow = kHd * 2 + 16; // bytes per staged row: eight consecutive rows start in eight different 16-byte bank groups
+constexpr int kPfQWarp = 2 * 16 * kPfRow;  // one warp's queries: hi and lo, 16 rows each
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo_elem, float hi_elem) {
+    return static_cast<uint32_t>(f32_to_bf16(lo_elem)) | (static_cast<uint32_t>(f32_to_bf16(hi_elem)) << 16);
+}
+__device__ __forceinline__ float bf16_round(float x) { return bf16_to_f32(f32_to_bf16(x)); }
+
+__global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
+                                                             const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev, int n, int nh,
+                                                             int kvh, int cap, int seq, float scaling, float *__restrict__ out /* [n][nh*hd] */) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
-    __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];
-    __shared__ __align__(16) uint8_t s_v[kAttnChunk * kVRow];
-    __shared__ __align__(16) float s_q[8 * kHd];
-    const int kh = blockIdx.x, row = blockIdx.y;
-    const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
-    const int total = *pos_dev + row + 1;  // keys 0 .. this row's own position
-    const int head = kh * group + warp;
-    for (int i = tid; i < group * kHd; i += nthr) s_q[i] = q[(static_cast<size_t>(row) * nh + kh * group) * kHd + i] * scaling;
+    extern __shared__ __align__(16) uint8_t pf_smem[];
+    uint8_t *s_k = pf_smem, *s_v = s_k + kPfKeys * kPfRow, *s_q = s_v + kPfKeys * kPfRow;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, nthr = blockDim.x;
+    const int group = nh / kvh, tiles_per_block = (nthr >> 5) / group;
+    const int kh = blockIdx.x, btile = gridDim.y - 1 - blockIdx.y;  // the late rows see the most keys: they start first
+    const int head = kh * group + warp % group;
+    const int row0 = (btile * tiles_per_block + warp / group) * 16;
+    const int pos0 = *pos_dev;
+    // this warp's queries, scaled, as hi + lo
+    uint8_t *qw = s_q + warp * kPfQWarp;
+    for (int r = 0; r < 16; ++r) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (row0 + r < n) x = *reinterpret_cast<const float4 *>(q + (static_cast<size_t>(row0 + r) * nh + head) * kHd + lane * 4);
+        x.x *= scaling; x.y *= scaling; x.z *= scaling; x.w *= scaling;
+        const float hx = bf16_round(x.x), hy = bf16_round(x.y), hz = bf16_round(x.z), hw = bf16_round(x.w);
+        *reinterpret_cast<uint2 *>(qw + r * kPfRow + lane * 8) = make_uint2(pack_bf16(hx, hy), pack_bf16(hz, hw));
+        *reinterpret_cast<uint2 *>(qw + (16 + r) * kPfRow + lane * 8) = make_uint2(pack_bf16(x.x - hx, x.y - hy), pack_bf16(x.z - hz, x.w - hw));
+    }
+    __syncwarp();
+    const int block_rows_end = min(n, (btile + 1) * tiles_per_block * 16);
+    const int total = pos0 + block_rows_end;             // keys 0 .. total-1 are seen by some row of the block
+    const int lim0 = pos0 + row0 + g, lim1 = lim0 + 8;   // the last key this thread's two rows see
     const uint16_t *kb = kc + (static_cast<size_t>(seq) * kvh + kh) * cap * kHd;
     const uint16_t *vb = vc + (static_cast<size_t>(seq) * kvh + kh) * cap * kHd;
-    float mx = -INFINITY, sum = 0.0f;
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int pc = 0; pc < total; pc += kAttnChunk) {
-        const int n = min(kAttnChunk, total - pc);
-        __syncthreads();
-        for (int i = tid; i < n * 16; i += nthr) {
-            const int r = i >> 4, seg = i & 15;
-            *reinterpret_cast<uint4 *>(s_k + r * kKRow + seg * 16) = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + seg * 8);
-            *reinterpret_cast<uint4 *>(s_v + r * kVRow + seg * 16) = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + seg * 8);
-        }
-        __syncthreads();
-        float sc = -INFINITY;
-        if (lane < n) {
-            const uint8_t *kr = s_k + lane * kKRow;
-            const float *qh = s_q + warp * kHd;
-            float d0 = 0.f, d1 = 0.f;
+    // ldmatrix lane addresses (see the fragment layouts of mma.m16n8k16)
+    const uint32_t q_hi = ptx::smem_u32(qw) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
+    const uint32_t q_lo = q_hi + 16 * kPfRow;
+    const uint32_t k_lane = ptx::smem_u32(s_k) + (lane & 7) * kPfRow + (lane >> 3) * 16;
+    const uint32_t v_lane = ptx::smem_u32(s_v) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
+    float o[16][4];
 #pragma unroll
-            for (int it = 0; it < kHd / 8; ++it) {
-                const uint4 kk = *reinterpret_cast<const uint4 *>(kr + it * 16);
-                const float4 qa = *reinterpret_cast<const float4 *>(qh + it * 8), qb = *reinterpret_cast<const float4 *>(qh + it * 8 + 4);
-                d0 += qa.x * bf16_to_f32(kk.x & 0xffff) + qa.y * bf16_to_f32(kk.x >> 16) + qa.z * bf16_to_f32(kk.y & 0xffff) +
-                      qa.w * bf16_to_f32(kk.y >> 16);
-                d1 += qb.x * bf16_to_f32(kk.z & 0xffff) + qb.y * bf16_to_f32(kk.z >> 16) + qb.z * bf16_to_f32(kk.w & 0xffff) +
-                      qb.w * bf16_to_f32(kk.w >> 16);
+    for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
+    for (int pc = 0; pc < total; pc += kPfKeys) {
+        const int cnt = min(kPfKeys, total - pc);
+        __syncthreads();
+        for (int i = tid; i < kPfKeys * 16; i += nthr) {
+            const int r = i >> 4, sg = i & 15;
+            uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;  // rows past the end hold zeros: their weights are zero, their bits must be numbers
+            if (r < cnt) {
+                kk = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + sg * 8);
+                vv = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + sg * 8);
             }
-            sc = d0 + d1;
+            *reinterpret_cast<uint4 *>(s_k + r * kPfRow + sg * 16) = kk;
+            *reinterpret_cast<uint4 *>(s_v + r * kPfRow + sg * 16) = vv;
         }
-        float nm = sc;
+        __syncthreads();
+        if (pc > pos0 + row0 + 15) continue;  // none of this warp's rows sees this chunk (the barriers are at the loop's top)
+        float s[8][4];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) nm = fmaxf(nm, __shfl_xor_sync(0xffffffffu, nm, o));
-        nm = fmaxf(nm, mx);
-        const float corr = __expf(mx - nm);
-        const float w = lane < n ? __expf(sc - nm) : 0.0f;
-        float ws = w;
+        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ws += __shfl_xor_sync(0xffffffffu, ws, o);
-        sum = sum * corr + ws;
-        acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
-        const uint8_t *vr = s_v + lane * 8;
-#pragma unroll 8
-        for (int p = 0; p < n; ++p) {
-            const float wp = __shfl_sync(0xffffffffu, w, p);
-            const uint2 vv = *reinterpret_cast<const uint2 *>(vr + p * kVRow);
-            acc.x += wp * bf16_to_f32(vv.x & 0xffff);
-            acc.y += wp * bf16_to_f32(vv.x >> 16);
-            acc.z += wp * bf16_to_f32(vv.y & 0xffff);
-            acc.w += wp * bf16_to_f32(vv.y >> 16);
+        for (int kp = 0; kp < 4; ++kp) {  // 32 dimensions at a time
+            uint32_t ah0[4], al0[4], ah1[4], al1[4];
+            ptx::ldmatrix_x4(ah0, q_hi + kp * 64);
+            ptx::ldmatrix_x4(al0, q_lo + kp * 64);
+            ptx::ldmatrix_x4(ah1, q_hi + kp * 64 + 32);
+            ptx::ldmatrix_x4(al1, q_lo + kp * 64 + 32);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint32_t b[4];
+                ptx::ldmatrix_x4(b, k_lane + j * 8 * kPfRow + kp * 64);
+                ptx::mma_bf16(s[j], ah0, b[0], b[1]);
+                ptx::mma_bf16(s[j], al0, b[0], b[1]);
+                ptx::mma_bf16(s[j], ah1, b[2], b[3]);
+                ptx::mma_bf16(s[j], al1, b[2], b[3]);
+            }
         }
-        mx = nm;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int key = pc + 8 * j + 2 * t;
+            if (key > lim0) s[j][0] = -INFINITY;
+            if (key + 1 > lim0) s[j][1] = -INFINITY;
+            if (key > lim1) s[j][2] = -INFINITY;
+            if (key + 1 > lim1) s[j][3] = -INFINITY;
+            mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[j][2], s[j][3]));
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        // key 0 is visible to every row and lies in the first chunk, so the maxima are finite from there on
+        const float nm0 = fmaxf(m0, mx0), nm1 = fmaxf(m1, mx1);
+        const float corr0 = __expf(m0 - nm0), corr1 = __expf(m1 - nm1);
+        m0 = nm0;
+        m1 = nm1;
+        float ps0 = 0.0f, ps1 = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            s[j][0] = __expf(s[j][0] - nm0);
+            s[j][1] = __expf(s[j][1] - nm0);
+            s[j][2] = __expf(s[j][2] - nm1);
+            s[j][3] = __expf(s[j][3] - nm1);
+            ps0 += s[j][0] + s[j][1];
+            ps1 += s[j][2] + s[j][3];
+        }
+        l0 = l0 * corr0 + ps0;  // this thread's share of the row sums; the four lanes of a row meet at the end
+        l1 = l1 * corr1 + ps1;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            o[j][0] *= corr0; o[j][1] *= corr0;
+            o[j][2] *= corr1; o[j][3] *= corr1;
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {  // 16 keys at a time
+            if (pc + 16 * kk > pos0 + row0 + 15) break;  // the rest of the chunk is masked for the whole tile
+            uint32_t ph[4], pl[4];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {  // score tiles 2kk and 2kk+1 are the two key halves of this step
+                const float *sv = s[2 * kk + h];
+                const float h0 = bf16_round(sv[0]), h1 = bf16_round(sv[1]), h2 = bf16_round(sv[2]), h3 = bf16_round(sv[3]);
+                ph[2 * h] = pack_bf16(h0, h1);
+                ph[2 * h + 1] = pack_bf16(h2, h3);
+                pl[2 * h] = pack_bf16(sv[0] - h0, sv[1] - h1);
+                pl[2 * h + 1] = pack_bf16(sv[2] - h2, sv[3] - h3);
+            }
+#pragma unroll
+            for (int jp = 0; jp < 8; ++jp) {  // 16 dimensions at a time
+                uint32_t b[4];
+                ptx::ldmatrix_x4_trans(b, v_lane + kk * 16 * kPfRow + jp * 32);
+                ptx::mma_bf16(o[2 * jp], ph, b[0], b[1]);
+                ptx::mma_bf16(o[2 * jp], pl, b[0], b[1]);
+                ptx::mma_bf16(o[2 * jp + 1], ph, b[2], b[3]);
+                ptx::mma_bf16(o[2 * jp + 1], pl, b[2], b[3]);
+            }
+        }
     }
-    const float inv = 1.0f / sum;
-    *reinterpret_cast<float4 *>(out + (static_cast<size_t>(row) * nh + head) * kHd + lane * 4) = make_float4(acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    const float inv0 = 1.0f / l0, inv1 = 1.0f / l1;
+    const int r0 = row0 + g, r1 = r0 + 8;
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        if (r0 < n) *reinterpret_cast<float2 *>(out + (static_cast<size_t>(r0) * nh + head) * kHd + 8 * j + 2 * t) = make_float2(o[j][0] * inv0, o[j][1] * inv0);
+        if (r1 < n) *reinterpret_cast<float2 *>(out + (static_cast<size_t>(r1) * nh + head) * kHd + 8 * j + 2 * t) = make_float2(o[j][2] * inv1, o[j][3] * inv1);
+    }
 }
 
 __global__ void __launch_bounds__(256) attn_combine_kernel(const float *__restrict__ part, int splits,
@@ -842,9 +930,7 @@ int lbk_rope_kv_append_rows(lbk_ctx *c, float *q_dev, const float *k_dev, const 
     if (!q_dev || !k_dev || !v_dev || !cos_dev || !sin_dev || !pos_dev || !kcache_dev || !vcache_dev)
         return fail(LBK_ERR_INVALID, "lbk_rope_kv_append_rows: null buffer");
     if (head_dim == 0 || (head_dim & 1)) return fail(LBK_ERR_INVALID, "head_dim must be even");
-    if (n > 65535) return fail(LBK_ERR_UNSUPPORTED, "at most 65535 rows per call");
-    dim3 grid(static_cast<unsigned>(n_heads + kv_heads), static_cast<unsigned>(n));
-    LBK_CUDA(launch_chained(rope_append_rows_kernel, grid, dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
+    LBK_CUDA(launch_chained(rope_append_rows_kernel, dim3(static_cast<unsigned>(n)), dim3(256), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
                             static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap), static_cast<int>(seq), kcache_dev,
                             vcache_dev));
     LBK_DEC_POST();
@@ -858,9 +944,18 @@ int lbk_attn_prefill(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev,
     if (head_dim != kHd) return fail(LBK_ERR_UNSUPPORTED, "attention kernel is built for head_dim 128, got %zu", head_dim);
     if (kv_heads == 0 || n_heads % kv_heads || n_heads / kv_heads > 8) return fail(LBK_ERR_UNSUPPORTED, "query group size must be 1..8");
     if (n > 65535) return fail(LBK_ERR_UNSUPPORTED, "at most 65535 rows per call");
-    dim3 grid(static_cast<unsigned>(kv_heads), static_cast<unsigned>(n));
-    LBK_CUDA(launch_chained(attn_rows_kernel, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev,
-                            pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap), static_cast<int>(seq),
+    const size_t group = n_heads / kv_heads;
+    const size_t warps = (group == 1 || group == 2) ? 4 : group;  // one warp per (query head, 16-row tile)
+    const size_t rows_per_block = warps / group * 16;
+    const size_t smem = 2 * kPfKeys * kPfRow + warps * kPfQWarp;
+    static bool attr_set = false;  // the same value for every call; setting it twice is harmless
+    if (!attr_set) {
+        LBK_CUDA(cudaFuncSetAttribute(attn_prompt_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kPfKeys * kPfRow + 8 * kPfQWarp));
+        attr_set = true;
+    }
+    dim3 grid(static_cast<unsigned>(kv_heads), static_cast<unsigned>((n + rows_per_block - 1) / rows_per_block));
+    LBK_CUDA(launch_chained(attn_prompt_mma_kernel, grid, dim3(static_cast<unsigned>(32 * warps)), smem, st, q_dev, kcache_dev, vcache_dev, pos_dev,
+                            static_cast<int>(n), static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap), static_cast<int>(seq),
                             1.0f / sqrtf(static_cast<float>(head_dim)), out_dev));
     LBK_DEC_POST();
 }

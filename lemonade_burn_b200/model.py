@@ -317,6 +317,10 @@ class NativeBitNet:
     def cache_len(self, cache) -> int:
         return int(self._lib.lbk_kv_cache_len(cache))
 
+    def reset_cache(self, cache) -> None:
+        """Back to an empty sequence; the buffers and the recorded step are kept."""
+        _lib.check(self._lib.lbk_kv_cache_reset(cache))
+
     def forward(self, tokens, cache, all_logits: bool = False) -> np.ndarray:
         """model.rs:305: logits [n, vocab] (all_logits) or [vocab] of the last token, on the host."""
         toks = np.ascontiguousarray(tokens, dtype=np.uint32)
