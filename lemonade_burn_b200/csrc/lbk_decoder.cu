@@ -491,7 +491,8 @@ __global__ void __launch_bounds__(256) rope_append_rows_kernel(float *__restrict
 
 // Causal attention of n query rows of one sequence over its cache, on the tensor cores: a block
 // takes one KV head and 16-row tiles of the query heads that share it (one warp per (head, tile): 16 query rows x 128 dimensions),
-// walks the keys in chunks of 64 staged in shared memory as bf16 and keeps the running softmax in
+// walks the keys in chunks of 64 staged in shared memory as bf16 (two stages: the next chunk's
+// asynchronous copies run under this chunk's arithmetic) and keeps the running softmax in
 // the accumulator layout of mma.sync m16n8k16 (scores S = Q K^T: 8 tiles of 16x8; output O += P V:
 // 16 tiles of 16x8). The f32 queries and the probabilities are each split into two bf16 terms
 // (x = hi + lo, |error| <= 2^-17 |x|), so that the only rounding beyond f32 summation is the bf16
@@ -499,6 +500,7 @@ __global__ void __launch_bounds__(256) rope_append_rows_kernel(float *__restrict
 constexpr int kPfKeys = 64;          // keys per staged chunk
 constexpr int kPfRow = kHd * 2 + 16; // bytes per staged row: eight consecutive rows start in eight different 16-byte bank groups
 constexpr int kPfQWarp = 2 * 16 * kPfRow;  // one warp's queries: hi and lo, 16 rows each
+constexpr int kPfStage = 2 * kPfKeys * kPfRow;  // one staged chunk: keys, then values
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo_elem, float hi_elem) {
     return static_cast<uint32_t>(f32_to_bf16(lo_elem)) | (static_cast<uint32_t>(f32_to_bf16(hi_elem)) << 16);
@@ -511,7 +513,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
     ptx::pdl_trigger();
     ptx::pdl_wait();
     extern __shared__ __align__(16) uint8_t pf_smem[];
-    uint8_t *s_k = pf_smem, *s_v = s_k + kPfKeys * kPfRow, *s_q = s_v + kPfKeys * kPfRow;
+    uint8_t *s_kv = pf_smem, *s_q = pf_smem + 2 * kPfStage;  // two stages of [K chunk][V chunk], then the queries
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, nthr = blockDim.x;
     const int group = nh / kvh, tiles_per_block = (nthr >> 5) / group;
     const int kh = blockIdx.x, btile = gridDim.y - 1 - blockIdx.y;  // the late rows see the most keys: they start first
@@ -537,27 +539,41 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
     // ldmatrix lane addresses (see the fragment layouts of mma.m16n8k16)
     const uint32_t q_hi = ptx::smem_u32(qw) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
     const uint32_t q_lo = q_hi + 16 * kPfRow;
-    const uint32_t k_lane = ptx::smem_u32(s_k) + (lane & 7) * kPfRow + (lane >> 3) * 16;
-    const uint32_t v_lane = ptx::smem_u32(s_v) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
+    const uint32_t k_lane0 = ptx::smem_u32(s_kv) + (lane & 7) * kPfRow + (lane >> 3) * 16;
+    const uint32_t v_lane0 = ptx::smem_u32(s_kv) + kPfKeys * kPfRow + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
+    // chunk `pc` into stage `buf`: asynchronous copies, one group per chunk; rows past the end are zeros
+    // (their weights are zero, but their bits must be numbers)
+    auto stage = [&](int buf, int pc) {
+        const int cnt = min(kPfKeys, total - pc);
+        uint8_t *dk = s_kv + buf * kPfStage, *dv = dk + kPfKeys * kPfRow;
+        for (int i = tid; i < kPfKeys * 16; i += nthr) {
+            const int r = i >> 4, sg = i & 15;
+            if (r < cnt) {
+                ptx::cp_async_16(ptx::smem_u32(dk + r * kPfRow + sg * 16), kb + static_cast<size_t>(pc + r) * kHd + sg * 8);
+                ptx::cp_async_16(ptx::smem_u32(dv + r * kPfRow + sg * 16), vb + static_cast<size_t>(pc + r) * kHd + sg * 8);
+            } else {
+                *reinterpret_cast<uint4 *>(dk + r * kPfRow + sg * 16) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4 *>(dv + r * kPfRow + sg * 16) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+        ptx::cp_async_commit();
+    };
     float o[16][4];
 #pragma unroll
     for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-    for (int pc = 0; pc < total; pc += kPfKeys) {
-        const int cnt = min(kPfKeys, total - pc);
-        __syncthreads();
-        for (int i = tid; i < kPfKeys * 16; i += nthr) {
-            const int r = i >> 4, sg = i & 15;
-            uint4 kk = make_uint4(0u, 0u, 0u, 0u), vv = kk;  // rows past the end hold zeros: their weights are zero, their bits must be numbers
-            if (r < cnt) {
-                kk = *reinterpret_cast<const uint4 *>(kb + static_cast<size_t>(pc + r) * kHd + sg * 8);
-                vv = *reinterpret_cast<const uint4 *>(vb + static_cast<size_t>(pc + r) * kHd + sg * 8);
-            }
-            *reinterpret_cast<uint4 *>(s_k + r * kPfRow + sg * 16) = kk;
-            *reinterpret_cast<uint4 *>(s_v + r * kPfRow + sg * 16) = vv;
+    stage(0, 0);
+    for (int pc = 0, it = 0; pc < total; pc += kPfKeys, ++it) {
+        if (it) __syncthreads();  // everyone is done with the stage that the next chunk overwrites
+        if (pc + kPfKeys < total) {
+            stage((it & 1) ^ 1, pc + kPfKeys);
+            ptx::cp_async_wait<1>();
+        } else {
+            ptx::cp_async_wait<0>();
         }
-        __syncthreads();
+        __syncthreads();  // this chunk has landed, for every thread's copies
         if (pc > pos0 + row0 + 15) continue;  // none of this warp's rows sees this chunk (the barriers are at the loop's top)
+        const uint32_t k_lane = k_lane0 + (it & 1) * kPfStage, v_lane = v_lane0 + (it & 1) * kPfStage;
         float s[8][4];
 #pragma unroll
         for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
@@ -947,10 +963,10 @@ int lbk_attn_prefill(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev,
     const size_t group = n_heads / kv_heads;
     const size_t warps = (group == 1 || group == 2) ? 4 : group;  // one warp per (query head, 16-row tile)
     const size_t rows_per_block = warps / group * 16;
-    const size_t smem = 2 * kPfKeys * kPfRow + warps * kPfQWarp;
+    const size_t smem = 2 * kPfStage + warps * kPfQWarp;
     static bool attr_set = false;  // the same value for every call; setting it twice is harmless
     if (!attr_set) {
-        LBK_CUDA(cudaFuncSetAttribute(attn_prompt_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kPfKeys * kPfRow + 8 * kPfQWarp));
+        LBK_CUDA(cudaFuncSetAttribute(attn_prompt_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * kPfStage + 8 * kPfQWarp));
         attr_set = true;
     }
     dim3 grid(static_cast<unsigned>(kv_heads), static_cast<unsigned>((n + rows_per_block - 1) / rows_per_block));
