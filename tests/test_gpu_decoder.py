@@ -377,18 +377,19 @@ def test_prefill_rows_against_numpy(ctx, pos0, n, nh, kvh):
     ctx.check_device_error()
 
 
-@pytest.mark.parametrize("n", [2, 7, 40, 300])
-def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n):
+@pytest.mark.parametrize("n,wide", [(2, False), (7, False), (40, False), (300, False), (70, True)])
+def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
     """lbk_model_forward with several tokens (one pass of n rows: GEMV batch up to 16 rows, the
     tcgen05 GEMM above; causal attention over the cache) against the same tokens fed one call at a
     time through the decode step, and against the CPU restatement for the first rows. The integer
     projections are the same for both routes; the float summation orders of attention and of the
     LM head differ, so the bar is the decoder's own: max |delta logit| <= 2e-3 of max |logit|, the
     greedy token equal where the margin is clear. A second prompt pass then continues the same
-    cache (positions n..n+4), followed by a decode step."""
+    cache (positions n..n+4), followed by a decode step. `wide`: BitNet-2B4T layer shapes (hidden 2560,
+    20/5 heads, intermediate 6912), two layers, reduced vocabulary."""
     from lemonade_burn_b200 import model
     from oracle import decoder_oracle as D
-    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 512)
+    cfg = model.Config(2560, 6912, 20, 5, 2, 8000, 1e-5, 500000.0, 512) if wide else model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 512)
     tensors = model.random_checkpoint(cfg, 33)
     model.save_checkpoint(tmp_path, cfg, tensors)
     nat = model.NativeBitNet(tmp_path, ctx)
@@ -417,7 +418,7 @@ def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n):
     kvh, hd = cfg.num_key_value_heads, cfg.head_dim()
     okc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
     ovc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
-    for i in range(min(n, 4)):
+    for i in range(min(n, 2 if wide else 4)):
         close(got[i], D.decode_step(cfg.__dict__, w, int(toks[i]), okc, ovc, i))
     ctx.check_device_error()
     nat.close()
