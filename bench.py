@@ -231,6 +231,38 @@ def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
     return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res}
 
 
+def converter_pass(torch, ctx, device, layers=30):
+    """The converter's arithmetic for a whole BitNet-2B4T-shaped model: 7 x `layers` bf16 master
+    tensors N(0, 0.02) resident on the device -> scales, packed rows and counts (two launches per
+    tensor: f64 absmean, then ternarise + pack). Algorithmic bytes: the masters are read twice and a
+    quarter byte per weight is written. The digests are timed apart (a chain per tensor, one GPU
+    thread each). Beside it the CPU restatement of the same work on one tensor, one thread."""
+    from lemonade_burn_b200 import convert
+    from oracle import oracle as O
+    shapes = [(2560, 2560), (640, 2560), (640, 2560), (2560, 2560), (6912, 2560), (6912, 2560), (2560, 6912)]
+    g = torch.Generator(device=device).manual_seed(17)
+    ws = [(0.02 * torch.randn(r, c, generator=g, device=device)).to(torch.bfloat16) for _ in range(layers) for r, c in shapes]
+    weights = sum(w.numel() for w in ws)
+    convert.convert_bitlinear(ws[:7], ctx, sha=False)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    res = convert.convert_bitlinear(ws, ctx, sha=False)
+    dt = time.perf_counter() - t0
+    t0 = time.perf_counter()
+    convert.convert_bitlinear(ws, ctx, sha=True)
+    dt_sha = time.perf_counter() - t0
+    w0 = ws[4].float().cpu().numpy()
+    t0 = time.perf_counter()
+    t, scale = O.ternarize_absmean(w0)
+    packed = O.pack_matrix(t)
+    dt_cpu = time.perf_counter() - t0
+    same = bool(np.array_equal(res[4].packed.cpu().numpy(), packed)) and np.float32(scale).tobytes() == np.float32(res[4].scale).tobytes()
+    nbytes = weights * 4.25
+    return {"workload": f"{len(ws)} bf16 tensors, {weights} weights", "ms": dt * 1e3, "GBps": nbytes / dt / 1e9,
+            "algorithmic_bytes": nbytes, "weights_per_s": weights / dt, "ms_with_sha256": dt_sha * 1e3,
+            "cpu_port_one_thread_weights_per_s": w0.size / dt_cpu, "matches_cpu_port": same}
+
+
 # ---------------------------------------------------------------------------------------
 # config 4: 70B-shaped ternary decoder, tensor parallel (column-parallel q/k/v/gate/up,
 # row-parallel o/down with an exact int32 all-reduce), batch-64 decode weight sweep
@@ -653,6 +685,9 @@ def run_ours(args):
         torch.cuda.empty_cache()
         extra["config3_prompt"] = config3_prompt(torch, ctx)
         torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and "convert" in args.extras:
+        extra["converter"] = converter_pass(torch, ctx, device)
+        torch.cuda.empty_cache()
     tp_res = None
     if args.tp70b or world > 1:
         tp_res = tp70b_sweep(torch, dist, ctx, device, world, rank, layers=args.tp_layers)
@@ -692,8 +727,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tp70b", action="store_true", help="also time the 70B-shaped tensor-parallel sweep at N=1")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS)
-    ap.add_argument("--extras", default="config0,config2,config3",
-                    help="side measurements to add under `extra` (comma list of config0, config2, config3; 'none' for a profiler run)")
+    ap.add_argument("--extras", default="config0,config2,config3,convert",
+                    help="side measurements to add under `extra` (comma list of config0, config2, config3, convert; 'none' for a profiler run)")
     ap.add_argument("--decode-batches", type=int, nargs="+", default=[1, 16], help="batch sizes of the config-3 decode step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

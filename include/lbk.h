@@ -342,6 +342,27 @@ const float *lbk_plan_output_arena(const lbk_plan *plan);
 size_t lbk_plan_weight_bytes(const lbk_plan *plan);
 int lbk_plan_destroy(lbk_plan *plan);
 
+/* ---- converter: master weights -> packed ternary, on the device --------------------------------
+ * lb-convert's per-tensor work (crates/lb-convert/src/main.rs:62-87) for n BitLinear weights at
+ * once: absmean scale with an f64 sum (lb-ternary/src/pack.rs:129-138), ternary values
+ * clamp(round_ties_even(w * scale), -1, 1) (pack.rs:140-142), packed rows in the layout of
+ * pack.rs:88-103 (padding columns hold zero weights). src_dev: [rows][cols] row-major, f32 or bf16
+ * bits; packed_dev: rows * padded(cols)/4 bytes, 4-byte aligned. On the host afterwards:
+ * scales_out[n] (the stored `wscale` = 1/mean|W|), counts_out[n][3] (how many -1, 0, +1; may be
+ * NULL) and sha256_out[n][32] (digest of the int8 ternary array [rows*cols], the value the
+ * converter's --check compares with torch, main.rs:141-170; may be NULL: one GPU thread per
+ * tensor walks the digest chain, about 0.1 s per million weights, all tensors side by side).
+ * Synchronises `stream`. */
+#define LBK_DTYPE_F32 0
+#define LBK_DTYPE_BF16 1
+typedef struct lbk_convert_item {
+    const void *src_dev;
+    size_t rows, cols;
+    uint8_t *packed_dev;
+} lbk_convert_item;
+int lbk_convert_bitlinear(lbk_ctx *ctx, const lbk_convert_item *items, size_t n, int src_dtype, float *scales_out,
+                          uint64_t *counts_out, uint8_t *sha256_out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -84,6 +84,7 @@ SYMBOLS = [
     ("lbk_kv_cache_free", _i, [_vp]),
     ("lbk_model_forward", _i, [_vp, _vp, _vp, _sz, _i, _vp]),
     ("lbk_model_decode", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    ("lbk_convert_bitlinear", _i, [_vp, _vp, _sz, _i, _vp, _vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),
     ("lbk_plan_finalize", _i, [_vp]),

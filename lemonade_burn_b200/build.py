@@ -11,7 +11,7 @@ ROOT = PKG.parent
 CSRC = PKG / "csrc"
 LIB = PKG / "liblbk.so"
 
-SOURCES = ["lbk_api.cu", "lbk_gemv.cu", "lbk_quant.cu", "lbk_bf16.cu", "lbk_plan.cu", "lbk_sweep.cu", "lbk_gemm.cu", "lbk_noalloc.cu", "lbk_decoder.cu", "lbk_tp.cu", "lbk_model.cu"]
+SOURCES = ["lbk_api.cu", "lbk_gemv.cu", "lbk_quant.cu", "lbk_bf16.cu", "lbk_plan.cu", "lbk_sweep.cu", "lbk_gemm.cu", "lbk_noalloc.cu", "lbk_decoder.cu", "lbk_tp.cu", "lbk_model.cu", "lbk_convert.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "-shared",
