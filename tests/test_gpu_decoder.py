@@ -317,7 +317,7 @@ def test_native_runtime_matches_python_mirror(ctx, tmp_path):
         model.NativeBitNet(tmp_path, ctx)
 
 
-@pytest.mark.parametrize("pos0,n,nh,kvh", [(0, 1, 8, 2), (0, 37, 8, 2), (5, 64, 20, 5), (100, 33, 4, 4), (0, 130, 16, 2)])
+@pytest.mark.parametrize("pos0,n,nh,kvh", [(0, 1, 8, 2), (0, 37, 8, 2), (5, 64, 20, 5), (100, 33, 4, 4), (0, 130, 16, 2), (1024, 1024, 20, 5)])
 def test_prefill_rows_against_numpy(ctx, pos0, n, nh, kvh):
     """lbk_rope_kv_append_rows + lbk_attn_prefill (n prompt rows of one sequence at once) against
     RoPE + causal softmax(qK/sqrt(d))V in float64 over a cache that already holds pos0 positions:
