@@ -93,10 +93,12 @@ __global__ void __launch_bounds__(kCvThreads) absmean_partial_kernel(const void 
     }
 }
 
+// clamp(round_ties_even(x), -1, 1) + 1 for x = w * scale: +1 exactly when x > 0.5 (0.5 itself rounds to
+// the even 0), -1 exactly when x < -0.5; a NaN fails both comparisons and becomes 0, as the reference's
+// cast to i8 makes it.
 __device__ __forceinline__ uint32_t ternary_code(float w, float scale) {
-    const float t = rintf(__fmul_rn(w, scale));  // round half to even
-    if (!(t == t)) return 1u;                    // NaN: clamp keeps it, the cast to i8 gives 0
-    return t >= 1.0f ? 2u : (t <= -1.0f ? 0u : 1u);
+    const float x = __fmul_rn(w, scale);
+    return 1u + static_cast<uint32_t>(x > 0.5f) - static_cast<uint32_t>(x < -0.5f);
 }
 
 // Eight lanes share a 128-weight block: lane q of them owns bytes 4q..4q+3, i.e. columns
@@ -308,8 +310,8 @@ int lbk_convert_bitlinear(lbk_ctx *c, const lbk_convert_item *items, size_t n, i
     for (size_t i = 0; i < n; ++i) {
         const lbk_convert_item &it = items[i];
         const size_t elems = it.rows * it.cols;
-        const size_t per_block = static_cast<size_t>(kCvThreads) * 64;
-        const int blocks_a = static_cast<int>(std::min<size_t>(std::min<size_t>(kCvPartials, static_cast<size_t>(ctx->sm_count) * 4), (elems + per_block - 1) / per_block));
+        const size_t per_block = static_cast<size_t>(kCvThreads) * 32;
+        const int blocks_a = static_cast<int>(std::min<size_t>(std::min<size_t>(kCvPartials, static_cast<size_t>(ctx->sm_count) * 6), (elems + per_block - 1) / per_block));
         const size_t pack_items = it.rows * ((it.cols + 127) / 128) * 8;
         const int blocks_t = static_cast<int>(std::min<size_t>(static_cast<size_t>(ctx->sm_count) * 8, (pack_items + kCvThreads - 1) / kCvThreads));
         double *partial = wk.partial + i * kCvPartials;
