@@ -249,6 +249,21 @@ int lbk_attn_prefill(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_de
  * the caches by the kernel. scratch as for lbk_attn_decode; counters_dev: b * kv_heads ints, zero
  * before the first call (the kernel leaves them zero). */
 int lbk_attn_decode_fused_supported(size_t n_heads, size_t kv_heads, size_t head_dim, size_t splits);
+/* The `_seq` forms read ONE POSITION PER SEQUENCE (pos_dev: b ints), for batches whose sequences
+ * have different lengths (continuous batching; the reference has no batch dimension). Everything
+ * else as in the forms above, which use pos_dev[0] for all sequences. lbk_advance_pos_seq adds one
+ * to the positions whose active_dev entry is non-zero (to all when active_dev is NULL). */
+int lbk_rope_kv_append_seq(lbk_ctx *ctx, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                           const float *sin_dev, const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads,
+                           size_t head_dim, size_t cap, uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream);
+int lbk_attn_decode_seq(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev,
+                        const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                        size_t splits, float *scratch_dev, float *out_dev, void *stream);
+int lbk_attn_decode_fused_seq(lbk_ctx *ctx, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                              const float *sin_dev, const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads,
+                              size_t head_dim, size_t cap, size_t splits, uint16_t *kcache_dev, uint16_t *vcache_dev,
+                              float *scratch_dev, int32_t *counters_dev, float *out_dev, void *stream);
+int lbk_advance_pos_seq(lbk_ctx *ctx, int32_t *pos_dev, const int32_t *active_dev, size_t b, void *stream);
 int lbk_attn_decode_fused(lbk_ctx *ctx, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
                           const float *sin_dev, const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads,
                           size_t head_dim, size_t cap, size_t splits, uint16_t *kcache_dev, uint16_t *vcache_dev,
@@ -312,6 +327,34 @@ int lbk_model_forward(lbk_model *model, lbk_kv_cache *cache, const uint32_t *tok
                       float *logits_out);
 int lbk_model_decode(lbk_model *model, lbk_kv_cache *cache, const int32_t *tokens_dev, float *logits_dev,
                      int32_t *next_dev, void *stream);
+/* Length of sequence `seq` of a cache (lbk_kv_cache_len is sequence 0). */
+size_t lbk_kv_cache_len_seq(const lbk_kv_cache *cache, size_t seq);
+
+/* ---- continuous batching ------------------------------------------------------------------------
+ * The reference's server hands requests to ONE worker that runs them one after the other
+ * (crates/lb-server/src/main.rs:92-166); a batched decode step only pays off with a scheduler in
+ * front of it. lbk_batcher owns a cache of `slots` sequences (1..16) of `capacity` positions each
+ * (0: the model's max_position_embeddings).
+ * lbk_batcher_submit    queues a request (prompt of n >= 1 tokens, at most max_new_tokens generated,
+ *                       generation also ends after eos_token unless it is negative, or when the
+ *                       slot's positions are used up) and returns its id.
+ * lbk_batcher_step      moves queued requests into free slots (the prompt pass of lbk_model_forward,
+ *                       into that slot; the first token comes from its last row), then advances every
+ *                       occupied slot by one greedy token (argmax, sample.rs:17-25) with the recorded
+ *                       decode step; sequences have their own positions, finished ones free their slot
+ *                       at once. pending_out (may be NULL): requests still queued or running.
+ * lbk_batcher_poll      tokens generated so far for a request (at most `capacity` are copied, n_out is
+ *                       the full count) and whether it has finished.
+ * lbk_batcher_forget    drops a finished request's record.
+ * Calls on one batcher must not overlap. */
+typedef struct lbk_batcher lbk_batcher;
+int lbk_batcher_create(lbk_model *model, size_t slots, size_t capacity, lbk_batcher **out);
+int lbk_batcher_submit(lbk_batcher *batcher, const uint32_t *prompt, size_t n, size_t max_new_tokens, int32_t eos_token,
+                       uint64_t *id_out);
+int lbk_batcher_step(lbk_batcher *batcher, size_t *pending_out);
+int lbk_batcher_poll(lbk_batcher *batcher, uint64_t id, uint32_t *tokens_out, size_t capacity, size_t *n_out, int *done_out);
+int lbk_batcher_forget(lbk_batcher *batcher, uint64_t id);
+int lbk_batcher_destroy(lbk_batcher *batcher);
 
 /* ---- plans: a whole decode-like sequence in one launch -----------------------------------
  * The reference runs 4 fused ternary ops per layer x 30 layers = 120 parallel regions per

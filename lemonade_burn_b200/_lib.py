@@ -84,6 +84,17 @@ SYMBOLS = [
     ("lbk_kv_cache_free", _i, [_vp]),
     ("lbk_model_forward", _i, [_vp, _vp, _vp, _sz, _i, _vp]),
     ("lbk_model_decode", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    ("lbk_kv_cache_len_seq", _sz, [_vp, _sz]),
+    ("lbk_batcher_create", _i, [_vp, _sz, _sz, _pp]),
+    ("lbk_batcher_submit", _i, [_vp, _vp, _sz, _sz, _i, _vp]),
+    ("lbk_batcher_step", _i, [_vp, _vp]),
+    ("lbk_batcher_poll", _i, [_vp, C.c_uint64, _vp, _sz, _vp, _vp]),
+    ("lbk_batcher_forget", _i, [_vp, C.c_uint64]),
+    ("lbk_batcher_destroy", _i, [_vp]),
+    ("lbk_rope_kv_append_seq", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_attn_decode_seq", _i, [_vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_attn_decode_fused_seq", _i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _sz, _sz, _sz, _sz, _sz, _vp, _vp, _vp, _vp, _vp, _vp]),
+    ("lbk_advance_pos_seq", _i, [_vp, _vp, _vp, _sz, _vp]),
     ("lbk_convert_bitlinear", _i, [_vp, _vp, _sz, _i, _vp, _vp, _vp, _vp]),
     ("lbk_plan_create", _i, [_vp, _pp]),
     ("lbk_plan_add", _i, [_vp, _vp, _pp, _sz, _pp, _pp]),

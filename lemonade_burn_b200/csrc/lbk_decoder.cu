@@ -95,12 +95,12 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x, const flo
 // cache together with v). cos/sin: [max_pos][hd] with both halves duplicated (model.rs:213-230).
 __global__ void rope_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                    const float *__restrict__ cos_t, const float *__restrict__ sin_t,
-                                   const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap,
+                                   const int *__restrict__ pos_dev, int pos_stride, int nh, int kvh, int hd, int cap,
                                    uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
 
-    const int b = blockIdx.y, h = blockIdx.x, pos = *pos_dev;
+    const int b = blockIdx.y, h = blockIdx.x, pos = pos_dev[b * pos_stride];  // stride 0: one position for all sequences
     const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
     const int half = hd >> 1;
     if (h < nh) {
@@ -133,7 +133,7 @@ constexpr int kHd = 128;
 constexpr int kPartStride = kHd + 4;  // acc[128], max, sum, 2 pad floats: keeps rows 16-byte aligned
 __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
                                                           const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
-                                                          int nh, int kvh, int cap, float scaling, int splits,
+                                                          int pos_stride, int nh, int kvh, int cap, float scaling, int splits,
                                                           float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
@@ -141,7 +141,7 @@ __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restri
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (warp >= group) return;
-    const int total = *pos_dev + 1;  // keys 0..pos
+    const int total = pos_dev[b * pos_stride] + 1;  // keys 0..pos
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -206,7 +206,7 @@ constexpr int kKRow = kHd * 2 + 16;      // bytes per staged K row
 constexpr int kVRow = kHd * 2;           // bytes per staged V row
 __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
                                                                  const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
-                                                                 int nh, int kvh, int cap, float scaling, int splits,
+                                                                 int pos_stride, int nh, int kvh, int cap, float scaling, int splits,
                                                                  float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
@@ -215,7 +215,7 @@ __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *_
     __shared__ __align__(16) float s_q[8 * kHd];
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
-    const int total = *pos_dev + 1;  // keys 0..pos
+    const int total = pos_dev[b * pos_stride] + 1;  // keys 0..pos
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -308,8 +308,8 @@ __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *_
 template <bool MERGE>
 __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restrict__ q_raw, const float *__restrict__ k_new,
                                                         const float *__restrict__ v_new, const float *__restrict__ cos_t,
-                                                        const float *__restrict__ sin_t, const int *__restrict__ pos_dev, int nh, int kvh,
-                                                        int cap, float scaling, int splits, uint16_t *__restrict__ kc,
+                                                        const float *__restrict__ sin_t, const int *__restrict__ pos_dev, int pos_stride, int nh,
+                                                        int kvh, int cap, float scaling, int splits, uint16_t *__restrict__ kc,
                                                         uint16_t *__restrict__ vc, float *__restrict__ part, int *__restrict__ counters,
                                                         float *__restrict__ out /* [b][nh*hd] */) {
     ptx::pdl_trigger();
@@ -320,7 +320,7 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
     __shared__ int s_last;
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
-    const int pos = *pos_dev, total = pos + 1;  // keys 0..pos
+    const int pos = pos_dev[b * pos_stride], total = pos + 1;  // keys 0..pos
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -863,10 +863,13 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const float *__restric
     if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff || first != first) ? 0 : bi;
 }
 
-__global__ void advance_pos_kernel(int *pos) {
+// pos[i] += 1 for the sequences that took part in the step (all of them without a mask)
+__global__ void advance_pos_kernel(int *pos, const int *__restrict__ active, int n) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
- *pos += 1; }
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && (!active || active[i])) pos[i] += 1;
+}
 
 }  // namespace
 }  // namespace lbk
@@ -902,24 +905,36 @@ int lbk_rms_norm(lbk_ctx *c, const float *x_dev, const float *w_dev, size_t rows
     LBK_DEC_POST();
 }
 
-int lbk_rope_kv_append(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
-                       const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
-                       uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream) {
+static int rope_kv_append_impl(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                               const int32_t *pos_dev, int pos_stride, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                               uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream) {
     LBK_DEC_PRE("lbk_rope_kv_append");
     if (b == 0) return LBK_OK;
     if (!q_dev || !k_dev || !v_dev || !cos_dev || !sin_dev || !pos_dev || !kcache_dev || !vcache_dev)
         return fail(LBK_ERR_INVALID, "lbk_rope_kv_append: null buffer");
     if (head_dim & 1) return fail(LBK_ERR_SHAPE, "head_dim must be even");
     dim3 grid(static_cast<unsigned>(n_heads + kv_heads), static_cast<unsigned>(b));
-    LBK_CUDA(launch_chained(rope_append_kernel, dim3(grid), dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
+    LBK_CUDA(launch_chained(rope_append_kernel, dim3(grid), dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads),
                                             static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap),
                                             kcache_dev, vcache_dev));
     LBK_DEC_POST();
 }
 
-int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev, const int32_t *pos_dev,
-                    size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits, float *scratch_dev,
-                    float *out_dev, void *stream) {
+int lbk_rope_kv_append(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                       const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                       uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream) {
+    return rope_kv_append_impl(c, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, 0, b, n_heads, kv_heads, head_dim, cap, kcache_dev, vcache_dev, stream);
+}
+
+int lbk_rope_kv_append_seq(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                           const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap,
+                           uint16_t *kcache_dev, uint16_t *vcache_dev, void *stream) {
+    return rope_kv_append_impl(c, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, 1, b, n_heads, kv_heads, head_dim, cap, kcache_dev, vcache_dev, stream);
+}
+
+static int attn_decode_impl(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev, const int32_t *pos_dev,
+                            int pos_stride, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits,
+                            float *scratch_dev, float *out_dev, void *stream) {
     LBK_DEC_PRE("lbk_attn_decode");
     if (b == 0) return LBK_OK;
     if (!q_dev || !kcache_dev || !vcache_dev || !pos_dev || !scratch_dev || !out_dev) return fail(LBK_ERR_INVALID, "lbk_attn_decode: null buffer");
@@ -929,13 +944,25 @@ int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, 
     if (splits > 4096) return fail(LBK_ERR_UNSUPPORTED, "at most 4096 splits");
     dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
     const bool staged = n_heads / kv_heads >= 4;  // several query heads share the rows: fetch them once per block
-    LBK_CUDA(launch_chained(staged ? attn_partial_staged_kernel : attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads),
+    LBK_CUDA(launch_chained(staged ? attn_partial_staged_kernel : attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads),
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
                                               scratch_dev));
     LBK_CUDA(cudaGetLastError());
     LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st, scratch_dev, static_cast<int>(splits), out_dev));
     ctx->launches++;
     LBK_DEC_POST();
+}
+
+int lbk_attn_decode(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev, const int32_t *pos_dev,
+                    size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits, float *scratch_dev,
+                    float *out_dev, void *stream) {
+    return attn_decode_impl(c, q_dev, kcache_dev, vcache_dev, pos_dev, 0, b, n_heads, kv_heads, head_dim, cap, splits, scratch_dev, out_dev, stream);
+}
+
+int lbk_attn_decode_seq(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev, const uint16_t *vcache_dev, const int32_t *pos_dev,
+                        size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits, float *scratch_dev,
+                        float *out_dev, void *stream) {
+    return attn_decode_impl(c, q_dev, kcache_dev, vcache_dev, pos_dev, 1, b, n_heads, kv_heads, head_dim, cap, splits, scratch_dev, out_dev, stream);
 }
 
 int lbk_rope_kv_append_rows(lbk_ctx *c, float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
@@ -983,9 +1010,10 @@ int lbk_attn_decode_fused_supported(size_t n_heads, size_t kv_heads, size_t head
                : 0;
 }
 
-int lbk_attn_decode_fused(lbk_ctx *c, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
-                          const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits,
-                          uint16_t *kcache_dev, uint16_t *vcache_dev, float *scratch_dev, int32_t *counters_dev, float *out_dev, void *stream) {
+static int attn_decode_fused_impl(lbk_ctx *c, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev,
+                                  const float *sin_dev, const int32_t *pos_dev, int pos_stride, size_t b, size_t n_heads, size_t kv_heads,
+                                  size_t head_dim, size_t cap, size_t splits, uint16_t *kcache_dev, uint16_t *vcache_dev, float *scratch_dev,
+                                  int32_t *counters_dev, float *out_dev, void *stream) {
     LBK_DEC_PRE("lbk_attn_decode_fused");
     if (b == 0) return LBK_OK;
     if (!q_dev || !k_dev || !v_dev || !cos_dev || !sin_dev || !pos_dev || !kcache_dev || !vcache_dev || !scratch_dev || !counters_dev || !out_dev)
@@ -998,12 +1026,12 @@ int lbk_attn_decode_fused(lbk_ctx *c, const float *q_dev, const float *k_dev, co
     // (1.60 ms against 1.49 ms per batch-1 step), so it is used only when there is a single slice.
     if (splits == 1) {
         LBK_CUDA(launch_chained(attn_fused_kernel<true>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
-                                cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
+                                cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
                                 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
                                 counters_dev, out_dev));
     } else {
         LBK_CUDA(launch_chained(attn_fused_kernel<false>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
-                                cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
+                                cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
                                 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
                                 counters_dev, out_dev));
         LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st,
@@ -1075,10 +1103,33 @@ int lbk_argmax(lbk_ctx *c, const float *logits_dev, size_t rows, size_t n, int32
     return LBK_OK;
 }
 
+int lbk_attn_decode_fused(lbk_ctx *c, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                          const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits,
+                          uint16_t *kcache_dev, uint16_t *vcache_dev, float *scratch_dev, int32_t *counters_dev, float *out_dev, void *stream) {
+    return attn_decode_fused_impl(c, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, 0, b, n_heads, kv_heads, head_dim, cap, splits, kcache_dev,
+                                  vcache_dev, scratch_dev, counters_dev, out_dev, stream);
+}
+
+int lbk_attn_decode_fused_seq(lbk_ctx *c, const float *q_dev, const float *k_dev, const float *v_dev, const float *cos_dev, const float *sin_dev,
+                              const int32_t *pos_dev, size_t b, size_t n_heads, size_t kv_heads, size_t head_dim, size_t cap, size_t splits,
+                              uint16_t *kcache_dev, uint16_t *vcache_dev, float *scratch_dev, int32_t *counters_dev, float *out_dev,
+                              void *stream) {
+    return attn_decode_fused_impl(c, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, 1, b, n_heads, kv_heads, head_dim, cap, splits, kcache_dev,
+                                  vcache_dev, scratch_dev, counters_dev, out_dev, stream);
+}
+
 int lbk_advance_pos(lbk_ctx *c, int32_t *pos_dev, void *stream) {
     LBK_DEC_PRE("lbk_advance_pos");
     if (!pos_dev) return fail(LBK_ERR_INVALID, "lbk_advance_pos: null buffer");
-    LBK_CUDA(launch_chained(advance_pos_kernel, dim3(1), dim3(1), 0, st, pos_dev));
+    LBK_CUDA(launch_chained(advance_pos_kernel, dim3(1), dim3(32), 0, st, pos_dev, static_cast<const int *>(nullptr), 1));
+    LBK_DEC_POST();
+}
+
+int lbk_advance_pos_seq(lbk_ctx *c, int32_t *pos_dev, const int32_t *active_dev, size_t b, void *stream) {
+    LBK_DEC_PRE("lbk_advance_pos_seq");
+    if (b == 0) return LBK_OK;
+    if (!pos_dev) return fail(LBK_ERR_INVALID, "lbk_advance_pos_seq: null buffer");
+    LBK_CUDA(launch_chained(advance_pos_kernel, dim3(static_cast<unsigned>((b + 127) / 128)), dim3(128), 0, st, pos_dev, active_dev, static_cast<int>(b)));
     LBK_DEC_POST();
 }
 

@@ -18,6 +18,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <deque>
 #include <map>
 #include <memory>
 #include <string>
@@ -213,8 +214,9 @@ struct Cache {
     Model *model = nullptr;
     size_t b = 0, cap = 0, splits = 1;
     uint16_t *k = nullptr, *v = nullptr;  // [layers][b][kv_heads][cap][head_dim]
-    int32_t *pos = nullptr;               // cache length, on the device
-    size_t len = 0;                       // the same, on the host
+    int32_t *pos = nullptr;               // [b] cache length of every sequence, on the device
+    int32_t *active = nullptr;            // [b] 1: the sequence takes part in the step (its position advances)
+    std::vector<size_t> lens;             // the lengths again, on the host
     // work buffers of one step
     int32_t *tokens = nullptr, *next = nullptr, *counters = nullptr;
     float *x = nullptr, *x2 = nullptr, *n = nullptr, *q = nullptr, *kk = nullptr, *vv = nullptr, *attn = nullptr, *o = nullptr, *g = nullptr,
@@ -227,6 +229,30 @@ struct Cache {
     int32_t *pf_tokens = nullptr;
     float *pf_x = nullptr, *pf_n = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_o = nullptr, *pf_g = nullptr,
           *pf_u = nullptr, *pf_act = nullptr, *pf_d = nullptr, *pf_logits = nullptr;
+};
+
+// Continuous batching over one cache of `slots` sequences: what the reference's server would need in
+// front of a batched decode step (its worker serves one request at a time,
+// crates/lb-server/src/main.rs:92-166). Requests wait in a queue; a free slot takes the next one
+// (its prompt goes through the prompt pass into that slot); every step advances all occupied slots
+// by one greedy token (sample.rs:17-25) with the recorded decode step; a finished request frees
+// its slot at once.
+struct Request {
+    uint64_t id = 0;
+    std::vector<uint32_t> prompt, out;
+    size_t max_new = 0;
+    int32_t eos = -1;
+    bool done = false;
+    int slot = -1;
+};
+
+struct Batcher {
+    Model *model = nullptr;
+    Cache *cache = nullptr;
+    std::deque<uint64_t> queue;
+    std::map<uint64_t, Request> reqs;
+    std::vector<uint64_t> slot_req;  // 0: the slot is free
+    uint64_t next_id = 1;
 };
 
 namespace {
@@ -305,11 +331,11 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
         }
         uint16_t *kc = c->k + li * layer_kv, *vc = c->v + li * layer_kv;
         if (attn_fused) {
-            LBK_TRY(lbk_attn_decode_fused(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, c->splits, kc, vc, c->scratch,
+            LBK_TRY(lbk_attn_decode_fused_seq(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, c->splits, kc, vc, c->scratch,
                                           c->counters, c->attn, st));
         } else {
-            LBK_TRY(lbk_rope_kv_append(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, kc, vc, st));
-            LBK_TRY(lbk_attn_decode(h, c->q, kc, vc, c->pos, b, nh, kvh, hd, c->cap, c->splits, c->scratch, c->attn, st));
+            LBK_TRY(lbk_rope_kv_append_seq(h, c->q, c->kk, c->vv, m->cos, m->sin, c->pos, b, nh, kvh, hd, c->cap, kc, vc, st));
+            LBK_TRY(lbk_attn_decode_seq(h, c->q, kc, vc, c->pos, b, nh, kvh, hd, c->cap, c->splits, c->scratch, c->attn, st));
         }
         const lbk_weight *ow[1] = {l.o};
         float *oo[1] = {c->o};
@@ -347,7 +373,7 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
     else LBK_TRY(lbk_rms_norm(h, x, m->final_norm, b, H, eps, c->n, st));
     LBK_TRY(lbk_bf16_linear(h, c->n, b, m->embed, cfg.vocab_size, H, c->logits, st));
     LBK_TRY(lbk_argmax(h, c->logits, b, cfg.vocab_size, c->next, st));  // sample.rs:17-25
-    LBK_TRY(lbk_advance_pos(h, c->pos, st));
+    LBK_TRY(lbk_advance_pos_seq(h, c->pos, c->active, b, st));
     return LBK_OK;
 }
 
@@ -375,11 +401,12 @@ int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {
     return LBK_OK;
 }
 
-// `n` (2..kPrefillChunk) consecutive tokens of the cache's single sequence in one pass: the
+// `n` (1..kPrefillChunk) consecutive tokens of sequence `seq` of the cache in one pass: the
 // projections see n token rows (the tcgen05 GEMM above 16 rows), attention is causal over the cache
 // (model.rs:305-374 with m = n). Logits of every row (`all_logits`) or of the last one go to host
-// memory. Synchronous.
-int prefill_chunk(Model *m, Cache *c, const uint32_t *tokens, size_t n, int all_logits, float *logits_out) {
+// memory; `next_out` (host) receives the greedy token after the last row (sample.rs:17-25).
+// Synchronous.
+int prefill_chunk(Model *m, Cache *c, size_t seq, const uint32_t *tokens, size_t n, int all_logits, float *logits_out, int32_t *next_out = nullptr) {
     Ctx *ctx = m->ctx;
     lbk_ctx *h = reinterpret_cast<lbk_ctx *>(ctx);
     cudaStream_t st = ctx->own_stream;
@@ -407,8 +434,8 @@ int prefill_chunk(Model *m, Cache *c, const uint32_t *tokens, size_t n, int all_
         float *qkv_out[3] = {c->pf_q, c->pf_k, c->pf_v};
         LBK_TRY(lbk_ternary_linear_n(h, c->pf_n, n, qkv, 3, qkv_out, nullptr, st));
         uint16_t *kc = c->k + li * layer_kv, *vc = c->v + li * layer_kv;
-        LBK_TRY(lbk_rope_kv_append_rows(h, c->pf_q, c->pf_k, c->pf_v, m->cos, m->sin, c->pos, n, nh, kvh, hd, c->cap, 0, kc, vc, st));
-        LBK_TRY(lbk_attn_prefill(h, c->pf_q, kc, vc, c->pos, n, nh, kvh, hd, c->cap, 0, c->pf_attn, st));
+        LBK_TRY(lbk_rope_kv_append_rows(h, c->pf_q, c->pf_k, c->pf_v, m->cos, m->sin, c->pos + seq, n, nh, kvh, hd, c->cap, seq, kc, vc, st));
+        LBK_TRY(lbk_attn_prefill(h, c->pf_q, kc, vc, c->pos + seq, n, nh, kvh, hd, c->cap, seq, c->pf_attn, st));
         LBK_TRY(lbk_rms_norm(h, c->pf_attn, l.attn_sub_norm, n, nh * hd, eps, c->pf_attn, st));
         const lbk_weight *ow[1] = {l.o};
         float *oo[1] = {c->pf_o};
@@ -442,10 +469,15 @@ int prefill_chunk(Model *m, Cache *c, const uint32_t *tokens, size_t n, int all_
             LBK_CUDA(cudaMemcpyAsync(logits_out, c->pf_logits, V * 4, cudaMemcpyDeviceToHost, st));
         }
     }
-    const int32_t new_len = static_cast<int32_t>(c->len + n);
+    if (next_out) {
+        if (!logits_out || all_logits) LBK_TRY(lbk_bf16_linear(h, c->pf_n + (n - 1) * H, 1, m->embed, V, H, c->pf_logits, st));
+        LBK_TRY(lbk_argmax(h, c->pf_logits, 1, V, c->pf_tokens, st));  // the token buffer is free again
+        LBK_CUDA(cudaMemcpyAsync(next_out, c->pf_tokens, 4, cudaMemcpyDeviceToHost, st));
+    }
+    const int32_t new_len = static_cast<int32_t>(c->lens[seq] + n);
     LBK_CUDA(cudaStreamSynchronize(st));
-    LBK_CUDA(cudaMemcpy(c->pos, &new_len, 4, cudaMemcpyHostToDevice));
-    c->len += n;
+    LBK_CUDA(cudaMemcpy(c->pos + seq, &new_len, 4, cudaMemcpyHostToDevice));
+    c->lens[seq] += n;
     return LBK_OK;
 }
 
@@ -455,11 +487,11 @@ int ensure_graph(Model *m, Cache *c) {
     if (c->step) return LBK_OK;
     Ctx *ctx = m->ctx;
     cudaStream_t st = ctx->own_stream;
-    int32_t saved = 0;
-    LBK_CUDA(cudaMemcpy(&saved, c->pos, sizeof(saved), cudaMemcpyDeviceToHost));
-    LBK_TRY(enqueue_step(m, c, st));  // eager warm-up: writes the K/V row of position `saved`, which the real step rewrites
+    std::vector<int32_t> saved(c->b);
+    LBK_CUDA(cudaMemcpy(saved.data(), c->pos, c->b * 4, cudaMemcpyDeviceToHost));
+    LBK_TRY(enqueue_step(m, c, st));  // eager warm-up: writes the K/V rows of the saved positions, which the real step rewrites
     LBK_CUDA(cudaStreamSynchronize(st));
-    LBK_CUDA(cudaMemcpy(c->pos, &saved, sizeof(saved), cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpy(c->pos, saved.data(), c->b * 4, cudaMemcpyHostToDevice));
     const uint64_t before = ctx->launches;
     LBK_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
     const int status = enqueue_step(m, c, st);
@@ -670,7 +702,7 @@ int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cac
     LBK_CUDA(cudaMemset(c->k, 0, kv_elems * 2));
     LBK_CUDA(cudaMemset(c->v, 0, kv_elems * 2));
     struct { void **p; size_t bytes; } bufs[] = {
-        {reinterpret_cast<void **>(&c->pos), 4}, {reinterpret_cast<void **>(&c->tokens), batch * 4}, {reinterpret_cast<void **>(&c->next), batch * 4},
+        {reinterpret_cast<void **>(&c->pos), batch * 4}, {reinterpret_cast<void **>(&c->active), batch * 4}, {reinterpret_cast<void **>(&c->tokens), batch * 4}, {reinterpret_cast<void **>(&c->next), batch * 4},
         {reinterpret_cast<void **>(&c->counters), batch * kvh * 4}, {reinterpret_cast<void **>(&c->x), batch * H * 4},
         {reinterpret_cast<void **>(&c->x2), batch * H * 4}, {reinterpret_cast<void **>(&c->n), batch * H * 4},
         {reinterpret_cast<void **>(&c->q), batch * nh * hd * 4}, {reinterpret_cast<void **>(&c->kk), batch * kvh * hd * 4},
@@ -682,19 +714,22 @@ int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cac
         LBK_TRY(dev_alloc(c->device_allocs, bf.bytes, bf.p));
         LBK_CUDA(cudaMemset(*bf.p, 0, bf.bytes));
     }
+    c->lens.assign(batch, 0);
+    const std::vector<int32_t> ones(batch, 1);
+    LBK_CUDA(cudaMemcpy(c->active, ones.data(), batch * 4, cudaMemcpyHostToDevice));
     *out = reinterpret_cast<lbk_kv_cache *>(cache.release());
     return LBK_OK;
 }
 
-size_t lbk_kv_cache_len(const lbk_kv_cache *cp) { return cp ? reinterpret_cast<const Cache *>(cp)->len : 0; }
+size_t lbk_kv_cache_len(const lbk_kv_cache *cp) { return cp ? reinterpret_cast<const Cache *>(cp)->lens[0] : 0; }
 
 int lbk_kv_cache_reset(lbk_kv_cache *cp) {
     if (!cp) return fail(LBK_ERR_INVALID, "cache is null");
     Cache *c = reinterpret_cast<Cache *>(cp);
     LBK_CUDA(cudaSetDevice(c->model->ctx->device));
     LBK_CUDA(cudaDeviceSynchronize());
-    LBK_CUDA(cudaMemset(c->pos, 0, 4));
-    c->len = 0;
+    LBK_CUDA(cudaMemset(c->pos, 0, c->b * 4));
+    c->lens.assign(c->b, 0);
     return LBK_OK;
 }
 
@@ -703,7 +738,8 @@ int lbk_model_decode(lbk_model *mp, lbk_kv_cache *cp, const int32_t *tokens_dev,
     Model *m = reinterpret_cast<Model *>(mp);
     Cache *c = reinterpret_cast<Cache *>(cp);
     if (c->model != m) return fail(LBK_ERR_INVALID, "the cache belongs to another model");
-    if (c->len >= c->cap) return fail(LBK_ERR_INVALID, "the cache is full (%zu positions)", c->cap);
+    for (size_t l : c->lens)
+        if (l >= c->cap) return fail(LBK_ERR_INVALID, "the cache is full (%zu positions)", c->cap);
     LBK_CUDA(cudaSetDevice(m->ctx->device));
     LBK_TRY(ensure_graph(m, c));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -712,7 +748,7 @@ int lbk_model_decode(lbk_model *mp, lbk_kv_cache *cp, const int32_t *tokens_dev,
     m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
     if (logits_dev) LBK_CUDA(cudaMemcpyAsync(logits_dev, c->logits, c->b * m->cfg.vocab_size * 4, cudaMemcpyDeviceToDevice, st));
     if (next_dev) LBK_CUDA(cudaMemcpyAsync(next_dev, c->next, c->b * 4, cudaMemcpyDeviceToDevice, st));
-    c->len += 1;
+    for (size_t &l : c->lens) l += 1;
     return LBK_OK;
 }
 
@@ -723,7 +759,7 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
     if (c->model != m) return fail(LBK_ERR_INVALID, "the cache belongs to another model");
     if (c->b != 1) return fail(LBK_ERR_INVALID, "lbk_model_forward drives one sequence; this cache was made for %zu", c->b);
     if (n == 0) return LBK_OK;
-    if (c->len + n > c->cap) return fail(LBK_ERR_INVALID, "%zu tokens do not fit: %zu of %zu positions are used", n, c->len, c->cap);
+    if (c->lens[0] + n > c->cap) return fail(LBK_ERR_INVALID, "%zu tokens do not fit: %zu of %zu positions are used", n, c->lens[0], c->cap);
     LBK_CUDA(cudaSetDevice(m->ctx->device));
     cudaStream_t st = m->ctx->own_stream;
     const size_t V = m->cfg.vocab_size;
@@ -737,7 +773,7 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
             if (rows == 1) {  // a single left-over token takes the decode step
                 LBK_TRY(lbk_model_forward(mp, cp, tokens + i0, 1, all_logits, dst));
             } else {
-                LBK_TRY(prefill_chunk(m, c, tokens + i0, rows, all_logits, dst));
+                LBK_TRY(prefill_chunk(m, c, 0, tokens + i0, rows, all_logits, dst));
             }
         }
         return LBK_OK;
@@ -749,10 +785,149 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
         LBK_CUDA(cudaStreamSynchronize(st));  // `tk` is a stack variable
         LBK_CUDA(cudaGraphLaunch(c->step, st));
         m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
-        c->len += 1;
+        c->lens[0] += 1;
         if (logits_out) LBK_CUDA(cudaMemcpyAsync(logits_out, c->logits, V * 4, cudaMemcpyDeviceToHost, st));
     }
     LBK_CUDA(cudaStreamSynchronize(st));
+    return LBK_OK;
+}
+
+size_t lbk_kv_cache_len_seq(const lbk_kv_cache *cp, size_t seq) {
+    const Cache *c = reinterpret_cast<const Cache *>(cp);
+    return c && seq < c->b ? c->lens[seq] : 0;
+}
+
+int lbk_batcher_create(lbk_model *mp, size_t slots, size_t capacity, lbk_batcher **out) {
+    if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_batcher_create: null argument");
+    *out = nullptr;
+    lbk_kv_cache *cache = nullptr;
+    LBK_TRY(lbk_model_new_cache(mp, slots, capacity, &cache));
+    Batcher *b = new Batcher();
+    b->model = reinterpret_cast<Model *>(mp);
+    b->cache = reinterpret_cast<Cache *>(cache);
+    b->slot_req.assign(slots, 0);
+    *out = reinterpret_cast<lbk_batcher *>(b);
+    return LBK_OK;
+}
+
+int lbk_batcher_destroy(lbk_batcher *bp) {
+    if (!bp) return LBK_OK;
+    Batcher *b = reinterpret_cast<Batcher *>(bp);
+    lbk_kv_cache_free(reinterpret_cast<lbk_kv_cache *>(b->cache));
+    delete b;
+    return LBK_OK;
+}
+
+int lbk_batcher_submit(lbk_batcher *bp, const uint32_t *prompt, size_t n, size_t max_new_tokens, int32_t eos_token, uint64_t *id_out) {
+    if (!bp || !prompt || !id_out) return fail(LBK_ERR_INVALID, "lbk_batcher_submit: null argument");
+    Batcher *b = reinterpret_cast<Batcher *>(bp);
+    if (n == 0 || max_new_tokens == 0) return fail(LBK_ERR_INVALID, "a request needs a prompt and at least one token to generate");
+    if (n > b->cache->cap) return fail(LBK_ERR_INVALID, "a prompt of %zu tokens does not fit %zu positions", n, b->cache->cap);
+    const size_t V = b->model->cfg.vocab_size;
+    for (size_t i = 0; i < n; ++i)
+        if (prompt[i] >= V) return fail(LBK_ERR_INVALID, "token %u is outside the vocabulary of %zu", prompt[i], V);
+    Request r;
+    r.id = b->next_id++;
+    r.prompt.assign(prompt, prompt + n);
+    r.max_new = max_new_tokens;
+    r.eos = eos_token;
+    b->queue.push_back(r.id);
+    *id_out = r.id;
+    b->reqs.emplace(r.id, std::move(r));
+    return LBK_OK;
+}
+
+int lbk_batcher_step(lbk_batcher *bp, size_t *pending_out) {
+    if (!bp) return fail(LBK_ERR_INVALID, "lbk_batcher_step: null argument");
+    Batcher *b = reinterpret_cast<Batcher *>(bp);
+    Model *m = b->model;
+    Cache *c = b->cache;
+    LBK_CUDA(cudaSetDevice(m->ctx->device));
+    cudaStream_t st = m->ctx->own_stream;
+    const size_t slots = c->b;
+    // a sequence is finished by its end token, its budget, or a full cache; its slot goes back at once
+    auto finished = [&](const Request &r, size_t slot) {
+        return (r.eos >= 0 && static_cast<int32_t>(r.out.back()) == r.eos) || r.out.size() >= r.max_new || c->lens[slot] >= c->cap;
+    };
+    auto retire = [&](Request &r, size_t slot) -> int {
+        r.done = true;
+        r.slot = -1;
+        b->slot_req[slot] = 0;
+        const int32_t zero = 0;  // an idle slot still runs through the step: keep its position inside the cache
+        LBK_CUDA(cudaMemcpy(c->pos + slot, &zero, 4, cudaMemcpyHostToDevice));
+        c->lens[slot] = 0;
+        return LBK_OK;
+    };
+    // admission: prompts into free slots
+    for (size_t slot = 0; slot < slots && !b->queue.empty(); ++slot) {
+        if (b->slot_req[slot]) continue;
+        Request &r = b->reqs.at(b->queue.front());
+        b->queue.pop_front();
+        int32_t first = 0;
+        for (size_t i0 = 0; i0 < r.prompt.size(); i0 += kPrefillChunk) {
+            const size_t rows = std::min(kPrefillChunk, r.prompt.size() - i0);
+            const bool last = i0 + rows == r.prompt.size();
+            LBK_TRY(prefill_chunk(m, c, slot, r.prompt.data() + i0, rows, 0, nullptr, last ? &first : nullptr));
+        }
+        r.out.push_back(static_cast<uint32_t>(first));
+        r.slot = static_cast<int>(slot);
+        b->slot_req[slot] = r.id;
+        if (finished(r, slot)) LBK_TRY(retire(r, slot));
+    }
+    // one decode step for the occupied slots
+    std::vector<int32_t> tokens(slots, 0), active(slots, 0), next(slots, 0);
+    size_t n_active = 0;
+    for (size_t slot = 0; slot < slots; ++slot)
+        if (b->slot_req[slot]) {
+            tokens[slot] = static_cast<int32_t>(b->reqs.at(b->slot_req[slot]).out.back());
+            active[slot] = 1;
+            ++n_active;
+        }
+    if (n_active) {
+        LBK_TRY(ensure_graph(m, c));
+        LBK_CUDA(cudaMemcpyAsync(c->tokens, tokens.data(), slots * 4, cudaMemcpyHostToDevice, st));
+        LBK_CUDA(cudaMemcpyAsync(c->active, active.data(), slots * 4, cudaMemcpyHostToDevice, st));
+        LBK_CUDA(cudaStreamSynchronize(st));  // the host vectors are pageable
+        LBK_CUDA(cudaGraphLaunch(c->step, st));
+        m->ctx->launches += 7 * m->cfg.num_hidden_layers + 6;
+        LBK_CUDA(cudaMemcpyAsync(next.data(), c->next, slots * 4, cudaMemcpyDeviceToHost, st));
+        LBK_CUDA(cudaStreamSynchronize(st));
+        for (size_t slot = 0; slot < slots; ++slot) {
+            if (!b->slot_req[slot]) continue;
+            Request &r = b->reqs.at(b->slot_req[slot]);
+            c->lens[slot] += 1;
+            r.out.push_back(static_cast<uint32_t>(next[slot]));
+            if (finished(r, slot)) LBK_TRY(retire(r, slot));
+        }
+    }
+    if (pending_out) {
+        size_t occupied = 0;
+        for (uint64_t id : b->slot_req) occupied += id != 0;
+        *pending_out = occupied + b->queue.size();
+    }
+    return LBK_OK;
+}
+
+int lbk_batcher_poll(lbk_batcher *bp, uint64_t id, uint32_t *tokens_out, size_t capacity, size_t *n_out, int *done_out) {
+    if (!bp || !n_out) return fail(LBK_ERR_INVALID, "lbk_batcher_poll: null argument");
+    Batcher *b = reinterpret_cast<Batcher *>(bp);
+    auto it = b->reqs.find(id);
+    if (it == b->reqs.end()) return fail(LBK_ERR_INVALID, "no request %llu", static_cast<unsigned long long>(id));
+    const Request &r = it->second;
+    *n_out = r.out.size();
+    if (tokens_out)
+        for (size_t i = 0; i < r.out.size() && i < capacity; ++i) tokens_out[i] = r.out[i];
+    if (done_out) *done_out = r.done ? 1 : 0;
+    return LBK_OK;
+}
+
+int lbk_batcher_forget(lbk_batcher *bp, uint64_t id) {
+    if (!bp) return fail(LBK_ERR_INVALID, "lbk_batcher_forget: null argument");
+    Batcher *b = reinterpret_cast<Batcher *>(bp);
+    auto it = b->reqs.find(id);
+    if (it == b->reqs.end()) return fail(LBK_ERR_INVALID, "no request %llu", static_cast<unsigned long long>(id));
+    if (!it->second.done) return fail(LBK_ERR_INVALID, "request %llu is still running", static_cast<unsigned long long>(id));
+    b->reqs.erase(it);
     return LBK_OK;
 }
 

@@ -338,13 +338,80 @@ class NativeBitNet:
                                               C.c_void_p(nxt.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
         return logits, nxt
 
+    def batcher(self, slots: int, capacity: int = 0) -> "Batcher":
+        return Batcher(self, slots, capacity)
+
     def close(self):
         if getattr(self, "handle", None):
+            for bt in list(getattr(self, "_batchers", [])):
+                bt.close()
             for c in self._caches:
                 self._lib.lbk_kv_cache_free(c)
             self._caches = []
             self._lib.lbk_model_free(self.handle)
             self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Batcher:
+    """Continuous batching in front of the batched decode step (lbk_batcher_*): requests queue up, take
+    free slots of one shared cache (prompt pass into the slot), advance together one greedy token per
+    step, and leave as soon as they finish. The reference's server runs its requests one at a time
+    (crates/lb-server/src/main.rs:92-166)."""
+
+    def __init__(self, net: NativeBitNet, slots: int, capacity: int = 0):
+        self.net = net
+        self._lib = net._lib
+        h = C.c_void_p()
+        _lib.check(self._lib.lbk_batcher_create(net.handle, slots, capacity, C.byref(h)))
+        self.handle = h
+        if not hasattr(net, "_batchers"):
+            net._batchers = []
+        net._batchers.append(self)
+
+    def submit(self, prompt, max_new_tokens: int, eos: int = -1) -> int:
+        toks = np.ascontiguousarray(prompt, dtype=np.uint32)
+        rid = C.c_uint64()
+        _lib.check(self._lib.lbk_batcher_submit(self.handle, toks.ctypes.data_as(C.c_void_p), len(toks), max_new_tokens, eos, C.byref(rid)))
+        return int(rid.value)
+
+    def step(self) -> int:
+        """One scheduling step; returns how many requests are still queued or running."""
+        pending = C.c_size_t()
+        _lib.check(self._lib.lbk_batcher_step(self.handle, C.byref(pending)))
+        return int(pending.value)
+
+    def poll(self, rid: int):
+        """(tokens generated so far, finished?)"""
+        n, done = C.c_size_t(), C.c_int()
+        _lib.check(self._lib.lbk_batcher_poll(self.handle, rid, None, 0, C.byref(n), C.byref(done)))
+        out = np.empty(n.value, dtype=np.uint32)
+        _lib.check(self._lib.lbk_batcher_poll(self.handle, rid, out.ctypes.data_as(C.c_void_p), len(out), C.byref(n), C.byref(done)))
+        return out.tolist(), bool(done.value)
+
+    def forget(self, rid: int) -> None:
+        _lib.check(self._lib.lbk_batcher_forget(self.handle, rid))
+
+    def run(self, max_steps: int = 1 << 30) -> int:
+        """Steps until nothing is queued or running; returns the number of steps."""
+        steps = 0
+        while steps < max_steps:
+            steps += 1
+            if self.step() == 0:
+                break
+        return steps
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self._lib.lbk_batcher_destroy(self.handle)
+            self.handle = None
+            if self in getattr(self.net, "_batchers", []):
+                self.net._batchers.remove(self)
 
     def __del__(self):
         try:

@@ -1,0 +1,132 @@
+"""Continuous batching (lbk_batcher_*) and the per-sequence positions under it. The batched decode
+step computes every sequence's row independently (per-row quantisation, integer dots, row-wise
+norms, one attention problem per sequence), so a request must produce the same tokens whether it
+shares the step with others or not: the bar is token equality. Against the single-sequence runtime
+(another LM-head kernel: one row instead of several) the first token, which comes from the same
+prompt pass, must be equal."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("nh,kvh,splits", [(8, 2, 4), (4, 4, 3)])
+def test_attention_with_a_position_per_sequence(ctx, nh, kvh, splits):
+    """lbk_attn_decode_fused_seq (4 query heads per KV head) / lbk_rope_kv_append_seq + lbk_attn_decode_seq
+    (one per KV head) with positions 0, 36 and 130 in one batch against RoPE + softmax(qK/sqrt(d))V
+    in float64 per sequence; lbk_advance_pos_seq moves only the active ones. Tolerance 1e-5 absolute."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    b, hd, cap = 3, 128, 160
+    posv = [0, 36, 130]
+    g = torch.Generator().manual_seed(nh)
+    q = torch.randn(b, nh, hd, generator=g)
+    kn = torch.randn(b, kvh, hd, generator=g)
+    vn = torch.rand(b, kvh, hd, generator=g)
+    k = torch.randn(b, kvh, cap, hd, generator=g).bfloat16()
+    v = torch.rand(b, kvh, cap, hd, generator=g).bfloat16()
+    ang = torch.rand(cap, hd // 2, generator=g) * 6.0
+    cos = torch.cat([torch.cos(ang), torch.cos(ang)], dim=1).contiguous()
+    sin = torch.cat([torch.sin(ang), torch.sin(ang)], dim=1).contiguous()
+
+    def rope(x, pos):
+        x1, x2 = x[..., :hd // 2], x[..., hd // 2:]
+        return x * cos[pos] + torch.cat([-x2, x1], dim=-1) * sin[pos]
+
+    qd, knd, vnd, kd, vd = q.cuda(), kn.cuda(), vn.cuda(), k.cuda(), v.cuda()
+    cd, sd, pd = cos.cuda(), sin.cuda(), torch.tensor(posv, dtype=torch.int32).cuda()
+    scratch = torch.empty(b * nh * splits * (hd + 4), device="cuda")
+    counters = torch.zeros(b * kvh, dtype=torch.int32, device="cuda")
+    out = torch.zeros(b, nh * hd, device="cuda")
+    st = torch.cuda.current_stream().cuda_stream
+    if nh // kvh >= 4:
+        _lib.check(lib.lbk_attn_decode_fused_seq(ctx.handle, qd.data_ptr(), knd.data_ptr(), vnd.data_ptr(), cd.data_ptr(), sd.data_ptr(),
+                                                 pd.data_ptr(), b, nh, kvh, hd, cap, splits, kd.data_ptr(), vd.data_ptr(),
+                                                 scratch.data_ptr(), counters.data_ptr(), out.data_ptr(), st))
+    else:
+        _lib.check(lib.lbk_rope_kv_append_seq(ctx.handle, qd.data_ptr(), knd.data_ptr(), vnd.data_ptr(), cd.data_ptr(), sd.data_ptr(),
+                                              pd.data_ptr(), b, nh, kvh, hd, cap, kd.data_ptr(), vd.data_ptr(), st))
+        _lib.check(lib.lbk_attn_decode_seq(ctx.handle, qd.data_ptr(), kd.data_ptr(), vd.data_ptr(), pd.data_ptr(), b, nh, kvh, hd, cap,
+                                           splits, scratch.data_ptr(), out.data_ptr(), st))
+    got = out.cpu().numpy().reshape(b, nh, hd)
+    kgot, vgot = kd.cpu(), vd.cpu()
+    for bi, pos in enumerate(posv):
+        assert torch.equal(vgot[bi, :, pos], vn[bi].bfloat16())
+        dk = (kgot[bi, :, pos].float() - rope(kn[bi], pos).bfloat16().float()).abs()
+        assert float(dk.max()) <= 2.0 ** -7 * float(kn[bi].abs().max()) * 2
+        untouched = [p for p in range(cap) if p != pos]
+        assert torch.equal(kgot[bi][:, untouched], k[bi][:, untouched])
+        kf, vf = kgot[bi, :, :pos + 1].double().numpy(), vgot[bi, :, :pos + 1].double().numpy()
+        qf = rope(q[bi], pos).double().numpy()
+        for h in range(nh):
+            kv = h // (nh // kvh)
+            sc = kf[kv] @ qf[h] / np.sqrt(hd)
+            w = np.exp(sc - sc.max())
+            w /= w.sum()
+            assert np.abs(got[bi, h] - w @ vf[kv]).max() < 1e-5
+    active = torch.tensor([1, 0, 1], dtype=torch.int32).cuda()
+    _lib.check(lib.lbk_advance_pos_seq(ctx.handle, pd.data_ptr(), active.data_ptr(), b, st))
+    assert pd.cpu().tolist() == [1, 36, 131]
+    _lib.check(lib.lbk_advance_pos_seq(ctx.handle, pd.data_ptr(), None, b, st))
+    assert pd.cpu().tolist() == [2, 37, 132]
+    ctx.check_device_error()
+
+
+def test_batcher_tokens_do_not_depend_on_company(ctx, tmp_path):
+    """Seven requests of different prompt lengths (1..70 tokens: GEMV and GEMM prompt passes) and
+    budgets through three slots: (1) all submitted at once (slots are refilled as requests finish),
+    (2) one at a time. Same tokens both ways, the first of each equal to the single-sequence
+    runtime's greedy token after the prompt; budgets, the end token and the cache capacity end a
+    request; a finished record can be dropped, a running one cannot."""
+    from lemonade_burn_b200 import _lib, model
+    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 96)
+    model.save_checkpoint(tmp_path, cfg, model.random_checkpoint(cfg, 5))
+    nat = model.NativeBitNet(tmp_path, ctx)
+    rng = np.random.default_rng(9)
+    lens, budgets = [1, 5, 17, 70, 3, 40, 2], [6, 12, 4, 9, 1, 30, 7]
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.uint32) for n in lens]
+
+    bt = nat.batcher(3, 96)
+    ids = [bt.submit(p, m) for p, m in zip(prompts, budgets)]
+    with pytest.raises(_lib.LbkError, match="still running"):
+        bt.forget(ids[0])
+    steps = bt.run(1000)
+    together = []
+    for rid, m in zip(ids, budgets):
+        toks, done = bt.poll(rid)
+        assert done and len(toks) == m
+        together.append(toks)
+        bt.forget(rid)
+    with pytest.raises(_lib.LbkError, match="no request"):
+        bt.poll(ids[0])
+    assert steps < sum(budgets)           # the requests really shared steps
+    alone = []
+    for p, m in zip(prompts, budgets):
+        rid = bt.submit(p, m)
+        bt.run(1000)
+        toks, done = bt.poll(rid)
+        assert done
+        alone.append(toks)
+    assert together == alone
+    single = nat.new_cache(1, 96)
+    for p, toks in zip(prompts, together):
+        nat.reset_cache(single)
+        assert int(np.argmax(nat.forward(p, single))) == toks[0]
+    # the end token stops a request early; the capacity stops one that asks for too much
+    eos = together[5][3]
+    rid = bt.submit(prompts[5], 30, eos=eos)
+    bt.run(1000)
+    toks, done = bt.poll(rid)
+    assert done and toks == together[5][:together[5].index(eos) + 1]
+    rid = bt.submit(prompts[3], 1000)
+    bt.run(1000)
+    toks, done = bt.poll(rid)
+    assert done and len(toks) == 96 - 70 + 1 and toks[:9] == together[3]
+    with pytest.raises(_lib.LbkError, match="does not fit"):
+        bt.submit(np.zeros(97, dtype=np.uint32), 1)
+    with pytest.raises(_lib.LbkError, match="vocabulary"):
+        bt.submit(np.array([cfg.vocab_size], dtype=np.uint32), 1)
+    ctx.check_device_error()
+    bt.close()
+    nat.close()
