@@ -227,8 +227,31 @@ def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
                 times.append(time.perf_counter() - t0)
             best = min(times[1:])
             res.append({"prompt_tokens": n, "ms": best * 1e3, "tok_per_s": n / best, "next_token": int(np.argmax(logits))})
+        serving = batcher_case(torch, nat, rng, cfg)
         nat.close()
-    return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res}
+    return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res, "batcher": serving}
+
+
+def batcher_case(torch, nat, rng, cfg, slots=16, requests=48, prompt=128, new_tokens=64):
+    """Continuous batching (lbk_batcher_*): `requests` prompts of `prompt` tokens, `new_tokens` greedy
+    tokens each, through `slots` slots; wall clock from the first step to the last. Beside it the same
+    requests one after the other through one slot (what the reference's single worker does)."""
+    out = {}
+    for name, nslots, nreq in (("batched", slots, requests), ("one_at_a_time", 1, max(requests // 8, 2))):
+        bt = nat.batcher(nslots, prompt + new_tokens)
+        warm = bt.submit(rng.integers(0, cfg.vocab_size, size=prompt).astype(np.uint32), 2)
+        bt.run()
+        bt.forget(warm)
+        ids = [bt.submit(rng.integers(0, cfg.vocab_size, size=prompt).astype(np.uint32), new_tokens) for _ in range(nreq)]
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        steps = bt.run()
+        dt = time.perf_counter() - t0
+        gen = sum(len(bt.poll(i)[0]) for i in ids)
+        out[name] = {"slots": nslots, "requests": nreq, "prompt_tokens": prompt, "new_tokens": new_tokens, "steps": steps,
+                     "seconds": dt, "generated_tok_per_s": gen / dt, "requests_per_s": nreq / dt}
+        bt.close()
+    return out
 
 
 def converter_pass(torch, ctx, device, layers=30):
