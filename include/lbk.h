@@ -121,8 +121,10 @@ int lbk_bf16_gemv_host(lbk_ctx *ctx, const uint16_t *w, size_t rows, size_t cols
  * `stream` is a cudaStream_t passed as void* (NULL = legacy default stream). */
 
 /* ops.rs:301-329 with everything resident: per-token absmax int8 quantisation, the packed
- * ternary x int8 dot in int32, and the 1/(s_a*s_w) epilogue. m <= LBK_GEMV_MAX_M runs one
- * fused bandwidth-bound kernel; larger m runs quantise + the tcgen05 int8 GEMM.
+ * ternary x int8 dot in int32, and the 1/(s_a*s_w) epilogue. Few token rows (up to 4, or up to 8
+ * when the rows are shorter than 4096 columns) run one fused bandwidth-bound kernel; more rows run
+ * quantise + the tcgen05 int8 GEMM, which is flat in m where the fused kernel's arithmetic grows
+ * with it. The results are the same bits either way.
  * x_dev: f32 [m, cols] (16-byte aligned); outs_dev[i]: f32 [m, rows_i]; iouts_dev may be NULL. */
 int lbk_ternary_linear_n(lbk_ctx *ctx, const float *x_dev, size_t m, const lbk_weight *const *ws,
                          size_t n, float *const *outs_dev, int32_t *const *iouts_dev,

@@ -130,6 +130,22 @@ static int check_group(const lbk_weight *const *ws, size_t n, const Ctx *ctx) {
     return LBK_OK;
 }
 
+// GEMV kernel or quantise + tcgen05 GEMM? The GEMV kernel streams the weights once per eight token
+// rows and its arithmetic grows with the rows; the GEMM path costs two launches but is flat in m.
+// Measured per call at 2B4T shapes (K 2560: q/k/v, o, gate/up; K 6912: down), GEMV against GEMM:
+// 4 rows 5.7 / 9.2 us and 9.3 / 13.3 us; 8 rows 7.6 / 9.4 and 15.0 / 13.3; 9 rows 9.7 / 9.4 and
+// 23.3 / 13.4; 16 rows 12.9 / 9.9 and 25.4 / 13.4. LBK_GEMV_ROWS=n forces "GEMV up to n rows" for A/B runs.
+bool use_gemv(const Ctx *ctx, size_t kp, size_t m) {
+    static const int forced = [] {
+        const char *e = getenv("LBK_GEMV_ROWS");
+        const int n = e ? atoi(e) : 0;
+        return n > LBK_GEMV_MAX_M ? LBK_GEMV_MAX_M : n;
+    }();
+    if (m > LBK_GEMV_MAX_M || !gemv_fits(ctx, kp, m)) return false;
+    if (forced > 0) return m <= static_cast<size_t>(forced);
+    return m <= 4 || (m <= 8 && kp < 4096);
+}
+
 // Dispatch of one fused group on device buffers: GEMV kernel for small m, else quantise (if
 // needed) + the tcgen05 GEMM.
 static int run_group(Ctx *ctx, GroupArgs g, cudaStream_t stream, int8_t *q_scratch, float *s_scratch,
@@ -144,7 +160,7 @@ static int run_group(Ctx *ctx, GroupArgs g, cudaStream_t stream, int8_t *q_scrat
         }
         return LBK_OK;
     }
-    if (g.m <= LBK_GEMV_MAX_M && gemv_fits(ctx, kp, g.m)) return launch_gemv(ctx, g, stream);
+    if (use_gemv(ctx, kp, g.m)) return launch_gemv(ctx, g, stream);
     if (g.x) {
         if (!q_scratch) return fail(LBK_ERR_INVALID, "internal: GEMM path needs quantiser scratch");
         LBK_TRY(launch_quantize(ctx, g.x, g.m, g.w[0]->cols, q_scratch, s_scratch, sum_scratch, stream));
@@ -374,7 +390,7 @@ int lbk_ternary_linear_n(lbk_ctx *c, const float *x_dev, size_t m, const lbk_wei
     float *s = nullptr;
     int32_t *sum = nullptr;
     const size_t kp = g.w[0]->kp;
-    if (!(m <= LBK_GEMV_MAX_M && gemv_fits(ctx, kp, m))) {
+    if (!use_gemv(ctx, kp, m)) {
         // GEMM path: quantised activations go through context scratch. The scratch is shared
         // by every call on this context, so such calls must be issued on one stream.
         size_t sizes[3] = {m * kp, m * sizeof(float), m * sizeof(int32_t)};

@@ -14,6 +14,7 @@
 // above 16 rows) with causal attention over the cache, as the reference's forward does with
 // m > 1. One decode step is recorded into a CUDA graph the first time a cache is used and
 // replayed afterwards (the position lives in device memory).
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -694,8 +695,7 @@ int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cac
     c->cap = capacity;
     const lbk_model_config &cfg = m->cfg;
     const size_t H = cfg.hidden_size, I = cfg.intermediate_size, nh = cfg.num_attention_heads, kvh = cfg.num_key_value_heads, hd = m->head_dim;
-    c->splits = (capacity + 31) / 32;  // 32 positions per attention slice
-    if (c->splits > 256) c->splits = 256;
+    c->splits = std::min<size_t>((capacity + 31) / 32, 256);  // 32 positions per attention slice (the Python mirror's attention_splits)
     const size_t kv_elems = cfg.num_hidden_layers * batch * kvh * capacity * hd;
     LBK_TRY(dev_alloc(c->device_allocs, kv_elems * 2, reinterpret_cast<void **>(&c->k)));
     LBK_TRY(dev_alloc(c->device_allocs, kv_elems * 2, reinterpret_cast<void **>(&c->v)));
