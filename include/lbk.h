@@ -233,6 +233,15 @@ int lbk_attn_decode(lbk_ctx *ctx, const float *q_dev, const uint16_t *kcache_dev
 int lbk_relu2_mul(lbk_ctx *ctx, const float *g_dev, const float *u_dev, size_t n, float *out_dev, void *stream);
 /* x += y (the residual adds of model.rs:359,365). */
 int lbk_add_inplace(lbk_ctx *ctx, float *x_dev, const float *y_dev, size_t n, void *stream);
+/* A norm whose result goes straight into a projection: the normalised rows leave as the quantised
+ * activations of quant.rs:37-75 (q_dev int8 [rows][padded(n)], scale_dev[rows], sum_dev[rows]) ready
+ * for lbk_ternary_gemm_dev, with the same bits as lbk_rms_norm / lbk_add_rms_norm /
+ * lbk_relu2_mul_rms_norm followed by lbk_quantize_acts_dev. `pre` as for lbk_ternary_linear_pre:
+ * LBK_PRE_RMS (x), LBK_PRE_ADD_RMS (x += y first; x_dev is updated), LBK_PRE_RELU2_MUL_RMS
+ * (relu(x)^2 * y). n % 4 == 0 and n <= 8192 (lbk_norm_quant_supported); 16-byte aligned buffers. */
+int lbk_norm_quant_supported(size_t n);
+int lbk_norm_quant(lbk_ctx *ctx, int pre, float *x_dev, const float *y_dev, const float *w_dev, size_t rows, size_t n,
+                   float eps, int8_t *q_dev, float *scale_dev, int32_t *sum_dev, void *stream);
 /* Prompt ingestion: n consecutive positions of ONE sequence (`seq` of the cache's batch) at once.
  * lbk_rope_kv_append_rows: RoPE on q_dev [n][n_heads*hd] in place and on k_dev [n][kv_heads*hd];
  * k and v_dev are appended at positions *pos_dev .. *pos_dev + n - 1.

@@ -84,6 +84,8 @@ SYMBOLS = [
     ("lbk_kv_cache_free", _i, [_vp]),
     ("lbk_model_forward", _i, [_vp, _vp, _vp, _sz, _i, _vp]),
     ("lbk_model_decode", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
+    ("lbk_norm_quant_supported", _i, [_sz]),
+    ("lbk_norm_quant", _i, [_vp, _i, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp, _vp, _vp]),
     ("lbk_kv_cache_len_seq", _sz, [_vp, _sz]),
     ("lbk_batcher_create", _i, [_vp, _sz, _sz, _pp]),
     ("lbk_batcher_submit", _i, [_vp, _vp, _sz, _sz, _i, _vp]),

@@ -784,6 +784,95 @@ __global__ void __launch_bounds__(256) relu2_mul_rms_norm_kernel(const float *__
     }
 }
 
+// A norm whose result feeds a projection directly: the normalised row is quantised where it stands
+// (quant.rs:100-118: scale = 127 / max(amax, 1e-5), round half to even, clamp, sum) instead of going
+// to memory as f32 and through the quantise kernel. PRE selects what is normalised: x (LBK_PRE_RMS),
+// x + y with the sum written back to x (LBK_PRE_ADD_RMS), relu(x)^2 * y (LBK_PRE_RELU2_MUL_RMS). The
+// f32 values that get quantised are computed exactly as the norm kernels above compute them, so
+// the int8 rows equal those of norm kernel + quantise kernel bit for bit.
+template <int PRE>
+__global__ void __launch_bounds__(256) norm_quant_kernel(float *x, const float *__restrict__ y, const float *__restrict__ w, int n, int kp,
+                                                        float eps, int8_t *__restrict__ q, float *__restrict__ scale, int32_t *__restrict__ sum) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    __shared__ float s_red[8];
+    __shared__ int s_isum[8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    float *xr = x + static_cast<size_t>(blockIdx.x) * n;
+    const float *yr = y ? y + static_cast<size_t>(blockIdx.x) * n : nullptr;
+    const int n4 = n >> 2;  // callers guarantee n % 4 == 0, n <= 8192, 16-byte aligned rows
+    float4 v[8];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = tid + j * 256;
+        if (i < n4) {
+            const float4 a = reinterpret_cast<const float4 *>(xr)[i];
+            if (PRE == LBK_PRE_RMS) {
+                v[j] = a;
+            } else if (PRE == LBK_PRE_ADD_RMS) {
+                const float4 c = reinterpret_cast<const float4 *>(yr)[i];
+                v[j] = make_float4(a.x + c.x, a.y + c.y, a.z + c.z, a.w + c.w);
+                reinterpret_cast<float4 *>(xr)[i] = v[j];
+            } else {
+                const float4 c = reinterpret_cast<const float4 *>(yr)[i];
+                const float r0 = fmaxf(a.x, 0.f), r1 = fmaxf(a.y, 0.f), r2 = fmaxf(a.z, 0.f), r3 = fmaxf(a.w, 0.f);
+                v[j] = make_float4(r0 * r0 * c.x, r1 * r1 * c.y, r2 * r2 * c.z, r3 * r3 * c.w);
+            }
+        } else {
+            v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+    const float r = 1.0f / sqrtf(block_sum(ss, s_red) / static_cast<float>(n) + eps);
+    float am = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = tid + j * 256;
+        if (i < n4) {
+            const float4 gw = __ldg(reinterpret_cast<const float4 *>(w) + i);
+            v[j] = make_float4(v[j].x * r * gw.x, v[j].y * r * gw.y, v[j].z * r * gw.z, v[j].w * r * gw.w);
+            am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));  // fmaxf drops a NaN, as f32::max does
+        }
+    }
+    for (int o = 16; o > 0; o >>= 1) am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, o));
+    __syncthreads();  // block_sum's readers are done with s_red
+    if (lane == 0) s_red[warp] = am;
+    __syncthreads();
+    am = s_red[0];
+#pragma unroll
+    for (int wv = 1; wv < 8; ++wv) am = fmaxf(am, s_red[wv]);
+    const float sc = __fdiv_rn(127.0f, fmaxf(am, 1e-5f));
+    int8_t *qr = q + static_cast<size_t>(blockIdx.x) * kp;
+    int acc = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int i = (tid + j * 256) * 4;
+        if (i < kp) {  // columns from n to kp hold zeros
+            int qv[4];
+            const float f[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = __float2int_rn(__fmul_rn(f[e], sc));  // NaN -> 0 like `NaN as i8`
+                qv[e] = max(-128, min(127, t));
+                acc += qv[e];
+            }
+            *reinterpret_cast<uint32_t *>(qr + i) = (qv[0] & 255) | ((qv[1] & 255) << 8) | ((qv[2] & 255) << 16) | (static_cast<uint32_t>(qv[3] & 255) << 24);
+        }
+    }
+    for (int i = (tid + 8 * 256) * 4; i < kp; i += 256 * 4) *reinterpret_cast<uint32_t *>(qr + i) = 0u;
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) s_isum[warp] = acc;
+    __syncthreads();
+    if (tid == 0) {
+        int t = 0;
+#pragma unroll
+        for (int wv = 0; wv < 8; ++wv) t += s_isum[wv];
+        scale[blockIdx.x] = sc;
+        sum[blockIdx.x] = t;
+    }
+}
+
 __global__ void relu2_mul_kernel(const float *__restrict__ g, const float *__restrict__ u, size_t n, float *__restrict__ out) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
@@ -1081,6 +1170,30 @@ int lbk_relu2_mul_rms_norm(lbk_ctx *c, const float *g_dev, const float *u_dev, c
     if (!fused_norm_ok(g_dev, u_dev, w_dev, out_dev, n))
         return fail(LBK_ERR_UNSUPPORTED, "lbk_relu2_mul_rms_norm needs 16-byte aligned rows of a multiple of 4, at most 8192, columns");
     LBK_CUDA(launch_chained(relu2_mul_rms_norm_kernel, dim3(static_cast<unsigned>(rows)), dim3(256), 0, st, g_dev, u_dev, w_dev, static_cast<int>(n), eps, out_dev));
+    LBK_DEC_POST();
+}
+
+int lbk_norm_quant_supported(size_t n) { return n != 0 && n % 4 == 0 && n <= 8192 ? 1 : 0; }
+
+int lbk_norm_quant(lbk_ctx *c, int pre, float *x_dev, const float *y_dev, const float *w_dev, size_t rows, size_t n, float eps, int8_t *q_dev,
+                   float *scale_dev, int32_t *sum_dev, void *stream) {
+    LBK_DEC_PRE("lbk_norm_quant");
+    if (rows == 0) return LBK_OK;
+    if (!x_dev || !w_dev || !q_dev || !scale_dev || !sum_dev || (pre != LBK_PRE_RMS && !y_dev)) return fail(LBK_ERR_INVALID, "lbk_norm_quant: null buffer");
+    if (!lbk_norm_quant_supported(n)) return fail(LBK_ERR_UNSUPPORTED, "lbk_norm_quant: rows of a multiple of 4 and at most 8192 values");
+    if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(w_dev) | reinterpret_cast<uintptr_t>(q_dev)) & 15)
+        return fail(LBK_ERR_INVALID, "lbk_norm_quant: buffers must be 16-byte aligned");
+    const int kp = static_cast<int>((n + 127) / 128 * 128);
+    const dim3 grid(static_cast<unsigned>(rows)), block(256);
+    if (pre == LBK_PRE_RMS) {
+        LBK_CUDA(launch_chained(norm_quant_kernel<LBK_PRE_RMS>, grid, block, 0, st, x_dev, y_dev, w_dev, static_cast<int>(n), kp, eps, q_dev, scale_dev, sum_dev));
+    } else if (pre == LBK_PRE_ADD_RMS) {
+        LBK_CUDA(launch_chained(norm_quant_kernel<LBK_PRE_ADD_RMS>, grid, block, 0, st, x_dev, y_dev, w_dev, static_cast<int>(n), kp, eps, q_dev, scale_dev, sum_dev));
+    } else if (pre == LBK_PRE_RELU2_MUL_RMS) {
+        LBK_CUDA(launch_chained(norm_quant_kernel<LBK_PRE_RELU2_MUL_RMS>, grid, block, 0, st, x_dev, y_dev, w_dev, static_cast<int>(n), kp, eps, q_dev, scale_dev, sum_dev));
+    } else {
+        return fail(LBK_ERR_INVALID, "lbk_norm_quant: unknown transform %d", pre);
+    }
     LBK_DEC_POST();
 }
 

@@ -230,6 +230,9 @@ struct Cache {
     int32_t *pf_tokens = nullptr;
     float *pf_x = nullptr, *pf_n = nullptr, *pf_q = nullptr, *pf_k = nullptr, *pf_v = nullptr, *pf_attn = nullptr, *pf_o = nullptr, *pf_g = nullptr,
           *pf_u = nullptr, *pf_act = nullptr, *pf_d = nullptr, *pf_logits = nullptr;
+    int8_t *pf_q8 = nullptr;   // quantised input rows of the next projection (lbk_norm_quant)
+    float *pf_qscale = nullptr;
+    int32_t *pf_qsum = nullptr;
 };
 
 // Continuous batching over one cache of `slots` sequences: what the reference's server would need in
@@ -396,7 +399,9 @@ int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {
         {reinterpret_cast<void **>(&c->pf_attn), rows * nh * hd * 4}, {reinterpret_cast<void **>(&c->pf_o), rows * H * 4},
         {reinterpret_cast<void **>(&c->pf_g), rows * I * 4}, {reinterpret_cast<void **>(&c->pf_u), rows * I * 4},
         {reinterpret_cast<void **>(&c->pf_act), rows * I * 4}, {reinterpret_cast<void **>(&c->pf_d), rows * H * 4},
-        {reinterpret_cast<void **>(&c->pf_logits), kLogitRows * cfg.vocab_size * 4}};
+        {reinterpret_cast<void **>(&c->pf_logits), kLogitRows * cfg.vocab_size * 4},
+        {reinterpret_cast<void **>(&c->pf_q8), rows * (std::max(std::max(H, I), nh * hd) + 127) / 128 * 128},
+        {reinterpret_cast<void **>(&c->pf_qscale), rows * 4}, {reinterpret_cast<void **>(&c->pf_qsum), rows * 4}};
     for (auto &bf : bufs) LBK_TRY(dev_alloc(c->pf_allocs, bf.bytes, bf.p));
     c->pf_rows = rows;
     return LBK_OK;
@@ -427,25 +432,41 @@ int prefill_chunk(Model *m, Cache *c, size_t seq, const uint32_t *tokens, size_t
         return lbk_rms_norm(h, x, w, n, H, eps, c->pf_n, st);
     };
     const size_t layer_kv = c->b * kvh * c->cap * hd;
+    // From 9 rows on every projection takes the GEMM path, whose input is the quantised rows: the norm
+    // in front of a projection then writes those directly (lbk_norm_quant) and the f32 copy of the
+    // normalised rows, with the quantise kernel that would read it back, goes away. Same bits.
+    const bool nq = n >= 9 && lbk_norm_quant_supported(H) && lbk_norm_quant_supported(I) && lbk_norm_quant_supported(nh * hd);
+    auto norm_q = [&](int pre, float *x, const float *y, const float *w, size_t width) -> int {
+        return lbk_norm_quant(h, pre, x, y, w, n, width, eps, c->pf_q8, c->pf_qscale, c->pf_qsum, st);
+    };
+    auto project = [&](const float *x_f32, const lbk_weight *const *ws, size_t nw, float *const *outs) -> int {
+        if (nq) return lbk_ternary_gemm_dev(h, ws, nw, c->pf_q8, c->pf_qscale, c->pf_qsum, n, outs, nullptr, st);
+        return lbk_ternary_linear_n(h, x_f32, n, ws, nw, outs, nullptr, st);
+    };
     LBK_TRY(lbk_embed_bf16(h, m->embed, c->pf_tokens, n, H, c->pf_x, st));
-    LBK_TRY(lbk_rms_norm(h, c->pf_x, m->layers[0].input_norm, n, H, eps, c->pf_n, st));
+    if (nq) LBK_TRY(norm_q(LBK_PRE_RMS, c->pf_x, nullptr, m->layers[0].input_norm, H));
+    else LBK_TRY(lbk_rms_norm(h, c->pf_x, m->layers[0].input_norm, n, H, eps, c->pf_n, st));
     for (size_t li = 0; li < L; ++li) {
         const Model::Layer &l = m->layers[li];
         const lbk_weight *qkv[3] = {l.q, l.k, l.v};
         float *qkv_out[3] = {c->pf_q, c->pf_k, c->pf_v};
-        LBK_TRY(lbk_ternary_linear_n(h, c->pf_n, n, qkv, 3, qkv_out, nullptr, st));
+        LBK_TRY(project(c->pf_n, qkv, 3, qkv_out));
         uint16_t *kc = c->k + li * layer_kv, *vc = c->v + li * layer_kv;
         LBK_TRY(lbk_rope_kv_append_rows(h, c->pf_q, c->pf_k, c->pf_v, m->cos, m->sin, c->pos + seq, n, nh, kvh, hd, c->cap, seq, kc, vc, st));
         LBK_TRY(lbk_attn_prefill(h, c->pf_q, kc, vc, c->pos + seq, n, nh, kvh, hd, c->cap, seq, c->pf_attn, st));
-        LBK_TRY(lbk_rms_norm(h, c->pf_attn, l.attn_sub_norm, n, nh * hd, eps, c->pf_attn, st));
+        if (nq) LBK_TRY(norm_q(LBK_PRE_RMS, c->pf_attn, nullptr, l.attn_sub_norm, nh * hd));
+        else LBK_TRY(lbk_rms_norm(h, c->pf_attn, l.attn_sub_norm, n, nh * hd, eps, c->pf_attn, st));
         const lbk_weight *ow[1] = {l.o};
         float *oo[1] = {c->pf_o};
-        LBK_TRY(lbk_ternary_linear_n(h, c->pf_attn, n, ow, 1, oo, nullptr, st));
-        LBK_TRY(add_norm(c->pf_x, c->pf_o, l.post_attn_norm));
+        LBK_TRY(project(c->pf_attn, ow, 1, oo));
+        if (nq) LBK_TRY(norm_q(LBK_PRE_ADD_RMS, c->pf_x, c->pf_o, l.post_attn_norm, H));
+        else LBK_TRY(add_norm(c->pf_x, c->pf_o, l.post_attn_norm));
         const lbk_weight *gu[2] = {l.gate, l.up};
         float *guo[2] = {c->pf_g, c->pf_u};
-        LBK_TRY(lbk_ternary_linear_n(h, c->pf_n, n, gu, 2, guo, nullptr, st));
-        if (fused_i) {
+        LBK_TRY(project(c->pf_n, gu, 2, guo));
+        if (nq) {
+            LBK_TRY(norm_q(LBK_PRE_RELU2_MUL_RMS, c->pf_g, c->pf_u, l.ffn_sub_norm, I));
+        } else if (fused_i) {
             LBK_TRY(lbk_relu2_mul_rms_norm(h, c->pf_g, c->pf_u, l.ffn_sub_norm, n, I, eps, c->pf_act, st));
         } else {
             LBK_TRY(lbk_relu2_mul(h, c->pf_g, c->pf_u, n * I, c->pf_act, st));
@@ -453,8 +474,9 @@ int prefill_chunk(Model *m, Cache *c, size_t seq, const uint32_t *tokens, size_t
         }
         const lbk_weight *dw[1] = {l.down};
         float *dout[1] = {c->pf_d};
-        LBK_TRY(lbk_ternary_linear_n(h, c->pf_act, n, dw, 1, dout, nullptr, st));
-        LBK_TRY(add_norm(c->pf_x, c->pf_d, li + 1 < L ? m->layers[li + 1].input_norm : m->final_norm));
+        LBK_TRY(project(c->pf_act, dw, 1, dout));
+        if (nq && li + 1 < L) LBK_TRY(norm_q(LBK_PRE_ADD_RMS, c->pf_x, c->pf_d, m->layers[li + 1].input_norm, H));
+        else LBK_TRY(add_norm(c->pf_x, c->pf_d, li + 1 < L ? m->layers[li + 1].input_norm : m->final_norm));
     }
     // pf_n holds the final norm of every row
     if (logits_out) {

@@ -162,6 +162,39 @@ def test_fused_norms_match_their_parts(ctx):
     ctx.check_device_error()
 
 
+def test_norm_quant_matches_norm_then_quantise(ctx):
+    """lbk_norm_quant (the norm of a projection's input with the activation quantiser inside) gives
+    the bits of the norm kernel followed by lbk_quantize_acts_dev: int8 rows with their zero padding,
+    scales, sums, and the updated residual for the add form."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    lib = _lib.load()
+    st = torch.cuda.current_stream().cuda_stream
+    for rows, n in [(1, 2560), (17, 6912), (40, 8192), (5, 512), (3, 100)]:
+        kp = (n + 127) // 128 * 128
+        g = torch.Generator().manual_seed(n)
+        x = (3.0 * torch.randn(rows, n, generator=g)).cuda(); y = torch.randn(rows, n, generator=g).cuda()
+        w = torch.rand(n, generator=g).cuda() + 0.5
+        for pre in (1, 2, 3):
+            xa, xb = x.clone(), x.clone()
+            f = torch.empty_like(x)
+            if pre == 1:
+                assert lib.lbk_rms_norm(ctx.handle, xa.data_ptr(), w.data_ptr(), rows, n, 1e-5, f.data_ptr(), st) == 0
+            elif pre == 2:
+                assert lib.lbk_add_rms_norm(ctx.handle, xa.data_ptr(), y.data_ptr(), w.data_ptr(), rows, n, 1e-5, f.data_ptr(), st) == 0
+            else:
+                assert lib.lbk_relu2_mul_rms_norm(ctx.handle, xa.data_ptr(), y.data_ptr(), w.data_ptr(), rows, n, 1e-5, f.data_ptr(), st) == 0
+            q1 = torch.full((rows, kp), 77, dtype=torch.int8, device="cuda"); q2 = q1.clone()
+            s1 = torch.empty(rows, device="cuda"); s2 = torch.empty(rows, device="cuda")
+            t1 = torch.empty(rows, dtype=torch.int32, device="cuda"); t2 = torch.empty(rows, dtype=torch.int32, device="cuda")
+            _lib.check(lib.lbk_quantize_acts_dev(ctx.handle, f.data_ptr(), rows, n, q1.data_ptr(), s1.data_ptr(), t1.data_ptr(), st))
+            _lib.check(lib.lbk_norm_quant(ctx.handle, pre, xb.data_ptr(), y.data_ptr(), w.data_ptr(), rows, n, 1e-5, q2.data_ptr(),
+                                          s2.data_ptr(), t2.data_ptr(), st))
+            assert torch.equal(q1, q2) and torch.equal(s1, s2) and torch.equal(t1, t2) and torch.equal(xa, xb), (rows, n, pre)
+    assert not lib.lbk_norm_quant_supported(8196) and not lib.lbk_norm_quant_supported(6)
+    ctx.check_device_error()
+
+
 @pytest.mark.parametrize("m,cols", [(1, 2560), (1, 6912), (2, 6912), (4, 2560), (1, 512)])
 def test_projection_with_input_transform(oracle, ctx, m, cols):
     """lbk_ternary_linear_pre against the separate kernels it replaces (norm / residual add / gate,
