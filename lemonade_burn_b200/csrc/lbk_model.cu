@@ -222,6 +222,9 @@ struct Cache {
     int32_t *tokens = nullptr, *next = nullptr, *counters = nullptr;
     float *x = nullptr, *x2 = nullptr, *n = nullptr, *q = nullptr, *kk = nullptr, *vv = nullptr, *attn = nullptr, *o = nullptr, *g = nullptr,
           *u = nullptr, *d = nullptr, *act = nullptr, *logits = nullptr, *scratch = nullptr;
+    int8_t *q8 = nullptr;  // quantised input rows of the next projection (batches of 9 and more)
+    float *qscale = nullptr;
+    int32_t *qsum = nullptr;
     cudaGraphExec_t step = nullptr;
     std::vector<void *> device_allocs;
     // work buffers of the prompt path (lbk_model_forward with several tokens), sized for pf_rows rows
@@ -313,13 +316,25 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
         LBK_TRY(lbk_add_inplace(h, xin, y, b * H, st));
         return lbk_rms_norm(h, xin, w, b, H, eps, c->n, st);
     };
+    // From 9 sequences on every projection takes the quantise + GEMM path; the norm in front of it then
+    // writes the quantised rows itself (lbk_norm_quant): no f32 copy, no quantise kernel. Same bits.
+    const bool nq = b >= 9 && lbk_norm_quant_supported(H) && lbk_norm_quant_supported(I) && lbk_norm_quant_supported(nh * hd);
+    auto norm_q = [&](int pre, float *xx, const float *yy, const float *w, size_t width) -> int {
+        return lbk_norm_quant(h, pre, xx, yy, w, b, width, eps, c->q8, c->qscale, c->qsum, st);
+    };
+    auto proj_q = [&](const lbk_weight *const *ws, size_t nw, float *const *outs) -> int {
+        return lbk_ternary_gemm_dev(h, ws, nw, c->q8, c->qscale, c->qsum, b, outs, nullptr, st);
+    };
     LBK_TRY(lbk_embed_bf16(h, m->embed, c->tokens, b, H, x, st));
     bool have_d = false;  // c->d holds the previous layer's down projection, not yet added to x
     for (size_t li = 0; li < L; ++li) {
         const Model::Layer &l = m->layers[li];
         const lbk_weight *qkv[3] = {l.q, l.k, l.v};
         float *qkv_out[3] = {c->q, c->kk, c->vv};
-        if (!have_d) {
+        if (nq) {
+            LBK_TRY(norm_q(have_d ? LBK_PRE_ADD_RMS : LBK_PRE_RMS, x, have_d ? c->d : nullptr, l.input_norm, H));
+            LBK_TRY(proj_q(qkv, 3, qkv_out));
+        } else if (!have_d) {
             if (pre_h) {
                 LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_RMS, x, nullptr, l.input_norm, eps, nullptr, b, qkv, 3, qkv_out, nullptr, st));
             } else {
@@ -343,6 +358,18 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
         }
         const lbk_weight *ow[1] = {l.o};
         float *oo[1] = {c->o};
+        if (nq) {
+            const lbk_weight *gu[2] = {l.gate, l.up}, *dw[1] = {l.down};
+            float *guo[2] = {c->g, c->u}, *dout[1] = {c->d};
+            LBK_TRY(norm_q(LBK_PRE_RMS, c->attn, nullptr, l.attn_sub_norm, nh * hd));
+            LBK_TRY(proj_q(ow, 1, oo));
+            LBK_TRY(norm_q(LBK_PRE_ADD_RMS, x, c->o, l.post_attn_norm, H));
+            LBK_TRY(proj_q(gu, 2, guo));
+            LBK_TRY(norm_q(LBK_PRE_RELU2_MUL_RMS, c->g, c->u, l.ffn_sub_norm, I));
+            LBK_TRY(proj_q(dw, 1, dout));
+            have_d = true;
+            continue;
+        }
         if (pre_a) {
             LBK_TRY(lbk_ternary_linear_pre(h, LBK_PRE_RMS, c->attn, nullptr, l.attn_sub_norm, eps, nullptr, b, ow, 1, oo, nullptr, st));
         } else {
@@ -731,6 +758,8 @@ int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cac
         {reinterpret_cast<void **>(&c->vv), batch * kvh * hd * 4}, {reinterpret_cast<void **>(&c->attn), batch * nh * hd * 4},
         {reinterpret_cast<void **>(&c->o), batch * H * 4}, {reinterpret_cast<void **>(&c->g), batch * I * 4}, {reinterpret_cast<void **>(&c->u), batch * I * 4},
         {reinterpret_cast<void **>(&c->d), batch * H * 4}, {reinterpret_cast<void **>(&c->act), batch * I * 4},
+        {reinterpret_cast<void **>(&c->q8), batch * ((std::max(std::max(H, I), nh * hd) + 127) / 128 * 128)},
+        {reinterpret_cast<void **>(&c->qscale), batch * 4}, {reinterpret_cast<void **>(&c->qsum), batch * 4},
         {reinterpret_cast<void **>(&c->logits), batch * cfg.vocab_size * 4}, {reinterpret_cast<void **>(&c->scratch), batch * nh * c->splits * (hd + 4) * 4}};
     for (auto &bf : bufs) {
         LBK_TRY(dev_alloc(c->device_allocs, bf.bytes, bf.p));

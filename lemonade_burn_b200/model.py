@@ -193,11 +193,26 @@ class BitNet:
                 chk(lib.lbk_rms_norm(h, P(xout), P(w), b, H, eps, P(n), st))
             return n
 
+        # From 9 sequences on every projection takes the quantise + GEMM path; the norm in front of it
+        # then writes the quantised rows itself (lbk_norm_quant): no f32 copy, no quantise kernel.
+        nq = b >= 9 and all(ops.norm_quant_supported(wd) for wd in (H, I, nh * hd))
+        if nq:
+            q8 = self._buf("q8", (b, row_bytes(max(H, I, nh * hd)) * 4), torch.int8)
+            qs, qsum = self._buf("qs", (b,)), self._buf("qsum", (b,), torch.int32)
+            normq = lambda pre, xx, yy, w: ops.norm_quant(pre, xx, yy, w, e, q8, qs, qsum, self.ctx)
+            projq = lambda lins: ops.ternary_gemm_q(q8, qs, qsum, b, lins)
+
         chk(lib.lbk_embed_bf16(h, P(self.lm_head), P(tokens), b, H, P(x), st))
         d = None  # output of the previous layer's down projection, not yet added to the residual x
         for li, l in enumerate(self.layers):
             qkv_l = [l["q"], l["k"], l["v"]]
-            if d is None:
+            if nq:
+                if d is None:
+                    normq(ops.PRE_RMS, x, None, l["input_norm"])
+                else:
+                    normq(ops.PRE_ADD_RMS, x, d, l["input_norm"])
+                q, k, v = projq(qkv_l)
+            elif d is None:
                 if pre_h:
                     q, k, v = ops.ternary_linear_pre(ops.PRE_RMS, x, None, l["input_norm"], e, qkv_l)
                 else:
@@ -216,6 +231,14 @@ class BitNet:
                                            P(cache.k[li]), P(cache.v[li]), st))
                 chk(lib.lbk_attn_decode(h, P(q), P(cache.k[li]), P(cache.v[li]), P(cache.pos), b, nh, kvh, hd, cache.cap, splits,
                                         P(scratch), P(attn), st))
+            if nq:
+                normq(ops.PRE_RMS, attn, None, l["attn_sub_norm"])
+                o = projq([l["o"]])[0]
+                normq(ops.PRE_ADD_RMS, x, o, l["post_attn_norm"])
+                g, u = projq([l["gate"], l["up"]])
+                normq(ops.PRE_RELU2_MUL_RMS, g, u, l["ffn_sub_norm"])
+                d = projq([l["down"]])[0]
+                continue
             if pre_a:
                 o = ops.ternary_linear_pre(ops.PRE_RMS, attn, None, l["attn_sub_norm"], e, [l["o"]])[0]
             else:

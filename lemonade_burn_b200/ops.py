@@ -96,6 +96,33 @@ def ternary_linear_pre(pre: int, x: torch.Tensor, y: Optional[torch.Tensor], w: 
     return outs
 
 
+def norm_quant_supported(width: int) -> bool:
+    return bool(_lib.load().lbk_norm_quant_supported(width))
+
+
+def norm_quant(pre: int, x: torch.Tensor, y: Optional[torch.Tensor], w: torch.Tensor, eps: float, q8: torch.Tensor,
+               scale: torch.Tensor, qsum: torch.Tensor, ctx: Optional[Context] = None) -> None:
+    """The norm in front of a projection (PRE_* as for ternary_linear_pre; PRE_ADD_RMS updates x) with
+    the activation quantiser inside: fills q8 int8 [m, padded(k)], scale [m], qsum [m] for ternary_gemm_q."""
+    ctx = ctx or default_context()
+    m, k = x.shape
+    ptr = lambda t: C.c_void_p(t.data_ptr()) if t is not None else None
+    _lib.check(ctx._lib.lbk_norm_quant(ctx.handle, pre, ptr(x), ptr(y), ptr(w), m, k, C.c_float(eps), ptr(q8), ptr(scale), ptr(qsum),
+                                       C.c_void_p(_stream_ptr())))
+
+
+def ternary_gemm_q(q8: torch.Tensor, scale: torch.Tensor, qsum: torch.Tensor, m: int,
+                   linears: Sequence[TernaryLinear]) -> List[torch.Tensor]:
+    """ternary_gemm_multi (gemm.rs:128-195) on rows that are quantised already (norm_quant)."""
+    ctx = linears[0].ctx
+    outs = [torch.empty((m, l.rows), dtype=torch.float32, device=q8.device) for l in linears]
+    wp, _k1 = _lib.ptr_array([l.weight.handle.value for l in linears])
+    op, _k2 = _lib.ptr_array([o.data_ptr() for o in outs])
+    _lib.check(ctx._lib.lbk_ternary_gemm_dev(ctx.handle, wp, len(linears), C.c_void_p(q8.data_ptr()), C.c_void_p(scale.data_ptr()),
+                                             C.c_void_p(qsum.data_ptr()), m, op, None, C.c_void_p(_stream_ptr())))
+    return outs
+
+
 def ternary_linear(x: torch.Tensor, lin: TernaryLinear) -> torch.Tensor:
     """ops.rs:332-339"""
     return ternary_linear_multi(x, [lin])[0]

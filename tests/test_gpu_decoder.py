@@ -162,6 +162,36 @@ def test_fused_norms_match_their_parts(ctx):
     ctx.check_device_error()
 
 
+def test_batch_of_twelve_native_equals_mirror(ctx, tmp_path):
+    """Nine and more sequences take the norm + quantise kernels and the GEMM path in both the Python
+    mirror and the native runtime: same bits from both, and each row within the decoder's bar
+    (2e-3 of max |logit|) of the same sequence run alone (other projection kernels, another
+    LM-head kernel)."""
+    import torch
+    from lemonade_burn_b200 import model
+    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 32)
+    tensors = model.random_checkpoint(cfg, 77)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    py = model.BitNet.load(tmp_path, ctx)
+    nat = model.NativeBitNet(tmp_path, ctx)
+    b = 12
+    pc, nc = py.new_cache(b, 32), nat.new_cache(b, 32)
+    solo = [nat.new_cache(1, 32) for _ in range(2)]
+    g = torch.Generator().manual_seed(1)
+    for step in range(5):
+        toks = torch.randint(0, cfg.vocab_size, (b,), dtype=torch.int32, generator=g).cuda()
+        lp = py.forward(toks, pc)
+        ln, nxt = nat.decode(toks, nc)
+        torch.cuda.synchronize()
+        assert torch.equal(ln, lp) and torch.equal(nxt, py.argmax(lp))
+        for i, sc in enumerate(solo):
+            ref = nat.forward([int(toks[i])], sc)
+            got = ln[i].cpu().numpy()
+            assert np.abs(got - ref).max() <= TOL * np.abs(ref).max()
+    ctx.check_device_error()
+    nat.close()
+
+
 def test_norm_quant_matches_norm_then_quantise(ctx):
     """lbk_norm_quant (the norm of a projection's input with the activation quantiser inside) gives
     the bits of the norm kernel followed by lbk_quantize_acts_dev: int8 rows with their zero padding,
