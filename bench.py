@@ -193,7 +193,7 @@ def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
         kv_bytes = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * (context + steps // 2) * cfg.head_dim() * 2 * b
-        head_bytes = cfg.vocab_size * cfg.hidden_size * 2 * ((b + 3) // 4)   # the head streams W once per 4 token rows
+        head_bytes = cfg.vocab_size * cfg.hidden_size * 2 * ((b + 15) // 16)   # the head streams W once per 16 token rows
         nbytes = weight_bytes_per_sweep() + head_bytes + kv_bytes
         res.append({"batch": b, "ms_per_step": ms, "tok_per_s": b / (ms * 1e-3), "context": context,
                     "algorithmic_bytes_per_step": nbytes, "GBps": nbytes / (ms * 1e-3) / 1e9,
