@@ -205,7 +205,7 @@ def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
 
 def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
     """Config 3's other half: a prompt of n tokens through the native runtime (lbk_model_forward:
-    checkpoint on disk in the converter's format, up to 1024 rows per pass through the tcgen05 GEMM,
+    checkpoint on disk in the converter's format, up to 4096 rows per pass through the tcgen05 GEMM,
     tensor-core causal attention, last row's logits back on the host). Wall clock around the
     synchronous call, best of `reps`, fresh cache each time."""
     from lemonade_burn_b200 import model

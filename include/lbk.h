@@ -314,7 +314,7 @@ int lbk_advance_pos(lbk_ctx *ctx, int32_t *pos_dev, void *stream);
  * lbk_model_forward   BitNet::forward (model.rs:305-374) for one sequence (cache of batch 1):
  *                     appends `n` tokens at cache.len and writes the logits of every token
  *                     ([n][vocab], all_logits != 0) or of the last one ([vocab]) to host memory.
- *                     Several tokens go through the projections together, up to 1024 rows a pass.
+ *                     Several tokens go through the projections together, up to 4096 rows a pass.
  * lbk_model_decode    one new token for each of the cache's sequences: tokens_dev int32 [batch];
  *                     logits_dev f32 [batch][vocab] and/or next_dev int32 [batch] (greedy argmax,
  *                     sample.rs:17-25) may be null. Asynchronous on `stream`.

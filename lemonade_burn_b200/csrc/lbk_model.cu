@@ -10,7 +10,7 @@
 // Differences from the reference, all deliberate: the KV cache is bf16 with a fixed capacity
 // (the reference grows an f32 cache, model.rs:245); several independent sequences can advance
 // together (lbk_model_decode), which the reference cannot do. A call with several tokens of one
-// sequence (a prompt) sends up to 1024 rows at a time through the projections (the tcgen05 GEMM
+// sequence (a prompt) sends up to 4096 rows at a time through the projections (the tcgen05 GEMM
 // above 16 rows) with causal attention over the cache, as the reference's forward does with
 // m > 1. One decode step is recorded into a CUDA graph the first time a cache is used and
 // replayed afterwards (the position lives in device memory).
@@ -408,7 +408,15 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
     return LBK_OK;
 }
 
-constexpr size_t kPrefillChunk = 1024;  // prompt rows per pass (bounds the work buffers: 85 MB for the gate at 6912 columns)
+// Prompt rows per pass. More rows fill the GEMM's tile rounds better (a 4032-token prompt at 2B4T
+// shapes: 41.3 ms at 1024 rows a pass, 34.8 at 2048, 30.6 at 4096); the work buffers grow with them
+// (about 150 KB per row at those shapes, allocated for the rows a prompt really has).
+// LBK_PREFILL_ROWS overrides it for A/B runs.
+const size_t kPrefillChunk = [] {
+    const char *e = getenv("LBK_PREFILL_ROWS");
+    const long v = e ? atol(e) : 0;
+    return v >= 16 && v <= 8192 ? static_cast<size_t>(v) : static_cast<size_t>(4096);
+}();
 constexpr size_t kLogitRows = 128;      // rows of logits staged on the device at a time when every token's are wanted
 
 int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {

@@ -440,25 +440,27 @@ def test_prefill_rows_against_numpy(ctx, pos0, n, nh, kvh):
     ctx.check_device_error()
 
 
-@pytest.mark.parametrize("n,wide", [(2, False), (7, False), (40, False), (300, False), (70, True)])
+@pytest.mark.parametrize("n,wide", [(2, False), (7, False), (40, False), (300, False), (70, True), (1500, False)])
 def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
     """lbk_model_forward with several tokens (one pass of n rows: GEMV batch up to 16 rows, the
     tcgen05 GEMM above; causal attention over the cache) against the same tokens fed one call at a
     time through the decode step, and against the CPU restatement for the first rows. The integer
     projections are the same for both routes; the float summation orders of attention and of the
     LM head differ, so the bar is the decoder's own: max |delta logit| <= 2e-3 of max |logit|, the
-    greedy token equal where the margin is clear. A second prompt pass then continues the same
+    greedy token equal where the margin is clear (the 1500-row case states its own, statistical bar).
+    A second prompt pass then continues the same
     cache (positions n..n+4), followed by a decode step. `wide`: BitNet-2B4T layer shapes (hidden 2560,
     20/5 heads, intermediate 6912), two layers, reduced vocabulary."""
     from lemonade_burn_b200 import model
     from oracle import decoder_oracle as D
-    cfg = model.Config(2560, 6912, 20, 5, 2, 8000, 1e-5, 500000.0, 512) if wide else model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 512)
+    cap = 512 if n < 400 else 2048
+    cfg = model.Config(2560, 6912, 20, 5, 2, 8000, 1e-5, 500000.0, cap) if wide else model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, cap)
     tensors = model.random_checkpoint(cfg, 33)
     model.save_checkpoint(tmp_path, cfg, tensors)
     nat = model.NativeBitNet(tmp_path, ctx)
     rng = np.random.default_rng(n)
     toks = rng.integers(0, cfg.vocab_size, size=n + 6).astype(np.uint32)
-    c_seq, c_pf = nat.new_cache(1, 512), nat.new_cache(1, 512)
+    c_seq, c_pf = nat.new_cache(1, cap), nat.new_cache(1, cap)
     ref = np.stack([nat.forward([int(t)], c_seq) for t in toks])
 
     def close(a, r):
@@ -470,17 +472,27 @@ def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
 
     got = nat.forward(toks[:n], c_pf, all_logits=True)
     assert got.shape == (n, cfg.vocab_size) and nat.cache_len(c_pf) == n
-    for i in range(n):
-        close(got[i], ref[i])
+    if n <= 400:
+        for i in range(n):
+            close(got[i], ref[i])
+    else:
+        # Over a thousand rows a few meet an activation that sits on a rounding boundary of the int8
+        # quantiser: a 1e-6 difference in the attention sum then moves it by one step (1/127 of the
+        # row's maximum), which is worth a few 1e-3 of the logit range in this small model. So: 99 %
+        # of the rows inside the bar, every row inside three times the bar.
+        err = np.array([np.abs(got[i] - ref[i]).max() / np.abs(ref[i]).max() for i in range(n)])
+        assert np.quantile(err, 0.99) <= TOL and err.max() <= 3 * TOL, (np.quantile(err, 0.99), err.max())
     last = nat.forward(toks[n:n + 5], c_pf)              # continues the cache; last row's logits only
     assert nat.cache_len(c_pf) == n + 5
-    close(last, ref[n + 4])
-    close(nat.forward([int(toks[n + 5])], c_pf), ref[n + 5])   # and a decode step on top
+    tail_tol = TOL if n <= 400 else 3 * TOL
+    assert np.abs(last - ref[n + 4]).max() <= tail_tol * np.abs(ref[n + 4]).max()
+    step = nat.forward([int(toks[n + 5])], c_pf)          # and a decode step on top
+    assert np.abs(step - ref[n + 5]).max() <= tail_tol * np.abs(ref[n + 5]).max()
     # the CPU restatement, first rows
     w = _to_oracle_weights(cfg, tensors)
     kvh, hd = cfg.num_key_value_heads, cfg.head_dim()
-    okc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
-    ovc = [np.zeros((kvh, 512, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+    okc = [np.zeros((kvh, cap, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+    ovc = [np.zeros((kvh, cap, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
     for i in range(min(n, 2 if wide else 4)):
         close(got[i], D.decode_step(cfg.__dict__, w, int(toks[i]), okc, ovc, i))
     ctx.check_device_error()
