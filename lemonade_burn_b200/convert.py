@@ -56,9 +56,9 @@ class Converted:
 
 def convert_bitlinear(weights: Sequence[torch.Tensor], ctx: Optional[Context] = None, sha: bool = True) -> List[Converted]:
     """main.rs:62-87 for a list of rank-2 CUDA tensors, all bf16 or all f32."""
-    ctx = ctx or default_context()
     if not weights:
         return []
+    ctx = ctx or default_context()
     dt = weights[0].dtype
     if dt not in (torch.bfloat16, torch.float32):
         raise TypeError("master weights must be bf16 or f32")
