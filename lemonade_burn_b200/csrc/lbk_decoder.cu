@@ -497,7 +497,8 @@ __global__ void __launch_bounds__(256) rope_append_rows_kernel(float *__restrict
 // 16 tiles of 16x8). The f32 queries and the probabilities are each split into two bf16 terms
 // (x = hi + lo, |error| <= 2^-17 |x|), so that the only rounding beyond f32 summation is the bf16
 // of the cache itself, as in the decode kernels. Row i of the prompt sees keys 0 .. pos0 + i.
-constexpr int kPfKeys = 64;          // keys per staged chunk
+constexpr int kPfKeys = 64;          // keys per staged chunk (32, with three blocks per SM instead of two, measured the same or slower)
+constexpr int kPfNJ = kPfKeys / 8;   // score tiles (16 rows x 8 keys) per chunk
 constexpr int kPfRow = kHd * 2 + 16; // bytes per staged row: eight consecutive rows start in eight different 16-byte bank groups
 constexpr int kPfQWarp = 2 * 16 * kPfRow;  // one warp's queries: hi and lo, 16 rows each
 constexpr int kPfStage = 2 * kPfKeys * kPfRow;  // one staged chunk: keys, then values
@@ -574,9 +575,9 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
         __syncthreads();  // this chunk has landed, for every thread's copies
         if (pc > pos0 + row0 + 15) continue;  // none of this warp's rows sees this chunk (the barriers are at the loop's top)
         const uint32_t k_lane = k_lane0 + (it & 1) * kPfStage, v_lane = v_lane0 + (it & 1) * kPfStage;
-        float s[8][4];
+        float s[kPfNJ][4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+        for (int j = 0; j < kPfNJ; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
         for (int kp = 0; kp < 4; ++kp) {  // 32 dimensions at a time
             uint32_t ah0[4], al0[4], ah1[4], al1[4];
@@ -585,7 +586,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
             ptx::ldmatrix_x4(ah1, q_hi + kp * 64 + 32);
             ptx::ldmatrix_x4(al1, q_lo + kp * 64 + 32);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
+            for (int j = 0; j < kPfNJ; ++j) {
                 uint32_t b[4];
                 ptx::ldmatrix_x4(b, k_lane + j * 8 * kPfRow + kp * 64);
                 ptx::mma_bf16(s[j], ah0, b[0], b[1]);
@@ -596,7 +597,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
         }
         float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kPfNJ; ++j) {
             const int key = pc + 8 * j + 2 * t;
             if (key > lim0) s[j][0] = -INFINITY;
             if (key + 1 > lim0) s[j][1] = -INFINITY;
@@ -616,7 +617,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
         m1 = nm1;
         float ps0 = 0.0f, ps1 = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < kPfNJ; ++j) {
             s[j][0] = __expf(s[j][0] - nm0);
             s[j][1] = __expf(s[j][1] - nm0);
             s[j][2] = __expf(s[j][2] - nm1);
@@ -632,7 +633,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
             o[j][2] *= corr1; o[j][3] *= corr1;
         }
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) {  // 16 keys at a time
+        for (int kk = 0; kk < kPfKeys / 16; ++kk) {  // 16 keys at a time
             if (pc + 16 * kk > pos0 + row0 + 15) break;  // the rest of the chunk is masked for the whole tile
             uint32_t ph[4], pl[4];
 #pragma unroll
