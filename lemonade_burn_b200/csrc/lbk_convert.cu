@@ -8,7 +8,8 @@
 //   t     = clamp(round_ties_even(w * scale), -1, 1)   pack.rs:140-142
 //   byte j of block b: bits 2k..2k+1 = t + 1 of column b*128 + k*32 + j; padding columns hold code 1 (pack.rs:88-103)
 //
-// The f64 sum is taken as a fixed tree (per thread, per warp, per block, then over the blocks),
+// All tensors of a call go through two launches (absmean, then ternarise + pack); a tensor owns a
+// range of blocks in each. The f64 sum is taken as a fixed tree (per thread, per warp, per block, then over the blocks),
 // not left to right as the reference's iterator does. For weights that come from bf16 (8
 // significant bits each) every partial sum is exact in f64 up to millions of terms, so the order
 // does not matter; for arbitrary f32 inputs the two sums can differ in the last bits of the f64,
@@ -35,13 +36,43 @@ __device__ __forceinline__ float load_weight(const void *src, size_t i) {
 
 // sum |w| in f64: partial[block]; the block that finishes last folds the partial sums (always in
 // index order, whichever block that is) and writes scale = 1 / max((f32)(sum / n), 1e-5).
+// One tensor of a batched launch: its buffers and the ranges of blocks that work on it in the two passes.
+struct CvDev {
+    const void *src;
+    uint8_t *packed;
+    unsigned long long rows, cols;
+    unsigned a0, a1;  // blocks [a0, a1) of the absmean launch
+    unsigned t0, t1;  // blocks [t0, t1) of the ternarise launch
+};
+
+// the tensor whose block range holds `block` (ranges are consecutive and non-empty)
+template <bool SECOND>
+__device__ __forceinline__ int find_item(const CvDev *__restrict__ items, int n, unsigned block) {
+    int lo = 0, hi = n - 1;
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        const unsigned end = SECOND ? items[mid].t1 : items[mid].a1;
+        if (block < end) hi = mid;
+        else lo = mid + 1;
+    }
+    return lo;
+}
+
 template <bool BF16>
-__global__ void __launch_bounds__(kCvThreads) absmean_partial_kernel(const void *__restrict__ src, size_t n, double *__restrict__ partial,
-                                                                    unsigned *__restrict__ ticket, float *__restrict__ scale_out) {
+__global__ void __launch_bounds__(kCvThreads) absmean_partial_kernel(const CvDev *__restrict__ items, int n_items, double *__restrict__ partials,
+                                                                    unsigned *__restrict__ tickets, float *__restrict__ scales) {
     __shared__ double s_red[kCvThreads / 32];
     __shared__ bool s_last;
+    const int item = find_item<false>(items, n_items, blockIdx.x);
+    const CvDev it = items[item];
+    const void *src = it.src;
+    const size_t n = it.rows * it.cols;
+    const unsigned block = blockIdx.x - it.a0, n_blocks = it.a1 - it.a0;
+    double *partial = partials + static_cast<size_t>(item) * kCvPartials;
+    unsigned *ticket = tickets + item;
+    float *scale_out = scales + item;
     constexpr int V = BF16 ? 8 : 4;  // elements per 16-byte load
-    const size_t tid = static_cast<size_t>(blockIdx.x) * kCvThreads + threadIdx.x, stride = static_cast<size_t>(gridDim.x) * kCvThreads;
+    const size_t tid = static_cast<size_t>(block) * kCvThreads + threadIdx.x, stride = static_cast<size_t>(n_blocks) * kCvThreads;
     const size_t nv = (reinterpret_cast<uintptr_t>(src) & 15) == 0 ? n / V : 0;
     double s = 0.0;
     auto add16 = [&](const uint4 &v) {
@@ -75,15 +106,15 @@ __global__ void __launch_bounds__(kCvThreads) absmean_partial_kernel(const void 
         double t = 0.0;
 #pragma unroll
         for (int w = 0; w < kCvThreads / 32; ++w) t += s_red[w];
-        partial[blockIdx.x] = t;
+        partial[block] = t;
         __threadfence();
-        s_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+        s_last = atomicAdd(ticket, 1u) == n_blocks - 1;
     }
     __syncthreads();
     if (!s_last || threadIdx.x >= 32) return;
     __threadfence();
     double t = 0.0;
-    for (unsigned i = threadIdx.x; i < gridDim.x; i += 32) t += __ldcg(partial + i);
+    for (unsigned i = threadIdx.x; i < n_blocks; i += 32) t += __ldcg(partial + i);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
     if (threadIdx.x == 0) {
@@ -104,14 +135,12 @@ __device__ __forceinline__ uint32_t ternary_code(float w, float scale) {
 // Eight lanes share a 128-weight block: lane q of them owns bytes 4q..4q+3, i.e. columns
 // k*32 + 4q .. 4q+3 for k = 0..3, so a warp reads whole 32-byte sectors and writes 128 bytes.
 template <bool BF16, typename Index>
-__global__ void __launch_bounds__(kCvThreads) ternarize_pack_kernel(const void *__restrict__ src, size_t rows, size_t cols,
-                                                                   const float *__restrict__ scale_ptr, uint8_t *__restrict__ packed,
-                                                                   unsigned long long *__restrict__ counts) {
-    const float scale = *scale_ptr;
+__device__ __forceinline__ void ternarize_pack_body(const void *__restrict__ src, size_t rows, size_t cols, float scale, uint8_t *__restrict__ packed,
+                                                    unsigned long long *__restrict__ counts, unsigned block, unsigned n_blocks) {
     const size_t bpr = (cols + 127) / 128, items = rows * bpr * 8;
     const bool vec = (cols & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0;
     unsigned n_real = 0u, n_fields = 0u, n_code1 = 0u, n_code2 = 0u;
-    for (size_t it = static_cast<size_t>(blockIdx.x) * kCvThreads + threadIdx.x; it < items; it += static_cast<size_t>(gridDim.x) * kCvThreads) {
+    for (size_t it = static_cast<size_t>(block) * kCvThreads + threadIdx.x; it < items; it += static_cast<size_t>(n_blocks) * kCvThreads) {
         const Index gi = static_cast<Index>(it >> 3), ri = gi / static_cast<Index>(bpr);  // 32-bit division where the sizes allow
         const size_t row = ri, blk = gi - ri * static_cast<Index>(bpr);
         const int j0 = static_cast<int>(it & 7) * 4;
@@ -174,6 +203,20 @@ __global__ void __launch_bounds__(kCvThreads) ternarize_pack_kernel(const void *
     }
     __syncthreads();
     if (threadIdx.x < 3 && s_cnt[threadIdx.x]) atomicAdd(counts + threadIdx.x, static_cast<unsigned long long>(s_cnt[threadIdx.x]));
+}
+
+template <bool BF16>
+__global__ void __launch_bounds__(kCvThreads) ternarize_pack_kernel(const CvDev *__restrict__ items, int n_items, const float *__restrict__ scales,
+                                                                   unsigned long long *__restrict__ counts) {
+    const int item = find_item<true>(items, n_items, blockIdx.x);
+    const CvDev it = items[item];
+    const float scale = scales[item];
+    const unsigned block = blockIdx.x - it.t0, n_blocks = it.t1 - it.t0;
+    const unsigned long long pack_items = it.rows * ((it.cols + 127) / 128) * 8;
+    if (pack_items < (1ull << 32))  // 32-bit division where the sizes allow
+        ternarize_pack_body<BF16, uint32_t>(it.src, it.rows, it.cols, scale, it.packed, counts + 3 * item, block, n_blocks);
+    else
+        ternarize_pack_body<BF16, size_t>(it.src, it.rows, it.cols, scale, it.packed, counts + 3 * item, block, n_blocks);
 }
 
 // ---- sha256 of the ternary int8 array (row-major [rows][cols], one byte per weight: 0xff, 0, 1) ----
@@ -294,7 +337,9 @@ int lbk_convert_bitlinear(lbk_ctx *c, const lbk_convert_item *items, size_t n, i
         unsigned long long *counts = nullptr;
         ShaItem *sha_items = nullptr;
         uint32_t *digests = nullptr;
+        CvDev *table = nullptr;
         ~Work() {
+            cudaFree(table);
             cudaFree(partial);
             cudaFree(scales);
             cudaFree(counts);
@@ -307,30 +352,31 @@ int lbk_convert_bitlinear(lbk_ctx *c, const lbk_convert_item *items, size_t n, i
     LBK_CUDA(cudaMalloc(&wk.counts, n * 4 * sizeof(unsigned long long)));  // [n][3] counts, then n tickets
     LBK_CUDA(cudaMemsetAsync(wk.counts, 0, n * 4 * sizeof(unsigned long long), st));
     unsigned *tickets = reinterpret_cast<unsigned *>(wk.counts + 3 * n);
+    // two launches for the whole batch: every tensor gets a range of blocks in each
+    std::vector<CvDev> table(n);
+    unsigned a_blocks = 0, t_blocks = 0;
     for (size_t i = 0; i < n; ++i) {
         const lbk_convert_item &it = items[i];
         const size_t elems = it.rows * it.cols;
         const size_t per_block = static_cast<size_t>(kCvThreads) * 32;
-        const int blocks_a = static_cast<int>(std::min<size_t>(std::min<size_t>(kCvPartials, static_cast<size_t>(ctx->sm_count) * 6), (elems + per_block - 1) / per_block));
+        const unsigned blocks_a = static_cast<unsigned>(std::min<size_t>(std::min<size_t>(kCvPartials, static_cast<size_t>(ctx->sm_count) * 6), (elems + per_block - 1) / per_block));
         const size_t pack_items = it.rows * ((it.cols + 127) / 128) * 8;
-        const int blocks_t = static_cast<int>(std::min<size_t>(static_cast<size_t>(ctx->sm_count) * 8, (pack_items + kCvThreads - 1) / kCvThreads));
-        double *partial = wk.partial + i * kCvPartials;
-        const bool small = pack_items < (1ull << 32);
-        if (bf16) {
-            absmean_partial_kernel<true><<<blocks_a, kCvThreads, 0, st>>>(it.src_dev, elems, partial, tickets + i, wk.scales + i);
-            if (small)
-                ternarize_pack_kernel<true, uint32_t><<<blocks_t, kCvThreads, 0, st>>>(it.src_dev, it.rows, it.cols, wk.scales + i, it.packed_dev, wk.counts + 3 * i);
-            else
-                ternarize_pack_kernel<true, size_t><<<blocks_t, kCvThreads, 0, st>>>(it.src_dev, it.rows, it.cols, wk.scales + i, it.packed_dev, wk.counts + 3 * i);
-        } else {
-            absmean_partial_kernel<false><<<blocks_a, kCvThreads, 0, st>>>(it.src_dev, elems, partial, tickets + i, wk.scales + i);
-            if (small)
-                ternarize_pack_kernel<false, uint32_t><<<blocks_t, kCvThreads, 0, st>>>(it.src_dev, it.rows, it.cols, wk.scales + i, it.packed_dev, wk.counts + 3 * i);
-            else
-                ternarize_pack_kernel<false, size_t><<<blocks_t, kCvThreads, 0, st>>>(it.src_dev, it.rows, it.cols, wk.scales + i, it.packed_dev, wk.counts + 3 * i);
-        }
-        ctx->launches += 2;
+        const unsigned blocks_t = static_cast<unsigned>(std::min<size_t>(static_cast<size_t>(ctx->sm_count) * 8, (pack_items + kCvThreads * 4 - 1) / (kCvThreads * 4)));
+        table[i] = CvDev{it.src_dev, it.packed_dev, it.rows, it.cols, a_blocks, a_blocks + blocks_a, t_blocks, t_blocks + blocks_t};
+        a_blocks += blocks_a;
+        t_blocks += blocks_t;
     }
+    LBK_CUDA(cudaMalloc(&wk.table, n * sizeof(CvDev)));
+    LBK_CUDA(cudaMemcpyAsync(wk.table, table.data(), n * sizeof(CvDev), cudaMemcpyHostToDevice, st));
+    LBK_CUDA(cudaStreamSynchronize(st));  // `table` is pageable
+    if (bf16) {
+        absmean_partial_kernel<true><<<a_blocks, kCvThreads, 0, st>>>(wk.table, static_cast<int>(n), wk.partial, tickets, wk.scales);
+        ternarize_pack_kernel<true><<<t_blocks, kCvThreads, 0, st>>>(wk.table, static_cast<int>(n), wk.scales, wk.counts);
+    } else {
+        absmean_partial_kernel<false><<<a_blocks, kCvThreads, 0, st>>>(wk.table, static_cast<int>(n), wk.partial, tickets, wk.scales);
+        ternarize_pack_kernel<false><<<t_blocks, kCvThreads, 0, st>>>(wk.table, static_cast<int>(n), wk.scales, wk.counts);
+    }
+    ctx->launches += 2;
     LBK_CUDA(cudaGetLastError());
     std::vector<uint32_t> digests;
     if (sha256_out) {
