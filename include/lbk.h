@@ -338,6 +338,9 @@ int lbk_model_forward(lbk_model *model, lbk_kv_cache *cache, const uint32_t *tok
                       float *logits_out);
 int lbk_model_decode(lbk_model *model, lbk_kv_cache *cache, const int32_t *tokens_dev, float *logits_dev,
                      int32_t *next_dev, void *stream);
+/* Rows a prompt pass takes at once (1..8192; default 4096). More rows fill the GEMM's tile rounds
+ * better, fewer bound the work buffers (about 150 KB per row at 2B4T shapes). */
+int lbk_model_set_prefill_rows(lbk_model *model, size_t rows);
 /* Length of sequence `seq` of a cache (lbk_kv_cache_len is sequence 0). */
 size_t lbk_kv_cache_len_seq(const lbk_kv_cache *cache, size_t seq);
 

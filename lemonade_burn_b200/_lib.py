@@ -86,6 +86,7 @@ SYMBOLS = [
     ("lbk_model_decode", _i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     ("lbk_norm_quant_supported", _i, [_sz]),
     ("lbk_norm_quant", _i, [_vp, _i, _vp, _vp, _vp, _sz, _sz, _f, _vp, _vp, _vp, _vp]),
+    ("lbk_model_set_prefill_rows", _i, [_vp, _sz]),
     ("lbk_kv_cache_len_seq", _sz, [_vp, _sz]),
     ("lbk_batcher_create", _i, [_vp, _sz, _sz, _pp]),
     ("lbk_batcher_submit", _i, [_vp, _vp, _sz, _sz, _i, _vp]),

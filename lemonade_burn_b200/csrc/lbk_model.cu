@@ -205,6 +205,7 @@ struct Model {
     };
     std::vector<Layer> layers;
     float *final_norm = nullptr;
+    size_t prefill_rows = 0;    // prompt rows per pass (lbk_model_set_prefill_rows)
     uint16_t *embed = nullptr;  // bf16 [vocab][hidden], also the LM head (tied)
     float *cos = nullptr, *sin = nullptr;
     std::vector<void *> device_allocs;
@@ -411,7 +412,7 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
 // Prompt rows per pass. More rows fill the GEMM's tile rounds better (a 4032-token prompt at 2B4T
 // shapes: 41.3 ms at 1024 rows a pass, 34.8 at 2048, 30.6 at 4096); the work buffers grow with them
 // (about 150 KB per row at those shapes, allocated for the rows a prompt really has).
-// LBK_PREFILL_ROWS overrides it for A/B runs.
+// LBK_PREFILL_ROWS changes the default; lbk_model_set_prefill_rows sets it per model.
 const size_t kPrefillChunk = [] {
     const char *e = getenv("LBK_PREFILL_ROWS");
     const long v = e ? atol(e) : 0;
@@ -442,7 +443,7 @@ int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {
     return LBK_OK;
 }
 
-// `n` (1..kPrefillChunk) consecutive tokens of sequence `seq` of the cache in one pass: the
+// `n` (at most the model's prefill_rows) consecutive tokens of sequence `seq` of the cache in one pass: the
 // projections see n token rows (the tcgen05 GEMM above 16 rows), attention is causal over the cache
 // (model.rs:305-374 with m = n). Logits of every row (`all_logits`) or of the last one go to host
 // memory; `next_out` (host) receives the greedy token after the last row (sample.rs:17-25).
@@ -599,6 +600,7 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
     std::unique_ptr<Model, int (*)(Model *)> model(new Model(), [](Model *m) { return lbk_model_free(reinterpret_cast<lbk_model *>(m)); });
     Model *m = model.get();
     m->ctx = ctx;
+    m->prefill_rows = kPrefillChunk;
     bool ok = true;
     lbk_model_config &cfg = m->cfg;
     cfg.hidden_size = json_size(cj.get("hidden_size"), ok);
@@ -825,8 +827,8 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
     for (size_t i = 0; i < n; ++i)
         if (tokens[i] >= V) return fail(LBK_ERR_INVALID, "token %u is outside the vocabulary of %zu", tokens[i], V);
     if (n >= 2) {  // a prompt: whole chunks of rows through the projections at once
-        for (size_t i0 = 0; i0 < n; i0 += kPrefillChunk) {
-            const size_t rows = n - i0 < kPrefillChunk ? n - i0 : kPrefillChunk;
+        for (size_t i0 = 0; i0 < n; i0 += m->prefill_rows) {
+            const size_t rows = n - i0 < m->prefill_rows ? n - i0 : m->prefill_rows;
             const bool last = i0 + rows == n;
             float *dst = logits_out ? (all_logits ? logits_out + i0 * V : (last ? logits_out : nullptr)) : nullptr;
             if (rows == 1) {  // a single left-over token takes the decode step
@@ -848,6 +850,13 @@ int lbk_model_forward(lbk_model *mp, lbk_kv_cache *cp, const uint32_t *tokens, s
         if (logits_out) LBK_CUDA(cudaMemcpyAsync(logits_out, c->logits, V * 4, cudaMemcpyDeviceToHost, st));
     }
     LBK_CUDA(cudaStreamSynchronize(st));
+    return LBK_OK;
+}
+
+int lbk_model_set_prefill_rows(lbk_model *mp, size_t rows) {
+    if (!mp) return fail(LBK_ERR_INVALID, "lbk_model_set_prefill_rows: model is null");
+    if (rows < 1 || rows > 8192) return fail(LBK_ERR_INVALID, "rows per prompt pass must be 1..8192 (got %zu)", rows);
+    reinterpret_cast<Model *>(mp)->prefill_rows = rows;
     return LBK_OK;
 }
 
@@ -923,8 +932,8 @@ int lbk_batcher_step(lbk_batcher *bp, size_t *pending_out) {
         Request &r = b->reqs.at(b->queue.front());
         b->queue.pop_front();
         int32_t first = 0;
-        for (size_t i0 = 0; i0 < r.prompt.size(); i0 += kPrefillChunk) {
-            const size_t rows = std::min(kPrefillChunk, r.prompt.size() - i0);
+        for (size_t i0 = 0; i0 < r.prompt.size(); i0 += m->prefill_rows) {
+            const size_t rows = std::min(m->prefill_rows, r.prompt.size() - i0);
             const bool last = i0 + rows == r.prompt.size();
             LBK_TRY(prefill_chunk(m, c, slot, r.prompt.data() + i0, rows, 0, nullptr, last ? &first : nullptr));
         }

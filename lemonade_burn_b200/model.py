@@ -348,6 +348,10 @@ class NativeBitNet:
     def cache_len(self, cache) -> int:
         return int(self._lib.lbk_kv_cache_len(cache))
 
+    def set_prefill_rows(self, rows: int) -> None:
+        """Rows a prompt pass takes at once (default 4096)."""
+        _lib.check(self._lib.lbk_model_set_prefill_rows(self.handle, rows))
+
     def reset_cache(self, cache) -> None:
         """Back to an empty sequence; the buffers and the recorded step are kept."""
         _lib.check(self._lib.lbk_kv_cache_reset(cache))

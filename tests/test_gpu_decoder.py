@@ -440,8 +440,9 @@ def test_prefill_rows_against_numpy(ctx, pos0, n, nh, kvh):
     ctx.check_device_error()
 
 
-@pytest.mark.parametrize("n,wide", [(2, False), (7, False), (40, False), (300, False), (70, True), (1500, False)])
-def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
+@pytest.mark.parametrize("n,wide,pass_rows", [(2, False, 0), (7, False, 0), (40, False, 0), (300, False, 0), (70, True, 0), (1500, False, 0),
+                                              (300, False, 64), (70, True, 17)])
+def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide, pass_rows):
     """lbk_model_forward with several tokens (one pass of n rows: GEMV batch up to 16 rows, the
     tcgen05 GEMM above; causal attention over the cache) against the same tokens fed one call at a
     time through the decode step, and against the CPU restatement for the first rows. The integer
@@ -450,7 +451,8 @@ def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
     greedy token equal where the margin is clear (the 1500-row case states its own, statistical bar).
     A second prompt pass then continues the same
     cache (positions n..n+4), followed by a decode step. `wide`: BitNet-2B4T layer shapes (hidden 2560,
-    20/5 heads, intermediate 6912), two layers, reduced vocabulary."""
+    20/5 heads, intermediate 6912), two layers, reduced vocabulary. `pass_rows`: rows a pass takes
+    (default 4096), so that a prompt goes through several passes."""
     from lemonade_burn_b200 import model
     from oracle import decoder_oracle as D
     cap = 512 if n < 400 else 2048
@@ -458,6 +460,8 @@ def test_native_prompt_pass_matches_token_by_token(ctx, tmp_path, n, wide):
     tensors = model.random_checkpoint(cfg, 33)
     model.save_checkpoint(tmp_path, cfg, tensors)
     nat = model.NativeBitNet(tmp_path, ctx)
+    if pass_rows:   # several passes per prompt, the last one ragged
+        nat.set_prefill_rows(pass_rows)
     rng = np.random.default_rng(n)
     toks = rng.integers(0, cfg.vocab_size, size=n + 6).astype(np.uint32)
     c_seq, c_pf = nat.new_cache(1, cap), nat.new_cache(1, cap)
