@@ -109,6 +109,14 @@ def test_batcher_tokens_do_not_depend_on_company(ctx, tmp_path):
         assert done
         alone.append(toks)
     assert together == alone
+    # a prompt that enters its slot in several passes (32 rows at a time, the last one ragged) gives the
+    # same bits: every row's projections, attention and norms are computed independently of its neighbours
+    nat.set_prefill_rows(32)
+    for i in (3, 5, 2):
+        rid = bt.submit(prompts[i], budgets[i])
+        bt.run(1000)
+        assert bt.poll(rid)[0] == together[i]
+    nat.set_prefill_rows(4096)
     single = nat.new_cache(1, 96)
     for p, toks in zip(prompts, together):
         nat.reset_cache(single)
