@@ -56,11 +56,20 @@ int lbk_abi_version(void);
  * device is compute capability 10.x. No counterpart in the reference (CPU only). */
 int lbk_init(int device, lbk_ctx **out);
 int lbk_destroy(lbk_ctx *ctx);
-/* Reads and clears the device-side error word (set when a bounded wait inside a kernel gave
- * up). Synchronises the device. Returns LBK_OK or LBK_ERR_TIMEOUT. */
+/* Reads and clears the device-side error word. Synchronises the device. Returns LBK_OK;
+ * LBK_ERR_TIMEOUT when a bounded wait inside a kernel gave up; LBK_ERR_INVALID when a decoder-step
+ * kernel found its position (read from pos_dev) outside [0, cap): such a kernel touches no memory
+ * and the step's results are invalid (the reference asserts pos0 + m <= rope_len on the host,
+ * crates/lb-model/src/model.rs:309). */
 int lbk_check_device_error(lbk_ctx *ctx);
 /* Number of kernel launches this context has issued since creation (benchmark bookkeeping). */
 uint64_t lbk_launch_count(const lbk_ctx *ctx);
+/* Which kernel serves few token rows. rows = 0 (the default) keeps the measured rule of
+ * lbk_ternary_linear_n; rows = n (1..LBK_GEMV_MAX_M) sends every call of at most n token rows to the
+ * fused bandwidth-bound kernel and the rest to quantise + GEMM. The results are the same bits either
+ * way; the setting exists for measurements and for hosts whose shapes differ from the ones the rule
+ * was measured on. The reference's counterpart is the kernel selector (gemm.rs:25-92, LB_KERNEL). */
+int lbk_set_gemv_rows(lbk_ctx *ctx, int rows);
 
 /* ---- layout helpers: crates/lb-ternary/src/pack.rs:22-24,83-85 -------------------------- */
 
@@ -125,7 +134,12 @@ int lbk_bf16_gemv_host(lbk_ctx *ctx, const uint16_t *w, size_t rows, size_t cols
  * when the rows are shorter than 4096 columns) run one fused bandwidth-bound kernel; more rows run
  * quantise + the tcgen05 int8 GEMM, which is flat in m where the fused kernel's arithmetic grows
  * with it. The results are the same bits either way.
- * x_dev: f32 [m, cols] (16-byte aligned); outs_dev[i]: f32 [m, rows_i]; iouts_dev may be NULL. */
+ * x_dev: f32 [m, cols] (16-byte aligned); outs_dev[i]: f32 [m, rows_i]; iouts_dev may be NULL.
+ * The quantise + GEMM path keeps the quantised rows in scratch memory of the context, which grows
+ * (cudaMalloc) the first time a larger m * cols is seen: make the first call of each shape outside
+ * any stream capture, and issue all calls of one context on one stream (they share that scratch).
+ * A block once handed out stays valid until lbk_destroy, so a recorded graph keeps working after
+ * later, larger calls. */
 int lbk_ternary_linear_n(lbk_ctx *ctx, const float *x_dev, size_t m, const lbk_weight *const *ws,
                          size_t n, float *const *outs_dev, int32_t *const *iouts_dev,
                          void *stream);
@@ -192,6 +206,12 @@ int lbk_tp_region_close(lbk_ctx *ctx, void *region);
 int lbk_tp_region_free(lbk_ctx *ctx, void *region);
 int lbk_tp_comm_create(lbk_ctx *ctx, int world, int rank, void *const *regions, lbk_tp_comm **out);
 int lbk_tp_comm_destroy(lbk_tp_comm *comm);
+/* How many times a kernel of this communicator looks at a peer's word before it gives up (default
+ * 2^24, several seconds). A peer that never arrives then costs LBK_ERR_TIMEOUT from
+ * lbk_check_device_error and invalid results of that call; the context stays usable. The
+ * reference turns a failed request into an error reply instead of a dead worker
+ * (crates/lb-server/src/main.rs:92-100); this is the device-side half of the same rule. */
+int lbk_tp_comm_set_wait_limit(lbk_tp_comm *comm, uint32_t polls);
 void *lbk_tp_partial_buffer(lbk_tp_comm *comm);
 int lbk_tp_quantize(lbk_tp_comm *comm, const float *x_dev, size_t m, size_t k, int8_t *q_dev, float *scale_dev,
                     int32_t *sum_dev, void *stream);
@@ -302,7 +322,8 @@ int lbk_ternary_linear_pre(lbk_ctx *ctx, int pre, const float *x_dev, const floa
                            int32_t *const *iouts_dev, void *stream);
 /* argmax (crates/lb-model/src/sample.rs:17-25): first index of the maximum of each row. */
 int lbk_argmax(lbk_ctx *ctx, const float *logits_dev, size_t rows, size_t n, int32_t *out_dev, void *stream);
-/* *pos_dev += 1 (cache.len = total, model.rs:367). */
+/* *pos_dev += 1 (cache.len = total, model.rs:367). The caller keeps the position below `cap`: a
+ * step launched at position >= cap is refused by its kernels (see lbk_check_device_error). */
 int lbk_advance_pos(lbk_ctx *ctx, int32_t *pos_dev, void *stream);
 
 /* ---- the decoder as a native runtime (crates/lb-model/src/model.rs) ----------------------------
@@ -374,8 +395,8 @@ int lbk_batcher_destroy(lbk_batcher *batcher);
  * The reference runs 4 fused ternary ops per layer x 30 layers = 120 parallel regions per
  * token (crates/lb-ternary/benches/kbench.rs:148-194, crates/lb-model/src/model.rs:331-366).
  * A plan records such a sequence once and replays it with a single persistent-kernel
- * launch. Groups in a plan must not read each other's outputs unless `barrier` is set on
- * the reading group. */
+ * launch. Groups in a plan must be independent: none may read another's outputs, because the
+ * launch walks all of them at once (the reference's sweep has no decoder math between them either). */
 int lbk_plan_create(lbk_ctx *ctx, lbk_plan **out);
 /* Appends one fused group (same meaning as lbk_ternary_linear_n with m == 1). With x_dev
  * and outs_dev both NULL the group reads its input from, and writes its f32 outputs to, the

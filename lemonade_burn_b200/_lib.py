@@ -25,6 +25,7 @@ SYMBOLS = [
     ("lbk_destroy", _i, [_vp]),
     ("lbk_check_device_error", _i, [_vp]),
     ("lbk_launch_count", C.c_uint64, [_vp]),
+    ("lbk_set_gemv_rows", _i, [_vp, _i]),
     ("lbk_padded_cols", _sz, [_sz]),
     ("lbk_row_bytes", _sz, [_sz]),
     ("lbk_weight_upload", _i, [_vp, _sz, _sz, _vp, _sz, _f, _pp]),
@@ -72,6 +73,7 @@ SYMBOLS = [
     ("lbk_tp_region_free", _i, [_vp, _vp]),
     ("lbk_tp_comm_create", _i, [_vp, _i, _i, _pp, _pp]),
     ("lbk_tp_comm_destroy", _i, [_vp]),
+    ("lbk_tp_comm_set_wait_limit", _i, [_vp, C.c_uint32]),
     ("lbk_tp_partial_buffer", _vp, [_vp]),
     ("lbk_tp_quantize", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     ("lbk_tp_reduce_scale", _i, [_vp, _vp, _f, _sz, _sz, _vp, _vp, _vp]),

@@ -72,33 +72,36 @@ int encode_weight_maps(Weight *w) {
 
 // Quantised activations int8 [m][kp] as [box_rows][128 bytes] boxes with the 128-byte swizzle
 // (the K-major operand layout of the tensor core); rows past m read as zeros.
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char *e = getenv("LBK_NO_PDL");
-        return !(e && e[0] == '1');
-    }();
-    return on;
-}
-
 int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int box_rows) {
     return encode_2d_u8(map, q, kp, m, kp, 128, static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+// Grow-only scratch. A block that has been handed out is never freed before the context is
+// destroyed: a CUDA graph recorded by a caller (a decode step captured at 5..8 sequences, whose
+// projections take the quantise + GEMM path) has this address baked in, and a later, larger request
+// must not turn it into a dangling pointer. A larger request gets a new block; the old ones stay
+// (each at least 1.25x its predecessor, so together they hold less than five times the largest).
 int ctx_scratch(Ctx *ctx, size_t bytes, void **out) {
     if (bytes > ctx->scratch_bytes) {
-        if (ctx->scratch) {
-            LBK_CUDA(cudaStreamSynchronize(ctx->own_stream));
-            LBK_CUDA(cudaFree(ctx->scratch));
-            ctx->scratch = nullptr;
-            ctx->scratch_bytes = 0;
-        }
-        size_t want = bytes + (bytes >> 2) + 4096;
-        cudaError_t e = cudaMalloc(&ctx->scratch, want);
+        const size_t want = bytes + (bytes >> 2) + 4096;
+        void *fresh = nullptr;
+        cudaError_t e = cudaMalloc(&fresh, want);
         if (e != cudaSuccess) return fail(LBK_ERR_NOMEM, "cudaMalloc(%zu) failed: %s", want, cudaGetErrorString(e));
+        if (ctx->scratch) ctx->retired_scratch.push_back(ctx->scratch);
+        ctx->scratch = fresh;
         ctx->scratch_bytes = want;
     }
     *out = ctx->scratch;
     return LBK_OK;
+}
+
+// What a non-zero error word means. Code 7 is written by the decoder-step kernels when a position
+// read from device memory lies outside the cache; every other code marks a bounded wait that ran out.
+int device_error_status(int word) {
+    if (word == 7)
+        return fail(LBK_ERR_INVALID, "a decode position was outside its cache (position < 0 or >= capacity); the kernels of that step "
+                                     "refused to run and its results are invalid");
+    return fail(LBK_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d); results of that launch are invalid", word);
 }
 
 static size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
@@ -134,15 +137,11 @@ static int check_group(const lbk_weight *const *ws, size_t n, const Ctx *ctx) {
 // rows and its arithmetic grows with the rows; the GEMM path costs two launches but is flat in m.
 // Measured per call at 2B4T shapes (K 2560: q/k/v, o, gate/up; K 6912: down), GEMV against GEMM:
 // 4 rows 5.7 / 9.2 us and 9.3 / 13.3 us; 8 rows 7.6 / 9.4 and 15.0 / 13.3; 9 rows 9.7 / 9.4 and
-// 23.3 / 13.4; 16 rows 12.9 / 9.9 and 25.4 / 13.4. LBK_GEMV_ROWS=n forces "GEMV up to n rows" for A/B runs.
+// 23.3 / 13.4; 16 rows 12.9 / 9.9 and 25.4 / 13.4. lbk_set_gemv_rows(ctx, n) replaces the rule by
+// "GEMV up to n rows" on that context.
 bool use_gemv(const Ctx *ctx, size_t kp, size_t m) {
-    static const int forced = [] {
-        const char *e = getenv("LBK_GEMV_ROWS");
-        const int n = e ? atoi(e) : 0;
-        return n > LBK_GEMV_MAX_M ? LBK_GEMV_MAX_M : n;
-    }();
     if (m > LBK_GEMV_MAX_M || !gemv_fits(ctx, kp, m)) return false;
-    if (forced > 0) return m <= static_cast<size_t>(forced);
+    if (ctx->gemv_rows > 0) return m <= static_cast<size_t>(ctx->gemv_rows);
     return m <= 4 || (m <= 8 && kp < 4096);
 }
 
@@ -225,6 +224,7 @@ int lbk_destroy(lbk_ctx *c) {
     cudaSetDevice(ctx->device);
     cudaDeviceSynchronize();
     if (ctx->scratch) cudaFree(ctx->scratch);
+    for (void *p : ctx->retired_scratch) cudaFree(p);
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->small_scratch) cudaFree(ctx->small_scratch);
     if (ctx->gemm_acc) cudaFree(ctx->gemm_acc);
@@ -242,8 +242,15 @@ int lbk_check_device_error(lbk_ctx *c) {
     LBK_CUDA(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
     if (word != 0) {
         LBK_CUDA(cudaMemset(ctx->err_word, 0, sizeof(int)));
-        return fail(LBK_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d); results of that launch are invalid", word);
+        return device_error_status(word);
     }
+    return LBK_OK;
+}
+
+int lbk_set_gemv_rows(lbk_ctx *c, int rows) {
+    if (!c) return fail(LBK_ERR_INVALID, "context is null");
+    if (rows < 0 || rows > LBK_GEMV_MAX_M) return fail(LBK_ERR_INVALID, "lbk_set_gemv_rows: %d is outside 0..%d", rows, LBK_GEMV_MAX_M);
+    C_(c)->gemv_rows = rows;
     return LBK_OK;
 }
 
@@ -533,7 +540,7 @@ static int host_group(Ctx *ctx, const lbk_weight *const *ws, size_t n, size_t m,
     LBK_CUDA(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
     if (word) {
         LBK_CUDA(cudaMemset(ctx->err_word, 0, sizeof(int)));
-        return fail(LBK_ERR_TIMEOUT, "a bounded device-side wait gave up (code %d)", word);
+        return device_error_status(word);
     }
     return LBK_OK;
 }

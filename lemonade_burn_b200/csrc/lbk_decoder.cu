@@ -91,16 +91,30 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const float *x, const flo
     for (int i = threadIdx.x; i < n; i += 256) orow[i] = xr[i] * r * w[i];
 }
 
+// A position read from device memory is trusted by nobody: a step replayed once too often (a
+// recorded graph launched after the cache filled up) would otherwise write K/V rows past the
+// sequence's slab and read the RoPE tables out of range. Every kernel that takes its position
+// from `pos_dev` checks it first; a block whose position is outside [0, cap) records error code 7
+// in the context's error word and returns before touching memory. `last` is the highest
+// position the kernel uses (pos itself for one token, pos + n - 1 for a prompt pass). The reference
+// asserts the same on the host (model.rs:309).
+__device__ __forceinline__ bool pos_in_cache(int first, int last, int cap, int *err_word) {
+    if (first >= 0 && last < cap && first <= last) return true;
+    if (threadIdx.x == 0) atomicExch(err_word, 7);
+    return false;
+}
+
 // One block per (sequence, head). q heads first, then k heads (which are also written to the
 // cache together with v). cos/sin: [max_pos][hd] with both halves duplicated (model.rs:213-230).
 __global__ void rope_append_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                    const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                    const int *__restrict__ pos_dev, int pos_stride, int nh, int kvh, int hd, int cap,
-                                   uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
+                                   uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache, int *err_word) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
 
     const int b = blockIdx.y, h = blockIdx.x, pos = pos_dev[b * pos_stride];  // stride 0: one position for all sequences
+    if (!pos_in_cache(pos, pos, cap, err_word)) return;
     const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
     const int half = hd >> 1;
     if (h < nh) {
@@ -134,14 +148,15 @@ constexpr int kPartStride = kHd + 4;  // acc[128], max, sum, 2 pad floats: keeps
 __global__ void __launch_bounds__(256) attn_partial_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
                                                           const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
                                                           int pos_stride, int nh, int kvh, int cap, float scaling, int splits,
-                                                          float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
+                                                          float *__restrict__ part /* [b][nh][splits][kPartStride] */, int *err_word) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
 
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (warp >= group) return;
     const int total = pos_dev[b * pos_stride] + 1;  // keys 0..pos
+    if (!pos_in_cache(total - 1, total - 1, cap, err_word)) return;
+    if (warp >= group) return;
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -207,7 +222,7 @@ constexpr int kVRow = kHd * 2;           // bytes per staged V row
 __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
                                                                  const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev,
                                                                  int pos_stride, int nh, int kvh, int cap, float scaling, int splits,
-                                                                 float *__restrict__ part /* [b][nh][splits][kPartStride] */) {
+                                                                 float *__restrict__ part /* [b][nh][splits][kPartStride] */, int *err_word) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
     __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];
@@ -216,6 +231,7 @@ __global__ void __launch_bounds__(256) attn_partial_staged_kernel(const float *_
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
     const int total = pos_dev[b * pos_stride] + 1;  // keys 0..pos
+    if (!pos_in_cache(total - 1, total - 1, cap, err_word)) return;
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -311,7 +327,7 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
                                                         const float *__restrict__ sin_t, const int *__restrict__ pos_dev, int pos_stride, int nh,
                                                         int kvh, int cap, float scaling, int splits, uint16_t *__restrict__ kc,
                                                         uint16_t *__restrict__ vc, float *__restrict__ part, int *__restrict__ counters,
-                                                        float *__restrict__ out /* [b][nh*hd] */) {
+                                                        float *__restrict__ out /* [b][nh*hd] */, int *err_word) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
     __shared__ __align__(16) uint8_t s_k[kAttnChunk * kKRow];  // later: the merge's weights, [group][splits]
@@ -321,6 +337,7 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
     const int sp = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int group = nh / kvh, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, nthr = blockDim.x;
     const int pos = pos_dev[b * pos_stride], total = pos + 1;  // keys 0..pos
+    if (!pos_in_cache(pos, pos, cap, err_word)) return;  // every block of the sequence leaves: the counters stay zero
     const int per = (total + splits - 1) / splits;
     const int p0 = sp * per, p1 = min(total, p0 + per);
     const int head = kh * group + warp;
@@ -463,10 +480,11 @@ __global__ void __launch_bounds__(256, 3) attn_fused_kernel(const float *__restr
 __global__ void __launch_bounds__(256) rope_append_rows_kernel(float *__restrict__ q, const float *__restrict__ k, const float *__restrict__ v,
                                                               const float *__restrict__ cos_t, const float *__restrict__ sin_t,
                                                               const int *__restrict__ pos_dev, int nh, int kvh, int hd, int cap, int seq,
-                                                              uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache) {
+                                                              uint16_t *__restrict__ kcache, uint16_t *__restrict__ vcache, int *err_word) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
     const int row = blockIdx.x, pos = *pos_dev + row, half = hd >> 1;  // one block per prompt row, all its heads
+    if (!pos_in_cache(*pos_dev, *pos_dev + static_cast<int>(gridDim.x) - 1, cap, err_word)) return;
     const float *c = cos_t + static_cast<size_t>(pos) * hd, *s = sin_t + static_cast<size_t>(pos) * hd;
     for (int it = threadIdx.x; it < (nh + kvh) * half; it += blockDim.x) {
         const int h = it / half, i = it - h * half;
@@ -510,9 +528,10 @@ __device__ __forceinline__ float bf16_round(float x) { return bf16_to_f32(f32_to
 
 __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__restrict__ q, const uint16_t *__restrict__ kc,
                                                              const uint16_t *__restrict__ vc, const int *__restrict__ pos_dev, int n, int nh,
-                                                             int kvh, int cap, int seq, float scaling, float *__restrict__ out /* [n][nh*hd] */) {
+                                                             int kvh, int cap, int seq, float scaling, float *__restrict__ out /* [n][nh*hd] */, int *err_word) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
+    if (!pos_in_cache(*pos_dev, *pos_dev + n - 1, cap, err_word)) return;
     extern __shared__ __align__(16) uint8_t pf_smem[];
     uint8_t *s_kv = pf_smem, *s_q = pf_smem + 2 * kPfStage;  // two stages of [K chunk][V chunk], then the queries
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3, nthr = blockDim.x;
@@ -954,11 +973,13 @@ __global__ void __launch_bounds__(32) argmax_merge_kernel(const float *__restric
 }
 
 // pos[i] += 1 for the sequences that took part in the step (all of them without a mask)
+// Saturates far below overflow: a position that was already refused by the kernels above (code 7)
+// must stay refused however often the step is replayed, never wrap round to a valid one.
 __global__ void advance_pos_kernel(int *pos, const int *__restrict__ active, int n) {
     ptx::pdl_trigger();  // the next kernel of the step may be scheduled now
     ptx::pdl_wait();     // everything this kernel reads or overwrites is settled from here on
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n && (!active || active[i])) pos[i] += 1;
+    if (i < n && (!active || active[i]) && pos[i] < (1 << 30)) pos[i] += 1;
 }
 
 }  // namespace
@@ -1006,7 +1027,7 @@ static int rope_kv_append_impl(lbk_ctx *c, float *q_dev, const float *k_dev, con
     dim3 grid(static_cast<unsigned>(n_heads + kv_heads), static_cast<unsigned>(b));
     LBK_CUDA(launch_chained(rope_append_kernel, dim3(grid), dim3(64), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads),
                                             static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap),
-                                            kcache_dev, vcache_dev));
+                                            kcache_dev, vcache_dev, ctx->err_word));
     LBK_DEC_POST();
 }
 
@@ -1036,7 +1057,7 @@ static int attn_decode_impl(lbk_ctx *c, const float *q_dev, const uint16_t *kcac
     const bool staged = n_heads / kv_heads >= 4;  // several query heads share the rows: fetch them once per block
     LBK_CUDA(launch_chained(staged ? attn_partial_staged_kernel : attn_partial_kernel, dim3(grid), dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, kcache_dev, vcache_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads),
                                               static_cast<int>(cap), 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits),
-                                              scratch_dev));
+                                              scratch_dev, ctx->err_word));
     LBK_CUDA(cudaGetLastError());
     LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st, scratch_dev, static_cast<int>(splits), out_dev));
     ctx->launches++;
@@ -1065,7 +1086,7 @@ int lbk_rope_kv_append_rows(lbk_ctx *c, float *q_dev, const float *k_dev, const 
     if (head_dim == 0 || (head_dim & 1)) return fail(LBK_ERR_INVALID, "head_dim must be even");
     LBK_CUDA(launch_chained(rope_append_rows_kernel, dim3(static_cast<unsigned>(n)), dim3(256), 0, st, q_dev, k_dev, v_dev, cos_dev, sin_dev, pos_dev, static_cast<int>(n_heads),
                             static_cast<int>(kv_heads), static_cast<int>(head_dim), static_cast<int>(cap), static_cast<int>(seq), kcache_dev,
-                            vcache_dev));
+                            vcache_dev, ctx->err_word));
     LBK_DEC_POST();
 }
 
@@ -1089,7 +1110,7 @@ int lbk_attn_prefill(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev,
     dim3 grid(static_cast<unsigned>(kv_heads), static_cast<unsigned>((n + rows_per_block - 1) / rows_per_block));
     LBK_CUDA(launch_chained(attn_prompt_mma_kernel, grid, dim3(static_cast<unsigned>(32 * warps)), smem, st, q_dev, kcache_dev, vcache_dev, pos_dev,
                             static_cast<int>(n), static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap), static_cast<int>(seq),
-                            1.0f / sqrtf(static_cast<float>(head_dim)), out_dev));
+                            1.0f / sqrtf(static_cast<float>(head_dim)), out_dev, ctx->err_word));
     LBK_DEC_POST();
 }
 
@@ -1118,12 +1139,12 @@ static int attn_decode_fused_impl(lbk_ctx *c, const float *q_dev, const float *k
         LBK_CUDA(launch_chained(attn_fused_kernel<true>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
                                 cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
                                 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
-                                counters_dev, out_dev));
+                                counters_dev, out_dev, ctx->err_word));
     } else {
         LBK_CUDA(launch_chained(attn_fused_kernel<false>, grid, dim3(static_cast<unsigned>(32 * (n_heads / kv_heads))), 0, st, q_dev, k_dev, v_dev,
                                 cos_dev, sin_dev, pos_dev, pos_stride, static_cast<int>(n_heads), static_cast<int>(kv_heads), static_cast<int>(cap),
                                 1.0f / sqrtf(static_cast<float>(head_dim)), static_cast<int>(splits), kcache_dev, vcache_dev, scratch_dev,
-                                counters_dev, out_dev));
+                                counters_dev, out_dev, ctx->err_word));
         LBK_CUDA(launch_chained(attn_combine_kernel, dim3(static_cast<unsigned>(b * n_heads)), dim3(256), (splits + 1) * sizeof(float), st,
                                 scratch_dev, static_cast<int>(splits), out_dev));
         ctx->launches++;

@@ -94,22 +94,7 @@ struct GemmParams {
     const float *qscale;
     const int32_t *qsum;
     int *err_word;
-#ifdef LBK_TIMELINE
-    long long *timeline;  // [grid][16]: cycles each role spent waiting, debugging only
-    long long *trace;     // CTA 0: [8][512] clock per K block and event, debugging only
-#endif
 };
-
-#ifdef LBK_TIMELINE
-#define TL_WAIT(slot, expr) ([&]() { const long long t0__ = clock64(); const bool r__ = (expr); tl[slot] += clock64() - t0__; return r__; }())
-#else
-#define TL_WAIT(slot, expr) (expr)
-#endif
-#ifdef LBK_TIMELINE
-#define TRACE(ev, idx) do { if (p.trace && blockIdx.x == 0 && (idx) < 512) p.trace[(ev) * 512 + (idx)] = clock64(); } while (0)
-#else
-#define TRACE(ev, idx) do { } while (0)
-#endif
 
 // ---- tcgen05 wrappers ----------------------------------------------------------------------
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
@@ -244,10 +229,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
 
     const int k_blocks = p.k_blocks;
     bool ok = true;
-#ifdef LBK_TIMELINE
-    long long tl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    const long long tl_begin = clock64();
-#endif
     // tile -> (matrix, weight-row tile, token tile); token tiles vary fastest so that CTAs
     // running side by side share the same packed weights in L2
     auto decode_tile = [&](int tile, int &mat, int &m_tile, int &n_tile) {
@@ -279,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 for (int kb = kb0; kb < kb1; kb += G, ++gr) {
                     if ((kb % kPackBlocks) == 0) {
                         const int ps = pit % PS, pround = pit / PS;
-                        if (pround > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort))) {
+                        if (pround > 0 && !wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort)) {
                             ok = false;
                             break;
                         }
@@ -289,7 +270,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                         ++pit;
                     }
                     const int s = gr % PG, round = gr / PG;
-                    if (round > 0 && !TL_WAIT(0, wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort))) {
+                    if (round > 0 && !wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort)) {
                         ok = false;
                         break;
                     }
@@ -317,7 +298,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 if ((kb % kPackBlocks) == 0) {
                     if (++ps == PS) ps = 0;
                     if (ps == 0) pphase ^= 1u;
-                    if (!TL_WAIT(1, wait_bar(bar(C::kBarFullPack + ps), pphase, s_abort))) {
+                    if (!wait_bar(bar(C::kBarFullPack + ps), pphase, s_abort)) {
                         ok = false;
                         break;
                     }
@@ -328,7 +309,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     if (kb + b >= kb1) break;
                     if (!wrote) {
                         // the TMEM slots of this parity were last read by group gr - 2
-                        if (gr >= 2 && !TL_WAIT(2, wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort))) {
+                        if (gr >= 2 && !wait_bar(bar(C::kBarConsumed + lg), lg_phase, s_abort)) {
                             ok = false;
                             break;
                         }
@@ -378,7 +359,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
             const uint64_t bdesc0 = smem_desc_sw128(base);  // activation block stage 0; stage s adds s * kActBytes / 16
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tcount) {
                 const int a = tcount & 1, around = tcount >> 1;
-                if (around > 0 && !TL_WAIT(3, wait_bar(bar(C::kBarAccEmpty + a), (around - 1) & 1, s_abort))) {
+                if (around > 0 && !wait_bar(bar(C::kBarAccEmpty + a), (around - 1) & 1, s_abort)) {
                     ok = false;
                     break;
                 }
@@ -392,7 +373,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 const int n_mma = left < p.nt ? (left + 15) & ~15 : p.nt;
                 const uint32_t idesc = C::kIdesc | (static_cast<uint32_t>(n_mma >> 3) << 17);
                 for (int kb = kb0; kb < kb1; kb += G) {
-                    if (!TL_WAIT(4, wait_bar(bar(C::kBarFull + sp), full_phase, s_abort))) {
+                    if (!wait_bar(bar(C::kBarFull + sp), full_phase, s_abort)) {
                         ok = false;
                         break;
                     }
@@ -441,10 +422,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 }
             }
             asm volatile("bar.sync 2, 128;" ::: "memory");  // the four epilogue warps
-#ifdef LBK_TIMELINE
-            const long long tl_e0 = clock64();
-#endif
-            if (!TL_WAIT(6, wait_bar(bar(C::kBarAccFull + a), around & 1, s_abort))) {
+            if (!wait_bar(bar(C::kBarAccFull + a), around & 1, s_abort)) {
                 ok = false;
                 break;
             }
@@ -502,25 +480,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                 }
             }
             tc_fence_before();
-#ifdef LBK_TIMELINE
-            tl[7] += clock64() - tl_e0;  // wait + drain of this tile
-            tl[5] += 1;
-#endif
             asm volatile("bar.sync 2, 128;" ::: "memory");  // all four warps are done with qs/inv of this parity
             if (lane == 0) ptx::mbar_arrive(bar(C::kBarAccEmpty + a));
         }
     }
 
     if (!ok && lane == 0) atomicExch(p.err_word, 5);
-#ifdef LBK_TIMELINE
-    if (p.timeline && lane == 0) {
-        long long *d = p.timeline + static_cast<long long>(blockIdx.x) * 16;
-        if (warp == kTmaWarp) d[0] = tl[0];
-        if (warp == kExpWarp0) { d[1] = tl[1]; d[2] = tl[2]; }
-        if (warp == kMmaWarp) { d[3] = tl[3]; d[4] = tl[4]; d[5] = tl[5]; d[8] = clock64() - tl_begin; }
-        if (warp == 0) { d[6] = tl[6]; d[7] = clock64() - tl_begin; d[9] = tl[7]; d[10] = tl[5]; }
-    }
-#endif
     tc_fence_before();
     __syncthreads();
     if (warp == kMmaWarp) {
@@ -569,12 +534,6 @@ static int choose_ksplit(int tiles, int k_blocks, int sms, int *kb_part) {
     return best;
 }
 
-#ifdef LBK_TIMELINE
-static long long *g_gemm_timeline = nullptr, *g_gemm_trace = nullptr;
-extern "C" void lbk_debug_set_gemm_timeline(long long *buf) { g_gemm_timeline = buf; }
-extern "C" void lbk_debug_set_gemm_trace(long long *buf) { g_gemm_trace = buf; }
-
-#endif
 
 // Token rows per tile for a launch: the multiple of 16 (at most 192) whose tile count fills whole
 // rounds of the grid best. Per K block a tile costs the larger of the tensor-pipe time
@@ -631,10 +590,6 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.qscale = g.qscale;
     p.qsum = g.qsum;
     p.err_word = ctx->err_word;
-#ifdef LBK_TIMELINE
-    p.timeline = g_gemm_timeline;
-    p.trace = g_gemm_trace;
-#endif
     if (tiles == 0 || p.k_blocks == 0) return LBK_OK;
     p.ksplit = choose_ksplit(tiles, p.k_blocks, ctx->sm_count, &p.kb_part);
     if (p.ksplit > 1) {

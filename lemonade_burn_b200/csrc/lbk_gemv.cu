@@ -55,9 +55,6 @@ struct GemvParams {
     float wscale[LBK_MAX_GROUP];
     float *out[LBK_MAX_GROUP];
     int32_t *iout[LBK_MAX_GROUP];
-#ifdef LBK_TIMELINE
-    long long *timeline;   // [warps_total][8] clock samples, debugging only
-#endif
     alignas(64) CUtensorMap tmap[LBK_MAX_GROUP];
 };
 
@@ -107,12 +104,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     const int g = lane >> 2, t = lane & 3;
     const int chunks = p.chunks;
     ptx::pdl_trigger();  // the kernel after this one may be scheduled; it orders itself with pdl_wait
-#ifdef LBK_TIMELINE
-    long long tl_start = clock64(), tl_prologue = 0, tl_first = 0, tl_polls = 0;
-    long long tl_a = 0, tl_b = 0, tl_c = 0, tl_d = 0;
-    unsigned long long tl_gstart;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_gstart));
-#endif
 
     // ---- this warp's run --------------------------------------------------------------------
     // Whole tiles per warp when every warp has several; otherwise (the decode shapes: 160..864
@@ -166,21 +157,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     // Weights do not depend on the kernel before this one, activations do: set up the ring and
     // start the first weight loads, THEN wait for the predecessor (a chained launch overlaps all of
     // this with its tail), then read the activation rows.
-#ifdef LBK_TIMELINE
-    long long tl_e = 0, tl_f = 0;
-    const long long tl_s0 = clock64();
-#endif
     if (lane == 0) {
         for (int s = 0; s < kStages; ++s) ptx::mbar_init(full0 + s * 8, 1);
         ptx::fence_barrier_init();
-#ifdef LBK_TIMELINE
-        tl_e = clock64();
-#endif
         const int first = n_items < kStages ? n_items : kStages;
         for (int i = 0; i < first; ++i) issue(i);
-#ifdef LBK_TIMELINE
-        tl_f = clock64();
-#endif
     }
     ptx::pdl_wait();
     RowCache rc;
@@ -192,9 +173,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         if (p.pre != LBK_PRE_RMS) load_cached(p.pre_y + static_cast<size_t>(slot) * k, k, idx, nthr, rc_y);
     }
 
-#ifdef LBK_TIMELINE
-    tl_a = clock64();  // after barrier init + first TMA issues
-#endif
     // ---- prologue: quantised activations into shared memory (overlaps the first loads) -----
     float *s_part = reinterpret_cast<float *>(sm + L.part);
     int *s_parti = reinterpret_cast<int *>(sm + L.parti);
@@ -253,13 +231,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                 const float am = warp_max(max_cached(rc));
                 if (lane == 0) s_part[slot * kWarps + sub] = am;
             }
-#ifdef LBK_TIMELINE
-            tl_b = clock64();  // row loaded, warp max done
-#endif
             __syncthreads();
-#ifdef LBK_TIMELINE
-            tl_c = clock64();  // after the first CTA barrier
-#endif
             if (have) {
                 float am = 0.0f;
                 for (int w = 0; w < P; ++w) am = fmaxf(am, s_part[slot * kWarps + w]);
@@ -301,9 +273,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
                 }
             }
         }
-#ifdef LBK_TIMELINE
-        tl_d = clock64();  // quantised and stored
-#endif
         __syncthreads();
         if (tid >= 32 && tid < 32 + m) {  // a different warp from the one that writes s_inv below: both run at once
             const int tk = tid - 32;
@@ -334,9 +303,6 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     __syncthreads();
 
     if (n_items == 0 && !p.split) return;
-#ifdef LBK_TIMELINE
-    tl_prologue = clock64();
-#endif
 
     // ---- main loop -----------------------------------------------------------------------
     const LaneOffsets off = lane_offsets(lane);
@@ -388,17 +354,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
     };
     int first_chunk = chunk_begin;  // chunk at which this warp entered the current tile
     for (int item = 0; item < n_items; ++item) {
-#ifdef LBK_TIMELINE
-        const long long tl_w0 = clock64();
-#endif
         if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
             ok = false;
             break;
         }
-#ifdef LBK_TIMELINE
-        if (item == 0) tl_first = clock64();
-        else tl_polls += clock64() - tl_w0;  // cycles spent waiting for data after the first item
-#endif
         consume_stage<MT>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
         __syncwarp();  // every lane has read the stage before it is refilled
         if (lane == 0 && item + kStages < n_items) issue(s);
@@ -446,25 +405,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_kernel(const __grid_constant
         }
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 1);
-#ifdef LBK_TIMELINE
-    if (lane == 0 && p.timeline) {
-        unsigned long long gend;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(gend));
-        long long *d = p.timeline + gw * 16;
-        d[0] = tl_prologue - tl_start; d[1] = tl_first - tl_prologue; d[2] = clock64() - tl_first;
-        d[3] = n_items; d[4] = static_cast<long long>(tl_gstart); d[5] = static_cast<long long>(gend); d[6] = tl_polls; d[7] = blockIdx.x;
-        d[13] = tl_s0 - tl_start; d[14] = tl_e - tl_s0; d[15] = tl_f - tl_e;
-        d[8] = tl_a - tl_start; d[9] = tl_b - tl_a; d[10] = tl_c - tl_b; d[11] = tl_d - tl_c; d[12] = tl_prologue - tl_d;
-    }
-#endif
 }
 
 }  // namespace
 
-#ifdef LBK_TIMELINE
-static long long *g_timeline = nullptr;
-extern "C" void lbk_debug_set_timeline(long long *buf) { g_timeline = buf; }
-#endif
 
 int gemv_xq_stride(size_t kp) {
     const size_t chunks = (kp / 4 + kChunkBytes - 1) / kChunkBytes;
@@ -528,9 +472,6 @@ int launch_gemv(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.pre_eps = g.pre_eps;
     if (g.pre != 0 && !(g.x && gemv_pre_supported(g.m, cols)))
         return fail(LBK_ERR_UNSUPPORTED, "input transform: %zu token rows of %zu columns are not held in registers by the decode kernel", g.m, cols);
-#ifdef LBK_TIMELINE
-    p.timeline = g_timeline;
-#endif
     if (tiles == 0) return LBK_OK;
 
     // few tiles per warp: let the 16 warps of a CTA share its tiles chunk by chunk

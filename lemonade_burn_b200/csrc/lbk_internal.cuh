@@ -48,9 +48,11 @@ struct Ctx {
     // grow-only device scratch for the host-pointer entry points and the GEMM pre-pass
     void *scratch = nullptr;
     size_t scratch_bytes = 0;
+    std::vector<void *> retired_scratch;  // earlier, smaller scratch blocks: kept until lbk_destroy (recorded graphs may point into them)
     cudaStream_t own_stream = nullptr;  // used by the host-pointer entry points
     void *small_scratch = nullptr;      // kSmallScratchBytes, allocated once at init (reductions)
     int32_t *gemm_acc = nullptr;        // kGemmAccBytes, allocated once at init: int32 sums of a prefill GEMM split along K
+    int gemv_rows = 0;                  // lbk_set_gemv_rows: 0 = measured rule, n = fused kernel up to n token rows
 };
 
 struct Weight {
@@ -64,6 +66,7 @@ struct Weight {
 };
 
 int ctx_scratch(Ctx *ctx, size_t bytes, void **out);
+int device_error_status(int word);  // status and message for a non-zero error word
 // One-time per-context kernel attribute set-up (opt-in shared memory sizes).
 int kernels_init(Ctx *ctx);
 int gemv_init(Ctx *ctx);
@@ -97,9 +100,7 @@ struct GroupArgs {
 bool gemv_pre_supported(size_t m, size_t cols);
 
 // Launch with programmatic stream serialisation: the grid may be scheduled while the previous
-// kernel of the stream drains; the kernel orders itself with ptx::pdl_wait(). The environment
-// variable LBK_NO_PDL=1 turns every such launch into an ordinary one (for A/B timing).
-bool pdl_enabled();
+// kernel of the stream drains; the kernel orders itself with ptx::pdl_wait().
 template <typename... KArgs, typename... Args>
 cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
     cudaLaunchConfig_t cfg{};
@@ -111,7 +112,7 @@ cudaError_t launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     attr.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr.val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = &attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -412,12 +412,8 @@ int enqueue_step(Model *m, Cache *c, cudaStream_t st) {
 // Prompt rows per pass. More rows fill the GEMM's tile rounds better (a 4032-token prompt at 2B4T
 // shapes: 41.3 ms at 1024 rows a pass, 34.8 at 2048, 30.6 at 4096); the work buffers grow with them
 // (about 150 KB per row at those shapes, allocated for the rows a prompt really has).
-// LBK_PREFILL_ROWS changes the default; lbk_model_set_prefill_rows sets it per model.
-const size_t kPrefillChunk = [] {
-    const char *e = getenv("LBK_PREFILL_ROWS");
-    const long v = e ? atol(e) : 0;
-    return v >= 16 && v <= 8192 ? static_cast<size_t>(v) : static_cast<size_t>(4096);
-}();
+// lbk_model_set_prefill_rows changes it per model.
+constexpr size_t kPrefillChunk = 4096;
 constexpr size_t kLogitRows = 128;      // rows of logits staged on the device at a time when every token's are wanted
 
 int ensure_prefill_buffers(Model *m, Cache *c, size_t rows) {
@@ -618,9 +614,11 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
     const Json *jb = cj.get("bos_token_id");
     cfg.bos_token_id = jb && jb->kind == Json::Num ? static_cast<int>(jb->num) : 0;
     // model.rs:151-153: only the relu2, tied-embedding family
+    // (both fields are required members of the reference's Config, model.rs:22-36: a file without them does not load there either)
     const Json *ja = cj.get("hidden_act"), *jtie = cj.get("tie_word_embeddings");
-    if (ja && !(ja->kind == Json::Str && ja->str == "relu2")) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: hidden_act must be relu2");
-    if (jtie && !(jtie->kind == Json::Bool && jtie->b)) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: tie_word_embeddings must be true");
+    if (!ja || !jtie) return fail(LBK_ERR_INVALID, "%s/config.json: missing field %s", directory, !ja ? "hidden_act" : "tie_word_embeddings");
+    if (!(ja->kind == Json::Str && ja->str == "relu2")) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: hidden_act must be relu2");
+    if (!(jtie->kind == Json::Bool && jtie->b)) return fail(LBK_ERR_UNSUPPORTED, "unsupported config: tie_word_embeddings must be true");
     if (!cfg.num_attention_heads || !cfg.num_key_value_heads || cfg.hidden_size % cfg.num_attention_heads ||
         cfg.num_attention_heads % cfg.num_key_value_heads || !cfg.num_hidden_layers || !cfg.max_position_embeddings)
         return fail(LBK_ERR_INVALID, "config.json: inconsistent head counts or sizes");

@@ -69,9 +69,6 @@ struct SweepParams {
     const CtaRec *cta;       // [grid]
     int xq_bytes;            // bytes per activation slot
     int *err_word;
-#ifdef LBK_TIMELINE
-    long long *timeline;     // [warps][16] clock samples, debugging only
-#endif
 };
 
 namespace {
@@ -104,11 +101,6 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
     const int gw = blockIdx.x * kWarps + warp;
-#ifdef LBK_TIMELINE
-    long long tl_start = clock64(), tl_setup = 0, tl_quant = 0, tl_wait = 0, tl_items = 0, tl_nq = 0;
-    unsigned long long tl_g0;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tl_g0));
-#endif
     // The tables and activation rows are read again by the next launch while half a gigabyte of
     // weights streams through L2 in between: ask L2 to keep the former and drop the latter first.
     const uint64_t keep = ptx::policy_evict_last(), stream_once = ptx::policy_evict_first();
@@ -192,9 +184,6 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         ptx::fence_barrier_init();
         for (int s = 0; s < kSweepStages && issued < n_stages; ++s) issue(s);
     }
-#ifdef LBK_TIMELINE
-    tl_setup = clock64() - tl_start;
-#endif
 
     // ---- CTA prologue: quantise the activation row of every group this CTA touches ----------
     // (quant.rs:100-118). Four warps per slot; rows of up to 4096 columns are read once.
@@ -226,9 +215,6 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         if (tid < n_slots) s_sum[tid] = s_parti[tid * 4] + s_parti[tid * 4 + 1] + s_parti[tid * 4 + 2] + s_parti[tid * 4 + 3];
         __syncthreads();
     }
-#ifdef LBK_TIMELINE
-    tl_quant = clock64() - tl_start - tl_setup;
-#endif
     if (n_stages <= 0) return;
 
     // ---- consume cursor ----------------------------------------------------------------
@@ -319,17 +305,10 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         const int c1 = min(cgrp.chunks, c0 + remaining);
         remaining -= c1 - c0;
         for (int chunk = c0; chunk < c1; ++chunk) {
-#ifdef LBK_TIMELINE
-            const long long tw0 = clock64();
-#endif
             if (!ptx::mbar_wait(full0 + s * 8, phase, kWaitLimit)) {
                 ok = false;
                 break;
             }
-#ifdef LBK_TIMELINE
-            tl_wait += clock64() - tw0;
-            ++tl_items;
-#endif
             if (chunk == c0) consume_stage<1, true>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
             else consume_stage<1, false>(stage_ptr + s * kStageBytes, off, xrow, static_cast<uint32_t>(chunk) * kChunkCols, acc);
             __syncwarp();  // every lane has read the stage before it is refilled
@@ -347,16 +326,6 @@ __global__ void __launch_bounds__(kThreads, 1) sweep_kernel(const SweepParams p)
         else write_tile(v_lo, v_hi);
     }
     if (!ok && lane == 0) atomicExch(p.err_word, 2);
-#ifdef LBK_TIMELINE
-    if (lane == 0 && p.timeline) {
-        unsigned long long g1;
-        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(g1));
-        long long *d = p.timeline + static_cast<long long>(gw) * 16;
-        d[0] = tl_setup; d[1] = tl_quant; d[2] = tl_wait; d[3] = tl_items; d[4] = static_cast<long long>(tl_g0);
-        d[5] = static_cast<long long>(g1); d[6] = clock64() - tl_start; d[7] = tl_nq;
-
-    }
-#endif
 }
 
 }  // namespace
@@ -521,10 +490,6 @@ int sweep_build(Ctx *ctx, const std::vector<GroupArgs> &groups, SweepTables **ou
     return LBK_OK;
 }
 
-#ifdef LBK_TIMELINE
-static long long *g_sweep_timeline = nullptr;
-extern "C" void lbk_debug_set_sweep_timeline(long long *buf) { g_sweep_timeline = buf; }
-#endif
 
 int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream) {
     if (!tb || tb->grid == 0) return LBK_OK;
@@ -536,9 +501,6 @@ int sweep_launch(Ctx *ctx, const SweepTables *tb, cudaStream_t stream) {
     p.handoff = tb->handoff;
     p.xq_bytes = tb->xq_bytes;
     p.err_word = ctx->err_word;
-#ifdef LBK_TIMELINE
-    p.timeline = g_sweep_timeline;
-#endif
     sweep_kernel<<<tb->grid, kThreads, tb->smem, stream>>>(p);
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;

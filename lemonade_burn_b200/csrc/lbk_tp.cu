@@ -30,7 +30,7 @@ namespace lbk {
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpMaxTokens = 256;                   // token rows per call on the fused path
 constexpr size_t kTpPartialBytes = 8u << 20;        // int32 partial dots of one call
-constexpr uint32_t kTpWaitLimit = 1u << 24;         // polls of a peer's word before giving up
+constexpr uint32_t kTpWaitLimit = 1u << 24;         // default: polls of a peer's word before giving up (lbk_tp_comm_set_wait_limit)
 
 // The same layout in every rank's region.
 struct TpRegion {
@@ -45,6 +45,7 @@ struct TpComm {
     Ctx *ctx;
     int world, rank;
     TpRegion *region[kTpMaxWorld];  // region[r] as mapped in this process; region[rank] is local
+    uint32_t wait_limit = kTpWaitLimit;
 };
 
 namespace {
@@ -62,7 +63,7 @@ __device__ __forceinline__ int quant_one(float v, float scale) {
 // all ranks' slices.
 __global__ void __launch_bounds__(256) tp_quantize_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ x, int k,
                                                           int kp, int8_t *__restrict__ q, float *__restrict__ scale,
-                                                          int32_t *__restrict__ sum, int *err_word) {
+                                                          int32_t *__restrict__ sum, int *err_word, uint32_t wait_limit) {
     __shared__ float s_f[8];
     __shared__ int s_i[8];
     __shared__ float s_scale;
@@ -101,7 +102,7 @@ __global__ void __launch_bounds__(256) tp_quantize_kernel(const TpPtrs peers, in
             unsigned long long got = 0;
             uint32_t polls = 0;
             while (((got = *slot) >> 32) != seq) {
-                if (++polls > kTpWaitLimit) {
+                if (++polls > wait_limit) {
                     ok = false;
                     break;
                 }
@@ -153,17 +154,21 @@ __global__ void __launch_bounds__(256) tp_quantize_kernel(const TpPtrs peers, in
 // `total4` = m * rows / 4 (rows is a multiple of 4 on this path).
 __global__ void __launch_bounds__(256) tp_reduce_scale_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ ascale,
                                                               float wscale, int rows, int total4, float *__restrict__ out,
-                                                              int32_t *__restrict__ dots_out, int *err_word) {
+                                                              int32_t *__restrict__ dots_out, int *err_word, uint32_t wait_limit) {
     TpRegion *me = peers.r[rank];
     const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->r_seq);
     const int tid = threadIdx.x;
-    // this rank's partial dots were written by the kernel before this one: say so to everybody
-    if (blockIdx.x == 0 && tid < world) *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->ready[rank][0]) = seq;
+    // this rank's partial dots were written by the kernel before this one (complete at the kernel
+    // boundary); the fence orders them, system wide, before the flag that tells every peer so
+    if (blockIdx.x == 0 && tid < world) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->ready[rank][0]) = seq;
+    }
     if (tid < world) {
         volatile unsigned int *flag = &me->ready[tid][0];
         uint32_t polls = 0;
         while (static_cast<int>(*flag - seq) < 0) {  // a peer can only be at this call or, once we are through, past it
-            if (++polls > kTpWaitLimit) {
+            if (++polls > wait_limit) {
                 atomicExch(err_word, 6);
                 break;
             }
@@ -288,6 +293,13 @@ int lbk_tp_comm_destroy(lbk_tp_comm *t) {
     return LBK_OK;
 }
 
+int lbk_tp_comm_set_wait_limit(lbk_tp_comm *t, uint32_t polls) {
+    if (!t) return fail(LBK_ERR_INVALID, "tensor-parallel communicator is null");
+    if (polls == 0) return fail(LBK_ERR_INVALID, "a wait limit of 0 polls would give up before looking");
+    reinterpret_cast<TpComm *>(t)->wait_limit = polls;
+    return LBK_OK;
+}
+
 void *lbk_tp_partial_buffer(lbk_tp_comm *t) {
     if (!t) return nullptr;
     TpComm *tc = reinterpret_cast<TpComm *>(t);
@@ -310,7 +322,7 @@ int lbk_tp_quantize(lbk_tp_comm *t, const float *x_dev, size_t m, size_t k, int8
     LBK_CUDA(cudaSetDevice(tc->ctx->device));
     tp_quantize_kernel<<<static_cast<unsigned>(m), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         ptrs_of(tc), tc->world, tc->rank, x_dev, static_cast<int>(k), static_cast<int>(lbk_padded_cols(k)), q_dev, scale_dev, sum_dev,
-        tc->ctx->err_word);
+        tc->ctx->err_word, tc->wait_limit);
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
@@ -331,7 +343,7 @@ int lbk_tp_reduce_scale(lbk_tp_comm *t, const float *scale_dev, float wscale, si
     if (grid > 2 * tc->ctx->sm_count) grid = 2 * tc->ctx->sm_count;
     tp_reduce_scale_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), tc->world, tc->rank, scale_dev, wscale,
                                                                                static_cast<int>(rows), total4, out_dev, dots_out_dev,
-                                                                               tc->ctx->err_word);
+                                                                               tc->ctx->err_word, tc->wait_limit);
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;

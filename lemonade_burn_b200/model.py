@@ -73,15 +73,26 @@ class KvCache:
     """model.rs:136-141, here fixed capacity, bf16, [layers][b][kv_heads][cap][head_dim]."""
 
     def __init__(self, cfg: Config, b: int, cap: int, device):
+        if cap < 1 or cap > cfg.max_position_embeddings:  # the RoPE tables end there (model.rs:213-230, 309)
+            raise ValueError(f"capacity {cap} is outside 1..max_position_embeddings ({cfg.max_position_embeddings})")
+        if b < 1:
+            raise ValueError("a cache serves at least one sequence")
         shape = (cfg.num_hidden_layers, b, cfg.num_key_value_heads, cap, cfg.head_dim())
         self.k = torch.zeros(shape, dtype=torch.bfloat16, device=device)
         self.v = torch.zeros(shape, dtype=torch.bfloat16, device=device)
         self.pos = torch.zeros(1, dtype=torch.int32, device=device)  # cache.len, on the device
         self.b, self.cap = b, cap
+        self.host_len = 0  # the same length on the host: `forward` refuses a step that would not fit
 
     @property
     def len(self) -> int:
         return int(self.pos.item())
+
+    def reserve(self, n: int = 1) -> None:
+        """Raises unless `n` more positions fit (model.rs:309 asserts pos0 + m <= rope_len). Called by
+        `BitNet.forward` before anything is launched; the kernels check the device-side position too."""
+        if self.host_len + n > self.cap:
+            raise ValueError(f"the cache is full: {self.host_len} of {self.cap} positions are used, {n} more do not fit")
 
 
 class BitNet:
@@ -130,6 +141,9 @@ class BitNet:
         from safetensors import safe_open
         directory = Path(directory)
         raw = json.loads((directory / "config.json").read_text())
+        for key in ("hidden_act", "tie_word_embeddings"):  # required fields of the reference's Config (model.rs:22-36)
+            if key not in raw:
+                raise ValueError(f"{directory / 'config.json'}: missing field {key}")
         cfg = Config(**{k: raw[k] for k in Config.__dataclass_fields__ if k in raw})
         path = directory / FILE_NAME
         tensors = {}
@@ -142,7 +156,7 @@ class BitNet:
         return cls(cfg, tensors, ctx, device)
 
     def new_cache(self, b: int = 1, cap: Optional[int] = None) -> KvCache:
-        """model.rs:234-236"""
+        """model.rs:234-236. The capacity cannot exceed the RoPE tables (max_position_embeddings)."""
         return KvCache(self.cfg, b, cap or self.cfg.max_position_embeddings, self.device)
 
     # ---- one decode step -------------------------------------------------------------------------
@@ -159,6 +173,7 @@ class BitNet:
         b = tokens.shape[0]
         if b != cache.b:
             raise ValueError("batch size differs from the cache's")
+        cache.reserve(1)
         if splits is None:
             splits = attention_splits(cache.cap)
         H, I, nh, kvh, hd = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim()
@@ -264,6 +279,7 @@ class BitNet:
             add_norm(x, d, self.final_norm, x)
         logits = ops.bf16_linear(n, self.lm_head, self.ctx)
         chk(lib.lbk_advance_pos(h, P(cache.pos), st))
+        cache.host_len += 1
         return logits
 
     def argmax(self, logits: torch.Tensor) -> torch.Tensor:

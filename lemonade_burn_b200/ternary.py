@@ -74,6 +74,11 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.lbk_launch_count(self.handle))
 
+    def set_gemv_rows(self, rows: int) -> None:
+        """0: the measured rule decides between the fused few-row kernel and quantise + GEMM;
+        n: the fused kernel takes every call of at most n token rows (same bits either way)."""
+        _lib.check(self._lib.lbk_set_gemv_rows(self.handle, rows))
+
 
 _default_ctx: Optional[Context] = None
 

@@ -38,6 +38,37 @@ def test_ternary_linear3_qkv(oracle, ctx, m):
     ctx.check_device_error()
 
 
+@pytest.mark.parametrize("cols", [2560, 6912])
+@pytest.mark.parametrize("m", [5, 9, 12, 16])
+def test_fused_kernel_forced_up_to_16_rows(oracle, ctx, m, cols):
+    """By default 9..16 token rows (and 5..8 of long rows) go to quantise + GEMM; lbk_set_gemv_rows(16)
+    sends them to the fused few-row kernel's second token tile instead. Both must give the oracle's
+    bits, and the setting must be undone by 0."""
+    import torch
+    from lemonade_burn_b200 import ops
+    lins = [make_linear(oracle, r, cols, 40 + i, ctx, sc) for i, (r, sc) in enumerate([(1040, 41.0), (656, 57.5)])]
+    x = np.random.default_rng(m + cols).standard_normal((m, cols)).astype(np.float32)
+    q, s, ssum = oracle.quantize_acts(x)
+    wf, wi = oracle.simd_gemm_multi([p for _, p, _ in lins], [w for _, _, w in lins], q, s, ssum, want_i32=True)
+    xd = torch.from_numpy(x).cuda()
+    try:
+        for forced in (16, 0):
+            ctx.set_gemv_rows(forced)
+            before = ctx.launch_count()
+            outs, iouts = ops.ternary_linear_multi(xd, [l for l, _, _ in lins], want_i32=True)
+            torch.cuda.synchronize()
+            launches = ctx.launch_count() - before
+            assert (launches == 1) if forced else (launches >= 2), "one fused launch when forced, quantise + GEMM otherwise"
+            for o_, i_, ef, ei in zip(outs, iouts, wf, wi):
+                assert np.array_equal(i_.cpu().numpy(), ei)
+                assert np.array_equal(o_.cpu().numpy().view(np.uint32), ef.view(np.uint32))
+    finally:
+        ctx.set_gemv_rows(0)
+    with pytest.raises(Exception):
+        ctx.set_gemv_rows(17)
+    ctx.check_device_error()
+
+
 def test_ternary_linear2_gate_up_and_down(oracle, ctx):
     import torch
     from lemonade_burn_b200 import ops

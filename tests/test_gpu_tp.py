@@ -152,3 +152,57 @@ def test_nccl_ranks_match_unsharded():
         p.join(timeout=120)
         assert p.exitcode == 0
     assert all(ok for _, ok in res), res
+
+
+def test_missing_peer_times_out_and_the_context_survives(oracle, ctx):
+    """Failure detection without a fault: a two-rank communicator whose second region is a local buffer
+    that nobody ever writes (the peer "never arrives"). With a short wait limit the exchange kernel gives
+    up, RETURNS, and lbk_check_device_error reports LBK_ERR_TIMEOUT; the error word clears and the same
+    context then runs an ordinary op with the right bits. The reference's rule is the same one level up:
+    a failed request becomes an error reply, never a dead worker (crates/lb-server/src/main.rs:92-100)."""
+    import torch
+    from lemonade_burn_b200 import _lib, ops
+    lib, h = ctx._lib, ctx.handle
+    regions, handle = [], (C.c_ubyte * 64)()
+    for _ in range(2):
+        r = C.c_void_p()
+        _lib.check(lib.lbk_tp_region_alloc(h, C.byref(r), handle))
+        regions.append(r)
+    arr, _keep = _lib.ptr_array([r.value for r in regions])
+    comm = C.c_void_p()
+    _lib.check(lib.lbk_tp_comm_create(h, 2, 0, arr, C.byref(comm)))
+    try:
+        with pytest.raises(_lib.LbkError):
+            _lib.check(lib.lbk_tp_comm_set_wait_limit(comm, 0))
+        _lib.check(lib.lbk_tp_comm_set_wait_limit(comm, 20000))  # a few milliseconds of polling
+        m, k = 3, 512
+        x = torch.randn(m, k, device="cuda")
+        q = torch.empty((m, k), dtype=torch.int8, device="cuda")
+        s = torch.empty(m, device="cuda")
+        ssum = torch.empty(m, dtype=torch.int32, device="cuda")
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        _lib.check(lib.lbk_tp_quantize(comm, C.c_void_p(x.data_ptr()), m, k, C.c_void_p(q.data_ptr()), C.c_void_p(s.data_ptr()),
+                                       C.c_void_p(ssum.data_ptr()), st))
+        torch.cuda.synchronize()          # the kernel came back by itself
+        with pytest.raises(_lib.LbkError) as info:
+            ctx.check_device_error()
+        assert info.value.status == 5     # LBK_ERR_TIMEOUT
+        ctx.check_device_error()          # the word was cleared by the read
+        # the reduce kernel's wait runs out the same way
+        out = torch.empty((m, 8), device="cuda")
+        _lib.check(lib.lbk_tp_reduce_scale(comm, C.c_void_p(s.data_ptr()), C.c_float(1.0), m, 8, C.c_void_p(out.data_ptr()), None, st))
+        torch.cuda.synchronize()
+        with pytest.raises(_lib.LbkError) as info:
+            ctx.check_device_error()
+        assert info.value.status == 5
+    finally:
+        lib.lbk_tp_comm_destroy(comm)
+        for r in regions:
+            lib.lbk_tp_region_free(h, r)
+    # the context is intact: an ordinary op gives the oracle's bits
+    packed, ws, xh = _case(oracle, rows=256, cols=512, m=2)
+    lin = ops.TernaryLinear(torch.from_numpy(packed).cuda(), float(ws), 512, ctx)
+    outs, iouts = ops.ternary_linear_multi(torch.from_numpy(xh).cuda(), [lin], want_i32=True)
+    qq, ss, sm = oracle.quantize_acts(xh)
+    assert np.array_equal(iouts[0].cpu().numpy(), oracle.ternary_gemm_i32(packed, 512, qq, sm))
+    ctx.check_device_error()

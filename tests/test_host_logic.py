@@ -32,3 +32,35 @@ def test_attention_slices():
     from lemonade_burn_b200 import model
     assert model.attention_splits(1) == 1 and model.attention_splits(32) == 1 and model.attention_splits(33) == 2
     assert model.attention_splits(4160) == 130 and model.attention_splits(1 << 20) == 256
+
+
+def test_cache_refuses_positions_beyond_its_capacity():
+    """BitNet::forward asserts pos0 + m <= rope_len (model.rs:309). Here: a cache cannot be larger than
+    the RoPE tables, and the host-side length refuses the step that would not fit, before any launch."""
+    from lemonade_burn_b200 import model
+    cfg = model.Config(256, 384, 2, 1, 1, 100, 1e-5, 500000.0, 8)
+    with pytest.raises(ValueError, match="max_position_embeddings"):
+        model.KvCache(cfg, 1, 9, "cpu")
+    with pytest.raises(ValueError):
+        model.KvCache(cfg, 0, 4, "cpu")
+    cache = model.KvCache(cfg, 2, 3, "cpu")
+    for _ in range(3):
+        cache.reserve(1)
+        cache.host_len += 1
+    with pytest.raises(ValueError, match="cache is full"):
+        cache.reserve(1)
+    assert cache.host_len == 3
+
+
+def test_config_json_needs_the_reference_fields(tmp_path):
+    """hidden_act and tie_word_embeddings are required members of the reference's Config
+    (model.rs:22-36): a config.json without them is refused, like one with another activation."""
+    import json
+    from lemonade_burn_b200 import model
+    cfg = model.Config(256, 384, 2, 1, 1, 100, 1e-5, 500000.0, 8)
+    for drop in ("hidden_act", "tie_word_embeddings"):
+        raw = dict(cfg.__dict__)
+        del raw[drop]
+        (tmp_path / "config.json").write_text(json.dumps(raw))
+        with pytest.raises(ValueError, match=drop):
+            model.BitNet.load(tmp_path, ctx=object())
