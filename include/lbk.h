@@ -93,6 +93,9 @@ size_t lbk_weight_rows(const lbk_weight *w);
 size_t lbk_weight_cols(const lbk_weight *w);
 float lbk_weight_scale(const lbk_weight *w);
 const void *lbk_weight_data(const lbk_weight *w); /* device pointer */
+/* Copies the packed rows back to host memory (len must be rows * lbk_row_bytes(cols)): the bytes a
+ * PackedTernary holds in `data` (pack.rs:60-65). Synchronous. */
+int lbk_weight_download(const lbk_weight *w, uint8_t *packed_out, size_t len);
 
 /* ---- host-pointer entry points: one per public function of lb-ternary -------------------
  * All buffers are HOST memory; the call copies in, runs the CUDA kernels, copies out and
@@ -349,6 +352,41 @@ typedef struct lbk_model_config {
     int bos_token_id;
 } lbk_model_config;
 int lbk_model_load(lbk_ctx *ctx, const char *directory, lbk_model **out);
+/* The same loader for one rank of a tensor-parallel group (the reference has one process and no
+ * sharding; its loader is model.rs:149-232). q/k/v/gate/up keep rows [rank*rows/world, ...) of the
+ * packed matrix, a contiguous range of the file; o/down keep columns [rank*cols/world, ...), a whole
+ * number of 128-column blocks, cut out of every packed row while loading. Norm gains, the embedding /
+ * head table and the RoPE tables are whole on every rank. The parts are read with the accessors
+ * below (lbk_model_new_cache refuses a sharded model: its step needs the other ranks).
+ * Loading never holds more host memory than two pinned staging buffers (lbk_load_stats.staging_bytes):
+ * file -> pinned buffer -> device, one buffer being refilled while the other one's copy is in flight;
+ * all packed matrices of the rank live in one device allocation. */
+int lbk_model_load_shard(lbk_ctx *ctx, const char *directory, int rank, int world, lbk_model **out);
+typedef struct lbk_load_stats {
+    double seconds;          /* wall clock of the load, device copies finished */
+    size_t bytes_read;       /* from the file */
+    size_t bytes_to_device;  /* copied host -> device (less than bytes_read for column shards) */
+    size_t staging_bytes;    /* pinned host memory the loader held */
+} lbk_load_stats;
+int lbk_model_load_stats(const lbk_model *model, lbk_load_stats *out);
+/* Parts of a loaded model (owned by it; device pointers). */
+#define LBK_LIN_Q 0
+#define LBK_LIN_K 1
+#define LBK_LIN_V 2
+#define LBK_LIN_O 3
+#define LBK_LIN_GATE 4
+#define LBK_LIN_UP 5
+#define LBK_LIN_DOWN 6
+#define LBK_NORM_INPUT 0
+#define LBK_NORM_POST_ATTN 1
+#define LBK_NORM_ATTN_SUB 2
+#define LBK_NORM_FFN_SUB 3
+#define LBK_NORM_FINAL 4
+const lbk_weight *lbk_model_linear(const lbk_model *model, size_t layer, int which);
+const float *lbk_model_norm(const lbk_model *model, size_t layer, int which); /* `layer` is ignored for LBK_NORM_FINAL */
+const uint16_t *lbk_model_embedding(const lbk_model *model);
+const float *lbk_model_rope_cos(const lbk_model *model);
+const float *lbk_model_rope_sin(const lbk_model *model);
 int lbk_model_get_config(const lbk_model *model, lbk_model_config *out);
 int lbk_model_free(lbk_model *model);
 int lbk_model_new_cache(lbk_model *model, size_t batch, size_t capacity, lbk_kv_cache **out);

@@ -35,6 +35,7 @@ SYMBOLS = [
     ("lbk_weight_cols", _sz, [_vp]),
     ("lbk_weight_scale", _f, [_vp]),
     ("lbk_weight_data", _vp, [_vp]),
+    ("lbk_weight_download", _i, [_vp, _vp, _sz]),
     ("lbk_quantize_acts", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp]),
     ("lbk_ternary_gemm_i32", _i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     ("lbk_ternary_gemm_multi", _i, [_vp, _pp, _sz, _vp, _vp, _vp, _sz, _pp]),
@@ -78,6 +79,13 @@ SYMBOLS = [
     ("lbk_tp_quantize", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     ("lbk_tp_reduce_scale", _i, [_vp, _vp, _f, _sz, _sz, _vp, _vp, _vp]),
     ("lbk_model_load", _i, [_vp, C.c_char_p, _pp]),
+    ("lbk_model_load_shard", _i, [_vp, C.c_char_p, _i, _i, _pp]),
+    ("lbk_model_load_stats", _i, [_vp, _vp]),
+    ("lbk_model_linear", _vp, [_vp, _sz, _i]),
+    ("lbk_model_norm", _vp, [_vp, _sz, _i]),
+    ("lbk_model_embedding", _vp, [_vp]),
+    ("lbk_model_rope_cos", _vp, [_vp]),
+    ("lbk_model_rope_sin", _vp, [_vp]),
     ("lbk_model_get_config", _i, [_vp, _vp]),
     ("lbk_model_free", _i, [_vp]),
     ("lbk_model_new_cache", _i, [_vp, _sz, _sz, _pp]),

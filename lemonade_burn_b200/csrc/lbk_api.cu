@@ -333,6 +333,16 @@ int lbk_weight_free(lbk_weight *w_) {
     return LBK_OK;
 }
 
+int lbk_weight_download(const lbk_weight *w_, uint8_t *packed_out, size_t len) {
+    if (!w_ || (len && !packed_out)) return fail(LBK_ERR_INVALID, "lbk_weight_download: null argument");
+    const Weight *w = W_(w_);
+    if (len != w->rows * w->rb) return fail(LBK_ERR_SHAPE, "packed data length mismatch: got %zu bytes, %zu x %zu needs %zu", len, w->rows, w->cols, w->rows * w->rb);
+    if (len == 0) return LBK_OK;
+    LBK_CUDA(cudaSetDevice(w->ctx->device));
+    LBK_CUDA(cudaMemcpy(packed_out, w->data, len, cudaMemcpyDeviceToHost));
+    return LBK_OK;
+}
+
 size_t lbk_weight_rows(const lbk_weight *w) { return w ? W_(w)->rows : 0; }
 size_t lbk_weight_cols(const lbk_weight *w) { return w ? W_(w)->cols : 0; }
 float lbk_weight_scale(const lbk_weight *w) { return w ? W_(w)->scale : 0.0f; }

@@ -14,6 +14,11 @@
 // above 16 rows) with causal attention over the cache, as the reference's forward does with
 // m > 1. One decode step is recorded into a CUDA graph the first time a cache is used and
 // replayed afterwards (the position lives in device memory).
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <time.h>
+#include <unistd.h>
+
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -210,6 +215,8 @@ struct Model {
     float *cos = nullptr, *sin = nullptr;
     std::vector<void *> device_allocs;
     std::vector<lbk_weight *> weights;
+    int rank = 0, world = 1;  // tensor-parallel shard this model holds (lbk_model_load_shard)
+    lbk_load_stats stats{};
 };
 
 struct Cache {
@@ -583,9 +590,118 @@ int lbk_model_free(lbk_model *mp) {
     return LBK_OK;
 }
 
-int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
+// ---- loader ------------------------------------------------------------------------------------
+// The reference maps the file and copies every tensor into a framework tensor, which doubles its
+// resident memory while loading (crates/lb-model/src/model.rs:172-183, docs/BENCHMARKS.md:57-59).
+// Here tensor bytes go file -> one of two pinned staging buffers (pread) -> device (one
+// cudaMemcpyAsync / cudaMemcpy2DAsync per piece on the context's stream); a buffer is refilled while
+// the other one's copy is in flight. The host never holds more than the two buffers, whatever the
+// model's size. All packed weights live in ONE device arena (256-byte aligned slices, wrapped as
+// weights without a copy).
+//
+// Tensor parallel (rank, world): q/k/v/gate/up keep their row range [rank*rows/world, ...), which is a
+// contiguous byte range of the file (rows are contiguous in the lb-ternary layout, pack.rs:46-49);
+// o/down keep a column range that is a multiple of 128 columns, i.e. bytes [rank*rb/world, ...) of
+// every packed row, cut out by a strided copy from the staging buffer. Norm gains, the embedding
+// (also the head; a rank uses vocabulary rows [rank*V/world, ...) of it) and the RoPE tables are
+// whole on every rank.
+namespace {
+
+constexpr size_t kStageBytes = 32u << 20;
+
+struct Stager {
+    int fd = -1;
+    size_t file_size = 0, data0 = 0;
+    cudaStream_t st = nullptr;
+    unsigned char *buf[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    bool busy[2] = {false, false};
+    int next = 0;
+    size_t bytes_read = 0, bytes_to_device = 0;
+    ~Stager() {
+        for (int i = 0; i < 2; ++i) {
+            if (busy[i]) cudaEventSynchronize(done[i]);
+            if (done[i]) cudaEventDestroy(done[i]);
+            if (buf[i]) cudaFreeHost(buf[i]);
+        }
+        if (fd >= 0) close(fd);
+    }
+    int init(cudaStream_t stream) {
+        st = stream;
+        for (int i = 0; i < 2; ++i) {
+            cudaError_t e = cudaMallocHost(reinterpret_cast<void **>(&buf[i]), kStageBytes);
+            if (e != cudaSuccess) return fail(LBK_ERR_NOMEM, "pinned staging buffer: %s", cudaGetErrorString(e));
+            LBK_CUDA(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+        }
+        return LBK_OK;
+    }
+    int acquire(int *slot) {
+        const int s = next;
+        next ^= 1;
+        if (busy[s]) {
+            LBK_CUDA(cudaEventSynchronize(done[s]));
+            busy[s] = false;
+        }
+        *slot = s;
+        return LBK_OK;
+    }
+    int fill(int s, size_t file_off, size_t n, const char *what) {
+        if (file_off + n > file_size) return fail(LBK_ERR_INVALID, "the file is truncated: %s needs bytes up to %zu, the file has %zu", what, file_off + n, file_size);
+        size_t got = 0;
+        while (got < n) {
+            const ssize_t r = pread(fd, buf[s] + got, n - got, static_cast<off_t>(file_off + got));
+            if (r <= 0) return fail(LBK_ERR_INVALID, "cannot read %s (%zu of %zu bytes)", what, got, n);
+            got += static_cast<size_t>(r);
+        }
+        bytes_read += n;
+        return LBK_OK;
+    }
+    int release(int s) {
+        LBK_CUDA(cudaEventRecord(done[s], st));
+        busy[s] = true;
+        return LBK_OK;
+    }
+    // `n` contiguous bytes at data offset `off` -> dst
+    int copy_linear(size_t off, size_t n, void *dst, const char *what) {
+        for (size_t o = 0; o < n; o += kStageBytes) {
+            const size_t len = n - o < kStageBytes ? n - o : kStageBytes;
+            int s;
+            LBK_TRY(acquire(&s));
+            LBK_TRY(fill(s, data0 + off + o, len, what));
+            LBK_CUDA(cudaMemcpyAsync(static_cast<char *>(dst) + o, buf[s], len, cudaMemcpyHostToDevice, st));
+            bytes_to_device += len;
+            LBK_TRY(release(s));
+        }
+        return LBK_OK;
+    }
+    // bytes [c0, c0 + width) of each of `rows` rows of pitch `pitch` starting at data offset `off` -> dst (pitch = width)
+    int copy_columns(size_t off, size_t rows, size_t pitch, size_t c0, size_t width, void *dst, const char *what) {
+        const size_t rows_per = kStageBytes / pitch;
+        if (rows_per == 0) return fail(LBK_ERR_UNSUPPORTED, "%s: a row of %zu bytes does not fit the staging buffer", what, pitch);
+        for (size_t r = 0; r < rows; r += rows_per) {
+            const size_t nr = rows - r < rows_per ? rows - r : rows_per;
+            int s;
+            LBK_TRY(acquire(&s));
+            LBK_TRY(fill(s, data0 + off + r * pitch, nr * pitch, what));
+            LBK_CUDA(cudaMemcpy2DAsync(static_cast<char *>(dst) + r * width, width, buf[s] + c0, pitch, width, nr, cudaMemcpyHostToDevice, st));
+            bytes_to_device += nr * width;
+            LBK_TRY(release(s));
+        }
+        return LBK_OK;
+    }
+};
+
+double now_seconds() {
+    timespec ts;
+    clock_gettime(CLOCK_MONOTONIC, &ts);
+    return static_cast<double>(ts.tv_sec) + 1e-9 * static_cast<double>(ts.tv_nsec);
+}
+
+int load_impl(lbk_ctx *c, const char *directory, int rank, int world, lbk_model **out) {
     if (!c || !directory || !out) return fail(LBK_ERR_INVALID, "lbk_model_load: null argument");
     *out = nullptr;
+    if (world < 1 || rank < 0 || rank >= world) return fail(LBK_ERR_INVALID, "rank %d of %d", rank, world);
+    const double t0 = now_seconds();
     Ctx *ctx = reinterpret_cast<Ctx *>(c);
     LBK_CUDA(cudaSetDevice(ctx->device));
     const std::string dir(directory);
@@ -596,6 +712,8 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
     std::unique_ptr<Model, int (*)(Model *)> model(new Model(), [](Model *m) { return lbk_model_free(reinterpret_cast<lbk_model *>(m)); });
     Model *m = model.get();
     m->ctx = ctx;
+    m->rank = rank;
+    m->world = world;
     m->prefill_rows = kPrefillChunk;
     bool ok = true;
     lbk_model_config &cfg = m->cfg;
@@ -624,19 +742,27 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
         return fail(LBK_ERR_INVALID, "config.json: inconsistent head counts or sizes");
     m->head_dim = cfg.hidden_size / cfg.num_attention_heads;
     if (m->head_dim != 128) return fail(LBK_ERR_UNSUPPORTED, "the attention kernels are built for head_dim 128, this model has %zu", m->head_dim);
+    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, hd = m->head_dim, W = static_cast<size_t>(world);
+    if (world > 1 && (cfg.num_key_value_heads % W || I % (128 * W) || (cfg.num_attention_heads * hd) % (128 * W) || cfg.vocab_size % W))
+        return fail(LBK_ERR_UNSUPPORTED, "%d ranks do not divide this model: KV heads %zu, intermediate %zu and attention width %zu (in blocks of 128 columns), vocabulary %zu",
+                    world, cfg.num_key_value_heads, I, cfg.num_attention_heads * hd, cfg.vocab_size);
 
     // ---- model.lbt.safetensors: u64 header length, JSON header, data -------------------------
     const std::string path = dir + "/model.lbt.safetensors";
-    FILE *f = fopen(path.c_str(), "rb");
-    if (!f) return fail(LBK_ERR_INVALID, "cannot open %s", path.c_str());
-    std::unique_ptr<FILE, int (*)(FILE *)> closer(f, fclose);
+    Stager sg;
+    sg.fd = open(path.c_str(), O_RDONLY);
+    if (sg.fd < 0) return fail(LBK_ERR_INVALID, "cannot open %s", path.c_str());
+    struct stat sb;
+    if (fstat(sg.fd, &sb) != 0) return fail(LBK_ERR_INVALID, "cannot stat %s", path.c_str());
+    sg.file_size = static_cast<size_t>(sb.st_size);
     unsigned char lenb[8];
-    if (fread(lenb, 1, 8, f) != 8) return fail(LBK_ERR_INVALID, "%s: truncated", path.c_str());
+    if (sg.file_size < 8 || pread(sg.fd, lenb, 8, 0) != 8) return fail(LBK_ERR_INVALID, "%s: truncated", path.c_str());
     uint64_t hlen = 0;
     for (int i = 7; i >= 0; --i) hlen = (hlen << 8) | lenb[i];
     if (hlen == 0 || hlen > (100u << 20)) return fail(LBK_ERR_INVALID, "%s: implausible header length %llu", path.c_str(), static_cast<unsigned long long>(hlen));
+    if (8 + hlen > sg.file_size) return fail(LBK_ERR_INVALID, "%s: truncated header", path.c_str());
     std::string header(hlen, '\0');
-    if (fread(&header[0], 1, hlen, f) != hlen) return fail(LBK_ERR_INVALID, "%s: truncated header", path.c_str());
+    if (pread(sg.fd, &header[0], hlen, 8) != static_cast<ssize_t>(hlen)) return fail(LBK_ERR_INVALID, "%s: truncated header", path.c_str());
     Json hj;
     if (!parse_json(header, hj) || hj.kind != Json::Obj) return fail(LBK_ERR_INVALID, "%s: header is not a JSON object", path.c_str());
     const Json *meta = hj.get("__metadata__");
@@ -658,9 +784,9 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
         if (e.end < e.begin) return fail(LBK_ERR_INVALID, "%s: malformed offsets of %s", path.c_str(), kv.first.c_str());
         entries[kv.first] = e;
     }
-    const long data0 = static_cast<long>(8 + hlen);
-    std::vector<unsigned char> staging;
-    auto read_tensor = [&](const std::string &name, const char *dtype, size_t elems, size_t elem_bytes) -> int {
+    sg.data0 = static_cast<size_t>(8 + hlen);
+    LBK_TRY(sg.init(ctx->own_stream));
+    auto find_tensor = [&](const std::string &name, const char *dtype, size_t elems, size_t elem_bytes, const TensorEntry **e_out) -> int {
         auto it = entries.find(name);
         if (it == entries.end()) return fail(LBK_ERR_INVALID, "%s: tensor %s is missing", path.c_str(), name.c_str());
         const TensorEntry &e = it->second;
@@ -668,56 +794,138 @@ int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) {
         for (size_t d : e.shape) n *= d;
         if (e.dtype != dtype || n != elems || e.end - e.begin != elems * elem_bytes)
             return fail(LBK_ERR_SHAPE, "%s: %s has dtype %s and %zu elements, expected %s and %zu", path.c_str(), name.c_str(), e.dtype.c_str(), n, dtype, elems);
-        staging.resize(elems * elem_bytes);
-        if (fseek(f, data0 + static_cast<long>(e.begin), SEEK_SET) != 0 || fread(staging.data(), 1, staging.size(), f) != staging.size())
-            return fail(LBK_ERR_INVALID, "%s: cannot read %s", path.c_str(), name.c_str());
+        if (sg.data0 + e.end > sg.file_size)
+            return fail(LBK_ERR_INVALID, "%s is truncated: %s ends at byte %zu, the file has %zu", path.c_str(), name.c_str(), sg.data0 + e.end, sg.file_size);
+        *e_out = &e;
         return LBK_OK;
     };
-    auto load_vec = [&](const std::string &name, size_t elems, float **dst) -> int {  // model.rs:165: norm gains are F32
-        LBK_TRY(read_tensor(name, "F32", elems, 4));
-        LBK_TRY(dev_alloc(m->device_allocs, elems * 4, reinterpret_cast<void **>(dst)));
-        LBK_CUDA(cudaMemcpy(*dst, staging.data(), elems * 4, cudaMemcpyHostToDevice));
-        return LBK_OK;
+    // norm gains (model.rs:165: F32) share one small arena
+    const size_t L = cfg.num_hidden_layers;
+    float *norms = nullptr;
+    LBK_TRY(dev_alloc(m->device_allocs, (L * (3 * H + I) + H) * 4, reinterpret_cast<void **>(&norms)));
+    size_t norm_off = 0;
+    auto load_vec = [&](const std::string &name, size_t elems, float **dst) -> int {
+        const TensorEntry *e;
+        LBK_TRY(find_tensor(name, "F32", elems, 4, &e));
+        *dst = norms + norm_off;
+        norm_off += elems;
+        return sg.copy_linear(e->begin, elems * 4, *dst, name.c_str());
     };
-    auto load_linear = [&](const std::string &name, size_t rows, size_t cols, lbk_weight **dst) -> int {
-        LBK_TRY(read_tensor(name + ".wscale", "F32", 1, 4));
-        float scale;
-        memcpy(&scale, staging.data(), 4);
-        LBK_TRY(read_tensor(name + ".qweight", "U8", rows * lbk_row_bytes(cols), 1));
-        LBK_TRY(lbk_weight_upload(c, rows, cols, staging.data(), staging.size(), scale, dst));
-        m->weights.push_back(*dst);
-        return LBK_OK;
-    };
-    const size_t H = cfg.hidden_size, I = cfg.intermediate_size, hd = m->head_dim;
-    m->layers.resize(cfg.num_hidden_layers);
-    for (size_t i = 0; i < cfg.num_hidden_layers; ++i) {
+    // one arena for every packed matrix of this rank
+    struct Lin { const char *name; size_t rows, cols; bool split_cols; };
+    const Lin lins[7] = {{".self_attn.q_proj", cfg.num_attention_heads * hd, H, false}, {".self_attn.k_proj", cfg.num_key_value_heads * hd, H, false},
+                         {".self_attn.v_proj", cfg.num_key_value_heads * hd, H, false}, {".self_attn.o_proj", H, cfg.num_attention_heads * hd, true},
+                         {".mlp.gate_proj", I, H, false}, {".mlp.up_proj", I, H, false}, {".mlp.down_proj", H, I, true}};
+    size_t arena_bytes = 0;
+    for (const Lin &ln : lins) {
+        const size_t rows = ln.split_cols ? ln.rows : ln.rows / W, cols = ln.split_cols ? ln.cols / W : ln.cols;
+        arena_bytes += (rows * lbk_row_bytes(cols) + 255) / 256 * 256;
+    }
+    arena_bytes *= L;
+    unsigned char *arena = nullptr;
+    LBK_TRY(dev_alloc(m->device_allocs, arena_bytes, reinterpret_cast<void **>(&arena)));
+    size_t arena_off = 0;
+    m->layers.resize(L);
+    for (size_t i = 0; i < L; ++i) {
         const std::string p = "model.layers." + std::to_string(i);
         Model::Layer &l = m->layers[i];
         LBK_TRY(load_vec(p + ".input_layernorm.weight", H, &l.input_norm));
         LBK_TRY(load_vec(p + ".post_attention_layernorm.weight", H, &l.post_attn_norm));
         LBK_TRY(load_vec(p + ".self_attn.attn_sub_norm.weight", H, &l.attn_sub_norm));
         LBK_TRY(load_vec(p + ".mlp.ffn_sub_norm.weight", I, &l.ffn_sub_norm));
-        LBK_TRY(load_linear(p + ".self_attn.q_proj", cfg.num_attention_heads * hd, H, &l.q));
-        LBK_TRY(load_linear(p + ".self_attn.k_proj", cfg.num_key_value_heads * hd, H, &l.k));
-        LBK_TRY(load_linear(p + ".self_attn.v_proj", cfg.num_key_value_heads * hd, H, &l.v));
-        LBK_TRY(load_linear(p + ".self_attn.o_proj", H, cfg.num_attention_heads * hd, &l.o));
-        LBK_TRY(load_linear(p + ".mlp.gate_proj", I, H, &l.gate));
-        LBK_TRY(load_linear(p + ".mlp.up_proj", I, H, &l.up));
-        LBK_TRY(load_linear(p + ".mlp.down_proj", H, I, &l.down));
+        lbk_weight **dst[7] = {&l.q, &l.k, &l.v, &l.o, &l.gate, &l.up, &l.down};
+        for (int k = 0; k < 7; ++k) {
+            const Lin &ln = lins[k];
+            const std::string name = p + ln.name;
+            const TensorEntry *es, *ew;
+            LBK_TRY(find_tensor(name + ".wscale", "F32", 1, 4, &es));
+            float scale = 0.0f;
+            if (pread(sg.fd, &scale, 4, static_cast<off_t>(sg.data0 + es->begin)) != 4) return fail(LBK_ERR_INVALID, "cannot read %s.wscale", name.c_str());
+            const size_t rb = lbk_row_bytes(ln.cols);
+            LBK_TRY(find_tensor(name + ".qweight", "U8", ln.rows * rb, 1, &ew));
+            unsigned char *dev = arena + arena_off;
+            size_t rows = ln.rows, cols = ln.cols;
+            if (!ln.split_cols) {
+                rows = ln.rows / W;
+                LBK_TRY(sg.copy_linear(ew->begin + static_cast<size_t>(rank) * rows * rb, rows * rb, dev, name.c_str()));
+            } else if (world == 1) {
+                LBK_TRY(sg.copy_linear(ew->begin, rows * rb, dev, name.c_str()));
+            } else {
+                cols = ln.cols / W;
+                const size_t width = rb / W;
+                LBK_TRY(sg.copy_columns(ew->begin, rows, rb, static_cast<size_t>(rank) * width, width, dev, name.c_str()));
+            }
+            arena_off += (rows * lbk_row_bytes(cols) + 255) / 256 * 256;
+            LBK_TRY(lbk_weight_wrap(c, rows, cols, dev, scale, dst[k]));
+            m->weights.push_back(*dst[k]);
+        }
     }
     LBK_TRY(load_vec("model.norm.weight", H, &m->final_norm));
-    LBK_TRY(read_tensor("model.embed_tokens.weight", "BF16", cfg.vocab_size * H, 2));  // model.rs:204
-    LBK_TRY(dev_alloc(m->device_allocs, staging.size(), reinterpret_cast<void **>(&m->embed)));
-    LBK_CUDA(cudaMemcpy(m->embed, staging.data(), staging.size(), cudaMemcpyHostToDevice));
+    const TensorEntry *ee;
+    LBK_TRY(find_tensor("model.embed_tokens.weight", "BF16", cfg.vocab_size * H, 2, &ee));  // model.rs:204
+    LBK_TRY(dev_alloc(m->device_allocs, cfg.vocab_size * H * 2, reinterpret_cast<void **>(&m->embed)));
+    LBK_TRY(sg.copy_linear(ee->begin, cfg.vocab_size * H * 2, m->embed, "model.embed_tokens.weight"));
     std::vector<float> cs, sn;
     rope_tables(cfg, hd, cs, sn);
     LBK_TRY(dev_alloc(m->device_allocs, cs.size() * 4, reinterpret_cast<void **>(&m->cos)));
     LBK_TRY(dev_alloc(m->device_allocs, sn.size() * 4, reinterpret_cast<void **>(&m->sin)));
-    LBK_CUDA(cudaMemcpy(m->cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
-    LBK_CUDA(cudaMemcpy(m->sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpyAsync(m->cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice, ctx->own_stream));
+    LBK_CUDA(cudaMemcpyAsync(m->sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice, ctx->own_stream));
+    LBK_CUDA(cudaStreamSynchronize(ctx->own_stream));  // also: `cs`, `sn` and the staging buffers go away now
+    m->stats.seconds = now_seconds() - t0;
+    m->stats.bytes_read = sg.bytes_read;
+    m->stats.bytes_to_device = sg.bytes_to_device;
+    m->stats.staging_bytes = 2 * kStageBytes;
     *out = reinterpret_cast<lbk_model *>(model.release());
     return LBK_OK;
 }
+
+}  // namespace
+
+int lbk_model_load(lbk_ctx *c, const char *directory, lbk_model **out) { return load_impl(c, directory, 0, 1, out); }
+
+int lbk_model_load_shard(lbk_ctx *c, const char *directory, int rank, int world, lbk_model **out) { return load_impl(c, directory, rank, world, out); }
+
+int lbk_model_load_stats(const lbk_model *mp, lbk_load_stats *out) {
+    if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_model_load_stats: null argument");
+    *out = reinterpret_cast<const Model *>(mp)->stats;
+    return LBK_OK;
+}
+
+const lbk_weight *lbk_model_linear(const lbk_model *mp, size_t layer, int which) {
+    const Model *m = reinterpret_cast<const Model *>(mp);
+    if (!m || layer >= m->layers.size()) return nullptr;
+    const Model::Layer &l = m->layers[layer];
+    switch (which) {
+        case LBK_LIN_Q: return l.q;
+        case LBK_LIN_K: return l.k;
+        case LBK_LIN_V: return l.v;
+        case LBK_LIN_O: return l.o;
+        case LBK_LIN_GATE: return l.gate;
+        case LBK_LIN_UP: return l.up;
+        case LBK_LIN_DOWN: return l.down;
+        default: return nullptr;
+    }
+}
+
+const float *lbk_model_norm(const lbk_model *mp, size_t layer, int which) {
+    const Model *m = reinterpret_cast<const Model *>(mp);
+    if (!m) return nullptr;
+    if (which == LBK_NORM_FINAL) return m->final_norm;
+    if (layer >= m->layers.size()) return nullptr;
+    const Model::Layer &l = m->layers[layer];
+    switch (which) {
+        case LBK_NORM_INPUT: return l.input_norm;
+        case LBK_NORM_POST_ATTN: return l.post_attn_norm;
+        case LBK_NORM_ATTN_SUB: return l.attn_sub_norm;
+        case LBK_NORM_FFN_SUB: return l.ffn_sub_norm;
+        default: return nullptr;
+    }
+}
+
+const uint16_t *lbk_model_embedding(const lbk_model *mp) { return mp ? reinterpret_cast<const Model *>(mp)->embed : nullptr; }
+const float *lbk_model_rope_cos(const lbk_model *mp) { return mp ? reinterpret_cast<const Model *>(mp)->cos : nullptr; }
+const float *lbk_model_rope_sin(const lbk_model *mp) { return mp ? reinterpret_cast<const Model *>(mp)->sin : nullptr; }
 
 int lbk_model_get_config(const lbk_model *mp, lbk_model_config *out) {
     if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_model_get_config: null argument");
@@ -741,6 +949,8 @@ int lbk_model_new_cache(lbk_model *mp, size_t batch, size_t capacity, lbk_kv_cac
     if (!mp || !out) return fail(LBK_ERR_INVALID, "lbk_model_new_cache: null argument");
     *out = nullptr;
     Model *m = reinterpret_cast<Model *>(mp);
+    if (m->world > 1)
+        return fail(LBK_ERR_UNSUPPORTED, "this model holds shard %d of %d: its step needs the other ranks (drive it through the tensor-parallel layer calls)", m->rank, m->world);
     if (batch == 0 || batch > LBK_GEMV_MAX_M) return fail(LBK_ERR_UNSUPPORTED, "a cache serves 1..%d sequences (got %zu)", LBK_GEMV_MAX_M, batch);
     if (capacity == 0) capacity = m->cfg.max_position_embeddings;
     if (capacity > m->cfg.max_position_embeddings) return fail(LBK_ERR_INVALID, "capacity %zu exceeds max_position_embeddings %zu", capacity, m->cfg.max_position_embeddings);

@@ -337,16 +337,26 @@ class _ModelConfig(C.Structure):
                [("rms_norm_eps", C.c_float), ("rope_theta", C.c_float), ("bos_token_id", C.c_int)]
 
 
+class _LoadStats(C.Structure):
+    _fields_ = [("seconds", C.c_double), ("bytes_read", C.c_size_t), ("bytes_to_device", C.c_size_t), ("staging_bytes", C.c_size_t)]
+
+
 class NativeBitNet:
     """The same decoder driven entirely by liblbk.so (lbk_model_load / new_cache / forward / decode):
     what a host without a tensor framework binds. Same checkpoint, same kernels, same results as
     `BitNet`; this class only marshals pointers."""
 
-    def __init__(self, directory, ctx: Optional[Context] = None):
+    def __init__(self, directory, ctx: Optional[Context] = None, rank: int = 0, world: int = 1):
+        """world > 1: this rank's shard only (rows of q/k/v/gate/up, 128-aligned column ranges of
+        o/down); such a model serves the tensor-parallel step, not `new_cache` / `forward`."""
         self.ctx = ctx or default_context()
         self._lib = self.ctx._lib
+        self.rank, self.world = rank, world
         h = C.c_void_p()
-        _lib.check(self._lib.lbk_model_load(self.ctx.handle, str(directory).encode(), C.byref(h)))
+        if world == 1:
+            _lib.check(self._lib.lbk_model_load(self.ctx.handle, str(directory).encode(), C.byref(h)))
+        else:
+            _lib.check(self._lib.lbk_model_load_shard(self.ctx.handle, str(directory).encode(), rank, world, C.byref(h)))
         self.handle = h
         raw = _ModelConfig()
         _lib.check(self._lib.lbk_model_get_config(h, C.byref(raw)))
@@ -354,6 +364,32 @@ class NativeBitNet:
                           raw.num_hidden_layers, raw.vocab_size, raw.rms_norm_eps, raw.rope_theta, raw.max_position_embeddings,
                           bos_token_id=raw.bos_token_id)
         self._caches = []
+
+    LINEAR_IDS = {"q": 0, "k": 1, "v": 2, "o": 3, "gate": 4, "up": 5, "down": 6}
+    NORM_IDS = {"input_norm": 0, "post_attn_norm": 1, "attn_sub_norm": 2, "ffn_sub_norm": 3, "final_norm": 4}
+
+    def load_stats(self) -> dict:
+        """Seconds, bytes read, bytes copied to the device and pinned staging bytes of the load."""
+        s = _LoadStats()
+        _lib.check(self._lib.lbk_model_load_stats(self.handle, C.byref(s)))
+        return {"seconds": s.seconds, "bytes_read": s.bytes_read, "bytes_to_device": s.bytes_to_device, "staging_bytes": s.staging_bytes}
+
+    def linear_handle(self, layer: int, name: str) -> int:
+        h = self._lib.lbk_model_linear(self.handle, layer, self.LINEAR_IDS[name])
+        if not h:
+            raise ValueError(f"no linear {name} in layer {layer}")
+        return h
+
+    def linear_bytes(self, layer: int, name: str) -> np.ndarray:
+        """The packed rows this model (or shard) holds for one projection, copied to the host."""
+        h = self.linear_handle(layer, name)
+        rows, cols = self._lib.lbk_weight_rows(h), self._lib.lbk_weight_cols(h)
+        out = np.empty((rows, row_bytes(cols)), dtype=np.uint8)
+        _lib.check(self._lib.lbk_weight_download(h, out.ctypes.data_as(C.c_void_p), out.size))
+        return out
+
+    def norm_ptr(self, layer: int, name: str) -> int:
+        return int(self._lib.lbk_model_norm(self.handle, layer, self.NORM_IDS[name]))
 
     def new_cache(self, b: int = 1, cap: int = 0):
         c = C.c_void_p()

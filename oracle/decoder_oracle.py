@@ -127,3 +127,21 @@ def compare_logits(got, ref, margin=0.5):
     return {"rows": int(ref.shape[0]), "top1_agree": int((top_g == top_r).sum()), "clear_rows": int(clear.sum()),
             "clear_agree": int(((top_g == top_r) & clear).sum()), "max_abs_delta": float(d.max()), "mean_abs_delta": float(d.mean()),
             "max_abs_logit": float(np.abs(ref).max())}
+
+
+def bf16_bits_to_f32(bits: np.ndarray) -> np.ndarray:
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def check_step(cfg, w, tokens, k_bits, v_bits, pos, fast=True):
+    """One decode step for each of b independent sequences that already hold `pos` cached positions
+    (the reference has no batch dimension: b single-token forwards, model.rs:305-374 with m = 1).
+    k_bits / v_bits: uint16 bf16 bits [layers][b][kvh][cap][hd], the device cache as it was BEFORE the
+    step. Returns logits f32 [b, vocab]."""
+    L = cfg["num_hidden_layers"]
+    out = []
+    for bi, tok in enumerate(tokens):
+        kc = [bf16_bits_to_f32(k_bits[li][bi]) for li in range(L)]
+        vc = [bf16_bits_to_f32(v_bits[li][bi]) for li in range(L)]
+        out.append(decode_step(cfg, w, int(tok), kc, vc, pos, kv_bf16=True, fast=fast))
+    return np.stack(out)

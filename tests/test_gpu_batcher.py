@@ -138,3 +138,51 @@ def test_batcher_tokens_do_not_depend_on_company(ctx, tmp_path):
     ctx.check_device_error()
     bt.close()
     nat.close()
+
+
+def test_batcher_tokens_against_the_oracle(ctx, oracle, tmp_path):
+    """Requests served by the batcher against the CPU restatement of the reference's generation loop
+    (crates/lb-server/src/main.rs:102-166 with greedy sampling, sample.rs:17-25; decoder step
+    oracle/decoder_oracle.py). Six slots: batches of 5..8 sequences take the quantise + GEMM route for
+    the long-row projection inside the recorded step, and prompts of mixed lengths (1..40 tokens) run
+    their own prompt passes on the same context in between, so the recorded step's buffers must stay
+    valid while other calls come and go. Teacher-forced check: the oracle is fed the batcher's own
+    tokens; at every step the batcher's token must be the oracle's first maximum, or, where float
+    rounding could decide (the oracle's lead over the batcher's token is below 2e-3 of max |logit|, the
+    decoder tests' bar), at least within that margin."""
+    import torch
+    from lemonade_burn_b200 import model
+    from oracle import decoder_oracle as D
+    cfg = model.Config(512, 768, 4, 1, 2, 1000, 1e-5, 500000.0, 64)
+    tensors = model.random_checkpoint(cfg, 21)
+    model.save_checkpoint(tmp_path, cfg, tensors)
+    nat = model.NativeBitNet(tmp_path, ctx)
+    w = {k: (v.view(torch.int16).numpy().view(np.uint16) if v.dtype == torch.bfloat16 else v.numpy()) for k, v in tensors.items()}
+    w["_cos"], w["_sin"] = D.rope_tables(cfg.head_dim(), cfg.rope_theta, cfg.max_position_embeddings)
+    rng = np.random.default_rng(4)
+    lens, budgets = [1, 9, 40, 3, 17, 2, 25, 6], [5, 7, 4, 8, 6, 9, 3, 5]
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).astype(np.uint32) for n in lens]
+    bt = nat.batcher(6, 64)
+    ids = [bt.submit(p, m) for p, m in zip(prompts, budgets)]
+    bt.run(1000)
+    c = cfg.__dict__
+    kvh, hd = cfg.num_key_value_heads, cfg.head_dim()
+    checked = 0
+    for p, m, rid in zip(prompts, budgets, ids):
+        toks, done = bt.poll(rid)
+        assert done and len(toks) == m
+        kc = [np.zeros((kvh, 64, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+        vc = [np.zeros((kvh, 64, hd), np.float32) for _ in range(cfg.num_hidden_layers)]
+        seq = [int(t) for t in p] + [int(t) for t in toks[:-1]]
+        for pos, tok in enumerate(seq):
+            logits = D.decode_step(c, w, tok, kc, vc, pos)
+            if pos >= len(p) - 1:
+                mine = toks[pos - (len(p) - 1)]
+                best = int(np.argmax(logits))
+                if mine != best:
+                    assert logits[best] - logits[mine] < 2e-3 * np.abs(logits).max(), (rid, pos, mine, best)
+                checked += 1
+    assert checked == sum(budgets)
+    ctx.check_device_error()
+    bt.close()
+    nat.close()

@@ -43,16 +43,37 @@ def _call(ctx, name, x, lins):
     return st, outs, iouts
 
 
+def _call_into(ctx, name, x, lins, outs, iouts):
+    """The same call into buffers that already exist: nothing in the test allocates around it."""
+    import torch
+    from lemonade_burn_b200 import _lib
+    wp, k1 = _lib.ptr_array([l.weight.handle.value for l in lins])
+    op, k2 = _lib.ptr_array([o.data_ptr() for o in outs])
+    ip, k3 = _lib.ptr_array([o.data_ptr() for o in iouts])
+    st = getattr(ctx._lib, name)(ctx.handle, C.c_void_p(x.data_ptr()), x.shape[0], wp, len(lins), op, ip,
+                                 C.c_void_p(torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    return st, outs, iouts
+
+
 def test_static_scratch_matches_regular_entry_twice(oracle, ctx):
     import torch
     cols = 640
     lins = _group(ctx, oracle, cols, [(300, 41.0), (96, 57.5)], 5)
     g = torch.Generator().manual_seed(9)
-    for m in (70, 33):  # second call is smaller: anything left over from the first must not matter
+    # 70 then 33 rows: the second call is smaller, so anything left over from the first must not matter.
+    # 8, 4 and 1 rows: the regular entry point takes its fused few-row kernel there, this one still
+    # quantises and runs the GEMM; the bits must be the same.
+    for m in (70, 33, 8, 4, 1):
         x = torch.randn(m, cols, generator=g).cuda()
         st_a, out_a, iout_a = _call(ctx, "lbk_ternary_linear_n", x, lins)
         st_b, out_b, iout_b = _call(ctx, "lbk_ternary_linear_prefill_static", x, lins)
         assert st_a == 0 and st_b == 0, ctx._lib.lbk_last_error()
+        # the property the entry point exists for: the call takes no device memory (measured after the
+        # outputs are allocated, around the call alone; cudaMemGetInfo would show any cudaMalloc)
+        free_before = torch.cuda.mem_get_info()[0]
+        st_c, out_c, iout_c = _call_into(ctx, "lbk_ternary_linear_prefill_static", x, lins, out_b, iout_b)
+        assert st_c == 0 and torch.cuda.mem_get_info()[0] == free_before
         for a, b in zip(iout_a, iout_b):
             assert torch.equal(a, b)                      # int32 accumulators: bit exact
         for a, b in zip(out_a, out_b):
