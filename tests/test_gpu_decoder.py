@@ -530,14 +530,12 @@ def test_full_size_step_at_4096_positions_against_oracle(ctx, oracle, full_size_
     greedy tokens against the CPU restatement fed the same cache (the reference has no batch
     dimension: 16 single-token forwards there). Bar, in the reference's own metrics
     (crates/lb-model/src/bin/lb-run.rs:223-259): greedy token equal wherever the oracle's margin over
-    the runner-up exceeds twice the logit tolerance, and max |delta logit| below FULL_TOL of
-    max |logit|. FULL_TOL is 1e-2 here, five times the two-layer tests' bar: float summation order
-    differs between the kernels and numpy, a last-bit difference in a normalised activation on a
-    rounding boundary moves one int8 code, and thirty layers of relu^2 and sub-norms carry it to the
-    logits (the pinning test of the restatement measures the same effect against transformers)."""
+    the runner-up exceeds twice the logit tolerance, and max |delta logit| below TOL = 2e-3 of
+    max |logit|, the bar of the two-layer tests (measured on a B200: 1.6e-6 at batch 1, 8.8e-5 at
+    batch 16, every greedy token equal)."""
     import torch
     from oracle import decoder_oracle as D
-    FULL_TOL = 1e-2
+    FULL_TOL = TOL
     cfg, net, w = full_size_net
     context, cap = 4096, 4096 + 64
     cache = net.new_cache(b=b, cap=cap)
