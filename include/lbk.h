@@ -200,6 +200,9 @@ int lbk_scale_epilogue_dev(lbk_ctx *ctx, const int32_t *dots_dev, const float *s
  * Waits on a peer are bounded: a rank that never arrives yields LBK_ERR_TIMEOUT from
  * lbk_check_device_error, not a hang. Results are bit-identical to the unsharded operator. */
 typedef struct lbk_tp_comm lbk_tp_comm;
+#define LBK_PRE_RMS 1            /* input transforms, see lbk_ternary_linear_pre */
+#define LBK_PRE_ADD_RMS 2
+#define LBK_PRE_RELU2_MUL_RMS 3
 size_t lbk_tp_region_bytes(void);
 size_t lbk_tp_max_tokens(void);
 size_t lbk_tp_partial_bytes(void);
@@ -220,6 +223,54 @@ int lbk_tp_quantize(lbk_tp_comm *comm, const float *x_dev, size_t m, size_t k, i
                     int32_t *sum_dev, void *stream);
 int lbk_tp_reduce_scale(lbk_tp_comm *comm, const float *scale_dev, float wscale, size_t m, size_t rows,
                         float *out_dev, int32_t *dots_out_dev, void *stream);
+
+/* The token-sharded form of the same layer, for the decoder step (no reference counterpart; the step
+ * it serves is crates/lb-model/src/model.rs:331-366). Every rank owns ceil(m / world) consecutive
+ * token rows (lbk_tp_token_range) and keeps the residual stream for those tokens only.
+ *   lbk_tp_norm_quant            the sub-norm in front of a row-parallel projection (attn_sub_norm,
+ *                                ffn_sub_norm; pre = LBK_PRE_RMS on x, or LBK_PRE_RELU2_MUL_RMS on
+ *                                relu(x)^2 * y) and the activation quantiser, on this rank's COLUMN
+ *                                slice [m, k_local] of the input, for all m tokens. The mean of squares
+ *                                is over all k_full columns and the quantiser's maximum over the whole
+ *                                row: two 8-byte exchanges per token inside the kernel. w_dev is the
+ *                                slice of the gain. k_local: a multiple of 128, at most 16384.
+ *   (lbk_ternary_gemm_dev writes the slice's int32 dots into lbk_tp_partial_buffer)
+ *   lbk_tp_reduce_norm_gather    for this rank's tokens: sum of all ranks' int32 dots (exact), scale
+ *                                epilogue with ascale_dev[t] * wscale (gemm.rs:141), xres += that row
+ *                                (the residual, [own tokens][hidden]), the next norm with gain w_dev
+ *                                over the full row, the quantiser, and the int8 row + scale + sum
+ *                                stored into every rank's region. When the call returns to the stream
+ *                                all m tokens' rows are in THIS rank's region: lbk_tp_gather_q
+ *                                ([m][hidden] int8), lbk_tp_gather_scale, lbk_tp_gather_sum, ready for
+ *                                lbk_ternary_gemm_dev of the next column-parallel group.
+ *                                flags: LBK_TP_NO_REDUCE (xres already holds the rows: the embedding,
+ *                                before the first layer), LBK_TP_GATHER_F32 (gather the normalised rows
+ *                                as f32, lbk_tp_gather_f32: the head's input; m <= lbk_tp_max_f32_rows).
+ *                                y_out_dev (optional, [own tokens][hidden]) receives the projection's rows.
+ *   lbk_tp_argmax                greedy token over a head whose vocabulary rows are split across ranks:
+ *                                idx_local_dev[t] = lbk_argmax of this rank's logits_local_dev
+ *                                [m][vocab_local]; next_dev[t] = first maximum over all ranks
+ *                                (sample.rs:17-25).
+ * m <= lbk_tp_max_rows(), hidden <= lbk_tp_max_width() and a multiple of 128. All ranks make the same
+ * calls in the same order; waits are bounded as above. Integer sums are exact, so the projection rows
+ * equal the unsharded operator's bits whenever the quantised inputs do; the sub-norm's sum of squares
+ * is added in rank order, which can differ from the single-GPU kernel's order in the last bit. */
+#define LBK_TP_NO_REDUCE 1
+#define LBK_TP_GATHER_F32 2
+size_t lbk_tp_max_rows(void);
+size_t lbk_tp_max_width(void);
+size_t lbk_tp_max_f32_rows(void);
+int lbk_tp_token_range(const lbk_tp_comm *comm, size_t m, size_t *first_out, size_t *count_out);
+int lbk_tp_norm_quant(lbk_tp_comm *comm, int pre, const float *x_dev, const float *y_dev, const float *w_dev, size_t m, size_t k_local,
+                      size_t k_full, float eps, int8_t *q_dev, float *scale_dev, int32_t *sum_dev, void *stream);
+int lbk_tp_reduce_norm_gather(lbk_tp_comm *comm, int flags, const float *ascale_dev, float wscale, float *xres_dev, const float *w_dev,
+                              float eps, size_t m, size_t hidden, float *y_out_dev, void *stream);
+const int8_t *lbk_tp_gather_q(lbk_tp_comm *comm);
+const float *lbk_tp_gather_scale(lbk_tp_comm *comm);
+const int32_t *lbk_tp_gather_sum(lbk_tp_comm *comm);
+const float *lbk_tp_gather_f32(lbk_tp_comm *comm);
+int lbk_tp_argmax(lbk_tp_comm *comm, const float *logits_local_dev, const int32_t *idx_local_dev, size_t m, size_t vocab_local,
+                  int32_t *next_dev, void *stream);
 
 /* ternary_gemm_multi (gemm.rs:128-195) on already quantised device inputs. */
 int lbk_ternary_gemm_dev(lbk_ctx *ctx, const lbk_weight *const *ws, size_t n, const int8_t *q_dev,
@@ -316,9 +367,6 @@ int lbk_relu2_mul_rms_norm(lbk_ctx *ctx, const float *g_dev, const float *u_dev,
  * x, y, w, xout: 16-byte aligned, xout must not alias x or y. LBK_ERR_UNSUPPORTED when
  * lbk_ternary_linear_pre_supported(m, cols) is 0 (rows too long to hold in registers at that m):
  * use the separate kernels above then. */
-#define LBK_PRE_RMS 1
-#define LBK_PRE_ADD_RMS 2
-#define LBK_PRE_RELU2_MUL_RMS 3
 int lbk_ternary_linear_pre_supported(size_t m, size_t cols);
 int lbk_ternary_linear_pre(lbk_ctx *ctx, int pre, const float *x_dev, const float *y_dev, const float *w_dev, float eps,
                            float *xout_dev, size_t m, const lbk_weight *const *ws, size_t n, float *const *outs_dev,

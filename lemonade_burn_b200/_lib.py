@@ -78,6 +78,17 @@ SYMBOLS = [
     ("lbk_tp_partial_buffer", _vp, [_vp]),
     ("lbk_tp_quantize", _i, [_vp, _vp, _sz, _sz, _vp, _vp, _vp, _vp]),
     ("lbk_tp_reduce_scale", _i, [_vp, _vp, _f, _sz, _sz, _vp, _vp, _vp]),
+    ("lbk_tp_max_rows", _sz, []),
+    ("lbk_tp_max_width", _sz, []),
+    ("lbk_tp_max_f32_rows", _sz, []),
+    ("lbk_tp_token_range", _i, [_vp, _sz, _vp, _vp]),
+    ("lbk_tp_norm_quant", _i, [_vp, _i, _vp, _vp, _vp, _sz, _sz, _sz, _f, _vp, _vp, _vp, _vp]),
+    ("lbk_tp_reduce_norm_gather", _i, [_vp, _i, _vp, _f, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
+    ("lbk_tp_gather_q", _vp, [_vp]),
+    ("lbk_tp_gather_scale", _vp, [_vp]),
+    ("lbk_tp_gather_sum", _vp, [_vp]),
+    ("lbk_tp_gather_f32", _vp, [_vp]),
+    ("lbk_tp_argmax", _i, [_vp, _vp, _vp, _sz, _sz, _vp, _vp]),
     ("lbk_model_load", _i, [_vp, C.c_char_p, _pp]),
     ("lbk_model_load_shard", _i, [_vp, C.c_char_p, _i, _i, _pp]),
     ("lbk_model_load_stats", _i, [_vp, _vp]),

@@ -29,7 +29,10 @@ namespace lbk {
 
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpMaxTokens = 256;                   // token rows per call on the fused path
-constexpr size_t kTpPartialBytes = 8u << 20;        // int32 partial dots of one call
+constexpr int kTpMaxRows = 2048;                    // token rows per call on the token-sharded path
+constexpr int kTpMaxWidth = 8192;                   // widest row that is reduced and gathered (the hidden size)
+constexpr int kTpGatherFRows = kTpMaxRows;          // token rows whose normalised f32 rows can be gathered (the head's input)
+constexpr size_t kTpPartialBytes = static_cast<size_t>(kTpMaxRows) * kTpMaxWidth * 4;  // int32 partial dots of one call
 constexpr uint32_t kTpWaitLimit = 1u << 24;         // default: polls of a peer's word before giving up (lbk_tp_comm_set_wait_limit)
 
 // The same layout in every rank's region.
@@ -39,6 +42,17 @@ struct TpRegion {
     unsigned int q_seq, q_done, r_seq, r_done;              // this rank's own counters (never written by peers)
     unsigned int pad_[28];
     int32_t partial[kTpPartialBytes / 4];
+    // ---- token-sharded path: statistics exchange, reduce-scatter flags, gathered rows ----
+    unsigned long long stat[2][2][kTpMaxWorld][kTpMaxRows];  // [parity][round][writer][token]: (sequence << 32) | float bits
+    unsigned long long best[2][kTpMaxWorld][kTpMaxRows];     // [parity][writer][token]: (ordered logit << 32) | ~index
+    unsigned int rs_ready[kTpMaxWorld][32];                  // [r][0]: sequence of rank r's partial dots
+    unsigned int ag_ready[kTpMaxWorld][32];                  // [r][0]: sequence of the rows rank r has written into THIS region
+    unsigned int am_ready[kTpMaxWorld][32];                  // [r][0]: sequence of rank r's entries of `best` in THIS region
+    unsigned int nq_seq, nq_done, rg_seq, rg_done, rg_written, am_seq, pad2_[26];
+    float gather_scale[kTpMaxRows];                          // per-token activation scale of the gathered rows
+    int32_t gather_sum[kTpMaxRows];                          // per-token sum of the gathered int8 codes
+    int8_t gather_q[static_cast<size_t>(kTpMaxRows) * kTpMaxWidth];     // all tokens' quantised rows, written by their owners
+    float gather_f[static_cast<size_t>(kTpGatherFRows) * kTpMaxWidth];  // all tokens' normalised f32 rows (head input)
 };
 
 struct TpComm {
@@ -209,6 +223,386 @@ __global__ void __launch_bounds__(256) tp_reduce_scale_kernel(const TpPtrs peers
     }
 }
 
+
+// =================================================================================================
+// Token-sharded path. A row-parallel layer (o, down) of the decoder step as
+//
+//   tp_norm_quant_kernel       sub-norm + per-token quantisation of this rank's COLUMN slice of the
+//                              layer input, for all tokens: two 8-byte exchanges per token (the
+//                              slice's sum of squares, then its max |normalised value|), so that the
+//                              norm and the scale are those of the whole row (model.rs:358,364;
+//                              quant.rs:100-118)
+//   (GEMM: int32 partial dots of the slice into this rank's region)
+//   tp_reduce_norm_gather_kernel  each rank owns ceil(m/world) TOKENS. For its tokens it adds the
+//                              int32 partial dots of all ranks (reads 1/world of every peer's
+//                              buffer: exact, order-free), applies the scale epilogue (gemm.rs:141),
+//                              adds the residual row it keeps for those tokens, applies the NEXT
+//                              norm (full rows are local now: no exchange), quantises, and stores
+//                              the int8 row with its scale and sum into EVERY rank's region, from
+//                              where the next column-parallel GEMM of every rank reads all tokens.
+//
+// Per layer and rank this moves (world-1)/world * m * hidden * 4 bytes in (reduce-scatter) and
+// (world-1)/world * m * hidden bytes out (all-gather), against world * m * hidden * 4 in for a
+// one-shot all-reduce; the element-wise work is done once per token, not once per rank.
+//
+// Why nothing is overwritten too early. gather_q of call N is written by a rank only after it has
+// seen every rank's rs_ready flag of call N, which a rank raises after its own row-parallel GEMM
+// of call N, i.e. after its earlier GEMM that read gather_q of call N-1 (stream order). A rank's
+// partial dots of call N are read by the peers before they raise ag_ready of call N, and the rank
+// leaves its kernel (and reaches the GEMM that overwrites them) only after it has seen all of those.
+// The statistics slots alternate by the parity of the sequence number; a rank can be at most one
+// call ahead of a peer because every call needs every peer's value of that call.
+
+constexpr int kNqThreads = 512;
+constexpr int kNqCache = 8;  // float4 per thread: column slices of up to 16384 columns
+constexpr int kRgThreads = 1024;
+
+__device__ __forceinline__ float block_sum_f(float v, float *s_red, int nwarps) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < nwarps; ++w) total += s_red[w];  // fixed order
+    return total;
+}
+
+__device__ __forceinline__ float block_max_f(float v, float *s_red, int nwarps) {
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < nwarps; ++w) total = fmaxf(total, s_red[w]);
+    return total;
+}
+
+__device__ __forceinline__ int block_sum_i(int v, int *s_red, int nwarps) {
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    int total = 0;
+    for (int w = 0; w < nwarps; ++w) total += s_red[w];
+    return total;
+}
+
+// Warp 0 of a block: publishes `mine` for (round, row) in every rank's region and collects all
+// ranks' values. Sum: added in rank order, so that every rank derives the same bits. Max: order-free.
+__device__ __forceinline__ float exchange_stat(const TpPtrs &peers, int world, int rank, int par, int round, int row, unsigned int seq,
+                                               float mine, bool is_sum, int *err_word, uint32_t wait_limit) {
+    const int lane = threadIdx.x & 31;
+    float other = 0.0f;
+    bool ok = true;
+    if (lane < world) {
+        const unsigned long long word = (static_cast<unsigned long long>(seq) << 32) | __float_as_uint(mine);
+        *reinterpret_cast<volatile unsigned long long *>(&peers.r[lane]->stat[par][round][rank][row]) = word;
+        volatile unsigned long long *slot = &peers.r[rank]->stat[par][round][lane][row];
+        unsigned long long got = 0;
+        uint32_t polls = 0;
+        while (((got = *slot) >> 32) != seq) {
+            if (++polls > wait_limit) {
+                ok = false;
+                break;
+            }
+        }
+        other = __uint_as_float(static_cast<unsigned int>(got));
+    }
+    if (!ok) atomicExch(err_word, 6);
+    float total = 0.0f;
+    for (int r = 0; r < world; ++r) {
+        const float v = __shfl_sync(0xffffffffu, other, r);
+        total = is_sum ? total + v : fmaxf(total, v);
+    }
+    return total;
+}
+
+// One CTA per token row. PRE = LBK_PRE_RMS: s = x; LBK_PRE_RELU2_MUL_RMS: s = relu(x)^2 * y.
+// Then n_i = (s_i * r) * w_i with r = 1/sqrt(sum over ALL ranks of s^2 / k_full + eps), and the
+// quantiser of quant.rs:100-118 with the maximum over all ranks.
+template <int PRE>
+__global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ x,
+                                                                  const float *__restrict__ y, const float *__restrict__ w, int kl, int k_full,
+                                                                  float eps, int8_t *__restrict__ q, float *__restrict__ scale,
+                                                                  int32_t *__restrict__ sum, int *err_word, uint32_t wait_limit) {
+    __shared__ float s_red[kNqThreads / 32];
+    __shared__ int s_redi[kNqThreads / 32];
+    __shared__ float s_bcast;
+    const int row = blockIdx.x, tid = threadIdx.x;
+    TpRegion *me = peers.r[rank];
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->nq_seq);
+    const int par = seq & 1;
+    const int n4 = kl >> 2;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * kl);
+    const float4 *yr = y ? reinterpret_cast<const float4 *>(y + static_cast<size_t>(row) * kl) : nullptr;
+    float4 v[kNqCache];
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kNqCache; ++j) {
+        const int i = tid + j * kNqThreads;
+        v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i < n4) {
+            const float4 a = xr[i];
+            if (PRE == LBK_PRE_RMS) {
+                v[j] = a;
+            } else {
+                const float4 c = yr[i];
+                const float r0 = fmaxf(a.x, 0.f), r1 = fmaxf(a.y, 0.f), r2 = fmaxf(a.z, 0.f), r3 = fmaxf(a.w, 0.f);
+                v[j] = make_float4(r0 * r0 * c.x, r1 * r1 * c.y, r2 * r2 * c.z, r3 * r3 * c.w);
+            }
+        }
+        ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
+    }
+    ss = block_sum_f(ss, s_red, kNqThreads / 32);
+    if (tid < 32) {
+        const float total = exchange_stat(peers, world, rank, par, 0, row, seq, ss, true, err_word, wait_limit);
+        if (tid == 0) s_bcast = 1.0f / sqrtf(total / static_cast<float>(k_full) + eps);
+    }
+    __syncthreads();
+    const float r = s_bcast;
+    float am = 0.0f;
+#pragma unroll
+    for (int j = 0; j < kNqCache; ++j) {
+        const int i = tid + j * kNqThreads;
+        if (i < n4) {
+            const float4 gw = __ldg(reinterpret_cast<const float4 *>(w) + i);
+            v[j] = make_float4(v[j].x * r * gw.x, v[j].y * r * gw.y, v[j].z * r * gw.z, v[j].w * r * gw.w);
+            am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));  // fmaxf drops a NaN, as f32::max does
+        }
+    }
+    am = block_max_f(am, s_red, kNqThreads / 32);
+    __syncthreads();  // s_bcast has been read by everybody
+    if (tid < 32) {
+        const float total = exchange_stat(peers, world, rank, par, 1, row, seq, am, false, err_word, wait_limit);
+        if (tid == 0) s_bcast = __fdiv_rn(127.0f, fmaxf(total, 1e-5f));
+    }
+    __syncthreads();
+    const float sc = s_bcast;
+    int8_t *qr = q + static_cast<size_t>(row) * kl;  // kl is a whole number of 128-column blocks: no padding
+    int acc = 0;
+#pragma unroll
+    for (int j = 0; j < kNqCache; ++j) {
+        const int i = tid + j * kNqThreads;
+        if (i < n4) {
+            const int q0 = quant_one(v[j].x, sc), q1 = quant_one(v[j].y, sc), q2 = quant_one(v[j].z, sc), q3 = quant_one(v[j].w, sc);
+            acc += q0 + q1 + q2 + q3;
+            reinterpret_cast<uint32_t *>(qr)[i] = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | (static_cast<uint32_t>(q3 & 255) << 24);
+        }
+    }
+    acc = block_sum_i(acc, s_redi, kNqThreads / 32);
+    if (tid == 0) {
+        scale[row] = sc;
+        sum[row] = acc;
+        __threadfence();
+        if (atomicAdd(&me->nq_done, 1u) == gridDim.x - 1) {  // the last CTA moves the sequence on: every CTA has read it
+            me->nq_done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int *>(&me->nq_seq) = seq + 1;
+        }
+    }
+}
+
+struct RgArgs {
+    int world, rank, m, hidden, mt;   // mt = ceil(m / world) tokens per rank
+    int reduce;                       // 1: add all ranks' partial dots, scale, add to the residual; 0: the residual rows are the input
+    int gather_f32;                   // 1: gather the normalised f32 rows (head input) instead of int8 rows
+    const float *ascale;              // [m] activation scales of the row-parallel GEMM's input (reduce = 1)
+    float wscale;
+    float *xres;                      // [mt][hidden] residual rows of this rank's tokens
+    const float *w;                   // [hidden] gain of the norm that follows
+    float eps;
+    float *y_out;                     // optional [mt][hidden]: the projection's scaled output rows
+    int *err_word;
+    uint32_t wait_limit;
+};
+
+// One CTA per token this rank owns (a single CTA if it owns none: it still raises and awaits the flags).
+__global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const TpPtrs peers, const RgArgs a) {
+    __shared__ float s_red[kRgThreads / 32];
+    __shared__ int s_redi[kRgThreads / 32];
+    const int tid = threadIdx.x, world = a.world, rank = a.rank, H = a.hidden;
+    TpRegion *me = peers.r[rank];
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->rg_seq);
+    const int t0 = rank * a.mt;
+    const int own = max(0, min(a.m - t0, a.mt));
+    const int lt = blockIdx.x;  // local token
+    if (a.reduce) {
+        // this rank's partial dots were written by the kernel before this one; the fence orders them,
+        // system wide, before the flag that tells every peer so
+        if (blockIdx.x == 0 && tid < world) {
+            __threadfence_system();
+            *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->rs_ready[rank][0]) = seq;
+        }
+        if (tid < world) {
+            volatile unsigned int *flag = &me->rs_ready[tid][0];
+            uint32_t polls = 0;
+            while (static_cast<int>(*flag - seq) < 0) {
+                if (++polls > a.wait_limit) {
+                    atomicExch(a.err_word, 6);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (lt < own) {
+        const int t = t0 + lt, n4 = H >> 2;
+        float4 v[2];
+        float ss = 0.0f;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int g = tid + it * kRgThreads;
+            v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (g < n4) {
+                float4 x = reinterpret_cast<const float4 *>(a.xres + static_cast<size_t>(lt) * H)[g];
+                if (a.reduce) {
+                    // one 16-byte load per rank, all in flight before the first add; volatile: the same
+                    // addresses hold new numbers every call
+                    int4 d[kTpMaxWorld];
+#pragma unroll
+                    for (int r = 0; r < kTpMaxWorld; ++r) {
+                        d[r] = make_int4(0, 0, 0, 0);
+                        if (r < world) {
+                            const int4 *src = reinterpret_cast<const int4 *>(peers.r[r]->partial + static_cast<size_t>(t) * H) + g;
+                            asm volatile("ld.volatile.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(d[r].x), "=r"(d[r].y), "=r"(d[r].z), "=r"(d[r].w) : "l"(src));
+                        }
+                    }
+                    int4 acc = make_int4(0, 0, 0, 0);
+#pragma unroll
+                    for (int r = 0; r < kTpMaxWorld; ++r) {
+                        acc.x += d[r].x; acc.y += d[r].y; acc.z += d[r].z; acc.w += d[r].w;
+                    }
+                    const float inv = __fdiv_rn(1.0f, __fmul_rn(a.ascale[t], a.wscale));  // gemm.rs:141
+                    const float4 yv = make_float4(__fmul_rn(__int2float_rn(acc.x), inv), __fmul_rn(__int2float_rn(acc.y), inv),
+                                                  __fmul_rn(__int2float_rn(acc.z), inv), __fmul_rn(__int2float_rn(acc.w), inv));
+                    if (a.y_out) reinterpret_cast<float4 *>(a.y_out + static_cast<size_t>(lt) * H)[g] = yv;
+                    x = make_float4(x.x + yv.x, x.y + yv.y, x.z + yv.z, x.w + yv.w);  // the residual add (model.rs:359,365)
+                    reinterpret_cast<float4 *>(a.xres + static_cast<size_t>(lt) * H)[g] = x;
+                }
+                v[it] = x;
+            }
+            ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
+        }
+        const float r = 1.0f / sqrtf(block_sum_f(ss, s_red, kRgThreads / 32) / static_cast<float>(H) + a.eps);
+        float am = 0.0f;
+#pragma unroll
+        for (int it = 0; it < 2; ++it) {
+            const int g = tid + it * kRgThreads;
+            if (g < n4) {
+                const float4 gw = __ldg(reinterpret_cast<const float4 *>(a.w) + g);
+                v[it] = make_float4(v[it].x * r * gw.x, v[it].y * r * gw.y, v[it].z * r * gw.z, v[it].w * r * gw.w);
+                am = fmaxf(am, fmaxf(fmaxf(fabsf(v[it].x), fabsf(v[it].y)), fmaxf(fabsf(v[it].z), fabsf(v[it].w))));
+            }
+        }
+        if (a.gather_f32) {
+#pragma unroll
+            for (int it = 0; it < 2; ++it) {
+                const int g = tid + it * kRgThreads;
+                if (g < n4)
+                    for (int p = 0; p < world; ++p) reinterpret_cast<float4 *>(peers.r[p]->gather_f + static_cast<size_t>(t) * H)[g] = v[it];
+            }
+        } else {
+            const float sc = __fdiv_rn(127.0f, fmaxf(block_max_f(am, s_red, kRgThreads / 32), 1e-5f));
+            int acc = 0;
+#pragma unroll
+            for (int it = 0; it < 2; ++it) {
+                const int g = tid + it * kRgThreads;
+                if (g < n4) {
+                    const int q0 = quant_one(v[it].x, sc), q1 = quant_one(v[it].y, sc), q2 = quant_one(v[it].z, sc), q3 = quant_one(v[it].w, sc);
+                    acc += q0 + q1 + q2 + q3;
+                    const uint32_t word = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | (static_cast<uint32_t>(q3 & 255) << 24);
+                    for (int p = 0; p < world; ++p) reinterpret_cast<uint32_t *>(peers.r[p]->gather_q + static_cast<size_t>(t) * H)[g] = word;
+                }
+            }
+            acc = block_sum_i(acc, s_redi, kRgThreads / 32);
+            if (tid < world) {
+                peers.r[tid]->gather_scale[t] = sc;
+                peers.r[tid]->gather_sum[t] = acc;
+            }
+        }
+    }
+    // Every row this rank owns is in every region once ALL its CTAs are here. The CTA that arrives
+    // last says so to every rank and then waits until every peer has said the same; the others leave
+    // at once. The kernel ends when that CTA ends, so whatever follows in the stream finds all tokens'
+    // rows in this rank's region, and no CTA waits for a peer while CTAs of its own grid still have
+    // to be scheduled.
+    __threadfence_system();
+    __syncthreads();
+    __shared__ int s_last;
+    if (tid == 0) {
+        s_last = atomicAdd(&me->rg_written, 1u) == gridDim.x - 1;
+        if (s_last) me->rg_written = 0;
+    }
+    __syncthreads();
+    if (s_last) {
+        if (tid < world) {
+            __threadfence_system();
+            *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->ag_ready[rank][0]) = seq;
+            volatile unsigned int *flag = &me->ag_ready[tid][0];
+            uint32_t polls = 0;
+            while (static_cast<int>(*flag - seq) < 0) {
+                if (++polls > a.wait_limit) {
+                    atomicExch(a.err_word, 6);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        __threadfence();
+        if (atomicAdd(&me->rg_done, 1u) == gridDim.x - 1) {
+            me->rg_done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int *>(&me->rg_seq) = seq + 1;
+        }
+    }
+}
+
+// Greedy token over a vocabulary split by rows across ranks (sample.rs:17-25: the FIRST maximum).
+// One CTA; thread t owns token t. idx_local[t] is this rank's first maximum of its slice.
+__device__ __forceinline__ unsigned int ordered_bits(float f) {
+    const unsigned int u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ logits, const int32_t *__restrict__ idx_local,
+                                                        int m, int vl, int32_t *__restrict__ next, int *err_word, uint32_t wait_limit) {
+    TpRegion *me = peers.r[rank];
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->am_seq);
+    const int par = seq & 1, tid = threadIdx.x;
+    for (int t = tid; t < m; t += blockDim.x) {
+        const int li = idx_local[t];
+        const unsigned int gi = static_cast<unsigned int>(rank * vl + li);
+        const unsigned long long key = (static_cast<unsigned long long>(ordered_bits(logits[static_cast<size_t>(t) * vl + li])) << 32) | (~gi);
+        for (int p = 0; p < world; ++p) peers.r[p]->best[par][rank][t] = key;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < world) {
+        __threadfence_system();
+        *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->am_ready[rank][0]) = seq;
+        volatile unsigned int *flag = &me->am_ready[tid][0];
+        uint32_t polls = 0;
+        while (static_cast<int>(*flag - seq) < 0) {
+            if (++polls > wait_limit) {
+                atomicExch(err_word, 6);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    for (int t = tid; t < m; t += blockDim.x) {
+        unsigned long long bestk = 0;
+        for (int r = 0; r < world; ++r) {
+            const unsigned long long k = *reinterpret_cast<volatile unsigned long long *>(&me->best[par][r][t]);
+            bestk = k > bestk ? k : bestk;  // larger logit first, then the smaller index (its complement is larger)
+        }
+        next[t] = static_cast<int32_t>(~static_cast<unsigned int>(bestk));
+    }
+    __syncthreads();
+    if (tid == 0) *reinterpret_cast<volatile unsigned int *>(&me->am_seq) = seq + 1;
+}
+
 }  // namespace
 
 }  // namespace lbk
@@ -232,6 +626,9 @@ int lbk_tp_region_alloc(lbk_ctx *c, void **region_out, unsigned char handle_out[
     const unsigned int one = 1;
     LBK_CUDA(cudaMemcpy(&static_cast<TpRegion *>(p)->q_seq, &one, sizeof(one), cudaMemcpyHostToDevice));
     LBK_CUDA(cudaMemcpy(&static_cast<TpRegion *>(p)->r_seq, &one, sizeof(one), cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpy(&static_cast<TpRegion *>(p)->nq_seq, &one, sizeof(one), cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpy(&static_cast<TpRegion *>(p)->rg_seq, &one, sizeof(one), cudaMemcpyHostToDevice));
+    LBK_CUDA(cudaMemcpy(&static_cast<TpRegion *>(p)->am_seq, &one, sizeof(one), cudaMemcpyHostToDevice));
     static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the C ABI passes IPC handles as 64 bytes");
     cudaIpcMemHandle_t h;
     e = cudaIpcGetMemHandle(&h, p);
@@ -344,6 +741,97 @@ int lbk_tp_reduce_scale(lbk_tp_comm *t, const float *scale_dev, float wscale, si
     tp_reduce_scale_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), tc->world, tc->rank, scale_dev, wscale,
                                                                                static_cast<int>(rows), total4, out_dev, dots_out_dev,
                                                                                tc->ctx->err_word, tc->wait_limit);
+    LBK_CUDA(cudaGetLastError());
+    tc->ctx->launches++;
+    return LBK_OK;
+}
+
+size_t lbk_tp_max_rows(void) { return kTpMaxRows; }
+size_t lbk_tp_max_width(void) { return kTpMaxWidth; }
+size_t lbk_tp_max_f32_rows(void) { return kTpGatherFRows; }
+
+int lbk_tp_token_range(const lbk_tp_comm *t, size_t m, size_t *first_out, size_t *count_out) {
+    if (!t || !first_out || !count_out) return fail(LBK_ERR_INVALID, "lbk_tp_token_range: null argument");
+    const TpComm *tc = reinterpret_cast<const TpComm *>(t);
+    const size_t mt = (m + tc->world - 1) / tc->world, t0 = static_cast<size_t>(tc->rank) * mt;
+    *first_out = t0 < m ? t0 : m;
+    *count_out = t0 < m ? (m - t0 < mt ? m - t0 : mt) : 0;
+    return LBK_OK;
+}
+
+int lbk_tp_norm_quant(lbk_tp_comm *t, int pre, const float *x_dev, const float *y_dev, const float *w_dev, size_t m, size_t k_local,
+                      size_t k_full, float eps, int8_t *q_dev, float *scale_dev, int32_t *sum_dev, void *stream) {
+    if (!t) return fail(LBK_ERR_INVALID, "tensor-parallel communicator is null");
+    TpComm *tc = reinterpret_cast<TpComm *>(t);
+    if (pre != LBK_PRE_RMS && pre != LBK_PRE_RELU2_MUL_RMS) return fail(LBK_ERR_INVALID, "lbk_tp_norm_quant: transform %d (LBK_PRE_RMS or LBK_PRE_RELU2_MUL_RMS)", pre);
+    if (m == 0 || m > kTpMaxRows) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_norm_quant takes 1..%d token rows (got %zu); every rank must take part", kTpMaxRows, m);
+    if (!x_dev || !w_dev || !q_dev || !scale_dev || !sum_dev || (pre == LBK_PRE_RELU2_MUL_RMS && !y_dev)) return fail(LBK_ERR_INVALID, "lbk_tp_norm_quant: null buffer");
+    if (k_local == 0 || k_local % 128 || k_local > static_cast<size_t>(kNqCache) * kNqThreads * 4 || k_full < k_local)
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_norm_quant: the column slice must be a multiple of 128 columns, at most %d (got %zu of %zu)", kNqCache * kNqThreads * 4, k_local, k_full);
+    if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(w_dev) | reinterpret_cast<uintptr_t>(q_dev)) & 15)
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_norm_quant needs 16-byte aligned buffers");
+    LBK_CUDA(cudaSetDevice(tc->ctx->device));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const dim3 grid(static_cast<unsigned>(m)), block(kNqThreads);
+    if (pre == LBK_PRE_RMS)
+        tp_norm_quant_kernel<LBK_PRE_RMS><<<grid, block, 0, st>>>(ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), static_cast<int>(k_full), eps,
+                                                                   q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit);
+    else
+        tp_norm_quant_kernel<LBK_PRE_RELU2_MUL_RMS><<<grid, block, 0, st>>>(ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), static_cast<int>(k_full),
+                                                                             eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit);
+    LBK_CUDA(cudaGetLastError());
+    tc->ctx->launches++;
+    return LBK_OK;
+}
+
+int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev, float wscale, float *xres_dev, const float *w_dev, float eps,
+                              size_t m, size_t hidden, float *y_out_dev, void *stream) {
+    if (!t) return fail(LBK_ERR_INVALID, "tensor-parallel communicator is null");
+    TpComm *tc = reinterpret_cast<TpComm *>(t);
+    const bool reduce = !(flags & LBK_TP_NO_REDUCE), f32 = (flags & LBK_TP_GATHER_F32) != 0;
+    if (m == 0 || m > kTpMaxRows || (f32 && m > kTpGatherFRows))
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_reduce_norm_gather takes 1..%d token rows (%d when f32 rows are gathered), got %zu; every rank must take part", kTpMaxRows, kTpGatherFRows, m);
+    if (hidden == 0 || hidden % 128 || hidden > kTpMaxWidth) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_reduce_norm_gather: rows of a multiple of 128 and at most %d columns (got %zu)", kTpMaxWidth, hidden);
+    if (!xres_dev || !w_dev || (reduce && !ascale_dev)) return fail(LBK_ERR_INVALID, "lbk_tp_reduce_norm_gather: null buffer");
+    if ((reinterpret_cast<uintptr_t>(xres_dev) | reinterpret_cast<uintptr_t>(w_dev) | reinterpret_cast<uintptr_t>(y_out_dev)) & 15)
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_reduce_norm_gather needs 16-byte aligned buffers");
+    LBK_CUDA(cudaSetDevice(tc->ctx->device));
+    RgArgs a{};
+    a.world = tc->world;
+    a.rank = tc->rank;
+    a.m = static_cast<int>(m);
+    a.hidden = static_cast<int>(hidden);
+    a.mt = static_cast<int>((m + tc->world - 1) / tc->world);
+    a.reduce = reduce ? 1 : 0;
+    a.gather_f32 = f32 ? 1 : 0;
+    a.ascale = ascale_dev;
+    a.wscale = wscale;
+    a.xres = xres_dev;
+    a.w = w_dev;
+    a.eps = eps;
+    a.y_out = y_out_dev;
+    a.err_word = tc->ctx->err_word;
+    a.wait_limit = tc->wait_limit;
+    const int t0 = a.rank * a.mt, own = a.m - t0 < 0 ? 0 : (a.m - t0 < a.mt ? a.m - t0 : a.mt);
+    tp_reduce_norm_gather_kernel<<<own > 0 ? own : 1, kRgThreads, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), a);
+    LBK_CUDA(cudaGetLastError());
+    tc->ctx->launches++;
+    return LBK_OK;
+}
+
+const int8_t *lbk_tp_gather_q(lbk_tp_comm *t) { return t ? reinterpret_cast<TpComm *>(t)->region[reinterpret_cast<TpComm *>(t)->rank]->gather_q : nullptr; }
+const float *lbk_tp_gather_scale(lbk_tp_comm *t) { return t ? reinterpret_cast<TpComm *>(t)->region[reinterpret_cast<TpComm *>(t)->rank]->gather_scale : nullptr; }
+const int32_t *lbk_tp_gather_sum(lbk_tp_comm *t) { return t ? reinterpret_cast<TpComm *>(t)->region[reinterpret_cast<TpComm *>(t)->rank]->gather_sum : nullptr; }
+const float *lbk_tp_gather_f32(lbk_tp_comm *t) { return t ? reinterpret_cast<TpComm *>(t)->region[reinterpret_cast<TpComm *>(t)->rank]->gather_f : nullptr; }
+
+int lbk_tp_argmax(lbk_tp_comm *t, const float *logits_local_dev, const int32_t *idx_local_dev, size_t m, size_t vocab_local, int32_t *next_dev, void *stream) {
+    if (!t) return fail(LBK_ERR_INVALID, "tensor-parallel communicator is null");
+    TpComm *tc = reinterpret_cast<TpComm *>(t);
+    if (m == 0 || m > kTpMaxRows) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_argmax takes 1..%d token rows (got %zu)", kTpMaxRows, m);
+    if (!logits_local_dev || !idx_local_dev || !next_dev || vocab_local == 0) return fail(LBK_ERR_INVALID, "lbk_tp_argmax: null buffer or empty slice");
+    LBK_CUDA(cudaSetDevice(tc->ctx->device));
+    tp_argmax_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), tc->world, tc->rank, logits_local_dev, idx_local_dev, static_cast<int>(m),
+                                                                      static_cast<int>(vocab_local), next_dev, tc->ctx->err_word, tc->wait_limit);
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;

@@ -192,3 +192,228 @@ class RowParallelTernary:
         _lib.check(lib.lbk_tp_reduce_scale(comm.handle, C.c_void_p(scale.data_ptr()), C.c_float(self.scale), m, self.rows,
                                            C.c_void_p(out.data_ptr()), C.c_void_p(dots.data_ptr()), st))
         return out, dots
+
+
+# ---- the decoder step, tensor parallel ----------------------------------------------------------
+
+def token_range(m: int, world: int, rank: int):
+    """(first token, count) of the ceil(m / world) consecutive token rows rank `rank` owns."""
+    mt = (m + world - 1) // world
+    t0 = min(rank * mt, m)
+    return t0, max(0, min(m - t0, mt))
+
+
+class _Lin:
+    """A packed matrix by handle (a TernaryLinear's, or one owned by a loaded model shard)."""
+
+    def __init__(self, handle: int, rows: int, cols: int, scale: float, keep=None):
+        self.handle, self.rows, self.cols, self.scale, self._keep = handle, rows, cols, scale, keep
+
+
+class TpBitNet:
+    """BitNet::forward (crates/lb-model/src/model.rs:305-374) over `world` GPUs, one process each.
+
+    Sharding, as the 70B-shaped configuration states it: q/k/v/gate/up column-parallel (a rank holds
+    a row range of the packed matrix = its own attention heads / its slice of the intermediate
+    features), o/down row-parallel (a rank holds a 128-aligned column range). The K/V cache holds the
+    rank's own KV heads only, and attention runs on the rank's heads. Between the projections the
+    activations are exchanged by the library's own peer-memory kernels (lbk_tp_norm_quant,
+    lbk_tp_reduce_norm_gather: reduce-scatter of the exact int32 partial dots by token rows, residual
+    add + next norm + quantisation on the owner, all-gather of int8 rows); the residual stream lives
+    token-sharded. The head is split by vocabulary rows; lbk_tp_argmax picks the greedy token.
+    With world == 1 the same calls run without peers (the exchanges are trivial)."""
+
+    def __init__(self, cfg, layers, final_norm, embed, comm: TpComm, ctx, device="cuda"):
+        """layers: per layer a dict with _Lin entries q, k, v, o, gate, up, down (already this rank's
+        shards) and f32 CUDA tensors input_norm, post_attn_norm (full), attn_sub_norm, ffn_sub_norm
+        (this rank's column slices). embed: bf16 CUDA [vocab, hidden] (whole)."""
+        import torch
+        from .model import rope_tables
+        self.cfg, self.layers, self.final_norm, self.embed, self.comm, self.ctx = cfg, layers, final_norm, embed, comm, ctx
+        self.world, self.rank, self.device = comm.world, comm.rank, torch.device(device)
+        W = self.world
+        self.hd = cfg.head_dim()
+        if self.hd != 128 or cfg.num_key_value_heads % W or cfg.vocab_size % W or cfg.hidden_size % 128:
+            raise ValueError("this model does not divide over the ranks (KV heads, vocabulary) or its head size is not 128")
+        self.nh_l, self.kvh_l = cfg.num_attention_heads // W, cfg.num_key_value_heads // W
+        self.il = cfg.intermediate_size // W
+        self.vl = cfg.vocab_size // W
+        cos, sin = rope_tables(cfg)
+        self.cos, self.sin = torch.from_numpy(cos).to(self.device), torch.from_numpy(sin).to(self.device)
+        lib = ctx._lib
+        self.gq, self.gs = int(lib.lbk_tp_gather_q(comm.handle)), int(lib.lbk_tp_gather_scale(comm.handle))
+        self.gsum, self.gf = int(lib.lbk_tp_gather_sum(comm.handle)), int(lib.lbk_tp_gather_f32(comm.handle))
+        self._bufs = {}
+
+    # ---- construction ----------------------------------------------------------------------------
+    @classmethod
+    def from_tensors(cls, cfg, tensors, comm: TpComm, ctx, device="cuda"):
+        """Shards a full checkpoint dict (names as in model.lbt.safetensors; CPU or CUDA tensors)."""
+        import torch
+        from . import ops
+        W, r = comm.world, comm.rank
+        H, I = cfg.hidden_size, cfg.intermediate_size
+        nhd = cfg.num_attention_heads * cfg.head_dim()
+        dev = torch.device(device)
+
+        def col(name, cols):  # column-parallel: a row range
+            qw = tensors[f"{name}.qweight"]
+            lin = ops.TernaryLinear(shard_rows(qw, W, r).contiguous().to(dev), float(tensors[f"{name}.wscale"].reshape(-1)[0]), cols, ctx)
+            return _Lin(lin.weight.handle.value, lin.rows, cols, lin.scale, lin)
+
+        def row(name, cols):  # row-parallel: a column range
+            sl, lc = shard_cols(tensors[f"{name}.qweight"], cols, W, r)
+            lin = ops.TernaryLinear(sl.contiguous().to(dev), float(tensors[f"{name}.wscale"].reshape(-1)[0]), lc, ctx)
+            return _Lin(lin.weight.handle.value, lin.rows, lc, lin.scale, lin)
+
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            p = f"model.layers.{i}"
+            vec = lambda n: tensors[f"{p}.{n}.weight"].to(dev).float().contiguous()
+            sub_a, sub_f = vec("self_attn.attn_sub_norm"), vec("mlp.ffn_sub_norm")
+            layers.append(dict(q=col(f"{p}.self_attn.q_proj", H), k=col(f"{p}.self_attn.k_proj", H), v=col(f"{p}.self_attn.v_proj", H),
+                               o=row(f"{p}.self_attn.o_proj", nhd), gate=col(f"{p}.mlp.gate_proj", H), up=col(f"{p}.mlp.up_proj", H),
+                               down=row(f"{p}.mlp.down_proj", I), input_norm=vec("input_layernorm"), post_attn_norm=vec("post_attention_layernorm"),
+                               attn_sub_norm=sub_a[r * nhd // W:(r + 1) * nhd // W].contiguous(), ffn_sub_norm=sub_f[r * I // W:(r + 1) * I // W].contiguous()))
+        return cls(cfg, layers, tensors["model.norm.weight"].to(dev).float().contiguous(), tensors["model.embed_tokens.weight"].to(dev).contiguous(),
+                   comm, ctx, device)
+
+    @classmethod
+    def from_native(cls, native, comm: TpComm, device="cuda"):
+        """Wraps a shard loaded by lbk_model_load_shard (model.NativeBitNet with rank / world): the packed
+        matrices stay where the loader put them; norm gains and the embedding are viewed in place."""
+        import torch
+        cfg, lib, W, r = native.cfg, native._lib, comm.world, comm.rank
+        if (native.rank, native.world) != (r, W):
+            raise ValueError("the model shard and the communicator disagree on rank / world")
+        H, I, nhd = cfg.hidden_size, cfg.intermediate_size, cfg.num_attention_heads * cfg.head_dim()
+
+        def lin(layer, name):
+            h = native.linear_handle(layer, name)
+            return _Lin(h, int(lib.lbk_weight_rows(h)), int(lib.lbk_weight_cols(h)), float(lib.lbk_weight_scale(h)), native)
+
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            layers.append(dict(q=lin(i, "q"), k=lin(i, "k"), v=lin(i, "v"), o=lin(i, "o"), gate=lin(i, "gate"), up=lin(i, "up"), down=lin(i, "down"),
+                               input_norm=_DevView(native.norm_ptr(i, "input_norm"), H), post_attn_norm=_DevView(native.norm_ptr(i, "post_attn_norm"), H),
+                               attn_sub_norm=_DevView(native.norm_ptr(i, "attn_sub_norm") + 4 * (r * nhd // W), nhd // W),
+                               ffn_sub_norm=_DevView(native.norm_ptr(i, "ffn_sub_norm") + 4 * (r * I // W), I // W)))
+        return cls(cfg, layers, _DevView(native.norm_ptr(0, "final_norm"), H), _DevView(int(lib.lbk_model_embedding(native.handle)), cfg.vocab_size * H, 2),
+                   comm, native.ctx, device)
+
+    # ---- state -----------------------------------------------------------------------------------
+    def new_cache(self, b: int, cap: int):
+        """K/V rows of this rank's KV heads: bf16 [layers][b][kv_heads / world][cap][128]; one position per sequence."""
+        import torch
+        cfg = self.cfg
+        if cap < 1 or cap > cfg.max_position_embeddings:
+            raise ValueError(f"capacity {cap} is outside 1..max_position_embeddings ({cfg.max_position_embeddings})")
+        shape = (cfg.num_hidden_layers, b, self.kvh_l, cap, self.hd)
+        return dict(k=torch.zeros(shape, dtype=torch.bfloat16, device=self.device), v=torch.zeros(shape, dtype=torch.bfloat16, device=self.device),
+                    pos=torch.zeros(b, dtype=torch.int32, device=self.device), b=b, cap=cap, host_len=[0] * b)
+
+    def _buf(self, name, shape, dtype=None):
+        import torch
+        key = (name, tuple(shape), dtype or torch.float32)
+        if key not in self._bufs:
+            self._bufs[key] = torch.zeros(shape, dtype=dtype or torch.float32, device=self.device)
+        return self._bufs[key]
+
+    # ---- one step ----------------------------------------------------------------------------------
+    def forward(self, tokens, cache, prompt: bool = False):
+        """tokens: int32 CUDA [m]. prompt=False: one new token for each of the cache's m sequences.
+        prompt=True: m consecutive tokens of sequence 0 (a cache made for one sequence). Returns
+        (logits of this rank's vocabulary slice: [m, vocab / world], or [1, vocab / world] for the last
+        prompt token; greedy tokens int32 [m] or [1], the same on every rank) and advances the cache."""
+        import torch
+        from . import _lib
+        from .model import attention_splits
+        cfg, lib, h, comm = self.cfg, self.ctx._lib, self.ctx.handle, self.comm
+        m = int(tokens.shape[0])
+        if (not prompt and m != cache["b"]) or (prompt and cache["b"] != 1):
+            raise ValueError("token count and cache do not match")
+        need = m if prompt else 1
+        for used in cache["host_len"]:
+            if used + need > cache["cap"]:  # model.rs:309
+                raise ValueError(f"the cache is full: {used} of {cache['cap']} positions are used, {need} more do not fit")
+        H, I, hd, eps = cfg.hidden_size, cfg.intermediate_size, self.hd, cfg.rms_norm_eps
+        nh_l, kvh_l, il, L = self.nh_l, self.kvh_l, self.il, cfg.num_hidden_layers
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        P = lambda t: C.c_void_p(t.data_ptr() if hasattr(t, "data_ptr") else int(t))
+        chk = _lib.check
+        t0, cnt = token_range(m, self.world, self.rank)
+        mt = (m + self.world - 1) // self.world
+        xres = self._buf("xres", (max(mt, 1), H))
+        q = self._buf("q", (m, nh_l * hd)); k = self._buf("k", (m, kvh_l * hd)); v = self._buf("v", (m, kvh_l * hd))
+        attn = self._buf("attn", (m, nh_l * hd))
+        g = self._buf("g", (m, il)); u = self._buf("u", (m, il))
+        q8 = self._buf("q8", (m, max(nh_l * hd, il)), torch.int8)
+        qs, qsum = self._buf("qs", (m,)), self._buf("qsum", (m,), torch.int32)
+        splits = attention_splits(cache["cap"])
+        scratch = self._buf("attn_part", (m * nh_l * splits * (hd + 4),))
+        counters = self._buf("attn_counters", (m * kvh_l,), torch.int32)
+        rows_out = 1 if prompt else m
+        logits = self._buf("logits", (rows_out, self.vl))
+        idx, nxt = self._buf("idx", (rows_out,), torch.int32), self._buf("next", (rows_out,), torch.int32)
+
+        def gemm(qp, sp, sump, lins, outs, iouts):
+            wp, k1 = _lib.ptr_array([l.handle for l in lins])
+            op, k2 = _lib.ptr_array([o.data_ptr() for o in outs]) if outs else (None, None)
+            ip, k3 = _lib.ptr_array(iouts) if iouts else (None, None)
+            chk(lib.lbk_ternary_gemm_dev(h, wp, len(lins), C.c_void_p(qp), C.c_void_p(sp) if sp else None, C.c_void_p(sump), m, op, ip, st))
+
+        def reduce_norm_gather(flags, ascale, wscale, gain):
+            chk(lib.lbk_tp_reduce_norm_gather(comm.handle, flags, P(ascale) if ascale is not None else None, C.c_float(wscale), P(xres), P(gain),
+                                              C.c_float(eps), m, H, None, st))
+
+        if cnt:
+            chk(lib.lbk_embed_bf16(h, P(self.embed), C.c_void_p(tokens.data_ptr() + 4 * t0), cnt, H, P(xres), st))
+        reduce_norm_gather(1, None, 1.0, self.layers[0]["input_norm"])  # LBK_TP_NO_REDUCE
+        for li, l in enumerate(self.layers):
+            gemm(self.gq, self.gs, self.gsum, [l["q"], l["k"], l["v"]], [q, k, v], None)
+            kc, vc = cache["k"][li], cache["v"][li]
+            if prompt:
+                chk(lib.lbk_rope_kv_append_rows(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"], 0,
+                                                P(kc), P(vc), st))
+                chk(lib.lbk_attn_prefill(h, P(q), P(kc), P(vc), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"], 0, P(attn), st))
+            elif lib.lbk_attn_decode_fused_supported(nh_l, kvh_l, hd, splits):
+                chk(lib.lbk_attn_decode_fused_seq(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"],
+                                                  splits, P(kc), P(vc), P(scratch), P(counters), P(attn), st))
+            else:
+                chk(lib.lbk_rope_kv_append_seq(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"],
+                                               P(kc), P(vc), st))
+                chk(lib.lbk_attn_decode_seq(h, P(q), P(kc), P(vc), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"], splits, P(scratch), P(attn), st))
+            chk(lib.lbk_tp_norm_quant(comm.handle, 1, P(attn), None, P(l["attn_sub_norm"]), m, nh_l * hd, cfg.num_attention_heads * hd, C.c_float(eps),
+                                      P(q8), P(qs), P(qsum), st))
+            gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["o"]], None, [comm.partial_ptr])
+            reduce_norm_gather(0, qs, l["o"].scale, l["post_attn_norm"])
+            gemm(self.gq, self.gs, self.gsum, [l["gate"], l["up"]], [g, u], None)
+            chk(lib.lbk_tp_norm_quant(comm.handle, 3, P(g), P(u), P(l["ffn_sub_norm"]), m, il, I, C.c_float(eps), P(q8), P(qs), P(qsum), st))
+            gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["down"]], None, [comm.partial_ptr])
+            last = li + 1 == L
+            reduce_norm_gather(2 if last else 0, qs, l["down"].scale, self.final_norm if last else self.layers[li + 1]["input_norm"])
+        # the head: this rank's vocabulary rows of the tied embedding (model.rs:370-373), then the greedy token
+        head_in = self.gf + (4 * H * (m - 1) if prompt else 0)
+        chk(lib.lbk_bf16_linear(h, C.c_void_p(head_in), rows_out, C.c_void_p(_ptr(self.embed) + 2 * H * self.vl * self.rank), self.vl, H, P(logits), st))
+        chk(lib.lbk_argmax(h, P(logits), rows_out, self.vl, P(idx), st))
+        chk(lib.lbk_tp_argmax(comm.handle, P(logits), P(idx), rows_out, self.vl, P(nxt), st))
+        if prompt:
+            cache["pos"].add_(m)
+        else:
+            chk(lib.lbk_advance_pos_seq(h, P(cache["pos"]), None, m, st))
+        cache["host_len"] = [x + need for x in cache["host_len"]]
+        return logits, nxt
+
+
+class _DevView:
+    """A device address with an element count (memory owned by a loaded model)."""
+
+    def __init__(self, ptr: int, n: int, elem_bytes: int = 4):
+        self.ptr, self.n, self.elem_bytes = int(ptr), n, elem_bytes
+
+    def data_ptr(self) -> int:
+        return self.ptr
+
+
+def _ptr(t) -> int:
+    return int(t.data_ptr())

@@ -206,3 +206,183 @@ def test_missing_peer_times_out_and_the_context_survives(oracle, ctx):
     qq, ss, sm = oracle.quantize_acts(xh)
     assert np.array_equal(iouts[0].cpu().numpy(), oracle.ternary_gemm_i32(packed, 512, qq, sm))
     ctx.check_device_error()
+
+
+# ---- the tensor-parallel decoder step ---------------------------------------------------------------
+
+def _oracle_weights(cfg, tensors):
+    import torch
+    from oracle import decoder_oracle as D
+    w = {k: (v.view(torch.int16).numpy().view(np.uint16) if v.dtype == torch.bfloat16 else v.numpy()) for k, v in tensors.items()}
+    w["_cos"], w["_sin"] = D.rope_tables(cfg.head_dim(), cfg.rope_theta, cfg.max_position_embeddings)
+    return w
+
+
+def _tp_decoder_case(ctx, comm, world, rank, cfg, seed, b, steps, prompt_len, native_dir=None):
+    """Runs `steps` decode steps for b sequences and one prompt pass of prompt_len tokens on a TpBitNet
+    and compares this rank's slice of the logits and the greedy tokens with the CPU restatement
+    (oracle/decoder_oracle.py, fed the same random-init weights). Returns the worst relative deviation.
+    Bar: 2e-3 of max |logit| (the decoder tests' bar); greedy token equal where the margin is clear."""
+    import torch
+    from lemonade_burn_b200 import model, tp
+    from oracle import decoder_oracle as D
+    TOL = 2e-3
+    tensors = model.random_checkpoint(cfg, seed)
+    if native_dir is not None:
+        nat = model.NativeBitNet(native_dir, ctx, rank=rank, world=world)
+        net = tp.TpBitNet.from_native(nat, comm)
+    else:
+        net = tp.TpBitNet.from_tensors(cfg, tensors, comm, ctx)
+    w = _oracle_weights(cfg, tensors)
+    c = cfg.__dict__
+    kvh, hd, L, cap = cfg.num_key_value_heads, cfg.head_dim(), cfg.num_hidden_layers, cfg.max_position_embeddings
+    vl = cfg.vocab_size // world
+    sl = slice(rank * vl, (rank + 1) * vl)
+    worst = 0.0
+    rng = np.random.default_rng(seed)
+    cache = net.new_cache(b, cap)
+    okc = [[np.zeros((kvh, cap, hd), np.float32) for _ in range(L)] for _ in range(b)]
+    ovc = [[np.zeros((kvh, cap, hd), np.float32) for _ in range(L)] for _ in range(b)]
+    for s in range(steps):
+        toks = rng.integers(0, cfg.vocab_size, size=b).astype(np.int32)
+        logits, nxt = net.forward(torch.from_numpy(toks).cuda(), cache)
+        torch.cuda.synchronize()
+        got, nx = logits.cpu().numpy(), nxt.cpu().numpy()
+        for bi in range(b):
+            ref = D.decode_step(c, w, int(toks[bi]), okc[bi], ovc[bi], s)
+            scale = np.abs(ref).max()
+            err = np.abs(got[bi] - ref[sl]).max() / scale
+            worst = max(worst, err)
+            assert err < TOL, f"step {s} seq {bi}: max |delta logit| / max |logit| = {err}"
+            srt = np.sort(ref)
+            if srt[-1] - srt[-2] > 4 * TOL * scale:
+                assert nx[bi] == int(np.argmax(ref)), (s, bi)
+    assert cache["pos"].cpu().tolist() == [steps] * b
+    if prompt_len:
+        pc = net.new_cache(1, cap)
+        toks = rng.integers(0, cfg.vocab_size, size=prompt_len).astype(np.int32)
+        logits, nxt = net.forward(torch.from_numpy(toks).cuda(), pc, prompt=True)
+        torch.cuda.synchronize()
+        kc = [np.zeros((kvh, cap, hd), np.float32) for _ in range(L)]
+        vc = [np.zeros((kvh, cap, hd), np.float32) for _ in range(L)]
+        for pos, t in enumerate(toks):
+            ref = D.decode_step(c, w, int(t), kc, vc, pos)
+        scale = np.abs(ref).max()
+        err = np.abs(logits.cpu().numpy()[0] - ref[sl]).max() / scale
+        worst = max(worst, err)
+        assert err < TOL, f"prompt: {err}"
+        srt = np.sort(ref)
+        if srt[-1] - srt[-2] > 4 * TOL * scale:
+            assert int(nxt.cpu()[0]) == int(np.argmax(ref))
+        assert pc["pos"].cpu().tolist() == [prompt_len]
+        with pytest.raises(ValueError, match="cache is full"):
+            net.forward(torch.zeros(cap, dtype=torch.int32).cuda(), pc, prompt=True)
+    ctx.check_device_error()
+    return worst
+
+
+@pytest.mark.parametrize("heads,kv", [(8, 2), (4, 2)])
+def test_tp_decoder_step_with_one_rank(oracle, ctx, heads, kv):
+    """The tensor-parallel step's own kernels (sub-norm + quantise with the statistics exchange, reduce +
+    residual + norm + gather, vocabulary-split argmax) with a single rank: the exchanges are trivial, the
+    arithmetic and the buffers are the multi-rank ones. Four query heads per KV head take the fused
+    attention kernel, two the separate ones."""
+    from lemonade_burn_b200 import model, tp
+    cfg = model.Config(heads * 128, 1536, heads, kv, 2, 1024, 1e-5, 500000.0, 24)
+    comm = tp.TpComm(ctx, 1, 0)
+    try:
+        _tp_decoder_case(ctx, comm, 1, 0, cfg, seed=3 + heads, b=3, steps=3, prompt_len=9)
+    finally:
+        comm.close()
+
+
+def _tp_decoder_worker(rank, world, port, tmp, ok_q):
+    sys.path.insert(0, str(ROOT))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from lemonade_burn_b200 import _lib, model, ops, ternary, tp
+        from oracle import oracle as o
+        ctx = ternary.Context(rank)
+        comm = tp.TpComm(ctx, world, rank)
+        lib, h = ctx._lib, ctx.handle
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+        # (1) integers: a row-parallel projection at the 70B-shaped down projection's slice width
+        # (28672 / 8 = 3584 columns per rank at eight ranks), 64 token rows, twenty calls on one
+        # communicator alternating two matrices; the scaled rows this rank owns must be the oracle's bits
+        ok = True
+        cases = []
+        for seed, rows, cols in ((5, 1024, 3584 * world), (6, 512, 1024 * world)):
+            packed, ws, x = _case(o, rows=rows, cols=cols, m=64, seed=seed)
+            q, s, ssum = o.quantize_acts(x)
+            wf = o.simd_gemm_multi([packed], [ws], q, s, ssum)[0][0]
+            lc = cols // world
+            sl, _ = tp.shard_cols(packed, cols, world, rank)
+            lin = ops.TernaryLinear(torch.from_numpy(np.ascontiguousarray(sl)).cuda(), float(ws), lc, ctx)
+            xl = torch.from_numpy(np.ascontiguousarray(x[:, rank * lc:(rank + 1) * lc])).cuda()
+            cases.append((lin, xl, wf, s, rows, lc, float(ws)))
+        t0, cnt = tp.token_range(64, world, rank)
+        for it in range(20):
+            lin, xl, wf, s, rows, lc, ws = cases[it % 2]
+            q8 = torch.empty((64, lc), dtype=torch.int8, device="cuda")
+            sc = torch.empty(64, device="cuda")
+            sm = torch.empty(64, dtype=torch.int32, device="cuda")
+            _lib.check(lib.lbk_tp_quantize(comm.handle, C.c_void_p(xl.data_ptr()), 64, lc, C.c_void_p(q8.data_ptr()), C.c_void_p(sc.data_ptr()),
+                                           C.c_void_p(sm.data_ptr()), st))
+            wp, _k1 = _lib.ptr_array([lin.weight.handle.value])
+            ip, _k2 = _lib.ptr_array([comm.partial_ptr])
+            _lib.check(lib.lbk_ternary_gemm_dev(h, wp, 1, C.c_void_p(q8.data_ptr()), None, C.c_void_p(sm.data_ptr()), 64, None, ip, st))
+            xres = torch.zeros((max(cnt, 1), rows), device="cuda")
+            y = torch.full((max(cnt, 1), rows), float("nan"), device="cuda")
+            gain = torch.ones(rows, device="cuda")
+            _lib.check(lib.lbk_tp_reduce_norm_gather(comm.handle, 0, C.c_void_p(sc.data_ptr()), C.c_float(ws), C.c_void_p(xres.data_ptr()),
+                                                     C.c_void_p(gain.data_ptr()), C.c_float(1e-5), 64, rows, C.c_void_p(y.data_ptr()), st))
+            torch.cuda.synchronize()
+            ok = ok and np.array_equal(sc.cpu().numpy().view(np.uint32), s.view(np.uint32))
+            ok = ok and np.array_equal(y.cpu().numpy()[:cnt].view(np.uint32), wf[t0:t0 + cnt].view(np.uint32))
+            ok = ok and torch.equal(xres[:cnt], y[:cnt])   # the residual rows started at zero
+        ctx.check_device_error()
+        # (2) the whole decoder step against the oracle, from a full checkpoint sliced in Python and from
+        # the native loader's shards of the file rank 0 wrote
+        heads = 4 * world
+        cfg = model.Config(heads * 128, 128 * 3 * world, heads, world, 2, 128 * world, 1e-5, 500000.0, 24)
+        worst = _tp_decoder_case(ctx, comm, world, rank, cfg, seed=12, b=5, steps=3, prompt_len=11)
+        if rank == 0:
+            model.save_checkpoint(tmp, cfg, model.random_checkpoint(cfg, 12))
+        dist.barrier()
+        worst = max(worst, _tp_decoder_case(ctx, comm, world, rank, cfg, seed=12, b=2, steps=2, prompt_len=0, native_dir=tmp))
+        ctx.check_device_error()
+        dist.barrier()
+        comm.close()
+        ok_q.put((rank, bool(ok), float(worst)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_tp_decoder_ranks_match_oracle(tmp_path):
+    """The tensor-parallel decoder on every GPU of the box (2, 4 or 8 ranks as child processes over NCCL
+    for the rendezvous; the data path is the library's own peer-memory kernels): exact integers of a
+    row-parallel projection at the 70B-shaped slice widths over twenty alternating calls, then decode
+    steps and a prompt pass against the CPU restatement, from Python-sliced weights and from the
+    native loader's shards."""
+    import torch
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else 4 if n >= 4 else 2 if n >= 2 else 1
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    mpc = mp.get_context("spawn")
+    ok_q = mpc.Queue()
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    procs = [mpc.Process(target=_tp_decoder_worker, args=(r, world, port, str(tmp_path), ok_q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [ok_q.get(timeout=600) for _ in procs]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    assert all(ok for _, ok, _ in res), res
+    print("tensor-parallel decoder, worst relative logit deviation per rank:", [(r, w) for r, _, w in res])
