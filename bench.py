@@ -46,6 +46,14 @@ METRIC = "decode tok/s (BitNet-2B shape)"
 WORKLOAD = "bitnet2b_decode_sweep"
 
 
+def bench_config(world: int) -> dict:
+    """The `config` object of the JSON line, the same keys and values for both arms."""
+    return {"workload": WORKLOAD, "layers": LAYERS, "hidden": HIDDEN, "intermediate": INTER, "batch": 1,
+            "groups_per_step": LAYERS * len(GROUPS), "packed_weight_bytes": weight_bytes_per_sweep(),
+            "l2": "inputs larger than L2 (521 MB of distinct weights per step)",
+            "parallelism": "replicas" if world > 1 else "single"}
+
+
 def weight_bytes_per_sweep() -> int:
     return LAYERS * sum(sum(rows) * cols // 4 for cols, rows in GROUPS)
 
@@ -97,12 +105,16 @@ def config0_gemv(torch, ops, ctx, device, copies: int = 64, reps: int = 20):
             "us_per_call": us, "GBps": nbytes / us / 1e3, "algorithmic_bytes_per_call": nbytes}
 
 
-# int8 tensor-core peak measured on this pool's B200 with a no-load tcgen05.mma kind::i8 loop
-# (M=128, N=256 and N=128, K=32; 4568-4588 TOPS; nominal dense figure 4500)
-INT8_PEAK_TOPS_MEASURED = 4568.0
+def int8_peak(ctx):
+    """The int8 tensor-core rate with nothing to load or store (lbk_int8_peak_probe: one kernel, a few
+    milliseconds), at the GEMM's token-tile widths. The best of them is the denominator of every
+    "fraction of measured int8 peak" in this run; the nominal dense figure of the part is 4500 TOPS."""
+    rates = {str(n): ctx.int8_peak_tops(n, 20000) for n in (64, 128, 192, 256)}
+    return {"workload": "tcgen05.mma kind::i8, M=128 x N token rows x K=32, operands resident, 20000 x 4 MMAs per SM",
+            "TOPS_by_token_rows": rates, "TOPS": max(rates.values()), "nominal_dense_TOPS": 4500.0}
 
 
-def config2_prefill(torch, ops, ctx, device, ms=(64, 256, 1024, 2048), reps=5, per_graph=10):
+def config2_prefill(torch, ops, ctx, device, peak_tops, ms=(64, 256, 1024, 2048), reps=5, per_graph=10):
     """Config 2: prefill ternary GEMM at the BitNet-2B projections, per token count. One call =
     per-token int8 quantisation kernel + tcgen05 GEMM kernel; timed as CUDA-graph replays."""
     import ctypes as C
@@ -144,18 +156,32 @@ def config2_prefill(torch, ops, ctx, device, ms=(64, 256, 1024, 2048), reps=5, p
             us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
             tops = 2.0 * m * rows * cols / us / 1e6
             out.append({"k": cols, "n": rows, "m": m, "us": us, "int8_TOPS": tops,
-                        "frac_of_measured_int8_peak": tops / INT8_PEAK_TOPS_MEASURED, "frac_of_nominal_4500": tops / 4500.0})
-    return {"workload": "prefill ternary GEMM, quantise + tcgen05 kernel per call", "peak_TOPS_measured": INT8_PEAK_TOPS_MEASURED,
+                        "frac_of_measured_int8_peak": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0})
+    return {"workload": "prefill ternary GEMM, quantise + tcgen05 kernel per call", "peak_TOPS_measured": peak_tops,
             "cases": out}
 
 
-def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
+def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096, check=True):
     """Config 3: full decode step of a random-init BitNet-b1.58-2B4T-architecture decoder (30 layers,
     20/5 heads of 128, tied 128256-token bf16 head) at position `context` of a seeded bf16 KV cache,
-    greedy next token on the device. One CUDA graph per step, replayed `steps` times."""
+    greedy next token on the device. One CUDA graph per step, replayed `steps` times. Outside the timed
+    region the step at position `context` is compared with the CPU restatement of the reference's
+    decoder fed the same weights and cache (logits and greedy tokens, the reference's own metrics,
+    crates/lb-model/src/bin/lb-run.rs:223-259); at the larger batch the first two sequences are checked."""
     from lemonade_burn_b200 import model
     cfg = model.Config.bitnet_2b4t(max_pos=context + 64)
-    net = model.BitNet(cfg, model.random_checkpoint(cfg, 11, device=device), ctx, device)
+    tensors = model.random_checkpoint(cfg, 11, device=device)
+    net = model.BitNet(cfg, tensors, ctx, device)
+    peak, _ = measured_peaks()
+    w = None
+    if check:
+        from oracle import decoder_oracle as D
+        w = {}
+        for k, v in tensors.items():
+            v = v.cpu()
+            w[k] = v.view(torch.int16).numpy().view(np.uint16) if v.dtype == torch.bfloat16 else v.numpy()
+        w["_cos"], w["_sin"] = D.rope_tables(cfg.head_dim(), cfg.rope_theta, cfg.max_position_embeddings)
+    del tensors
     res = []
     for b in batches:
         cache = net.new_cache(b=b, cap=context + 64)
@@ -165,39 +191,63 @@ def config3_decode(torch, ctx, device, batches=(1, 16), steps=20, context=4096):
                 t[li].copy_(torch.randn(t[li].shape, generator=g, device=device).to(torch.bfloat16))
         tokens = torch.randint(0, cfg.vocab_size, (b,), dtype=torch.int32, device=device, generator=g)
         nxt = torch.zeros(b, dtype=torch.int32, device=device)
+        logits_keep = torch.zeros((b, cfg.vocab_size), device=device)
+        n_chk = min(b, 2)
+        k_bits = v_bits = None
+        if check:  # the cache as it is before the step, for the sequences that are checked
+            k_bits = cache.k[:, :n_chk].cpu().view(torch.int16).numpy().view(np.uint16)
+            v_bits = cache.v[:, :n_chk].cpu().view(torch.int16).numpy().view(np.uint16)
 
         def step():
             logits = net.forward(tokens, cache)
+            logits_keep.copy_(logits)
             nxt.copy_(net.argmax(logits))
 
-        cache.pos.fill_(context)
+        def rewind():
+            cache.pos.fill_(context)
+            cache.host_len = context
+
+        rewind()
         step()
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
-        cache.pos.fill_(context)
+        rewind()
         with torch.cuda.stream(side):
             with torch.cuda.graph(graph, stream=side):
                 step()
         torch.cuda.synchronize()
-        cache.pos.fill_(context)
+        rewind()
         graph.replay()
         torch.cuda.synchronize()
-        cache.pos.fill_(context)
+        report = None
+        if check:
+            from oracle import decoder_oracle as D
+            want = D.check_step(cfg.__dict__, w, tokens[:n_chk].cpu().numpy(), k_bits, v_bits, context)
+            got = logits_keep[:n_chk].cpu().numpy()
+            report = D.compare_logits(got, want, margin=4e-3 * float(np.abs(want).max()))
+            report["greedy_equal"] = bool(np.array_equal(nxt[:n_chk].cpu().numpy(), want.argmax(axis=1)))
+            report["sequences_checked"] = n_chk
+            report["relative_max_delta"] = report["max_abs_delta"] / report["max_abs_logit"]
+        rewind()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(steps):
             graph.replay()
         e1.record()
         torch.cuda.synchronize()
+        ctx.check_device_error()
         ms = e0.elapsed_time(e1) / steps
         kv_bytes = cfg.num_hidden_layers * 2 * cfg.num_key_value_heads * (context + steps // 2) * cfg.head_dim() * 2 * b
         head_bytes = cfg.vocab_size * cfg.hidden_size * 2 * ((b + 15) // 16)   # the head streams W once per 16 token rows
         nbytes = weight_bytes_per_sweep() + head_bytes + kv_bytes
+        gbs = nbytes / (ms * 1e-3) / 1e9
         res.append({"batch": b, "ms_per_step": ms, "tok_per_s": b / (ms * 1e-3), "context": context,
-                    "algorithmic_bytes_per_step": nbytes, "GBps": nbytes / (ms * 1e-3) / 1e9,
-                    "next_tokens": nxt.cpu().tolist()[:4]})
+                    "algorithmic_bytes_per_step": nbytes, "GBps": gbs,
+                    "roofline": {"bound": "hbm", "achieved": gbs, "peak": peak, "unit": "GB/s", "frac": gbs / peak,
+                                 "algorithmic_bytes": {"packed_weights": weight_bytes_per_sweep(), "bf16_head": head_bytes, "bf16_kv_cache": kv_bytes}},
+                    "next_tokens": nxt.cpu().tolist()[:4], "check_against_cpu_restatement": report})
         del cache, graph
         torch.cuda.empty_cache()
     return {"workload": "BitNet-2B4T-architecture decode step, random init, bf16 KV cache, greedy", "cases": res}
@@ -303,9 +353,10 @@ def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers
     exchange) is timed as well. Returns a dict for the JSON line."""
     from lemonade_burn_b200 import tp
 
-    def rand_packed(rows, rb, gen):
-        b = torch.randint(0, 256, (rows, rb), dtype=torch.uint8, device=device, generator=gen)
-        return b & ~((b >> 1) & b & 0x55)  # clear code 3 -> valid ternary (P(0)=0.5, P(+-1)=0.25)
+    def rand_packed(rows, rb, gen):  # i.i.d. codes, P(-1) = P(+1) = 0.3, P(0) = 0.4
+        v = torch.randint(0, 10, (4, rows, rb), dtype=torch.uint8, device=device, generator=gen)
+        codes = (v >= 3).to(torch.uint8) + (v >= 7).to(torch.uint8)
+        return codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)
 
     gen = torch.Generator(device=device).manual_seed(777 + rank)
     H, I = TP_HIDDEN, TP_INTER
@@ -389,10 +440,12 @@ def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers
            "tok_per_s": batch / (ms_step * 1e-3), "int8_TOPS": 2.0 * batch * packed_total * 4 / (ms_step * 1e-3) / 1e12,
            "packed_weight_bytes_total": packed_total, "allreduce_int32_bytes_per_layer": 2 * batch * H * 4,
            "collectives": "two fused peer-memory kernels per row-parallel layer (NVLink loads/stores)" if world > 1 else "none (one rank)",
-           "launch": mode, "weights": "valid ternary codes, P(0)=0.5, drawn per rank at shard size"}
+           "launch": mode, "weights": "i.i.d. ternary codes, P(0)=0.4, drawn per rank at shard size",
+           "ms_per_80_layers": ms_step * TP_LAYERS / layers}
     if world > 1:
         ms_nccl, _ = timed(batch, layers, False, steps)
         res["ms_per_step_nccl_allreduce"] = ms_nccl
+        res["ms_per_80_layers_nccl_allreduce"] = ms_nccl * TP_LAYERS / layers
     pl = min(prefill_layers, layers)
     ms_pf, mode_pf = timed(prefill_tokens, pl, False, 3)
     res["prefill"] = {"tokens": prefill_tokens, "layers_timed": pl, "ms_per_layer": ms_pf / pl,
@@ -403,6 +456,163 @@ def tp70b_sweep(torch, dist, ctx, device, world, rank, steps=5, warmup=2, layers
     if comm is not None:
         dist.barrier()
         comm.close()
+    return res
+
+
+def tp70b_decoder(torch, dist, ctx, device, world, rank, layers=TP_LAYERS, batch=TP_BATCH, context=1024, steps=5, warmup=2,
+                  prefill_tokens=2048):
+    """Config 4 as a decoder: hidden 8192, intermediate 28672, 64 Q / 8 KV heads of 128, `layers` layers,
+    random init with P(0) = 0.4 (every rank holds slices of the same seeded model). One decode step for
+    `batch` sequences at position `context` of a seeded bf16 K/V cache (one CUDA graph per step), and one
+    prompt pass of `prefill_tokens` tokens. Sharding: q/k/v/gate/up by rows, o/down by 128-aligned columns,
+    attention and K/V cache by heads, the head by vocabulary rows; the exchanges are the library's own
+    peer-memory kernels (strong scaling: the work is fixed, the ranks split it). Before the timing one
+    row-parallel projection (layer 0's down, all 28672 columns) is compared with the CPU port of the
+    reference's kernels on this rank's token rows."""
+    from lemonade_burn_b200 import _lib, model, tp
+    import ctypes as C
+    cap = context + 64
+    cfg = model.Config(TP_HIDDEN, TP_INTER, 64, 8, layers, 128256, 1e-5, 500000.0, max(cap, prefill_tokens + 64))
+    comm = tp.TpComm(ctx, world, rank)
+    t_build = time.perf_counter()
+    net = tp.TpBitNet.random_init(cfg, 70, comm, ctx, device, p_zero=0.4)
+    torch.cuda.synchronize()
+    t_build = time.perf_counter() - t_build
+    lib, h = ctx._lib, ctx.handle
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def sync_all():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- check: layer 0's down projection through the row-parallel path against the CPU port -------
+    from oracle import oracle as o
+    o.build()
+    H, I = TP_HIDDEN, TP_INTER
+    lc = I // world
+    full = net._packed_for_check(H, I, 70 * 100003 + 6).cpu().numpy()
+    gx = torch.Generator(device=device).manual_seed(4242)
+    x = torch.randn(batch, I, generator=gx, device=device)
+    xl = x[:, rank * lc:(rank + 1) * lc].contiguous()
+    q8 = torch.empty((batch, lc), dtype=torch.int8, device=device)
+    sc = torch.empty(batch, device=device)
+    sm = torch.empty(batch, dtype=torch.int32, device=device)
+    _lib.check(lib.lbk_tp_quantize(comm.handle, C.c_void_p(xl.data_ptr()), batch, lc, C.c_void_p(q8.data_ptr()), C.c_void_p(sc.data_ptr()),
+                                   C.c_void_p(sm.data_ptr()), st))
+    down = net.layers[0]["down"]
+    wp, _k1 = _lib.ptr_array([down.handle])
+    ip, _k2 = _lib.ptr_array([comm.partial_ptr])
+    _lib.check(lib.lbk_ternary_gemm_dev(h, wp, 1, C.c_void_p(q8.data_ptr()), None, C.c_void_p(sm.data_ptr()), batch, None, ip, st))
+    t0, cnt = tp.token_range(batch, world, rank)
+    xres = torch.zeros((max(cnt, 1), H), device=device)
+    y = torch.zeros((max(cnt, 1), H), device=device)
+    gain = torch.ones(H, device=device)
+    _lib.check(lib.lbk_tp_reduce_norm_gather(comm.handle, 0, C.c_void_p(sc.data_ptr()), C.c_float(down.scale), C.c_void_p(xres.data_ptr()),
+                                             C.c_void_p(gain.data_ptr()), C.c_float(1e-5), batch, H, C.c_void_p(y.data_ptr()), st))
+    torch.cuda.synchronize()
+    xq, xs, xsum = o.quantize_acts(x.cpu().numpy())
+    want = o.simd_gemm_multi([full], [down.scale], xq[t0:t0 + max(cnt, 1)], xs[t0:t0 + max(cnt, 1)], xsum[t0:t0 + max(cnt, 1)])[0][0]
+    same = bool(cnt == 0 or np.array_equal(y.cpu().numpy()[:cnt].view(np.uint32), want[:cnt].view(np.uint32)))
+    flag = torch.tensor([1 if same else 0], device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    del full, x, xl, q8, y, xres
+    ctx.check_device_error()
+
+    # ---- decode: `batch` sequences at position `context` ----------------------------------------------
+    cache = net.new_cache(batch, cap)
+    g = torch.Generator(device=device).manual_seed(300 + rank)
+    for tsr in (cache["k"], cache["v"]):
+        for li in range(layers):
+            tsr[li].copy_(torch.randn(tsr[li].shape, generator=g, device=device).to(torch.bfloat16))
+    gt = torch.Generator(device=device).manual_seed(9)
+    tokens = torch.randint(0, cfg.vocab_size, (batch,), dtype=torch.int32, device=device, generator=gt)
+
+    def rewind():
+        cache["pos"].fill_(context)
+        cache["host_len"] = [context] * batch
+
+    for _ in range(warmup):
+        rewind()
+        net.forward(tokens, cache)
+    sync_all()
+    # per-operation breakdown of one eager step (events between the calls; the graph below has no gaps)
+    rewind()
+    trace = []
+    net.forward(tokens, cache, trace=trace)
+    torch.cuda.synchronize()
+    by_op = {}
+    for (n0, e0_), (n1, e1_) in zip(trace[:-1], trace[1:]):
+        by_op[n1] = by_op.get(n1, 0.0) + e0_.elapsed_time(e1_)
+    sync_all()
+    rewind()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            net.forward(tokens, cache)
+    torch.cuda.current_stream().wait_stream(side)
+    sync_all()
+    rewind()
+    graph.replay()
+    sync_all()
+    rewind()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        graph.replay()
+    e1.record()
+    sync_all()
+    ctx.check_device_error()
+    tms = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+    ms_step = float(tms[0])
+    del graph
+    # ---- prompt pass -------------------------------------------------------------------------------------
+    pc = net.new_cache(1, prefill_tokens + 64)
+    ptoks = torch.randint(0, cfg.vocab_size, (prefill_tokens,), dtype=torch.int32, device=device, generator=gt)
+    times = []
+    for rep in range(3):
+        pc["pos"].zero_()
+        pc["host_len"] = [0]
+        sync_all()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        p0.record()
+        net.forward(ptoks, pc, prompt=True)
+        p1.record()
+        sync_all()
+        times.append(p0.elapsed_time(p1))
+    ctx.check_device_error()
+    pms = torch.tensor([min(times[1:])], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(pms, op=dist.ReduceOp.MAX)
+    per_layer = (H + 2 * TP_KV) * H // 4 + H * H // 4 + 2 * I * H // 4 + H * I // 4
+    kv_bytes = layers * 2 * 8 * (context + 1) * 128 * 2 * batch
+    head_bytes = cfg.vocab_size * H * 2 * ((batch + 15) // 16)
+    dec_bytes = layers * per_layer + kv_bytes + head_bytes
+    peak, _ = measured_peaks()
+    res = {"workload": "ternary70b_tp_decoder", "layers": layers, "hidden": H, "intermediate": I, "heads": "64 Q / 8 KV of 128", "vocab": cfg.vocab_size,
+           "batch": batch, "context": context, "parallelism": f"tp{world}", "scaling": "strong",
+           "decode": {"ms_per_step": ms_step, "tok_per_s": batch / (ms_step * 1e-3), "launch": "cuda graph",
+                      "algorithmic_bytes_per_step_all_ranks": dec_bytes, "GBps_per_gpu": dec_bytes / world / (ms_step * 1e-3) / 1e9,
+                      "frac_of_measured_hbm_per_gpu": dec_bytes / world / (ms_step * 1e-3) / 1e9 / peak,
+                      "eager_step_ms_by_operation_rank0": {k: round(v, 4) for k, v in by_op.items()},
+                      "eager_step_ms_rank0": round(sum(by_op.values()), 4)},
+           "prefill": {"tokens": prefill_tokens, "ms": float(pms[0]), "tok_per_s": prefill_tokens / (float(pms[0]) * 1e-3),
+                       "int8_TOPS_per_gpu": 2.0 * prefill_tokens * per_layer * 4 * layers / world / (float(pms[0]) * 1e-3) / 1e12,
+                       "launch": "eager"},
+           "exchange": ("reduce-scatter of int32 partial dots by token rows + all-gather of int8 rows, peer loads/stores in the library's kernels "
+                        f"({(world - 1) * batch * H * 4 // world} + {(world - 1) * batch * H // world} bytes per rank and row-parallel layer at decode)") if world > 1
+                       else "none (one rank)",
+           "check_down_proj_rows_equal_cpu_port_bits": bool(int(flag[0])), "weights": "i.i.d. ternary P(0)=0.4, shared seeds, sliced per rank",
+           "build_seconds": t_build}
+    del cache, pc, net
+    torch.cuda.empty_cache()
+    sync_all()
+    comm.close()
     return res
 
 
@@ -563,7 +773,7 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": toks, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 / toks, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": LAYERS, "hidden": HIDDEN, "intermediate": INTER, "batch": 1},
+        "config": bench_config(int(os.environ.get("WORLD_SIZE", "1"))),
         "cpu_baseline": {"value": toks, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": toks, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -669,6 +879,26 @@ def run_ours(args):
         clocks["sampled"] = ("during the timed region and an untimed continuation of the same load"
                              if continued else "during the timed region")
 
+    sustained = None
+    if rank == 0 and "sustained" in args.extras:
+        # The headline's timed region is a burst of a few milliseconds. The same launch repeated for more
+        # than two seconds shows what the part holds once the power cap has had time to act.
+        n_sus = max(1000, int(2.5 / (dev_ms * 1e-3 / args.steps)))
+        sus = ClockSampler(local)
+        sus.start()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        for _ in range(n_sus):
+            plan.run()
+        s1.record()
+        torch.cuda.synchronize()
+        sus_clocks = sus.stop()
+        sus_ms = s0.elapsed_time(s1) / n_sus
+        sus_gbs = algorithmic_bytes_per_sweep() / (sus_ms * 1e-3) / 1e9
+        sustained = {"steps": n_sus, "seconds": sus_ms * n_sus * 1e-3, "ms_per_step": sus_ms, "tok_per_s": 1e3 / sus_ms, "GBps": sus_gbs,
+                     "clocks": sus_clocks,
+                     "us_times_median_sm_mhz": (sus_ms * 1e3 * sus_clocks["sm_mhz"]) if sus_clocks.get("sm_mhz") else None}
+
     times = torch.tensor([dev_ms, e2e_s * 1e3], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
@@ -697,6 +927,11 @@ def run_ours(args):
                 off += cols
         cpu_toks, cores, kern, sample = cpu_sweep_baseline(packed_layers, xs, budget_s=10.0, max_layers=n_cpu_layers)
         extra = {}
+        if sustained is not None:
+            sustained["frac_of_measured_hbm"] = sustained["GBps"] / peak
+            sustained["frac_of_nominal_8TBs"] = sustained["GBps"] / 8000.0
+            sustained["burst_us_times_median_sm_mhz"] = (sweep_s * 1e6 * clocks["sm_mhz"]) if clocks.get("sm_mhz") else None
+            extra["sustained"] = sustained
 
         def side(name, fn):
             """A side measurement must not cost the headline line (measured above): its failure is reported in its place."""
@@ -709,7 +944,9 @@ def run_ours(args):
         if "config0" in args.extras:
             side("config0_gemv", lambda: config0_gemv(torch, ops, ctx, device))
         if "config2" in args.extras:
-            side("config2_prefill", lambda: config2_prefill(torch, ops, ctx, device))
+            side("int8_peak", lambda: int8_peak(ctx))
+            peak_tops = extra["int8_peak"].get("TOPS", 4500.0) if isinstance(extra.get("int8_peak"), dict) else 4500.0
+            side("config2_prefill", lambda: config2_prefill(torch, ops, ctx, device, peak_tops))
     del plan, linears
     torch.cuda.empty_cache()
     if rank == 0 and world == 1 and "config3" in args.extras:
@@ -717,20 +954,30 @@ def run_ours(args):
         side("config3_prompt", lambda: config3_prompt(torch, ctx))
     if rank == 0 and world == 1 and "convert" in args.extras:
         side("converter", lambda: converter_pass(torch, ctx, device))
-    tp_res = None
-    if args.tp70b or world > 1:
-        tp_res = tp70b_sweep(torch, dist, ctx, device, world, rank, layers=args.tp_layers)
+    tp_res = tp_dec = None
+    if "tp" in args.extras:
+        # config 4 at every N (N = 1 is the base of the strong-scaling curve): the decoder with the
+        # library's own exchanges, then the projection sweep through NCCL all-reduces beside it
+        try:
+            tp_dec = tp70b_decoder(torch, dist, ctx, device, world, rank, layers=args.tp_layers)
+        except Exception as exc:
+            tp_dec = {"error": f"{type(exc).__name__}: {exc}"}
+        torch.cuda.empty_cache()
+        if args.tp70b or world > 1:
+            try:
+                tp_res = tp70b_sweep(torch, dist, ctx, device, world, rank, layers=min(args.tp_layers, 16), prefill_layers=4)
+            except Exception as exc:
+                tp_res = {"error": f"{type(exc).__name__}: {exc}"}
     if rank == 0:
+        if tp_dec is not None:
+            extra["tp70b"] = tp_dec
         if tp_res is not None:
-            extra["tp70b"] = tp_res
+            extra["tp70b_projection_sweep_nccl"] = tp_res
         line = {
             "metric": METRIC, "value": tok_s, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8 x ternary -> int32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "layers": LAYERS, "hidden": HIDDEN, "intermediate": INTER, "batch": 1,
-                       "groups_per_step": LAYERS * len(GROUPS), "packed_weight_bytes": weight_bytes_per_sweep(),
-                       "l2": "inputs larger than L2 (521 MB of distinct weights per step)",
-                       "parallelism": "replicas" if world > 1 else "single"},
+            "config": bench_config(world),
             "e2e": {"value": e2e_tok_s, "unit": "tok/s", "h2d_bytes_per_step": nx * 4, "d2h_bytes_per_step": ny * 4},
             "gpu_launches": int(launches),
             "clocks": clocks,
@@ -756,8 +1003,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tp70b", action="store_true", help="also time the 70B-shaped tensor-parallel sweep at N=1")
     ap.add_argument("--tp-layers", type=int, default=TP_LAYERS)
-    ap.add_argument("--extras", default="config0,config2,config3,convert",
-                    help="side measurements to add under `extra` (comma list of config0, config2, config3, convert; 'none' for a profiler run)")
+    ap.add_argument("--extras", default="sustained,config0,config2,config3,convert,tp",
+                    help="side measurements to add under `extra` (comma list of sustained, config0, config2, config3, convert, tp; "
+                         "'none' for a profiler run)")
     ap.add_argument("--decode-batches", type=int, nargs="+", default=[1, 16], help="batch sizes of the config-3 decode step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)

@@ -71,6 +71,14 @@ uint64_t lbk_launch_count(const lbk_ctx *ctx);
  * was measured on. The reference's counterpart is the kernel selector (gemm.rs:25-92, LB_KERNEL). */
 int lbk_set_gemv_rows(lbk_ctx *ctx, int rows);
 
+/* Measures the rate at which this GPU executes the int8 tensor-core instruction the prefill GEMM is
+ * built on (tcgen05.mma kind::i8, 128 weight rows x token_rows x K 32; operands resident, nothing
+ * loaded or stored): one kernel of `iterations` groups of four MMAs per SM, timed with CUDA events on
+ * the context's stream. tops_out: 1e12 multiply-add operations x 2 per second. token_rows: 64, 128,
+ * 192 or 256. This is the measured denominator of "fraction of int8 peak"; it has no counterpart in
+ * the reference. Synchronous; about 20000 iterations take a few milliseconds. */
+int lbk_int8_peak_probe(lbk_ctx *ctx, size_t token_rows, size_t iterations, double *tops_out);
+
 /* ---- layout helpers: crates/lb-ternary/src/pack.rs:22-24,83-85 -------------------------- */
 
 size_t lbk_padded_cols(size_t cols);

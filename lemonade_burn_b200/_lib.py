@@ -26,6 +26,7 @@ SYMBOLS = [
     ("lbk_check_device_error", _i, [_vp]),
     ("lbk_launch_count", C.c_uint64, [_vp]),
     ("lbk_set_gemv_rows", _i, [_vp, _i]),
+    ("lbk_int8_peak_probe", _i, [_vp, _sz, _sz, _vp]),
     ("lbk_padded_cols", _sz, [_sz]),
     ("lbk_row_bytes", _sz, [_sz]),
     ("lbk_weight_upload", _i, [_vp, _sz, _sz, _vp, _sz, _f, _pp]),

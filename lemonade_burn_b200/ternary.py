@@ -74,6 +74,12 @@ class Context:
     def launch_count(self) -> int:
         return int(self._lib.lbk_launch_count(self.handle))
 
+    def int8_peak_tops(self, token_rows: int = 192, iterations: int = 20000) -> float:
+        """Measured rate of the int8 tensor-core instruction with resident operands (lbk_int8_peak_probe)."""
+        out = C.c_double()
+        _lib.check(self._lib.lbk_int8_peak_probe(self.handle, token_rows, iterations, C.byref(out)))
+        return float(out.value)
+
     def set_gemv_rows(self, rows: int) -> None:
         """0: the measured rule decides between the fused few-row kernel and quantise + GEMM;
         n: the fused kernel takes every call of at most n token rows (same bits either way)."""

@@ -279,6 +279,58 @@ class TpBitNet:
                    comm, ctx, device)
 
     @classmethod
+    def random_init(cls, cfg, seed: int, comm: TpComm, ctx, device="cuda", p_zero: float = 0.4):
+        """Random-init weights of the given architecture, generated on the device and kept as this
+        rank's shards only: i.i.d. ternary codes with P(0) = p_zero and P(-1) = P(+1), norm gains near 1,
+        bf16 embedding N(0, 0.02). Every tensor has its own seed, the same on every rank, so that the
+        ranks hold slices of one model; the full tensor exists only while it is sliced."""
+        import torch
+        from . import ops
+        from .pack import row_bytes as _rb
+        W, r = comm.world, comm.rank
+        H, I = cfg.hidden_size, cfg.intermediate_size
+        nhd = cfg.num_attention_heads * cfg.head_dim()
+        kvd = cfg.num_key_value_heads * cfg.head_dim()
+        dev = torch.device(device)
+        scale = float(np.float32(1.0) / np.float32(0.02 * np.sqrt(2.0 / np.pi)))  # 1 / mean|N(0, 0.02)|
+
+        def packed(rows, cols, tseed):
+            g = torch.Generator(device=dev).manual_seed(tseed)
+            lo = int(round((1.0 - p_zero) / 2 * 1000))
+            v = torch.randint(0, 1000, (4, rows, _rb(cols)), dtype=torch.int16, generator=g, device=dev)
+            codes = (v >= lo).to(torch.uint8) + (v >= 1000 - lo).to(torch.uint8)
+            return codes[0] | (codes[1] << 2) | (codes[2] << 4) | (codes[3] << 6)
+
+        def col(rows, cols, tseed):
+            lin = ops.TernaryLinear(shard_rows(packed(rows, cols, tseed), W, r).contiguous(), scale, cols, ctx)
+            return _Lin(lin.weight.handle.value, lin.rows, cols, lin.scale, lin)
+
+        def row(rows, cols, tseed):
+            sl, lc = shard_cols(packed(rows, cols, tseed), cols, W, r)
+            lin = ops.TernaryLinear(sl.contiguous(), scale, lc, ctx)
+            return _Lin(lin.weight.handle.value, lin.rows, lc, lin.scale, lin)
+
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            s0 = seed * 100003 + i * 16
+            g = torch.Generator(device=dev).manual_seed(s0 + 15)
+            gain = lambda n: (1.0 + 0.05 * torch.randn(n, generator=g, device=dev)).float()
+            inp, post, sub_a, sub_f = gain(H), gain(H), gain(nhd), gain(I)
+            layers.append(dict(q=col(nhd, H, s0), k=col(kvd, H, s0 + 1), v=col(kvd, H, s0 + 2), o=row(H, nhd, s0 + 3),
+                               gate=col(I, H, s0 + 4), up=col(I, H, s0 + 5), down=row(H, I, s0 + 6), input_norm=inp, post_attn_norm=post,
+                               attn_sub_norm=sub_a[r * nhd // W:(r + 1) * nhd // W].contiguous(), ffn_sub_norm=sub_f[r * I // W:(r + 1) * I // W].contiguous()))
+        g = torch.Generator(device=dev).manual_seed(seed * 100003 + 99991)
+        final = (1.0 + 0.05 * torch.randn(H, generator=g, device=dev)).float()
+        embed = torch.empty((cfg.vocab_size, H), dtype=torch.bfloat16, device=dev)
+        step = 8192
+        for v0 in range(0, cfg.vocab_size, step):  # in slabs: the f32 draw of the whole table would be twice its size
+            n = min(step, cfg.vocab_size - v0)
+            embed[v0:v0 + n] = (0.02 * torch.randn(n, H, generator=g, device=dev)).to(torch.bfloat16)
+        net = cls(cfg, layers, final, embed, comm, ctx, device)
+        net._packed_for_check = packed
+        return net
+
+    @classmethod
     def from_native(cls, native, comm: TpComm, device="cuda"):
         """Wraps a shard loaded by lbk_model_load_shard (model.NativeBitNet with rank / world): the packed
         matrices stay where the loader put them; norm gains and the embedding are viewed in place."""
@@ -320,11 +372,13 @@ class TpBitNet:
         return self._bufs[key]
 
     # ---- one step ----------------------------------------------------------------------------------
-    def forward(self, tokens, cache, prompt: bool = False):
+    def forward(self, tokens, cache, prompt: bool = False, trace=None):
         """tokens: int32 CUDA [m]. prompt=False: one new token for each of the cache's m sequences.
         prompt=True: m consecutive tokens of sequence 0 (a cache made for one sequence). Returns
         (logits of this rank's vocabulary slice: [m, vocab / world], or [1, vocab / world] for the last
-        prompt token; greedy tokens int32 [m] or [1], the same on every rank) and advances the cache."""
+        prompt token; greedy tokens int32 [m] or [1], the same on every rank) and advances the cache.
+        trace: a list that receives (operation name, CUDA event recorded after it) pairs, for a per-operation
+        time breakdown of an eager step (not for use under graph capture)."""
         import torch
         from . import _lib
         from .model import attention_splits
@@ -356,6 +410,12 @@ class TpBitNet:
         logits = self._buf("logits", (rows_out, self.vl))
         idx, nxt = self._buf("idx", (rows_out,), torch.int32), self._buf("next", (rows_out,), torch.int32)
 
+        def mark(name):
+            if trace is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                trace.append((name, ev))
+
         def gemm(qp, sp, sump, lins, outs, iouts):
             wp, k1 = _lib.ptr_array([l.handle for l in lins])
             op, k2 = _lib.ptr_array([o.data_ptr() for o in outs]) if outs else (None, None)
@@ -366,11 +426,14 @@ class TpBitNet:
             chk(lib.lbk_tp_reduce_norm_gather(comm.handle, flags, P(ascale) if ascale is not None else None, C.c_float(wscale), P(xres), P(gain),
                                               C.c_float(eps), m, H, None, st))
 
+        mark("start")
         if cnt:
             chk(lib.lbk_embed_bf16(h, P(self.embed), C.c_void_p(tokens.data_ptr() + 4 * t0), cnt, H, P(xres), st))
         reduce_norm_gather(1, None, 1.0, self.layers[0]["input_norm"])  # LBK_TP_NO_REDUCE
+        mark("embed + norm + gather")
         for li, l in enumerate(self.layers):
             gemm(self.gq, self.gs, self.gsum, [l["q"], l["k"], l["v"]], [q, k, v], None)
+            mark("q/k/v GEMM")
             kc, vc = cache["k"][li], cache["v"][li]
             if prompt:
                 chk(lib.lbk_rope_kv_append_rows(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"], 0,
@@ -383,15 +446,23 @@ class TpBitNet:
                 chk(lib.lbk_rope_kv_append_seq(h, P(q), P(k), P(v), P(self.cos), P(self.sin), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"],
                                                P(kc), P(vc), st))
                 chk(lib.lbk_attn_decode_seq(h, P(q), P(kc), P(vc), P(cache["pos"]), m, nh_l, kvh_l, hd, cache["cap"], splits, P(scratch), P(attn), st))
+            mark("attention (RoPE, K/V append, softmax)")
             chk(lib.lbk_tp_norm_quant(comm.handle, 1, P(attn), None, P(l["attn_sub_norm"]), m, nh_l * hd, cfg.num_attention_heads * hd, C.c_float(eps),
                                       P(q8), P(qs), P(qsum), st))
+            mark("sub-norm + quantise (statistics exchange)")
             gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["o"]], None, [comm.partial_ptr])
+            mark("o GEMM")
             reduce_norm_gather(0, qs, l["o"].scale, l["post_attn_norm"])
+            mark("reduce-scatter + residual + norm + all-gather")
             gemm(self.gq, self.gs, self.gsum, [l["gate"], l["up"]], [g, u], None)
+            mark("gate/up GEMM")
             chk(lib.lbk_tp_norm_quant(comm.handle, 3, P(g), P(u), P(l["ffn_sub_norm"]), m, il, I, C.c_float(eps), P(q8), P(qs), P(qsum), st))
+            mark("sub-norm + quantise (statistics exchange)")
             gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["down"]], None, [comm.partial_ptr])
+            mark("down GEMM")
             last = li + 1 == L
             reduce_norm_gather(2 if last else 0, qs, l["down"].scale, self.final_norm if last else self.layers[li + 1]["input_norm"])
+            mark("reduce-scatter + residual + norm + all-gather")
         # the head: this rank's vocabulary rows of the tied embedding (model.rs:370-373), then the greedy token
         head_in = self.gf + (4 * H * (m - 1) if prompt else 0)
         chk(lib.lbk_bf16_linear(h, C.c_void_p(head_in), rows_out, C.c_void_p(_ptr(self.embed) + 2 * H * self.vl * self.rank), self.vl, H, P(logits), st))
@@ -401,6 +472,7 @@ class TpBitNet:
             cache["pos"].add_(m)
         else:
             chk(lib.lbk_advance_pos_seq(h, P(cache["pos"]), None, m, st))
+        mark("head + greedy token")
         cache["host_len"] = [x + need for x in cache["host_len"]]
         return logits, nxt
 

@@ -115,3 +115,16 @@ def test_full_size_fused_group_and_permutation(oracle, ctx, m):
     o3 = ops.ternary_linear_multi(xd[perm].contiguous(), [la, lb])
     assert torch.equal(o3[0], outs[0][perm]) and torch.equal(o3[1], outs[1][perm])
     ctx.check_device_error()
+
+
+def test_int8_peak_probe_is_plausible(ctx):
+    """lbk_int8_peak_probe: the no-load rate of the tensor-core instruction the GEMM is built on. The
+    nominal dense int8 figure of the part is 4500 TOPS; the probe must land within a factor of two of
+    it at 192 and 256 token rows and must not report more at 64 rows than at 256."""
+    r64, r192, r256 = ctx.int8_peak_tops(64, 5000), ctx.int8_peak_tops(192, 5000), ctx.int8_peak_tops(256, 5000)
+    assert 2250.0 < r192 < 9000.0 and 2250.0 < r256 < 9000.0, (r64, r192, r256)
+    assert r64 <= r256 * 1.05
+    ctx.check_device_error()
+    from lemonade_burn_b200 import _lib
+    with pytest.raises(_lib.LbkError):
+        ctx.int8_peak_tops(100, 10)
