@@ -241,7 +241,7 @@ int lbk_tp_reduce_scale(lbk_tp_comm *comm, const float *scale_dev, float wscale,
  *                                slice [m, k_local] of the input, for all m tokens. The mean of squares
  *                                is over all k_full columns and the quantiser's maximum over the whole
  *                                row: two 8-byte exchanges per token inside the kernel. w_dev is the
- *                                slice of the gain. k_local: a multiple of 128, at most 16384.
+ *                                slice of the gain. k_local: a multiple of 128, at most 32768.
  *   (lbk_ternary_gemm_dev writes the slice's int32 dots into lbk_tp_partial_buffer)
  *   lbk_tp_reduce_norm_gather    for this rank's tokens: sum of all ranks' int32 dots (exact), scale
  *                                epilogue with ascale_dev[t] * wscale (gemm.rs:141), xres += that row

@@ -100,26 +100,31 @@ __device__ __forceinline__ uint32_t f32_to_bf16_rn(float v) {  // round to neare
     return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
 }
 
+//
+// Long rows go through in column chunks (`c0`, `ccols`: whole 32-column slices) so that sixteen token
+// rows of a chunk fit in shared memory; the launches of one token group run one after the other on
+// the stream and every chunk after the first adds to what the earlier ones stored (`accumulate`), in
+// chunk order, so the sum has one fixed order.
 __global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w, int rows,
-                                                                  int cols, int m_total, int t0, int xs_stride /* bytes */,
-                                                                  float *__restrict__ out) {
+                                                                  int cols, int m_total, int t0, int xs_stride /* bytes */, int c0, int ccols,
+                                                                  int accumulate, float *__restrict__ out) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
     extern __shared__ __align__(16) uint8_t s_raw[];
     uint8_t *s_hi = s_raw, *s_lo = s_raw + kMmaTok * xs_stride;  // [16 tokens][xs_stride] bf16
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < kMmaTok * (cols >> 1); i += kThreads) {  // two columns per step
-        const int tk = i / (cols >> 1), c = (i - tk * (cols >> 1)) * 2;
+    for (int i = tid; i < kMmaTok * (ccols >> 1); i += kThreads) {  // two columns per step
+        const int tk = i / (ccols >> 1), c = (i - tk * (ccols >> 1)) * 2;
         float2 v = make_float2(0.f, 0.f);
-        if (t0 + tk < m_total) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(t0 + tk) * cols + c);
+        if (t0 + tk < m_total) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(t0 + tk) * cols + c0 + c);
         const uint32_t h0 = f32_to_bf16_rn(v.x), h1 = f32_to_bf16_rn(v.y);
         const uint32_t l0 = f32_to_bf16_rn(v.x - __uint_as_float(h0 << 16)), l1 = f32_to_bf16_rn(v.y - __uint_as_float(h1 << 16));
         *reinterpret_cast<uint32_t *>(s_hi + tk * xs_stride + c * 2) = h0 | (h1 << 16);
         *reinterpret_cast<uint32_t *>(s_lo + tk * xs_stride + c * 2) = l0 | (l1 << 16);
     }
     __syncthreads();
-    const int slices = cols >> 5;
+    const int slices = ccols >> 5;
     const int groups = (rows + 15) >> 4;  // 16 weight rows per warp step
     const int warps_total = gridDim.x * (kThreads / 32);
     const uint8_t *xa = s_hi + g * xs_stride + t * 16, *xb = s_hi + (g + 8) * xs_stride + t * 16;
@@ -127,8 +132,8 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *
     for (int grp = blockIdx.x * (kThreads / 32) + warp; grp < groups; grp += warps_total) {
         const int r0 = grp * 16;
         const int ra = min(r0 + g, rows - 1), rb = min(r0 + 8 + g, rows - 1);  // clamped rows are computed and dropped
-        const uint4 *wa = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(ra) * cols) + t;
-        const uint4 *wb = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(rb) * cols) + t;
+        const uint4 *wa = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(ra) * cols + c0) + t;
+        const uint4 *wb = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(rb) * cols + c0) + t;
         float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
         for (int c = 0; c < slices; ++c) {
@@ -153,8 +158,9 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *
             for (int hh = 0; hh < 2; ++hh) {
                 const int tk = t0 + g + hh * 8;
                 if (tk < m_total) {
-                    if (row < rows) out[static_cast<size_t>(tk) * rows + row] = d[hh * 2];
-                    if (row + 1 < rows) out[static_cast<size_t>(tk) * rows + row + 1] = d[hh * 2 + 1];
+                    float *o = out + static_cast<size_t>(tk) * rows + row;
+                    if (row < rows) o[0] = accumulate ? o[0] + d[hh * 2] : d[hh * 2];
+                    if (row + 1 < rows) o[1] = accumulate ? o[1] + d[hh * 2 + 1] : d[hh * 2 + 1];
                 }
             }
         }
@@ -172,15 +178,23 @@ int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, si
     const int grid = ctx->sm_count * 4;
     // two or more token rows: tensor cores, sixteen rows per pass over W (needs whole 32-column slices
     // and 16-byte aligned rows; anything else takes the FMA kernel below)
-    const int xs_stride = static_cast<int>(cols * 2 + 64);  // +64: the 16-byte loads of two token rows land on distinct banks
+    // rows of more than 3072 columns are cut into chunks of at most that many (whole 32-column slices)
+    constexpr size_t kMaxChunk = 3072;
+    const size_t n_chunks = (cols + kMaxChunk - 1) / kMaxChunk;
+    const size_t chunk = ((cols + n_chunks - 1) / n_chunks + 31) / 32 * 32;
+    const int xs_stride = static_cast<int>(chunk * 2 + 64);  // +64: the 16-byte loads of two token rows land on distinct banks
     if (m >= 2 && (cols & 31) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
         static_cast<size_t>(2 * kMmaTok) * xs_stride <= ctx->smem_optin) {
         const size_t smem = static_cast<size_t>(2 * kMmaTok) * xs_stride;
         LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
         for (size_t t0 = 0; t0 < m; t0 += kMmaTok) {
-            LBK_CUDA(launch_chained(bf16_linear_mma_kernel, dim3(ctx->sm_count), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows),
-                                    static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, out));
-            ctx->launches++;
+            for (size_t c0 = 0; c0 < cols; c0 += chunk) {
+                const size_t cc = cols - c0 < chunk ? cols - c0 : chunk;
+                LBK_CUDA(launch_chained(bf16_linear_mma_kernel, dim3(ctx->sm_count), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows),
+                                        static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
+                                        static_cast<int>(cc), c0 ? 1 : 0, out));
+                ctx->launches++;
+            }
         }
         return LBK_OK;
     }

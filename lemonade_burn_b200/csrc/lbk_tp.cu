@@ -253,8 +253,8 @@ __global__ void __launch_bounds__(256) tp_reduce_scale_kernel(const TpPtrs peers
 // The statistics slots alternate by the parity of the sequence number; a rank can be at most one
 // call ahead of a peer because every call needs every peer's value of that call.
 
-constexpr int kNqThreads = 512;
-constexpr int kNqCache = 8;  // float4 per thread: column slices of up to 16384 columns
+constexpr int kNqThreads = 1024;
+constexpr int kNqCache = 8;  // float4 per thread: column slices of up to 32768 columns
 constexpr int kRgThreads = 1024;
 
 __device__ __forceinline__ float block_sum_f(float v, float *s_red, int nwarps) {

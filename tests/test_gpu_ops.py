@@ -104,11 +104,13 @@ def test_dtype_and_shape_errors(oracle, ctx):
 
 
 @pytest.mark.parametrize("m,rows,cols", [(1, 1000, 2560), (3, 1000, 2560), (4, 1000, 2560), (7, 1000, 2560), (16, 1003, 2560),
-                                         (19, 37, 512), (2, 1000, 2568), (5, 64, 40)])
+                                         (19, 37, 512), (2, 1000, 2568), (5, 64, 40), (20, 530, 8192), (3, 100, 6912), (2, 64, 3104)])
 def test_bf16_linear(oracle, ctx, m, rows, cols):
     """One token row takes the FMA kernel, two or more the tensor-core kernel (activations split into
     two bf16 terms), ragged row counts and more than sixteen token rows included; column counts that
-    are not whole 32-column slices fall back to the FMA kernel."""
+    are not whole 32-column slices fall back to the FMA kernel; rows longer than 3072 columns go
+    through in column chunks that add up in a fixed order (8192: the 70B-shaped head; 3104: two
+    chunks of unequal length)."""
     import torch
     from lemonade_burn_b200 import ops
     g = torch.Generator().manual_seed(m)
