@@ -121,7 +121,9 @@ def test_bf16_linear(oracle, ctx, m, rows, cols):
     for t in range(m):
         ref = oracle.bf16_gemv(bits, x[t].numpy())
         assert np.abs(out[t] - ref).max() < 1e-4  # bf16.rs:113-136 bound
-        assert np.allclose(out[t], ref, rtol=1e-3, atol=1e-5)
+        # and relative to the row's range: the two-term bf16 split of the activations leaves 2^-17 per
+        # product (measured 4e-6 .. 7e-6 of max |out| for 2560 .. 8192 columns)
+        assert np.abs(out[t] - ref).max() <= 1e-5 * np.abs(ref).max()
 
 
 def test_plan_replays_groups(oracle, ctx):
