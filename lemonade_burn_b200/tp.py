@@ -102,6 +102,33 @@ class TpComm:
             self._lib.lbk_tp_region_free(self.ctx.handle, self._mine)
 
 
+class PeerLost(RuntimeError):
+    """A rank of the tensor-parallel group did not show up for a step."""
+
+
+class PeerGuard:
+    """Host-side liveness check between steps. The peer-memory kernels bound their waits and report
+    LBK_ERR_TIMEOUT when a peer never arrives, but by then a step's worth of launches is queued; this
+    check finds a missing rank BEFORE the next launch: every rank posts a key for the step in a
+    key-value store (torch.distributed's TCPStore or any object with set / wait) and waits, with a
+    timeout, for the keys of all ranks. A rank that left (or the store's host that went away) turns into
+    PeerLost on the others, the same rule as the reference's server, where a failing request becomes an
+    error reply and never a dead worker (crates/lb-server/src/main.rs:92-100). A rank leaves only
+    between steps, with none of its kernels in flight."""
+
+    def __init__(self, store, world: int, rank: int, timeout_s: float = 5.0, prefix: str = "lbk/alive"):
+        self.store, self.world, self.rank, self.timeout_s, self.prefix = store, world, rank, timeout_s, prefix
+
+    def arrive(self, step: int) -> None:
+        """Call on every rank before it launches step `step`. Raises PeerLost if a rank is missing."""
+        from datetime import timedelta
+        try:
+            self.store.set(f"{self.prefix}/{step}/{self.rank}", b"1")
+            self.store.wait([f"{self.prefix}/{step}/{r}" for r in range(self.world)], timedelta(seconds=self.timeout_s))
+        except Exception as exc:  # timeout, or the store's host is gone
+            raise PeerLost(f"rank {self.rank}: not every rank of {self.world} arrived for step {step} within {self.timeout_s} s ({type(exc).__name__})") from exc
+
+
 # ---- device-resident layers -------------------------------------------------------------------
 
 class ColumnParallelTernary:

@@ -95,3 +95,109 @@ def test_shard_helpers_reject_bad_cuts():
         tp.shard_rows(packed, 4, 0)
     sl, lc = tp.shard_cols(packed, 384, 3, 1)
     assert lc == 128 and sl.shape == (6, 32)
+
+
+def _token_sharded_worker(rank, world, port, q_out):
+    """The token-sharded form of a row-parallel layer on CPU ranks: int32 partial dots of the column
+    slices, reduce-scatter by token rows (here: integer all-reduce, then the owner keeps its rows),
+    scale epilogue + residual on the owner, all-gather of the owners' rows. Uneven ownership (5 tokens
+    over 2 ranks, 3 over 4 with an empty rank) included."""
+    sys.path.insert(0, str(ROOT))
+    import torch
+    import torch.distributed as dist
+    from lemonade_burn_b200 import tp
+    from oracle import oracle as o
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        ok = True
+        for m in (5, 3, 1):
+            rng = np.random.default_rng(11 + m)
+            rows, cols = 256, 512 * world
+            t = rng.choice(np.array([-1, 0, 1], dtype=np.int8), size=(rows, cols), p=[0.3, 0.4, 0.3])
+            packed = o.pack_matrix(t)
+            x = rng.standard_normal((m, cols)).astype(np.float32)
+            resid = rng.standard_normal((m, rows)).astype(np.float32)
+            wscale = np.float32(33.25)
+            q, s, ssum = o.quantize_acts(x)
+            want = (resid + o.ternary_gemm(packed, cols, wscale, q, s, ssum)).astype(np.float32)
+            sl, lc = tp.shard_cols(packed, cols, world, rank)
+            ql = np.ascontiguousarray(q[:, rank * lc:(rank + 1) * lc])          # every rank quantises with the whole row's scale
+            lsum = ql.astype(np.int32).sum(axis=1).astype(np.int32)
+            part = torch.from_numpy(o.ternary_gemm_i32(np.ascontiguousarray(sl), lc, ql, lsum))
+            dist.all_reduce(part, op=dist.ReduceOp.SUM)
+            t0, cnt = tp.token_range(m, world, rank)
+            inv = (np.float32(1.0) / (s * wscale)).astype(np.float32)
+            mine = (resid[t0:t0 + cnt] + part.numpy()[t0:t0 + cnt].astype(np.float32) * inv[t0:t0 + cnt, None]).astype(np.float32)
+            mt = (m + world - 1) // world
+            pad = np.zeros((mt, rows), np.float32)
+            pad[:cnt] = mine
+            parts = [torch.empty((mt, rows)) for _ in range(world)]
+            dist.all_gather(parts, torch.from_numpy(pad))
+            full = torch.cat(parts, dim=0).numpy()[:m]
+            ok = ok and np.array_equal(full.view(np.uint32), want.view(np.uint32))
+            spans = [tp.token_range(m, world, r) for r in range(world)]
+            ok = ok and sum(c for _, c in spans) == m and all(a + c == spans[i + 1][0] or spans[i + 1][1] == 0 for i, (a, c) in enumerate(spans[:-1]))
+        q_out.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_token_sharded_exchange_is_exact(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_token_sharded_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=120) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert all(ok for _, ok in res), res
+
+
+def _leaving_worker(rank, world, port, q_out):
+    sys.path.insert(0, str(ROOT))
+    import time
+    from datetime import timedelta
+    import torch.distributed as dist
+    from lemonade_burn_b200 import tp
+    store = dist.TCPStore("127.0.0.1", port, world, is_master=(rank == 0), timeout=timedelta(seconds=20))
+    guard = tp.PeerGuard(store, world, rank, timeout_s=1.5)
+    done = 0
+    try:
+        for step in range(4):
+            if rank == 1 and step == 2:
+                q_out.put((rank, "left", done))      # leaves between steps, nothing in flight
+                return
+            guard.arrive(step)
+            done += 1                                  # a step would be launched here
+        q_out.put((rank, "finished", done))
+    except tp.PeerLost as exc:
+        q_out.put((rank, "peer lost", done))
+        time.sleep(0.2)
+
+
+def test_a_rank_that_leaves_between_steps_is_an_error_not_a_hang():
+    """Failure detection on the host: rank 1 of 2 leaves after two steps; rank 0 must find out before
+    launching the third (PeerLost within the guard's timeout), not wait forever."""
+    import time
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_leaving_worker, args=(r, 2, port, q)) for r in range(2)]
+    t0 = time.time()
+    for p in procs:
+        p.start()
+    res = dict((r, (what, n)) for r, what, n in [q.get(timeout=60) for _ in procs])
+    for p in procs:
+        p.join(timeout=30)
+        assert p.exitcode == 0
+    assert res[1] == ("left", 2)
+    assert res[0] == ("peer lost", 2)
+    assert time.time() - t0 < 45
