@@ -116,11 +116,36 @@ def int8_peak(ctx):
 
 def config2_prefill(torch, ops, ctx, device, peak_tops, ms=(64, 256, 1024, 2048), reps=5, per_graph=10):
     """Config 2: prefill ternary GEMM at the BitNet-2B projections, per token count. One call =
-    per-token int8 quantisation kernel + tcgen05 GEMM kernel; timed as CUDA-graph replays."""
+    per-token int8 quantisation kernel + tcgen05 GEMM kernel (`us`, the operator as the decoder calls
+    it on f32 activations); beside it the GEMM alone on rows that are quantised already (`gemm_only_us`:
+    in the decoder the norm in front of a projection writes the quantised rows itself, so this is the
+    projection's cost there). Timed as CUDA-graph replays."""
     import ctypes as C
     from lemonade_burn_b200 import _lib
     g = torch.Generator(device=device).manual_seed(2222)
     out = []
+
+    def timed(call):
+        for _ in range(2):
+            call(torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                for _ in range(per_graph):
+                    call(side.cuda_stream)
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
+
     for rows, cols in ((INTER, HIDDEN), (HIDDEN, INTER)):
         u = torch.rand((4, rows, cols // 4), generator=g, device=device)
         codes = (u > 0.3).to(torch.uint8) + (u > 0.7).to(torch.uint8)
@@ -129,34 +154,29 @@ def config2_prefill(torch, ops, ctx, device, peak_tops, ms=(64, 256, 1024, 2048)
         for m in ms:
             x = torch.randn(m, cols, generator=g, device=device)
             y = torch.empty(m, rows, device=device)
+            q8 = torch.empty((m, cols), dtype=torch.int8, device=device)
+            qs = torch.empty(m, device=device)
+            qsum = torch.empty(m, dtype=torch.int32, device=device)
             wp, _k1 = _lib.ptr_array([lin.weight.handle.value])
             op, _k2 = _lib.ptr_array([y.data_ptr()])
 
             def call(stream):
                 _lib.check(ctx._lib.lbk_ternary_linear_n(ctx.handle, C.c_void_p(x.data_ptr()), m, wp, 1, op, None, C.c_void_p(stream)))
 
-            for _ in range(2):
-                call(torch.cuda.current_stream().cuda_stream)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                with torch.cuda.graph(graph, stream=side):
-                    for _ in range(per_graph):
-                        call(side.cuda_stream)
-            torch.cuda.synchronize()
-            graph.replay()
-            torch.cuda.synchronize()
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            for _ in range(reps):
-                graph.replay()
-            e1.record()
-            torch.cuda.synchronize()
-            us = e0.elapsed_time(e1) * 1e3 / (reps * per_graph)
-            tops = 2.0 * m * rows * cols / us / 1e6
+            def call_gemm(stream):
+                _lib.check(ctx._lib.lbk_ternary_gemm_dev(ctx.handle, wp, 1, C.c_void_p(q8.data_ptr()), C.c_void_p(qs.data_ptr()),
+                                                         C.c_void_p(qsum.data_ptr()), m, op, None, C.c_void_p(stream)))
+
+            us = timed(call)
+            _lib.check(ctx._lib.lbk_quantize_acts_dev(ctx.handle, C.c_void_p(x.data_ptr()), m, cols, C.c_void_p(q8.data_ptr()), C.c_void_p(qs.data_ptr()),
+                                                      C.c_void_p(qsum.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+            us_gemm = timed(call_gemm)
+            ops_n = 2.0 * m * rows * cols
+            tops = ops_n / us / 1e6
             out.append({"k": cols, "n": rows, "m": m, "us": us, "int8_TOPS": tops,
-                        "frac_of_measured_int8_peak": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0})
+                        "frac_of_measured_int8_peak": tops / peak_tops, "frac_of_nominal_4500": tops / 4500.0,
+                        "gemm_only_us": us_gemm, "gemm_only_int8_TOPS": ops_n / us_gemm / 1e6,
+                        "gemm_only_frac_of_measured_int8_peak": ops_n / us_gemm / 1e6 / peak_tops})
     return {"workload": "prefill ternary GEMM, quantise + tcgen05 kernel per call", "peak_TOPS_measured": peak_tops,
             "cases": out}
 

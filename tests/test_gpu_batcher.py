@@ -10,16 +10,16 @@ import pytest
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("nh,kvh,splits", [(8, 2, 4), (4, 4, 3)])
-def test_attention_with_a_position_per_sequence(ctx, nh, kvh, splits):
+@pytest.mark.parametrize("nh,kvh,splits,b", [(8, 2, 4, 3), (4, 4, 3, 3), (8, 2, 4, 9), (8, 1, 1, 12)])
+def test_attention_with_a_position_per_sequence(ctx, nh, kvh, splits, b):
     """lbk_attn_decode_fused_seq (4 query heads per KV head) / lbk_rope_kv_append_seq + lbk_attn_decode_seq
     (one per KV head) with positions 0, 36 and 130 in one batch against RoPE + softmax(qK/sqrt(d))V
     in float64 per sequence; lbk_advance_pos_seq moves only the active ones. Tolerance 1e-5 absolute."""
     import torch
     from lemonade_burn_b200 import _lib
     lib = _lib.load()
-    b, hd, cap = 3, 128, 160
-    posv = [0, 36, 130]
+    hd, cap = 128, 160
+    posv = [0, 36, 130, 63, 64, 65, 1, 159, 100, 17, 128, 5][:b]
     g = torch.Generator().manual_seed(nh)
     q = torch.randn(b, nh, hd, generator=g)
     kn = torch.randn(b, kvh, hd, generator=g)
@@ -65,11 +65,12 @@ def test_attention_with_a_position_per_sequence(ctx, nh, kvh, splits):
             w = np.exp(sc - sc.max())
             w /= w.sum()
             assert np.abs(got[bi, h] - w @ vf[kv]).max() < 1e-5
-    active = torch.tensor([1, 0, 1], dtype=torch.int32).cuda()
+    act = ([1, 0, 1] + [0] * b)[:b]
+    active = torch.tensor(act, dtype=torch.int32).cuda()
     _lib.check(lib.lbk_advance_pos_seq(ctx.handle, pd.data_ptr(), active.data_ptr(), b, st))
-    assert pd.cpu().tolist() == [1, 36, 131]
+    assert pd.cpu().tolist() == [p + a for p, a in zip(posv, act)]
     _lib.check(lib.lbk_advance_pos_seq(ctx.handle, pd.data_ptr(), None, b, st))
-    assert pd.cpu().tolist() == [2, 37, 132]
+    assert pd.cpu().tolist() == [p + a + 1 for p, a in zip(posv, act)]
     ctx.check_device_error()
 
 

@@ -269,17 +269,21 @@ def test_projection_with_input_transform(oracle, ctx, m, cols):
     ctx.check_device_error()
 
 
-@pytest.mark.parametrize("total,splits,nh,kvh", [(1, 1, 8, 2), (37, 4, 8, 2), (1000, 32, 8, 2), (4097, 130, 20, 5), (300, 256, 16, 2)])
-def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh):
+@pytest.mark.parametrize("total,splits,nh,kvh,b", [(1, 1, 8, 2, 2), (37, 4, 8, 2, 2), (1000, 32, 8, 2, 2), (4097, 130, 20, 5, 2), (300, 256, 16, 2, 2),
+                                                  (1, 1, 8, 2, 9), (37, 4, 8, 2, 8), (1000, 3, 16, 2, 9), (1089, 1, 8, 1, 10), (4097, 130, 20, 5, 8),
+                                                  (300, 256, 16, 2, 8), (130, 2, 8, 2, 16)])
+def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh, b):
     """lbk_attn_decode_fused (RoPE on q and the new k, append of the new K/V row, slices, merge by the
     last block) against RoPE + softmax(qK/sqrt(d))V in float64, two calls in a row on the same
     buffers (the merge counters must come back to zero). The appended rows must be the bf16 of the
-    rotated k and of v. Tolerance 1e-5 absolute on outputs of magnitude <= 1."""
+    rotated k and of v. Eight sequences and more take the tensor-core kernel (whole-chunk slices, empty
+    slices when there are more slices than chunks, one slice written straight to the output).
+    Tolerance 1e-5 absolute on outputs of magnitude <= 1."""
     import torch
     from lemonade_burn_b200 import _lib
     lib = _lib.load()
     assert lib.lbk_attn_decode_fused_supported(nh, kvh, 128, splits)
-    b, hd, cap = 2, 128, max(total, 8)
+    hd, cap = 128, max(total, 8)
     g = torch.Generator().manual_seed(total + nh)
     q = torch.randn(b, nh, hd, generator=g)
     kn = torch.randn(b, kvh, hd, generator=g)
