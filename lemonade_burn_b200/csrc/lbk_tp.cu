@@ -24,6 +24,7 @@
 #include <cstring>
 
 #include "lbk_internal.cuh"
+#include "lbk_ptx.cuh"
 
 namespace lbk {
 
@@ -328,6 +329,12 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
     __shared__ float s_red[kNqThreads / 32];
     __shared__ int s_redi[kNqThreads / 32];
     __shared__ float s_bcast;
+    // Launched with programmatic stream serialisation: the kernel behind this one (the row-parallel
+    // GEMM) may be scheduled now and stream its first weight tiles while this one runs; it waits for
+    // this grid's results itself. Everything this kernel reads was written by kernels that are
+    // complete once the wait below returns.
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     TpRegion *me = peers.r[rank];
     const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->nq_seq);
@@ -420,6 +427,8 @@ struct RgArgs {
 __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const TpPtrs peers, const RgArgs a) {
     __shared__ float s_red[kRgThreads / 32];
     __shared__ int s_redi[kRgThreads / 32];
+    ptx::pdl_trigger();  // the column-parallel GEMM behind this kernel may start fetching its weights
+    ptx::pdl_wait();     // the partial dots (the GEMM before this kernel) are complete from here on
     const int tid = threadIdx.x, world = a.world, rank = a.rank, H = a.hidden;
     TpRegion *me = peers.r[rank];
     const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->rg_seq);
@@ -525,11 +534,12 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
     // last says so to every rank and then waits until every peer has said the same; the others leave
     // at once. The kernel ends when that CTA ends, so whatever follows in the stream finds all tokens'
     // rows in this rank's region, and no CTA waits for a peer while CTAs of its own grid still have
-    // to be scheduled.
-    __threadfence_system();
+    // to be scheduled. One fence per CTA: the block barrier orders every thread's stores before
+    // thread 0's fence, and the fence is cumulative.
     __syncthreads();
     __shared__ int s_last;
     if (tid == 0) {
+        __threadfence_system();
         s_last = atomicAdd(&me->rg_written, 1u) == gridDim.x - 1;
         if (s_last) me->rg_written = 0;
     }
@@ -567,6 +577,8 @@ __device__ __forceinline__ unsigned int ordered_bits(float f) {
 }
 __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ logits, const int32_t *__restrict__ idx_local,
                                                         int m, int vl, int32_t *__restrict__ next, int *err_word, uint32_t wait_limit) {
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
     TpRegion *me = peers.r[rank];
     const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->am_seq);
     const int par = seq & 1, tid = threadIdx.x;
@@ -576,10 +588,9 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpPtrs peers, int
         const unsigned long long key = (static_cast<unsigned long long>(ordered_bits(logits[static_cast<size_t>(t) * vl + li])) << 32) | (~gi);
         for (int p = 0; p < world; ++p) peers.r[p]->best[par][rank][t] = key;
     }
-    __threadfence_system();
     __syncthreads();
     if (tid < world) {
-        __threadfence_system();
+        __threadfence_system();  // cumulative over the barrier: every thread's keys are out before the flag
         *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->am_ready[rank][0]) = seq;
         volatile unsigned int *flag = &me->am_ready[tid][0];
         uint32_t polls = 0;
@@ -774,11 +785,11 @@ int lbk_tp_norm_quant(lbk_tp_comm *t, int pre, const float *x_dev, const float *
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const dim3 grid(static_cast<unsigned>(m)), block(kNqThreads);
     if (pre == LBK_PRE_RMS)
-        tp_norm_quant_kernel<LBK_PRE_RMS><<<grid, block, 0, st>>>(ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), static_cast<int>(k_full), eps,
-                                                                   q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit);
+        LBK_CUDA(launch_chained(tp_norm_quant_kernel<LBK_PRE_RMS>, grid, block, 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local),
+                                static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
     else
-        tp_norm_quant_kernel<LBK_PRE_RELU2_MUL_RMS><<<grid, block, 0, st>>>(ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), static_cast<int>(k_full),
-                                                                             eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit);
+        LBK_CUDA(launch_chained(tp_norm_quant_kernel<LBK_PRE_RELU2_MUL_RMS>, grid, block, 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev,
+                                static_cast<int>(k_local), static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
@@ -813,7 +824,7 @@ int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev
     a.err_word = tc->ctx->err_word;
     a.wait_limit = tc->wait_limit;
     const int t0 = a.rank * a.mt, own = a.m - t0 < 0 ? 0 : (a.m - t0 < a.mt ? a.m - t0 : a.mt);
-    tp_reduce_norm_gather_kernel<<<own > 0 ? own : 1, kRgThreads, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), a);
+    LBK_CUDA(launch_chained(tp_reduce_norm_gather_kernel, dim3(static_cast<unsigned>(own > 0 ? own : 1)), dim3(kRgThreads), 0, static_cast<cudaStream_t>(stream), ptrs_of(tc), a));
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
@@ -830,8 +841,8 @@ int lbk_tp_argmax(lbk_tp_comm *t, const float *logits_local_dev, const int32_t *
     if (m == 0 || m > kTpMaxRows) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_argmax takes 1..%d token rows (got %zu)", kTpMaxRows, m);
     if (!logits_local_dev || !idx_local_dev || !next_dev || vocab_local == 0) return fail(LBK_ERR_INVALID, "lbk_tp_argmax: null buffer or empty slice");
     LBK_CUDA(cudaSetDevice(tc->ctx->device));
-    tp_argmax_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(ptrs_of(tc), tc->world, tc->rank, logits_local_dev, idx_local_dev, static_cast<int>(m),
-                                                                      static_cast<int>(vocab_local), next_dev, tc->ctx->err_word, tc->wait_limit);
+    LBK_CUDA(launch_chained(tp_argmax_kernel, dim3(1), dim3(1024), 0, static_cast<cudaStream_t>(stream), ptrs_of(tc), tc->world, tc->rank, logits_local_dev, idx_local_dev,
+                            static_cast<int>(m), static_cast<int>(vocab_local), next_dev, tc->ctx->err_word, tc->wait_limit));
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
