@@ -283,7 +283,19 @@ def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
     res = []
     with tempfile.TemporaryDirectory() as d:
         model.save_checkpoint(d, cfg, model.random_checkpoint(cfg, 11))
+
+        def rss_kb(field):
+            for line in open("/proc/self/status"):
+                if line.startswith(field):
+                    return int(line.split()[1])
+            return 0
+
+        rss0 = rss_kb("VmRSS:")
         nat = model.NativeBitNet(d, ctx)
+        loader = nat.load_stats()
+        loader.update(file_bytes=os.path.getsize(os.path.join(d, model.FILE_NAME)), host_rss_growth_bytes=(rss_kb("VmRSS:") - rss0) * 1024,
+                      GBps=loader["bytes_read"] / loader["seconds"] / 1e9,
+                      note="file -> two 32 MiB pinned buffers -> device; the reference's loader peaks at twice the model in host memory")
         rng = np.random.default_rng(5)
         cache = nat.new_cache(1, max(lengths) + 64)
         for n in lengths:
@@ -299,7 +311,7 @@ def config3_prompt(torch, ctx, lengths=(128, 1024, 2048), reps=3):
             res.append({"prompt_tokens": n, "ms": best * 1e3, "tok_per_s": n / best, "next_token": int(np.argmax(logits))})
         serving = batcher_case(torch, nat, rng, cfg)
         nat.close()
-    return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res, "batcher": serving}
+    return {"workload": "BitNet-2B4T-architecture prompt pass, native runtime, random init", "cases": res, "batcher": serving, "loader": loader}
 
 
 def batcher_case(torch, nat, rng, cfg, slots=16, requests=48, prompt=128, new_tokens=64):

@@ -105,16 +105,20 @@ __device__ __forceinline__ uint32_t f32_to_bf16_rn(float v) {  // round to neare
 // rows of a chunk fit in shared memory; the launches of one token group run one after the other on
 // the stream and every chunk after the first adds to what the earlier ones stored (`accumulate`), in
 // chunk order, so the sum has one fixed order.
-__global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w, int rows,
-                                                                  int cols, int m_total, int t0, int xs_stride /* bytes */, int c0, int ccols,
-                                                                  int accumulate, float *__restrict__ out) {
+constexpr int kMmaThreads = 512;  // sixteen warps: twice the loads in flight per SM of the eight the FMA kernel uses
+// TT = token tiles of 16 rows per pass over W: 1 (2..16 rows) or 2 (17 rows and more: half the passes)
+template <int TT>
+__global__ void __launch_bounds__(kMmaThreads) bf16_linear_mma_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w, int rows,
+                                                                     int cols, int m_total, int t0, int xs_stride /* bytes */, int c0, int ccols,
+                                                                     int accumulate, float *__restrict__ out) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
     extern __shared__ __align__(16) uint8_t s_raw[];
-    uint8_t *s_hi = s_raw, *s_lo = s_raw + kMmaTok * xs_stride;  // [16 tokens][xs_stride] bf16
+    constexpr int kTokRows = TT * kMmaTok;
+    uint8_t *s_hi = s_raw, *s_lo = s_raw + kTokRows * xs_stride;  // [16 TT tokens][xs_stride] bf16
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < kMmaTok * (ccols >> 1); i += kThreads) {  // two columns per step
+    for (int i = tid; i < kTokRows * (ccols >> 1); i += kMmaThreads) {  // two columns per step
         const int tk = i / (ccols >> 1), c = (i - tk * (ccols >> 1)) * 2;
         float2 v = make_float2(0.f, 0.f);
         if (t0 + tk < m_total) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(t0 + tk) * cols + c0 + c);
@@ -126,41 +130,53 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_mma_kernel(const float *
     __syncthreads();
     const int slices = ccols >> 5;
     const int groups = (rows + 15) >> 4;  // 16 weight rows per warp step
-    const int warps_total = gridDim.x * (kThreads / 32);
+    const int warps_total = gridDim.x * (kMmaThreads / 32);
     const uint8_t *xa = s_hi + g * xs_stride + t * 16, *xb = s_hi + (g + 8) * xs_stride + t * 16;
-    const size_t lo_off = static_cast<size_t>(kMmaTok) * xs_stride;
-    for (int grp = blockIdx.x * (kThreads / 32) + warp; grp < groups; grp += warps_total) {
+    const size_t lo_off = static_cast<size_t>(kTokRows) * xs_stride;
+    const size_t tile_off = static_cast<size_t>(kMmaTok) * xs_stride;
+    for (int grp = blockIdx.x * (kMmaThreads / 32) + warp; grp < groups; grp += warps_total) {
         const int r0 = grp * 16;
         const int ra = min(r0 + g, rows - 1), rb = min(r0 + 8 + g, rows - 1);  // clamped rows are computed and dropped
         const uint4 *wa = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(ra) * cols + c0) + t;
         const uint4 *wb = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(rb) * cols + c0) + t;
-        float d0[4] = {0.f, 0.f, 0.f, 0.f}, d1[4] = {0.f, 0.f, 0.f, 0.f};
+        float d0[TT][4], d1[TT][4];
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) d0[tt][e] = d1[tt][e] = 0.f;
 #pragma unroll 4
         for (int c = 0; c < slices; ++c) {
             const uint4 va = __ldcs(wa + c * 4), vb = __ldcs(wb + c * 4);  // streamed once
-            const uint4 h0 = *reinterpret_cast<const uint4 *>(xa + c * 64), h1 = *reinterpret_cast<const uint4 *>(xb + c * 64);
-            const uint4 l0 = *reinterpret_cast<const uint4 *>(xa + lo_off + c * 64), l1 = *reinterpret_cast<const uint4 *>(xb + lo_off + c * 64);
-            mma_bf16(d0, h0.x, h1.x, h0.y, h1.y, va.x, va.y);
-            mma_bf16(d0, h0.z, h1.z, h0.w, h1.w, va.z, va.w);
-            mma_bf16(d0, l0.x, l1.x, l0.y, l1.y, va.x, va.y);
-            mma_bf16(d0, l0.z, l1.z, l0.w, l1.w, va.z, va.w);
-            mma_bf16(d1, h0.x, h1.x, h0.y, h1.y, vb.x, vb.y);
-            mma_bf16(d1, h0.z, h1.z, h0.w, h1.w, vb.z, vb.w);
-            mma_bf16(d1, l0.x, l1.x, l0.y, l1.y, vb.x, vb.y);
-            mma_bf16(d1, l0.z, l1.z, l0.w, l1.w, vb.z, vb.w);
+#pragma unroll
+            for (int tt = 0; tt < TT; ++tt) {
+                const uint8_t *pa = xa + tt * tile_off + c * 64, *pb = xb + tt * tile_off + c * 64;
+                const uint4 h0 = *reinterpret_cast<const uint4 *>(pa), h1 = *reinterpret_cast<const uint4 *>(pb);
+                const uint4 l0 = *reinterpret_cast<const uint4 *>(pa + lo_off), l1 = *reinterpret_cast<const uint4 *>(pb + lo_off);
+                mma_bf16(d0[tt], h0.x, h1.x, h0.y, h1.y, va.x, va.y);
+                mma_bf16(d0[tt], h0.z, h1.z, h0.w, h1.w, va.z, va.w);
+                mma_bf16(d0[tt], l0.x, l1.x, l0.y, l1.y, va.x, va.y);
+                mma_bf16(d0[tt], l0.z, l1.z, l0.w, l1.w, va.z, va.w);
+                mma_bf16(d1[tt], h0.x, h1.x, h0.y, h1.y, vb.x, vb.y);
+                mma_bf16(d1[tt], h0.z, h1.z, h0.w, h1.w, vb.z, vb.w);
+                mma_bf16(d1[tt], l0.x, l1.x, l0.y, l1.y, vb.x, vb.y);
+                mma_bf16(d1[tt], l0.z, l1.z, l0.w, l1.w, vb.z, vb.w);
+            }
         }
         // D[token][row]: lane (g, t) holds tokens g, g+8 and rows 2t, 2t+1 of each 8-row half
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const float *d = half ? d1 : d0;
-            const int row = r0 + half * 8 + 2 * t;
+        for (int tt = 0; tt < TT; ++tt) {
 #pragma unroll
-            for (int hh = 0; hh < 2; ++hh) {
-                const int tk = t0 + g + hh * 8;
-                if (tk < m_total) {
-                    float *o = out + static_cast<size_t>(tk) * rows + row;
-                    if (row < rows) o[0] = accumulate ? o[0] + d[hh * 2] : d[hh * 2];
-                    if (row + 1 < rows) o[1] = accumulate ? o[1] + d[hh * 2 + 1] : d[hh * 2 + 1];
+            for (int half = 0; half < 2; ++half) {
+                const float *d = half ? d1[tt] : d0[tt];
+                const int row = r0 + half * 8 + 2 * t;
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int tk = t0 + tt * kMmaTok + g + hh * 8;
+                    if (tk < m_total) {
+                        float *o = out + static_cast<size_t>(tk) * rows + row;
+                        if (row < rows) o[0] = accumulate ? o[0] + d[hh * 2] : d[hh * 2];
+                        if (row + 1 < rows) o[1] = accumulate ? o[1] + d[hh * 2 + 1] : d[hh * 2 + 1];
+                    }
                 }
             }
         }
@@ -178,21 +194,29 @@ int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, si
     const int grid = ctx->sm_count * 4;
     // two or more token rows: tensor cores, sixteen rows per pass over W (needs whole 32-column slices
     // and 16-byte aligned rows; anything else takes the FMA kernel below)
-    // rows of more than 3072 columns are cut into chunks of at most that many (whole 32-column slices)
-    constexpr size_t kMaxChunk = 3072;
-    const size_t n_chunks = (cols + kMaxChunk - 1) / kMaxChunk;
+    // Rows go through in column chunks (whole 32-column slices) sized so that the staged token rows fit
+    // in shared memory: 16 token rows per pass over W with chunks of at most 3072 columns; from 17 rows
+    // on, 32 token rows per pass with chunks of at most 1536 (half the passes over W).
+    const int tt = m > static_cast<size_t>(kMmaTok) ? 2 : 1;
+    const size_t max_chunk = tt == 2 ? 1536 : 3072;
+    const size_t n_chunks = (cols + max_chunk - 1) / max_chunk;
     const size_t chunk = ((cols + n_chunks - 1) / n_chunks + 31) / 32 * 32;
     const int xs_stride = static_cast<int>(chunk * 2 + 64);  // +64: the 16-byte loads of two token rows land on distinct banks
-    if (m >= 2 && (cols & 31) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 &&
-        static_cast<size_t>(2 * kMmaTok) * xs_stride <= ctx->smem_optin) {
-        const size_t smem = static_cast<size_t>(2 * kMmaTok) * xs_stride;
-        LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        for (size_t t0 = 0; t0 < m; t0 += kMmaTok) {
+    const size_t smem = static_cast<size_t>(2 * tt * kMmaTok) * xs_stride;
+    if (m >= 2 && (cols & 31) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 && smem <= ctx->smem_optin) {
+        if (tt == 2) LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        else LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+        for (size_t t0 = 0; t0 < m; t0 += static_cast<size_t>(tt) * kMmaTok) {
             for (size_t c0 = 0; c0 < cols; c0 += chunk) {
                 const size_t cc = cols - c0 < chunk ? cols - c0 : chunk;
-                LBK_CUDA(launch_chained(bf16_linear_mma_kernel, dim3(ctx->sm_count), dim3(kThreads), smem, stream, x, w, static_cast<int>(rows),
-                                        static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
-                                        static_cast<int>(cc), c0 ? 1 : 0, out));
+                if (tt == 2)
+                    LBK_CUDA(launch_chained(bf16_linear_mma_kernel<2>, dim3(ctx->sm_count), dim3(kMmaThreads), smem, stream, x, w, static_cast<int>(rows),
+                                            static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
+                                            static_cast<int>(cc), c0 ? 1 : 0, out));
+                else
+                    LBK_CUDA(launch_chained(bf16_linear_mma_kernel<1>, dim3(ctx->sm_count), dim3(kMmaThreads), smem, stream, x, w, static_cast<int>(rows),
+                                            static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
+                                            static_cast<int>(cc), c0 ? 1 : 0, out));
                 ctx->launches++;
             }
         }

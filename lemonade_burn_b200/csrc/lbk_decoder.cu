@@ -702,7 +702,7 @@ __global__ void __launch_bounds__(256) attn_prompt_mma_kernel(const float *__res
 // (attn_combine_kernel merges the slices), or the finished rows in `out` when there is one slice.
 constexpr int kDmWarps = 4;
 constexpr int kDmStage = 2 * kPfKeys * kPfRow;              // one staged chunk: 64 keys, then 64 values
-constexpr int kDmQ = 2 * 16 * kPfRow;                       // the group's queries: hi and lo, 16 rows each
+constexpr int kDmQ = 2 * 8 * kPfRow;                        // the group's queries: hi and lo, 8 rows each (a group has at most 8 heads)
 constexpr int kDmSmem = 2 * kDmStage + kDmQ;
 constexpr int kDmMergeRow = kHd + 4;                        // floats per (warp, head) in the merge area (aliases stage 0)
 static_assert(kDmWarps * 8 * kDmMergeRow * 4 <= kDmStage, "the merge area must fit in a stage");
@@ -741,7 +741,7 @@ __global__ void __launch_bounds__(kDmWarps * 32) attn_decode_mma_kernel(const fl
         __threadfence();  // the asynchronous copies below read the row back through L2
     }
     // the group's queries: RoPE, the 1/sqrt(d) of the scores, split into two bf16 terms; rows past the group are zero
-    for (int r = warp; r < 16; r += kDmWarps) {
+    for (int r = warp; r < 8; r += kDmWarps) {
         float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
         if (r < group) {
             const float *qh = q_raw + (static_cast<size_t>(b) * nh + kh * group + r) * kHd;
@@ -754,11 +754,13 @@ __global__ void __launch_bounds__(kDmWarps * 32) attn_decode_mma_kernel(const fl
         }
         const float hx = bf16_round(x.x), hy = bf16_round(x.y), hz = bf16_round(x.z), hw = bf16_round(x.w);
         *reinterpret_cast<uint2 *>(s_q + r * kPfRow + lane * 8) = make_uint2(pack_bf16(hx, hy), pack_bf16(hz, hw));
-        *reinterpret_cast<uint2 *>(s_q + (16 + r) * kPfRow + lane * 8) = make_uint2(pack_bf16(x.x - hx, x.y - hy), pack_bf16(x.z - hz, x.w - hw));
+        *reinterpret_cast<uint2 *>(s_q + (8 + r) * kPfRow + lane * 8) = make_uint2(pack_bf16(x.x - hx, x.y - hy), pack_bf16(x.z - hz, x.w - hw));
     }
     __syncthreads();  // the new row is in the cache and the queries are in shared memory
-    const uint32_t q_hi = ptx::smem_u32(s_q) + ((lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
-    const uint32_t q_lo = q_hi + 16 * kPfRow;
+    // Only rows 0..7 of the 16-row tile exist: the lanes that would address rows 8..15 read rows 0..7
+    // again and the fragments of rows g + 8 (registers 1 and 3) are cleared after the load.
+    const uint32_t q_hi = ptx::smem_u32(s_q) + (lane & 7) * kPfRow + (lane >> 4) * 16;
+    const uint32_t q_lo = q_hi + 8 * kPfRow;
     const uint32_t k_lane0 = ptx::smem_u32(s_kv) + (warp * 16 + (lane & 7)) * kPfRow + (lane >> 3) * 16;
     const uint32_t v_lane0 = ptx::smem_u32(s_kv) + kPfKeys * kPfRow + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * kPfRow + (lane >> 4) * 16;
     auto stage = [&](int buf, int pc) {
@@ -803,6 +805,7 @@ __global__ void __launch_bounds__(kDmWarps * 32) attn_decode_mma_kernel(const fl
             ptx::ldmatrix_x4(al0, q_lo + kp * 64);
             ptx::ldmatrix_x4(ah1, q_hi + kp * 64 + 32);
             ptx::ldmatrix_x4(al1, q_lo + kp * 64 + 32);
+            ah0[1] = ah0[3] = al0[1] = al0[3] = ah1[1] = ah1[3] = al1[1] = al1[3] = 0u;
 #pragma unroll
             for (int j = 0; j < 2; ++j) {
                 uint32_t bb[4];
