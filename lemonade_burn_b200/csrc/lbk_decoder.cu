@@ -1358,6 +1358,12 @@ static int attn_decode_fused_impl(lbk_ctx *c, const float *q_dev, const float *k
     // Eight sequences and more: the tensor-core kernel (one pass over the staged rows for all query
     // heads of a group); below that the step is a latency chain and the staged kernel's shape is kept.
     if (b >= 8) {
+        // Fewer, longer slices than the caller's count when the batch alone fills the GPU: a block's fixed
+        // work (queries, merge, partial results) is then spread over several 64-key chunks and the two
+        // stages overlap. About four waves of three blocks per SM; the scratch layout follows the count used.
+        const size_t want = (12 * static_cast<size_t>(ctx->sm_count) + b * kv_heads - 1) / (b * kv_heads);
+        if (want < splits) splits = want < 1 ? 1 : want;
+        grid = dim3(static_cast<unsigned>(splits), static_cast<unsigned>(kv_heads), static_cast<unsigned>(b));
         static bool attr_set = false;  // the same value for every call; setting it twice is harmless
         if (!attr_set) {
             LBK_CUDA(cudaFuncSetAttribute(attn_decode_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDmSmem));

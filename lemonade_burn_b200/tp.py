@@ -430,9 +430,7 @@ class TpBitNet:
         g = self._buf("g", (m, il)); u = self._buf("u", (m, il))
         q8 = self._buf("q8", (m, max(nh_l * hd, il)), torch.int8)
         qs, qsum = self._buf("qs", (m,)), self._buf("qsum", (m,), torch.int32)
-        # slices of the key range per (sequence, KV head): enough blocks to fill the SMs a few times over,
-        # no more (64 sequences x 8 KV heads need 4 slices, not the 34 a single sequence would get)
-        splits = max(1, min(attention_splits(cache["cap"]), -(-1776 // (m * kvh_l))))
+        splits = attention_splits(cache["cap"])  # an upper bound: the batched kernel takes fewer, longer slices when the batch fills the GPU
         scratch = self._buf("attn_part", (m * nh_l * splits * (hd + 4),))
         counters = self._buf("attn_counters", (m * kvh_l,), torch.int32)
         rows_out = 1 if prompt else m
