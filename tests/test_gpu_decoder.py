@@ -271,7 +271,7 @@ def test_projection_with_input_transform(oracle, ctx, m, cols):
 
 @pytest.mark.parametrize("total,splits,nh,kvh,b", [(1, 1, 8, 2, 2), (37, 4, 8, 2, 2), (1000, 32, 8, 2, 2), (4097, 130, 20, 5, 2), (300, 256, 16, 2, 2),
                                                   (1, 1, 8, 2, 9), (37, 4, 8, 2, 8), (1000, 3, 16, 2, 9), (1089, 1, 8, 1, 10), (4097, 130, 20, 5, 8),
-                                                  (300, 256, 16, 2, 8), (130, 2, 8, 2, 16)])
+                                                  (300, 256, 16, 2, 8), (130, 2, 8, 2, 16), (4097, 130, 20, 5, 16)])
 def test_fused_attention_against_numpy(ctx, total, splits, nh, kvh, b):
     """lbk_attn_decode_fused (RoPE on q and the new k, append of the new K/V row, slices, merge by the
     last block) against RoPE + softmax(qK/sqrt(d))V in float64, two calls in a row on the same
