@@ -242,6 +242,8 @@ int lbk_check_device_error(lbk_ctx *c) {
     LBK_CUDA(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
     if (word != 0) {
         LBK_CUDA(cudaMemset(ctx->err_word, 0, sizeof(int)));
+        // a launch that gave up may have left partial sums in the split-K buffer, which is zero at rest
+        if (ctx->gemm_acc) LBK_CUDA(cudaMemset(ctx->gemm_acc, 0, kGemmAccBytes));
         return device_error_status(word);
     }
     return LBK_OK;
@@ -550,6 +552,7 @@ static int host_group(Ctx *ctx, const lbk_weight *const *ws, size_t n, size_t m,
     LBK_CUDA(cudaMemcpy(&word, ctx->err_word, sizeof(int), cudaMemcpyDeviceToHost));
     if (word) {
         LBK_CUDA(cudaMemset(ctx->err_word, 0, sizeof(int)));
+        if (ctx->gemm_acc) LBK_CUDA(cudaMemset(ctx->gemm_acc, 0, kGemmAccBytes));
         return device_error_status(word);
     }
     return LBK_OK;

@@ -508,13 +508,16 @@ int gemm_init(Ctx *ctx) {
     LBK_TRY(init_one<192>(ctx));
     LBK_TRY(init_one<64>(ctx));
     LBK_CUDA(cudaMalloc(&ctx->gemm_acc, kGemmAccBytes));
+    LBK_CUDA(cudaMemset(ctx->gemm_acc, 0, kGemmAccBytes));  // kept zero between launches: the scaling kernel zeroes what it reads
     return LBK_OK;
 }
 
 // Parts to cut every tile's K blocks into. A launch with few tiles against the SM count (small
 // token batches, tensor-parallel shards) or with a ragged last round leaves SMs idle; parts add
 // their int32 sums into a zeroed buffer and a small kernel scales them afterwards. Cost model in
-// K-block times of one CTA (about 500 cycles); the zeroing and the scaling kernel are charged as 30.
+// K-block times of one CTA (about 500 cycles); the parts' atomic adds, the scaling launch and its
+// traffic are charged as 30 (14 was tried once the zeroing launches were gone: the 70B-shaped gate/up
+// projection at 64 token rows then split in two and took twice as long, 14.7 MB of sums added twice).
 static int choose_ksplit(int tiles, int k_blocks, int sms, int *kb_part) {
     int best = 1;
     long long best_cost = static_cast<long long>((tiles + sms - 1) / sms) * k_blocks;
@@ -606,11 +609,12 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
                 const size_t bytes = g.m * g.w[i]->rows * sizeof(int32_t);
                 if (g.iout[i]) {
                     p.acc[i] = g.iout[i];
+                    LBK_CUDA(cudaMemsetAsync(p.acc[i], 0, bytes, stream));  // the caller's buffer holds whatever it held
                 } else {
+                    // the context's buffer is zero at rest (launch_scale_epilogue_group zeroes what it reads)
                     p.acc[i] = reinterpret_cast<int32_t *>(reinterpret_cast<char *>(ctx->gemm_acc) + off);
                     off += (bytes + 255) / 256 * 256;
                 }
-                LBK_CUDA(cudaMemsetAsync(p.acc[i], 0, bytes, stream));
             }
         }
     }
@@ -636,9 +640,22 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     }
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;
-    if (p.ksplit > 1) {
-        for (int i = 0; i < g.n; ++i)
-            if (g.out[i]) LBK_TRY(launch_scale_epilogue(ctx, p.acc[i], g.qscale, g.w[i]->scale, g.m, g.w[i]->rows, g.out[i], stream));
+    if (p.ksplit > 1) {  // one launch scales every matrix of the group (and zeroes the context's sums again)
+        int32_t *dots[LBK_MAX_GROUP];
+        float *outs[LBK_MAX_GROUP];
+        float ws[LBK_MAX_GROUP];
+        int rows[LBK_MAX_GROUP];
+        bool clean[LBK_MAX_GROUP];
+        bool any = false;
+        for (int i = 0; i < g.n; ++i) {
+            dots[i] = p.acc[i];
+            outs[i] = g.out[i];
+            ws[i] = g.w[i]->scale;
+            rows[i] = static_cast<int>(g.w[i]->rows);
+            clean[i] = g.iout[i] == nullptr;
+            any = any || g.out[i] != nullptr || clean[i];
+        }
+        if (any) LBK_TRY(launch_scale_epilogue_group(ctx, g.n, dots, outs, ws, rows, clean, g.qscale, g.m, stream));
     }
     return LBK_OK;
 }

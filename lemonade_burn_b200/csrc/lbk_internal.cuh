@@ -137,6 +137,9 @@ int launch_quantize_ex(Ctx *ctx, const float *x, size_t m, size_t k, int8_t *q, 
 int launch_scale_epilogue(Ctx *ctx, const int32_t *dots, const float *ascale, float wscale, size_t m, size_t rows,
                           float *out, cudaStream_t stream);
 
+int launch_scale_epilogue_group(Ctx *ctx, int n, int32_t *const *dots, float *const *outs, const float *wscale, const int *rows, const bool *clean,
+                                const float *ascale, size_t m, cudaStream_t stream);
+
 // tcgen05 int8 GEMM on quantised inputs (any m).
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
 

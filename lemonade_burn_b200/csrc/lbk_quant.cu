@@ -137,7 +137,52 @@ __global__ void __launch_bounds__(256) scale_epilogue_kernel(const int32_t *__re
     }
 }
 
+// The same for up to LBK_MAX_GROUP matrices that share the token rows, in one launch (blockIdx.y is
+// the matrix). `clean`: the sums live in the context's own accumulation buffer, which is kept zero
+// between launches: every word is zeroed again once it has been read.
+struct EpilogueGroup {
+    int32_t *dots[LBK_MAX_GROUP];
+    float *out[LBK_MAX_GROUP];
+    float wscale[LBK_MAX_GROUP];
+    int rows[LBK_MAX_GROUP];
+    int clean[LBK_MAX_GROUP];
+};
+__global__ void __launch_bounds__(256) scale_epilogue_group_kernel(const EpilogueGroup g, const float *__restrict__ ascale, int m) {
+    const int mat = blockIdx.y, rows = g.rows[mat];
+    int32_t *dots = g.dots[mat];
+    float *out = g.out[mat];
+    if (!out) return;
+    const float ws = g.wscale[mat];
+    const size_t total = static_cast<size_t>(m) * rows;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float inv = __fdiv_rn(1.0f, __fmul_rn(ascale[i / rows], ws));
+        out[i] = __fmul_rn(__int2float_rn(dots[i]), inv);
+        if (g.clean[mat]) dots[i] = 0;
+    }
+}
+
 }  // namespace
+
+int launch_scale_epilogue_group(Ctx *ctx, int n, int32_t *const *dots, float *const *outs, const float *wscale, const int *rows, const bool *clean,
+                                const float *ascale, size_t m, cudaStream_t stream) {
+    EpilogueGroup g{};
+    size_t most = 0;
+    for (int i = 0; i < n; ++i) {
+        g.dots[i] = dots[i];
+        g.out[i] = outs[i];
+        g.wscale[i] = wscale[i];
+        g.rows[i] = rows[i];
+        g.clean[i] = clean[i] ? 1 : 0;
+        if (outs[i] && m * static_cast<size_t>(rows[i]) > most) most = m * static_cast<size_t>(rows[i]);
+    }
+    if (most == 0) return LBK_OK;
+    size_t blocks = (most + 255) / 256;
+    if (blocks > static_cast<size_t>(ctx->sm_count) * 8) blocks = static_cast<size_t>(ctx->sm_count) * 8;
+    scale_epilogue_group_kernel<<<dim3(static_cast<unsigned>(blocks), static_cast<unsigned>(n)), 256, 0, stream>>>(g, ascale, static_cast<int>(m));
+    LBK_CUDA(cudaGetLastError());
+    ctx->launches++;
+    return LBK_OK;
+}
 
 int launch_scale_epilogue(Ctx *ctx, const int32_t *dots, const float *ascale, float wscale, size_t m, size_t rows,
                           float *out, cudaStream_t stream) {
