@@ -7,8 +7,8 @@
 // Orientation: the 128 weight rows of a tile are the MMA's M side, NT token rows its N side
 // (D[row][token] in TMEM). Per 128-column block of K (one packed 32-byte block per weight row):
 //
-//   TMA warp       int8 activations [NT tok][128 B] (SWIZZLE_128B, the K-major B operand) and
-//                  packed weights [128 rows][32 B] into a deep shared-memory ring
+//   2 TMA threads  int8 activations [NT tok][128 B] (SWIZZLE_128B, the K-major B operand) and
+//                  packed weights [128 rows][32 B] into shared-memory rings of their own
 //   2 x 4 expander thread r owns weight row r = TMEM lane r: 32 packed bytes -> 32 words of u8
 //   warps          codes, word c = columns 4c..4c+3 = (packed word >> 2k) & 0x03030303; the two
 //                  sets of four warps take alternate K blocks (one set alone was the bottleneck)
@@ -37,8 +37,10 @@ constexpr int kPackBlocks = 4;      // K-blocks per packed-weight stage: [128 ro
 constexpr int kPackBytes = kBMW * kBlockBytes * kPackBlocks;  // 16 KB, SWIZZLE_128B
 constexpr int kEpiWarps = 4, kExpWarps = 4, kExpSets = 2;
 // warps 0-3 epilogue, 4-7 and 8-11 expanders (warp % 4 = the TMEM lane quadrant a warp may touch)
-constexpr int kExpWarp0 = 4, kTmaWarp = 12, kMmaWarp = 13;
-constexpr int kThreads = 14 * 32;
+// warp 12 feeds the activation ring, warp 14 the packed-weight ring: two threads, so that the weight
+// stream from HBM runs ahead by its own ring's depth whatever the activation ring is waiting for
+constexpr int kExpWarp0 = 4, kTmaWarp = 12, kMmaWarp = 13, kPackWarp = 14;
+constexpr int kThreads = 15 * 32;
 constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr uint32_t kTmemCols = 512;
 
@@ -49,7 +51,9 @@ struct Cfg {
     static constexpr int kGroup = NT == 192 ? 2 : 4;            // K blocks per hand-off (see kBarFull below)
     static constexpr int kGroupStages = kLoadStages / kGroup;   // activation ring in hand-off units
     static constexpr int kAStages = 2 * kGroup;                 // expanded weight tiles in TMEM (32 columns each): two groups
-    static constexpr int kPackStages = 3;                       // packed-weight ring
+    // Packed-weight ring, 16 KB a stage. With 64 token rows the weights come straight from HBM (no
+    // other token tile shares them through L2) and the ring has to cover the memory latency.
+    static constexpr int kPackStages = NT == 192 ? 3 : 8;
     static constexpr uint32_t kPack0 = kLoadStages * kActBytes;
     static constexpr uint32_t kAcc0 = 0, kAcc1 = NT, kA0 = 2 * NT;  // TMEM column map: two accumulators, then the weight tiles
     static_assert(2 * NT + kAStages * 32 <= 512, "TMEM budget");
@@ -76,6 +80,7 @@ struct Cfg {
     static constexpr int kBarAccFull = kBarEmptyPack + kPackStages;   // [2]
     static constexpr int kBarAccEmpty = kBarAccFull + 2;      // [2]
     static_assert(kBarAccEmpty + 2 <= 48, "barrier area too small");
+    static_assert(kTotal + 1024 <= 232448, "shared memory budget");
     static_assert(2 < kGroupStages, "a consumed-barrier phase must still be observable two groups later");
 };
 
@@ -222,10 +227,12 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
-    // Everything above overlapped the tail of the kernel before this one when the launch was
-    // programmatic (the quantiser that produces this kernel's activations); from here on its
-    // results are read. Without such a launch this returns at once.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    // When the launch was programmatic, everything above overlapped the tail of the kernel before
+    // this one (the quantiser that produces this kernel's activations). The roles that read its
+    // results or write what it may still read (activation loads, epilogue) wait for it below; the
+    // packed weights are constants, and their loads start at once. The kernel behind this one may be
+    // scheduled as blocks of this one retire (it orders itself with its own wait).
+    ptx::pdl_trigger();
 
     const int k_blocks = p.k_blocks;
     bool ok = true;
@@ -249,26 +256,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         kb1 = kb0 + p.kb_part < k_blocks ? kb0 + p.kb_part : k_blocks;
     };
 
-    if (warp == kTmaWarp) {
-        // ================= TMA producer =================
+    if (warp == kPackWarp) {
+        // ================= TMA producer: packed weights =================
         if (lane == 0) {
-            int gr = 0, pit = 0;  // groups of activation blocks, packed-weight stages
+            int pit = 0;
+            for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+                int tile, kb0, kb1, mat, m_tile, n_tile;
+                item_range(item, tile, kb0, kb1);
+                decode_tile(tile, mat, m_tile, n_tile);
+                for (int kb = kb0; kb < kb1; kb += kPackBlocks, ++pit) {  // kb0 is a multiple of kPackBlocks
+                    const int ps = pit % PS, pround = pit / PS;
+                    if (pround > 0 && !wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::mbar_arrive_expect_tx(bar(C::kBarFullPack + ps), kPackBytes);
+                    ptx::tma_load_2d(base + C::kPack0 + ps * kPackBytes, &p.wpk[mat], bar(C::kBarFullPack + ps), kb * kBlockBytes, n_tile * kBMW);
+                }
+            }
+        }
+    } else if (warp == kTmaWarp) {
+        // ================= TMA producer: activations =================
+        if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            int gr = 0;  // groups of activation blocks
             for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
                 int tile, kb0, kb1, mat, m_tile, n_tile;
                 item_range(item, tile, kb0, kb1);
                 decode_tile(tile, mat, m_tile, n_tile);
                 for (int kb = kb0; kb < kb1; kb += G, ++gr) {
-                    if ((kb % kPackBlocks) == 0) {
-                        const int ps = pit % PS, pround = pit / PS;
-                        if (pround > 0 && !wait_bar(bar(C::kBarEmptyPack + ps), (pround - 1) & 1, s_abort)) {
-                            ok = false;
-                            break;
-                        }
-                        ptx::mbar_arrive_expect_tx(bar(C::kBarFullPack + ps), kPackBytes);
-                        ptx::tma_load_2d(base + C::kPack0 + ps * kPackBytes, &p.wpk[mat], bar(C::kBarFullPack + ps),
-                                         kb * kBlockBytes, n_tile * kBMW);
-                        ++pit;
-                    }
                     const int s = gr % PG, round = gr / PG;
                     if (round > 0 && !wait_bar(bar(C::kBarConsumed + s), (round - 1) & 1, s_abort)) {
                         ok = false;
@@ -399,6 +415,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
         // ================= epilogue (warps 0..3 = TMEM lane quadrants 0..3) =================
         int *s_qs = reinterpret_cast<int *>(sm + C::kTok);
         float *s_inv = reinterpret_cast<float *>(sm + C::kTok + 2 * NT * 4);
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         int tcount = 0;
         for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++tcount) {
             const int a = tcount & 1, around = tcount >> 1;
