@@ -49,7 +49,7 @@ struct TpRegion {
     unsigned int rs_ready[kTpMaxWorld][32];                  // [r][0]: sequence of rank r's partial dots
     unsigned int ag_ready[kTpMaxWorld][32];                  // [r][0]: sequence of the rows rank r has written into THIS region
     unsigned int am_ready[kTpMaxWorld][32];                  // [r][0]: sequence of rank r's entries of `best` in THIS region
-    unsigned int nq_seq, nq_done, rg_seq, rg_done, rg_written, am_seq, pad2_[26];
+    unsigned int nq_seq, nq_done, rg_seq, rg_spare, rg_written, am_seq, pad2_[26];
     float gather_scale[kTpMaxRows];                          // per-token activation scale of the gathered rows
     int32_t gather_sum[kTpMaxRows];                          // per-token sum of the gathered int8 codes
     int8_t gather_q[static_cast<size_t>(kTpMaxRows) * kTpMaxWidth];     // all tokens' quantised rows, written by their owners
@@ -292,6 +292,7 @@ __device__ __forceinline__ int block_sum_i(int v, int *s_red, int nwarps) {
 // ranks' values. Sum: added in rank order, so that every rank derives the same bits. Max: order-free.
 __device__ __forceinline__ float exchange_stat(const TpPtrs &peers, int world, int rank, int par, int round, int row, unsigned int seq,
                                                float mine, bool is_sum, int *err_word, uint32_t wait_limit) {
+    if (world == 1) return mine;  // total = 0 + mine and max(0, mine): the same bits as the loop below gives
     const int lane = threadIdx.x & 31;
     float other = 0.0f;
     bool ok = true;
@@ -400,6 +401,7 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
     if (tid == 0) {
         scale[row] = sc;
         sum[row] = acc;
+        if (world == 1) return;  // no exchange happened: the sequence number was not used
         __threadfence();
         if (atomicAdd(&me->nq_done, 1u) == gridDim.x - 1) {  // the last CTA moves the sequence on: every CTA has read it
             me->nq_done = 0;
@@ -435,9 +437,10 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
     const int t0 = rank * a.mt;
     const int own = max(0, min(a.m - t0, a.mt));
     const int lt = blockIdx.x;  // local token
-    if (a.reduce) {
-        // this rank's partial dots were written by the kernel before this one; the fence orders them,
-        // system wide, before the flag that tells every peer so
+    if (a.reduce && world > 1) {
+        // this rank's partial dots were written by the kernel before this one, which is complete (the
+        // wait above): they sit in this GPU's memory, where the peers' loads find them. The flag tells
+        // every peer so.
         if (blockIdx.x == 0 && tid < world) {
             __threadfence_system();
             *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->rs_ready[rank][0]) = seq;
@@ -535,7 +538,9 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
     // at once. The kernel ends when that CTA ends, so whatever follows in the stream finds all tokens'
     // rows in this rank's region, and no CTA waits for a peer while CTAs of its own grid still have
     // to be scheduled. One fence per CTA: the block barrier orders every thread's stores before
-    // thread 0's fence, and the fence is cumulative.
+    // thread 0's fence, and the fence is cumulative. The last CTA also moves the sequence number on:
+    // every CTA of the grid has read it by then. With one rank there is nobody to tell.
+    if (world == 1) return;
     __syncthreads();
     __shared__ int s_last;
     if (tid == 0) {
@@ -546,7 +551,7 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
     __syncthreads();
     if (s_last) {
         if (tid < world) {
-            __threadfence_system();
+            __threadfence_system();  // the other CTAs' rows, seen through the count, before the flag
             *reinterpret_cast<volatile unsigned int *>(&peers.r[tid]->ag_ready[rank][0]) = seq;
             volatile unsigned int *flag = &me->ag_ready[tid][0];
             uint32_t polls = 0;
@@ -558,14 +563,7 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
             }
         }
         __syncthreads();
-    }
-    if (tid == 0) {
-        __threadfence();
-        if (atomicAdd(&me->rg_done, 1u) == gridDim.x - 1) {
-            me->rg_done = 0;
-            __threadfence();
-            *reinterpret_cast<volatile unsigned int *>(&me->rg_seq) = seq + 1;
-        }
+        if (tid == 0) *reinterpret_cast<volatile unsigned int *>(&me->rg_seq) = seq + 1;
     }
 }
 
