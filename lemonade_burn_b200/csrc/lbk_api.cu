@@ -76,6 +76,10 @@ int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int b
     return encode_2d_u8(map, q, kp, m, kp, 128, static_cast<uint32_t>(box_rows), CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
+int encode_bytes_map(CUtensorMap *map, const void *base, size_t inner, size_t outer, size_t pitch, int box_inner, int box_outer) {
+    return encode_2d_u8(map, base, inner, outer, pitch, static_cast<uint32_t>(box_inner), static_cast<uint32_t>(box_outer), CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 // Grow-only scratch. A block that has been handed out is never freed before the context is
 // destroyed: a CUDA graph recorded by a caller (a decode step captured at 5..8 sequences, whose
 // projections take the quantise + GEMM path) has this address baked in, and a later, larger request
@@ -228,6 +232,7 @@ int lbk_destroy(lbk_ctx *c) {
     if (ctx->err_word) cudaFree(ctx->err_word);
     if (ctx->small_scratch) cudaFree(ctx->small_scratch);
     if (ctx->gemm_acc) cudaFree(ctx->gemm_acc);
+    if (ctx->bf16_x) cudaFree(ctx->bf16_x);
     if (ctx->own_stream) cudaStreamDestroy(ctx->own_stream);
     delete ctx;
     return LBK_OK;

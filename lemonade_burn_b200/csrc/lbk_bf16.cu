@@ -8,10 +8,13 @@
 // not bit for bit (the reference allows 1e-4 absolute, bf16.rs:113-136).
 #include "lbk_internal.cuh"
 #include "lbk_ptx.cuh"
+#include "lbk_tcgen05.cuh"
 
 namespace lbk {
 
 namespace {
+
+using namespace tc;
 
 constexpr int kThreads = 256;
 constexpr int kTok = 4;  // token rows per pass over W
@@ -75,180 +78,283 @@ __global__ void __launch_bounds__(kThreads) bf16_linear_kernel(const float *__re
     }
 }
 
-// Two to sixteen token rows per pass over W on the tensor cores (mma.sync m16n8k16, bf16 x bf16 ->
-// f32). The f32 activations are split into two bf16 terms, x = hi + lo with lo = bf16(x - hi), so
-// that the products are those of the reference's f32 math to within 2^-17 relative; W's bf16 values
-// are exact. Token rows are the MMA's M side, 16 weight rows per warp step its N side.
-//
-// K is consumed 32 columns at a time and the MMA's k slots are permuted so that every lane's
-// operands are contiguous: lane (g, t) loads the 16 bytes W[row g][32c + 8t .. 8t+7] (eight rows x
-// 64 contiguous bytes per load instruction, whole sectors) and one 16-byte word of x per token row
-// at the same columns; slots (2t, 2t+1) and (2t+8, 2t+9) of the first MMA take columns 8t+0..3,
-// those of the second 8t+4..7. The permutation is the same for both operands, so the sum is the
-// plain dot product.
-constexpr int kMmaTok = 16;
-
-__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
-
 __device__ __forceinline__ uint32_t f32_to_bf16_rn(float v) {  // round to nearest even; NaN kept a NaN
     const uint32_t u = __float_as_uint(v);
     if ((u & 0x7fffffffu) > 0x7f800000u) return (u >> 16) | 0x40u;
     return (u + 0x7fffu + ((u >> 16) & 1u)) >> 16;
 }
 
+// ---- two token rows and more: the 5th-generation tensor cores ----------------------------------
 //
-// Long rows go through in column chunks (`c0`, `ccols`: whole 32-column slices) so that sixteen token
-// rows of a chunk fit in shared memory; the launches of one token group run one after the other on
-// the stream and every chunk after the first adds to what the earlier ones stored (`accumulate`), in
-// chunk order, so the sum has one fixed order.
-constexpr int kMmaThreads = 512;  // sixteen warps: twice the loads in flight per SM of the eight the FMA kernel uses
-// TT = token tiles of 16 rows per pass over W: 1 (2..16 rows) or 2 (17 rows and more: half the passes)
-template <int TT>
-__global__ void __launch_bounds__(kMmaThreads) bf16_linear_mma_kernel(const float *__restrict__ x, const uint16_t *__restrict__ w, int rows,
-                                                                     int cols, int m_total, int t0, int xs_stride /* bytes */, int c0, int ccols,
-                                                                     int accumulate, float *__restrict__ out) {
+// out[t, r] = sum_k x[t, k] * W[r, k] as a tcgen05 GEMM (kind::f16, bf16 operands, f32 accumulators in
+// tensor memory). The 128 table rows of a tile are the MMA's M side, the token rows its N side. An
+// f32 activation is two bf16 terms, x = hi + lo with lo = bf16(x - hi) (a product is then the
+// reference's f32 product to within 2^-17 relative; W's bf16 values are exact): the hi rows and the
+// lo rows of up to 64 tokens are ONE B operand of up to 128 rows, so that one instruction does both
+// terms, and the epilogue adds the two halves of the accumulator. Accuracy: the difference from the
+// reference's sums is the tensor core's own f32 accumulation (its order and rounding), growing with
+// the column count: 3e-6 / 7e-6 / 1e-5 of max |out| at 2560 / 6912 / 8192 columns, measured; a third
+// bf16 term (x exactly) changed none of these digits and is not used. The reference allows 1e-4
+// absolute (bf16.rs:113-136). Both operands come straight from shared memory, where TMA puts them
+// (SWIZZLE_128B, 64 columns = 128 bytes a K block); no thread touches the table. One persistent CTA
+// per SM walks the table's 128-row tiles, each over the whole of K: the table is read once per 64
+// token rows, the activations (2 x 64 x cols bf16, L2 resident) once per tile. Bound: HBM,
+// rows * cols * 2 bytes.
+//
+// What it replaced: an mma.sync kernel that took 16 or 32 token rows per pass over the table and ran
+// at 2 TB/s (its activation fragments came from shared memory once per 16 table rows: four bytes of
+// shared-memory reads per table byte). Rows that are not whole 16-byte units, or longer than the
+// context's activation buffer, take the FMA kernel above, four token rows per pass.
+constexpr int kTcTokMax = 64;                  // token rows per pass over the table
+constexpr int kTcRows = 128;                   // table rows per tile (MMA M, TMEM lanes)
+constexpr int kTcKB = 64;                      // columns per stage: 128 bytes of bf16
+constexpr int kTcTerms = 2;                    // bf16 terms per f32 activation
+constexpr int kTcStages = 6;
+constexpr int kTcWBytes = kTcRows * 128;       // 16 KB
+constexpr int kTcXBytes = kTcTerms * kTcTokMax * 128; // 16 KB
+constexpr int kTcStageBytes = kTcWBytes + kTcXBytes;
+constexpr int kTcBars = kTcStages * kTcStageBytes;
+constexpr int kTcMisc = kTcBars + 32 * 8;
+constexpr int kTcSmem = kTcMisc + 64 + 1024;
+constexpr int kTcThreads = 6 * 32;             // warps 0-3 epilogue, 4 TMA, 5 MMA
+constexpr uint32_t kTcTmemCols = 256;          // two accumulators of up to 128 columns
+constexpr size_t kTcMaxCols = 32768;           // the activation buffer of the context is sized for this (8 MB)
+
+struct HeadParams {
+    CUtensorMap w;      // bytes [rows][cols * 2], box [128][128], SWIZZLE_128B
+    CUtensorMap x;      // bytes [2 * ntp][cols * 2] (hi rows, then lo rows), box [2 * ntp][128], SWIZZLE_128B
+    float *out;         // [m][rows]; this pass writes token rows t0 .. t0 + ntok - 1
+    int rows, k_blocks, tiles, ntp, ntok, t0;
+    int *err_word;
+};
+
+// x f32 [ntok][cols] -> bf16 [2 * ntp][cols]: rows 0 .. ntp-1 the hi terms, ntp .. 2 ntp-1 the lo terms
+// (hi = bf16(x), lo = bf16(x - hi)); token rows past ntok zero
+__global__ void __launch_bounds__(256) split_x_kernel(const float *__restrict__ x, int cols, int ntok, int ntp, uint16_t *__restrict__ xs) {
     ptx::pdl_trigger();
     ptx::pdl_wait();
-    extern __shared__ __align__(16) uint8_t s_raw[];
-    constexpr int kTokRows = TT * kMmaTok;
-    uint8_t *s_hi = s_raw, *s_lo = s_raw + kTokRows * xs_stride;  // [16 TT tokens][xs_stride] bf16
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int g = lane >> 2, t = lane & 3;
-    for (int i = tid; i < kTokRows * (ccols >> 1); i += kMmaThreads) {  // two columns per step
-        const int tk = i / (ccols >> 1), c = (i - tk * (ccols >> 1)) * 2;
+    const int pairs = cols >> 1;
+    for (int i = blockIdx.x * 256 + threadIdx.x; i < ntp * pairs; i += gridDim.x * 256) {
+        const int tk = i / pairs, c = (i - tk * pairs) * 2;
         float2 v = make_float2(0.f, 0.f);
-        if (t0 + tk < m_total) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(t0 + tk) * cols + c0 + c);
+        if (tk < ntok) v = *reinterpret_cast<const float2 *>(x + static_cast<size_t>(tk) * cols + c);
         const uint32_t h0 = f32_to_bf16_rn(v.x), h1 = f32_to_bf16_rn(v.y);
         const uint32_t l0 = f32_to_bf16_rn(v.x - __uint_as_float(h0 << 16)), l1 = f32_to_bf16_rn(v.y - __uint_as_float(h1 << 16));
-        *reinterpret_cast<uint32_t *>(s_hi + tk * xs_stride + c * 2) = h0 | (h1 << 16);
-        *reinterpret_cast<uint32_t *>(s_lo + tk * xs_stride + c * 2) = l0 | (l1 << 16);
+        *reinterpret_cast<uint32_t *>(xs + static_cast<size_t>(tk) * cols + c) = h0 | (h1 << 16);
+        *reinterpret_cast<uint32_t *>(xs + static_cast<size_t>(ntp + tk) * cols + c) = l0 | (l1 << 16);
     }
+}
+
+// the four K = 16 steps of one 64-column block: both descriptors advance 32 bytes (2 units) a step
+__device__ __forceinline__ void umma_bf16_ss_block(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate_first) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p, q;\n"
+        ".reg .b64 a1, a2, a3, b1, b2, b3;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "setp.eq.b32 q, 0, 0;\n"
+        "add.u64 a1, %1, 2;\n"
+        "add.u64 a2, %1, 4;\n"
+        "add.u64 a3, %1, 6;\n"
+        "add.u64 b1, %2, 2;\n"
+        "add.u64 b2, %2, 4;\n"
+        "add.u64 b3, %2, 6;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a1, b1, %3, q;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a2, b2, %3, q;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], a3, b3, %3, q;\n"
+        "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
+        : "memory");
+}
+
+__global__ void __launch_bounds__(kTcThreads, 1) bf16_head_kernel(const __grid_constant__ HeadParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *sm = smem_raw + (base - raw);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t bar0 = base + kTcBars;
+    volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(sm + kTcMisc);
+    volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kTcMisc + 4);
+    // barriers: full[stage], empty[stage], acc_full[2], acc_empty[2]
+    auto bar = [&](int idx) { return bar0 + idx * 8; };
+    constexpr int kFull = 0, kEmpty = kTcStages, kAccFull = 2 * kTcStages, kAccEmpty = 2 * kTcStages + 2;
+    if (tid == 0) {
+        for (int i = 0; i < kTcStages; ++i) {
+            ptx::mbar_init(bar(kFull + i), 1);
+            ptx::mbar_init(bar(kEmpty + i), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(bar(kAccFull + a), 1);
+            ptx::mbar_init(bar(kAccEmpty + a), 4);
+        }
+        *s_abort = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 5) {
+        tmem_alloc(base + kTcMisc, kTcTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
     __syncthreads();
-    const int slices = ccols >> 5;
-    const int groups = (rows + 15) >> 4;  // 16 weight rows per warp step
-    const int warps_total = gridDim.x * (kMmaThreads / 32);
-    const uint8_t *xa = s_hi + g * xs_stride + t * 16, *xb = s_hi + (g + 8) * xs_stride + t * 16;
-    const size_t lo_off = static_cast<size_t>(kTokRows) * xs_stride;
-    const size_t tile_off = static_cast<size_t>(kMmaTok) * xs_stride;
-    for (int grp = blockIdx.x * (kMmaThreads / 32) + warp; grp < groups; grp += warps_total) {
-        const int r0 = grp * 16;
-        const int ra = min(r0 + g, rows - 1), rb = min(r0 + 8 + g, rows - 1);  // clamped rows are computed and dropped
-        const uint4 *wa = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(ra) * cols + c0) + t;
-        const uint4 *wb = reinterpret_cast<const uint4 *>(w + static_cast<size_t>(rb) * cols + c0) + t;
-        float d0[TT][4], d1[TT][4];
-#pragma unroll
-        for (int tt = 0; tt < TT; ++tt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) d0[tt][e] = d1[tt][e] = 0.f;
-        // Software pipeline over groups of kPf slices: the next group's 2 * kPf loads are issued before
-        // the current group's MMAs, so that a warp always has loads in flight (without it a warp
-        // alternated between waiting for its loads and computing, and the table streamed at 1.9 TB/s).
-        constexpr int kPf = 4;
-        uint4 ca[kPf], cb[kPf];
-#pragma unroll
-        for (int u = 0; u < kPf; ++u) {
-            ca[u] = u < slices ? __ldcs(wa + u * 4) : make_uint4(0u, 0u, 0u, 0u);  // streamed once
-            cb[u] = u < slices ? __ldcs(wb + u * 4) : make_uint4(0u, 0u, 0u, 0u);
-        }
-        for (int c0s = 0; c0s < slices; c0s += kPf) {
-            uint4 na[kPf], nb[kPf];
-#pragma unroll
-            for (int u = 0; u < kPf; ++u) {
-                const int c = c0s + kPf + u;
-                na[u] = c < slices ? __ldcs(wa + c * 4) : make_uint4(0u, 0u, 0u, 0u);
-                nb[u] = c < slices ? __ldcs(wb + c * 4) : make_uint4(0u, 0u, 0u, 0u);
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    ptx::pdl_trigger();
+    const int n = kTcTerms * p.ntp;  // MMA N: the hi rows and the lo rows of this pass's tokens
+    bool ok = true;
+
+    if (warp == 4) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            const int my_tiles = p.tiles > static_cast<int>(blockIdx.x) ? (p.tiles - static_cast<int>(blockIdx.x) + static_cast<int>(gridDim.x) - 1) / static_cast<int>(gridDim.x) : 0;
+            const int total = my_tiles * p.k_blocks;
+            const int pre = total < kTcStages ? total : kTcStages;
+            const uint32_t stage_tx = static_cast<uint32_t>(kTcWBytes + n * 128);
+            // The table is a constant: the first ring of its blocks is on its way before the kernel in
+            // front (the one that writes the activations' two terms) is known to be complete.
+            for (int it = 0; it < pre; ++it) {
+                const int tile = static_cast<int>(blockIdx.x) + (it / p.k_blocks) * static_cast<int>(gridDim.x), kb = it % p.k_blocks;
+                ptx::mbar_arrive_expect_tx(bar(kFull + it), stage_tx);
+                ptx::tma_load_2d(base + it * kTcStageBytes, &p.w, bar(kFull + it), kb * 128, tile * kTcRows);
             }
-#pragma unroll
-            for (int u = 0; u < kPf; ++u) {
-                const int c = c0s + u;
-                if (c < slices) {
-                    const uint4 va = ca[u], vb = cb[u];
-#pragma unroll
-                    for (int tt = 0; tt < TT; ++tt) {
-                        const uint8_t *pa = xa + tt * tile_off + c * 64, *pb = xb + tt * tile_off + c * 64;
-                        const uint4 h0 = *reinterpret_cast<const uint4 *>(pa), h1 = *reinterpret_cast<const uint4 *>(pb);
-                        const uint4 l0 = *reinterpret_cast<const uint4 *>(pa + lo_off), l1 = *reinterpret_cast<const uint4 *>(pb + lo_off);
-                        mma_bf16(d0[tt], h0.x, h1.x, h0.y, h1.y, va.x, va.y);
-                        mma_bf16(d0[tt], h0.z, h1.z, h0.w, h1.w, va.z, va.w);
-                        mma_bf16(d0[tt], l0.x, l1.x, l0.y, l1.y, va.x, va.y);
-                        mma_bf16(d0[tt], l0.z, l1.z, l0.w, l1.w, va.z, va.w);
-                        mma_bf16(d1[tt], h0.x, h1.x, h0.y, h1.y, vb.x, vb.y);
-                        mma_bf16(d1[tt], h0.z, h1.z, h0.w, h1.w, vb.z, vb.w);
-                        mma_bf16(d1[tt], l0.x, l1.x, l0.y, l1.y, vb.x, vb.y);
-                        mma_bf16(d1[tt], l0.z, l1.z, l0.w, l1.w, vb.z, vb.w);
-                    }
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int it = 0; it < pre; ++it)
+                ptx::tma_load_2d(base + it * kTcStageBytes + kTcWBytes, &p.x, bar(kFull + it), (it % p.k_blocks) * 128, 0);
+            int s = 0, round = 1, tile = static_cast<int>(blockIdx.x) + (pre / p.k_blocks) * static_cast<int>(gridDim.x), kb = pre % p.k_blocks;
+            for (int it = pre; it < total; ++it) {
+                if (!wait_bar(bar(kEmpty + s), (round - 1) & 1, s_abort)) {
+                    ok = false;
+                    break;
                 }
-            }
-#pragma unroll
-            for (int u = 0; u < kPf; ++u) {
-                ca[u] = na[u];
-                cb[u] = nb[u];
-            }
-        }
-        // D[token][row]: lane (g, t) holds tokens g, g+8 and rows 2t, 2t+1 of each 8-row half
-#pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {
-                const float *d = half ? d1[tt] : d0[tt];
-                const int row = r0 + half * 8 + 2 * t;
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                    const int tk = t0 + tt * kMmaTok + g + hh * 8;
-                    if (tk < m_total) {
-                        float *o = out + static_cast<size_t>(tk) * rows + row;
-                        if (row < rows) o[0] = accumulate ? o[0] + d[hh * 2] : d[hh * 2];
-                        if (row + 1 < rows) o[1] = accumulate ? o[1] + d[hh * 2 + 1] : d[hh * 2 + 1];
-                    }
+                ptx::mbar_arrive_expect_tx(bar(kFull + s), stage_tx);
+                ptx::tma_load_2d(base + s * kTcStageBytes, &p.w, bar(kFull + s), kb * 128, tile * kTcRows);
+                ptx::tma_load_2d(base + s * kTcStageBytes + kTcWBytes, &p.x, bar(kFull + s), kb * 128, 0);
+                if (++s == kTcStages) {
+                    s = 0;
+                    ++round;
+                }
+                if (++kb == p.k_blocks) {
+                    kb = 0;
+                    tile += static_cast<int>(gridDim.x);
                 }
             }
         }
+    } else if (warp == 5) {
+        // ================= MMA issuer (one thread) =================
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | ((kTcRows >> 4) << 24);
+            const uint64_t adesc0 = smem_desc_sw128(base), bdesc0 = smem_desc_sw128(base + kTcWBytes);
+            int it = 0, tcount = 0;
+            for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++tcount) {
+                const int a = tcount & 1, around = tcount >> 1;
+                if (around > 0 && !wait_bar(bar(kAccEmpty + a), (around - 1) & 1, s_abort)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + a * 128;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const int s = it % kTcStages, round = it / kTcStages;
+                    if (!wait_bar(bar(kFull + s), round & 1, s_abort)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint64_t off = static_cast<uint64_t>(s) * (kTcStageBytes >> 4);
+                    umma_bf16_ss_block(d_tmem, adesc0 + off, bdesc0 + off, idesc, kb ? 1u : 0u);
+                    umma_commit(bar(kEmpty + s));  // the stage is free once these MMAs retire
+                }
+                if (!ok) break;
+                umma_commit(bar(kAccFull + a));
+            }
+        }
+    } else {
+        // ================= epilogue (warps 0..3 = TMEM lane quadrants 0..3) =================
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // out may still be read by the kernel in front
+        int tcount = 0;
+        for (int tile = blockIdx.x; tile < p.tiles && ok; tile += gridDim.x, ++tcount) {
+            const int a = tcount & 1, around = tcount >> 1;
+            if (!wait_bar(bar(kAccFull + a), around & 1, s_abort)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int row = tile * kTcRows + warp * 32 + lane;
+            const uint32_t acc = tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + a * 128;
+#pragma unroll 1
+            for (int c = 0; c * 32 < p.ntok; ++c) {
+                uint32_t hi[32], lo[32];
+                tmem_ld32(acc + c * 32, hi);
+                tmem_ld32(acc + p.ntp + c * 32, lo);
+                tmem_ld_wait();
+                if (row < p.rows) {
+                    float *o = p.out + static_cast<size_t>(p.t0 + c * 32) * p.rows + row;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        if (c * 32 + i < p.ntok) o[static_cast<size_t>(i) * p.rows] = __fadd_rn(__uint_as_float(hi[i]), __uint_as_float(lo[i]));
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kAccEmpty + a));
+        }
+    }
+    if (!ok && lane == 0) atomicExch(p.err_word, 5);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTcTmemCols);
     }
 }
 
 }  // namespace
 
+int bf16_init(Ctx *ctx) {
+    if (static_cast<size_t>(kTcSmem) > ctx->smem_optin) return fail(LBK_ERR_UNSUPPORTED, "bf16 head kernel needs %d B of shared memory", kTcSmem);
+    LBK_CUDA(cudaFuncSetAttribute(bf16_head_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmem));
+    // the activations' bf16 terms of one pass: [2 * 64 token rows][up to kTcMaxCols]
+    LBK_CUDA(cudaMalloc(&ctx->bf16_x, kTcTerms * kTcTokMax * kTcMaxCols * sizeof(uint16_t)));
+    return LBK_OK;
+}
+
+// two token rows and more, rows of whole 16-byte units: the tcgen05 kernel, 64 token rows per pass
+static int launch_bf16_head_tc(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows, size_t cols, float *out, cudaStream_t stream) {
+    HeadParams p{};
+    LBK_TRY(encode_bytes_map(&p.w, w, cols * 2, rows, cols * 2, 128, kTcRows));
+    p.rows = static_cast<int>(rows);
+    p.k_blocks = static_cast<int>((cols + kTcKB - 1) / kTcKB);
+    p.tiles = static_cast<int>((rows + kTcRows - 1) / kTcRows);
+    p.out = out;
+    p.err_word = ctx->err_word;
+    uint16_t *xs = static_cast<uint16_t *>(ctx->bf16_x);
+    const int grid = p.tiles < ctx->sm_count ? p.tiles : ctx->sm_count;
+    for (size_t t0 = 0; t0 < m; t0 += kTcTokMax) {
+        const int ntok = static_cast<int>(m - t0 < static_cast<size_t>(kTcTokMax) ? m - t0 : kTcTokMax);
+        const int ntp = (ntok + 15) & ~15;
+        const size_t pairs = static_cast<size_t>(ntp) * (cols >> 1);
+        const unsigned sgrid = static_cast<unsigned>((pairs + 255) / 256 < static_cast<size_t>(ctx->sm_count) * 4 ? (pairs + 255) / 256 : static_cast<size_t>(ctx->sm_count) * 4);
+        LBK_CUDA(launch_chained(split_x_kernel, dim3(sgrid), dim3(256), 0, stream, x + t0 * cols, static_cast<int>(cols), ntok, ntp, xs));
+        LBK_TRY(encode_bytes_map(&p.x, xs, cols * 2, static_cast<size_t>(kTcTerms * ntp), cols * 2, 128, kTcTerms * ntp));
+        p.ntp = ntp;
+        p.ntok = ntok;
+        p.t0 = static_cast<int>(t0);
+        LBK_CUDA(launch_chained(bf16_head_kernel, dim3(static_cast<unsigned>(grid)), dim3(kTcThreads), static_cast<size_t>(kTcSmem), stream, p));
+        LBK_CUDA(cudaGetLastError());
+        ctx->launches += 2;
+    }
+    return LBK_OK;
+}
+
 int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows,
                        size_t cols, float *out, cudaStream_t stream) {
     if (m == 0 || rows == 0) return LBK_OK;
+    if (m >= 2 && (cols & 7) == 0 && cols <= kTcMaxCols && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0)
+        return launch_bf16_head_tc(ctx, x, m, w, rows, cols, out, stream);
     const size_t smem1 = cols * sizeof(float);
     if (smem1 * kTok > ctx->smem_optin)
         return fail(LBK_ERR_UNSUPPORTED, "bf16_linear: %zu columns do not fit in shared memory", cols);
     const int grid = ctx->sm_count * 4;
-    // two or more token rows: tensor cores, sixteen rows per pass over W (needs whole 32-column slices
-    // and 16-byte aligned rows; anything else takes the FMA kernel below)
-    // Rows go through in column chunks (whole 32-column slices) sized so that the staged token rows fit
-    // in shared memory: 16 token rows per pass over W with chunks of at most 3072 columns; from 17 rows
-    // on, 32 token rows per pass with chunks of at most 1536 (half the passes over W).
-    const int tt = m > static_cast<size_t>(kMmaTok) ? 2 : 1;
-    const size_t max_chunk = tt == 2 ? 1536 : 3072;
-    const size_t n_chunks = (cols + max_chunk - 1) / max_chunk;
-    const size_t chunk = ((cols + n_chunks - 1) / n_chunks + 31) / 32 * 32;
-    const int xs_stride = static_cast<int>(chunk * 2 + 64);  // +64: the 16-byte loads of two token rows land on distinct banks
-    const size_t smem = static_cast<size_t>(2 * tt * kMmaTok) * xs_stride;
-    if (m >= 2 && (cols & 31) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 7) == 0 && smem <= ctx->smem_optin) {
-        if (tt == 2) LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        else LBK_CUDA(cudaFuncSetAttribute(bf16_linear_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
-        for (size_t t0 = 0; t0 < m; t0 += static_cast<size_t>(tt) * kMmaTok) {
-            for (size_t c0 = 0; c0 < cols; c0 += chunk) {
-                const size_t cc = cols - c0 < chunk ? cols - c0 : chunk;
-                if (tt == 2)
-                    LBK_CUDA(launch_chained(bf16_linear_mma_kernel<2>, dim3(ctx->sm_count), dim3(kMmaThreads), smem, stream, x, w, static_cast<int>(rows),
-                                            static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
-                                            static_cast<int>(cc), c0 ? 1 : 0, out));
-                else
-                    LBK_CUDA(launch_chained(bf16_linear_mma_kernel<1>, dim3(ctx->sm_count), dim3(kMmaThreads), smem, stream, x, w, static_cast<int>(rows),
-                                            static_cast<int>(cols), static_cast<int>(m), static_cast<int>(t0), xs_stride, static_cast<int>(c0),
-                                            static_cast<int>(cc), c0 ? 1 : 0, out));
-                ctx->launches++;
-            }
-        }
-        return LBK_OK;
-    }
     for (size_t t0 = 0; t0 < m; t0 += kTok) {
         const size_t left = m - t0;
         if (left >= kTok) {

@@ -26,6 +26,7 @@
 // next) + a 4-deep ring of 32-column weight tiles. Bound: int8 tensor pipe; 2*m*rows*cols ops.
 #include "lbk_internal.cuh"
 #include "lbk_ptx.cuh"
+#include "lbk_tcgen05.cuh"
 
 namespace lbk {
 
@@ -41,7 +42,6 @@ constexpr int kEpiWarps = 4, kExpWarps = 4, kExpSets = 2;
 // stream from HBM runs ahead by its own ring's depth whatever the activation ring is waiting for
 constexpr int kExpWarp0 = 4, kTmaWarp = 12, kMmaWarp = 13, kPackWarp = 14;
 constexpr int kThreads = 15 * 32;
-constexpr uint32_t kWaitLimit = 1u << 22;
 constexpr uint32_t kTmemCols = 512;
 
 template <int NT>  // capacity in token rows per tile (MMA N): 192 or 64; a launch uses nt <= NT
@@ -101,34 +101,7 @@ struct GemmParams {
     int *err_word;
 };
 
-// ---- tcgen05 wrappers ----------------------------------------------------------------------
-__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-// mbarrier arrive once every MMA issued so far by this thread has completed
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+using namespace tc;
 
 // A operand from TMEM (u8 codes), B from shared memory (s8 activations).
 // The four K = 32 steps of one 128-column block in one go: A advances 8 TMEM columns and B 32
@@ -154,40 +127,6 @@ __device__ __forceinline__ void umma_i8_ts_block(uint32_t d_tmem, uint32_t a_tme
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
-        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
-        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
-          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
-          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
-          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
-        : "memory");
-}
-__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-// K-major SWIZZLE_128B shared-memory matrix descriptor: rows of 128 bytes, 8-row groups 1024 B
-// apart (SBO), version 1, layout type 2; `addr` may be advanced by 32 B per K=32 step.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);   // start address
-    d |= static_cast<uint64_t>(1) << 16;                  // leading byte offset (unused for SW128 K-major)
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride byte offset
-    d |= static_cast<uint64_t>(1) << 46;                  // descriptor version (Blackwell)
-    d |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
-    return d;
-}
-
-// Bounded wait that also gives up as soon as another role has flagged an abort.
-__device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
-    for (uint32_t i = 0; i < kWaitLimit; ++i) {
-        if (ptx::mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
-}
-
 template <int NT>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
     using C = Cfg<NT>;

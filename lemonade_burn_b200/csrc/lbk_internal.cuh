@@ -50,6 +50,7 @@ struct Ctx {
     size_t scratch_bytes = 0;
     std::vector<void *> retired_scratch;  // earlier, smaller scratch blocks: kept until lbk_destroy (recorded graphs may point into them)
     cudaStream_t own_stream = nullptr;  // used by the host-pointer entry points
+    void *bf16_x = nullptr;             // allocated once at init: the bf16 head's activations as two bf16 terms (one pass of 64 token rows)
     void *small_scratch = nullptr;      // kSmallScratchBytes, allocated once at init (reductions)
     int32_t *gemm_acc = nullptr;        // kGemmAccBytes, allocated once at init: int32 sums of a prefill GEMM split along K
     int gemv_rows = 0;                  // lbk_set_gemv_rows: 0 = measured rule, n = fused kernel up to n token rows
@@ -74,6 +75,8 @@ int gemm_init(Ctx *ctx);
 int sweep_init(Ctx *ctx);
 int encode_weight_maps(Weight *w);
 int encode_act_map(CUtensorMap *map, const int8_t *q, size_t m, size_t kp, int box_rows);
+// bytes [outer][inner] with row pitch `pitch`, boxes [box_outer][box_inner bytes], 128-byte swizzle, zeros past the edges
+int encode_bytes_map(CUtensorMap *map, const void *base, size_t inner, size_t outer, size_t pitch, int box_inner, int box_outer);
 
 // ---- launchers -----------------------------------------------------------------------
 struct GroupArgs {
@@ -143,6 +146,7 @@ int launch_scale_epilogue_group(Ctx *ctx, int n, int32_t *const *dots, float *co
 // tcgen05 int8 GEMM on quantised inputs (any m).
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
 
+int bf16_init(Ctx *ctx);
 int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows,
                        size_t cols, float *out, cudaStream_t stream);
 

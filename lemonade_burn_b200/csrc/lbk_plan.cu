@@ -94,6 +94,7 @@ int kernels_init(Ctx *ctx) {
     LBK_TRY(gemv_init(ctx));
     LBK_TRY(gemm_init(ctx));
     LBK_TRY(sweep_init(ctx));
+    LBK_TRY(bf16_init(ctx));
     return LBK_OK;
 }
 

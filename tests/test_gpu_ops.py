@@ -104,13 +104,13 @@ def test_dtype_and_shape_errors(oracle, ctx):
 
 
 @pytest.mark.parametrize("m,rows,cols", [(1, 1000, 2560), (3, 1000, 2560), (4, 1000, 2560), (7, 1000, 2560), (16, 1003, 2560),
-                                         (19, 37, 512), (2, 1000, 2568), (5, 64, 40), (20, 530, 8192), (3, 100, 6912), (2, 64, 3104)])
+                                         (19, 37, 512), (2, 1000, 2568), (5, 64, 40), (20, 530, 8192), (3, 100, 6912), (2, 64, 3104),
+                                         (64, 300, 2560), (65, 260, 1024), (130, 129, 512), (3, 50, 36), (6, 40, 2562)])
 def test_bf16_linear(oracle, ctx, m, rows, cols):
-    """One token row takes the FMA kernel, two or more the tensor-core kernel (activations split into
-    two bf16 terms), ragged row counts and more than sixteen token rows included; column counts that
-    are not whole 32-column slices fall back to the FMA kernel; rows longer than 3072 columns go
-    through in column chunks that add up in a fixed order (8192: the 70B-shaped head; 3104: two
-    chunks of unequal length)."""
+    """One token row takes the FMA kernel, two or more the tcgen05 kernel (activations split into two
+    bf16 terms; 64 token rows per pass over the table, so 65 and 130 rows take two and three passes),
+    ragged row counts, a ragged last K block (2568, 40 columns) and long rows (8192: the 70B-shaped
+    head) included; rows that are not whole 16-byte units (36, 2562 columns) take the FMA kernel."""
     import torch
     from lemonade_burn_b200 import ops
     g = torch.Generator().manual_seed(m)
@@ -122,8 +122,9 @@ def test_bf16_linear(oracle, ctx, m, rows, cols):
         ref = oracle.bf16_gemv(bits, x[t].numpy())
         assert np.abs(out[t] - ref).max() < 1e-4  # bf16.rs:113-136 bound
         # and relative to the row's range: the two-term bf16 split of the activations leaves 2^-17 per
-        # product (measured 4e-6 .. 7e-6 of max |out| for 2560 .. 8192 columns)
-        assert np.abs(out[t] - ref).max() <= 1e-5 * np.abs(ref).max()
+        # product and the tensor core's own f32 accumulation adds an error that grows with the column
+        # count (measured 3e-6 / 7e-6 / 1.0e-5 of max |out| at 2560 / 6912 / 8192 columns)
+        assert np.abs(out[t] - ref).max() <= 2e-5 * np.abs(ref).max()
 
 
 def test_plan_replays_groups(oracle, ctx):
