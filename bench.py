@@ -638,6 +638,15 @@ def tp70b_decoder(torch, dist, ctx, device, world, rank, layers=TP_LAYERS, batch
         sync_all()
         times.append(p0.elapsed_time(p1))
     ctx.check_device_error()
+    # per-operation breakdown of one eager prompt pass
+    prewind()
+    ptrace = []
+    net.forward(ptoks, pc, prompt=True, trace=ptrace)
+    torch.cuda.synchronize()
+    p_by_op = {}
+    for (n0, e0_), (n1, e1_) in zip(ptrace[:-1], ptrace[1:]):
+        p_by_op[n1] = p_by_op.get(n1, 0.0) + e0_.elapsed_time(e1_)
+    sync_all()
     pms = torch.tensor([min(times[1:])], dtype=torch.float64, device=device)
     if world > 1:
         dist.all_reduce(pms, op=dist.ReduceOp.MAX)
@@ -655,7 +664,7 @@ def tp70b_decoder(torch, dist, ctx, device, world, rank, layers=TP_LAYERS, batch
                       "eager_step_ms_rank0": round(sum(by_op.values()), 4)},
            "prefill": {"tokens": prefill_tokens, "ms": float(pms[0]), "tok_per_s": prefill_tokens / (float(pms[0]) * 1e-3),
                        "int8_TOPS_per_gpu": 2.0 * prefill_tokens * per_layer * 4 * layers / world / (float(pms[0]) * 1e-3) / 1e12,
-                       "launch": pmode},
+                       "launch": pmode, "eager_ms_by_operation_rank0": {k: round(v, 3) for k, v in p_by_op.items()}},
            "exchange": ("reduce-scatter of int32 partial dots by token rows + all-gather of int8 rows, peer loads/stores in the library's kernels "
                         f"({(world - 1) * batch * H * 4 // world} + {(world - 1) * batch * H // world} bytes per rank and row-parallel layer at decode)") if world > 1
                        else "none (one rank)",

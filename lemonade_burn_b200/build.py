@@ -12,7 +12,7 @@ CSRC = PKG / "csrc"
 LIB = PKG / "liblbk.so"
 OBJ = PKG / "_build"  # object files (git-ignored)
 
-SOURCES = ["lbk_api.cu", "lbk_gemv.cu", "lbk_quant.cu", "lbk_bf16.cu", "lbk_plan.cu", "lbk_sweep.cu", "lbk_gemm.cu", "lbk_noalloc.cu", "lbk_decoder.cu", "lbk_tp.cu", "lbk_model.cu", "lbk_convert.cu", "lbk_probe.cu"]
+SOURCES = ["lbk_api.cu", "lbk_gemv.cu", "lbk_quant.cu", "lbk_bf16.cu", "lbk_plan.cu", "lbk_sweep.cu", "lbk_gemm.cu", "lbk_noalloc.cu", "lbk_decoder.cu", "lbk_tp.cu", "lbk_model.cu", "lbk_convert.cu", "lbk_probe.cu", "lbk_attn_tc.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

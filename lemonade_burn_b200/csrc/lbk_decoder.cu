@@ -1321,6 +1321,8 @@ int lbk_attn_prefill(lbk_ctx *c, const float *q_dev, const uint16_t *kcache_dev,
     if (head_dim != kHd) return fail(LBK_ERR_UNSUPPORTED, "attention kernel is built for head_dim 128, got %zu", head_dim);
     if (kv_heads == 0 || n_heads % kv_heads || n_heads / kv_heads > 8) return fail(LBK_ERR_UNSUPPORTED, "query group size must be 1..8");
     if (n > 65535) return fail(LBK_ERR_UNSUPPORTED, "at most 65535 rows per call");
+    // 64 rows and more: 128-row tiles on tcgen05; fewer: 16-row tiles on mma.sync (a 128-row tile would be mostly padding)
+    if (n >= 64) return launch_attn_prompt_tc(ctx, q_dev, kcache_dev, vcache_dev, pos_dev, n, n_heads, kv_heads, cap, seq, out_dev, st);
     const size_t group = n_heads / kv_heads;
     const size_t warps = (group == 1 || group == 2) ? 4 : group;  // one warp per (query head, 16-row tile)
     const size_t rows_per_block = warps / group * 16;

@@ -147,6 +147,11 @@ int launch_scale_epilogue_group(Ctx *ctx, int n, int32_t *const *dots, float *co
 int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream);
 
 int bf16_init(Ctx *ctx);
+
+// causal attention of a prompt pass on tcgen05 (head_dim 128)
+int attn_tc_init(Ctx *ctx);
+int launch_attn_prompt_tc(Ctx *ctx, const float *q, const uint16_t *kc, const uint16_t *vc, const int32_t *pos_dev, size_t n, size_t nh, size_t kvh,
+                          size_t cap, size_t seq, float *out, cudaStream_t stream);
 int launch_bf16_linear(Ctx *ctx, const float *x, size_t m, const uint16_t *w, size_t rows,
                        size_t cols, float *out, cudaStream_t stream);
 

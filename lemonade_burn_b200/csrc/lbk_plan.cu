@@ -95,6 +95,7 @@ int kernels_init(Ctx *ctx) {
     LBK_TRY(gemm_init(ctx));
     LBK_TRY(sweep_init(ctx));
     LBK_TRY(bf16_init(ctx));
+    LBK_TRY(attn_tc_init(ctx));
     return LBK_OK;
 }
 
