@@ -6,24 +6,30 @@
 //
 // One CTA takes 128 query rows of one head and walks the keys in blocks of 128:
 //
-//   TMA thread      K and V blocks [128 keys][128 dims] bf16 from the cache into a two-stage ring
-//                   (SWIZZLE_128B, two 64-dimension halves each)
+//   TMA thread      K blocks (a ring of three) and V blocks (a ring of two), [128 keys][128 dims] bf16
+//                   from the cache (SWIZZLE_128B, two 64-dimension halves each)
 //   MMA thread      S = Q K^T: tcgen05.mma kind::f16, A = the queries (shared memory, written once by
 //                   the CTA as two bf16 terms hi + lo, log2(e)/sqrt(d) folded in), B = the K block as it
-//                   lies in the cache (K-major), f32 scores in tensor memory; then O_j = P V: A = the
+//                   lies in the cache (K-major), f32 scores in tensor memory; O += P V: A = the
 //                   probabilities from TENSOR MEMORY (two bf16 terms again), B = the V block as it
 //                   lies in the cache: its contraction index (the key) is the strided one, which is
-//                   the MN-major operand form of the instruction, so V is never transposed
-//   4 softmax warps thread r owns query row r = TMEM lane r: a row's maximum and sum are plain loops
-//                   over the thread's own 128 scores (no shuffles); exp, the two bf16 terms of every
-//                   probability written back to tensor memory as the next MMA's A operand; the
-//                   block's P V product is read from tensor memory and added to the running output,
-//                   which lives in the thread's registers with the usual max/sum rescaling
+//                   the MN-major operand form of the instruction, so V is never transposed. The
+//                   output accumulates in tensor memory over all key blocks.
+//   4 softmax warps thread r owns query row r = TMEM lane r: it takes its 128 scores into registers
+//                   (the score buffer is free for the next block's Q K^T from then on), finds the
+//                   row's maximum with a plain loop, and writes 2^(s - m) as two bf16 terms into one
+//                   of two probability buffers in tensor memory. m is the maximum the row's earlier
+//                   probabilities were scaled with; it is only moved (and the output in tensor
+//                   memory and the running sum rescaled, by a whole warp at a time) when a block's
+//                   maximum exceeds it by more than 8, i.e. probabilities stay below 2^8: the
+//                   quotient O / sum at the end does not depend on m.
 //
+// While the threads work on block j the tensor core runs Q K^T of block j + 1 and P V of block j - 1.
 // f32 queries and probabilities as hi + lo (|error| <= 2^-17 |x|) keep the only rounding beyond f32
-// summation the bf16 of the cache itself, as in the decode kernels. What this replaces: the same
-// arithmetic on mma.sync with 16-row tiles per warp (attn_prompt_mma_kernel), which stays for
-// passes of fewer than 64 rows.
+// summation the bf16 of the cache itself, as in the decode kernels; the sums over keys are the
+// tensor core's f32 accumulation (about 2e-8 of the largest output per 16 keys, measured on the bf16
+// head: 5e-6 at 2048 keys). What this replaces: the same arithmetic on mma.sync with 16-row tiles
+// per warp (attn_prompt_mma_kernel), which stays for passes of fewer than 64 rows.
 //
 // Rows of V past the keys written so far may hold anything (they are multiplied by exact zeros,
 // and 0 * NaN is NaN): the block that reaches past them has them zeroed in shared memory first.
@@ -41,14 +47,17 @@ constexpr int kHd = 128;
 constexpr int kTile = 128;                  // query rows per CTA = keys per block
 constexpr int kHalf = kTile * 128;          // bytes of a [128 rows][64 dims] bf16 half tile
 constexpr int kQBytes = 4 * kHalf;          // hi half 0, hi half 1, lo half 0, lo half 1
-constexpr int kStageBytes = 4 * kHalf;      // K half 0, K half 1, V half 0, V half 1
-constexpr int kStages = 2;
-constexpr int kBars = kQBytes + kStages * kStageBytes;
-constexpr int kMisc = kBars + 16 * 8;
+constexpr int kBlockBytes = 2 * kHalf;      // a K or V block: two halves
+constexpr int kKStages = 3, kVStages = 2;
+constexpr int kK0 = kQBytes, kV0 = kK0 + kKStages * kBlockBytes;
+constexpr int kBars = kV0 + kVStages * kBlockBytes;
+constexpr int kMisc = kBars + 24 * 8;
 constexpr int kSmem = kMisc + 64 + 1024;
+static_assert(kSmem <= 232448, "shared memory budget");
 constexpr int kThreads = 6 * 32;            // warps 0-3 softmax (TMEM lane quadrants), 4 TMA, 5 MMA
 constexpr uint32_t kTmemCols = 512;
-constexpr uint32_t kColS = 0, kColO = 128, kColPhi = 256, kColPlo = 320;
+constexpr uint32_t kColS = 0, kColO = 128, kColP = 256;  // P buffer b: hi at kColP + 128 b, lo 64 columns further
+constexpr float kRescaleStep = 8.0f;        // in units of log 2
 
 struct AttnParams {
     CUtensorMap k, v;     // bytes [cache rows][256], box [128][128], SWIZZLE_128B
@@ -118,14 +127,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(sm + kMisc);
     volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kMisc + 4);
     auto bar = [&](int idx) { return bar0 + idx * 8; };
-    constexpr int kKFull = 0, kVFull = 2, kKvEmpty = 4, kSFull = 6, kPReady = 7, kOFull = 8;
+    constexpr int kKFull = 0, kKEmpty = 3, kVFull = 6, kVEmpty = 8, kSFull = 10, kSFree = 11, kPReady = 12, kOFull = 13;
     if (tid == 0) {
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < kKStages; ++s) {
             ptx::mbar_init(bar(kKFull + s), 1);
+            ptx::mbar_init(bar(kKEmpty + s), 1);
+        }
+        for (int s = 0; s < kVStages; ++s) {
             ptx::mbar_init(bar(kVFull + s), 1);
-            ptx::mbar_init(bar(kKvEmpty + s), 1);
+            ptx::mbar_init(bar(kVEmpty + s), 1);
         }
         ptx::mbar_init(bar(kSFull), 1);
+        ptx::mbar_init(bar(kSFree), 4);
         ptx::mbar_init(bar(kPReady), 4);
         ptx::mbar_init(bar(kOFull), 1);
         *s_abort = 0;
@@ -181,20 +194,30 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     if (warp == 4) {
         // ================= TMA producer =================
         if (lane == 0) {
+            int ks = 0, kround = 0;
             for (int j = 0; j < nb; ++j) {
-                const int s = j & 1;
-                if (j >= kStages && !wait_bar(bar(kKvEmpty + s), ((j >> 1) - 1) & 1, s_abort)) {
+                const int y = cache_row0 + j * kTile;
+                if (kround > 0 && !wait_bar(bar(kKEmpty + ks), (kround - 1) & 1, s_abort)) {
                     ok = false;
                     break;
                 }
-                const uint32_t st = base + kQBytes + s * kStageBytes;
-                const int y = cache_row0 + j * kTile;
-                ptx::mbar_arrive_expect_tx(bar(kKFull + s), 2 * kHalf);
-                ptx::tma_load_2d(st, &p.k, bar(kKFull + s), 0, y);
-                ptx::tma_load_2d(st + kHalf, &p.k, bar(kKFull + s), 128, y);
-                ptx::mbar_arrive_expect_tx(bar(kVFull + s), 2 * kHalf);
-                ptx::tma_load_2d(st + 2 * kHalf, &p.v, bar(kVFull + s), 0, y);
-                ptx::tma_load_2d(st + 3 * kHalf, &p.v, bar(kVFull + s), 128, y);
+                const uint32_t kst = base + kK0 + ks * kBlockBytes;
+                ptx::mbar_arrive_expect_tx(bar(kKFull + ks), kBlockBytes);
+                ptx::tma_load_2d(kst, &p.k, bar(kKFull + ks), 0, y);
+                ptx::tma_load_2d(kst + kHalf, &p.k, bar(kKFull + ks), 128, y);
+                if (++ks == kKStages) {
+                    ks = 0;
+                    ++kround;
+                }
+                const int vs = j & 1;
+                if (j >= kVStages && !wait_bar(bar(kVEmpty + vs), ((j >> 1) - 1) & 1, s_abort)) {
+                    ok = false;
+                    break;
+                }
+                const uint32_t vst = base + kV0 + vs * kBlockBytes;
+                ptx::mbar_arrive_expect_tx(bar(kVFull + vs), kBlockBytes);
+                ptx::tma_load_2d(vst, &p.v, bar(kVFull + vs), 0, y);
+                ptx::tma_load_2d(vst + kHalf, &p.v, bar(kVFull + vs), 128, y);
             }
         }
     } else if (warp == 5) {
@@ -204,46 +227,53 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             constexpr uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
             constexpr uint32_t idesc_o = idesc_s | (1u << 16);
             const uint64_t q_desc = smem_desc_sw128(base);
-            auto issue_s = [&](int j) {  // S = Qhi K^T + Qlo K^T over the 8 steps of 16 dimensions
-                const uint64_t k_desc = smem_desc_sw128(base + kQBytes + (j & 1) * kStageBytes);
+            int ks = 0, kphase = 0;  // ring position of the K block the next Q K^T reads
+            auto issue_s = [&]() {   // S = Qhi K^T + Qlo K^T over the 8 steps of 16 dimensions
+                const uint64_t k_desc = smem_desc_sw128(base + kK0 + ks * kBlockBytes);
 #pragma unroll
                 for (int t = 0; t < 2; ++t)
 #pragma unroll
-                    for (int ks = 0; ks < 8; ++ks) {
-                        const uint64_t off = static_cast<uint64_t>((ks >> 2) * (kHalf >> 4) + (ks & 3) * 2);
-                        umma_f16_ss(tmem_base + kColS, q_desc + static_cast<uint64_t>(t * 2 * (kHalf >> 4)) + off, k_desc + off, idesc_s, (t | ks) ? 1u : 0u);
+                    for (int st = 0; st < 8; ++st) {
+                        const uint64_t off = static_cast<uint64_t>((st >> 2) * (kHalf >> 4) + (st & 3) * 2);
+                        umma_f16_ss(tmem_base + kColS, q_desc + static_cast<uint64_t>(t * 2 * (kHalf >> 4)) + off, k_desc + off, idesc_s, (t | st) ? 1u : 0u);
                     }
                 umma_commit(bar(kSFull));
+                umma_commit(bar(kKEmpty + ks));
+                if (++ks == kKStages) {
+                    ks = 0;
+                    kphase ^= 1;
+                }
             };
-            if (!wait_bar(bar(kKFull), 0, s_abort)) ok = false;
+            if (!wait_bar(bar(kKFull + 0), 0, s_abort)) ok = false;
             if (ok) {
                 tc_fence_after();
-                issue_s(0);
+                issue_s();
             }
             for (int j = 0; j < nb && ok; ++j) {
-                const int s = j & 1;
-                if (!wait_bar(bar(kPReady), j & 1, s_abort) || !wait_bar(bar(kVFull + s), (j >> 1) & 1, s_abort)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                const uint64_t v_desc = smem_desc_mn_sw128(base + kQBytes + s * kStageBytes + 2 * kHalf);
-#pragma unroll
-                for (int t = 0; t < 2; ++t)
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)  // 16 keys a step: 8 columns of P, two 1024-byte key groups of V
-                        umma_f16_ts(tmem_base + kColO, tmem_base + (t ? kColPlo : kColPhi) + ks * 8, v_desc + static_cast<uint64_t>(ks * (2048 >> 4)), idesc_o,
-                                    (t | ks) ? 1u : 0u);
-                umma_commit(bar(kOFull));
-                umma_commit(bar(kKvEmpty + s));  // every MMA that read this stage is before this point
                 if (j + 1 < nb) {
-                    if (!wait_bar(bar(kKFull + (s ^ 1)), ((j + 1) >> 1) & 1, s_abort)) {
+                    // the threads hold block j's scores in registers: the score buffer is free
+                    if (!wait_bar(bar(kSFree), j & 1, s_abort) || !wait_bar(bar(kKFull + ks), kphase, s_abort)) {
                         ok = false;
                         break;
                     }
                     tc_fence_after();
-                    issue_s(j + 1);
+                    issue_s();
                 }
+                const int vs = j & 1;
+                if (!wait_bar(bar(kPReady), j & 1, s_abort) || !wait_bar(bar(kVFull + vs), (j >> 1) & 1, s_abort)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t v_desc = smem_desc_mn_sw128(base + kV0 + vs * kBlockBytes);
+                const uint32_t p_hi = tmem_base + kColP + (j & 1) * 128;
+#pragma unroll
+                for (int t = 0; t < 2; ++t)
+#pragma unroll
+                    for (int st = 0; st < 8; ++st)  // 16 keys a step: 8 columns of P, two 1024-byte key groups of V
+                        umma_f16_ts(tmem_base + kColO, p_hi + t * 64 + st * 8, v_desc + static_cast<uint64_t>(st * (2048 >> 4)), idesc_o, (j | t | st) ? 1u : 0u);
+                umma_commit(bar(kOFull));
+                umma_commit(bar(kVEmpty + vs));
             }
         }
     } else {
@@ -251,61 +281,87 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
         const int r = warp * 32 + lane;
         const int qpos = pos0 + row0 + r;  // the last key this row sees
         const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
-        float o[kHd];
-#pragma unroll
-        for (int i = 0; i < kHd; ++i) o[i] = 0.0f;
-        float m = -INFINITY, l = 0.0f;
+        float m = -INFINITY, l = 0.0f;     // m: the maximum the probabilities so far were scaled with
+        // a wait whose outcome the whole warp shares: the tensor-memory loads and stores below are warp-wide instructions
+        auto wait_all = [&](uint32_t b, uint32_t parity) { return __all_sync(0xffffffffu, wait_bar(b, parity, s_abort)) != 0; };
         for (int j = 0; j < nb; ++j) {
-            if (!wait_bar(bar(kSFull), j & 1, s_abort)) {
+            if (!wait_all(bar(kSFull), j & 1)) {
                 ok = false;
                 break;
             }
             tc_fence_after();
+            uint32_t sv[kTile];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_field + kColS + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(bar(kSFree));
             const int key0 = j * kTile;
             const bool diag = key0 + kTile - 1 > qpos;  // some keys of this block are in this row's future
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + lane_field + kColS + c * 32, v);
-                tmem_ld_wait();
+            if (diag) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (!diag || key0 + c * 32 + i <= qpos) mx = fmaxf(mx, __uint_as_float(v[i]));
+                for (int i = 0; i < kTile; ++i)
+                    if (key0 + i > qpos) sv[i] = 0xff800000u;  // -inf: 2^(-inf - m) = 0
             }
-            // key 0 <= qpos always: from the first block on the maximum is finite for rows that exist
-            const float nm = fmaxf(m, mx);
-            const float corr = ex2(m - nm);
-            m = nm;
-            float ps = 0.0f;
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kTile; i += 4) {
+                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            // key 0 <= qpos always: in the first block the maximum is finite for rows that exist
+            if (__any_sync(0xffffffffu, j == 0 || mx > m + kRescaleStep)) {
+                const float nm = fmaxf(m, mx);
+                if (j > 0) {
+                    // the output so far (P V of every earlier block) is complete and nothing adds to it before
+                    // this warp says its probabilities are ready
+                    if (!wait_all(bar(kOFull), (j - 1) & 1)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const float corr = ex2(m - nm);
+                    l *= corr;
 #pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t v[32];
+                        tmem_ld32(tmem_base + lane_field + kColO + c * 32, v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
+                        tmem_st32(tmem_base + lane_field + kColO + c * 32, v);
+                    }
+                }
+                m = nm;
+            }
+            float ps0 = 0.0f, ps1 = 0.0f;
+            const uint32_t p_hi = tmem_base + lane_field + kColP + (j & 1) * 128;
+#pragma unroll
             for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + lane_field + kColS + c * 32, v);
-                tmem_ld_wait();
                 uint32_t ph[16], pl[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float e0 = ex2(__uint_as_float(v[2 * i]) - nm), e1 = ex2(__uint_as_float(v[2 * i + 1]) - nm);
-                    if (diag) {
-                        if (key0 + c * 32 + 2 * i > qpos) e0 = 0.0f;
-                        if (key0 + c * 32 + 2 * i + 1 > qpos) e1 = 0.0f;
-                    }
-                    ps += e0 + e1;
+                    const float e0 = ex2(__uint_as_float(sv[c * 32 + 2 * i]) - m), e1 = ex2(__uint_as_float(sv[c * 32 + 2 * i + 1]) - m);
+                    ps0 += e0;
+                    ps1 += e1;
                     split_pair(e0, e1, ph[i], pl[i]);
                 }
-                tmem_st16(tmem_base + lane_field + kColPhi + c * 16, ph);
-                tmem_st16(tmem_base + lane_field + kColPlo + c * 16, pl);
+                tmem_st16(p_hi + c * 16, ph);
+                tmem_st16(p_hi + 64 + c * 16, pl);
             }
-            l = l * corr + ps;
+            l += ps0 + ps1;
             // rows of V that no kernel has written: zero them before the tensor core multiplies them by zeros
             if (key0 + kTile > written) {
-                if (!wait_bar(bar(kVFull + (j & 1)), (j >> 1) & 1, s_abort)) {
+                if (!wait_all(bar(kVFull + (j & 1)), (j >> 1) & 1)) {
                     ok = false;
                     break;
                 }
                 if (key0 + r >= written) {
-                    uint8_t *vrow = sm + kQBytes + (j & 1) * kStageBytes + 2 * kHalf + r * 128;
+                    uint8_t *vrow = sm + kV0 + (j & 1) * kBlockBytes + r * 128;
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         *reinterpret_cast<uint4 *>(vrow + u * 16) = make_uint4(0u, 0u, 0u, 0u);
@@ -318,30 +374,27 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(bar(kPReady));
-            if (corr != 1.0f) {
-#pragma unroll
-                for (int i = 0; i < kHd; ++i) o[i] *= corr;
-            }
-            if (!wait_bar(bar(kOFull), j & 1, s_abort)) {
-                ok = false;
-                break;
-            }
+        }
+        if (ok && nb > 0) {
+            if (!wait_all(bar(kOFull), (nb - 1) & 1)) ok = false;
             tc_fence_after();
-#pragma unroll
+        }
+        if (ok && nb > 0) {
+            const float inv = 1.0f / l;
+            float *dst = p.out + (static_cast<size_t>(row0 + (r < rows_here ? r : 0)) * p.nh + head) * kHd;
+#pragma unroll 1
             for (int c = 0; c < 4; ++c) {
                 uint32_t v[32];
                 tmem_ld32(tmem_base + lane_field + kColO + c * 32, v);
                 tmem_ld_wait();
+                if (r < rows_here) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c * 32 + i] += __uint_as_float(v[i]);
+                    for (int i = 0; i < 32; i += 4)
+                        *reinterpret_cast<float4 *>(dst + c * 32 + i) = make_float4(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv,
+                                                                                    __uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+                }
             }
             tc_fence_before();
-        }
-        if (ok && r < rows_here) {
-            const float inv = 1.0f / l;
-            float *dst = p.out + (static_cast<size_t>(row0 + r) * p.nh + head) * kHd;
-#pragma unroll
-            for (int i = 0; i < kHd; i += 4) *reinterpret_cast<float4 *>(dst + i) = make_float4(o[i] * inv, o[i + 1] * inv, o[i + 2] * inv, o[i + 3] * inv);
         }
     }
     if (!ok && pos_ok && lane == 0) atomicExch(p.err_word, 5);

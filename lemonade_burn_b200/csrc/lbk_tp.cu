@@ -255,8 +255,8 @@ __global__ void __launch_bounds__(256) tp_reduce_scale_kernel(const TpPtrs peers
 // call ahead of a peer because every call needs every peer's value of that call.
 
 constexpr int kNqThreads = 1024;
-constexpr int kNqCache = 8;  // float4 per thread: column slices of up to 32768 columns
-constexpr int kRgThreads = 1024;
+constexpr int kNqCache = 8;  // float4 per thread: column slices of up to 32768 columns (8192 with 256 threads)
+constexpr size_t kTpManyRows = 256;  // from this many token rows on (a prompt pass) the exchange kernels run 256 threads a block
 
 __device__ __forceinline__ float block_sum_f(float v, float *s_red, int nwarps) {
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -322,13 +322,16 @@ __device__ __forceinline__ float exchange_stat(const TpPtrs &peers, int world, i
 // One CTA per token row. PRE = LBK_PRE_RMS: s = x; LBK_PRE_RELU2_MUL_RMS: s = relu(x)^2 * y.
 // Then n_i = (s_i * r) * w_i with r = 1/sqrt(sum over ALL ranks of s^2 / k_full + eps), and the
 // quantiser of quant.rs:100-118 with the maximum over all ranks.
-template <int PRE>
-__global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ x,
+// T threads a block: 1024 for a decode batch (few rows: the latency of one row counts, and rows of up to
+// 32768 columns fit), 256 for the many rows of a prompt pass when a row fits (four rows in flight per SM
+// instead of one: a row's chain of load, three block reductions and two exchanges no longer idles the SM).
+template <int PRE, int T>
+__global__ void __launch_bounds__(T) tp_norm_quant_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ x,
                                                                   const float *__restrict__ y, const float *__restrict__ w, int kl, int k_full,
                                                                   float eps, int8_t *__restrict__ q, float *__restrict__ scale,
                                                                   int32_t *__restrict__ sum, int *err_word, uint32_t wait_limit) {
-    __shared__ float s_red[kNqThreads / 32];
-    __shared__ int s_redi[kNqThreads / 32];
+    __shared__ float s_red[T / 32];
+    __shared__ int s_redi[T / 32];
     __shared__ float s_bcast;
     // Launched with programmatic stream serialisation: the kernel behind this one (the row-parallel
     // GEMM) may be scheduled now and stream its first weight tiles while this one runs; it waits for
@@ -347,7 +350,7 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
     float ss = 0.0f;
 #pragma unroll
     for (int j = 0; j < kNqCache; ++j) {
-        const int i = tid + j * kNqThreads;
+        const int i = tid + j * T;
         v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
         if (i < n4) {
             const float4 a = xr[i];
@@ -361,7 +364,7 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
         }
         ss += v[j].x * v[j].x + v[j].y * v[j].y + v[j].z * v[j].z + v[j].w * v[j].w;
     }
-    ss = block_sum_f(ss, s_red, kNqThreads / 32);
+    ss = block_sum_f(ss, s_red, T / 32);
     if (tid < 32) {
         const float total = exchange_stat(peers, world, rank, par, 0, row, seq, ss, true, err_word, wait_limit);
         if (tid == 0) s_bcast = 1.0f / sqrtf(total / static_cast<float>(k_full) + eps);
@@ -371,14 +374,14 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
     float am = 0.0f;
 #pragma unroll
     for (int j = 0; j < kNqCache; ++j) {
-        const int i = tid + j * kNqThreads;
+        const int i = tid + j * T;
         if (i < n4) {
             const float4 gw = __ldg(reinterpret_cast<const float4 *>(w) + i);
             v[j] = make_float4(v[j].x * r * gw.x, v[j].y * r * gw.y, v[j].z * r * gw.z, v[j].w * r * gw.w);
             am = fmaxf(am, fmaxf(fmaxf(fabsf(v[j].x), fabsf(v[j].y)), fmaxf(fabsf(v[j].z), fabsf(v[j].w))));  // fmaxf drops a NaN, as f32::max does
         }
     }
-    am = block_max_f(am, s_red, kNqThreads / 32);
+    am = block_max_f(am, s_red, T / 32);
     __syncthreads();  // s_bcast has been read by everybody
     if (tid < 32) {
         const float total = exchange_stat(peers, world, rank, par, 1, row, seq, am, false, err_word, wait_limit);
@@ -390,14 +393,14 @@ __global__ void __launch_bounds__(kNqThreads) tp_norm_quant_kernel(const TpPtrs 
     int acc = 0;
 #pragma unroll
     for (int j = 0; j < kNqCache; ++j) {
-        const int i = tid + j * kNqThreads;
+        const int i = tid + j * T;
         if (i < n4) {
             const int q0 = quant_one(v[j].x, sc), q1 = quant_one(v[j].y, sc), q2 = quant_one(v[j].z, sc), q3 = quant_one(v[j].w, sc);
             acc += q0 + q1 + q2 + q3;
             reinterpret_cast<uint32_t *>(qr)[i] = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | (static_cast<uint32_t>(q3 & 255) << 24);
         }
     }
-    acc = block_sum_i(acc, s_redi, kNqThreads / 32);
+    acc = block_sum_i(acc, s_redi, T / 32);
     if (tid == 0) {
         scale[row] = sc;
         sum[row] = acc;
@@ -426,9 +429,11 @@ struct RgArgs {
 };
 
 // One CTA per token this rank owns (a single CTA if it owns none: it still raises and awaits the flags).
-__global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const TpPtrs peers, const RgArgs a) {
-    __shared__ float s_red[kRgThreads / 32];
-    __shared__ int s_redi[kRgThreads / 32];
+// T threads a block as in tp_norm_quant_kernel: 1024 for decode batches, 256 for the rows of a prompt pass.
+template <int T>
+__global__ void __launch_bounds__(T) tp_reduce_norm_gather_kernel(const TpPtrs peers, const RgArgs a) {
+    __shared__ float s_red[T / 32];
+    __shared__ int s_redi[T / 32];
     ptx::pdl_trigger();  // the column-parallel GEMM behind this kernel may start fetching its weights
     ptx::pdl_wait();     // the partial dots (the GEMM before this kernel) are complete from here on
     const int tid = threadIdx.x, world = a.world, rank = a.rank, H = a.hidden;
@@ -459,11 +464,12 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
     }
     if (lt < own) {
         const int t = t0 + lt, n4 = H >> 2;
-        float4 v[2];
+        constexpr int kIt = kTpMaxWidth / 4 / T;  // 16-byte units of a row per thread
+        float4 v[kIt];
         float ss = 0.0f;
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const int g = tid + it * kRgThreads;
+        for (int it = 0; it < kIt; ++it) {
+            const int g = tid + it * T;
             v[it] = make_float4(0.f, 0.f, 0.f, 0.f);
             if (g < n4) {
                 float4 x = reinterpret_cast<const float4 *>(a.xres + static_cast<size_t>(lt) * H)[g];
@@ -495,11 +501,11 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
             }
             ss += v[it].x * v[it].x + v[it].y * v[it].y + v[it].z * v[it].z + v[it].w * v[it].w;
         }
-        const float r = 1.0f / sqrtf(block_sum_f(ss, s_red, kRgThreads / 32) / static_cast<float>(H) + a.eps);
+        const float r = 1.0f / sqrtf(block_sum_f(ss, s_red, T / 32) / static_cast<float>(H) + a.eps);
         float am = 0.0f;
 #pragma unroll
-        for (int it = 0; it < 2; ++it) {
-            const int g = tid + it * kRgThreads;
+        for (int it = 0; it < kIt; ++it) {
+            const int g = tid + it * T;
             if (g < n4) {
                 const float4 gw = __ldg(reinterpret_cast<const float4 *>(a.w) + g);
                 v[it] = make_float4(v[it].x * r * gw.x, v[it].y * r * gw.y, v[it].z * r * gw.z, v[it].w * r * gw.w);
@@ -508,17 +514,17 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
         }
         if (a.gather_f32) {
 #pragma unroll
-            for (int it = 0; it < 2; ++it) {
-                const int g = tid + it * kRgThreads;
+            for (int it = 0; it < kIt; ++it) {
+                const int g = tid + it * T;
                 if (g < n4)
                     for (int p = 0; p < world; ++p) reinterpret_cast<float4 *>(peers.r[p]->gather_f + static_cast<size_t>(t) * H)[g] = v[it];
             }
         } else {
-            const float sc = __fdiv_rn(127.0f, fmaxf(block_max_f(am, s_red, kRgThreads / 32), 1e-5f));
+            const float sc = __fdiv_rn(127.0f, fmaxf(block_max_f(am, s_red, T / 32), 1e-5f));
             int acc = 0;
 #pragma unroll
-            for (int it = 0; it < 2; ++it) {
-                const int g = tid + it * kRgThreads;
+            for (int it = 0; it < kIt; ++it) {
+                const int g = tid + it * T;
                 if (g < n4) {
                     const int q0 = quant_one(v[it].x, sc), q1 = quant_one(v[it].y, sc), q2 = quant_one(v[it].z, sc), q3 = quant_one(v[it].w, sc);
                     acc += q0 + q1 + q2 + q3;
@@ -526,7 +532,7 @@ __global__ void __launch_bounds__(kRgThreads) tp_reduce_norm_gather_kernel(const
                     for (int p = 0; p < world; ++p) reinterpret_cast<uint32_t *>(peers.r[p]->gather_q + static_cast<size_t>(t) * H)[g] = word;
                 }
             }
-            acc = block_sum_i(acc, s_redi, kRgThreads / 32);
+            acc = block_sum_i(acc, s_redi, T / 32);
             if (tid < world) {
                 peers.r[tid]->gather_scale[t] = sc;
                 peers.r[tid]->gather_sum[t] = acc;
@@ -781,13 +787,19 @@ int lbk_tp_norm_quant(lbk_tp_comm *t, int pre, const float *x_dev, const float *
         return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_norm_quant needs 16-byte aligned buffers");
     LBK_CUDA(cudaSetDevice(tc->ctx->device));
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    const dim3 grid(static_cast<unsigned>(m)), block(kNqThreads);
-    if (pre == LBK_PRE_RMS)
-        LBK_CUDA(launch_chained(tp_norm_quant_kernel<LBK_PRE_RMS>, grid, block, 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local),
-                                static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
-    else
-        LBK_CUDA(launch_chained(tp_norm_quant_kernel<LBK_PRE_RELU2_MUL_RMS>, grid, block, 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev,
-                                static_cast<int>(k_local), static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
+    const dim3 grid(static_cast<unsigned>(m));
+    const bool small_blocks = m >= kTpManyRows && k_local <= static_cast<size_t>(kNqCache) * 256 * 4;
+#define LBK_NQ_LAUNCH(PRE, T)                                                                                                                            \
+    LBK_CUDA(launch_chained(tp_norm_quant_kernel<PRE, T>, grid, dim3(T), 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), \
+                            static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit))
+    if (pre == LBK_PRE_RMS) {
+        if (small_blocks) LBK_NQ_LAUNCH(LBK_PRE_RMS, 256);
+        else LBK_NQ_LAUNCH(LBK_PRE_RMS, 1024);
+    } else {
+        if (small_blocks) LBK_NQ_LAUNCH(LBK_PRE_RELU2_MUL_RMS, 256);
+        else LBK_NQ_LAUNCH(LBK_PRE_RELU2_MUL_RMS, 1024);
+    }
+#undef LBK_NQ_LAUNCH
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
@@ -822,7 +834,9 @@ int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev
     a.err_word = tc->ctx->err_word;
     a.wait_limit = tc->wait_limit;
     const int t0 = a.rank * a.mt, own = a.m - t0 < 0 ? 0 : (a.m - t0 < a.mt ? a.m - t0 : a.mt);
-    LBK_CUDA(launch_chained(tp_reduce_norm_gather_kernel, dim3(static_cast<unsigned>(own > 0 ? own : 1)), dim3(kRgThreads), 0, static_cast<cudaStream_t>(stream), ptrs_of(tc), a));
+    const dim3 rgrid(static_cast<unsigned>(own > 0 ? own : 1));
+    if (m >= kTpManyRows) LBK_CUDA(launch_chained(tp_reduce_norm_gather_kernel<256>, rgrid, dim3(256), 0, static_cast<cudaStream_t>(stream), ptrs_of(tc), a));
+    else LBK_CUDA(launch_chained(tp_reduce_norm_gather_kernel<1024>, rgrid, dim3(1024), 0, static_cast<cudaStream_t>(stream), ptrs_of(tc), a));
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;

@@ -292,6 +292,10 @@ def test_tp_decoder_step_with_one_rank(oracle, ctx, heads, kv):
     comm = tp.TpComm(ctx, 1, 0)
     try:
         _tp_decoder_case(ctx, comm, 1, 0, cfg, seed=3 + heads, b=3, steps=3, prompt_len=9)
+        # a prompt pass of 300 rows: the exchange kernels' 256-thread form (256 rows and more) and the
+        # 128-row attention tiles on tcgen05 (64 rows and more), the last tile ragged
+        long_cfg = model.Config(heads * 128, 1536, heads, kv, 2, 1024, 1e-5, 500000.0, 320)
+        _tp_decoder_case(ctx, comm, 1, 0, long_cfg, seed=5 + heads, b=1, steps=1, prompt_len=300)
     finally:
         comm.close()
 
