@@ -52,9 +52,12 @@ constexpr int kKStages = 3, kVStages = 2;
 constexpr int kK0 = kQBytes, kV0 = kK0 + kKStages * kBlockBytes;
 constexpr int kBars = kV0 + kVStages * kBlockBytes;
 constexpr int kMisc = kBars + 24 * 8;
-constexpr int kSmem = kMisc + 64 + 1024;
+constexpr int kPairMax = kMisc + 64;         // [2 halves][128 rows] f32: a row's two threads tell each other their maxima
+constexpr int kSmem = kPairMax + 2 * kTile * 4 + 1024;
 static_assert(kSmem <= 232448, "shared memory budget");
-constexpr int kThreads = 6 * 32;            // warps 0-3 softmax (TMEM lane quadrants), 4 TMA, 5 MMA
+constexpr int kSoftWarps = 8;                // two per TMEM lane quadrant: warp w and w + 4 share rows, each takes 64 of a block's 128 keys
+constexpr int kTmaWarp = 8, kMmaWarp = 9;
+constexpr int kThreads = 10 * 32;
 constexpr uint32_t kTmemCols = 512;
 constexpr uint32_t kColS = 0, kColO = 128, kColP = 256;  // P buffer b: hi at kColP + 128 b, lo 64 columns further
 constexpr float kRescaleStep = 8.0f;        // in units of log 2
@@ -138,13 +141,13 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             ptx::mbar_init(bar(kVEmpty + s), 1);
         }
         ptx::mbar_init(bar(kSFull), 1);
-        ptx::mbar_init(bar(kSFree), 4);
-        ptx::mbar_init(bar(kPReady), 4);
+        ptx::mbar_init(bar(kSFree), kSoftWarps);
+        ptx::mbar_init(bar(kPReady), kSoftWarps);
         ptx::mbar_init(bar(kOFull), 1);
         *s_abort = 0;
         ptx::fence_barrier_init();
     }
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tmem_alloc(base + kMisc, kTmemCols);
         tmem_relinquish();
     }
@@ -161,12 +164,12 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     if (!pos_ok && tid == 0) atomicExch(p.err_word, 7);
     // the queries of the tile: scaled, as hi + lo, in the K-major SWIZZLE_128B layout (row r of a half
     // tile at r * 128, its 16-byte units XOR-ed with r & 7)
-    if (warp < 4) {
-        const int r = warp * 32 + lane;
+    if (warp < kSoftWarps) {
+        const int r = (warp & 3) * 32 + lane;
         const bool live = r < rows_here && pos_ok;
         const float *qr = p.q + (static_cast<size_t>(row0 + (live ? r : 0)) * p.nh + head) * kHd;
 #pragma unroll 4
-        for (int u = 0; u < 16; ++u) {  // 16-byte unit u of the row: dimensions 8u .. 8u+7
+        for (int u = (warp >> 2) * 8; u < (warp >> 2) * 8 + 8; ++u) {  // 16-byte unit u of the row: dimensions 8u .. 8u+7; a row's two threads take a half each
             float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
             if (live) {
                 a = *reinterpret_cast<const float4 *>(qr + 8 * u);
@@ -191,7 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     const int nb = ok ? n_blocks : 0;
     const int cache_row0 = (p.seq * p.kvh + kh) * p.cap;
 
-    if (warp == 4) {
+    if (warp == kTmaWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
             int ks = 0, kround = 0;
@@ -220,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
                 ptx::tma_load_2d(vst + kHalf, &p.v, bar(kVFull + vs), 128, y);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kMmaWarp) {
         // ================= MMA issuer (one thread) =================
         if (lane == 0 && nb > 0) {
             // D f32, A and B bf16, M = 128, N = 128; for P V the B operand is MN-major (bit 16)
@@ -277,71 +280,79 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             }
         }
     } else {
-        // ================= softmax and output (warps 0..3 = TMEM lane quadrants) =================
-        const int r = warp * 32 + lane;
+        // ================= softmax and output (warps 0..7: quadrant warp & 3, key half warp >> 2) =================
+        const int quad = warp & 3, kh2 = warp >> 2;
+        const int r = quad * 32 + lane;
         const int qpos = pos0 + row0 + r;  // the last key this row sees
-        const uint32_t lane_field = static_cast<uint32_t>(warp * 32) << 16;
-        float m = -INFINITY, l = 0.0f;     // m: the maximum the probabilities so far were scaled with
+        const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
+        float *s_pair = reinterpret_cast<float *>(sm + kPairMax);
+        float m = -INFINITY, l = 0.0f;     // m: the maximum the probabilities so far were scaled with; l: this thread's half of the row's sum
         // a wait whose outcome the whole warp shares: the tensor-memory loads and stores below are warp-wide instructions
         auto wait_all = [&](uint32_t b, uint32_t parity) { return __all_sync(0xffffffffu, wait_bar(b, parity, s_abort)) != 0; };
+        auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory"); };  // the two warps of a quadrant
+        // Every warp meets its partner exactly twice per block and once after the loop, whatever a wait
+        // returned: a warp whose wait gave up (ok = false) skips the work, never the meetings.
         for (int j = 0; j < nb; ++j) {
-            if (!wait_all(bar(kSFull), j & 1)) {
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            uint32_t sv[kTile];
+            uint32_t sv[kTile / 2];  // keys kh2 * 64 .. + 63 of the block
+            float *pair = s_pair;
+            if (ok && !wait_all(bar(kSFull), j & 1)) ok = false;
+            if (ok) {
+                tc_fence_after();
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(tmem_base + lane_field + kColS + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
-            tmem_ld_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kSFree));
-            const int key0 = j * kTile;
-            const bool diag = key0 + kTile - 1 > qpos;  // some keys of this block are in this row's future
-            if (diag) {
+                for (int c = 0; c < 2; ++c) tmem_ld32(tmem_base + lane_field + kColS + kh2 * 64 + c * 32, reinterpret_cast<uint32_t(&)[32]>(sv[c * 32]));
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive(bar(kSFree));
+                const int key0 = j * kTile + kh2 * 64;
+                if (key0 + 63 > qpos) {  // some of these keys are in this row's future
 #pragma unroll
-                for (int i = 0; i < kTile; ++i)
-                    if (key0 + i > qpos) sv[i] = 0xff800000u;  // -inf: 2^(-inf - m) = 0
-            }
-            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+                    for (int i = 0; i < kTile / 2; ++i)
+                        if (key0 + i > qpos) sv[i] = 0xff800000u;  // -inf: 2^(-inf - m) = 0
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
 #pragma unroll
-            for (int i = 0; i < kTile; i += 4) {
-                mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
-                mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
-                mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
-                mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+                for (int i = 0; i < kTile / 2; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(sv[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(sv[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(sv[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(sv[i + 3]));
+                }
+                pair[kh2 * kTile + r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
             }
-            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            pair_sync();
+            const float mx = fmaxf(pair[r], pair[kTile + r]);  // the row's maximum over the block; both threads of the row hold the same m and mx
+            pair_sync();  // both have read before the next block's maxima are written
+            if (!ok) continue;
             // key 0 <= qpos always: in the first block the maximum is finite for rows that exist
             if (__any_sync(0xffffffffu, j == 0 || mx > m + kRescaleStep)) {
                 const float nm = fmaxf(m, mx);
                 if (j > 0) {
                     // the output so far (P V of every earlier block) is complete and nothing adds to it before
-                    // this warp says its probabilities are ready
+                    // both warps of the quadrant say their probabilities are ready
                     if (!wait_all(bar(kOFull), (j - 1) & 1)) {
                         ok = false;
-                        break;
+                        continue;
                     }
                     tc_fence_after();
                     const float corr = ex2(m - nm);
                     l *= corr;
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {  // this warp's 64 columns of the output
                         uint32_t v[32];
-                        tmem_ld32(tmem_base + lane_field + kColO + c * 32, v);
+                        tmem_ld32(tmem_base + lane_field + kColO + kh2 * 64 + c * 32, v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * corr);
-                        tmem_st32(tmem_base + lane_field + kColO + c * 32, v);
+                        tmem_st32(tmem_base + lane_field + kColO + kh2 * 64 + c * 32, v);
                     }
                 }
                 m = nm;
             }
             float ps0 = 0.0f, ps1 = 0.0f;
-            const uint32_t p_hi = tmem_base + lane_field + kColP + (j & 1) * 128;
+            const uint32_t p_hi = tmem_base + lane_field + kColP + (j & 1) * 128 + kh2 * 32;  // two keys a column
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t ph[16], pl[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -355,18 +366,15 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             }
             l += ps0 + ps1;
             // rows of V that no kernel has written: zero them before the tensor core multiplies them by zeros
-            if (key0 + kTile > written) {
+            if (j * kTile + kTile > written) {
                 if (!wait_all(bar(kVFull + (j & 1)), (j >> 1) & 1)) {
                     ok = false;
-                    break;
+                    continue;
                 }
-                if (key0 + r >= written) {
-                    uint8_t *vrow = sm + kV0 + (j & 1) * kBlockBytes + r * 128;
+                if (j * kTile + r >= written) {  // thread (row r, half kh2) zeroes one 64-dimension half of V row r
+                    uint8_t *vrow = sm + kV0 + (j & 1) * kBlockBytes + kh2 * kHalf + r * 128;
 #pragma unroll
-                    for (int u = 0; u < 8; ++u) {
-                        *reinterpret_cast<uint4 *>(vrow + u * 16) = make_uint4(0u, 0u, 0u, 0u);
-                        *reinterpret_cast<uint4 *>(vrow + kHalf + u * 16) = make_uint4(0u, 0u, 0u, 0u);
-                    }
+                    for (int u = 0; u < 8; ++u) *reinterpret_cast<uint4 *>(vrow + u * 16) = make_uint4(0u, 0u, 0u, 0u);
                 }
                 ptx::fence_proxy_async();
             }
@@ -379,13 +387,18 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             if (!wait_all(bar(kOFull), (nb - 1) & 1)) ok = false;
             tc_fence_after();
         }
+        // the row's sum: the two halves meet
+        float *pair_l = s_pair;
+        pair_l[kh2 * kTile + r] = l;
+        pair_sync();
+        const float lsum = pair_l[r] + pair_l[kTile + r];
         if (ok && nb > 0) {
-            const float inv = 1.0f / l;
-            float *dst = p.out + (static_cast<size_t>(row0 + (r < rows_here ? r : 0)) * p.nh + head) * kHd;
+            const float inv = 1.0f / lsum;
+            float *dst = p.out + (static_cast<size_t>(row0 + (r < rows_here ? r : 0)) * p.nh + head) * kHd + kh2 * 64;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {  // this warp's 64 dimensions of the row
                 uint32_t v[32];
-                tmem_ld32(tmem_base + lane_field + kColO + c * 32, v);
+                tmem_ld32(tmem_base + lane_field + kColO + kh2 * 64 + c * 32, v);
                 tmem_ld_wait();
                 if (r < rows_here) {
 #pragma unroll
@@ -400,7 +413,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     if (!ok && pos_ok && lane == 0) atomicExch(p.err_word, 5);
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
