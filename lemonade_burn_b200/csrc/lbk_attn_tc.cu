@@ -247,36 +247,44 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
                     kphase ^= 1;
                 }
             };
-            if (!wait_bar(bar(kKFull + 0), 0, s_abort)) ok = false;
-            if (ok) {
-                tc_fence_after();
-                issue_s();
-            }
-            for (int j = 0; j < nb && ok; ++j) {
-                if (j + 1 < nb) {
-                    // the threads hold block j's scores in registers: the score buffer is free
-                    if (!wait_bar(bar(kSFree), j & 1, s_abort) || !wait_bar(bar(kKFull + ks), kphase, s_abort)) {
-                        ok = false;
-                        break;
-                    }
-                    tc_fence_after();
-                    issue_s();
-                }
+            auto issue_pv = [&](int j) {  // O += Phi V + Plo V over the 8 steps of 16 keys: 8 columns of P, two 1024-byte key groups of V
                 const int vs = j & 1;
-                if (!wait_bar(bar(kPReady), j & 1, s_abort) || !wait_bar(bar(kVFull + vs), (j >> 1) & 1, s_abort)) {
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
                 const uint64_t v_desc = smem_desc_mn_sw128(base + kV0 + vs * kBlockBytes);
                 const uint32_t p_hi = tmem_base + kColP + (j & 1) * 128;
 #pragma unroll
                 for (int t = 0; t < 2; ++t)
 #pragma unroll
-                    for (int st = 0; st < 8; ++st)  // 16 keys a step: 8 columns of P, two 1024-byte key groups of V
+                    for (int st = 0; st < 8; ++st)
                         umma_f16_ts(tmem_base + kColO, p_hi + t * 64 + st * 8, v_desc + static_cast<uint64_t>(st * (2048 >> 4)), idesc_o, (j | t | st) ? 1u : 0u);
                 umma_commit(bar(kOFull));
                 umma_commit(bar(kVEmpty + vs));
+            };
+            // Every wait of this thread lets the tensor pipe run dry (its issue runs barely ahead of
+            // execution), so a turn of the loop waits once, for everything the next 32 MMAs need, and then
+            // issues P V of block j - 1 and Q K^T of block j + 1 back to back. P V goes first: Q K^T of
+            // block j is then always issued after P V of block j - 2, so scores of block j in the score
+            // buffer mean that the probability buffer of that parity has been read (the threads write
+            // block j's probabilities on that ground).
+            if (!wait_bar(bar(kKFull + 0), 0, s_abort)) ok = false;
+            if (ok) {
+                tc_fence_after();
+                issue_s();
+            }
+            for (int j = 0; j <= nb && ok; ++j) {
+                const bool has_pv = j > 0, has_s = j + 1 < nb;
+                if (!has_pv && !has_s) continue;
+                if (has_pv && (!wait_bar(bar(kPReady), (j - 1) & 1, s_abort) || !wait_bar(bar(kVFull + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort))) {
+                    ok = false;
+                    break;
+                }
+                // the threads hold block j's scores in registers: the score buffer is free
+                if (has_s && (!wait_bar(bar(kSFree), j & 1, s_abort) || !wait_bar(bar(kKFull + ks), kphase, s_abort))) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (has_pv) issue_pv(j - 1);
+                if (has_s) issue_s();
             }
         }
     } else {
