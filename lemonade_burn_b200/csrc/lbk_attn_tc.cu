@@ -130,7 +130,9 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
     volatile uint32_t *s_tmem = reinterpret_cast<volatile uint32_t *>(sm + kMisc);
     volatile int *s_abort = reinterpret_cast<volatile int *>(sm + kMisc + 4);
     auto bar = [&](int idx) { return bar0 + idx * 8; };
-    constexpr int kKFull = 0, kKEmpty = 3, kVFull = 6, kVEmpty = 8, kSFull = 10, kSFree = 11, kPReady = 12, kOFull = 13;
+    // kPReady and kOFull are pairs, one barrier per block parity: a wait for block j's completion can then never be
+    // answered by block j - 2's (a barrier's parity says which of two CONSECUTIVE phases completed, no more)
+    constexpr int kKFull = 0, kKEmpty = 3, kVFull = 6, kVEmpty = 8, kSFull = 10, kSFree = 11, kPReady = 12, kOFull = 14;
     if (tid == 0) {
         for (int s = 0; s < kKStages; ++s) {
             ptx::mbar_init(bar(kKFull + s), 1);
@@ -142,8 +144,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
         }
         ptx::mbar_init(bar(kSFull), 1);
         ptx::mbar_init(bar(kSFree), kSoftWarps);
-        ptx::mbar_init(bar(kPReady), kSoftWarps);
-        ptx::mbar_init(bar(kOFull), 1);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(bar(kPReady + i), kSoftWarps);
+            ptx::mbar_init(bar(kOFull + i), 1);
+        }
         *s_abort = 0;
         ptx::fence_barrier_init();
     }
@@ -256,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
 #pragma unroll
                     for (int st = 0; st < 8; ++st)
                         umma_f16_ts(tmem_base + kColO, p_hi + t * 64 + st * 8, v_desc + static_cast<uint64_t>(st * (2048 >> 4)), idesc_o, (j | t | st) ? 1u : 0u);
-                umma_commit(bar(kOFull));
+                umma_commit(bar(kOFull + (j & 1)));
                 umma_commit(bar(kVEmpty + vs));
             };
             // Every wait of this thread lets the tensor pipe run dry (its issue runs barely ahead of
@@ -273,7 +277,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             for (int j = 0; j <= nb && ok; ++j) {
                 const bool has_pv = j > 0, has_s = j + 1 < nb;
                 if (!has_pv && !has_s) continue;
-                if (has_pv && (!wait_bar(bar(kPReady), (j - 1) & 1, s_abort) || !wait_bar(bar(kVFull + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort))) {
+                if (has_pv && (!wait_bar(bar(kPReady + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort) || !wait_bar(bar(kVFull + ((j - 1) & 1)), ((j - 1) >> 1) & 1, s_abort))) {
                     ok = false;
                     break;
                 }
@@ -338,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
                 if (j > 0) {
                     // the output so far (P V of every earlier block) is complete and nothing adds to it before
                     // both warps of the quadrant say their probabilities are ready
-                    if (!wait_all(bar(kOFull), (j - 1) & 1)) {
+                    if (!wait_all(bar(kOFull + ((j - 1) & 1)), ((j - 1) >> 1) & 1)) {
                         ok = false;
                         continue;
                     }
@@ -389,10 +393,10 @@ __global__ void __launch_bounds__(kThreads, 1) attn_prompt_tc_kernel(const __gri
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(bar(kPReady));
+            if (lane == 0) ptx::mbar_arrive(bar(kPReady + (j & 1)));
         }
         if (ok && nb > 0) {
-            if (!wait_all(bar(kOFull), (nb - 1) & 1)) ok = false;
+            if (!wait_all(bar(kOFull + ((nb - 1) & 1)), ((nb - 1) >> 1) & 1)) ok = false;
             tc_fence_after();
         }
         // the row's sum: the two halves meet
