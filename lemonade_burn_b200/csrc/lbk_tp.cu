@@ -414,6 +414,93 @@ __global__ void __launch_bounds__(T) tp_norm_quant_kernel(const TpPtrs peers, in
     }
 }
 
+// The same for the many rows of a prompt pass when a row is too long for 256 threads' registers: the row's
+// values live in shared memory (4 bytes a column: 112 KB at 28672 columns, two blocks per SM; 56 KB at
+// half of that, three or four), the threads keep only their running sums, and 512 threads a block leave
+// room for several blocks per SM, so that one row's exchanges overlap another row's loads. Element by
+// element the arithmetic is tp_norm_quant_kernel's.
+constexpr int kNqSmemThreads = 512;
+template <int PRE>
+__global__ void __launch_bounds__(kNqSmemThreads) tp_norm_quant_smem_kernel(const TpPtrs peers, int world, int rank, const float *__restrict__ x,
+                                                                           const float *__restrict__ y, const float *__restrict__ w, int kl, int k_full,
+                                                                           float eps, int8_t *__restrict__ q, float *__restrict__ scale,
+                                                                           int32_t *__restrict__ sum, int *err_word, uint32_t wait_limit) {
+    constexpr int T = kNqSmemThreads;
+    extern __shared__ __align__(16) float4 s_row[];
+    __shared__ float s_red[T / 32];
+    __shared__ int s_redi[T / 32];
+    __shared__ float s_bcast;
+    ptx::pdl_trigger();
+    ptx::pdl_wait();
+    const int row = blockIdx.x, tid = threadIdx.x;
+    TpRegion *me = peers.r[rank];
+    const unsigned int seq = *reinterpret_cast<volatile unsigned int *>(&me->nq_seq);
+    const int par = seq & 1;
+    const int n4 = kl >> 2;
+    const float4 *xr = reinterpret_cast<const float4 *>(x + static_cast<size_t>(row) * kl);
+    const float4 *yr = y ? reinterpret_cast<const float4 *>(y + static_cast<size_t>(row) * kl) : nullptr;
+    float ss = 0.0f;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += T) {
+        const float4 a = xr[i];
+        float4 v;
+        if (PRE == LBK_PRE_RMS) {
+            v = a;
+        } else {
+            const float4 c = yr[i];
+            const float r0 = fmaxf(a.x, 0.f), r1 = fmaxf(a.y, 0.f), r2 = fmaxf(a.z, 0.f), r3 = fmaxf(a.w, 0.f);
+            v = make_float4(r0 * r0 * c.x, r1 * r1 * c.y, r2 * r2 * c.z, r3 * r3 * c.w);
+        }
+        s_row[i] = v;
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    }
+    ss = block_sum_f(ss, s_red, T / 32);
+    if (tid < 32) {
+        const float total = exchange_stat(peers, world, rank, par, 0, row, seq, ss, true, err_word, wait_limit);
+        if (tid == 0) s_bcast = 1.0f / sqrtf(total / static_cast<float>(k_full) + eps);
+    }
+    __syncthreads();
+    const float r = s_bcast;
+    float am = 0.0f;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += T) {
+        const float4 gw = __ldg(reinterpret_cast<const float4 *>(w) + i);
+        float4 v = s_row[i];
+        v = make_float4(v.x * r * gw.x, v.y * r * gw.y, v.z * r * gw.z, v.w * r * gw.w);
+        s_row[i] = v;
+        am = fmaxf(am, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    am = block_max_f(am, s_red, T / 32);
+    __syncthreads();  // s_bcast has been read by everybody
+    if (tid < 32) {
+        const float total = exchange_stat(peers, world, rank, par, 1, row, seq, am, false, err_word, wait_limit);
+        if (tid == 0) s_bcast = __fdiv_rn(127.0f, fmaxf(total, 1e-5f));
+    }
+    __syncthreads();
+    const float sc = s_bcast;
+    int8_t *qr = q + static_cast<size_t>(row) * kl;
+    int acc = 0;
+#pragma unroll 4
+    for (int i = tid; i < n4; i += T) {
+        const float4 v = s_row[i];
+        const int q0 = quant_one(v.x, sc), q1 = quant_one(v.y, sc), q2 = quant_one(v.z, sc), q3 = quant_one(v.w, sc);
+        acc += q0 + q1 + q2 + q3;
+        reinterpret_cast<uint32_t *>(qr)[i] = (q0 & 255) | ((q1 & 255) << 8) | ((q2 & 255) << 16) | (static_cast<uint32_t>(q3 & 255) << 24);
+    }
+    acc = block_sum_i(acc, s_redi, T / 32);
+    if (tid == 0) {
+        scale[row] = sc;
+        sum[row] = acc;
+        if (world == 1) return;
+        __threadfence();
+        if (atomicAdd(&me->nq_done, 1u) == gridDim.x - 1) {
+            me->nq_done = 0;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int *>(&me->nq_seq) = seq + 1;
+        }
+    }
+}
+
 struct RgArgs {
     int world, rank, m, hidden, mt;   // mt = ceil(m / world) tokens per rank
     int reduce;                       // 1: add all ranks' partial dots, scale, add to the residual; 0: the residual rows are the input
@@ -792,7 +879,22 @@ int lbk_tp_norm_quant(lbk_tp_comm *t, int pre, const float *x_dev, const float *
 #define LBK_NQ_LAUNCH(PRE, T)                                                                                                                            \
     LBK_CUDA(launch_chained(tp_norm_quant_kernel<PRE, T>, grid, dim3(T), 0, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev, static_cast<int>(k_local), \
                             static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit))
-    if (pre == LBK_PRE_RMS) {
+    if (m >= kTpManyRows && !small_blocks) {
+        // long rows of a prompt pass: the row in shared memory
+        const size_t smem = k_local * sizeof(float);
+        static bool attr_set = false;  // the same values for every call; setting them twice is harmless
+        if (!attr_set) {
+            LBK_CUDA(cudaFuncSetAttribute(tp_norm_quant_smem_kernel<LBK_PRE_RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kNqCache * kNqThreads * 16));
+            LBK_CUDA(cudaFuncSetAttribute(tp_norm_quant_smem_kernel<LBK_PRE_RELU2_MUL_RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, kNqCache * kNqThreads * 16));
+            attr_set = true;
+        }
+        if (pre == LBK_PRE_RMS)
+            LBK_CUDA(launch_chained(tp_norm_quant_smem_kernel<LBK_PRE_RMS>, grid, dim3(kNqSmemThreads), smem, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev, w_dev,
+                                    static_cast<int>(k_local), static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
+        else
+            LBK_CUDA(launch_chained(tp_norm_quant_smem_kernel<LBK_PRE_RELU2_MUL_RMS>, grid, dim3(kNqSmemThreads), smem, st, ptrs_of(tc), tc->world, tc->rank, x_dev, y_dev,
+                                    w_dev, static_cast<int>(k_local), static_cast<int>(k_full), eps, q_dev, scale_dev, sum_dev, tc->ctx->err_word, tc->wait_limit));
+    } else if (pre == LBK_PRE_RMS) {
         if (small_blocks) LBK_NQ_LAUNCH(LBK_PRE_RMS, 256);
         else LBK_NQ_LAUNCH(LBK_PRE_RMS, 1024);
     } else {

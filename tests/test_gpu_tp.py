@@ -300,6 +300,48 @@ def test_tp_decoder_step_with_one_rank(oracle, ctx, heads, kv):
         comm.close()
 
 
+@pytest.mark.parametrize("m,kl,pre", [(5, 1024, 1), (5, 12288, 3), (300, 1024, 1), (300, 2048, 3), (300, 12288, 1), (300, 12288, 3), (260, 28672, 3)])
+def test_sub_norm_quantise_block_forms(ctx, m, kl, pre):
+    """lbk_tp_norm_quant with one rank in its three forms: 1024 threads a row (decode batches), 256 threads
+    a row (256 rows and more, rows of at most 8192 columns) and the row in shared memory (256 rows and
+    more, longer rows), against a float64 restatement of the sub-norm (model.rs:358,363-364) and the
+    quantiser (quant.rs:100-118). The forms differ in the order of the sum of squares, so a code may
+    differ by one where the scaled value sits on a rounding boundary: at most 0.1 % of the codes, never
+    by more than one; scales to 1e-6."""
+    import torch
+    from lemonade_burn_b200 import _lib, tp
+    comm = tp.TpComm(ctx, 1, 0)
+    try:
+        lib = ctx._lib
+        g = torch.Generator().manual_seed(m * 7 + kl + pre)
+        x = torch.randn(m, kl, generator=g)
+        y = torch.randn(m, kl, generator=g) if pre == 3 else None
+        w = 1.0 + 0.1 * torch.randn(kl, generator=g)
+        xd, wd = x.cuda(), w.cuda()
+        yd = y.cuda() if y is not None else None
+        q8 = torch.empty((m, kl), dtype=torch.int8, device="cuda")
+        sc = torch.empty(m, device="cuda")
+        sm = torch.empty(m, dtype=torch.int32, device="cuda")
+        _lib.check(lib.lbk_tp_norm_quant(comm.handle, pre, C.c_void_p(xd.data_ptr()), C.c_void_p(yd.data_ptr()) if yd is not None else None,
+                                         C.c_void_p(wd.data_ptr()), m, kl, kl, C.c_float(1e-5), C.c_void_p(q8.data_ptr()), C.c_void_p(sc.data_ptr()),
+                                         C.c_void_p(sm.data_ptr()), C.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        torch.cuda.synchronize()
+        s = x.double() if pre == 1 else torch.clamp(x.double(), min=0) ** 2 * y.double()
+        r = 1.0 / torch.sqrt((s * s).mean(dim=1, keepdim=True) + 1e-5)
+        n = s * r * w.double()
+        scale = 127.0 / n.abs().amax(dim=1).clamp(min=1e-5)
+        qref = torch.clamp(torch.round(n * scale[:, None]), -128, 127)
+        got = q8.cpu().double()
+        diff = (got - qref).abs()
+        assert float(diff.max()) <= 1.0
+        assert float((diff != 0).double().mean()) < 1e-3
+        assert float(((sc.cpu().double() - scale) / scale).abs().max()) < 1e-6
+        assert torch.equal(sm.cpu().long(), q8.cpu().long().sum(dim=1))
+        ctx.check_device_error()
+    finally:
+        comm.close()
+
+
 def _tp_decoder_worker(rank, world, port, tmp, ok_q):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
