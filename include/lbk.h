@@ -265,6 +265,7 @@ int lbk_tp_reduce_scale(lbk_tp_comm *comm, const float *scale_dev, float wscale,
  * is added in rank order, which can differ from the single-GPU kernel's order in the last bit. */
 #define LBK_TP_NO_REDUCE 1
 #define LBK_TP_GATHER_F32 2
+#define LBK_TP_SCATTERED 4   /* the partial dots were stored by lbk_tp_gemm_scatter, not by lbk_ternary_gemm_dev */
 size_t lbk_tp_max_rows(void);
 size_t lbk_tp_max_width(void);
 size_t lbk_tp_max_f32_rows(void);
@@ -273,6 +274,12 @@ int lbk_tp_norm_quant(lbk_tp_comm *comm, int pre, const float *x_dev, const floa
                       size_t k_full, float eps, int8_t *q_dev, float *scale_dev, int32_t *sum_dev, void *stream);
 int lbk_tp_reduce_norm_gather(lbk_tp_comm *comm, int flags, const float *ascale_dev, float wscale, float *xres_dev, const float *w_dev,
                               float eps, size_t m, size_t hidden, float *y_out_dev, void *stream);
+/* The row-parallel projection fused with the first half of its exchange (17 .. lbk_tp_max_rows() token rows): the
+ * tcgen05 GEMM on this rank's column slice stores the int32 dots of every token row straight into the region of the
+ * rank that owns the row, tile by tile, from its epilogue (plain stores into peer memory; what
+ * lbk_ternary_gemm_dev + the peer loads of lbk_tp_reduce_norm_gather do in two steps). Follow it with
+ * lbk_tp_reduce_norm_gather(flags | LBK_TP_SCATTERED). The sums are the same integers either way. */
+int lbk_tp_gemm_scatter(lbk_tp_comm *comm, const lbk_weight *w, const int8_t *q_dev, const int32_t *sum_dev, size_t m, void *stream);
 const int8_t *lbk_tp_gather_q(lbk_tp_comm *comm);
 const float *lbk_tp_gather_scale(lbk_tp_comm *comm);
 const int32_t *lbk_tp_gather_sum(lbk_tp_comm *comm);

@@ -85,6 +85,7 @@ SYMBOLS = [
     ("lbk_tp_token_range", _i, [_vp, _sz, _vp, _vp]),
     ("lbk_tp_norm_quant", _i, [_vp, _i, _vp, _vp, _vp, _sz, _sz, _sz, _f, _vp, _vp, _vp, _vp]),
     ("lbk_tp_reduce_norm_gather", _i, [_vp, _i, _vp, _f, _vp, _vp, _f, _sz, _sz, _vp, _vp]),
+    ("lbk_tp_gemm_scatter", _i, [_vp, _vp, _vp, _vp, _sz, _vp]),
     ("lbk_tp_gather_q", _vp, [_vp]),
     ("lbk_tp_gather_scale", _vp, [_vp]),
     ("lbk_tp_gather_sum", _vp, [_vp]),

@@ -99,6 +99,9 @@ struct GemmParams {
     const float *qscale;
     const int32_t *qsum;
     int *err_word;
+    // matrix 0's int32 dots by token owner (see GroupArgs): rows of scatter_mt tokens per owner
+    int32_t *scatter[8];
+    int scatter_world, scatter_mt;
 };
 
 using namespace tc;
@@ -127,7 +130,9 @@ __device__ __forceinline__ void umma_i8_ts_block(uint32_t d_tmem, uint32_t a_tme
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate_first)
         : "memory");
 }
-template <int NT>
+// SC: matrix 0's int32 dots go to the token owners' buffers (GemmParams::scatter) instead of iout: an instantiation of its
+// own, so that the ordinary kernel's epilogue keeps its registers
+template <int NT, bool SC>
 __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant__ GemmParams p) {
     using C = Cfg<NT>;
     constexpr int G = C::kGroup, PG = C::kGroupStages, PS = C::kPackStages;
@@ -400,6 +405,24 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_kernel(const __grid_constant
                     sc[i] = s4.x; sc[i + 1] = s4.y; sc[i + 2] = s4.z; sc[i + 3] = s4.w;
                 }
                 tmem_ld_wait();
+                if constexpr (SC) {
+                    // The reduce-scatter of a row-parallel layer starts here: the int32 dots of a token go straight
+                    // into the buffer of the rank that owns the token (plain stores into peer memory, 128 consecutive
+                    // bytes per warp instruction), while the MMAs of the next tile run.
+                    if (row < rows) {
+                        const int tk = tok0 + c * 32;
+                        int o = tk / p.scatter_mt, lt = tk - o * p.scatter_mt;
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) {
+                            if (c * 32 + i < ntok) p.scatter[o][static_cast<size_t>(lt) * rows + row] = static_cast<int>(v[i]) - q[i];
+                            if (++lt == p.scatter_mt) {
+                                lt = 0;
+                                ++o;
+                            }
+                        }
+                    }
+                    continue;
+                }
                 if (p.ksplit > 1) {
                     // one of several parts of this tile: add the sums into the zeroed int32 buffer
                     // (the part that starts at block 0 also takes off sum(q)); a small kernel scales later
@@ -456,7 +479,8 @@ template <int NT>
 static int init_one(Ctx *ctx) {
     const size_t smem = Cfg<NT>::kTotal + 1024;
     if (smem > ctx->smem_optin) return fail(LBK_ERR_UNSUPPORTED, "gemm kernel needs %zu B of shared memory", smem);
-    LBK_CUDA(cudaFuncSetAttribute(gemm_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    LBK_CUDA(cudaFuncSetAttribute(gemm_kernel<NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
+    LBK_CUDA(cudaFuncSetAttribute(gemm_kernel<NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));
     return LBK_OK;
 }
 
@@ -551,6 +575,14 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     p.err_word = ctx->err_word;
     if (tiles == 0 || p.k_blocks == 0) return LBK_OK;
     p.ksplit = choose_ksplit(tiles, p.k_blocks, ctx->sm_count, &p.kb_part);
+    p.scatter_world = g.scatter_world;
+    p.scatter_mt = g.scatter_mt;
+    for (int i = 0; i < 8; ++i) p.scatter[i] = g.scatter_base[i];
+    if (g.scatter_world) {
+        if (g.n != 1 || g.scatter_mt < 1) return fail(LBK_ERR_INVALID, "gemm: scattered outputs take one matrix");
+        p.ksplit = 1;  // parts of a tile would have to add into peer memory
+        p.kb_part = p.k_blocks;
+    }
     if (p.ksplit > 1) {
         // int32 targets: the caller's integer outputs where given, else slices of the context's buffer
         size_t need = 0;
@@ -589,10 +621,12 @@ int launch_gemm(Ctx *ctx, const GroupArgs &g, cudaStream_t stream) {
     cfg.numAttrs = 1;
     if (nt > 64) {
         cfg.dynamicSmemBytes = Cfg<192>::kTotal + 1024;
-        LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<192>, p));
+        if (p.scatter_world) LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<192, true>, p));
+        else LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<192, false>, p));
     } else {
         cfg.dynamicSmemBytes = Cfg<64>::kTotal + 1024;
-        LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<64>, p));
+        if (p.scatter_world) LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<64, true>, p));
+        else LBK_CUDA(cudaLaunchKernelEx(&cfg, gemm_kernel<64, false>, p));
     }
     LBK_CUDA(cudaGetLastError());
     ctx->launches++;

@@ -85,6 +85,10 @@ struct GroupArgs {
     int32_t *iout[LBK_MAX_GROUP];
     int n = 0;
     size_t m = 0;
+    // tcgen05 GEMM only, one matrix: the int32 dots of token row t go to scatter_base[t / scatter_mt] at row
+    // t % scatter_mt instead of iout (the tensor-parallel layers: the bases are the token owners' buffers, peer memory)
+    int scatter_world = 0, scatter_mt = 0;
+    int32_t *scatter_base[8] = {};
     // exactly one of x (f32, quantised inside the kernel) or q/scale/sum is set
     const float *x = nullptr;
     const int8_t *q = nullptr;

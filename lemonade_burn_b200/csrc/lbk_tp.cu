@@ -503,7 +503,8 @@ __global__ void __launch_bounds__(kNqSmemThreads) tp_norm_quant_smem_kernel(cons
 
 struct RgArgs {
     int world, rank, m, hidden, mt;   // mt = ceil(m / world) tokens per rank
-    int reduce;                       // 1: add all ranks' partial dots, scale, add to the residual; 0: the residual rows are the input
+    int reduce;                       // 1: add all ranks' partial dots (read from their regions), scale, add to the residual; 2: the same, but the
+                                      // ranks' GEMMs have already stored their dots of this rank's tokens into THIS region ([source rank][mt][hidden]); 0: the residual rows are the input
     int gather_f32;                   // 1: gather the normalised f32 rows (head input) instead of int8 rows
     const float *ascale;              // [m] activation scales of the row-parallel GEMM's input (reduce = 1)
     float wscale;
@@ -568,7 +569,8 @@ __global__ void __launch_bounds__(T) tp_reduce_norm_gather_kernel(const TpPtrs p
                     for (int r = 0; r < kTpMaxWorld; ++r) {
                         d[r] = make_int4(0, 0, 0, 0);
                         if (r < world) {
-                            const int4 *src = reinterpret_cast<const int4 *>(peers.r[r]->partial + static_cast<size_t>(t) * H) + g;
+                            const int4 *src = a.reduce == 2 ? reinterpret_cast<const int4 *>(me->partial + (static_cast<size_t>(r) * a.mt + lt) * H) + g
+                                                            : reinterpret_cast<const int4 *>(peers.r[r]->partial + static_cast<size_t>(t) * H) + g;
                             asm volatile("ld.volatile.global.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(d[r].x), "=r"(d[r].y), "=r"(d[r].z), "=r"(d[r].w) : "l"(src));
                         }
                     }
@@ -911,7 +913,8 @@ int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev
                               size_t m, size_t hidden, float *y_out_dev, void *stream) {
     if (!t) return fail(LBK_ERR_INVALID, "tensor-parallel communicator is null");
     TpComm *tc = reinterpret_cast<TpComm *>(t);
-    const bool reduce = !(flags & LBK_TP_NO_REDUCE), f32 = (flags & LBK_TP_GATHER_F32) != 0;
+    const bool reduce = !(flags & LBK_TP_NO_REDUCE), f32 = (flags & LBK_TP_GATHER_F32) != 0, scattered = (flags & LBK_TP_SCATTERED) != 0;
+    if (scattered && !reduce) return fail(LBK_ERR_INVALID, "lbk_tp_reduce_norm_gather: LBK_TP_SCATTERED goes with a reduction");
     if (m == 0 || m > kTpMaxRows || (f32 && m > kTpGatherFRows))
         return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_reduce_norm_gather takes 1..%d token rows (%d when f32 rows are gathered), got %zu; every rank must take part", kTpMaxRows, kTpGatherFRows, m);
     if (hidden == 0 || hidden % 128 || hidden > kTpMaxWidth) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_reduce_norm_gather: rows of a multiple of 128 and at most %d columns (got %zu)", kTpMaxWidth, hidden);
@@ -925,7 +928,7 @@ int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev
     a.m = static_cast<int>(m);
     a.hidden = static_cast<int>(hidden);
     a.mt = static_cast<int>((m + tc->world - 1) / tc->world);
-    a.reduce = reduce ? 1 : 0;
+    a.reduce = reduce ? (scattered ? 2 : 1) : 0;
     a.gather_f32 = f32 ? 1 : 0;
     a.ascale = ascale_dev;
     a.wscale = wscale;
@@ -942,6 +945,34 @@ int lbk_tp_reduce_norm_gather(lbk_tp_comm *t, int flags, const float *ascale_dev
     LBK_CUDA(cudaGetLastError());
     tc->ctx->launches++;
     return LBK_OK;
+}
+
+// The row-parallel projection with the first half of its exchange inside: the tcgen05 GEMM on this rank's
+// column slice, whose epilogue stores the int32 dots of every token into the region of the rank that owns the
+// token (peer stores; [source rank][token of the owner][row]). lbk_tp_reduce_norm_gather with LBK_TP_SCATTERED
+// then adds up what arrived in its own region.
+int lbk_tp_gemm_scatter(lbk_tp_comm *t, const lbk_weight *w, const int8_t *q_dev, const int32_t *sum_dev, size_t m, void *stream) {
+    if (!t || !w) return fail(LBK_ERR_INVALID, "lbk_tp_gemm_scatter: null communicator or weight");
+    TpComm *tc = reinterpret_cast<TpComm *>(t);
+    const Weight *wt = reinterpret_cast<const Weight *>(w);
+    if (m < 17 || m > kTpMaxRows) return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_gemm_scatter takes 17..%d token rows (got %zu)", kTpMaxRows, m);
+    if (!q_dev || !sum_dev) return fail(LBK_ERR_INVALID, "lbk_tp_gemm_scatter: null q/sum");
+    const size_t mt = (m + tc->world - 1) / tc->world;
+    if (wt->rows > kTpMaxWidth || static_cast<size_t>(tc->world) * mt * wt->rows * sizeof(int32_t) > kTpPartialBytes)
+        return fail(LBK_ERR_UNSUPPORTED, "lbk_tp_gemm_scatter: %zu rows x %zu tokens do not fit the exchange buffer", static_cast<size_t>(wt->rows), m);
+    LBK_CUDA(cudaSetDevice(tc->ctx->device));
+    GroupArgs g;
+    g.w[0] = wt;
+    g.out[0] = nullptr;
+    g.iout[0] = nullptr;
+    g.n = 1;
+    g.m = m;
+    g.q = q_dev;
+    g.qsum = sum_dev;
+    g.scatter_world = tc->world;
+    g.scatter_mt = static_cast<int>(mt);
+    for (int o = 0; o < tc->world; ++o) g.scatter_base[o] = tc->region[o]->partial + static_cast<size_t>(tc->rank) * mt * wt->rows;
+    return launch_gemm(tc->ctx, g, static_cast<cudaStream_t>(stream));
 }
 
 const int8_t *lbk_tp_gather_q(lbk_tp_comm *t) { return t ? reinterpret_cast<TpComm *>(t)->region[reinterpret_cast<TpComm *>(t)->rank]->gather_q : nullptr; }

@@ -449,6 +449,20 @@ class TpBitNet:
             ip, k3 = _lib.ptr_array(iouts) if iouts else (None, None)
             chk(lib.lbk_ternary_gemm_dev(h, wp, len(lins), C.c_void_p(qp), C.c_void_p(sp) if sp else None, C.c_void_p(sump), m, op, ip, st))
 
+        # From 256 token rows on (a prompt pass) and with four ranks or more, a row-parallel projection stores its
+        # partial dots into the token owners' regions from its own epilogue (lbk_tp_gemm_scatter) and the exchange
+        # kernel adds up what arrived (measured at four ranks: exchange 19.4 -> 11.2 ms per 2048-token pass, the two
+        # projections 9.3 -> 16.8 ms, the pass 56.3 -> 55.4 ms; at two ranks the projections lose more than the
+        # exchange gains). Decode batches keep the GEMM that may split K over idle SMs and the exchange that pulls.
+        scatter = comm.world >= 4 and m >= 256
+        sflag = 4 if scatter else 0  # LBK_TP_SCATTERED
+
+        def row_parallel_gemm(lin):
+            if scatter:
+                chk(lib.lbk_tp_gemm_scatter(comm.handle, lin.handle, C.c_void_p(q8.data_ptr()), C.c_void_p(qsum.data_ptr()), m, st))
+            else:
+                gemm(q8.data_ptr(), None, qsum.data_ptr(), [lin], None, [comm.partial_ptr])
+
         def reduce_norm_gather(flags, ascale, wscale, gain):
             chk(lib.lbk_tp_reduce_norm_gather(comm.handle, flags, P(ascale) if ascale is not None else None, C.c_float(wscale), P(xres), P(gain),
                                               C.c_float(eps), m, H, None, st))
@@ -477,18 +491,18 @@ class TpBitNet:
             chk(lib.lbk_tp_norm_quant(comm.handle, 1, P(attn), None, P(l["attn_sub_norm"]), m, nh_l * hd, cfg.num_attention_heads * hd, C.c_float(eps),
                                       P(q8), P(qs), P(qsum), st))
             mark("sub-norm + quantise (statistics exchange)")
-            gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["o"]], None, [comm.partial_ptr])
+            row_parallel_gemm(l["o"])
             mark("o GEMM")
-            reduce_norm_gather(0, qs, l["o"].scale, l["post_attn_norm"])
+            reduce_norm_gather(sflag, qs, l["o"].scale, l["post_attn_norm"])
             mark("reduce-scatter + residual + norm + all-gather")
             gemm(self.gq, self.gs, self.gsum, [l["gate"], l["up"]], [g, u], None)
             mark("gate/up GEMM")
             chk(lib.lbk_tp_norm_quant(comm.handle, 3, P(g), P(u), P(l["ffn_sub_norm"]), m, il, I, C.c_float(eps), P(q8), P(qs), P(qsum), st))
             mark("sub-norm + quantise (statistics exchange)")
-            gemm(q8.data_ptr(), None, qsum.data_ptr(), [l["down"]], None, [comm.partial_ptr])
+            row_parallel_gemm(l["down"])
             mark("down GEMM")
             last = li + 1 == L
-            reduce_norm_gather(2 if last else 0, qs, l["down"].scale, self.final_norm if last else self.layers[li + 1]["input_norm"])
+            reduce_norm_gather((2 if last else 0) | sflag, qs, l["down"].scale, self.final_norm if last else self.layers[li + 1]["input_norm"])
             mark("reduce-scatter + residual + norm + all-gather")
         # the head: this rank's vocabulary rows of the tied embedding (model.rs:370-373), then the greedy token
         head_in = self.gf + (4 * H * (m - 1) if prompt else 0)

@@ -343,6 +343,14 @@ def test_sub_norm_quantise_block_forms(ctx, m, kl, pre):
 
 
 def _tp_decoder_worker(rank, world, port, tmp, ok_q):
+    try:
+        _tp_decoder_worker_body(rank, world, port, tmp, ok_q)
+    except BaseException as exc:  # the parent must hear of it at once, not after its queue timeout
+        ok_q.put((rank, False, f"{type(exc).__name__}: {exc}"))
+        raise
+
+
+def _tp_decoder_worker_body(rank, world, port, tmp, ok_q):
     sys.path.insert(0, str(ROOT))
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch
@@ -391,11 +399,42 @@ def _tp_decoder_worker(rank, world, port, tmp, ok_q):
             ok = ok and np.array_equal(y.cpu().numpy()[:cnt].view(np.uint32), wf[t0:t0 + cnt].view(np.uint32))
             ok = ok and torch.equal(xres[:cnt], y[:cnt])   # the residual rows started at zero
         ctx.check_device_error()
+        # (1b) the same projection with the first half of the exchange inside the GEMM (lbk_tp_gemm_scatter: the
+        # epilogue stores every token's partial dots into the owner's region) at 300 token rows, uneven ownership
+        # at three ranks included; the rows this rank owns must again be the oracle's bits
+        m2 = 300
+        packed, ws, x = _case(o, rows=1024, cols=1024 * world, m=m2, seed=9)
+        q, s, ssum = o.quantize_acts(x)
+        wf = o.simd_gemm_multi([packed], [ws], q, s, ssum)[0][0]
+        lc = 1024
+        sl, _ = tp.shard_cols(packed, 1024 * world, world, rank)
+        lin = ops.TernaryLinear(torch.from_numpy(np.ascontiguousarray(sl)).cuda(), float(ws), lc, ctx)
+        xl = torch.from_numpy(np.ascontiguousarray(x[:, rank * lc:(rank + 1) * lc])).cuda()
+        t2, c2 = tp.token_range(m2, world, rank)
+        for it in range(3):
+            q8 = torch.empty((m2, lc), dtype=torch.int8, device="cuda")
+            sc = torch.empty(m2, device="cuda")
+            sm = torch.empty(m2, dtype=torch.int32, device="cuda")
+            for r0 in (0, 150):  # lbk_tp_quantize takes 256 rows at most: two calls
+                _lib.check(lib.lbk_tp_quantize(comm.handle, C.c_void_p(xl.data_ptr() + 4 * r0 * lc), 150, lc, C.c_void_p(q8.data_ptr() + r0 * lc),
+                                               C.c_void_p(sc.data_ptr() + 4 * r0), C.c_void_p(sm.data_ptr() + 4 * r0), st))
+            _lib.check(lib.lbk_tp_gemm_scatter(comm.handle, lin.weight.handle, C.c_void_p(q8.data_ptr()), C.c_void_p(sm.data_ptr()), m2, st))
+            xres = torch.zeros((max(c2, 1), 1024), device="cuda")
+            y = torch.full((max(c2, 1), 1024), float("nan"), device="cuda")
+            gain = torch.ones(1024, device="cuda")
+            _lib.check(lib.lbk_tp_reduce_norm_gather(comm.handle, 4, C.c_void_p(sc.data_ptr()), C.c_float(float(ws)), C.c_void_p(xres.data_ptr()),
+                                                     C.c_void_p(gain.data_ptr()), C.c_float(1e-5), m2, 1024, C.c_void_p(y.data_ptr()), st))
+            torch.cuda.synchronize()
+            ok = ok and np.array_equal(y.cpu().numpy()[:c2].view(np.uint32), wf[t2:t2 + c2].view(np.uint32))
+        ctx.check_device_error()
         # (2) the whole decoder step against the oracle, from a full checkpoint sliced in Python and from
         # the native loader's shards of the file rank 0 wrote
         heads = 4 * world
         cfg = model.Config(heads * 128, 128 * 3 * world, heads, world, 2, 128 * world, 1e-5, 500000.0, 24)
         worst = _tp_decoder_case(ctx, comm, world, rank, cfg, seed=12, b=5, steps=3, prompt_len=11)
+        # a prompt pass of 300 rows: the scattering GEMM, the 256-thread exchange kernels, the tcgen05 attention
+        long_cfg = model.Config(heads * 128, 128 * 3 * world, heads, world, 2, 128 * world, 1e-5, 500000.0, 320)
+        worst = max(worst, _tp_decoder_case(ctx, comm, world, rank, long_cfg, seed=13, b=1, steps=1, prompt_len=300))
         if rank == 0:
             model.save_checkpoint(tmp, cfg, model.random_checkpoint(cfg, 12))
         dist.barrier()
@@ -426,9 +465,15 @@ def test_tp_decoder_ranks_match_oracle(tmp_path):
     procs = [mpc.Process(target=_tp_decoder_worker, args=(r, world, port, str(tmp_path), ok_q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [ok_q.get(timeout=600) for _ in procs]
+    res = []
+    for _ in procs:
+        res.append(ok_q.get(timeout=600))
+        if not res[-1][1]:  # a rank failed: the others would only wait for it
+            for p in procs:
+                p.terminate()
+            break
+    assert all(ok for _, ok, _ in res), res
     for p in procs:
         p.join(timeout=120)
         assert p.exitcode == 0
-    assert all(ok for _, ok, _ in res), res
     print("tensor-parallel decoder, worst relative logit deviation per rank:", [(r, w) for r, _, w in res])
