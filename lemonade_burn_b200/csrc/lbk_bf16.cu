@@ -3,7 +3,9 @@
 // Replaces bf16_gemv / dot_scalar / dot_avx2 / dot_avx512 (crates/lb-ternary/src/bf16.rs:14-105)
 // and the bf16_linear op above them (crates/lb-model/src/ops.rs:199-218):
 // out[t, r] = sum_k x[t, k] * bf16(W[r, k]), f32 products and f32 accumulation.
-// HBM-bound: W (rows*cols*2 bytes) is read once per group of up to kTok token rows.
+// HBM-bound: W (rows*cols*2 bytes) is read once per pass: one token row on the FMA kernel, up to
+// 64 rows per pass on tcgen05 (bf16_head_kernel below), up to kTok = 4 rows per pass on the FMA
+// kernel for rows that are not whole 16-byte units.
 // Summation order differs from the reference's 8-lane order, so results agree to rounding,
 // not bit for bit (the reference allows 1e-4 absolute, bf16.rs:113-136).
 #include "lbk_internal.cuh"
