@@ -8,7 +8,8 @@
 // (D[row][token] in TMEM). Per 128-column block of K (one packed 32-byte block per weight row):
 //
 //   2 TMA threads  int8 activations [NT tok][128 B] (SWIZZLE_128B, the K-major B operand) and
-//                  packed weights [128 rows][32 B] into shared-memory rings of their own
+//                  packed weights [128 rows][128 B] (four K blocks a box) into shared-memory rings
+//                  of their own
 //   2 x 4 expander thread r owns weight row r = TMEM lane r: 32 packed bytes -> 32 words of u8
 //   warps          codes, word c = columns 4c..4c+3 = (packed word >> 2k) & 0x03030303; the two
 //                  sets of four warps take alternate K blocks (one set alone was the bottleneck)
@@ -23,7 +24,8 @@
 //                  consecutive weight rows, so every store instruction writes 128 contiguous bytes
 //
 // TMEM columns: two accumulators of NT columns (the epilogue of one tile overlaps the MMAs of the
-// next) + a 4-deep ring of 32-column weight tiles. Bound: int8 tensor pipe; 2*m*rows*cols ops.
+// next) + a ring of 32-column weight tiles, two hand-off groups deep (4 tiles at NT = 192, 8 at
+// NT = 64). Bound: int8 tensor pipe; 2*m*rows*cols ops.
 #include "lbk_internal.cuh"
 #include "lbk_ptx.cuh"
 #include "lbk_tcgen05.cuh"
