@@ -99,7 +99,8 @@ def test_shard_helpers_reject_bad_cuts():
 
 def _token_sharded_worker(rank, world, port, q_out):
     """The token-sharded form of a row-parallel layer on CPU ranks: int32 partial dots of the column
-    slices, reduce-scatter by token rows (here: integer all-reduce, then the owner keeps its rows),
+    slices, reduce-scatter by token rows (here: integer all-reduce, then the owner keeps its rows; and
+    the scattering form, where every source rank delivers the owner's rows into the owner's buffer),
     scale epilogue + residual on the owner, all-gather of the owners' rows. Uneven ownership (5 tokens
     over 2 ranks, 3 over 4 with an empty rank) included."""
     sys.path.insert(0, str(ROOT))
@@ -126,8 +127,22 @@ def _token_sharded_worker(rank, world, port, q_out):
             ql = np.ascontiguousarray(q[:, rank * lc:(rank + 1) * lc])          # every rank quantises with the whole row's scale
             lsum = ql.astype(np.int32).sum(axis=1).astype(np.int32)
             part = torch.from_numpy(o.ternary_gemm_i32(np.ascontiguousarray(sl), lc, ql, lsum))
+            own_part = part.clone()
             dist.all_reduce(part, op=dist.ReduceOp.SUM)
             t0, cnt = tp.token_range(m, world, rank)
+            # the scattering form of the same exchange (the projection's epilogue stores a token row's dots
+            # straight into its owner's buffer, laid out [source rank][token of the owner][row]): what an
+            # owner finds in its buffer, added up over the source ranks in any order, is the all-reduce's rows
+            mt_s = (m + world - 1) // world
+            send = torch.zeros((world, mt_s, rows), dtype=torch.int32)
+            for owner in range(world):
+                o0, oc = tp.token_range(m, world, owner)
+                send[owner, :oc] = own_part[o0:o0 + oc]
+            got = [torch.empty_like(send) for _ in range(world)]
+            dist.all_gather(got, send)
+            arrived = torch.stack([got[src][rank] for src in range(world)])  # [source rank][token][row] in MY buffer
+            summed = arrived.flip(0).sum(dim=0, dtype=torch.int32)
+            ok = ok and torch.equal(summed[:cnt], part[t0:t0 + cnt])
             inv = (np.float32(1.0) / (s * wscale)).astype(np.float32)
             mine = (resid[t0:t0 + cnt] + part.numpy()[t0:t0 + cnt].astype(np.float32) * inv[t0:t0 + cnt, None]).astype(np.float32)
             mt = (m + world - 1) // world
