@@ -48,6 +48,24 @@ def test_layout_helpers_and_errors_without_gpu(lib):
         assert b"CUDA" in lib.lbk_last_error() or b"device" in lib.lbk_last_error()
 
 
+def test_header_is_plain_c_and_a_c_program_links(lib, tmp_path):
+    """The boundary is a C ABI: include/lbk.h compiles as C99 with -pedantic (no C++ in the signatures), and
+    a C program (tests/abi_c_client.c) links against liblbk.so and gets status codes and messages."""
+    import shutil
+    import subprocess
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no gcc")
+    inc = ROOT / "include"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", "-fsyntax-only", "-x", "c", str(inc / "lbk.h")], check=True)
+    libdir = ROOT / "lemonade_burn_b200"
+    exe = tmp_path / "abi_c_client"
+    subprocess.run([gcc, "-std=c99", "-Wall", "-Wextra", "-Werror", "-pedantic", f"-I{inc}", "-o", str(exe), str(ROOT / "tests" / "abi_c_client.c"),
+                    f"-L{libdir}", "-llbk", f"-Wl,-rpath,{libdir}"], check=True)
+    res = subprocess.run([str(exe)], stdout=subprocess.PIPE, text=True, timeout=120)
+    assert res.returncode == 0 and "C client ok" in res.stdout, res.stdout
+
+
 def test_missing_library_is_an_error(monkeypatch, tmp_path):
     """No fallback: a missing liblbk.so must raise, not route anywhere else."""
     from lemonade_burn_b200 import _lib
